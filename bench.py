@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Headline benchmark: quantized-GEMV weight bandwidth on the Qwen3-0.6B MLX 4-bit decode step.
+
+One step = every linear projection one decode token needs, on random-init weights of the
+Qwen3-0.6B architecture in MLX 4-bit g64 form: per layer q|k|v (one launch, shared x), o,
+gate|up (one launch, shared x), down — 28 layers — then the tied 151936x1024 LM head.
+113 launches, 197 matrices, 335 MB of packed weights per step (larger than L2, so every
+step streams them from HBM again).  Data is synthetic and seeded.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (see DESIGN.md for the fields).  `value` is GB/s of algorithmic bytes
+with inputs resident in HBM; `e2e` is the same step with the activations copied from pinned
+host memory and the logits copied back inside the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_package  # noqa: E402
+
+HIDDEN, LAYERS, VOCAB, FFN, QDIM, KVDIM, GS = 1024, 28, 151936, 3072, 2048, 1024, 64
+# (name, [(out_dim, in_dim) of the weights that share one x])
+LAYER_OPS = [("qkv", [(QDIM, HIDDEN), (KVDIM, HIDDEN), (KVDIM, HIDDEN)]),
+             ("o", [(HIDDEN, QDIM)]),
+             ("gate_up", [(FFN, HIDDEN), (FFN, HIDDEN)]),
+             ("down", [(HIDDEN, FFN)])]
+WORKLOAD = "qwen3-0.6b mlx4-g64 decode-step projections (28 layers x q|k|v,o,gate|up,down + LM head 151936x1024)"
+
+
+def algorithmic_bytes(out_dim, in_dim, batch=1):
+    """0.5625 B per weight (4-bit nibble + bf16 scale and bias per 64) + bf16-valued x + f32 out."""
+    return out_dim * in_dim * 0.5625 + batch * in_dim * 2 + batch * out_dim * 4
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.Q,
+                                       "--format=csv,noheader,nounits", "-lms", "100"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.p is not None:
+            self.p.terminate()
+            try:
+                self.p.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            c = [t.strip() for t in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.f.close()
+        os.unlink(self.f.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def shard_rows(out_dim, rank, world):
+    """Rows [lo, hi) of a projection owned by `rank`: contiguous, split on multiples of 8 rows."""
+    per = (out_dim // 8 + world - 1) // world * 8
+    lo = min(out_dim, rank * per)
+    return lo, min(out_dim, lo + per)
+
+
+class DecodeStepProjections:
+    """Weights, activations and the launch list of one decode step, (row-sharded for world > 1)."""
+
+    def __init__(self, rt, syn, rank=0, world=1, layers=LAYERS):
+        import torch
+        self.rt, self.torch, self.rank, self.world = rt, torch, rank, world
+        self.ops = []  # (name, [handles], x_tensor, [out_tensors], [(out_dim_shard, in_dim)], [full out_dim])
+        self.weight_bytes = 0
+        self.bytes_per_step = 0.0
+        ops = [(l, n, shapes) for l in range(layers) for n, shapes in LAYER_OPS] + [(layers, "lm_head", [(VOCAB, HIDDEN)])]
+        for l, name, shapes in ops:
+            in_dim = shapes[0][1]
+            x = torch.from_numpy(syn.activations(("x", l, name), in_dim)).cuda()
+            hs, outs, dims = [], [], []
+            for i, (out_dim, _) in enumerate(shapes):
+                # every layer of a random-init model has its own weights; generation is the slow
+                # part on the host, so layers draw from 4 distinct seeds (contents never repeat in L2:
+                # the copies are separate device buffers)
+                w, s, b = syn.mlx_weight((name, i, l % 4), out_dim, in_dim, GS)
+                lo, hi = shard_rows(out_dim, rank, world)
+                wpr, gpr = in_dim // 8, in_dim // GS
+                h = rt.UploadMLXWeight(w[lo * wpr:hi * wpr], s[lo * gpr:hi * gpr], b[lo * gpr:hi * gpr],
+                                       in_dim, hi - lo, GS, True)
+                hs.append(h)
+                outs.append(torch.empty(hi - lo, dtype=torch.float32, device="cuda"))
+                dims.append((hi - lo, in_dim))
+                self.weight_bytes += h.ResidentBytes()
+                self.bytes_per_step += algorithmic_bytes(hi - lo, in_dim)
+            self.ops.append((name, hs, x, outs, dims))
+        self.launches_per_step = len(self.ops)
+        self.logits = self.ops[-1][3][0]
+        if world > 1:
+            self.gathered = [[torch.empty(world * o.numel(), dtype=torch.float32, device="cuda") for o in op[3]]
+                             for op in self.ops]
+
+    def _launch(self, op, stream):
+        rt = self.rt
+        _, hs, x, outs, _ = op
+        xb = rt.wrap(x.data_ptr(), x.numel() * 4)
+        obs = [rt.wrap(o.data_ptr(), o.numel() * 4) for o in outs]
+        if len(hs) == 1:
+            rt.GemvMLX(obs[0], xb, hs[0], stream)
+        else:
+            rt.GemmMLXMulti(obs, xb, hs, 1, stream)
+
+    def step(self, stream, gather=True):
+        for k, op in enumerate(self.ops):
+            self._launch(op, stream)
+            if self.world > 1 and gather:
+                import torch.distributed as dist
+                for o, g in zip(op[3], self.gathered[k]):
+                    dist.all_gather_into_tensor(g, o)
+
+    def timed_launches(self, stream):
+        """One eager pass with events around every launch: [(name, bytes, ms)]."""
+        torch = self.torch
+        evs = []
+        for op in self.ops:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            self._launch(op, stream)
+            b.record(stream)
+            evs.append((op[0], sum(algorithmic_bytes(o, i) for o, i in op[4]), a, b))
+        torch.cuda.synchronize()
+        return [(n, by, a.elapsed_time(b)) for n, by, a, b in evs]
+
+
+def cpu_step(orc, syn, nthreads, layers):
+    """The same projections through the CPU oracle (mlx.GemvParallel order); returns bytes done."""
+    done = 0.0
+    ops = [(n, shapes) for _ in range(layers) for n, shapes in LAYER_OPS]
+    for name, shapes in ops:
+        in_dim = shapes[0][1]
+        if name not in cpu_step.cache:
+            cpu_step.cache[name] = syn.activations(("x", 0, name), in_dim)
+        x = cpu_step.cache[name]
+        for i, (out_dim, _) in enumerate(shapes):
+            if (name, i) not in cpu_step.cache:
+                cpu_step.cache[(name, i)] = syn.mlx_weight((name, i, 0), out_dim, in_dim, GS)
+            w, s, b = cpu_step.cache[(name, i)]
+            orc.mlx_gemv(x, w, s, b, out_dim, in_dim, GS, nthreads=nthreads)
+            done += algorithmic_bytes(out_dim, in_dim)
+    return done
+
+
+cpu_step.cache = {}
+
+
+def time_cpu(orc, syn, steps, warmup, layers):
+    """Times the oracle on all host cores over `layers` layers of the step per repetition."""
+    n = os.cpu_count() or 1
+    for _ in range(max(1, warmup)):
+        cpu_step(orc, syn, n, layers)
+    t0 = time.perf_counter()
+    total = 0.0
+    for _ in range(steps):
+        total += cpu_step(orc, syn, n, layers)
+    dt = time.perf_counter() - t0
+    return total / dt / 1e9, dt / steps * 1e3, n
+
+
+def run_reference(args):
+    """The reference's CPU path for this workload (its Go code cannot be built here: no Go
+    toolchain), restated in oracle/ and run on all host cores.  Each step is a bounded sample:
+    4 of the 28 layers (the layers are identical in shape), without the LM head."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    syn = load_package().synth
+    from oracle import binding as orc
+    layers = 4
+    gbs, ms, cores = time_cpu(orc, syn, args.steps, args.warmup, layers)
+    sample = "%d of 28 layers x 7 projections per step (%.1f MB of packed weights), mlx.GemvParallel order" % (
+        layers, layers * 8.85)
+    print(json.dumps({
+        "impl": "reference", "metric": "quant_gemv_weight_bandwidth", "value": round(gbs, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "timing": "wall clock, host cores"},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def run_ours(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        world = int(os.environ.get("WORLD_SIZE", str(1)))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(local)
+    wl = DecodeStepProjections(rt, syn, rank, world)
+    stream = torch.cuda.Stream()
+    hbm_peak, peak_kind = peaks()
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput: the step replayed as a CUDA graph -------------------
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            wl.step(stream)
+    torch.cuda.synchronize()
+    graph = None
+    if args.graph and world == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            wl.step(torch.cuda.current_stream())
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def run_steps(k):
+        if graph is not None:
+            for _ in range(k):
+                graph.replay()
+        else:
+            with torch.cuda.stream(stream):
+                for _ in range(k):
+                    wl.step(stream)
+
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    rec_stream = torch.cuda.current_stream() if graph is not None else stream
+    ev0.record(rec_stream)
+    run_steps(args.steps)
+    ev1.record(rec_stream)
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    # keep the GPU busy a little longer so the clock sampler sees the loaded state
+    t_end = time.time() + 1.0
+    while time.time() < t_end:
+        run_steps(20)
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler else None
+
+    # ---- eager launches (no graph), for comparison --------------------------------------
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    with torch.cuda.stream(stream):
+        for _ in range(args.steps):
+            wl.step(stream)
+    e1.record(stream)
+    barrier()
+    ms_eager = e0.elapsed_time(e1)
+
+    # ---- end to end: activations from pinned host memory, logits back -------------------
+    xs_host = [torch.from_numpy(syn.activations(("x", 0, op[0]), op[2].numel())).pin_memory() for op in wl.ops]
+    logits_host = torch.empty(wl.logits.numel(), dtype=torch.float32).pin_memory()
+    h2d = sum(x.numel() * 4 for x in xs_host)
+    d2h = logits_host.numel() * 4
+
+    def e2e_step():
+        for op, xh in zip(wl.ops, xs_host):
+            op[2].copy_(xh, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+        else:
+            wl.step(torch.cuda.current_stream())
+        logits_host.copy_(wl.logits, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    barrier()
+    ms_e2e = (time.perf_counter() - t0) * 1e3
+
+    # ---- per-launch durations for the roofline of the GEMV kernel -----------------------
+    with torch.cuda.stream(stream):
+        per = []
+        for _ in range(3):
+            per = wl.timed_launches(stream)
+    k_bytes = sum(b for _, b, _ in per)
+    k_ms = sum(t for _, _, t in per)
+    lm = [p for p in per if p[0] == "lm_head"][0]
+
+    # max over ranks
+    times = torch.tensor([ms_total, ms_eager, ms_e2e], dtype=torch.float64, device="cuda")
+    total_bytes = torch.tensor([wl.bytes_per_step], dtype=torch.float64, device="cuda")
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
+    ms_total, ms_eager, ms_e2e = [float(t) for t in times.cpu()]
+    job_bytes = float(total_bytes.cpu()[0])
+
+    if rank == 0:
+        gbs = job_bytes * args.steps / (ms_total * 1e-3) / 1e9
+        achieved = k_bytes / (k_ms * 1e-3) / 1e9
+        line = {
+            "metric": "quant_gemv_weight_bandwidth", "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_total / args.steps, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "batch": 1, "launch": "cuda graph replay" if graph is not None else "eager",
+                       "l2": "inputs larger than L2 (335 MB of weights per step vs 126 MB L2)",
+                       "parallelism": "row-sharded x%d + all-gather" % world if world > 1 else "single GPU"},
+            "decode_tok_s_projections_only": round(args.steps / (ms_total * 1e-3), 1),
+            "eager": {"value": round(job_bytes * args.steps / (ms_eager * 1e-3) / 1e9, 2), "unit": "GB/s",
+                      "ms_per_step": round(ms_eager / args.steps, 4)},
+            "e2e": {"value": round(job_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 2), "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": round(ms_e2e / args.steps, 4)},
+            "gpu_launches": wl.launches_per_step * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "mlx_gemv_kernel (all %d launches of a step, eager, CUDA events around each)" % len(per),
+                         "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                         "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind, "traffic": None,
+                         "lm_head_launch": {"bytes": lm[1], "ms": round(lm[2], 5),
+                                            "achieved": round(lm[1] / (lm[2] * 1e-3) / 1e9, 1),
+                                            "frac": round(lm[1] / (lm[2] * 1e-3) / 1e9 / hbm_peak, 4)}},
+            "clocks": clocks,
+        }
+        if not args.no_cpu and world == 1:
+            from oracle import binding as orc
+            gbs_cpu, ms_cpu, cores = time_cpu(orc, syn, 3, 1, 4)
+            line["cpu_baseline"] = {"value": round(gbs_cpu, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                                    "sample": "3 repetitions of 4 of the 28 layers x 7 projections (35 MB of packed "
+                                              "weights each), oracle restatement of mlx.GemvParallel"}
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--graph", type=int, default=1)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

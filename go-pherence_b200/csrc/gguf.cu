@@ -1,0 +1,386 @@
+// GGUF Q8_0 and Q4_K matrices: upload (device re-layout), bit-exact dequantisation and the
+// dequant-fused GEMV / small-batch projection.
+//
+// Replaces gemv_q8_0(_batch), gemv_q4_k(_batch), gemm_q4_raw_f32 and friends
+// (backends/nvidia/ptx/q8, ptx/q4) behind GPUGGUFMatrix.ProjectBatchToBuffer,
+// GemvQ4K*/GemvQ8_0* (backends/nvidia/runtime/gguf_matrix.go:121-135, q4k.go:351-595,
+// q8.go:225-301).  Arithmetic specification: dequantRowQ8_0To / dequantRowQ4KTo
+// (loader/gguf/quant_matrix.go:138-158, :281-329) followed by an f32 dot with x
+// (model/gguf_llama.go:626-685); activations stay f32.
+//
+// Device layouts (same byte count as the GGUF stream, chosen so a lane's 16-byte unit is a
+// run of consecutive elements with one scale):
+//   Q4_K  144-byte super-block = 16-byte header {f16 d, f16 dmin, 8 x 12-bit (sc | m<<6)}
+//         + 8 x 16 bytes; sub-block s in bytes [16s,16s+16), element 2i in the low nibble
+//         of byte i, element 2i+1 in the high nibble.
+//   Q8_0  plane of (q + 128) bytes [out][in], then f16 d [out][in/32].
+#include <string.h>
+
+#include "stream_gemv.cuh"
+
+namespace goph {
+
+// ---- Q4_K ---------------------------------------------------------------------------
+
+__device__ __forceinline__ float f16_bits_to_f32(uint32_t h) {
+  return __half2float(__ushort_as_half((unsigned short)h));
+}
+
+// The 12-bit field of sub-block s out of the 96-bit string (y,z,w).
+__device__ __forceinline__ uint32_t q4k_field(uint4 h, int s) {
+  int bit = 12 * s, wi = bit >> 5, sh = bit & 31;
+  uint32_t lo = wi == 0 ? h.y : wi == 1 ? h.z : h.w;
+  uint32_t hi = wi == 0 ? h.z : wi == 1 ? h.w : 0u;
+  return __funnelshift_r(lo, hi, sh) & 0xFFFu;
+}
+
+struct Q4KFmt {
+  static constexpr int kSlots = 8;  // 32 elements per unit
+  static constexpr bool kHasConsts = true;
+  struct Row {
+    uint4 q;
+    float sd, md;  // sc*d and m*dmin, each rounded to f32 as the reference does
+  };
+  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
+    const uint8_t* blk = a.w + (size_t)row * a.row_bytes + (size_t)(unit >> 3) * 144;
+    int s = unit & 7;
+    uint4 h = __ldg(reinterpret_cast<const uint4*>(blk));
+    t.q = ld_stream(reinterpret_cast<const uint4*>(blk + 16 + 16 * s));
+    uint32_t f = q4k_field(h, s);
+    t.sd = __fmul_rn((float)(f & 63u), f16_bits_to_f32(h.x & 0xFFFFu));
+    t.md = __fmul_rn((float)(f >> 6), f16_bits_to_f32(h.x >> 16));
+  }
+  // One shift serves two nibbles: odd positions read as 16+n, even positions as 256+n.
+  static __device__ __forceinline__ float2 consts(float se, float so) {
+    return make_float2(256.f * se + 16.f * so, se + so);
+  }
+  template <int M>
+  static __device__ __forceinline__ void dot(const Row& t, const float4 (&xv)[M][8], const float2 (&c)[M],
+                                             float (&acc)[M]) {
+    float2 F[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) F[m] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t w = k == 0 ? t.q.x : k == 1 ? t.q.y : k == 2 ? t.q.z : t.q.w;
+      constexpr uint32_t MA = 0x00780000u, EA = 0x41800000u, MB = 0x00078000u, EB = 0x43800000u;
+      uint32_t t0 = w << 15, t1 = w << 7, t2 = w >> 1, t3 = w >> 9;
+      float2 f0 = make_float2(__uint_as_float((t0 & MB) | EB), __uint_as_float((t0 & MA) | EA));
+      float2 f1 = make_float2(__uint_as_float((t1 & MB) | EB), __uint_as_float((t1 & MA) | EA));
+      float2 f2 = make_float2(__uint_as_float((t2 & MB) | EB), __uint_as_float((t2 & MA) | EA));
+      float2 f3 = make_float2(__uint_as_float((t3 & MB) | EB), __uint_as_float((t3 & MA) | EA));
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float4 xa = xv[m][2 * k], xb = xv[m][2 * k + 1];
+        fma2(F[m], f0, make_float2(xa.x, xa.y));
+        fma2(F[m], f1, make_float2(xa.z, xa.w));
+        fma2(F[m], f2, make_float2(xb.x, xb.y));
+        fma2(F[m], f3, make_float2(xb.z, xb.w));
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float d = (F[m].x + F[m].y) - c[m].x;
+      acc[m] = fmaf(t.sd, d, acc[m]);
+      acc[m] = fmaf(-t.md, c[m].y, acc[m]);
+    }
+  }
+  static __device__ __forceinline__ float finish(const StreamArgs&, int, float v) { return v; }
+};
+
+// GGUF super-block → device super-block, one thread per block.
+__global__ void q4k_relayout_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ dst, size_t nblocks) {
+  size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const uint8_t* s = raw + b * 144;
+  uint8_t* o = dst + b * 144;
+  o[0] = s[0];
+  o[1] = s[1];
+  o[2] = s[2];
+  o[3] = s[3];
+  const uint8_t* sc = s + 4;
+  uint32_t field[8];
+  for (int j = 0; j < 4; ++j) field[j] = (uint32_t)(sc[j] & 63) | ((uint32_t)(sc[j + 4] & 63) << 6);
+  for (int j = 4; j < 8; ++j) {
+    int k = j - 4;
+    uint32_t scv = (sc[j + 4] & 0xF) | ((sc[k] >> 6) << 4);
+    uint32_t mv = (sc[j + 4] >> 4) | ((sc[k + 4] >> 6) << 4);
+    field[j] = scv | (mv << 6);
+  }
+  uint32_t words[3] = {0, 0, 0};
+  for (int j = 0; j < 8; ++j) {
+    int bit = 12 * j, wi = bit >> 5, sh = bit & 31;
+    words[wi] |= field[j] << sh;
+    if (sh > 20) words[wi + 1] |= field[j] >> (32 - sh);
+  }
+  for (int i = 0; i < 12; ++i) o[4 + i] = (uint8_t)(words[i >> 2] >> (8 * (i & 3)));
+  const uint8_t* qs = s + 16;
+  for (int sb = 0; sb < 8; ++sb) {
+    const uint8_t* q = qs + (sb >> 1) * 32;
+    int hi = sb & 1;
+    for (int i = 0; i < 16; ++i) {
+      uint8_t e0 = hi ? (q[2 * i] >> 4) : (q[2 * i] & 0xF);
+      uint8_t e1 = hi ? (q[2 * i + 1] >> 4) : (q[2 * i + 1] & 0xF);
+      o[16 + 16 * sb + i] = e0 | (e1 << 4);
+    }
+  }
+}
+
+// dequantRowQ4KTo from the device layout: (sc*d)*q - (m*dmin), every step rounded.
+__global__ void q4k_dequant_kernel(const uint8_t* __restrict__ w, float* __restrict__ out, size_t nunits) {
+  size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (u >= nunits) return;
+  const uint8_t* blk = w + (u >> 3) * 144;
+  int s = (int)(u & 7);
+  uint4 h = *reinterpret_cast<const uint4*>(blk);
+  uint4 q = *reinterpret_cast<const uint4*>(blk + 16 + 16 * s);
+  uint32_t f = q4k_field(h, s);
+  float sd = __fmul_rn((float)(f & 63u), f16_bits_to_f32(h.x & 0xFFFFu));
+  float md = __fmul_rn((float)(f >> 6), f16_bits_to_f32(h.x >> 16));
+  float4* o = reinterpret_cast<float4*>(out + u * 32);
+  uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fsub_rn(__fmul_rn(sd, (float)((ws[k] >> (4 * e)) & 0xF)), md);
+    o[2 * k] = make_float4(v[0], v[1], v[2], v[3]);
+    o[2 * k + 1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+// ---- Q8_0 ---------------------------------------------------------------------------
+
+struct Q80Fmt {
+  static constexpr int kSlots = 4;  // 16 elements per unit
+  static constexpr bool kHasConsts = true;
+  struct Row {
+    uint4 q;
+    float d;
+  };
+  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
+    t.q = ld_stream(reinterpret_cast<const uint4*>(a.w + (size_t)row * a.in_dim) + unit);
+    const uint16_t* d16 = reinterpret_cast<const uint16_t*>(a.aux);
+    t.d = f16_bits_to_f32(__ldg(d16 + (size_t)row * (a.in_dim / 32) + (unit >> 1)));
+  }
+  // A stored byte u = q+128 placed on mantissa bits 15..22 under 2^8 reads as 256+u = 384+q.
+  static __device__ __forceinline__ float2 consts(float se, float so) { return make_float2(384.f * (se + so), 0.f); }
+  template <int M>
+  static __device__ __forceinline__ void dot(const Row& t, const float4 (&xv)[M][4], const float2 (&c)[M],
+                                             float (&acc)[M]) {
+    float2 F[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) F[m] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t w = k == 0 ? t.q.x : k == 1 ? t.q.y : k == 2 ? t.q.z : t.q.w;
+      constexpr uint32_t MK = 0x007F8000u, EX = 0x43800000u;
+      float2 f0 = make_float2(__uint_as_float(((w << 15) & MK) | EX), __uint_as_float(((w << 7) & MK) | EX));
+      float2 f1 = make_float2(__uint_as_float(((w >> 1) & MK) | EX), __uint_as_float(((w >> 9) & MK) | EX));
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float4 xa = xv[m][k];
+        fma2(F[m], f0, make_float2(xa.x, xa.y));
+        fma2(F[m], f1, make_float2(xa.z, xa.w));
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = fmaf(t.d, (F[m].x + F[m].y) - c[m].x, acc[m]);
+  }
+  static __device__ __forceinline__ float finish(const StreamArgs&, int, float v) { return v; }
+};
+
+// 34-byte GGUF blocks → biased byte plane + f16 scale plane; one thread per block.
+__global__ void q8_0_relayout_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ plane,
+                                     uint16_t* __restrict__ d16, size_t nblocks) {
+  size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblocks) return;
+  const uint8_t* s = raw + b * 34;
+  d16[b] = (uint16_t)(s[0] | (s[1] << 8));
+  for (int i = 0; i < 32; ++i) plane[b * 32 + i] = (uint8_t)(s[2 + i] ^ 0x80);
+}
+
+// dequantRowQ8_0To from the device layout: d * float32(int8).
+__global__ void q8_0_dequant_kernel(const uint8_t* __restrict__ plane, const uint16_t* __restrict__ d16,
+                                    float* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float d = f16_bits_to_f32(d16[i >> 5]);
+  out[i] = __fmul_rn(d, (float)((int)plane[i] - 128));
+}
+
+static bool valid_gguf(const goph_gguf_matrix* m) {
+  return m && m->magic == kMagicGGUF && m->data && m->in_dim > 0 && m->out_dim > 0 &&
+         (m->qtype == GOPH_GGUF_Q4_K || (m->qtype == GOPH_GGUF_Q8_0 && m->d16));
+}
+
+static long gguf_row_bytes(int qtype, int in_dim) {
+  if (qtype == GOPH_GGUF_Q8_0) return in_dim % 32 ? -1 : (long)in_dim / 32 * 34;
+  if (qtype == GOPH_GGUF_Q4_K) return in_dim % 256 ? -1 : (long)in_dim / 256 * 144;
+  return -1;
+}
+
+}  // namespace goph
+
+using namespace goph;
+
+GOPH_API int goph_gguf_upload(int device, int qtype, const uint8_t* raw, uint64_t raw_len, int in_dim, int out_dim,
+                              goph_gguf_matrix** out) {
+  clear_error();
+  if (!out) return fail(GOPH_E_INVALID, "goph_gguf_upload: nil result pointer");
+  *out = nullptr;
+  if (qtype != GOPH_GGUF_Q8_0 && qtype != GOPH_GGUF_Q4_K)
+    return fail(GOPH_E_UNSUPPORTED, "GGUF quant type %d is not Q8_0 or Q4_K", qtype);
+  if (in_dim <= 0 || out_dim <= 0) return fail(GOPH_E_INVALID, "invalid GGUF dims in=%d out=%d", in_dim, out_dim);
+  long rb = gguf_row_bytes(qtype, in_dim);
+  if (rb < 0)
+    return fail(GOPH_E_INVALID, "%s row n=%d not multiple of %d", qtype == GOPH_GGUF_Q8_0 ? "Q8_0" : "Q4_K", in_dim,
+                qtype == GOPH_GGUF_Q8_0 ? 32 : 256);
+  uint64_t need;
+  if (!mul_ok((uint64_t)rb, (uint64_t)out_dim, &need)) return fail(GOPH_E_INVALID, "GGUF matrix size overflow");
+  if (!raw || raw_len < need)
+    return fail(GOPH_E_INVALID, "raw length=%llu, want at least %llu", (unsigned long long)raw_len,
+                (unsigned long long)need);
+  if (int rc = use_device(device)) return rc;
+
+  goph_gguf_matrix* h = new goph_gguf_matrix();
+  memset(h, 0, sizeof *h);
+  h->magic = kMagicGGUF;
+  h->device = device;
+  h->qtype = qtype;
+  h->in_dim = in_dim;
+  h->out_dim = out_dim;
+  uint8_t* tmp = nullptr;
+  auto bail = [&](int rc) {
+    cudaFree(tmp);
+    if (rc) {
+      cudaFree(h->data);
+      cudaFree(h->d16);
+      delete h;
+    }
+    return rc;
+  };
+#define UP(call)                                              \
+  do {                                                        \
+    cudaError_t _e = (call);                                  \
+    if (_e != cudaSuccess) return bail(fail_cuda(_e, #call)); \
+  } while (0)
+  UP(cudaMalloc(&tmp, need));
+  UP(cudaMemcpy(tmp, raw, need, cudaMemcpyHostToDevice));
+  if (qtype == GOPH_GGUF_Q4_K) {
+    size_t nblocks = (size_t)out_dim * (in_dim / 256);
+    UP(cudaMalloc(&h->data, need));
+    q4k_relayout_kernel<<<(unsigned)((nblocks + 127) / 128), 128>>>(tmp, h->data, nblocks);
+    h->bytes = need;
+  } else {
+    size_t nblocks = (size_t)out_dim * (in_dim / 32);
+    UP(cudaMalloc(&h->data, nblocks * 32));
+    UP(cudaMalloc(&h->d16, nblocks * 2));
+    q8_0_relayout_kernel<<<(unsigned)((nblocks + 127) / 128), 128>>>(tmp, h->data, h->d16, nblocks);
+    h->bytes = nblocks * 34;
+  }
+  UP(cudaGetLastError());
+  UP(cudaDeviceSynchronize());
+#undef UP
+  *out = h;
+  return bail(GOPH_OK);
+}
+
+GOPH_API int goph_gguf_free(goph_gguf_matrix* m) {
+  clear_error();
+  if (!m) return GOPH_OK;
+  if (m->magic != kMagicGGUF) return fail(GOPH_E_INVALID, "goph_gguf_free: not a GGUF matrix handle");
+  if (int rc = use_device(m->device)) return rc;
+  cudaFree(m->data);
+  cudaFree(m->d16);
+  m->magic = 0;
+  delete m;
+  return GOPH_OK;
+}
+
+GOPH_API uint64_t goph_gguf_resident_bytes(const goph_gguf_matrix* m) {
+  return (m && m->magic == kMagicGGUF) ? m->bytes : 0;
+}
+
+GOPH_API int goph_gguf_dequant(const goph_gguf_matrix* m, float* out_dev, uint64_t out_len, void* stream) {
+  clear_error();
+  if (!valid_gguf(m)) return fail(GOPH_E_INVALID, "invalid GGUF matrix handle");
+  uint64_t need = (uint64_t)m->out_dim * m->in_dim;
+  if (!out_dev || out_len < need)
+    return fail(GOPH_E_INVALID, "dequant out length=%llu, want at least %llu", (unsigned long long)out_len,
+                (unsigned long long)need);
+  if ((uintptr_t)out_dev % 16) return fail(GOPH_E_INVALID, "dequant out must be 16-byte aligned");
+  if (int rc = use_device(m->device)) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (m->qtype == GOPH_GGUF_Q4_K) {
+    size_t nunits = need / 32;
+    q4k_dequant_kernel<<<(unsigned)((nunits + 255) / 256), 256, 0, s>>>(m->data, out_dev, nunits);
+  } else {
+    q8_0_dequant_kernel<<<(unsigned)((need + 255) / 256), 256, 0, s>>>(m->data, m->d16, out_dev, need);
+  }
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+GOPH_API int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
+                               const goph_gguf_matrix* m, void* stream) {
+  clear_error();
+  if (!valid_gguf(m)) return fail(GOPH_E_INVALID, "invalid GGUF matrix handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_x, need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)m->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)m->out_dim, &need_o))
+    return fail(GOPH_E_INVALID, "batch size overflow");
+  if (!x_dev || x_len < need_x || !out_dev || out_len < need_o)
+    return fail(GOPH_E_INVALID, "buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
+                (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
+  if (int rc = use_device(m->device)) return rc;
+  StreamArgs a;
+  memset(&a, 0, sizeof a);
+  a.w = m->data;
+  a.aux = m->d16;
+  a.out = out_dev;
+  a.x = x_dev;
+  a.rows = m->out_dim;
+  a.in_dim = m->in_dim;
+  const int force_rows = options().gguf_rows;
+  if (m->qtype == GOPH_GGUF_Q4_K) {
+    a.units = m->in_dim / 32;
+    a.row_bytes = m->in_dim / 256 * 144;
+    return stream_launch<Q4KFmt>(a, m->device, batch, (cudaStream_t)stream, force_rows);
+  }
+  a.units = m->in_dim / 16;
+  a.row_bytes = m->in_dim;
+  return stream_launch<Q80Fmt>(a, m->device, batch, (cudaStream_t)stream, force_rows);
+}
+
+GOPH_API int goph_gguf_project_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
+                                    int batch, const goph_gguf_matrix* m) {
+  clear_error();
+  if (!valid_gguf(m)) return fail(GOPH_E_INVALID, "invalid GGUF matrix handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_x, need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)m->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)m->out_dim, &need_o))
+    return fail(GOPH_E_INVALID, "batch size overflow");
+  if (!x_host || x_len < need_x || !out_host || out_len < need_o)
+    return fail(GOPH_E_INVALID, "host buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
+                (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
+  if (int rc = use_device(m->device)) return rc;
+  float *dx = nullptr, *dout = nullptr;
+  GOPH_CUDA(cudaMalloc(&dx, need_x * 4));
+  cudaError_t e = cudaMalloc(&dout, need_o * 4);
+  if (e != cudaSuccess) {
+    cudaFree(dx);
+    return fail_cuda(e, "cudaMalloc(out)");
+  }
+  int rc = GOPH_OK;
+  e = cudaMemcpy(dx, x_host, need_x * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) rc = fail_cuda(e, "cudaMemcpy(x)");
+  if (!rc) rc = goph_gguf_project(dout, need_o, dx, need_x, batch, m, nullptr);
+  if (!rc) {
+    e = cudaMemcpy(out_host, dout, need_o * 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail_cuda(e, "cudaMemcpy(out)");
+  }
+  cudaFree(dx);
+  cudaFree(dout);
+  return rc;
+}

@@ -1,0 +1,736 @@
+// MLX 4-bit affine weights: upload, bit-exact dequantisation, and the dequant-fused
+// GEMV / small-batch product.
+//
+// Replaces the reference's mlx_gemv / mlx_gemm / mlx_correct / gemv_q4sym PTX
+// (backends/nvidia/ptx/mlx/mlx.go, ptx/q4/gemv.go) behind nvidia.GemvMLX,
+// GemvMLXDirect and GemmMLX (backends/nvidia/runtime/mlx.go:287-488).  The arithmetic
+// specification is mlx.GemvTo (backends/mlx/gemv.go:164-209):
+//     out[r] = sum_g ( scale[r,g] * sum_{e in g} nibble*x  +  bias[r,g] * sum_{e in g} x ).
+//
+// Streaming kernel (mlx_gemv_kernel)
+//   * A warp owns R consecutive rows at a time.  Lane l of iteration `it` owns the 16
+//     bytes (32 nibbles, half of a 64-group) at unit u = 32*it + l of each of those rows,
+//     so one warp instruction is a 512-byte coalesced, L1-bypassing load per row.
+//   * x lives in shared memory as f32, permuted so that the eight float4 a lane needs
+//     for its unit are read with conflict-free LDS.128 ([batch][it][slot][lane]).
+//     Beside it sit two numbers per unit, c1 and c2 (below).
+//   * A nibble n becomes an f32 by bit placement only: put it in the top mantissa bits
+//     under a fixed exponent and the word reads as (K + n) for a constant K (16, or 256
+//     for the partner nibble when one shift serves two nibbles).  The constant is
+//     removed algebraically per unit:  sum (K+n)x = F,  sum n x = F - c1  with
+//     c1 = sum K x precomputed once per unit; c2 = sum x feeds the bias term.
+//   * Products are accumulated with fma.rn.f32x2 (two f32 FMAs per issue slot), one
+//     f32 accumulator per (row, batch) pair, reduced across the warp by shuffles.
+//   * The next step's weights are already in flight while the current step computes.
+#include <stdlib.h>
+#include <string.h>
+
+#include <vector>
+
+#include "goph_internal.cuh"
+
+namespace goph {
+
+enum { UNPACK_EXACT = 0, UNPACK_PAIR = 1, UNPACK_CVT = 2 };
+
+// Turns the eight nibbles of `w` into f[j] = off(j) + nibble_j.
+template <int MODE>
+struct Unpack;
+
+// Every nibble is moved to mantissa bits 19..22 under exponent 2^4: f = 16 + n.
+template <>
+struct Unpack<UNPACK_EXACT> {
+  static constexpr float kOffEven = 16.f, kOffOdd = 16.f;
+  static __device__ __forceinline__ void run(uint32_t w, float (&f)[8]) {
+    constexpr uint32_t M = 0x00780000u, E = 0x41800000u;
+    f[0] = __uint_as_float(((w << 19) & M) | E);
+    f[1] = __uint_as_float(((w << 15) & M) | E);
+    f[2] = __uint_as_float(((w << 11) & M) | E);
+    f[3] = __uint_as_float(((w << 7) & M) | E);
+    f[4] = __uint_as_float(((w << 3) & M) | E);
+    f[5] = __uint_as_float(((w >> 1) & M) | E);
+    f[6] = __uint_as_float(((w >> 5) & M) | E);
+    f[7] = __uint_as_float(((w >> 9) & M) | E);
+  }
+};
+
+// One shift serves two neighbouring nibbles: the odd one lands on bits 19..22 under 2^4
+// (16 + n), the even one on bits 15..18 under 2^8 (256 + n).
+template <>
+struct Unpack<UNPACK_PAIR> {
+  static constexpr float kOffEven = 256.f, kOffOdd = 16.f;
+  static __device__ __forceinline__ void run(uint32_t w, float (&f)[8]) {
+    constexpr uint32_t MA = 0x00780000u, EA = 0x41800000u, MB = 0x00078000u, EB = 0x43800000u;
+    uint32_t t0 = w << 15, t1 = w << 7, t2 = w >> 1, t3 = w >> 9;
+    f[0] = __uint_as_float((t0 & MB) | EB);
+    f[1] = __uint_as_float((t0 & MA) | EA);
+    f[2] = __uint_as_float((t1 & MB) | EB);
+    f[3] = __uint_as_float((t1 & MA) | EA);
+    f[4] = __uint_as_float((t2 & MB) | EB);
+    f[5] = __uint_as_float((t2 & MA) | EA);
+    f[6] = __uint_as_float((t3 & MB) | EB);
+    f[7] = __uint_as_float((t3 & MA) | EA);
+  }
+};
+
+// Plain integer-to-float conversion of each nibble (no offset to remove).
+template <>
+struct Unpack<UNPACK_CVT> {
+  static constexpr float kOffEven = 0.f, kOffOdd = 0.f;
+  static __device__ __forceinline__ void run(uint32_t w, float (&f)[8]) {
+    uint32_t lo = w & 0x0F0F0F0Fu, hi = (w >> 4) & 0x0F0F0F0Fu;
+    f[0] = (float)(lo & 0xFF);
+    f[1] = (float)(hi & 0xFF);
+    f[2] = (float)((lo >> 8) & 0xFF);
+    f[3] = (float)((hi >> 8) & 0xFF);
+    f[4] = (float)((lo >> 16) & 0xFF);
+    f[5] = (float)((hi >> 16) & 0xFF);
+    f[6] = (float)(lo >> 24);
+    f[7] = (float)(hi >> 24);
+  }
+};
+
+constexpr int kMaxSeg = 8;
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+
+struct MlxSeg {
+  const uint4* w;   // packed rows, `units` uint4 per row
+  const void* sb;   // {scale,bias} per (row, group)
+  float* out;       // [batch][rows]
+  int rows;
+  int task0;        // index of this segment's first warp task
+};
+
+struct MlxArgs {
+  MlxSeg seg[kMaxSeg];
+  int nseg;
+  int tasks;        // total warp tasks (row groups of R rows) over all segments
+  const float* x;   // [batch][in_dim]
+  int batch;
+  int in_dim;
+  int units;        // in_dim / 32
+  int iters;        // ceil(units / 32)
+  int groups;       // in_dim / group_size
+  int ug_shift;     // log2(group_size / 32)
+  int x_aligned;    // x is 16-byte aligned
+};
+
+// Shared memory: float4 xs[M][iters][8][32]; float2 xc[M][iters][32].
+__host__ __device__ inline size_t mlx_smem_bytes(int M, int iters) {
+  return (size_t)M * iters * (8 * 32 * 16 + 32 * 8);
+}
+
+template <int M, int MODE>
+__device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2* xc) {
+  const int per_m = a.iters * 256;
+  const int total = M * per_m;
+  for (int idx = threadIdx.x; idx < total; idx += kThreads) {
+    int m = idx / per_m, rem = idx - m * per_m;
+    int it = rem >> 8, slot = (rem >> 5) & 7, l = rem & 31;
+    int unit = it * 32 + l;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < a.batch && unit < a.units) {
+      const float* p = a.x + (size_t)m * a.in_dim + (size_t)unit * 32 + slot * 4;
+      if (a.x_aligned) {
+        v = __ldg(reinterpret_cast<const float4*>(p));
+      } else {
+        v = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+      }
+    }
+    xs[idx] = v;
+  }
+  __syncthreads();
+  const int nsum = M * a.iters * 32;
+  for (int idx = threadIdx.x; idx < nsum; idx += kThreads) {
+    int mi = idx >> 5, l = idx & 31;  // mi = m*iters + it
+    float se = 0.f, so = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      float4 v = xs[(mi * 8 + s) * 32 + l];
+      se += v.x + v.z;
+      so += v.y + v.w;
+    }
+    xc[idx] = make_float2(Unpack<MODE>::kOffEven * se + Unpack<MODE>::kOffOdd * so, se + so);
+  }
+  __syncthreads();
+}
+
+template <int R, int M, int MODE, bool SB_BF16>
+__global__ void __launch_bounds__(kThreads)
+mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float4* xs = reinterpret_cast<float4*>(smem_raw);
+  float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)M * a.iters * 8 * 32 * 16);
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int task_stride = gridDim.x * kWarps;
+  const int task_first = blockIdx.x * kWarps + warp;
+  const int iters = a.iters;
+
+  struct Tile {
+    uint4 w[R];
+    uint32_t sb_lo[R], sb_hi[R];  // scale, bias as f32 bit patterns
+  };
+
+  // Resolves a warp task to its segment and first row.
+  auto locate = [&](int task, int& seg, int& row0) {
+    seg = 0;
+#pragma unroll
+    for (int s = 1; s < kMaxSeg; ++s)
+      if (s < a.nseg && task >= a.seg[s].task0) seg = s;
+    row0 = (task - a.seg[seg].task0) * R;
+  };
+
+  auto load_tile = [&](int task, int it, Tile& t) {
+    int seg, row0;
+    locate(task, seg, row0);
+    const MlxSeg& sg = a.seg[seg];
+    int unit = it * 32 + lane;
+    if (unit >= a.units) unit = a.units - 1;  // x is zero there; any finite weight will do
+    int grp = unit >> a.ug_shift;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      int row = row0 + r;
+      if (row >= sg.rows) row = sg.rows - 1;
+      t.w[r] = ld_stream(sg.w + (size_t)row * a.units + unit);
+      if (SB_BF16) {
+        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(sg.sb) + (size_t)row * a.groups + grp);
+        t.sb_lo[r] = v << 16;
+        t.sb_hi[r] = v & 0xFFFF0000u;
+      } else {
+        float2 v = __ldg(reinterpret_cast<const float2*>(sg.sb) + (size_t)row * a.groups + grp);
+        t.sb_lo[r] = __float_as_uint(v.x);
+        t.sb_hi[r] = __float_as_uint(v.y);
+      }
+    }
+  };
+
+  // Issue the first weight loads before x is staged so both latencies overlap.
+  Tile cur, nxt;
+  int task = task_first, it = 0;
+  const bool has_work = task < a.tasks;
+  if (has_work) load_tile(task, 0, cur);
+
+  mlx_stage_x<M, MODE>(a, xs, xc);
+  if (!has_work) return;
+
+  float acc[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+
+  while (true) {
+    int ntask = task, nit = it + 1;
+    if (nit == iters) {
+      nit = 0;
+      ntask = task + task_stride;
+    }
+    const bool more = ntask < a.tasks;
+    if (more) load_tile(ntask, nit, nxt);
+
+    // ---- compute the current tile ----
+    float2 F[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) F[r][m] = make_float2(0.f, 0.f);
+
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float4 xa[M], xb[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float4* base = xs + ((size_t)(m * iters + it) * 8 + 2 * k) * 32 + lane;
+        xa[m] = base[0];
+        xb[m] = base[32];
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        uint32_t word = k == 0 ? cur.w[r].x : k == 1 ? cur.w[r].y : k == 2 ? cur.w[r].z : cur.w[r].w;
+        float f[8];
+        Unpack<MODE>::run(word, f);
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          fma2(F[r][m], make_float2(f[0], f[1]), make_float2(xa[m].x, xa[m].y));
+          fma2(F[r][m], make_float2(f[2], f[3]), make_float2(xa[m].z, xa[m].w));
+          fma2(F[r][m], make_float2(f[4], f[5]), make_float2(xb[m].x, xb[m].y));
+          fma2(F[r][m], make_float2(f[6], f[7]), make_float2(xb[m].z, xb[m].w));
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      float2 c = xc[(m * iters + it) * 32 + lane];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        float dot = (F[r][m].x + F[r][m].y) - c.x;
+        acc[r][m] = fmaf(__uint_as_float(cur.sb_lo[r]), dot, acc[r][m]);
+        acc[r][m] = fmaf(__uint_as_float(cur.sb_hi[r]), c.y, acc[r][m]);
+      }
+    }
+
+    if (it == iters - 1) {
+      int seg, row0;
+      locate(task, seg, row0);
+      const MlxSeg& sg = a.seg[seg];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float v = warp_sum(acc[r][m]);
+          acc[r][m] = 0.f;
+          if (lane == 0 && row0 + r < sg.rows && m < a.batch) sg.out[(size_t)m * sg.rows + row0 + r] = v;
+        }
+    }
+    if (!more) break;
+    cur = nxt;
+    task = ntask;
+    it = nit;
+  }
+}
+
+// Any group size / ragged in_dim: one warp per row, plain conversions, x from global.
+template <bool SB_BF16>
+__global__ void __launch_bounds__(kThreads)
+mlx_gemv_generic_kernel(const uint32_t* __restrict__ w, const void* __restrict__ sb,
+                        const float* __restrict__ x, float* __restrict__ out, int out_dim, int in_dim,
+                        int gs, int groups, int batch) {
+  int row = blockIdx.x * kWarps + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
+  if (row >= out_dim) return;
+  int words = in_dim / 8;
+  for (int m = 0; m < batch; ++m) {
+    const float* xm = x + (size_t)m * in_dim;
+    float acc = 0.f;
+    for (int j = lane; j < words; j += 32) {
+      uint32_t q = w[(size_t)row * words + j];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        int col = j * 8 + e;
+        int g = col / gs;
+        float s, b;
+        if (SB_BF16) {
+          uint32_t v = reinterpret_cast<const uint32_t*>(sb)[(size_t)row * groups + g];
+          s = __uint_as_float(v << 16);
+          b = __uint_as_float(v & 0xFFFF0000u);
+        } else {
+          float2 v = reinterpret_cast<const float2*>(sb)[(size_t)row * groups + g];
+          s = v.x;
+          b = v.y;
+        }
+        float xv = xm[col];
+        acc = fmaf(s * (float)((q >> (4 * e)) & 0xF) + b, xv, acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) out[(size_t)m * out_dim + row] = acc;
+  }
+}
+
+// mlx.DequantTo: one thread per packed word, float32(nibble)*scale then +bias, both
+// rounded (the intrinsics forbid contraction into an FMA).
+template <bool SB_BF16>
+__global__ void mlx_dequant_kernel(const uint32_t* __restrict__ w, const void* __restrict__ sb,
+                                   float* __restrict__ out, size_t total_words, int words_per_row,
+                                   int gs, int groups) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_words) return;
+  size_t row = i / words_per_row;
+  int j = (int)(i - row * words_per_row);
+  uint32_t q = w[i];
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    int g = (j * 8 + e) / gs;
+    float s, b;
+    if (SB_BF16) {
+      uint32_t t = reinterpret_cast<const uint32_t*>(sb)[row * groups + g];
+      s = __uint_as_float(t << 16);
+      b = __uint_as_float(t & 0xFFFF0000u);
+    } else {
+      float2 t = reinterpret_cast<const float2*>(sb)[row * groups + g];
+      s = t.x;
+      b = t.y;
+    }
+    v[e] = __fadd_rn(__fmul_rn((float)((q >> (4 * e)) & 0xF), s), b);
+  }
+  float4* o = reinterpret_cast<float4*>(out + i * 8);
+  o[0] = make_float4(v[0], v[1], v[2], v[3]);
+  o[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// Upload helpers: decide whether every scale/bias is a bf16 value, then interleave.
+__global__ void mlx_sb_probe_kernel(const float* __restrict__ s, const float* __restrict__ b, size_t n,
+                                    int* __restrict__ not_bf16) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if ((__float_as_uint(s[i]) & 0xFFFFu) | (__float_as_uint(b[i]) & 0xFFFFu)) *not_bf16 = 1;
+}
+
+__global__ void mlx_sb_pack_kernel(const float* __restrict__ s, const float* __restrict__ b, size_t n,
+                                   void* __restrict__ dst, int as_bf16) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  if (as_bf16)
+    reinterpret_cast<uint32_t*>(dst)[i] = (__float_as_uint(s[i]) >> 16) | (__float_as_uint(b[i]) & 0xFFFF0000u);
+  else
+    reinterpret_cast<float2*>(dst)[i] = make_float2(s[i], b[i]);
+}
+
+// ---- host side ------------------------------------------------------------------
+
+typedef void (*MlxKernel)(const MlxArgs);
+
+template <int R, int M, int MODE>
+static MlxKernel pick_sb(bool bf16) {
+  return bf16 ? (MlxKernel)mlx_gemv_kernel<R, M, MODE, true> : (MlxKernel)mlx_gemv_kernel<R, M, MODE, false>;
+}
+
+template <int R, int M>
+static MlxKernel pick_mode(int mode, bool bf16) {
+  if (M == 1) {
+    if (mode == UNPACK_PAIR) return pick_sb<R, M, (M == 1 ? UNPACK_PAIR : UNPACK_EXACT)>(bf16);
+    if (mode == UNPACK_CVT) return pick_sb<R, M, (M == 1 ? UNPACK_CVT : UNPACK_EXACT)>(bf16);
+  }
+  return pick_sb<R, M, UNPACK_EXACT>(bf16);
+}
+
+static MlxKernel pick_kernel(int R, int M, int mode, bool bf16) {
+  switch (M) {
+    case 1:
+      return R == 4 ? pick_mode<4, 1>(mode, bf16) : R == 2 ? pick_mode<2, 1>(mode, bf16) : pick_mode<1, 1>(mode, bf16);
+    case 2:
+      return R == 4 ? pick_mode<4, 2>(mode, bf16) : R == 2 ? pick_mode<2, 2>(mode, bf16) : pick_mode<1, 2>(mode, bf16);
+    case 4:
+      return R == 4 ? pick_mode<4, 4>(mode, bf16) : R == 2 ? pick_mode<2, 4>(mode, bf16) : pick_mode<1, 4>(mode, bf16);
+    default:
+      return R >= 2 ? pick_mode<2, 8>(mode, bf16) : pick_mode<1, 8>(mode, bf16);
+  }
+}
+
+static bool valid_handle(const goph_mlx_weight* w) {
+  return w && w->magic == kMagicMLX && w->qweight && w->sb && w->in_dim > 0 && w->out_dim > 0 &&
+         w->group_size > 0 && w->groups == w->in_dim / w->group_size;
+}
+
+static bool fast_path_ok(const goph_mlx_weight* w) {
+  int gs = w->group_size;
+  return w->in_dim % 32 == 0 && gs >= 32 && (gs & (gs - 1)) == 0;
+}
+
+// One launch of the streaming kernel for up to kMaxSeg weights sharing x, batch <= 8.
+static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, int n, const float* x,
+                         int batch, cudaStream_t stream) {
+  const goph_mlx_weight* w0 = ws[0];
+  DeviceState& st = device_state(w0->device);
+  MlxArgs a;
+  memset(&a, 0, sizeof a);
+  a.nseg = n;
+  a.x = x;
+  a.batch = batch;
+  a.in_dim = w0->in_dim;
+  a.units = w0->in_dim / 32;
+  a.iters = (a.units + 31) / 32;
+  a.groups = w0->groups;
+  int upg = w0->group_size / 32, sh = 0;
+  while ((1 << sh) < upg) ++sh;
+  a.ug_shift = sh;
+  a.x_aligned = ((uintptr_t)x % 16) == 0;
+
+  int M = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
+  long total_rows = 0;
+  for (int i = 0; i < n; ++i) total_rows += ws[i]->out_dim;
+  // Rows per warp: as many as keep every SM's 16 resident warps busy for two rounds.
+  int R = options().mlx_rows;
+  if (R != 1 && R != 2 && R != 4) {
+    long want = (long)st.sm_count * 2 * kWarps * 2;
+    R = total_rows / 4 >= want ? 4 : total_rows / 2 >= want ? 2 : 1;
+  }
+  if (M == 8 && R == 4) R = 2;
+  int tasks = 0;
+  for (int i = 0; i < n; ++i) {
+    a.seg[i].w = reinterpret_cast<const uint4*>(ws[i]->qweight);
+    a.seg[i].sb = ws[i]->sb;
+    a.seg[i].out = outs[i];
+    a.seg[i].rows = ws[i]->out_dim;
+    a.seg[i].task0 = tasks;
+    tasks += (ws[i]->out_dim + R - 1) / R;
+  }
+  a.tasks = tasks;
+
+  const int mode = options().mlx_unpack;
+  MlxKernel k = pick_kernel(R, M, mode, w0->sb_bf16 != 0);
+  size_t smem = mlx_smem_bytes(M, a.iters);
+  GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  GOPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kThreads, smem));
+  if (per_sm < 1) return fail(GOPH_E_UNSUPPORTED, "MLX GEMV kernel does not fit (smem %zu)", smem);
+  int grid = (tasks + kWarps - 1) / kWarps;
+  int cap = st.sm_count * per_sm;
+  if (grid > cap) grid = cap;
+  k<<<grid, kThreads, smem, stream>>>(a);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+static int launch_generic(const goph_mlx_weight* w, float* out, const float* x, int batch, cudaStream_t stream) {
+  int grid = (w->out_dim + kWarps - 1) / kWarps;
+  if (w->sb_bf16)
+    mlx_gemv_generic_kernel<true><<<grid, kThreads, 0, stream>>>(w->qweight, w->sb, x, out, w->out_dim, w->in_dim,
+                                                                 w->group_size, w->groups, batch);
+  else
+    mlx_gemv_generic_kernel<false><<<grid, kThreads, 0, stream>>>(w->qweight, w->sb, x, out, w->out_dim, w->in_dim,
+                                                                  w->group_size, w->groups, batch);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+// Products for n weights sharing x [batch,in]; outs[i] is [batch,out_i].
+static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const* ws, const float* x, int batch,
+                        cudaStream_t stream) {
+  const goph_mlx_weight* w0 = ws[0];
+  bool uniform = true;
+  for (int i = 0; i < n; ++i)
+    uniform = uniform && fast_path_ok(ws[i]) && ws[i]->sb_bf16 == w0->sb_bf16;
+  if (!uniform || n > kMaxSeg) {
+    for (int i = 0; i < n; ++i) {
+      const goph_mlx_weight* one = ws[i];
+      float* o = outs[i];
+      int rc = fast_path_ok(one) ? mlx_products(1, &o, &one, x, batch, stream)
+                                 : launch_generic(one, o, x, batch, stream);
+      if (rc) return rc;
+    }
+    return GOPH_OK;
+  }
+  int units = w0->in_dim / 32, iters = (units + 31) / 32;
+  if (mlx_smem_bytes(1, iters) > (size_t)kSmemBudget) {
+    for (int i = 0; i < n; ++i)
+      if (int rc = launch_generic(ws[i], outs[i], x, batch, stream)) return rc;
+    return GOPH_OK;
+  }
+  // Batch tile: the largest of 8/4/2/1 whose x fits in shared memory.
+  int tile = 8;
+  while (tile > 1 && mlx_smem_bytes(tile, iters) > (size_t)kSmemBudget) tile >>= 1;
+  for (int b0 = 0; b0 < batch; b0 += tile) {
+    int nb = batch - b0 < tile ? batch - b0 : tile;
+    float* sub[kMaxSeg];
+    for (int i = 0; i < n; ++i) sub[i] = outs[i] + (size_t)b0 * ws[i]->out_dim;
+    if (int rc = launch_stream(ws, sub, n, x + (size_t)b0 * w0->in_dim, nb, stream)) return rc;
+  }
+  return GOPH_OK;
+}
+
+}  // namespace goph
+
+using namespace goph;
+
+static int mlx_upload_common(int device, const uint32_t* weight, const float* scales, const float* biases,
+                             bool on_device, int in_dim, int out_dim, int gs, goph_mlx_weight** out) {
+  uint64_t groups = (uint64_t)in_dim / gs, want_w, want_s;
+  mul_ok((uint64_t)out_dim, (uint64_t)in_dim / 8, &want_w);
+  mul_ok((uint64_t)out_dim, groups, &want_s);
+  goph_mlx_weight* h = new goph_mlx_weight();
+  h->magic = kMagicMLX;
+  h->device = device;
+  h->in_dim = in_dim;
+  h->out_dim = out_dim;
+  h->group_size = gs;
+  h->groups = (int)groups;
+  float *ds = nullptr, *db = nullptr;
+  int* flag = nullptr;
+  auto cleanup = [&](int rc) {
+    if (!on_device) {
+      cudaFree(ds);
+      cudaFree(db);
+    }
+    cudaFree(flag);
+    if (rc) {
+      cudaFree(h->qweight);
+      cudaFree(h->sb);
+      delete h;
+    }
+    return rc;
+  };
+#define UP(call)                                            \
+  do {                                                      \
+    cudaError_t _e = (call);                                \
+    if (_e != cudaSuccess) return cleanup(fail_cuda(_e, #call)); \
+  } while (0)
+  UP(cudaMalloc(&h->qweight, want_w * 4));
+  UP(cudaMemcpy(h->qweight, weight, want_w * 4, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+  if (on_device) {
+    ds = const_cast<float*>(scales);
+    db = const_cast<float*>(biases);
+  } else {
+    UP(cudaMalloc(&ds, want_s * 4));
+    UP(cudaMalloc(&db, want_s * 4));
+    UP(cudaMemcpy(ds, scales, want_s * 4, cudaMemcpyHostToDevice));
+    UP(cudaMemcpy(db, biases, want_s * 4, cudaMemcpyHostToDevice));
+  }
+  UP(cudaMalloc(&flag, sizeof(int)));
+  UP(cudaMemset(flag, 0, sizeof(int)));
+  unsigned blocks = (unsigned)((want_s + 255) / 256);
+  mlx_sb_probe_kernel<<<blocks, 256>>>(ds, db, want_s, flag);
+  int not_bf16 = 0;
+  UP(cudaMemcpy(&not_bf16, flag, sizeof(int), cudaMemcpyDeviceToHost));
+  h->sb_bf16 = not_bf16 ? 0 : 1;
+  UP(cudaMalloc(&h->sb, want_s * (h->sb_bf16 ? 4 : 8)));
+  mlx_sb_pack_kernel<<<blocks, 256>>>(ds, db, want_s, h->sb, h->sb_bf16);
+  UP(cudaGetLastError());
+  UP(cudaDeviceSynchronize());
+#undef UP
+  h->bytes = want_w * 4 + want_s * (h->sb_bf16 ? 4 : 8);
+  *out = h;
+  return cleanup(GOPH_OK);
+}
+
+// validateMLXUploadInputs (backends/nvidia/runtime/mlx.go:34-55).
+static int mlx_validate_dims(int in_dim, int out_dim, int gs) {
+  if (in_dim <= 0 || out_dim <= 0 || gs <= 0 || in_dim % gs != 0 || in_dim % 8 != 0)
+    return fail(GOPH_E_INVALID, "invalid MLX dims inDim=%d outDim=%d groupSize=%d", in_dim, out_dim, gs);
+  return GOPH_OK;
+}
+
+GOPH_API int goph_mlx_upload(int device, const uint32_t* weight, uint64_t weight_len, const float* scales,
+                             const float* biases, uint64_t scale_len, int in_dim, int out_dim, int group_size,
+                             goph_mlx_weight** out) {
+  clear_error();
+  if (!out) return fail(GOPH_E_INVALID, "goph_mlx_upload: nil result pointer");
+  *out = nullptr;
+  if (int rc = mlx_validate_dims(in_dim, out_dim, group_size)) return rc;
+  uint64_t want_w, want_s;
+  if (!mul_ok((uint64_t)out_dim, (uint64_t)in_dim / 8, &want_w) ||
+      !mul_ok((uint64_t)out_dim, (uint64_t)(in_dim / group_size), &want_s) || want_w > (UINT64_MAX >> 3))
+    return fail(GOPH_E_INVALID, "MLX weight size overflow outDim=%d inDim=%d", out_dim, in_dim);
+  if (!weight || weight_len < want_w)
+    return fail(GOPH_E_INVALID, "weight length=%llu, want at least %llu", (unsigned long long)weight_len,
+                (unsigned long long)want_w);
+  if (!scales || !biases || scale_len < want_s)
+    return fail(GOPH_E_INVALID, "scale/bias length=%llu, want at least %llu", (unsigned long long)scale_len,
+                (unsigned long long)want_s);
+  if (int rc = use_device(device)) return rc;
+  return mlx_upload_common(device, weight, scales, biases, false, in_dim, out_dim, group_size, out);
+}
+
+GOPH_API int goph_mlx_upload_dev(int device, const uint32_t* weight_dev, const float* scales_dev,
+                                 const float* biases_dev, int in_dim, int out_dim, int group_size,
+                                 goph_mlx_weight** out) {
+  clear_error();
+  if (!out) return fail(GOPH_E_INVALID, "goph_mlx_upload_dev: nil result pointer");
+  *out = nullptr;
+  if (int rc = mlx_validate_dims(in_dim, out_dim, group_size)) return rc;
+  uint64_t want_w;
+  if (!mul_ok((uint64_t)out_dim, (uint64_t)in_dim / 8, &want_w) || want_w > (UINT64_MAX >> 3))
+    return fail(GOPH_E_INVALID, "MLX weight size overflow outDim=%d inDim=%d", out_dim, in_dim);
+  if (!weight_dev || !scales_dev || !biases_dev) return fail(GOPH_E_INVALID, "goph_mlx_upload_dev: nil buffer");
+  if (int rc = use_device(device)) return rc;
+  return mlx_upload_common(device, weight_dev, scales_dev, biases_dev, true, in_dim, out_dim, group_size, out);
+}
+
+GOPH_API int goph_mlx_free(goph_mlx_weight* w) {
+  clear_error();
+  if (!w) return GOPH_OK;
+  if (w->magic != kMagicMLX) return fail(GOPH_E_INVALID, "goph_mlx_free: not an MLX weight handle");
+  if (int rc = use_device(w->device)) return rc;
+  cudaFree(w->qweight);
+  cudaFree(w->sb);
+  w->magic = 0;
+  delete w;
+  return GOPH_OK;
+}
+
+GOPH_API uint64_t goph_mlx_resident_bytes(const goph_mlx_weight* w) {
+  return (w && w->magic == kMagicMLX) ? w->bytes : 0;
+}
+
+GOPH_API int goph_mlx_dequant(const goph_mlx_weight* w, float* out_dev, uint64_t out_len, void* stream) {
+  clear_error();
+  if (!valid_handle(w)) return fail(GOPH_E_INVALID, "goph_mlx_dequant: invalid weight handle");
+  uint64_t need = (uint64_t)w->out_dim * w->in_dim;
+  if (!out_dev || out_len < need)
+    return fail(GOPH_E_INVALID, "dequant out length=%llu, want at least %llu", (unsigned long long)out_len,
+                (unsigned long long)need);
+  if ((uintptr_t)out_dev % 16) return fail(GOPH_E_INVALID, "dequant out must be 16-byte aligned");
+  if (int rc = use_device(w->device)) return rc;
+  size_t words = (size_t)w->out_dim * (w->in_dim / 8);
+  unsigned blocks = (unsigned)((words + 255) / 256);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (w->sb_bf16)
+    mlx_dequant_kernel<true><<<blocks, 256, 0, s>>>(w->qweight, w->sb, out_dev, words, w->in_dim / 8,
+                                                    w->group_size, w->groups);
+  else
+    mlx_dequant_kernel<false><<<blocks, 256, 0, s>>>(w->qweight, w->sb, out_dev, words, w->in_dim / 8,
+                                                     w->group_size, w->groups);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+GOPH_API int goph_mlx_gemm_multi(int n, float* const* outs_dev, const goph_mlx_weight* const* ws,
+                                 const float* x_dev, uint64_t x_len, int batch, void* stream) {
+  clear_error();
+  if (n <= 0 || n > kMaxSeg || !outs_dev || !ws) return fail(GOPH_E_INVALID, "goph_mlx_gemm_multi: n=%d out of 1..%d", n, kMaxSeg);
+  if (batch <= 0) return fail(GOPH_E_INVALID, "goph_mlx_gemm_multi: batch=%d", batch);
+  for (int i = 0; i < n; ++i) {
+    if (!valid_handle(ws[i]) || !outs_dev[i]) return fail(GOPH_E_INVALID, "goph_mlx_gemm_multi: invalid weight or out %d", i);
+    if (ws[i]->device != ws[0]->device || ws[i]->in_dim != ws[0]->in_dim || ws[i]->group_size != ws[0]->group_size)
+      return fail(GOPH_E_INVALID, "goph_mlx_gemm_multi: weights %d and 0 differ in device/inDim/groupSize", i);
+  }
+  uint64_t need_x;
+  if (!mul_ok((uint64_t)batch, (uint64_t)ws[0]->in_dim, &need_x) || !x_dev || x_len < need_x)
+    return fail(GOPH_E_INVALID, "x length=%llu, want at least %llu", (unsigned long long)x_len,
+                (unsigned long long)((uint64_t)batch * ws[0]->in_dim));
+  if (int rc = use_device(ws[0]->device)) return rc;
+  return mlx_products(n, outs_dev, ws, x_dev, batch, (cudaStream_t)stream);
+}
+
+GOPH_API int goph_mlx_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                           const goph_mlx_weight* w, int batch, void* stream) {
+  clear_error();
+  if (!valid_handle(w)) return fail(GOPH_E_INVALID, "invalid MLX weight handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)w->out_dim, &need_o) || !out_dev || out_len < need_o)
+    return fail(GOPH_E_INVALID, "out length=%llu, want at least %llu", (unsigned long long)out_len,
+                (unsigned long long)((uint64_t)batch * w->out_dim));
+  return goph_mlx_gemm_multi(1, &out_dev, &w, x_dev, x_len, batch, stream);
+}
+
+GOPH_API int goph_mlx_gemv(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                           const goph_mlx_weight* w, void* stream) {
+  return goph_mlx_gemm(out_dev, out_len, x_dev, x_len, w, 1, stream);
+}
+
+GOPH_API int goph_mlx_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
+                                const goph_mlx_weight* w, int batch) {
+  clear_error();
+  if (!valid_handle(w)) return fail(GOPH_E_INVALID, "invalid MLX weight handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_x, need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)w->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)w->out_dim, &need_o))
+    return fail(GOPH_E_INVALID, "batch size overflow");
+  if (!x_host || x_len < need_x || !out_host || out_len < need_o)
+    return fail(GOPH_E_INVALID, "host buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
+                (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
+  if (int rc = use_device(w->device)) return rc;
+  float *dx = nullptr, *dout = nullptr;
+  GOPH_CUDA(cudaMalloc(&dx, need_x * 4));
+  cudaError_t e = cudaMalloc(&dout, need_o * 4);
+  if (e != cudaSuccess) {
+    cudaFree(dx);
+    return fail_cuda(e, "cudaMalloc(out)");
+  }
+  int rc = GOPH_OK;
+  e = cudaMemcpy(dx, x_host, need_x * 4, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) rc = fail_cuda(e, "cudaMemcpy(x)");
+  if (!rc) rc = goph_mlx_gemm(dout, need_o, dx, need_x, w, batch, nullptr);
+  if (!rc) {
+    e = cudaMemcpy(out_host, dout, need_o * 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail_cuda(e, "cudaMemcpy(out)");
+  }
+  cudaFree(dx);
+  cudaFree(dout);
+  return rc;
+}

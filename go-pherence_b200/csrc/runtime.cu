@@ -1,0 +1,145 @@
+// Runtime part of the C ABI: device binding, buffers, copies, error text.
+// Stands where backends/nvidia/runtime/runtime.go stands in the reference (Init,
+// EnsureContext, Malloc, Buffer.Upload/Download/Free, Sync).
+#include <stdarg.h>
+#include <string.h>
+
+#include "goph_internal.cuh"
+
+namespace goph {
+
+static DeviceState g_dev[kMaxDevices];
+static thread_local char g_err[512] = "";
+
+static Options g_opt;
+
+DeviceState& device_state(int device) { return g_dev[device]; }
+Options& options() { return g_opt; }
+
+void clear_error() { g_err[0] = 0; }
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof g_err, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  snprintf(g_err, sizeof g_err, "CUDA error %d (%s: %s) in %s", (int)e, cudaGetErrorName(e),
+           cudaGetErrorString(e), what);
+  cudaGetLastError();  // clear the sticky-free error slot for the next call
+  return e == cudaErrorMemoryAllocation ? GOPH_E_NOMEM : GOPH_E_CUDA;
+}
+
+int use_device(int device) {
+  if (device < 0 || device >= kMaxDevices) return fail(GOPH_E_INVALID, "device %d out of range", device);
+  if (!g_dev[device].ready) return fail(GOPH_E_NOINIT, "goph_init(%d) has not been called", device);
+  GOPH_CUDA(cudaSetDevice(device));
+  return GOPH_OK;
+}
+
+}  // namespace goph
+
+using namespace goph;
+
+GOPH_API int goph_init(int device) {
+  clear_error();
+  if (device < 0 || device >= kMaxDevices) return fail(GOPH_E_INVALID, "device %d out of range", device);
+  int n = 0;
+  GOPH_CUDA(cudaGetDeviceCount(&n));
+  if (device >= n) return fail(GOPH_E_INVALID, "device %d not present (%d visible)", device, n);
+  GOPH_CUDA(cudaSetDevice(device));
+  GOPH_CUDA(cudaFree(0));
+  DeviceState& st = device_state(device);
+  if (st.ready) return GOPH_OK;
+  cudaDeviceProp prop;
+  GOPH_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(GOPH_E_UNSUPPORTED, "device %d is sm_%d%d; this library holds sm_100a code only", device,
+                prop.major, prop.minor);
+  st.sm_count = prop.multiProcessorCount;
+  st.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+  st.ready = true;
+  return GOPH_OK;
+}
+
+GOPH_API int goph_set_option(const char* name, int value) {
+  clear_error();
+  if (!name) return fail(GOPH_E_INVALID, "goph_set_option: nil name");
+  Options& o = options();
+  bool rows_ok = value == 0 || value == 1 || value == 2 || value == 4;
+  if (!strcmp(name, "mlx_unpack")) {
+    if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_unpack=%d not in 0..2", value);
+    o.mlx_unpack = value;
+  } else if (!strcmp(name, "mlx_rows") && rows_ok) {
+    o.mlx_rows = value;
+  } else if (!strcmp(name, "gguf_rows") && rows_ok) {
+    o.gguf_rows = value;
+  } else if (!strcmp(name, "fp8_rows") && rows_ok) {
+    o.fp8_rows = value;
+  } else {
+    return fail(GOPH_E_INVALID, "goph_set_option: unknown option or bad value %s=%d", name, value);
+  }
+  return GOPH_OK;
+}
+
+GOPH_API const char* goph_last_error(void) { return g_err; }
+
+GOPH_API int goph_sm_count(int device) {
+  if (device < 0 || device >= kMaxDevices || !device_state(device).ready) return 0;
+  return device_state(device).sm_count;
+}
+
+GOPH_API int goph_malloc(int device, uint64_t bytes, void** out_dev) {
+  clear_error();
+  if (!out_dev) return fail(GOPH_E_INVALID, "goph_malloc: nil result pointer");
+  *out_dev = nullptr;
+  if (bytes == 0) return fail(GOPH_E_INVALID, "goph_malloc: zero bytes");
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaMalloc(out_dev, bytes));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_free(int device, void* dev) {
+  clear_error();
+  if (!dev) return GOPH_OK;
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaFree(dev));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_upload(int device, void* dst_dev, const void* src_host, uint64_t bytes) {
+  clear_error();
+  if (bytes == 0) return GOPH_OK;
+  if (!dst_dev || !src_host) return fail(GOPH_E_INVALID, "goph_upload: nil pointer");
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaMemcpy(dst_dev, src_host, bytes, cudaMemcpyHostToDevice));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_download(int device, void* dst_host, const void* src_dev, uint64_t bytes) {
+  clear_error();
+  if (bytes == 0) return GOPH_OK;
+  if (!dst_host || !src_dev) return fail(GOPH_E_INVALID, "goph_download: nil pointer");
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaMemcpy(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_memset(int device, void* dst_dev, int byte, uint64_t bytes) {
+  clear_error();
+  if (bytes == 0) return GOPH_OK;
+  if (!dst_dev) return fail(GOPH_E_INVALID, "goph_memset: nil pointer");
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaMemset(dst_dev, byte, bytes));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_sync(int device) {
+  clear_error();
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaDeviceSynchronize());
+  return GOPH_OK;
+}

@@ -1,0 +1,407 @@
+"""Host-side mirror of the reference's GPU operator API (backends/nvidia/runtime) over the
+C ABI of libgoph_b200.so.
+
+Function and type names are the reference's Go names so that callers and tests read the
+same.  Differences, both deliberate: (1) errors are raised as GophError instead of being
+returned, and (2) there is no CPU fallback — where the reference's DevBuf operators fall
+back to the CPU implementation when a launch fails (runtime/mlx.go:322-349), these raise.
+Importing this module never touches the GPU; the first call that needs the library loads
+it and fails loudly if it has not been built.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgoph_b200.so")
+
+GGUF_Q8_0 = 8   # loader/gguf/gguf.go:51
+GGUF_Q4_K = 12  # loader/gguf/gguf.go:54
+
+# Every symbol include/goph_b200.h declares.
+EXPORTS = [
+    "goph_init", "goph_set_option", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_download", "goph_memset", "goph_sync",
+    "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
+    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemm_host",
+    "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
+    "goph_gguf_project", "goph_gguf_project_host",
+    "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm",
+    "goph_fp8_gemm_host",
+]
+
+
+class GophError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("goph error %d: %s" % (code, text))
+        self.code = code
+
+
+_lib = None
+_device = 0
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built: there is no fallback."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise GophError(-1, "libgoph_b200.so is not built (run __graft_entry__.build()); "
+                                "there is no CPU or PyTorch fallback")
+        L = C.CDLL(LIB_PATH)
+        L.goph_last_error.restype = C.c_char_p
+        for name in ("goph_mlx_resident_bytes", "goph_gguf_resident_bytes", "goph_fp8_resident_bytes"):
+            getattr(L, name).restype = C.c_uint64
+            getattr(L, name).argtypes = [C.c_void_p]
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise GophError(rc, lib().goph_last_error().decode("utf-8", "replace"))
+
+
+def _vp(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        return C.c_void_p(0)
+    if hasattr(stream, "cuda_stream"):
+        return C.c_void_p(stream.cuda_stream)
+    return C.c_void_p(int(stream))
+
+
+def init(device=0):
+    """nvidia.Init + EnsureContext (runtime/runtime.go:142-274)."""
+    global _device
+    _check(lib().goph_init(int(device)))
+    _device = int(device)
+    return True
+
+
+def device():
+    return _device
+
+
+def SetOption(name, value):
+    """Tuning switches (the reference's GO_PHERENCE_* environment switches, model/gpu_forward.go:24-47)."""
+    _check(lib().goph_set_option(name.encode(), int(value)))
+
+
+def SMCount():
+    return lib().goph_sm_count(_device)
+
+
+def Sync():
+    """nvidia.SyncErr (runtime/runtime.go:563)."""
+    _check(lib().goph_sync(_device))
+
+
+class Buffer:
+    """nvidia.Buffer{Ptr, Size} (runtime/runtime.go:291-295): a device allocation, Size in bytes."""
+
+    def __init__(self, ptr, size, dev, owned=True):
+        self.Ptr, self.Size, self.device, self._owned = ptr, size, dev, owned
+
+    @property
+    def n(self):
+        return self.Size // 4
+
+    def Upload(self, data):
+        data = np.ascontiguousarray(data, dtype=np.float32)
+        self._up(data)
+
+    def UploadBytes(self, data):
+        self._up(np.ascontiguousarray(data, dtype=np.uint8))
+
+    def UploadUint32(self, data):
+        self._up(np.ascontiguousarray(data, dtype=np.uint32))
+
+    def _up(self, arr):
+        if arr.nbytes > self.Size:
+            raise GophError(1, "upload of %d bytes into a %d-byte buffer" % (arr.nbytes, self.Size))
+        _check(lib().goph_upload(self.device, C.c_void_p(self.Ptr), _vp(arr), C.c_uint64(arr.nbytes)))
+
+    def Download(self, n=None, dtype=np.float32):
+        n = self.Size // np.dtype(dtype).itemsize if n is None else n
+        out = np.empty(n, dtype=dtype)
+        if out.nbytes > self.Size:
+            raise GophError(1, "download of %d bytes from a %d-byte buffer" % (out.nbytes, self.Size))
+        _check(lib().goph_download(self.device, _vp(out), C.c_void_p(self.Ptr), C.c_uint64(out.nbytes)))
+        return out
+
+    def Zero(self):
+        _check(lib().goph_memset(self.device, C.c_void_p(self.Ptr), 0, C.c_uint64(self.Size)))
+
+    def Free(self):
+        """Idempotent, like Buffer.Free (runtime/runtime.go:323-359)."""
+        if self.Ptr and self._owned:
+            _check(lib().goph_free(self.device, C.c_void_p(self.Ptr)))
+        self.Ptr, self.Size = 0, 0
+
+
+def MallocBytes(n):
+    """nvidia.MallocBytes (runtime/q8.go:166-177)."""
+    p = C.c_void_p(0)
+    _check(lib().goph_malloc(_device, C.c_uint64(int(n)), C.byref(p)))
+    return Buffer(p.value, int(n), _device)
+
+
+def Malloc(n_float32):
+    """nvidia.Malloc (runtime/runtime.go:297)."""
+    return MallocBytes(int(n_float32) * 4)
+
+
+def wrap(ptr, size_bytes):
+    """A Buffer over memory owned by someone else (e.g. a torch tensor's data_ptr())."""
+    return Buffer(int(ptr), int(size_bytes), _device, owned=False)
+
+
+def from_numpy(arr):
+    arr = np.ascontiguousarray(arr)
+    b = MallocBytes(max(arr.nbytes, 4))
+    if arr.nbytes:
+        _check(lib().goph_upload(b.device, C.c_void_p(b.Ptr), _vp(arr), C.c_uint64(arr.nbytes)))
+    return b
+
+
+# ------------------------------------------------------------------------------- MLX
+class GPUMLXWeight:
+    """nvidia.GPUMLXWeight (runtime/mlx.go:21-32)."""
+
+    def __init__(self, handle, in_dim, out_dim, gs):
+        self._h = handle
+        self.InDim, self.OutDim, self.GroupSz, self.Groups = in_dim, out_dim, gs, in_dim // gs
+
+    def ResidentBytes(self):
+        return lib().goph_mlx_resident_bytes(self._h) if self._h else 0
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_mlx_free(self._h))
+            self._h = None
+
+
+def UploadMLXWeight(weight, scales, biases, inDim, outDim, groupSize, wantNative=False):
+    """nvidia.UploadMLXWeight (runtime/mlx.go:59).  wantNative is accepted for signature
+    compatibility; there is one device layout and one kernel family here."""
+    weight = np.ascontiguousarray(weight, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    biases = np.ascontiguousarray(biases, dtype=np.float32)
+    h = C.c_void_p(0)
+    _check(lib().goph_mlx_upload(_device, _vp(weight), C.c_uint64(weight.size), _vp(scales), _vp(biases),
+                                 C.c_uint64(min(scales.size, biases.size)), int(inDim), int(outDim),
+                                 int(groupSize), C.byref(h)))
+    return GPUMLXWeight(h, int(inDim), int(outDim), int(groupSize))
+
+
+def UploadMLXWeightNative(weight, scales, biases, inDim, outDim, groupSize):
+    """nvidia.UploadMLXWeightNative (runtime/mlx.go:189)."""
+    return UploadMLXWeight(weight, scales, biases, inDim, outDim, groupSize, True)
+
+
+def _mlx_handle(w):
+    if not isinstance(w, GPUMLXWeight) or not w._h:
+        raise GophError(1, "nil or freed GPUMLXWeight")
+    return w._h
+
+
+def DequantMLX(out, w, stream=None):
+    """mlx.DequantTo on the device (backends/mlx/dequant.go:30-42)."""
+    _check(lib().goph_mlx_dequant(_mlx_handle(w), C.c_void_p(out.Ptr), C.c_uint64(out.n), _stream_ptr(stream)))
+
+
+def GemvMLX(out, x, w, stream=None):
+    """nvidia.GemvMLX (runtime/mlx.go:287)."""
+    if out is None or x is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_mlx_gemv(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                               _mlx_handle(w), _stream_ptr(stream)))
+
+
+GemvMLXDirect = GemvMLX  # nvidia.GemvMLXDirect (runtime/mlx.go:455): same kernel here.
+
+
+def GemmMLX(out, input, w, B, stream=None):
+    """nvidia.GemmMLX (runtime/mlx.go:395)."""
+    if out is None or input is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_mlx_gemm(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(input.Ptr),
+                               C.c_uint64(input.n), _mlx_handle(w), int(B), _stream_ptr(stream)))
+
+
+def GemmMLXMulti(outs, x, weights, B=1, stream=None):
+    """mlx.Gemv2To generalised (backends/mlx/gemv.go:32-60): several weights, one x, one launch."""
+    n = len(weights)
+    if n != len(outs) or n == 0:
+        raise GophError(1, "outs/weights length mismatch")
+    op = (C.c_void_p * n)(*[o.Ptr for o in outs])
+    wp = (C.c_void_p * n)(*[_mlx_handle(w) for w in weights])
+    _check(lib().goph_mlx_gemm_multi(n, op, wp, C.c_void_p(x.Ptr), C.c_uint64(x.n), int(B), _stream_ptr(stream)))
+
+
+def GemmMLXHost(x, w, B=1):
+    """Host-slice form (x and result are numpy arrays), as the reference's slice operators."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(B * w.OutDim, dtype=np.float32)
+    _check(lib().goph_mlx_gemm_host(_vp(out), C.c_uint64(out.size), _vp(x), C.c_uint64(x.size), _mlx_handle(w), int(B)))
+    return out
+
+
+# ------------------------------------------------------------------------------ GGUF
+class GPUGGUFMatrix:
+    """nvidia.GPUGGUFMatrix (runtime/gguf_matrix.go:11-17); also stands for GPUQ4KMatrix and
+    GPUQ8_0Matrix (runtime/q4k.go:39-47, q8.go:20-25)."""
+
+    def __init__(self, handle, qtype, in_dim, out_dim):
+        self._h, self.QType, self.InDim, self.OutDim = handle, qtype, in_dim, out_dim
+
+    def ResidentBytes(self):
+        return lib().goph_gguf_resident_bytes(self._h) if self._h else 0
+
+    def ProjectBatchToBuffer(self, out, x, batch, stream=None):
+        """GPUGGUFMatrix.ProjectBatchToBuffer (runtime/gguf_matrix.go:121-135)."""
+        if not self._h:
+            raise GophError(1, "nil or freed GPUGGUFMatrix")
+        if out is None or x is None:
+            raise GophError(1, "nil buffer")
+        _check(lib().goph_gguf_project(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr),
+                                       C.c_uint64(x.n), int(batch), self._h, _stream_ptr(stream)))
+
+    def Dequant(self, out, stream=None):
+        if not self._h:
+            raise GophError(1, "nil or freed GPUGGUFMatrix")
+        _check(lib().goph_gguf_dequant(self._h, C.c_void_p(out.Ptr), C.c_uint64(out.n), _stream_ptr(stream)))
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_gguf_free(self._h))
+            self._h = None
+
+
+def _upload_gguf(qtype, raw, inDim, outDim):
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    h = C.c_void_p(0)
+    _check(lib().goph_gguf_upload(_device, int(qtype), _vp(raw), C.c_uint64(raw.size), int(inDim), int(outDim),
+                                  C.byref(h)))
+    return GPUGGUFMatrix(h, int(qtype), int(inDim), int(outDim))
+
+
+def UploadGGUFMatrix(qtype, raw, inDim, outDim):
+    """nvidia.UploadGGUFMatrix (runtime/gguf_matrix.go:19-39) for a QuantMatrix{QType, Raw, InDim, OutDim}."""
+    return _upload_gguf(qtype, raw, inDim, outDim)
+
+
+def UploadQ4KMatrixRaw(raw, inDim, outDim):
+    """nvidia.UploadQ4KMatrixRaw / UploadQ4KMatrixRows (runtime/q4k.go:163-172)."""
+    return _upload_gguf(GGUF_Q4_K, raw, inDim, outDim)
+
+
+UploadQ4KMatrixRows = UploadQ4KMatrixRaw
+
+
+def UploadQ8_0MatrixRows(raw, inDim, outDim):
+    """nvidia.UploadQ8_0MatrixRows (runtime/q8.go:109)."""
+    return _upload_gguf(GGUF_Q8_0, raw, inDim, outDim)
+
+
+def _gguf_host(x, batch, m):
+    if not isinstance(m, GPUGGUFMatrix) or not m._h:
+        raise GophError(1, "nil or freed GPUGGUFMatrix")
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(batch * m.OutDim, dtype=np.float32)
+    _check(lib().goph_gguf_project_host(_vp(out), C.c_uint64(out.size), _vp(x), C.c_uint64(x.size), int(batch), m._h))
+    return out
+
+
+def GemvQ4K(x, m):
+    """nvidia.GemvQ4K (runtime/q4k.go:571) with host slices; returns out."""
+    return _gguf_host(x, 1, m)
+
+
+def GemvQ4KBatch(x, batch, m):
+    """nvidia.GemvQ4KBatch (runtime/q4k.go:533)."""
+    return _gguf_host(x, batch, m)
+
+
+GemvQ8_0 = GemvQ4K            # nvidia.GemvQ8_0 (runtime/q8.go:277)
+GemvQ8_0Batch = GemvQ4KBatch  # nvidia.GemvQ8_0Batch (runtime/q8.go:239)
+
+
+def GemvQ4KBatchToBuffer(out, x, batch, m, stream=None):
+    """nvidia.GemvQ4KBatchToBuffer (runtime/q4k.go:351)."""
+    m.ProjectBatchToBuffer(out, x, batch, stream)
+
+
+GemvQ8_0BatchToBuffer = GemvQ4KBatchToBuffer  # runtime/q8.go:225
+
+
+# ------------------------------------------------------------------------------- FP8
+class GPUFP8E4M3Linear:
+    """nvidia.GPUFP8E4M3Linear (runtime/fp8.go:35-44)."""
+
+    def __init__(self, handle, out_dim, in_dim):
+        self._h, self.OutDim, self.InDim = handle, out_dim, in_dim
+
+    def ResidentBytes(self):
+        return lib().goph_fp8_resident_bytes(self._h) if self._h else 0
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_fp8_free(self._h))
+            self._h = None
+
+
+def UploadFP8E4M3Linear(weight, scale, bias, outDim, inDim):
+    """nvidia.UploadFP8E4M3Linear (runtime/fp8.go:48)."""
+    weight = np.ascontiguousarray(weight, dtype=np.uint8)
+    scale = np.ascontiguousarray(scale, dtype=np.float32)
+    bias_p, bias_n = C.c_void_p(0), 0
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+        bias_p, bias_n = _vp(bias), bias.size
+    h = C.c_void_p(0)
+    _check(lib().goph_fp8_upload(_device, _vp(weight), C.c_uint64(weight.size), _vp(scale), int(scale.size),
+                                 bias_p, int(bias_n), int(outDim), int(inDim), C.byref(h)))
+    return GPUFP8E4M3Linear(h, int(outDim), int(inDim))
+
+
+def _fp8_handle(w):
+    if not isinstance(w, GPUFP8E4M3Linear) or not w._h:
+        raise GophError(1, "nil or freed GPUFP8E4M3Linear")
+    return w._h
+
+
+def GemmFP8E4M3Buffer(out, x, batch, w, stream=None):
+    """nvidia.GemmFP8E4M3Buffer (runtime/fp8.go:271)."""
+    if out is None or x is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_fp8_gemm(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                               int(batch), _fp8_handle(w), _stream_ptr(stream)))
+
+
+def GemvFP8E4M3Buffer(out, x, w, stream=None):
+    """nvidia.GemvFP8E4M3Buffer (runtime/fp8.go:995)."""
+    GemmFP8E4M3Buffer(out, x, 1, w, stream)
+
+
+def GemmFP8E4M3(x, batch, w):
+    """nvidia.GemmFP8E4M3 (runtime/fp8.go:180) with host slices; returns out."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(batch * w.OutDim, dtype=np.float32)
+    _check(lib().goph_fp8_gemm_host(_vp(out), C.c_uint64(out.size), _vp(x), C.c_uint64(x.size), int(batch), _fp8_handle(w)))
+    return out
+
+
+def GemvFP8E4M3(x, w):
+    """nvidia.GemvFP8E4M3 (runtime/fp8.go:158)."""
+    return GemmFP8E4M3(x, 1, w)
+
+
+def DequantFP8E4M3(out, w, stream=None):
+    """fp8.Linear.DequantRowTo for every row (backends/simd/quant/fp8/fp8.go:181-198)."""
+    _check(lib().goph_fp8_dequant(_fp8_handle(w), C.c_void_p(out.Ptr), C.c_uint64(out.n), _stream_ptr(stream)))

@@ -1,0 +1,162 @@
+/* goph_b200.h — C ABI of libgoph_b200.so: B200 (sm_100a) kernels for the quantized
+ * matrix-product path of rcarmo/go-pherence.
+ *
+ * The library replaces the PTX modules that the reference loads at run time in
+ * backends/nvidia/runtime and the driver calls around them.  Every entry point takes
+ * plain integers, floats and pointers so that the reference's FFI (purego, no cgo) can
+ * bind it directly; the Go-side operator signatures stay as they are.  Each declaration
+ * cites the reference interface it stands behind (file:line inside the reference
+ * repository).
+ *
+ * Conventions
+ *   - Return value: 0 on success, otherwise a GOPH_E_* code; goph_last_error() gives the
+ *     text (with the CUDA error name when there is one).  Nothing throws, nothing aborts.
+ *   - Malformed arguments are rejected before any allocation or launch, as the reference
+ *     does (backends/nvidia/runtime/mlx.go:34-55, :231-249).
+ *   - There is NO CPU fallback: where the reference's DevBuf operators silently run the
+ *     CPU implementation on failure (mlx.go:322-349) this library returns an error.
+ *   - Pointers named *_dev are device addresses on the handle's GPU; all others are host.
+ *   - `stream` is a cudaStream_t / CUstream passed as void*; NULL is the legacy default
+ *     stream, which is what the reference launches on (runtime.go:676).
+ *   - Calls may come from any OS thread; the library sets the device it needs on every
+ *     call and keeps no thread-local state besides the error text.  Like the reference
+ *     (global cudaMu, runtime.go:134-139) callers serialise calls that share a handle.
+ *   - Matrices are row-major; x is [batch, in_dim], out is [batch, out_dim], both f32.
+ */
+#ifndef GOPH_B200_H
+#define GOPH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  GOPH_OK = 0,
+  GOPH_E_INVALID = 1, /* malformed argument (nil, short buffer, bad dims, overflow) */
+  GOPH_E_CUDA = 2,    /* a CUDA call failed; text carries the cudaError name */
+  GOPH_E_NOINIT = 3,  /* goph_init was not called for this device */
+  GOPH_E_UNSUPPORTED = 4,
+  GOPH_E_NOMEM = 5
+};
+
+/* GGUF tensor type ids accepted by goph_gguf_upload (loader/gguf/gguf.go:51,54). */
+enum { GOPH_GGUF_Q8_0 = 8, GOPH_GGUF_Q4_K = 12 };
+
+typedef struct goph_mlx_weight goph_mlx_weight;   /* nvidia.GPUMLXWeight      (runtime/mlx.go:21-32)   */
+typedef struct goph_gguf_matrix goph_gguf_matrix; /* nvidia.GPUGGUFMatrix / GPUQ4KMatrix / GPUQ8_0Matrix
+                                                     (runtime/gguf_matrix.go:11-17, q4k.go:39-47, q8.go:20-25) */
+typedef struct goph_fp8_linear goph_fp8_linear;   /* nvidia.GPUFP8E4M3Linear  (runtime/fp8.go:35-44)   */
+
+/* ---- runtime: replaces Init/EnsureContext/Malloc/Upload/Download/Sync -------------- */
+
+/* nvidia.Init + EnsureContext (runtime/runtime.go:142-274): bind `device`, create the
+ * primary context, read the SM count.  Idempotent per device. */
+int goph_init(int device);
+/* Text of the last error on the calling thread ("" if none). */
+const char* goph_last_error(void);
+/* nvidia.SMCount (runtime/runtime.go:285); 0 if the device is not initialised. */
+int goph_sm_count(int device);
+
+/* Tuning switches.  The reference reads its own from GO_PHERENCE_* environment variables at
+ * the call sites (model/gpu_forward.go:24-47, :776-785); here they are set by name:
+ *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
+ *                 1 one shift per nibble pair (default), 2 integer conversion
+ *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
+ * Unknown names and values out of range are rejected.  Results stay within the product
+ * tolerance for every setting. */
+int goph_set_option(const char* name, int value);
+
+/* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
+int goph_malloc(int device, uint64_t bytes, void** out_dev);
+int goph_free(int device, void* dev);
+/* Buffer.Upload / UploadBytes / UploadUint32 / Download (runtime/runtime.go:382-525):
+ * synchronous copies. */
+int goph_upload(int device, void* dst_dev, const void* src_host, uint64_t bytes);
+int goph_download(int device, void* dst_host, const void* src_dev, uint64_t bytes);
+int goph_memset(int device, void* dst_dev, int byte, uint64_t bytes);
+/* nvidia.Sync / SyncErr (runtime/runtime.go:551-577). */
+int goph_sync(int device);
+
+/* ---- MLX 4-bit affine weights (backends/mlx, backends/nvidia/runtime/mlx.go) -------- */
+
+/* nvidia.UploadMLXWeight / UploadMLXWeightNative (runtime/mlx.go:59, :189).
+ * weight: [out_dim, in_dim/8] uint32, element e of a word in bits 4e..4e+3;
+ * scales, biases: [out_dim, in_dim/group_size] f32.  *_len are element counts of the
+ * caller's slices (validated like validateMLXUploadInputs, mlx.go:34-55).
+ * Scales and biases are kept as bf16 on the device when every value is exactly
+ * representable in bf16 (checkpoints store them so; backends/mlx/load.go:148-157 widens
+ * them), otherwise as f32; either way the arithmetic uses the exact f32 values. */
+int goph_mlx_upload(int device, const uint32_t* weight, uint64_t weight_len, const float* scales,
+                    const float* biases, uint64_t scale_len, int in_dim, int out_dim,
+                    int group_size, goph_mlx_weight** out);
+/* Same, from buffers already on the device (no host copy). */
+int goph_mlx_upload_dev(int device, const uint32_t* weight_dev, const float* scales_dev,
+                        const float* biases_dev, int in_dim, int out_dim, int group_size,
+                        goph_mlx_weight** out);
+/* GPUMLXWeight.Free (runtime/mlx.go:252-275); NULL is accepted. */
+int goph_mlx_free(goph_mlx_weight* w);
+/* Bytes the weight occupies on the device (packed words + scale/bias table). */
+uint64_t goph_mlx_resident_bytes(const goph_mlx_weight* w);
+/* mlx.DequantTo on the device (backends/mlx/dequant.go:30-42): out_dev [out_dim,in_dim]
+ * f32, bit-identical to float32(nibble)*scale + bias with two roundings. */
+int goph_mlx_dequant(const goph_mlx_weight* w, float* out_dev, uint64_t out_len, void* stream);
+/* nvidia.GemvMLX / GemvMLXDirect (runtime/mlx.go:287-350, :455-488): out = W·x. */
+int goph_mlx_gemv(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                  const goph_mlx_weight* w, void* stream);
+/* nvidia.GemmMLX (runtime/mlx.go:395-431): x [batch,in] → out [batch,out]. */
+int goph_mlx_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                  const goph_mlx_weight* w, int batch, void* stream);
+/* mlx.Gemv2To generalised (backends/mlx/gemv.go:32-60): n ≤ 8 weights with equal in_dim and
+ * group size share one x [batch,in]; outs_dev[i] is [batch, out_dim_i].  One launch. */
+int goph_mlx_gemm_multi(int n, float* const* outs_dev, const goph_mlx_weight* const* ws,
+                        const float* x_dev, uint64_t x_len, int batch, void* stream);
+/* Host-slice form, as nvidia.GemvQ4K/GemmFP8E4M3 take Go slices (runtime/q4k.go:571,
+ * fp8.go:180): copies x in, runs, copies out back, synchronises. */
+int goph_mlx_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
+                       const goph_mlx_weight* w, int batch);
+
+/* ---- GGUF Q8_0 / Q4_K matrices (loader/gguf/quant_matrix.go, runtime/{q8,q4k,gguf_matrix}.go) */
+
+/* nvidia.UploadGGUFMatrix / UploadQ4KMatrixRaw / UploadQ8_0MatrixRows
+ * (runtime/gguf_matrix.go:19-39, q4k.go:172, q8.go:109): raw is the GGUF row-major block
+ * stream (34-byte Q8_0 blocks or 144-byte Q4_K super-blocks), out_dim rows of in_dim. */
+int goph_gguf_upload(int device, int qtype, const uint8_t* raw, uint64_t raw_len, int in_dim,
+                     int out_dim, goph_gguf_matrix** out);
+int goph_gguf_free(goph_gguf_matrix* m);
+uint64_t goph_gguf_resident_bytes(const goph_gguf_matrix* m);
+/* QuantMatrix.DequantRowTo for every row (loader/gguf/quant_matrix.go:42-60), bit-exact. */
+int goph_gguf_dequant(const goph_gguf_matrix* m, float* out_dev, uint64_t out_len, void* stream);
+/* GPUGGUFMatrix.ProjectBatchToBuffer / GemvQ4KBatchToBuffer / GemvQ8_0BatchToBuffer
+ * (runtime/gguf_matrix.go:121-135, q4k.go:351, q8.go:225): x [batch,in] f32 → out [batch,out]. */
+int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                      int batch, const goph_gguf_matrix* m, void* stream);
+/* nvidia.GemvQ4K / GemvQ4KBatch / GemvQ8_0 / GemvQ8_0Batch with Go slices
+ * (runtime/q4k.go:533-595, q8.go:239-301). */
+int goph_gguf_project_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
+                           int batch, const goph_gguf_matrix* m);
+
+/* ---- FP8 E4M3 linears (backends/simd/quant/fp8, runtime/fp8.go) ---------------------- */
+
+/* nvidia.UploadFP8E4M3Linear (runtime/fp8.go:48): weight [out_dim,in_dim] E4M3FN bytes,
+ * scale of length 1 (per tensor) or out_dim (per row), bias NULL or [out_dim]. */
+int goph_fp8_upload(int device, const uint8_t* weight, uint64_t weight_len, const float* scale,
+                    int scale_len, const float* bias, int bias_len, int out_dim, int in_dim,
+                    goph_fp8_linear** out);
+int goph_fp8_free(goph_fp8_linear* w);
+uint64_t goph_fp8_resident_bytes(const goph_fp8_linear* w);
+/* fp8.Linear.DequantRowTo for every row (backends/simd/quant/fp8/fp8.go:181-198), bit-exact. */
+int goph_fp8_dequant(const goph_fp8_linear* w, float* out_dev, uint64_t out_len, void* stream);
+/* nvidia.GemvFP8E4M3Buffer / GemmFP8E4M3Buffer (runtime/fp8.go:995, :271). */
+int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
+                  const goph_fp8_linear* w, void* stream);
+/* nvidia.GemvFP8E4M3 / GemmFP8E4M3 with Go slices (runtime/fp8.go:158, :180). */
+int goph_fp8_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
+                       int batch, const goph_fp8_linear* w);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GOPH_B200_H */
