@@ -50,6 +50,9 @@ inline bool mul_ok(uint64_t a, uint64_t b, uint64_t* out) {
 
 // Tuning switches set through goph_set_option.
 struct Options {
+  int mlx_path = 0;    // 0 by shape, 1 CUDA-core streaming kernel, 2 tensor-core kernel
+  int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
+  int mlx_pieces = 3;  // bf16 pieces per activation on the tensor-core path (3 exact f32, 1 bf16-valued x)
   int mlx_unpack = 1;
   int mlx_rows = 0, gguf_rows = 0, fp8_rows = 0;
 };
@@ -69,6 +72,7 @@ struct goph_mlx_weight {
   int sb_bf16;          // 1: sb is __nv_bfloat162 {scale,bias}; 0: float2 {scale,bias}
   uint32_t* qweight;    // [out_dim][in_dim/8]
   void* sb;             // [out_dim][groups]
+  void* tmaps;          // host copy of the two TMA tensor maps (tensor-core path) or nullptr
   uint64_t bytes;
 };
 

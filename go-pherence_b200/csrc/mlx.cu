@@ -28,6 +28,7 @@
 #include <vector>
 
 #include "goph_internal.cuh"
+#include "mlx_mma.cuh"
 
 namespace goph {
 
@@ -492,6 +493,15 @@ static int launch_generic(const goph_mlx_weight* w, float* out, const float* x, 
 static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const* ws, const float* x, int batch,
                         cudaStream_t stream) {
   const goph_mlx_weight* w0 = ws[0];
+  if (options().mlx_path == 2) {
+    bool all = true;
+    for (int i = 0; i < n; ++i) all = all && ws[i]->tmaps && ((uintptr_t)x % 16) == 0;
+    if (all) {
+      for (int i = 0; i < n; ++i)
+        if (int rc = mlx_mma_launch(ws[i], outs[i], x, batch, options().mlx_pieces, stream)) return rc;
+      return GOPH_OK;
+    }
+  }
   bool uniform = true;
   for (int i = 0; i < n; ++i)
     uniform = uniform && fast_path_ok(ws[i]) && ws[i]->sb_bf16 == w0->sb_bf16;
@@ -539,6 +549,7 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
   h->out_dim = out_dim;
   h->group_size = gs;
   h->groups = (int)groups;
+  h->tmaps = nullptr;
   float *ds = nullptr, *db = nullptr;
   int* flag = nullptr;
   auto cleanup = [&](int rc) {
@@ -583,6 +594,10 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
   UP(cudaDeviceSynchronize());
 #undef UP
   h->bytes = want_w * 4 + want_s * (h->sb_bf16 ? 4 : 8);
+  if (mlx_mma_supported(h) && mlx_mma_make_maps(h) != GOPH_OK) {
+    h->tmaps = nullptr;  // the CUDA-core kernels need no tensor maps
+    clear_error();
+  }
   *out = h;
   return cleanup(GOPH_OK);
 }
@@ -637,8 +652,17 @@ GOPH_API int goph_mlx_free(goph_mlx_weight* w) {
   if (int rc = use_device(w->device)) return rc;
   cudaFree(w->qweight);
   cudaFree(w->sb);
+  mlx_mma_free_maps(w);
   w->magic = 0;
   delete w;
+  return GOPH_OK;
+}
+
+GOPH_API int goph_kernel_status(int device, int* out_status) {
+  clear_error();
+  if (!out_status) return fail(GOPH_E_INVALID, "goph_kernel_status: nil result pointer");
+  if (int rc = use_device(device)) return rc;
+  *out_status = mlx_mma_status(device);
   return GOPH_OK;
 }
 

@@ -1,0 +1,112 @@
+"""Per-shape kernel throughput of the quantized products, measured with CUDA events.
+
+    python go-pherence_b200/microbench.py --format mlx4 --out 4096 --in 4096 [--batch 1]
+           [--opt mlx_unpack=0] [--launches 200] [--copies N]
+
+The launches are captured once into a CUDA graph and replayed, so the figure is device time
+per launch, not the host's launch rate.  The weight is uploaded `copies` times (default: enough copies to exceed 512 MB, four times
+the L2) and consecutive launches walk through the copies, so every launch streams its weights
+from HBM.  Prints one JSON line: microseconds per launch, GB/s of algorithmic bytes and the
+fraction of the measured HBM copy bandwidth.
+"""
+import argparse
+import json
+import os
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+from __graft_entry__ import load_package  # noqa: E402
+
+
+def algorithmic_bytes(fmt, out_dim, in_dim, batch):
+    per_weight = {"mlx4": 0.5625, "q4k": 0.5625, "q8_0": 1.0625, "fp8": 1.0}[fmt]
+    extra = 4 * out_dim if fmt == "fp8" else 0
+    return out_dim * in_dim * per_weight + extra + batch * in_dim * 4 + batch * out_dim * 4
+
+
+def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=10):
+    import torch
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(0)
+    for k, v in opts:
+        rt.SetOption(k, v)
+    nbytes = algorithmic_bytes(fmt, out_dim, in_dim, batch)
+    if copies <= 0:
+        copies = max(2, int(512e6 // nbytes) + 1)
+    copies = min(copies, 256)
+    handles = []
+    if fmt == "mlx4":
+        w, s, b = syn.mlx_weight("mb", out_dim, in_dim, 64)
+        handles = [rt.UploadMLXWeight(w, s, b, in_dim, out_dim, 64, True) for _ in range(copies)]
+    elif fmt in ("q4k", "q8_0"):
+        qt = rt.GGUF_Q4_K if fmt == "q4k" else rt.GGUF_Q8_0
+        raw = (syn.q4k_matrix if fmt == "q4k" else syn.q8_0_matrix)("mb", out_dim, in_dim)
+        handles = [rt.UploadGGUFMatrix(qt, raw, in_dim, out_dim) for _ in range(copies)]
+    else:
+        w = torch.randn(out_dim, in_dim).clamp_(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy().reshape(-1)
+        sc = syn.fp8_linear("mb", 8, 16)[1][:1].repeat(out_dim)
+        handles = [rt.UploadFP8E4M3Linear(w, sc, None, out_dim, in_dim) for _ in range(copies)]
+    x = torch.from_numpy(syn.activations("mb", batch * in_dim)).cuda()
+    out = torch.empty(batch * out_dim, dtype=torch.float32, device="cuda")
+    xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
+    stream = torch.cuda.current_stream()
+
+    def launch(h):
+        if fmt == "mlx4":
+            rt.GemmMLX(ob, xb, h, batch, stream)
+        elif fmt == "fp8":
+            rt.GemmFP8E4M3Buffer(ob, xb, batch, h, stream)
+        else:
+            h.ProjectBatchToBuffer(ob, xb, batch, stream)
+
+    for i in range(warmup):
+        launch(handles[i % copies])
+    torch.cuda.synchronize()
+    # the launches are replayed from a CUDA graph so the host's launch rate is not what is timed
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        stream = torch.cuda.current_stream()
+        for i in range(launches):
+            launch(handles[i % copies])
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+    peak = 6650.0
+    pk = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = float(json.load(open(pk))["hbm_gbs"])
+    gbs = nbytes / us / 1e3
+    res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "opts": dict(opts), "copies": copies,
+           "us_per_launch": round(us, 3), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
+           "bytes": nbytes}
+    for h in handles:
+        h.Free()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q8_0", "fp8"])
+    ap.add_argument("--out", type=int, default=4096)
+    ap.add_argument("--in", dest="in_dim", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--launches", type=int, default=200)
+    ap.add_argument("--copies", type=int, default=0)
+    ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
+    args = ap.parse_args()
+    opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
+    print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts)))
+
+
+if __name__ == "__main__":
+    main()

@@ -21,7 +21,7 @@ GGUF_Q4_K = 12  # loader/gguf/gguf.go:54
 
 # Every symbol include/goph_b200.h declares.
 EXPORTS = [
-    "goph_init", "goph_set_option", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_init", "goph_set_option", "goph_kernel_status", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
     "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemm_host",
@@ -90,6 +90,13 @@ def device():
 def SetOption(name, value):
     """Tuning switches (the reference's GO_PHERENCE_* environment switches, model/gpu_forward.go:24-47)."""
     _check(lib().goph_set_option(name.encode(), int(value)))
+
+
+def KernelStatus():
+    """0 unless a bounded device-side wait has given up (see goph_kernel_status)."""
+    v = C.c_int(0)
+    _check(lib().goph_kernel_status(_device, C.byref(v)))
+    return v.value
 
 
 def SMCount():

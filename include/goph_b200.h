@@ -62,12 +62,22 @@ int goph_sm_count(int device);
 
 /* Tuning switches.  The reference reads its own from GO_PHERENCE_* environment variables at
  * the call sites (model/gpu_forward.go:24-47, :776-785); here they are set by name:
+ *   "mlx_path"    kernel family for MLX weights: 0 chosen by shape (default), 1 CUDA-core
+ *                 streaming kernel, 2 tensor-core (tcgen05) kernel where the shape allows it
+ *   "mlx_pieces"  bf16 pieces each activation is split into on the tensor-core path: 3 (default,
+ *                 exact for any f32) or 1 (the caller guarantees x holds bf16 values)
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 1 one shift per nibble pair (default), 2 integer conversion
  *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
  * Unknown names and values out of range are rejected.  Results stay within the product
  * tolerance for every setting. */
 int goph_set_option(const char* name, int value);
+/* Device-side health word.  Every wait inside a kernel is bounded; a wait that gives up
+ * stores a non-zero code here and the kernel winds down instead of hanging.  0 = no wait
+ * has ever given up on this device.  (The reference localises device faults by synchronising
+ * after every launch under GO_PHERENCE_CUDA_LAUNCH_CHECK, runtime/runtime.go:687-694.)
+ * Synchronises with the device. */
+int goph_kernel_status(int device, int* out_status);
 
 /* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
 int goph_malloc(int device, uint64_t bytes, void** out_dev);
