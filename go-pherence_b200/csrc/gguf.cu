@@ -50,9 +50,9 @@ struct Q4KFmt {
     t.sd = __fmul_rn((float)(f & 63u), f16_bits_to_f32(h.x & 0xFFFFu));
     t.md = __fmul_rn((float)(f >> 6), f16_bits_to_f32(h.x >> 16));
   }
-  // One shift serves two nibbles: odd positions read as 16+n, even positions as 256+n.
+  // Every nibble is moved to the top mantissa bits under 2^4 and reads as 16+n.
   static __device__ __forceinline__ float2 consts(float se, float so) {
-    return make_float2(256.f * se + 16.f * so, se + so);
+    return make_float2(16.f * (se + so), se + so);
   }
   template <int M>
   static __device__ __forceinline__ void dot(const Row& t, const float4 (&xv)[M][8], const float2 (&c)[M],
@@ -63,12 +63,11 @@ struct Q4KFmt {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       uint32_t w = k == 0 ? t.q.x : k == 1 ? t.q.y : k == 2 ? t.q.z : t.q.w;
-      constexpr uint32_t MA = 0x00780000u, EA = 0x41800000u, MB = 0x00078000u, EB = 0x43800000u;
-      uint32_t t0 = w << 15, t1 = w << 7, t2 = w >> 1, t3 = w >> 9;
-      float2 f0 = make_float2(__uint_as_float((t0 & MB) | EB), __uint_as_float((t0 & MA) | EA));
-      float2 f1 = make_float2(__uint_as_float((t1 & MB) | EB), __uint_as_float((t1 & MA) | EA));
-      float2 f2 = make_float2(__uint_as_float((t2 & MB) | EB), __uint_as_float((t2 & MA) | EA));
-      float2 f3 = make_float2(__uint_as_float((t3 & MB) | EB), __uint_as_float((t3 & MA) | EA));
+      constexpr uint32_t MK = 0x00780000u, EX = 0x41800000u;
+      float2 f0 = make_float2(__uint_as_float(((w << 19) & MK) | EX), __uint_as_float(((w << 15) & MK) | EX));
+      float2 f1 = make_float2(__uint_as_float(((w << 11) & MK) | EX), __uint_as_float(((w << 7) & MK) | EX));
+      float2 f2 = make_float2(__uint_as_float(((w << 3) & MK) | EX), __uint_as_float(((w >> 1) & MK) | EX));
+      float2 f3 = make_float2(__uint_as_float(((w >> 5) & MK) | EX), __uint_as_float(((w >> 9) & MK) | EX));
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float4 xa = xv[m][2 * k], xb = xv[m][2 * k + 1];

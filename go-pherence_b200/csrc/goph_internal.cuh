@@ -50,10 +50,12 @@ inline bool mul_ok(uint64_t a, uint64_t b, uint64_t* out) {
 
 // Tuning switches set through goph_set_option.
 struct Options {
-  int mlx_path = 0;    // 0 by shape, 1 CUDA-core streaming kernel, 2 tensor-core kernel
+  int mlx_layout = 0;  // layout chosen at upload: 0 tiled when the shape allows it, 1 always row-major
+  int mlx_dbg = 0;     // tuning aid: leaves out parts of the tensor-core kernel (results are then wrong)
+  int mlx_probe = 0;   // 1: CTA 0 of the tensor-core kernel records per-role wait cycles
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
-  int mlx_pieces = 3;  // bf16 pieces per activation on the tensor-core path (3 exact f32, 1 bf16-valued x)
-  int mlx_unpack = 1;
+  int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
+  int mlx_unpack = 0;
   int mlx_rows = 0, gguf_rows = 0, fp8_rows = 0;
 };
 Options& options();
@@ -63,8 +65,14 @@ constexpr int kSmemBudget = 200 * 1024;
 
 }  // namespace goph
 
-// MLX weight resident on one GPU.  Packed words are kept in the checkpoint's own
-// row-major order; scale and bias of a group are interleaved so one load fetches both.
+// MLX weight resident on one GPU, in one of two layouts:
+//  row-major  packed words in the checkpoint's own order [out][in/8] (qweight) plus a table of
+//             {scale,bias} pairs [out][groups] (sb) — the CUDA-core kernels' layout;
+//  tiled      (tiled != nullptr; qweight and sb are then null) one 18 KiB block per 128 rows x
+//             256 elements, blocks ordered [tile][chunk]: 128 rows x 128 packed bytes stored as the
+//             shared-memory image the tensor-core kernel wants (16-byte unit u of row r at
+//             r*128 + ((u ^ (r & 7)) << 4)), then 128 x 16 bytes of bf16 {scale,bias} pairs.  Rows
+//             past out_dim are zero.  One stage of the kernel is one contiguous block.
 struct goph_mlx_weight {
   uint32_t magic;
   int device;
@@ -72,7 +80,7 @@ struct goph_mlx_weight {
   int sb_bf16;          // 1: sb is __nv_bfloat162 {scale,bias}; 0: float2 {scale,bias}
   uint32_t* qweight;    // [out_dim][in_dim/8]
   void* sb;             // [out_dim][groups]
-  void* tmaps;          // host copy of the two TMA tensor maps (tensor-core path) or nullptr
+  uint8_t* tiled;       // tiled layout or nullptr
   uint64_t bytes;
 };
 

@@ -363,6 +363,23 @@ __global__ void mlx_dequant_kernel(const uint32_t* __restrict__ w, const void* _
   o[1] = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// mlx.DequantTo from the tiled layout (bf16 table, group size 64).
+__global__ void mlx_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, float* __restrict__ out,
+                                         size_t total_words, int words_per_row, int nchunks) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_words) return;
+  int row = (int)(i / words_per_row), j = (int)(i - (size_t)row * words_per_row);
+  uint32_t q = *reinterpret_cast<const uint32_t*>(tiled + mlx_tiled_word_offset(row, j * 8, nchunks));
+  uint32_t t = *reinterpret_cast<const uint32_t*>(tiled + mlx_tiled_meta_offset(row, j * 8, nchunks));
+  float s = __uint_as_float(t << 16), b = __uint_as_float(t & 0xFFFF0000u);
+  float v[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = __fadd_rn(__fmul_rn((float)((q >> (4 * e)) & 0xF), s), b);
+  float4* o = reinterpret_cast<float4*>(out + i * 8);
+  o[0] = make_float4(v[0], v[1], v[2], v[3]);
+  o[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
 // Upload helpers: decide whether every scale/bias is a bf16 value, then interleave.
 __global__ void mlx_sb_probe_kernel(const float* __restrict__ s, const float* __restrict__ b, size_t n,
                                     int* __restrict__ not_bf16) {
@@ -413,7 +430,7 @@ static MlxKernel pick_kernel(int R, int M, int mode, bool bf16) {
 }
 
 static bool valid_handle(const goph_mlx_weight* w) {
-  return w && w->magic == kMagicMLX && w->qweight && w->sb && w->in_dim > 0 && w->out_dim > 0 &&
+  return w && w->magic == kMagicMLX && (w->tiled || (w->qweight && w->sb)) && w->in_dim > 0 && w->out_dim > 0 &&
          w->group_size > 0 && w->groups == w->in_dim / w->group_size;
 }
 
@@ -493,14 +510,18 @@ static int launch_generic(const goph_mlx_weight* w, float* out, const float* x, 
 static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const* ws, const float* x, int batch,
                         cudaStream_t stream) {
   const goph_mlx_weight* w0 = ws[0];
-  if (options().mlx_path == 2) {
-    bool all = true;
-    for (int i = 0; i < n; ++i) all = all && ws[i]->tmaps && ((uintptr_t)x % 16) == 0;
-    if (all) {
-      for (int i = 0; i < n; ++i)
-        if (int rc = mlx_mma_launch(ws[i], outs[i], x, batch, options().mlx_pieces, stream)) return rc;
-      return GOPH_OK;
+  bool any_tiled = false;
+  for (int i = 0; i < n; ++i) any_tiled = any_tiled || ws[i]->tiled;
+  if (any_tiled) {
+    // tiled weights run on the tensor cores; row-major ones in the same call take their own path
+    for (int i = 0; i < n; ++i) {
+      const goph_mlx_weight* one = ws[i];
+      float* o = outs[i];
+      int rc = one->tiled ? mlx_mma_launch(one, o, x, batch, options().mlx_digits, stream)
+                          : mlx_products(1, &o, &one, x, batch, stream);
+      if (rc) return rc;
     }
+    return GOPH_OK;
   }
   bool uniform = true;
   for (int i = 0; i < n; ++i)
@@ -549,7 +570,7 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
   h->out_dim = out_dim;
   h->group_size = gs;
   h->groups = (int)groups;
-  h->tmaps = nullptr;
+  h->tiled = nullptr;
   float *ds = nullptr, *db = nullptr;
   int* flag = nullptr;
   auto cleanup = [&](int rc) {
@@ -561,6 +582,7 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
     if (rc) {
       cudaFree(h->qweight);
       cudaFree(h->sb);
+      cudaFree(h->tiled);
       delete h;
     }
     return rc;
@@ -594,9 +616,12 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
   UP(cudaDeviceSynchronize());
 #undef UP
   h->bytes = want_w * 4 + want_s * (h->sb_bf16 ? 4 : 8);
-  if (mlx_mma_supported(h) && mlx_mma_make_maps(h) != GOPH_OK) {
-    h->tmaps = nullptr;  // the CUDA-core kernels need no tensor maps
-    clear_error();
+  if (options().mlx_layout == 0 && mlx_mma_supported(h)) {
+    if (int rc = mlx_mma_make_tiled(h)) return cleanup(rc);
+    cudaFree(h->qweight);
+    cudaFree(h->sb);
+    h->qweight = nullptr;
+    h->sb = nullptr;
   }
   *out = h;
   return cleanup(GOPH_OK);
@@ -652,7 +677,7 @@ GOPH_API int goph_mlx_free(goph_mlx_weight* w) {
   if (int rc = use_device(w->device)) return rc;
   cudaFree(w->qweight);
   cudaFree(w->sb);
-  mlx_mma_free_maps(w);
+  cudaFree(w->tiled);
   w->magic = 0;
   delete w;
   return GOPH_OK;
@@ -664,6 +689,12 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   if (int rc = use_device(device)) return rc;
   *out_status = mlx_mma_status(device);
   return GOPH_OK;
+}
+
+// Not part of the public header: tuning aid used by the in-tree microbenchmarks.
+GOPH_API int goph_debug_probe(int device, long long* out32) {
+  if (use_device(device)) return -1;
+  return mlx_mma_probe(device, out32);
 }
 
 GOPH_API uint64_t goph_mlx_resident_bytes(const goph_mlx_weight* w) {
@@ -682,7 +713,9 @@ GOPH_API int goph_mlx_dequant(const goph_mlx_weight* w, float* out_dev, uint64_t
   size_t words = (size_t)w->out_dim * (w->in_dim / 8);
   unsigned blocks = (unsigned)((words + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
-  if (w->sb_bf16)
+  if (w->tiled)
+    mlx_dequant_tiled_kernel<<<blocks, 256, 0, s>>>(w->tiled, out_dev, words, w->in_dim / 8, w->in_dim / 256);
+  else if (w->sb_bf16)
     mlx_dequant_kernel<true><<<blocks, 256, 0, s>>>(w->qweight, w->sb, out_dev, words, w->in_dim / 8,
                                                     w->group_size, w->groups);
   else

@@ -1,33 +1,39 @@
-// MLX 4-bit weights on the 5th-generation tensor cores (tcgen05 + TMEM), for any batch.
+// MLX 4-bit weights on the 5th-generation tensor cores (tcgen05 + TMEM), integer arithmetic.
 //
-// Why a GEMV goes to the tensor pipe: at B200's 7.7 TB/s one SM has to consume ~47 nibbles
-// per clock.  Turning a nibble into an f32 and multiplying it on the CUDA cores costs one
-// logic op per nibble on the half-rate integer pipe plus the FMA, which caps a CUDA-core
-// kernel well under the HBM roofline.  Here a logic op makes TWO bf16 operands, the products
-// run on the tensor pipe, and the CUDA cores only apply the per-group scales.
+// Why a GEMV goes to the tensor pipe: at B200's HBM rate one SM has to consume ~47 nibbles
+// per clock, and its integer/logic pipe issues 64 lane-ops per clock.  Any formulation that
+// turns each nibble into a float on the CUDA cores needs at least one logic op per nibble plus
+// the FMA and cannot reach the HBM roofline.  Here the nibbles stay integers: three logic ops
+// turn a packed word into eight unsigned bytes, the tensor cores multiply them (kind::i8, exact
+// int32 accumulation), and the CUDA cores only apply the per-group scales.
 //
-// Arithmetic (exact up to f32 accumulation order):
-//   * A operand: the nibble n is placed in the low mantissa bits of a bf16 with exponent 2^7,
-//     which reads as the integer 128 + n — exact, no rounding.
-//   * B operand: each activation row x (f32) is split into bf16 pieces hi + mid + lo = x
-//     (exactly), one B row per piece; a caller that knows x holds bf16 values uses one piece.
-//   * One accumulator block per 64-element group: D_g[row, col] = sum_{k in g} (128 + n) x.
-//     The epilogue forms  s_g * (D_g - 128 * xsum_g) + b_g * xsum_g  in f32 and adds it to the
-//     row's running sum, which is mlx.GemvTo's expression (backends/mlx/gemv.go:178-209).
+// Arithmetic
+//   * A operand (weights): nibble n as the unsigned byte n.
+//   * B operand (activations): each 64-element group of an activation row is put on a common
+//     power-of-two scale 2^(E-26), E the exponent of the group's largest magnitude, and every
+//     element becomes the integer q = round(x * 2^(26-E)), |q| <= 2^26 — at least as fine as
+//     the f32 spacing of the group's largest elements.  q is written as four balanced base-128
+//     digits, one signed-byte B row per digit (three digits is an option for bf16-valued x).
+//   * One int32 accumulator block per 64-element group: D_j[row] = sum_k n_k * digit_j(q_k),
+//     exact.  The epilogue rebuilds sum_k n_k q_k = (D0 + 128 D1) + 16384 (D2 + 128 D3) (two
+//     exact integers, one fused multiply-add), scales by 2^(E-26) and forms
+//     s_g * dot + b_g * sum(x)  in f32 — mlx.GemvTo's expression (backends/mlx/gemv.go:178-209).
 //
-// Pipeline of one CTA (persistent over 128-row tiles, 192 threads):
-//   warp 4   TMA producer: one 2-D tensor-map copy (128 rows x 128 B, 128B swizzle) of packed
-//            nibbles and one (128 rows x 16 B) of {scale,bias} pairs per 256-element K chunk
-//            into a shared-memory ring guarded by full/empty mbarriers.
-//   warps 0-3  thread r owns row r of the tile (TMEM lane r): reads its 128 bytes from the
-//            swizzled stage, widens them to 128 bf16 pairs, tcgen05.st's them into the A
-//            buffer in TMEM, writes its share of the B tile (x pieces) to shared memory, and
-//            two stages later reads D back with tcgen05.ld for the scale epilogue.
-//   warp 5   one thread issues 16 tcgen05.mma (M=128, N=16|32, K=16) per stage, A from TMEM,
-//            B from shared memory, and commits to an mbarrier.
-// Every wait is bounded: after ~2 s a waiter records a code in the status word and the CTA
-// winds down (TMEM freed, outstanding copies drained) instead of spinning.
-#include <cuda.h>
+// Pipeline of one CTA (448 threads, persistent over (128-row tile, K range) items):
+//   TMA producer warp: per 256-element chunk one bulk copy of the weight's 18 KiB block (the
+//     tiled layout stores exactly the shared-memory image of a stage, so every copy is one
+//     sequential burst) into a ring of up to 8 stages guarded by full/empty mbarriers.
+//     A third copy brings the chunk's B tile (the digits of x, laid out for the tensor core by
+//     mlx_prep_x_kernel, which runs once per launch in front of this kernel).
+//   8 converter warps: thread = (row, half chunk): swizzled LDS.128 -> bytes -> tcgen05.st into
+//     a four-deep ring of A buffers in TMEM.
+//   MMA thread: 8 tcgen05.mma (M128 x N x K32, A from TMEM, B straight from the stage) per
+//     chunk, tcgen05.commit to the accumulator's and the stage's mbarriers.
+//   4 epilogue warps: tcgen05.ld of the four group blocks, scales, running sums in registers;
+//     at the end of an item either store, or (K split) write partials to scratch and let the
+//     CTA that arrives last add them in split order (result independent of arrival order).
+// Every wait is bounded (~2 s): a waiter that gives up records a code in the status word and
+// the CTA winds down (copies drained, TMEM returned) instead of spinning.
 #include <string.h>
 
 #include "goph_internal.cuh"
@@ -41,10 +47,14 @@ constexpr int kTileRows = 128;
 constexpr int kChunkK = 256;                  // elements per pipeline stage
 constexpr int kStageWBytes = kTileRows * 128; // packed nibbles of a stage
 constexpr int kStageMBytes = kTileRows * 16;  // {scale,bias} bf16 pairs, 4 groups of 64
-constexpr int kStageBytes = kStageWBytes + kStageMBytes;
-constexpr int kRowThreads = 128;
-constexpr int kThreadsMMA = 192;
+constexpr int kStageBytes = kStageWBytes + kStageMBytes;  // the B tile follows
 constexpr long long kTimeoutCycles = 4000000000LL;
+
+constexpr int kConvWarps = 8, kEpiWarps = 4;
+constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
+constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
+constexpr int kMmaWarps = 2;  // two issuing threads take alternate stages so one's waits hide behind the other's MMAs
+constexpr int kThreads = (kWarpMMA + kMmaWarps) * 32;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -80,20 +90,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   }
   return true;
 }
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(map), "r"(x), "r"(y), "r"(bar)
-      : "memory");
+// mbar_wait that also adds the cycles spent waiting to acc when probing is on.
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, int* status, int code, bool probing,
+                                            long long& acc) {
+  if (!probing) return mbar_wait(bar, parity, status, code);
+  long long t0 = clock64();
+  bool r = mbar_wait(bar, parity, status, code);
+  acc += clock64() - t0;
+  return r;
 }
 
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -103,7 +119,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
-
 // Waits for the loads above; the registers are listed so no use of them can move before it.
 __device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
@@ -113,13 +128,13 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
                : "memory");
 }
 
-// D[tmem] (+)= A[tmem] * B[smem descriptor]; issued by one thread.
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor], 8-bit integers, int32 accumulate; one thread issues.
+__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
@@ -127,46 +142,37 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// bf16 pieces of an f32 by truncation: x = hi + mid + lo exactly (8 significant bits each).
-__device__ __forceinline__ void split3(float x, uint32_t& hi, uint32_t& mid, uint32_t& lo) {
-  uint32_t h = __float_as_uint(x) & 0xFFFF0000u;
-  float r1 = x - __uint_as_float(h);
-  uint32_t m = __float_as_uint(r1) & 0xFFFF0000u;
-  float r2 = r1 - __uint_as_float(m);
-  hi = h >> 16;
-  mid = m >> 16;
-  lo = __float_as_uint(r2) >> 16;
-}
-
 }  // namespace
 
 struct MmaArgs {
-  const float* x;        // [batch][in_dim]
-  float* out;            // [batch][out_dim]
-  int* status;           // device word: 0 ok, otherwise the first wait that gave up
-  float* scratch;        // split-K partial sums [item][batch][128]
+  const unsigned char* w;  // tiled weight blocks [tile][chunk]
+  const float* x;          // [batch][in_dim]
+  const unsigned char* xb; // prepared B operand: [chunk][N rows x 256 bytes], canonical K-major core matrices
+  const float* xtab;       // prepared tables: [batch][groups] sum of x, then [batch][groups] 2^(E-QBITS)
+  float* out;              // [batch][out_dim]
+  int* status;             // device word: 0 ok, otherwise the first wait that gave up
+  float* scratch;          // split-K partial sums [item][batch][128]
   unsigned int* counters;  // per-tile arrival counters, zero between launches
+  long long* probe;        // optional [4 roles][8] cycle counters of CTA 0 (tuning aid), or nullptr
+  int dbg;                 // tuning aid: bit0 skip tcgen05.st, bit1 skip tcgen05.mma, bit2 skip tcgen05.ld
   int out_dim, in_dim;
-  int batch;             // activation rows of this launch (<= MB of the instantiation)
-  int ntiles;            // ceil(out_dim / 128)
-  int nchunks;           // in_dim / 256
-  int splits;            // CTAs sharing the K range of one tile
-  int items;             // ntiles * splits
-  int stages;            // depth of the shared-memory ring
+  int batch;               // activation rows of this launch (<= MB of the instantiation)
+  int ntiles;              // ceil(out_dim / 128)
+  int nchunks;             // in_dim / 256
+  int splits;              // CTAs sharing the K range of one tile
+  int items;               // ntiles * splits
+  int stages;              // depth of the shared-memory ring
 };
 
-constexpr int kConvWarps = 8, kEpiWarps = 4;
-constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
-constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
-constexpr int kThreadsV2 = (kWarpMMA + 1) * 32;
-
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
-// 2 B tiles (16 K-steps x N rows x 32 B), the xsum table, mbarriers, the TMEM base holder.
+// 2 B tiles (8 K-steps x N rows x 32 bytes), per-(row,group) tables {sum x, 2^(E-26), 2^(26-E)},
+// mbarriers, the TMEM base holder.
 template <int N>
 struct MmaSmem {
-  static constexpr int kBTileBytes = 16 * N * 32;
+  static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
+  static constexpr int kStage = kStageBytes + kBTileBytes;
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim) {
-    return (size_t)stages * kStageBytes + 2 * kBTileBytes + (size_t)batch * (in_dim / 64) * 4 + 1024 + 512;
+    return (size_t)stages * kStage + (size_t)batch * (in_dim / 64) * 8 + 1024 + 512;
   }
 };
 
@@ -192,34 +198,88 @@ struct StageWalk {
   }
 };
 
-template <int N, int PIECES, int MB>
-__global__ void __launch_bounds__(kThreadsV2, 1)
-mlx_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap mmap,
-               const __grid_constant__ MmaArgs a) {
-  static_assert(MB * PIECES <= N, "activation pieces must fit the N columns");
+// ---- activation preparation -----------------------------------------------------------------
+// One block of 64 threads per (activation row, 64-element group): group sum, power-of-two scale,
+// and the base-128 digits of every element written where the tensor core expects them:
+// chunk (256 K) -> K-step (32) -> half (16 bytes) -> 8-row core matrix -> row -> byte.
+template <int DIGITS>
+__global__ void __launch_bounds__(64)
+mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, float* __restrict__ xtab, int batch,
+                  int in_dim, int N) {
+  constexpr int QBITS = DIGITS == 4 ? 26 : 19;  // |q| <= 2^QBITS keeps the top digit within a signed byte
+  const int groups = in_dim / 64;
+  const int m = blockIdx.x / groups, g = blockIdx.x - m * groups;
+  const int t = threadIdx.x;
+  const float v = x[(size_t)m * in_dim + g * 64 + t];
+  float s = v, mx = fabsf(v);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  __shared__ float sh[4];
+  if ((t & 31) == 0) {
+    sh[t >> 5] = s;
+    sh[2 + (t >> 5)] = mx;
+  }
+  __syncthreads();
+  s = sh[0] + sh[1];
+  mx = fmaxf(sh[2], sh[3]);
+  int e = (int)((__float_as_uint(mx) >> 23) & 0xFF);  // mx < 2^(e-126)
+  if (e < QBITS + 2) e = QBITS + 2;
+  if (e > 254) e = 254;  // inf/nan inputs: results are undefined, not a hang
+  if (t == 0) {
+    xtab[m * groups + g] = s;
+    xtab[(batch + m) * groups + g] = __uint_as_float((uint32_t)(e - 126 - QBITS + 127) << 23);  // 2^(E-QBITS)
+  }
+  const float fi = __uint_as_float((uint32_t)(QBITS - (e - 126) + 127) << 23);
+  int q = __float2int_rn(v * fi);
+  // position of element k inside its chunk's B tile
+  const int k = (g & 3) * 64 + t;          // element within the 256-element chunk
+  const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
+  const int pos = 8 * w + 4 * (j & 1) + (j >> 1);  // byte along K inside the step (order of the A bytes)
+  const size_t base = (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
+#pragma unroll
+  for (int d = 0; d < DIGITS; ++d) {
+    int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
+    q = (q - dig) >> 7;
+    int n = m * DIGITS + d;
+    xb[base + (n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
+  }
+}
+
+// N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
+// MB: activation rows the instantiation can take (MB * DIGITS <= N).
+template <int N, int DIGITS, int MB>
+__global__ void __launch_bounds__(kThreads, 1)
+mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
+  static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
+  static_assert(N == 16 || N == 32, "accumulator blocks of 16 or 32 columns");
+  constexpr int NB = N == 16 ? 4 : 2;           // depth of the A / accumulator rings in TMEM
+  constexpr uint32_t kCols = 512;               // NB * (64 + 4N) columns
+  constexpr int kStage = MmaSmem<N>::kStage;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  constexpr int kBTile = MmaSmem<N>::kBTileBytes;
   const int S = a.stages;
   unsigned char* ring = smem;
-  unsigned char* btile = ring + (size_t)S * kStageBytes;       // 2 tiles
-  float* xsum = reinterpret_cast<float*>(btile + 2 * kBTile);  // [batch][groups]
   const int groups = a.in_dim / 64;
-  uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xsum + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
-  // bars: full[S], empty[S], a_ready[2], mma_done[2], d_free[2]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+  float* xsum = reinterpret_cast<float*>(ring + (size_t)S * kStage);  // [batch][groups] sum of x
+  float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
+  uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
+  // bars: full[S], empty[S], a_ready[NB], mma_done[NB], d_free[NB]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 3 * NB);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
-  const uint32_t aready0 = smem_u32(bars + 2 * S), mdone0 = smem_u32(bars + 2 * S + 2), dfree0 = smem_u32(bars + 2 * S + 4);
+  const uint32_t aready0 = smem_u32(bars + 2 * S), mdone0 = smem_u32(bars + 2 * S + NB), dfree0 = smem_u32(bars + 2 * S + 2 * NB);
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, kConvThreads + kEpiThreads);
+      mbar_init(empty0 + 8 * s, kConvThreads + kEpiThreads + 1);  // converters, epilogue (meta), MMA commit (B tile)
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NB; ++b) {
       mbar_init(aready0 + 8 * b, kConvThreads);
       mbar_init(mdone0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiThreads);
@@ -227,96 +287,106 @@ mlx_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kWarpMMA) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(512u)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  // zero the B tiles once: rows no activation piece maps to stay zero for the whole launch
-  for (int i = tid; i < 2 * kBTile / 16; i += kThreadsV2) reinterpret_cast<uint4*>(btile)[i] = make_uint4(0, 0, 0, 0);
-  // per-group sums of x
-  for (int i = tid; i < a.batch * groups; i += kThreadsV2) {
-    const float* p = a.x + (size_t)(i / groups) * a.in_dim + (size_t)(i % groups) * 64;
-    float s = 0.f;
-    for (int k = 0; k < 64; k += 4) {
-      float4 v = __ldg(reinterpret_cast<const float4*>(p + k));
-      s += (v.x + v.y) + (v.z + v.w);
-    }
-    xsum[i] = s;
-  }
+  for (int i = tid; i < 2 * a.batch * groups; i += kThreads) xsum[i] = __ldg(a.xtab + i);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + 256;  // A: 2 x 128 cols; D: 2 x 4N cols
+  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NB * 64;  // A: NB x 64 cols; D: NB x 4N cols
   bool ok = true;
   StageWalk sw(a);
 
   if (warp == kWarpTMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      const bool pr = a.probe && blockIdx.x == 0;
+      long long w0 = 0, tstart = clock64();
+      int nst = 0;
       for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
         int slot = i % S, round = i / S;
-        if (round > 0) ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 1);
+        if (round > 0) ok = mbar_wait_t(empty0 + 8 * slot, (round - 1) & 1, a.status, 1, pr, w0);
         if (!ok) break;
-        uint32_t dst = smem_u32(ring + (size_t)slot * kStageBytes);
-        mbar_expect_tx(full0 + 8 * slot, kStageBytes);
-        tma_load_2d(dst, &wmap, sw.c * 128, sw.tile * kTileRows, full0 + 8 * slot);
-        tma_load_2d(dst + kStageWBytes, &mmap, sw.c * 16, sw.tile * kTileRows, full0 + 8 * slot);
+        ++nst;
+        uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
+        mbar_expect_tx(full0 + 8 * slot, kStage);
+        bulk_load_1d(dst, a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes, kStageBytes, full0 + 8 * slot);
+        bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N>::kBTileBytes, MmaSmem<N>::kBTileBytes,
+                     full0 + 8 * slot);
+      }
+      if (pr) {
+        a.probe[0] = clock64() - tstart;
+        a.probe[1] = w0;
+        a.probe[2] = nst;
       }
     }
-  } else if (warp == kWarpMMA) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp >= kWarpMMA) {
+    // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
-      // instruction descriptor: D f32, A bf16, B bf16, both K-major, N, M=128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+      const int mi = warp - kWarpMMA;
+      if (mi == 1 && sw.live(a)) sw.next(a);
+      // instruction descriptor: D s32, A u8, B s8, both K-major, N, M=128
+      const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
       constexpr uint32_t kLBO = (N / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
-      for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
-        int b = i & 1;
-        ok = mbar_wait(aready0 + 8 * b, (i >> 1) & 1, a.status, 2);
-        if (ok && i >= 2) ok = mbar_wait(dfree0 + 8 * b, ((i - 2) >> 1) & 1, a.status, 5);
+      const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
+      const bool pr = a.probe && blockIdx.x == 0 && mi == 0;
+      long long w0 = 0, w1 = 0, w2 = 0, tstart = clock64();
+      for (int i = mi; sw.live(a) && ok; i += kMmaWarps) {
+        int b = i % NB, slot = i % S;
+        if (!(a.dbg & 32)) ok = mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 8, pr, w2);
+        if (ok) ok = mbar_wait_t(aready0 + 8 * b, (i / NB) & 1, a.status, 2, pr, w0);
+        if (ok && i >= NB) ok = mbar_wait_t(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5, pr, w1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        uint32_t bbase = smem_u32(btile + (size_t)b * kBTile);
+        const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage + kStageBytes);
+        const uint32_t dcol = tmemD0 + b * (4 * N), acol = tmemA0 + b * 64;
+        if (a.dbg & 64) {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+          for (int step = 0; step < 8; step += 2)
+            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF),
+                       idesc, 0);
+        } else if (!(a.dbg & 2)) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            int step = g * 4 + j;
-            uint64_t desc = (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF) | ((uint64_t)(kLBO >> 4) << 16) |
-                            ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
-            umma_ts(tmemD0 + b * (4 * N) + g * N, tmemA0 + b * 128 + step * 8, desc, idesc, j > 0 ? 1u : 0u);
-          }
+          for (int step = 0; step < 8; ++step)  // K = 32 per step; two steps per 64-element group
+            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF),
+                       idesc, step & 1);
         }
         umma_commit(mdone0 + 8 * b);
+        umma_commit(empty0 + 8 * slot);
+        sw.next(a);
+        if (sw.live(a)) sw.next(a);
+      }
+      if (pr) {
+        a.probe[8] = clock64() - tstart;
+        a.probe[9] = w0;
+        a.probe[10] = w1;
+        a.probe[11] = w2;
       }
     }
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------------ converters
     // Thread = (row r of the tile, half h of the stage's eight 16-byte units).
-    const int q = warp & 3, h = warp >> 2;
-    const int r = q * 32 + lane;
-    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-    // B-tile share of the h == 0 threads: K-step j, half kc, pair p (elements k and k+4).
-    const int bj = r >> 3, bkc = (r >> 2) & 1, bp = r & 3;
-    float xn0[MB], xn1[MB];
-    auto fetch_x = [&](int chunk) {
-      int k = chunk * kChunkK + bj * 16 + bkc * 8 + bp;
-#pragma unroll
-      for (int m = 0; m < MB; ++m) {
-        bool in = m < a.batch;
-        xn0[m] = in ? __ldg(a.x + (size_t)m * a.in_dim + k) : 0.f;
-        xn1[m] = in ? __ldg(a.x + (size_t)m * a.in_dim + k + 4) : 0.f;
-      }
-    };
-    if (h == 0 && sw.live(a)) fetch_x(sw.c);
-    for (int i = 0; sw.live(a) && ok; ++i) {
-      int b = i & 1, slot = i % S;
-      if (i >= 2) ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, ((i - 2) >> 1) & 1, a.status, 3));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 4));
+    const int q4 = warp & 3, h = warp >> 2;
+    const int r = q4 * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
+    const bool pr = a.probe && blockIdx.x == 0 && tid == 0;
+    long long w0 = 0, w1 = 0, tstart = clock64();
+    for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
+      int b = i % NB, slot = i % S;
+      if (i >= NB) ok = __all_sync(0xffffffffu, mbar_wait_t(mdone0 + 8 * b, ((i - NB) / NB) & 1, a.status, 3, pr, w0));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 4, pr, w1));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const unsigned char* st = ring + (size_t)slot * kStageBytes;
-      // ---- widen this row's half of the stage (128 nibbles) into the A buffer ----
+      const unsigned char* st = ring + (size_t)slot * kStage;
+      if (a.dbg & 8) {
+        mbar_arrive(aready0 + 8 * b);
+        mbar_arrive(empty0 + 8 * slot);
+        continue;
+      }
+      // ---- this row's half of the stage: 128 nibbles -> 128 bytes -> 32 TMEM columns ----
       uint4 qv[4];
 #pragma unroll
       for (int uu = 0; uu < 4; ++uu) {
@@ -326,99 +396,95 @@ mlx_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
       for (int uu = 0; uu < 4; ++uu) {
         uint32_t ws[4] = {qv[uu].x, qv[uu].y, qv[uu].z, qv[uu].w};
-        uint32_t regs[16];
+        uint32_t regs[8];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          // nibble -> top mantissa bits of a bf16 under 2^4: the integer 16 + n, exactly
-          constexpr uint32_t MK = 0x00780078u, EX = 0x41804180u;
-          regs[4 * w + 0] = ((ws[w] << 3) & MK) | EX;  // elements (0,4) of the word
-          regs[4 * w + 1] = ((ws[w] >> 1) & MK) | EX;  // (1,5)
-          regs[4 * w + 2] = ((ws[w] >> 5) & MK) | EX;  // (2,6)
-          regs[4 * w + 3] = ((ws[w] >> 9) & MK) | EX;  // (3,7)
+          regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
+          regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
         }
-        tmem_st16(tmemA0 + lane_base + b * 128 + (h * 4 + uu) * 16, regs);
+        if (!(a.dbg & 1)) tmem_st8(tmemA0 + lane_base + b * 64 + (h * 4 + uu) * 8, regs);
+        else if (regs[0] == 0x12345678u && regs[7] == 1u) *last_flag = 1;
       }
-      // ---- the B tile of this stage (x pieces), then prefetch the next stage's x ----
-      if (h == 0) {
-        unsigned char* bt = btile + (size_t)b * kBTile + bj * (N * 32) + bkc * ((N / 8) * 128) + bp * 4;
-#pragma unroll
-        for (int m = 0; m < MB; ++m) {
-          if (PIECES == 3) {
-            uint32_t h0, m0, l0, h1, m1, l1;
-            split3(xn0[m], h0, m0, l0);
-            split3(xn1[m], h1, m1, l1);
-            constexpr int dummy = 0;
-            (void)dummy;
-            int n = 3 * m;
-            *reinterpret_cast<uint32_t*>(bt + (n >> 3) * 128 + (n & 7) * 16) = h0 | (h1 << 16);
-            *reinterpret_cast<uint32_t*>(bt + ((n + 1) >> 3) * 128 + ((n + 1) & 7) * 16) = m0 | (m1 << 16);
-            *reinterpret_cast<uint32_t*>(bt + ((n + 2) >> 3) * 128 + ((n + 2) & 7) * 16) = l0 | (l1 << 16);
-          } else {
-            *reinterpret_cast<uint32_t*>(bt + (m >> 3) * 128 + (m & 7) * 16) =
-                (__float_as_uint(xn0[m]) >> 16) | (__float_as_uint(xn1[m]) & 0xFFFF0000u);
-          }
-        }
-      }
-      sw.next(a);
-      if (h == 0 && sw.live(a)) fetch_x(sw.c);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(aready0 + 8 * b);
       mbar_arrive(empty0 + 8 * slot);
     }
+    if (pr) {
+      a.probe[16] = clock64() - tstart;
+      a.probe[17] = w0;
+      a.probe[18] = w1;
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;
-    const int r = q * 32 + lane;  // row of the tile == TMEM lane
+    const int q4 = warp & 3;
+    const int r = q4 * 32 + lane;  // row of the tile == TMEM lane
     const int et = tid - kConvThreads;
-    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     float acc[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+    const bool pr = a.probe && blockIdx.x == 0 && et == 0;
+    long long w0 = 0, w1 = 0, tstart = clock64();
     for (int i = 0; sw.live(a) && ok; ++i) {
-      int b = i & 1, slot = i % S;
-      ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, (i >> 1) & 1, a.status, 7));
+      int b = i % NB, slot = i % S;
+      ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 6, pr, w0));
+      uint4 mv = make_uint4(0, 0, 0, 0);
+      if (ok) {
+        mv = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStage + kStageWBytes + r * 16);
+        mbar_arrive(empty0 + 8 * slot);
+        ok = __all_sync(0xffffffffu, mbar_wait_t(mdone0 + 8 * b, (i / NB) & 1, a.status, 7, pr, w1));
+      }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint4 mv = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStageBytes + kStageWBytes + r * 16);
-      const uint32_t meta[4] = {mv.x, mv.y, mv.z, mv.w};
-      uint32_t t[4][16];
-#pragma unroll
-      for (int g = 0; g < 4; ++g) tmem_ld16(tmemD0 + lane_base + b * (4 * N) + g * N, t[g]);
-      tmem_wait_ld(t[0]);
-      tmem_wait_ld(t[1]);
-      tmem_wait_ld(t[2]);
-      tmem_wait_ld(t[3]);
-      uint32_t t2[4][16];
-      if (N == 32 && MB * PIECES > 16) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) tmem_ld16(tmemD0 + lane_base + b * (4 * N) + g * N + 16, t2[g]);
-        tmem_wait_ld(t2[0]);
-        tmem_wait_ld(t2[1]);
-        tmem_wait_ld(t2[2]);
-        tmem_wait_ld(t2[3]);
+      if (a.dbg & 16) {
+        mbar_arrive(dfree0 + 8 * b);
+        acc[0] += __uint_as_float(mv.x);
+        const bool done16 = sw.last_chunk();
+        const int row16 = sw.tile * kTileRows + r;
+        sw.next(a);
+        if (done16 && row16 < a.out_dim) a.out[row16] = acc[0];
+        continue;
       }
+      const uint32_t meta[4] = {mv.x, mv.y, mv.z, mv.w};
+      constexpr int NLD = (MB * DIGITS + 15) / 16;  // 16-column loads per group block
+      uint32_t t[4][NLD][16];
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int l = 0; l < NLD; ++l) {
+          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (4 * N) + g * N + l * 16, t[g][l]);
+          else {
+#pragma unroll
+            for (int z = 0; z < 16; ++z) t[g][l][z] = meta[g] + z;
+          }
+        }
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+#pragma unroll
+        for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[g][l]);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(dfree0 + 8 * b);
-      mbar_arrive(empty0 + 8 * slot);
-      const float* xs_c = xsum + sw.c * 4;
+      const int gbase = sw.c * 4;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         float sc = __uint_as_float(meta[g] << 16), bi = __uint_as_float(meta[g] & 0xFFFF0000u);
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
-          float xs = xs_c[m * groups + g];
-          float dot;
-          if (PIECES == 3) {
-            auto col = [&](int cidx) { return __uint_as_float(cidx < 16 ? t[g][cidx & 15] : t2[g][cidx & 15]); };
-            dot = (col(3 * m) + col(3 * m + 1)) + col(3 * m + 2);
-          } else {
-            dot = __uint_as_float(m < 16 ? t[g][m & 15] : t2[g][m & 15]);
+          if (m < a.batch) {
+            auto col = [&](int cidx) { return (int)t[g][cidx >> 4][cidx & 15]; };
+            float dotq;
+            if (DIGITS == 4) {
+              int lo = col(4 * m) + (col(4 * m + 1) << 7), hi = col(4 * m + 2) + (col(4 * m + 3) << 7);
+              dotq = fmaf((float)hi, 16384.f, (float)lo);
+            } else {
+              int lo = col(3 * m) + (col(3 * m + 1) << 7);
+              dotq = fmaf((float)col(3 * m + 2), 16384.f, (float)lo);
+            }
+            float dot = dotq * xfs[m * groups + gbase + g];
+            acc[m] = fmaf(sc, dot, acc[m]);
+            acc[m] = fmaf(bi, xsum[m * groups + gbase + g], acc[m]);
           }
-          acc[m] = fmaf(sc, dot - 16.f * xs, acc[m]);
-          acc[m] = fmaf(bi, xs, acc[m]);
         }
       }
       const bool item_done = sw.last_chunk();
@@ -459,6 +525,11 @@ mlx_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
     }
+    if (pr) {
+      a.probe[24] = clock64() - tstart;
+      a.probe[25] = w0;
+      a.probe[26] = w1;
+    }
   }
 
   // ---- wind down: everyone meets, outstanding copies are drained, TMEM is returned ----
@@ -476,73 +547,73 @@ mlx_mma_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   if (warp == kWarpMMA) {
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kCols) : "memory");
   }
 }
 
 // ---- host side --------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
+// Row-major words + {scale,bias} table -> tiled blocks; one thread per 16-byte unit / meta row.
+__global__ void mlx_tile_kernel(const uint32_t* __restrict__ qw, const uint32_t* __restrict__ sb,
+                                unsigned char* __restrict__ tiled, int out_dim, int in_dim, int ntiles, int nchunks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nblocks = (size_t)ntiles * nchunks;
+  if (idx >= nblocks * (128 * 9)) return;
+  size_t blk = idx / (128 * 9);
+  int rem = (int)(idx - blk * (128 * 9));
+  int tile = (int)(blk / nchunks), chunk = (int)(blk - (size_t)tile * nchunks);
+  int r = rem / 9, u = rem - r * 9;
+  int row = tile * 128 + r;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  unsigned char* dst = tiled + blk * kStageBytes;
+  if (u < 8) {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(qw + (size_t)row * (in_dim / 8) + chunk * 32 + u * 4);
+    *reinterpret_cast<uint4*>(dst + r * 128 + ((u ^ (r & 7)) << 4)) = v;
+  } else {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(sb + (size_t)row * (in_dim / 64) + chunk * 4);
+    *reinterpret_cast<uint4*>(dst + kStageWBytes + r * 16) = v;
   }
-  return fn;
 }
 
 bool mlx_mma_supported(const goph_mlx_weight* w) {
-  return w->sb_bf16 && w->group_size == 64 && w->in_dim % kChunkK == 0 && ((uintptr_t)w->qweight % 16) == 0 &&
-         ((uintptr_t)w->sb % 16) == 0;
+  return w->sb_bf16 && w->group_size == 64 && w->in_dim % kChunkK == 0 && w->in_dim <= 65536;
 }
 
-int mlx_mma_make_maps(goph_mlx_weight* w) {
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return fail(GOPH_E_UNSUPPORTED, "cuTensorMapEncodeTiled is not available from this driver");
-  CUtensorMap* maps = new CUtensorMap[2];
-  cuuint64_t dims[2] = {(cuuint64_t)w->in_dim / 2, (cuuint64_t)w->out_dim};
-  cuuint64_t strides[1] = {(cuuint64_t)w->in_dim / 2};
-  cuuint32_t box[2] = {128, (cuuint32_t)kTileRows}, elem[2] = {1, 1};
-  CUresult r = enc(&maps[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->qweight, dims, strides, box, elem,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r == CUDA_SUCCESS) {
-    cuuint64_t mdims[2] = {(cuuint64_t)w->groups * 4, (cuuint64_t)w->out_dim};
-    cuuint64_t mstrides[1] = {(cuuint64_t)w->groups * 4};
-    cuuint32_t mbox[2] = {16, (cuuint32_t)kTileRows};
-    r = enc(&maps[1], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->sb, mdims, mstrides, mbox, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+int mlx_mma_make_tiled(goph_mlx_weight* w) {
+  int ntiles = (w->out_dim + kTileRows - 1) / kTileRows, nchunks = w->in_dim / kChunkK;
+  size_t bytes = (size_t)ntiles * nchunks * kStageBytes;
+  unsigned char* t = nullptr;
+  GOPH_CUDA(cudaMalloc(&t, bytes));
+  size_t threads = (size_t)ntiles * nchunks * 128 * 9;
+  mlx_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(w->qweight, reinterpret_cast<const uint32_t*>(w->sb), t,
+                                                              w->out_dim, w->in_dim, ntiles, nchunks);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cudaFree(t);
+    return fail_cuda(e, "mlx_tile_kernel");
   }
-  if (r != CUDA_SUCCESS) {
-    delete[] maps;
-    return fail(GOPH_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  }
-  w->tmaps = maps;
+  w->tiled = t;
+  w->bytes = bytes;
   return GOPH_OK;
 }
 
-void mlx_mma_free_maps(goph_mlx_weight* w) {
-  delete[] reinterpret_cast<CUtensorMap*>(w->tmaps);
-  w->tmaps = nullptr;
-}
-
 struct MmaDeviceBufs {
+  unsigned char* xb = nullptr;  // prepared B operand of the launch in flight
+  float* xtab = nullptr;        // prepared per-(row, group) tables
+  long long* probe = nullptr;
   int* status = nullptr;
   float* scratch = nullptr;
   unsigned int* counters = nullptr;
 };
-// Fixed-size device scratch of the split-K fix-up: at most 2 x SM-count items of 128 rows x 32
+// Fixed-size device scratch of the split-K fix-up: at most 2 x 160 items of 128 rows x 8
 // activation rows, plus one counter per tile.  Allocated once per device.
-constexpr size_t kScratchFloats = (size_t)2 * 160 * kTileRows * 32;
+constexpr size_t kScratchFloats = (size_t)2 * 160 * kTileRows * 8;
 constexpr size_t kMaxCounters = 4096;
+// Prepared activations: up to 8 rows of up to 65536 elements (B operand: 32 rows x in_dim bytes).
+constexpr int kMaxPrepIn = 65536;  // mlx_mma_supported's bound on in_dim
+constexpr size_t kPrepXbBytes = (size_t)32 * kMaxPrepIn;
+constexpr size_t kPrepTabFloats = (size_t)2 * 8 * (kMaxPrepIn / 64);
 
 static MmaDeviceBufs* device_bufs(int device) {
   static MmaDeviceBufs bufs[kMaxDevices];
@@ -551,11 +622,22 @@ static MmaDeviceBufs* device_bufs(int device) {
     if (cudaMalloc(&b.status, sizeof(int)) != cudaSuccess) return nullptr;
     if (cudaMalloc(&b.scratch, kScratchFloats * sizeof(float)) != cudaSuccess) return nullptr;
     if (cudaMalloc(&b.counters, kMaxCounters * sizeof(unsigned int)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&b.probe, 32 * sizeof(long long)) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&b.xb, kPrepXbBytes) != cudaSuccess) return nullptr;
+    if (cudaMalloc(&b.xtab, kPrepTabFloats * sizeof(float)) != cudaSuccess) return nullptr;
+    cudaMemset(b.xb, 0, kPrepXbBytes);
+    cudaMemset(b.probe, 0, 32 * sizeof(long long));
     cudaMemset(b.status, 0, sizeof(int));
     cudaMemset(b.counters, 0, kMaxCounters * sizeof(unsigned int));
     cudaDeviceSynchronize();
   }
   return &b;
+}
+
+int mlx_mma_probe(int device, long long* out32) {
+  MmaDeviceBufs* b = device_bufs(device);
+  if (!b) return -1;
+  return cudaMemcpy(out32, b->probe, 32 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
 }
 
 int mlx_mma_status(int device) {
@@ -565,12 +647,12 @@ int mlx_mma_status(int device) {
   return v;
 }
 
-template <int N, int PIECES, int MB>
+template <int N, int DIGITS, int MB>
 static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t stream) {
   MmaArgs a = a0;
   DeviceState& st = device_state(w->device);
   size_t fixed = MmaSmem<N>::bytes(0, a.batch, a.in_dim);
-  int stages = (int)(((size_t)kSmemBudget - fixed) / kStageBytes);
+  int stages = (int)(((size_t)kSmemBudget - fixed) / MmaSmem<N>::kStage);
   if (stages > 8) stages = 8;
   if (stages < 3)
     return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
@@ -581,52 +663,59 @@ static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t 
     splits = st.sm_count / a.ntiles;
     if (splits > a.nchunks) splits = a.nchunks;
     if (splits < 1) splits = 1;
-    while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
   }
   if (options().mlx_splits > 0) splits = options().mlx_splits < a.nchunks ? options().mlx_splits : a.nchunks;
+  while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
   a.splits = splits;
   a.items = a.ntiles * splits;
   size_t smem = MmaSmem<N>::bytes(stages, a.batch, a.in_dim);
-  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: each allocates all 512 TMEM columns
-  auto kern = mlx_mma_kernel<N, PIECES, MB>;
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
+  // activations -> digits, sums and scales, once per launch
+  mlx_prep_x_kernel<DIGITS><<<a.batch * (a.in_dim / 64), 64, 0, stream>>>(a.x, const_cast<unsigned char*>(a.xb),
+                                                                         const_cast<float*>(a.xtab), a.batch, a.in_dim, N);
+  GOPH_CUDA(cudaGetLastError());
+  auto kern = mlx_mma_kernel<N, DIGITS, MB>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
-  const CUtensorMap* maps = reinterpret_cast<const CUtensorMap*>(w->tmaps);
-  kern<<<grid, kThreadsV2, smem, stream>>>(maps[0], maps[1], a);
+  kern<<<grid, kThreads, smem, stream>>>(a);
   GOPH_CUDA(cudaGetLastError());
   return GOPH_OK;
 }
 
-int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int pieces, cudaStream_t stream) {
-  if (!w->tmaps) return fail(GOPH_E_UNSUPPORTED, "weight has no tensor maps");
+int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream) {
+  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
   MmaDeviceBufs* bufs = device_bufs(w->device);
   if (!bufs) return fail(GOPH_E_NOMEM, "cannot allocate the tensor-core path's device scratch");
   MmaArgs a;
   memset(&a, 0, sizeof a);
+  a.w = w->tiled;
   a.status = bufs->status;
   a.scratch = bufs->scratch;
   a.counters = bufs->counters;
+  a.xb = bufs->xb;
+  a.xtab = bufs->xtab;
+  a.probe = options().mlx_probe ? bufs->probe : nullptr;
+  a.dbg = options().mlx_dbg;
   a.out_dim = w->out_dim;
   a.in_dim = w->in_dim;
   a.ntiles = (w->out_dim + kTileRows - 1) / kTileRows;
   a.nchunks = w->in_dim / kChunkK;
-  const int cap = pieces == 3 ? 10 : 32;  // activation rows one launch can take
+  const int cap = 8;  // activation rows one launch can take
   for (int b0 = 0; b0 < batch;) {
     int nb = batch - b0 < cap ? batch - b0 : cap;
     a.x = x + (size_t)b0 * w->in_dim;
     a.out = out + (size_t)b0 * w->out_dim;
     a.batch = nb;
     int rc;
-    if (pieces == 3) {
+    if (digits == 3) {
       rc = nb == 1 ? launch_one<16, 3, 1>(w, a, stream)
-         : nb == 2 ? launch_one<16, 3, 2>(w, a, stream)
          : nb <= 5 ? launch_one<16, 3, 5>(w, a, stream)
-                   : launch_one<32, 3, 10>(w, a, stream);
+                   : launch_one<32, 3, 8>(w, a, stream);
     } else {
-      rc = nb == 1 ? launch_one<16, 1, 1>(w, a, stream)
-         : nb <= 4 ? launch_one<16, 1, 4>(w, a, stream)
-         : nb <= 16 ? launch_one<16, 1, 16>(w, a, stream)
-                    : launch_one<32, 1, 32>(w, a, stream);
+      rc = nb == 1 ? launch_one<16, 4, 1>(w, a, stream)
+         : nb == 2 ? launch_one<16, 4, 2>(w, a, stream)
+         : nb <= 4 ? launch_one<16, 4, 4>(w, a, stream)
+                   : launch_one<32, 4, 8>(w, a, stream);
     }
     if (rc) return rc;
     b0 += nb;

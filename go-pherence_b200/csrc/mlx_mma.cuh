@@ -5,16 +5,28 @@
 
 namespace goph {
 
-// True when the weight's layout meets the tensor-map constraints of the tensor-core kernel
-// (bf16 scale/bias table, group size 64, in_dim a multiple of 256, 16-byte aligned buffers).
+// True when the weight's shape allows the tiled layout of the tensor-core kernel (bf16
+// scale/bias table, group size 64, in_dim a multiple of 256).
 bool mlx_mma_supported(const goph_mlx_weight* w);
-// Encodes the two TMA tensor maps of a weight (packed nibbles, {scale,bias} pairs).
-int mlx_mma_make_maps(goph_mlx_weight* w);
-void mlx_mma_free_maps(goph_mlx_weight* w);
-// out[batch][out_dim] = x[batch][in_dim] * W^T.  pieces: bf16 pieces per activation (3 = any
-// f32 exactly, 1 = x already holds bf16 values).
-int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int pieces, cudaStream_t stream);
+// Builds the tiled copy from the row-major buffers of w (which the caller then frees).
+int mlx_mma_make_tiled(goph_mlx_weight* w);
+// Byte offsets inside the tiled layout (shared with the dequantisation kernel).
+constexpr int kMlxTileRows = 128, kMlxChunkK = 256, kMlxBlockW = 128 * 128, kMlxBlockBytes = 128 * 128 + 128 * 16;
+__host__ __device__ inline size_t mlx_tiled_word_offset(int row, int col, int nchunks) {
+  size_t blk = (size_t)(row >> 7) * nchunks + (col >> 8);
+  int r = row & 127, u = (col & 255) >> 5, w = (col & 31) >> 3;
+  return blk * kMlxBlockBytes + r * 128 + ((u ^ (r & 7)) << 4) + w * 4;
+}
+__host__ __device__ inline size_t mlx_tiled_meta_offset(int row, int col, int nchunks) {
+  size_t blk = (size_t)(row >> 7) * nchunks + (col >> 8);
+  return blk * kMlxBlockBytes + kMlxBlockW + (row & 127) * 16 + ((col & 255) >> 6) * 4;
+}
+// out[batch][out_dim] = x[batch][in_dim] * W^T.  digits: base-128 digits each activation is
+// written in (4 = 27 bits under the group maximum, 3 = 20 bits).
+int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream);
 // Reads the device status word (0 = every wait completed); synchronises the copy stream.
 int mlx_mma_status(int device);
+// Copies the 32 cycle counters CTA 0 wrote when option mlx_probe is on (tuning aid).
+int mlx_mma_probe(int device, long long* out32);
 
 }  // namespace goph

@@ -70,15 +70,19 @@ GOPH_API int goph_set_option(const char* name, int value) {
   if (!name) return fail(GOPH_E_INVALID, "goph_set_option: nil name");
   Options& o = options();
   bool rows_ok = value == 0 || value == 1 || value == 2 || value == 4;
-  if (!strcmp(name, "mlx_path")) {
-    if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_path=%d not in 0..2", value);
-    o.mlx_path = value;
+  if (!strcmp(name, "mlx_layout")) {
+    if (value < 0 || value > 1) return fail(GOPH_E_INVALID, "mlx_layout=%d not 0 or 1", value);
+    o.mlx_layout = value;
+  } else if (!strcmp(name, "mlx_dbg")) {
+    o.mlx_dbg = value;
+  } else if (!strcmp(name, "mlx_probe")) {
+    o.mlx_probe = value != 0;
   } else if (!strcmp(name, "mlx_splits")) {
     if (value < 0 || value > 64) return fail(GOPH_E_INVALID, "mlx_splits=%d not in 0..64", value);
     o.mlx_splits = value;
-  } else if (!strcmp(name, "mlx_pieces")) {
-    if (value != 1 && value != 3) return fail(GOPH_E_INVALID, "mlx_pieces=%d not 1 or 3", value);
-    o.mlx_pieces = value;
+  } else if (!strcmp(name, "mlx_digits")) {
+    if (value != 3 && value != 4) return fail(GOPH_E_INVALID, "mlx_digits=%d not 3 or 4", value);
+    o.mlx_digits = value;
   } else if (!strcmp(name, "mlx_unpack")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_unpack=%d not in 0..2", value);
     o.mlx_unpack = value;

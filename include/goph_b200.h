@@ -62,12 +62,16 @@ int goph_sm_count(int device);
 
 /* Tuning switches.  The reference reads its own from GO_PHERENCE_* environment variables at
  * the call sites (model/gpu_forward.go:24-47, :776-785); here they are set by name:
- *   "mlx_path"    kernel family for MLX weights: 0 chosen by shape (default), 1 CUDA-core
- *                 streaming kernel, 2 tensor-core (tcgen05) kernel where the shape allows it
- *   "mlx_pieces"  bf16 pieces each activation is split into on the tensor-core path: 3 (default,
- *                 exact for any f32) or 1 (the caller guarantees x holds bf16 values)
+ *   "mlx_layout"  device layout chosen by goph_mlx_upload: 0 (default) the tiled layout of the
+ *                 tensor-core (tcgen05) kernel when the shape allows it (group size 64, in_dim a
+ *                 multiple of 256, bf16-valued scales and biases), 1 always the row-major layout of
+ *                 the CUDA-core kernels
+ *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
+ *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
+ *                 or 3 (20 bits; enough for bf16-valued activations)
+ *   "mlx_splits"  CTAs that share the K range of one 128-row tile (0 = chosen by shape)
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
- *                 1 one shift per nibble pair (default), 2 integer conversion
+ *                 (default), 1 one shift per nibble pair, 2 integer conversion
  *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
  * Unknown names and values out of range are rejected.  Results stay within the product
  * tolerance for every setting. */

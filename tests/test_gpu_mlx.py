@@ -14,14 +14,27 @@ pytestmark = pytest.mark.gpu
 QWEN3_LAYER = [(2048, 1024), (1024, 1024), (1024, 1024), (1024, 2048), (3072, 1024), (3072, 1024), (1024, 3072)]
 
 
-def upload(rt, syn, key, out_dim, in_dim, gs=64):
+def upload(rt, syn, key, out_dim, in_dim, gs=64, layout=0):
+    """layout 0: the library's choice (tiled + tensor cores when the shape allows), 1: row-major."""
     w, s, b = syn.mlx_weight(key, out_dim, in_dim, gs)
-    return rt.UploadMLXWeight(w, s, b, in_dim, out_dim, gs, True), (w, s, b)
+    rt.SetOption("mlx_layout", layout)
+    try:
+        return rt.UploadMLXWeight(w, s, b, in_dim, out_dim, gs, True), (w, s, b)
+    finally:
+        rt.SetOption("mlx_layout", 0)
 
 
-@pytest.mark.parametrize("out_dim,in_dim,gs", [(2048, 1024, 64), (1024, 3072, 64), (37, 96, 32), (5, 64, 16), (3, 24, 4), (4, 8, 4)])
-def test_dequant_bit_exact(gpu, pkg, out_dim, in_dim, gs):
-    h, (w, s, b) = upload(gpu, pkg.synth, "deq", out_dim, in_dim, gs)
+@pytest.fixture(autouse=True)
+def no_wait_gave_up(gpu):
+    """Every device-side wait is bounded; none may have given up during a test."""
+    yield
+    assert gpu.KernelStatus() == 0
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("out_dim,in_dim,gs", [(2048, 1024, 64), (1024, 3072, 64), (300, 256, 64), (37, 96, 32), (5, 64, 16), (3, 24, 4), (4, 8, 4)])
+def test_dequant_bit_exact(gpu, pkg, out_dim, in_dim, gs, layout):
+    h, (w, s, b) = upload(gpu, pkg.synth, "deq", out_dim, in_dim, gs, layout)
     out = out_with_canary(gpu, out_dim * in_dim)
     gpu.DequantMLX(out, h)
     gpu.Sync()
@@ -51,10 +64,11 @@ def test_dequant_bit_exact_f32_scales(gpu, pkg):
         t.Free()
 
 
-@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("digits", [4, 3])
 @pytest.mark.parametrize("out_dim,in_dim", QWEN3_LAYER)
-def test_gemv_qwen3_layer_shapes(gpu, pkg, out_dim, in_dim, mode):
-    gpu.SetOption("mlx_unpack", mode)
+def test_gemv_qwen3_layer_shapes_tensor_cores(gpu, pkg, out_dim, in_dim, digits):
+    # BASELINE config 0 on the tcgen05 path; bf16-valued activations, 4 or 3 base-128 digits
+    gpu.SetOption("mlx_digits", digits)
     try:
         h, (w, s, b) = upload(gpu, pkg.synth, ("cfg0", out_dim, in_dim), out_dim, in_dim)
         x = pkg.synth.activations(("cfg0", in_dim), in_dim)
@@ -68,15 +82,76 @@ def test_gemv_qwen3_layer_shapes(gpu, pkg, out_dim, in_dim, mode):
         for t in (h, xo, out):
             t.Free()
     finally:
-        gpu.SetOption("mlx_unpack", 1)
+        gpu.SetOption("mlx_digits", 4)
+
+
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 16])
+@pytest.mark.parametrize("out_dim,in_dim", [(4096, 4096), (1000, 4096), (128, 256), (129, 768), (2048, 14336)])
+def test_gemv_tensor_cores_k_splits(gpu, pkg, out_dim, in_dim, splits):
+    # the K range of a tile shared by several CTAs: partials added in split order by the last arriver
+    gpu.SetOption("mlx_splits", splits)
+    try:
+        h, (w, s, b) = upload(gpu, pkg.synth, ("split", out_dim, in_dim), out_dim, in_dim)
+        x = pkg.synth.activations(("split", in_dim), 2 * in_dim, bf16=False)
+        xo = gpu.from_numpy(x)
+        out = out_with_canary(gpu, 2 * out_dim)
+        gpu.GemmMLX(out, xo, h, 2)
+        gpu.Sync()
+        got = read_and_check_canary(out, 2 * out_dim)
+        again = out_with_canary(gpu, 2 * out_dim)
+        gpu.GemmMLX(again, xo, h, 2)
+        gpu.Sync()
+        assert np.array_equal(got, read_and_check_canary(again, 2 * out_dim))  # run-to-run identical
+        want = orc.mlx_gemm(x, 2, w, s, b, out_dim, in_dim, 64, nthreads=8)
+        assert pkg.synth.rel_err(got, want) <= TOL
+        for t in (h, xo, out, again):
+            t.Free()
+    finally:
+        gpu.SetOption("mlx_splits", 0)
+
+
+def test_tensor_core_path_handles_wide_dynamic_range(gpu, pkg):
+    # activations spanning 2^-20 .. 2^12 inside one group, zeros, and an all-zero group
+    out_dim, in_dim = 384, 1024
+    h, (w, s, b) = upload(gpu, pkg.synth, "range", out_dim, in_dim)
+    rng = pkg.synth.rng("range-x")
+    x = (rng.standard_normal(in_dim) * np.exp2(rng.integers(-20, 13, in_dim))).astype(F)
+    x[::7] = 0
+    x[64:128] = 0
+    xo = gpu.from_numpy(x); out = gpu.Malloc(out_dim)
+    gpu.GemvMLX(out, xo, h); gpu.Sync()
+    assert pkg.synth.rel_err(out.Download(), orc.mlx_gemv(x, w, s, b, out_dim, in_dim, 64)) <= TOL
+    for t in (h, xo, out):
+        t.Free()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+@pytest.mark.parametrize("out_dim,in_dim", QWEN3_LAYER)
+def test_gemv_qwen3_layer_shapes(gpu, pkg, out_dim, in_dim, mode):
+    gpu.SetOption("mlx_unpack", mode)
+    try:
+        h, (w, s, b) = upload(gpu, pkg.synth, ("cfg0", out_dim, in_dim), out_dim, in_dim, layout=1)
+        x = pkg.synth.activations(("cfg0", in_dim), in_dim)
+        xo = gpu.from_numpy(x)
+        out = out_with_canary(gpu, out_dim)
+        gpu.GemvMLX(out, xo, h)
+        gpu.Sync()
+        got = read_and_check_canary(out, out_dim)
+        want = orc.mlx_gemv(x, w, s, b, out_dim, in_dim, 64, nthreads=8)
+        assert pkg.synth.rel_err(got, want) <= TOL
+        for t in (h, xo, out):
+            t.Free()
+    finally:
+        gpu.SetOption("mlx_unpack", 0)
 
 
 @pytest.mark.parametrize("rows", [1, 2, 4])
 @pytest.mark.parametrize("out_dim,in_dim,gs", [(4096, 4096, 64), (1000, 4096, 128), (333, 768, 32), (1, 64, 64), (7, 2080, 32)])
 def test_gemv_row_tiles_and_ragged_shapes(gpu, pkg, out_dim, in_dim, gs, rows):
     gpu.SetOption("mlx_rows", rows)
+    gpu.SetOption("mlx_unpack", 0)
     try:
-        h, (w, s, b) = upload(gpu, pkg.synth, ("rag", out_dim, in_dim), out_dim, in_dim, gs)
+        h, (w, s, b) = upload(gpu, pkg.synth, ("rag", out_dim, in_dim), out_dim, in_dim, gs, layout=1)
         x = pkg.synth.activations(("rag", in_dim), in_dim, bf16=False)
         xo = gpu.from_numpy(x)
         out = out_with_canary(gpu, out_dim)
@@ -89,6 +164,7 @@ def test_gemv_row_tiles_and_ragged_shapes(gpu, pkg, out_dim, in_dim, gs, rows):
             t.Free()
     finally:
         gpu.SetOption("mlx_rows", 0)
+        gpu.SetOption("mlx_unpack", 0)
 
 
 @pytest.mark.parametrize("out_dim,in_dim,gs", [(19, 64, 16), (3, 24, 4), (40, 72, 8)])
@@ -108,11 +184,12 @@ def test_gemv_generic_group_sizes(gpu, pkg, out_dim, in_dim, gs):
     h.Free()
 
 
+@pytest.mark.parametrize("layout", [0, 1])
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 7, 8, 9, 13])
-def test_gemm_batches(gpu, pkg, batch):
-    # backends/mlx/gemm_test.go:29-66 batches, at a projection-sized shape
+def test_gemm_batches(gpu, pkg, batch, layout):
+    # backends/mlx/gemm_test.go:29-66 batches, at a projection-sized shape, both kernel families
     out_dim, in_dim, gs = 1536, 2048, 64
-    h, (w, s, b) = upload(gpu, pkg.synth, "gemm", out_dim, in_dim, gs)
+    h, (w, s, b) = upload(gpu, pkg.synth, "gemm", out_dim, in_dim, gs, layout)
     x = pkg.synth.activations(("gemm", batch), batch * in_dim)
     xo = gpu.from_numpy(x)
     out = out_with_canary(gpu, batch * out_dim)
@@ -125,7 +202,7 @@ def test_gemm_batches(gpu, pkg, batch):
     one = gpu.Malloc(out_dim)
     xr = gpu.from_numpy(x[(batch - 1) * in_dim:])
     gpu.GemvMLX(one, xr, h); gpu.Sync()
-    assert pkg.synth.rel_err(got[(batch - 1) * out_dim:], one.Download()) <= 1e-5
+    assert pkg.synth.rel_err(got[(batch - 1) * out_dim:], one.Download()) <= 1e-3
     for t in (h, xo, out, one, xr):
         t.Free()
 
@@ -225,5 +302,5 @@ def test_full_size_against_device_dequant(gpu, pkg, out_dim, in_dim):
     gpu.GemvMLX(gpu.wrap(o1.data_ptr(), out_dim * 4), gpu.wrap(xs.data_ptr(), in_dim * 4), h)
     gpu.Sync()
     lin = out[:out_dim] + out[out_dim:]
-    assert pkg.synth.rel_err(o1.cpu().numpy(), lin.cpu().numpy()) <= 1e-4
+    assert pkg.synth.rel_err(o1.cpu().numpy(), lin.cpu().numpy()) <= 1e-3
     h.Free()
