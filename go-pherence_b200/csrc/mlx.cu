@@ -25,6 +25,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <type_traits>
 #include <vector>
 
 #include "goph_internal.cuh"
@@ -167,53 +168,69 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int task_stride = gridDim.x * kWarps;
-  const int task_first = blockIdx.x * kWarps + warp;
   const int iters = a.iters;
+  const int units = a.units;
+  typedef typename std::conditional<SB_BF16, uint32_t, float2>::type SbT;
 
-  struct Tile {
-    uint4 w[R];
-    uint32_t sb_lo[R], sb_hi[R];  // scale, bias as f32 bit patterns
+  // Per-task state: where this warp's R rows start (16-byte units / table entries) and where
+  // their results go.  Computed once per task, not per iteration.
+  struct Rows {
+    const uint4* w[R];
+    const SbT* sb[R];
+    float* out;
+    int rows, row0;
   };
-
-  // Resolves a warp task to its segment and first row.
-  auto locate = [&](int task, int& seg, int& row0) {
-    seg = 0;
+  auto open_task = [&](int task, Rows& t) {
+    int seg = 0;
 #pragma unroll
     for (int s = 1; s < kMaxSeg; ++s)
       if (s < a.nseg && task >= a.seg[s].task0) seg = s;
-    row0 = (task - a.seg[seg].task0) * R;
-  };
-
-  auto load_tile = [&](int task, int it, Tile& t) {
-    int seg, row0;
-    locate(task, seg, row0);
     const MlxSeg& sg = a.seg[seg];
-    int unit = it * 32 + lane;
-    if (unit >= a.units) unit = a.units - 1;  // x is zero there; any finite weight will do
-    int grp = unit >> a.ug_shift;
+    t.row0 = (task - sg.task0) * R;
+    t.rows = sg.rows;
+    t.out = sg.out;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      int row = row0 + r;
-      if (row >= sg.rows) row = sg.rows - 1;
-      t.w[r] = ld_stream(sg.w + (size_t)row * a.units + unit);
+      int row = t.row0 + r < sg.rows ? t.row0 + r : sg.rows - 1;
+      t.w[r] = sg.w + (size_t)row * units;
+      t.sb[r] = reinterpret_cast<const SbT*>(sg.sb) + (size_t)row * a.groups;
+    }
+  };
+  struct Tile {
+    uint4 w[R];
+    uint32_t s[R], b[R];  // scale, bias as f32 bit patterns
+  };
+  auto load_tile = [&](const Rows& t, int it, Tile& d) {
+    int unit = it * 32 + lane;
+    if (unit >= units) unit = units - 1;  // x is zero there; any finite weight will do
+    const int grp = unit >> a.ug_shift;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      d.w[r] = ld_stream(t.w[r] + unit);
       if (SB_BF16) {
-        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(sg.sb) + (size_t)row * a.groups + grp);
-        t.sb_lo[r] = v << 16;
-        t.sb_hi[r] = v & 0xFFFF0000u;
+        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(t.sb[r]) + grp);
+        d.s[r] = v << 16;
+        d.b[r] = v & 0xFFFF0000u;
       } else {
-        float2 v = __ldg(reinterpret_cast<const float2*>(sg.sb) + (size_t)row * a.groups + grp);
-        t.sb_lo[r] = __float_as_uint(v.x);
-        t.sb_hi[r] = __float_as_uint(v.y);
+        float2 v = __ldg(reinterpret_cast<const float2*>(t.sb[r]) + grp);
+        d.s[r] = __float_as_uint(v.x);
+        d.b[r] = __float_as_uint(v.y);
       }
     }
   };
 
-  // Issue the first weight loads before x is staged so both latencies overlap.
+  // The weights do not depend on the kernel in front: issue the first loads, then wait for it
+  // (programmatic dependent launch) and stage x.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  Rows cur_rows, nxt_rows;
   Tile cur, nxt;
-  int task = task_first, it = 0;
+  int task = blockIdx.x * kWarps + warp;
   const bool has_work = task < a.tasks;
-  if (has_work) load_tile(task, 0, cur);
-
+  if (has_work) {
+    open_task(task, cur_rows);
+    load_tile(cur_rows, 0, cur);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   mlx_stage_x<M, MODE>(a, xs, xc);
   if (!has_work) return;
 
@@ -224,72 +241,68 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
     for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
 
   while (true) {
-    int ntask = task, nit = it + 1;
-    if (nit == iters) {
-      nit = 0;
-      ntask = task + task_stride;
-    }
-    const bool more = ntask < a.tasks;
-    if (more) load_tile(ntask, nit, nxt);
-
-    // ---- compute the current tile ----
-    float2 F[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int m = 0; m < M; ++m) F[r][m] = make_float2(0.f, 0.f);
-
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float4 xa[M], xb[M];
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        const float4* base = xs + ((size_t)(m * iters + it) * 8 + 2 * k) * 32 + lane;
-        xa[m] = base[0];
-        xb[m] = base[32];
+    const int ntask = task + task_stride;
+    const bool more_tasks = ntask < a.tasks;
+    for (int it = 0; it < iters; ++it) {
+      // next tile in flight while this one is computed
+      if (it + 1 < iters) {
+        load_tile(cur_rows, it + 1, nxt);
+      } else if (more_tasks) {
+        open_task(ntask, nxt_rows);
+        load_tile(nxt_rows, 0, nxt);
       }
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        uint32_t word = k == 0 ? cur.w[r].x : k == 1 ? cur.w[r].y : k == 2 ? cur.w[r].z : cur.w[r].w;
-        float f[8];
-        Unpack<MODE>::run(word, f);
-#pragma unroll
-        for (int m = 0; m < M; ++m) {
-          fma2(F[r][m], make_float2(f[0], f[1]), make_float2(xa[m].x, xa[m].y));
-          fma2(F[r][m], make_float2(f[2], f[3]), make_float2(xa[m].z, xa[m].w));
-          fma2(F[r][m], make_float2(f[4], f[5]), make_float2(xb[m].x, xb[m].y));
-          fma2(F[r][m], make_float2(f[6], f[7]), make_float2(xb[m].z, xb[m].w));
-        }
-      }
-    }
-#pragma unroll
-    for (int m = 0; m < M; ++m) {
-      float2 c = xc[(m * iters + it) * 32 + lane];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        float dot = (F[r][m].x + F[r][m].y) - c.x;
-        acc[r][m] = fmaf(__uint_as_float(cur.sb_lo[r]), dot, acc[r][m]);
-        acc[r][m] = fmaf(__uint_as_float(cur.sb_hi[r]), c.y, acc[r][m]);
-      }
-    }
-
-    if (it == iters - 1) {
-      int seg, row0;
-      locate(task, seg, row0);
-      const MlxSeg& sg = a.seg[seg];
+      float2 F[R][M];
 #pragma unroll
       for (int r = 0; r < R; ++r)
 #pragma unroll
+        for (int m = 0; m < M; ++m) F[r][m] = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float4 xa[M], xb[M];
+#pragma unroll
         for (int m = 0; m < M; ++m) {
-          float v = warp_sum(acc[r][m]);
-          acc[r][m] = 0.f;
-          if (lane == 0 && row0 + r < sg.rows && m < a.batch) sg.out[(size_t)m * sg.rows + row0 + r] = v;
+          const float4* base = xs + ((size_t)(m * iters + it) * 8 + 2 * k) * 32 + lane;
+          xa[m] = base[0];
+          xb[m] = base[32];
         }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          uint32_t word = k == 0 ? cur.w[r].x : k == 1 ? cur.w[r].y : k == 2 ? cur.w[r].z : cur.w[r].w;
+          float f[8];
+          Unpack<MODE>::run(word, f);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            fma2(F[r][m], make_float2(f[0], f[1]), make_float2(xa[m].x, xa[m].y));
+            fma2(F[r][m], make_float2(f[2], f[3]), make_float2(xa[m].z, xa[m].w));
+            fma2(F[r][m], make_float2(f[4], f[5]), make_float2(xb[m].x, xb[m].y));
+            fma2(F[r][m], make_float2(f[6], f[7]), make_float2(xb[m].z, xb[m].w));
+          }
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float2 c = xc[(m * iters + it) * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          float dot = (F[r][m].x + F[r][m].y) - c.x;
+          acc[r][m] = fmaf(__uint_as_float(cur.s[r]), dot, acc[r][m]);
+          acc[r][m] = fmaf(__uint_as_float(cur.b[r]), c.y, acc[r][m]);
+        }
+      }
+      cur = nxt;
     }
-    if (!more) break;
-    cur = nxt;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float v = warp_sum(acc[r][m]);
+        acc[r][m] = 0.f;
+        if (lane == 0 && cur_rows.row0 + r < cur_rows.rows && m < a.batch)
+          cur_rows.out[(size_t)m * cur_rows.rows + cur_rows.row0 + r] = v;
+      }
+    if (!more_tasks) break;
+    cur_rows = nxt_rows;
     task = ntask;
-    it = nit;
   }
 }
 
@@ -489,8 +502,18 @@ static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, i
   int grid = (tasks + kWarps - 1) / kWarps;
   int cap = st.sm_count * per_sm;
   if (grid > cap) grid = cap;
-  k<<<grid, kThreads, smem, stream>>>(a);
-  GOPH_CUDA(cudaGetLastError());
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, k, a));
   return GOPH_OK;
 }
 
@@ -514,11 +537,17 @@ static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const*
   for (int i = 0; i < n; ++i) any_tiled = any_tiled || ws[i]->tiled;
   if (any_tiled) {
     // tiled weights run on the tensor cores; row-major ones in the same call take their own path
+    bool prepared = false;  // weights of one call share x: its digits are prepared once
     for (int i = 0; i < n; ++i) {
       const goph_mlx_weight* one = ws[i];
       float* o = outs[i];
-      int rc = one->tiled ? mlx_mma_launch(one, o, x, batch, options().mlx_digits, stream)
-                          : mlx_products(1, &o, &one, x, batch, stream);
+      int rc;
+      if (one->tiled) {
+        rc = mlx_mma_launch(one, o, x, batch, options().mlx_digits, stream, prepared);
+        prepared = true;
+      } else {
+        rc = mlx_products(1, &o, &one, x, batch, stream);
+      }
       if (rc) return rc;
     }
     return GOPH_OK;
@@ -616,7 +645,10 @@ static int mlx_upload_common(int device, const uint32_t* weight, const float* sc
   UP(cudaDeviceSynchronize());
 #undef UP
   h->bytes = want_w * 4 + want_s * (h->sb_bf16 ? 4 : 8);
-  if (options().mlx_layout == 0 && mlx_mma_supported(h)) {
+  // Tiled layout + tensor-core kernel for matrices large enough to amortise that kernel's fixed
+  // cost (TMEM set-up, activation preparation, pipeline fill); small ones stay row-major.
+  const bool big = (uint64_t)out_dim * (uint64_t)in_dim >= (8u << 20);
+  if (mlx_mma_supported(h) && (options().mlx_layout == 2 || (options().mlx_layout == 0 && big))) {
     if (int rc = mlx_mma_make_tiled(h)) return cleanup(rc);
     cudaFree(h->qweight);
     cudaFree(h->sb);

@@ -100,6 +100,11 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, int* 
   return r;
 }
 
+// Programmatic dependent launch: let the next kernel in the stream start its prologue now /
+// wait until every kernel this one depends on has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
@@ -210,6 +215,8 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
   const int groups = in_dim / 64;
   const int m = blockIdx.x / groups, g = blockIdx.x - m * groups;
   const int t = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();  // x may be the output of the kernel in front
   const float v = x[(size_t)m * in_dim + g * 64 + t];
   float s = v, mx = fabsf(v);
 #pragma unroll
@@ -254,9 +261,9 @@ template <int N, int DIGITS, int MB>
 __global__ void __launch_bounds__(kThreads, 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
-  static_assert(N == 16 || N == 32, "accumulator blocks of 16 or 32 columns");
-  constexpr int NB = N == 16 ? 4 : 2;           // depth of the A / accumulator rings in TMEM
-  constexpr uint32_t kCols = 512;               // NB * (64 + 4N) columns
+  static_assert(N == 8 || N == 16 || N == 32, "accumulator blocks of 8, 16 or 32 columns");
+  constexpr int NB = N <= 16 ? 4 : 2;           // depth of the A / accumulator rings in TMEM
+  constexpr uint32_t kCols = 512;               // >= NB * (64 + 4N) columns
   constexpr int kStage = MmaSmem<N>::kStage;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
@@ -291,7 +298,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  for (int i = tid; i < 2 * a.batch * groups; i += kThreads) xsum[i] = __ldg(a.xtab + i);
+  pdl_launch_dependents();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -306,9 +313,25 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       const bool pr = a.probe && blockIdx.x == 0;
       long long w0 = 0, tstart = clock64();
       int nst = 0;
-      for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
+      // The weights do not depend on the kernel in front: fill the ring with them first, then
+      // wait for the activation digits and add the B tiles of those stages.
+      int i = 0;
+      {
+        StageWalk sw0 = sw;
+        for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
+          uint32_t dst = smem_u32(ring + (size_t)i * kStage);
+          mbar_expect_tx(full0 + 8 * i, kStage);
+          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, kStageBytes, full0 + 8 * i);
+        }
+        pdl_wait();
+        for (int j = 0; j < i; ++j, sw.next(a))
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N>::kBTileBytes,
+                       MmaSmem<N>::kBTileBytes, full0 + 8 * j);
+        nst = i;
+      }
+      for (; sw.live(a) && ok; ++i, sw.next(a)) {
         int slot = i % S, round = i / S;
-        if (round > 0) ok = mbar_wait_t(empty0 + 8 * slot, (round - 1) & 1, a.status, 1, pr, w0);
+        ok = mbar_wait_t(empty0 + 8 * slot, (round - 1) & 1, a.status, 1, pr, w0);
         if (!ok) break;
         ++nst;
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
@@ -424,6 +447,9 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     float acc[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+    pdl_wait();  // the tables come from the preparation kernel in front
+    for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     const bool pr = a.probe && blockIdx.x == 0 && et == 0;
     long long w0 = 0, w1 = 0, tstart = clock64();
     for (int i = 0; sw.live(a) && ok; ++i) {
@@ -453,6 +479,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       for (int g = 0; g < 4; ++g)
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
+          // (with N = 8 the load also brings the next block's eight columns, which are ignored)
           if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (4 * N) + g * N + l * 16, t[g][l]);
           else {
 #pragma unroll
@@ -648,7 +675,7 @@ int mlx_mma_status(int device) {
 }
 
 template <int N, int DIGITS, int MB>
-static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t stream) {
+static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t stream, bool prep) {
   MmaArgs a = a0;
   DeviceState& st = device_state(w->device);
   size_t fixed = MmaSmem<N>::bytes(0, a.batch, a.in_dim);
@@ -671,18 +698,31 @@ static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t 
   size_t smem = MmaSmem<N>::bytes(stages, a.batch, a.in_dim);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
   // activations -> digits, sums and scales, once per launch
-  mlx_prep_x_kernel<DIGITS><<<a.batch * (a.in_dim / 64), 64, 0, stream>>>(a.x, const_cast<unsigned char*>(a.xb),
-                                                                         const_cast<float*>(a.xtab), a.batch, a.in_dim, N);
-  GOPH_CUDA(cudaGetLastError());
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
+  cfg.blockDim = dim3(64);
+  if (prep)
+    GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS>, a.x, const_cast<unsigned char*>(a.xb),
+                                 const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
   auto kern = mlx_mma_kernel<N, DIGITS, MB>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
-  kern<<<grid, kThreads, smem, stream>>>(a);
-  GOPH_CUDA(cudaGetLastError());
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
 }
 
-int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream) {
+int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                   bool x_prepared) {
   if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
   MmaDeviceBufs* bufs = device_bufs(w->device);
   if (!bufs) return fail(GOPH_E_NOMEM, "cannot allocate the tensor-core path's device scratch");
@@ -706,16 +746,17 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
     a.x = x + (size_t)b0 * w->in_dim;
     a.out = out + (size_t)b0 * w->out_dim;
     a.batch = nb;
+    const bool prep = !(x_prepared && batch <= cap);
     int rc;
     if (digits == 3) {
-      rc = nb == 1 ? launch_one<16, 3, 1>(w, a, stream)
-         : nb <= 5 ? launch_one<16, 3, 5>(w, a, stream)
-                   : launch_one<32, 3, 8>(w, a, stream);
+      rc = nb <= 2 ? launch_one<8, 3, 2>(w, a, stream, prep)
+         : nb <= 5 ? launch_one<16, 3, 5>(w, a, stream, prep)
+                   : launch_one<32, 3, 8>(w, a, stream, prep);
     } else {
-      rc = nb == 1 ? launch_one<16, 4, 1>(w, a, stream)
-         : nb == 2 ? launch_one<16, 4, 2>(w, a, stream)
-         : nb <= 4 ? launch_one<16, 4, 4>(w, a, stream)
-                   : launch_one<32, 4, 8>(w, a, stream);
+      rc = nb == 1 ? launch_one<8, 4, 1>(w, a, stream, prep)
+         : nb == 2 ? launch_one<8, 4, 2>(w, a, stream, prep)
+         : nb <= 4 ? launch_one<16, 4, 4>(w, a, stream, prep)
+                   : launch_one<32, 4, 8>(w, a, stream, prep);
     }
     if (rc) return rc;
     b0 += nb;

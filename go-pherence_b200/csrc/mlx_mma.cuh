@@ -22,8 +22,10 @@ __host__ __device__ inline size_t mlx_tiled_meta_offset(int row, int col, int nc
   return blk * kMlxBlockBytes + kMlxBlockW + (row & 127) * 16 + ((col & 255) >> 6) * 4;
 }
 // out[batch][out_dim] = x[batch][in_dim] * W^T.  digits: base-128 digits each activation is
-// written in (4 = 27 bits under the group maximum, 3 = 20 bits).
-int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream);
+// written in (4 = 27 bits under the group maximum, 3 = 20 bits).  x_prepared: the previous
+// launch on this stream prepared the same x (same batch, same in_dim), skip the preparation.
+int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                   bool x_prepared = false);
 // Reads the device status word (0 = every wait completed); synchronises the copy stream.
 int mlx_mma_status(int device);
 // Copies the 32 cycle counters CTA 0 wrote when option mlx_probe is on (tuning aid).

@@ -70,8 +70,10 @@ GOPH_API int goph_set_option(const char* name, int value) {
   if (!name) return fail(GOPH_E_INVALID, "goph_set_option: nil name");
   Options& o = options();
   bool rows_ok = value == 0 || value == 1 || value == 2 || value == 4;
-  if (!strcmp(name, "mlx_layout")) {
-    if (value < 0 || value > 1) return fail(GOPH_E_INVALID, "mlx_layout=%d not 0 or 1", value);
+  if (!strcmp(name, "pdl")) {
+    o.pdl = value != 0;
+  } else if (!strcmp(name, "mlx_layout")) {
+    if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_layout=%d not in 0..2", value);
     o.mlx_layout = value;
   } else if (!strcmp(name, "mlx_dbg")) {
     o.mlx_dbg = value;

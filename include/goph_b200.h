@@ -62,10 +62,13 @@ int goph_sm_count(int device);
 
 /* Tuning switches.  The reference reads its own from GO_PHERENCE_* environment variables at
  * the call sites (model/gpu_forward.go:24-47, :776-785); here they are set by name:
- *   "mlx_layout"  device layout chosen by goph_mlx_upload: 0 (default) the tiled layout of the
- *                 tensor-core (tcgen05) kernel when the shape allows it (group size 64, in_dim a
- *                 multiple of 256, bf16-valued scales and biases), 1 always the row-major layout of
- *                 the CUDA-core kernels
+ *   "pdl"         1 (default) launches kernels with programmatic stream serialization so a kernel's
+ *                 prologue and weight prefetch overlap the tail of the kernel in front; 0 plain launches
+ *   "mlx_layout"  device layout chosen by goph_mlx_upload.  The tiled layout feeds the tensor-core
+ *                 (tcgen05) kernel and needs group size 64, in_dim a multiple of 256 and bf16-valued
+ *                 scales and biases; the row-major layout feeds the CUDA-core kernels.  0 (default):
+ *                 tiled for matrices of 8 Mi weights or more, row-major below; 1: always row-major;
+ *                 2: tiled whenever the shape allows
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)

@@ -14,8 +14,8 @@ pytestmark = pytest.mark.gpu
 QWEN3_LAYER = [(2048, 1024), (1024, 1024), (1024, 1024), (1024, 2048), (3072, 1024), (3072, 1024), (1024, 3072)]
 
 
-def upload(rt, syn, key, out_dim, in_dim, gs=64, layout=0):
-    """layout 0: the library's choice (tiled + tensor cores when the shape allows), 1: row-major."""
+def upload(rt, syn, key, out_dim, in_dim, gs=64, layout=2):
+    """layout 2: tiled + tensor cores whenever the shape allows, 1: row-major, 0: the library's choice by size."""
     w, s, b = syn.mlx_weight(key, out_dim, in_dim, gs)
     rt.SetOption("mlx_layout", layout)
     try:
@@ -31,7 +31,7 @@ def no_wait_gave_up(gpu):
     assert gpu.KernelStatus() == 0
 
 
-@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("layout", [2, 1])
 @pytest.mark.parametrize("out_dim,in_dim,gs", [(2048, 1024, 64), (1024, 3072, 64), (300, 256, 64), (37, 96, 32), (5, 64, 16), (3, 24, 4), (4, 8, 4)])
 def test_dequant_bit_exact(gpu, pkg, out_dim, in_dim, gs, layout):
     h, (w, s, b) = upload(gpu, pkg.synth, "deq", out_dim, in_dim, gs, layout)
@@ -184,7 +184,7 @@ def test_gemv_generic_group_sizes(gpu, pkg, out_dim, in_dim, gs):
     h.Free()
 
 
-@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("layout", [2, 1, 0])
 @pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 7, 8, 9, 13])
 def test_gemm_batches(gpu, pkg, batch, layout):
     # backends/mlx/gemm_test.go:29-66 batches, at a projection-sized shape, both kernel families
