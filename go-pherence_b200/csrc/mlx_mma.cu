@@ -764,4 +764,127 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
   return GOPH_OK;
 }
 
+
+// ---- GEMV without any allocation ---------------------------------------------------------------
+// Some callers must not allocate device memory when they run a product: a serving loop that has
+// handed the whole memory budget to its KV and expert pools (an allocation could fail, or block
+// behind a free), a thread that may not take the allocator's device-wide synchronisation in the
+// middle of a decode step, or code that has begun capturing a stream.  For them the scratch of the
+// tensor-core GEMV (status word, tile counters, the prepared activation digits and tables, the
+// split-K partial sums) lives in this file-scope device array instead of in buffers obtained with
+// cudaMalloc.  Every GPU that loads the library carries the array until the process exits.
+constexpr int kNoAllocMaxIn = 16384;     // largest in_dim the entry point accepts
+constexpr int kNoAllocMaxTiles = 4096;   // largest ceil(out_dim / 128)
+constexpr int kNoAllocMaxItems = 192;    // (tile, split) items that may have partial sums at once
+constexpr size_t kNaStatusOff = 0;
+constexpr size_t kNaCountersOff = 256;
+constexpr size_t kNaTabOff = kNaCountersOff + (size_t)kNoAllocMaxTiles * 4;
+constexpr size_t kNaXbOff = kNaTabOff + (size_t)2 * (kNoAllocMaxIn / 64) * 4;
+constexpr size_t kNaPartOff = kNaXbOff + (size_t)8 * kNoAllocMaxIn;
+constexpr size_t kNoAllocBytes = kNaPartOff + (size_t)kNoAllocMaxItems * kTileRows * 4;
+static_assert(kNaTabOff % 256 == 0 && kNaXbOff % 256 == 0 && kNaPartOff % 256 == 0, "256-byte aligned regions");
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];  // 248,064 bytes
+
+// Device address of the array on `device` (which must be current).  In host code the array's
+// name is only a handle for the runtime, never a pointer a kernel could use, so the address is
+// looked up once per device with cudaGetSymbolAddress and cached.
+static int noalloc_base(int device, unsigned char** base) {
+  static unsigned char* cached[kMaxDevices] = {};
+  if (!cached[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+    if (!p) return fail(GOPH_E_CUDA, "cudaGetSymbolAddress returned a null address for the scratch array");
+    cached[device] = static_cast<unsigned char*>(p);
+  }
+  *base = cached[device];
+  return GOPH_OK;
+}
+
+template <int DIGITS>
+static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, unsigned char* base,
+                          cudaStream_t stream) {
+  constexpr int N = 8, MB = 1;
+  DeviceState& st = device_state(w->device);
+  MmaArgs a;
+  memset(&a, 0, sizeof a);
+  a.w = w->tiled;
+  a.x = x;
+  a.out = out;
+  a.status = reinterpret_cast<int*>(base + kNaStatusOff);
+  a.counters = reinterpret_cast<unsigned int*>(base + kNaCountersOff);
+  a.xtab = reinterpret_cast<const float*>(base + kNaTabOff);
+  a.xb = base + kNaXbOff;
+  a.scratch = reinterpret_cast<float*>(base + kNaPartOff);
+  a.out_dim = w->out_dim;
+  a.in_dim = w->in_dim;
+  a.batch = 1;
+  a.ntiles = (w->out_dim + kTileRows - 1) / kTileRows;
+  a.nchunks = w->in_dim / kChunkK;
+  size_t fixed = MmaSmem<N>::bytes(0, 1, a.in_dim);
+  int stages = (int)(((size_t)kSmemBudget - fixed) / MmaSmem<N>::kStage);
+  if (stages > 8) stages = 8;
+  a.stages = stages;
+  int splits = 1;
+  if (a.ntiles < st.sm_count) {
+    splits = st.sm_count / a.ntiles;
+    if (splits > a.nchunks) splits = a.nchunks;
+    if (splits < 1) splits = 1;
+  }
+  while (splits > 1 && a.ntiles * splits > kNoAllocMaxItems) --splits;
+  a.splits = splits;
+  a.items = a.ntiles * splits;
+  // The array keeps whatever the last call left: the status word and the tile counters have to
+  // start at zero (the digits, tables and partial sums are fully rewritten before they are read).
+  GOPH_CUDA(cudaMemsetAsync(base, 0, kNaTabOff, stream));
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = 0;  // plain stream order behind the memset
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(a.in_dim / 64);
+  cfg.blockDim = dim3(64);
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS>, a.x, const_cast<unsigned char*>(a.xb),
+                               const_cast<float*>(a.xtab), 1, a.in_dim, N));
+  size_t smem = MmaSmem<N>::bytes(stages, 1, a.in_dim);
+  if (smem < 120 * 1024) smem = 120 * 1024;
+  auto kern = mlx_mma_kernel<N, DIGITS, MB>;
+  GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  return GOPH_OK;
+}
+
 }  // namespace goph
+
+using namespace goph;
+
+GOPH_API int goph_mlx_gemv_noalloc(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                                   const goph_mlx_weight* w, void* stream) {
+  clear_error();
+  if (!w || w->magic != kMagicMLX) return fail(GOPH_E_INVALID, "invalid MLX weight handle");
+  if (!w->tiled)
+    return fail(GOPH_E_UNSUPPORTED,
+                "goph_mlx_gemv_noalloc needs a weight in the tiled layout (group size 64, in_dim a multiple of 256, "
+                "uploaded with mlx_layout 0 or 2); this one is row-major");
+  if (w->in_dim > kNoAllocMaxIn)
+    return fail(GOPH_E_UNSUPPORTED, "goph_mlx_gemv_noalloc: in_dim=%d is above the built-in scratch limit of %d", w->in_dim,
+                kNoAllocMaxIn);
+  if ((w->out_dim + kTileRows - 1) / kTileRows > kNoAllocMaxTiles)
+    return fail(GOPH_E_UNSUPPORTED, "goph_mlx_gemv_noalloc: out_dim=%d is above the built-in scratch limit of %d", w->out_dim,
+                kNoAllocMaxTiles * kTileRows);
+  if (!x_dev || x_len < (uint64_t)w->in_dim || !out_dev || out_len < (uint64_t)w->out_dim)
+    return fail(GOPH_E_INVALID, "buffers x=%llu/%d out=%llu/%d", (unsigned long long)x_len, w->in_dim,
+                (unsigned long long)out_len, w->out_dim);
+  if ((uintptr_t)x_dev % 16) return fail(GOPH_E_INVALID, "goph_mlx_gemv_noalloc: x must be 16-byte aligned");
+  if (int rc = use_device(w->device)) return rc;
+  unsigned char* base = nullptr;
+  if (int rc = noalloc_base(w->device, &base)) return rc;
+  return options().mlx_digits == 3 ? launch_noalloc<3>(w, out_dev, x_dev, base, (cudaStream_t)stream)
+                                   : launch_noalloc<4>(w, out_dev, x_dev, base, (cudaStream_t)stream);
+}

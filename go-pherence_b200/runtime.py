@@ -24,7 +24,8 @@ EXPORTS = [
     "goph_init", "goph_set_option", "goph_kernel_status", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
-    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemm_host",
+    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
+    "goph_mlx_gemm_host",
     "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
     "goph_gguf_project", "goph_gguf_project_host",
     "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm",
@@ -228,6 +229,17 @@ def GemvMLX(out, x, w, stream=None):
         raise GophError(1, "nil buffer")
     _check(lib().goph_mlx_gemv(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
                                _mlx_handle(w), _stream_ptr(stream)))
+
+
+def GemvMLXNoAlloc(out, x, w, stream=None):
+    """out = W·x through goph_mlx_gemv_noalloc: the same product as GemvMLX for callers that cannot
+    allocate device memory at this point (committed memory budget, no allocator synchronisation
+    allowed mid-step, stream already being captured).  Tiled weights only, in_dim <= 16384, batch 1;
+    calls that may overlap on the GPU must be ordered by the caller (they share one scratch array)."""
+    if out is None or x is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_mlx_gemv_noalloc(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                                       _mlx_handle(w), _stream_ptr(stream)))
 
 
 GemvMLXDirect = GemvMLX  # nvidia.GemvMLXDirect (runtime/mlx.go:455): same kernel here.

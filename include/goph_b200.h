@@ -130,6 +130,24 @@ int goph_mlx_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t
  * group size share one x [batch,in]; outs_dev[i] is [batch, out_dim_i].  One launch. */
 int goph_mlx_gemm_multi(int n, float* const* outs_dev, const goph_mlx_weight* const* ws,
                         const float* x_dev, uint64_t x_len, int batch, void* stream);
+/* No counterpart in the reference.  out = W·x (batch 1) for a weight in the tiled layout, computed
+ * without allocating: no cudaMalloc, cudaFree or allocating library call happens inside.  It is
+ * meant for callers that cannot allocate device memory at the point where they need a product —
+ * a serving loop whose memory budget is fully committed to KV and expert pools, a thread that must
+ * not take the allocator's device-wide synchronisation in the middle of a decode step, or code that
+ * is already capturing its stream.  The kernel's scratch (health word, tile counters, prepared
+ * activation digits, split-K partial sums) lives in a 242 KiB array that is part of the library
+ * image on every GPU that loads it.
+ * Limits: in_dim <= 16384, out_dim <= 524288, batch 1, tiled layout only (group size 64, in_dim a
+ * multiple of 256, bf16-valued scales/biases, uploaded with "mlx_layout" 0 or 2) — anything else
+ * is rejected with GOPH_E_UNSUPPORTED and a text that names the limit.  x_dev must be 16-byte aligned.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that
+ * first call before any stream capture begins.  All calls on a device share the one array: calls
+ * that can overlap on the GPU (different streams without an ordering between them) race on it, so
+ * keep them in one stream or order them with events.  The array keeps the previous call's contents;
+ * the entry point clears the parts that must start at zero with a memset on `stream`. */
+int goph_mlx_gemv_noalloc(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                          const goph_mlx_weight* w, void* stream);
 /* Host-slice form, as nvidia.GemvQ4K/GemmFP8E4M3 take Go slices (runtime/q4k.go:571,
  * fp8.go:180): copies x in, runs, copies out back, synchronises. */
 int goph_mlx_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
