@@ -94,9 +94,75 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     return res
 
 
+def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, launches=40, opts=()):
+    """Selected-expert projection at the Qwen3-30B-A3B layer shape: `layers` distinct layers are walked
+    so consecutive calls do not find their experts in L2.  Bytes counted: the router plus three matrices
+    of every distinct expert the call's tokens selected."""
+    import numpy as np
+    import torch
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(0)
+    for k, v in opts:
+        rt.SetOption(k, v)
+    rt.SetOption("mlx_layout", 1)
+    g = syn.rng("moe-bench")
+    mods, keep = [], []
+    for l in range(layers):
+        m = rt.GPUMoELayer(experts, hidden, inter, 64, top_k, True, max(tokens, 1))
+        r = rt.UploadMLXWeight(*syn.mlx_weight(("r", l), experts, hidden, 64), hidden, experts, 64, True)
+        m.SetRouter(r)
+        keep.append(r)
+        for e in range(experts):
+            hs = []
+            for o, i in ((inter, hidden), (inter, hidden), (hidden, inter)):
+                w = g.integers(0, 2**32, size=o * i // 8, dtype=np.uint32)
+                sc = syn.bf16_round(np.abs(g.standard_normal(o * i // 64, dtype=np.float32)) * np.float32(0.02) + np.float32(1e-3))
+                hs.append(rt.UploadMLXWeight(w, sc, syn.bf16_round(np.float32(-8) * sc), i, o, 64, True))
+            m.SetExpert(e, *hs)
+            keep += hs
+        mods.append(m)
+    rt.SetOption("mlx_layout", 0)
+    x = torch.from_numpy(syn.activations("moe-bench", tokens * hidden)).cuda()
+    out = torch.empty(tokens * hidden, dtype=torch.float32, device="cuda")
+    xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
+    stream = torch.cuda.current_stream()
+    distinct = []
+    for m in mods:
+        m.Forward(ob, xb, tokens, stream)
+        torch.cuda.synchronize()
+        distinct.append(len(set(m.LastRouting(tokens)[0].reshape(-1).tolist())))
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(launches):
+            mods[i % layers].Forward(ob, xb, tokens, torch.cuda.current_stream())
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+    per_expert = (2 * inter * hidden + hidden * inter) * 0.5625
+    nbytes = sum(distinct) / layers * per_expert + experts * hidden * 0.5625 + tokens * hidden * 8
+    peak = 6650.0
+    pk = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = float(json.load(open(pk))["hbm_gbs"])
+    gbs = nbytes / us / 1e3
+    return {"format": "moe-mlx4", "tokens": tokens, "experts": experts, "top_k": top_k, "hidden": hidden, "inter": inter,
+            "distinct_experts_per_call": sum(distinct) / layers, "us_per_call": round(us, 2), "GBps": round(gbs, 1),
+            "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q8_0", "fp8"])
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q8_0", "fp8", "moe"])
     ap.add_argument("--out", type=int, default=4096)
     ap.add_argument("--in", dest="in_dim", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1)
@@ -105,6 +171,9 @@ def main():
     ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
     args = ap.parse_args()
     opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
+    if args.format == "moe":
+        print(json.dumps(run_moe(args.tokens, opts=opts)))
+        return
     print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts)))
 
 

@@ -30,6 +30,11 @@ EXPORTS = [
     "goph_gguf_project", "goph_gguf_project_host",
     "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm",
     "goph_fp8_gemm_host",
+    "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
+    "goph_moe_forward_logits", "goph_moe_last_routing",
+    "goph_shard_rows", "goph_gather_create", "goph_gather_export", "goph_gather_open_peer", "goph_gather_attach_local",
+    "goph_gather_free", "goph_gather_status", "goph_gather_shard_buffer", "goph_gather_all",
+    "goph_mlx_gemm_allgather", "goph_gguf_project_allgather", "goph_fp8_gemm_allgather", "goph_moe_forward_sharded",
 ]
 
 
@@ -424,3 +429,145 @@ def GemvFP8E4M3(x, w):
 def DequantFP8E4M3(out, w, stream=None):
     """fp8.Linear.DequantRowTo for every row (backends/simd/quant/fp8/fp8.go:181-198)."""
     _check(lib().goph_fp8_dequant(_fp8_handle(w), C.c_void_p(out.Ptr), C.c_uint64(out.n), _stream_ptr(stream)))
+
+
+# ------------------------------------------------------------------------------ MoE
+class GPUMoELayer:
+    """The MoE state of one layer as model.moeForwardGPU uses it (model/moe_gpu.go:49-130):
+    router weight, per-expert gate/up/down GPUMLXWeight, routing constants.  Experts left unset
+    are not resident on this GPU and contribute nothing (per-GPU expert placement)."""
+
+    def __init__(self, numExperts, hidden, inter, groupSize=64, topK=8, normTopK=True, maxTokens=32):
+        h = C.c_void_p(0)
+        _check(lib().goph_moe_create(_device, int(numExperts), int(hidden), int(inter), int(groupSize), int(topK),
+                                     int(bool(normTopK)), int(maxTokens), C.byref(h)))
+        self._h = h
+        self.NumExperts, self.Hidden, self.Inter = int(numExperts), int(hidden), int(inter)
+        self.TopK = min(int(topK) if topK > 0 else 8, int(numExperts))
+        self._keep = {}
+
+    def _handle(self):
+        if not self._h:
+            raise GophError(1, "nil or freed GPUMoELayer")
+        return self._h
+
+    def SetRouter(self, w):
+        _check(lib().goph_moe_set_router(self._handle(), _mlx_handle(w)))
+        self._keep["router"] = w
+
+    def SetExpert(self, eid, gate, up, down):
+        if gate is None and up is None and down is None:
+            _check(lib().goph_moe_set_expert(self._handle(), int(eid), None, None, None))
+            self._keep.pop(eid, None)
+            return
+        _check(lib().goph_moe_set_expert(self._handle(), int(eid), _mlx_handle(gate), _mlx_handle(up), _mlx_handle(down)))
+        self._keep[eid] = (gate, up, down)
+
+    def Forward(self, out, x, tokens=1, stream=None):
+        """moeForwardGPU for `tokens` rows of x (model/moe_gpu.go:49)."""
+        _check(lib().goph_moe_forward(self._handle(), C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr),
+                                      C.c_uint64(x.n), int(tokens), _stream_ptr(stream)))
+
+    def ForwardLogits(self, out, x, logits, tokens=1, stream=None):
+        """The selected-expert projection with router logits supplied by the caller."""
+        _check(lib().goph_moe_forward_logits(self._handle(), C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr),
+                                             C.c_uint64(x.n), C.c_void_p(logits.Ptr), C.c_uint64(logits.n),
+                                             int(tokens), _stream_ptr(stream)))
+
+    def LastRouting(self, tokens=1):
+        ids = np.empty(tokens * self.TopK, dtype=np.int32)
+        wts = np.empty(tokens * self.TopK, dtype=np.float32)
+        _check(lib().goph_moe_last_routing(self._handle(), int(tokens), _vp(ids), _vp(wts)))
+        return ids.reshape(tokens, self.TopK), wts.reshape(tokens, self.TopK)
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_moe_free(self._h))
+            self._h = None
+            self._keep = {}
+
+
+# ------------------------------------------------------------------------------ row sharding
+def ShardRows(outDim, rank, world, align=8):
+    """Rows [lo, hi) of a projection owned by `rank` (goph_shard_rows)."""
+    lo, hi = C.c_int(0), C.c_int(0)
+    _check(lib().goph_shard_rows(int(outDim), int(rank), int(world), int(align), C.byref(lo), C.byref(hi)))
+    return lo.value, hi.value
+
+
+class Gather:
+    """Exchange area of this rank for row-sharded outputs (no counterpart in the single-GPU reference)."""
+
+    def __init__(self, rank, world, capacityFloats):
+        h = C.c_void_p(0)
+        _check(lib().goph_gather_create(_device, int(rank), int(world), C.c_uint64(int(capacityFloats)), C.byref(h)))
+        self._h, self.rank, self.world, self.capacity, self.device = h, int(rank), int(world), int(capacityFloats), _device
+
+    def Export(self):
+        buf = (C.c_ubyte * 64)()
+        _check(lib().goph_gather_export(self._h, buf))
+        return bytes(buf)
+
+    def OpenPeer(self, peerRank, handle):
+        buf = (C.c_ubyte * 64)(*handle)
+        _check(lib().goph_gather_open_peer(self._h, int(peerRank), buf))
+
+    def AttachLocal(self, peer):
+        _check(lib().goph_gather_attach_local(self._h, peer._h))
+
+    def Connect(self, dist):
+        """Exchanges the area tokens over an initialised torch.distributed group (host-side plumbing)."""
+        handles = [None] * self.world
+        dist.all_gather_object(handles, self.Export())
+        for r, h in enumerate(handles):
+            if r != self.rank:
+                self.OpenPeer(r, h)
+        dist.barrier()
+
+    def Status(self):
+        v = C.c_int(0)
+        _check(lib().goph_gather_status(self._h, C.byref(v)))
+        return v.value
+
+    def ShardBuffer(self):
+        p = C.c_void_p(0)
+        _check(lib().goph_gather_shard_buffer(self._h, C.byref(p)))
+        return Buffer(p.value, self.capacity * 4, self.device, owned=False)
+
+    def _result(self, p, n):
+        return Buffer(p.value, int(n) * 4, self.device, owned=False)
+
+    def All(self, src, rows, count, dstOff, dstRowStride, stream=None):
+        p = C.c_void_p(0)
+        _check(lib().goph_gather_all(self._h, C.c_void_p(src.Ptr if src is not None else 0), int(rows), int(count),
+                                     C.c_int64(int(dstOff)), C.c_int64(int(dstRowStride)), _stream_ptr(stream), C.byref(p)))
+        return self._result(p, (rows - 1) * dstRowStride + max(dstRowStride, dstOff + count))
+
+    def GemmMLX(self, x, shard, B, rowLo, outDimFull, stream=None):
+        """GemmMLX for a weight split by rows over the GPUs; returns this rank's [B x outDimFull] buffer."""
+        p = C.c_void_p(0)
+        _check(lib().goph_mlx_gemm_allgather(self._h, _mlx_handle(shard), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(B),
+                                             int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
+        return self._result(p, B * outDimFull)
+
+    def ProjectGGUF(self, x, shard, batch, rowLo, outDimFull, stream=None):
+        p = C.c_void_p(0)
+        _check(lib().goph_gguf_project_allgather(self._h, shard._h, C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
+                                                 int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
+        return self._result(p, batch * outDimFull)
+
+    def GemmFP8E4M3(self, x, shard, batch, rowLo, outDimFull, stream=None):
+        p = C.c_void_p(0)
+        _check(lib().goph_fp8_gemm_allgather(self._h, _fp8_handle(shard), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
+                                             int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
+        return self._result(p, batch * outDimFull)
+
+    def MoEForward(self, layer, out, x, tokens, stream=None):
+        _check(lib().goph_moe_forward_sharded(self._h, layer._handle(), C.c_void_p(out.Ptr), C.c_uint64(out.n),
+                                              C.c_void_p(x.Ptr), C.c_uint64(x.n), int(tokens), int(layer.Hidden),
+                                              _stream_ptr(stream)))
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_gather_free(self._h))
+            self._h = None

@@ -48,6 +48,10 @@ enum { GOPH_GGUF_Q8_0 = 8, GOPH_GGUF_Q4_K = 12 };
 typedef struct goph_mlx_weight goph_mlx_weight;   /* nvidia.GPUMLXWeight      (runtime/mlx.go:21-32)   */
 typedef struct goph_gguf_matrix goph_gguf_matrix; /* nvidia.GPUGGUFMatrix / GPUQ4KMatrix / GPUQ8_0Matrix
                                                      (runtime/gguf_matrix.go:11-17, q4k.go:39-47, q8.go:20-25) */
+typedef struct goph_gather goph_gather;           /* exchange area of one rank for row-sharded outputs; no counterpart
+                                                     in the reference, which runs on one GPU (model/gpu_forward.go) */
+typedef struct goph_moe_layer goph_moe_layer;     /* the MoE fields of model.LlamaLayer: RouterW, ExpertGateW/UpW/DownW
+                                                     (model/moe.go:24-60) with their GPU copies (model/moe_gpu.go:60-110) */
 typedef struct goph_fp8_linear goph_fp8_linear;   /* nvidia.GPUFP8E4M3Linear  (runtime/fp8.go:35-44)   */
 
 /* ---- runtime: replaces Init/EnsureContext/Malloc/Upload/Download/Sync -------------- */
@@ -190,6 +194,78 @@ int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t
 /* nvidia.GemvFP8E4M3 / GemmFP8E4M3 with Go slices (runtime/fp8.go:158, :180). */
 int goph_fp8_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
                        int batch, const goph_fp8_linear* w);
+
+/* ---- mixture-of-experts selected-expert projection (MLX 4-bit experts) ------------------ */
+
+/* One MoE layer: its routing constants and device scratch for up to max_tokens tokens per call.
+ * Replaces the per-layer state of model.moeForwardGPU (model/moe_gpu.go:49-130): top_k <= 0 means
+ * 8 and is clamped to num_experts (model/moe.go:209-215); norm_topk as cfg.NormTopKProb. */
+int goph_moe_create(int device, int num_experts, int hidden, int inter, int group_size, int top_k,
+                    int norm_topk, int max_tokens, goph_moe_layer** out);
+/* Router weight [num_experts x hidden] (LlamaLayer.RouterW uploaded with goph_mlx_upload).  Borrowed. */
+int goph_moe_set_router(goph_moe_layer* m, const goph_mlx_weight* router);
+/* Expert eid's gate/up [inter x hidden] and down [hidden x inter] weights (borrowed; row-major
+ * layout).  All three NULL marks the expert as not resident on this GPU: goph_moe_forward then
+ * leaves its contribution out, which is how experts are placed across GPUs
+ * (backends/placement/expert_pool.go:101-153 keeps a resident subset; here the subset is per GPU). */
+int goph_moe_set_expert(goph_moe_layer* m, int eid, const goph_mlx_weight* gate,
+                        const goph_mlx_weight* up, const goph_mlx_weight* down);
+int goph_moe_free(goph_moe_layer* m);
+/* out[t] = sum over the top-k experts e of token t, in selection order, of
+ * weight_e * down_e . (silu(gate_e . x[t]) * (up_e . x[t])) — moeForwardWithREAP
+ * (model/moe.go:203-347) / moeForwardGPU (model/moe_gpu.go:49-303) for `tokens` rows of x
+ * [tokens x hidden].  Routing runs on the device; nothing is copied to the host. */
+int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_len, const float* x_dev,
+                     uint64_t x_len, int tokens, void* stream);
+/* Same with the router logits [tokens x num_experts] supplied by the caller (the selected-expert
+ * projection alone: MLXSelectedExpertPersistentCandidate.Run,
+ * backends/nvidia/runtime/mlx_selected_expert.go:77-177, fed by routing done elsewhere). */
+int goph_moe_forward_logits(goph_moe_layer* m, float* out_dev, uint64_t out_len, const float* x_dev,
+                            uint64_t x_len, const float* logits_dev, uint64_t logits_len, int tokens,
+                            void* stream);
+/* Expert ids (-1 = none) and weights [tokens x top_k] chosen by the last forward call. */
+int goph_moe_last_routing(goph_moe_layer* m, int tokens, int* ids_host, float* weights_host);
+
+/* ---- row-sharded products across the GPUs of one box ----------------------------------------
+ * The reference is single-GPU.  A projection [out x in] is split by rows: rank r of `world` uploads
+ * rows [lo, hi) as an ordinary weight handle (rows are contiguous in every format), computes
+ * [batch x (hi-lo)], and the blocks are exchanged so that every rank holds [batch x out].  One rank
+ * per GPU; ranks may be processes (areas shared through goph_gather_export/open_peer) or live in
+ * one process (goph_gather_attach_local).  Every rank must issue the same sequence of exchanges. */
+
+/* Rows [lo, hi) owned by `rank`: contiguous, cut at multiples of `align` rows, the same for every caller. */
+int goph_shard_rows(int out_dim, int rank, int world, int align, int* lo, int* hi);
+/* Exchange area for results of up to capacity_floats floats (world <= 8). */
+int goph_gather_create(int device, int rank, int world, uint64_t capacity_floats, goph_gather** out);
+/* 64-byte token by which another process maps this rank's area. */
+int goph_gather_export(goph_gather* g, unsigned char* handle64);
+int goph_gather_open_peer(goph_gather* g, int peer_rank, const unsigned char* handle64);
+/* Same-process form: connects g to the area of `peer` (another rank's handle), enabling peer access. */
+int goph_gather_attach_local(goph_gather* g, goph_gather* peer);
+int goph_gather_free(goph_gather* g);
+/* 0, or 100+q if rank q's block did not arrive within the wait limit (~2 s), or 200 if a replayed
+ * CUDA graph held an odd number of exchanges.  The waits are bounded; the context stays usable. */
+int goph_gather_status(goph_gather* g, int* out_status);
+/* Device buffer of capacity_floats floats in which a rank may build its block. */
+int goph_gather_shard_buffer(goph_gather* g, float** shard_dev);
+/* Writes this rank's block src[rows][count] to result[m * dst_row_stride + dst_off + j] on EVERY rank
+ * and returns, in *result_dev, this rank's result buffer; stream-ordered: kernels launched after it
+ * on `stream` see all ranks' blocks.  The buffer stays valid until the exchange after the next one. */
+int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int count, int64_t dst_off,
+                    int64_t dst_row_stride, void* stream, float** result_dev);
+/* Sharded product + exchange: `shard` holds rows [row_lo, row_lo + shard.out_dim) of a projection
+ * with out_dim_full rows; *result_dev receives [batch x out_dim_full] on every rank.
+ * (GemmMLX / ProjectBatchToBuffer / GemmFP8E4M3Buffer for a weight split over GPUs.) */
+int goph_mlx_gemm_allgather(goph_gather* g, const goph_mlx_weight* shard, const float* x_dev, uint64_t x_len,
+                            int batch, int row_lo, int out_dim_full, void* stream, float** result_dev);
+int goph_gguf_project_allgather(goph_gather* g, const goph_gguf_matrix* shard, const float* x_dev, uint64_t x_len,
+                                int batch, int row_lo, int out_dim_full, void* stream, float** result_dev);
+int goph_fp8_gemm_allgather(goph_gather* g, const goph_fp8_linear* shard, const float* x_dev, uint64_t x_len,
+                            int batch, int row_lo, int out_dim_full, void* stream, float** result_dev);
+/* goph_moe_forward on a layer whose experts are placed per GPU: every rank computes the partial sum
+ * of its resident experts, the partials [tokens x hidden] are exchanged and added in rank order. */
+int goph_moe_forward_sharded(goph_gather* g, goph_moe_layer* m, float* out_dev, uint64_t out_len,
+                             const float* x_dev, uint64_t x_len, int tokens, int hidden, void* stream);
 
 #ifdef __cplusplus
 }
