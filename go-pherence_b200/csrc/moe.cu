@@ -31,6 +31,7 @@ namespace goph {
 
 constexpr uint32_t kMagicMoE = 0x4d4f4558;  // "MOEX"
 constexpr int kMoeWarps = 8, kMoeThreads = kMoeWarps * 32;
+constexpr int kMoeMaxExperts = 1024;  // the routing kernel keeps one float and one int per expert in shared memory
 
 struct MoeTables {
   const uint4** gate_w;   // [E] packed rows (16-byte units) or null when the expert is not resident
@@ -39,6 +40,14 @@ struct MoeTables {
   const void** up_sb;
   const uint4** down_w;
   const void** down_sb;
+};
+
+// One selected, resident expert of the current call.
+struct __align__(16) MoeWork {
+  const uint4* w[3];   // gate, up, down rows
+  const void* sb[3];
+  int expert, count;   // count = items (token, slot) that chose it
+  int pad[2];
 };
 
 }  // namespace goph
@@ -56,9 +65,9 @@ struct goph_moe_layer {
   float* wts;                      // [max_tokens][top_k]
   float* act;                      // [max_tokens][top_k][inter]
   float* dpart;                    // [max_tokens][top_k][hidden] per-item down projections
-  int* lists;                      // [0] arrival counter, [1] number of selected resident experts,
-                                   // [2..2+E) their ids, [2+E..2+2E) items per expert,
-                                   // [2+2E..) items [E][max_tokens]
+  int* lists;                      // [0] arrival counter of the routing CTAs, [1] number of work entries
+  goph::MoeWork* work;             // [E] selected resident experts of the current call
+  int* items;                      // [E][max_tokens] item = token * top_k + slot, per expert
 };
 
 namespace goph {
@@ -76,107 +85,6 @@ __device__ __forceinline__ void unpack16(uint32_t w, float (&f)[8]) {
   f[7] = __uint_as_float(((w >> 9) & M) | E);
 }
 
-// Stages n floats (n a multiple of 32) as [iteration][slot][lane] float4 plus per-unit {16*sum, sum}.
-// No barrier inside: the caller synchronises after staging all vectors.
-__device__ __forceinline__ void moe_stage_values(const float* __restrict__ x, int n, float4* xs) {
-  const int units = n / 32, iters = (units + 31) / 32;
-  for (int idx = threadIdx.x; idx < iters * 256; idx += kMoeThreads) {
-    int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (unit < units) v = *reinterpret_cast<const float4*>(x + (size_t)unit * 32 + slot * 4);
-    xs[idx] = v;
-  }
-}
-__device__ __forceinline__ void moe_stage_consts(int n, const float4* xs, float2* xc) {
-  const int units = n / 32, iters = (units + 31) / 32;
-  for (int idx = threadIdx.x; idx < iters * 32; idx += kMoeThreads) {
-    int it = idx >> 5, l = idx & 31;
-    float s = 0.f;
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      float4 v = xs[(it * 8 + k) * 32 + l];
-      s += (v.x + v.y) + (v.z + v.w);
-    }
-    xc[idx] = make_float2(16.f * s, s);
-  }
-}
-
-struct MoeRow {
-  const uint4* w;
-  const void* sb;
-};
-
-// NW rows (of NW matrices, all `units` 16-byte units wide) against M staged vectors: acc[w][m] gets
-// the per-lane partial of row w . vector m.  Each packed word is unpacked once and used M times.
-template <bool SB_BF16, int NW, int M>
-__device__ __forceinline__ void moe_rows_dot(const MoeRow (&rows)[NW], int units, int ug_shift, const float4* xs,
-                                             const float2* xc, int xs_stride, int xc_stride, int lane,
-                                             float (&acc)[NW][M]) {
-  const int iters = (units + 31) / 32;
-#pragma unroll
-  for (int w = 0; w < NW; ++w)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[w][m] = 0.f;
-  for (int it = 0; it < iters; ++it) {
-    int unit = it * 32 + lane;
-    const bool valid = unit < units;
-    if (!valid) unit = units - 1;
-    uint4 q[NW];
-    float sc[NW], bi[NW];
-#pragma unroll
-    for (int w = 0; w < NW; ++w) q[w] = ld_stream(rows[w].w + unit);
-#pragma unroll
-    for (int w = 0; w < NW; ++w) {
-      if (SB_BF16) {
-        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(rows[w].sb) + (unit >> ug_shift));
-        sc[w] = __uint_as_float(v << 16);
-        bi[w] = __uint_as_float(v & 0xFFFF0000u);
-      } else {
-        float2 v = __ldg(reinterpret_cast<const float2*>(rows[w].sb) + (unit >> ug_shift));
-        sc[w] = v.x;
-        bi[w] = v.y;
-      }
-    }
-    float2 F[NW][M];
-#pragma unroll
-    for (int w = 0; w < NW; ++w)
-#pragma unroll
-      for (int m = 0; m < M; ++m) F[w][m] = make_float2(0.f, 0.f);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float f[NW][8];
-#pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        const uint32_t word = k == 0 ? q[w].x : k == 1 ? q[w].y : k == 2 ? q[w].z : q[w].w;
-        unpack16(word, f[w]);
-      }
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float4 xa = xs[m * xs_stride + (it * 8 + 2 * k) * 32 + lane];
-        float4 xb = xs[m * xs_stride + (it * 8 + 2 * k + 1) * 32 + lane];
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          fma2(F[w][m], make_float2(f[w][0], f[w][1]), make_float2(xa.x, xa.y));
-          fma2(F[w][m], make_float2(f[w][2], f[w][3]), make_float2(xa.z, xa.w));
-          fma2(F[w][m], make_float2(f[w][4], f[w][5]), make_float2(xb.x, xb.y));
-          fma2(F[w][m], make_float2(f[w][6], f[w][7]), make_float2(xb.z, xb.w));
-        }
-      }
-    }
-    if (valid) {
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float2 c = xc[m * xc_stride + it * 32 + lane];
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-          acc[w][m] = fmaf(sc[w], (F[w][m].x + F[w][m].y) - c.x, acc[w][m]);
-          acc[w][m] = fmaf(bi[w], c.y, acc[w][m]);
-        }
-      }
-    }
-  }
-}
-
 __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -185,58 +93,57 @@ __device__ __forceinline__ void pdl_prologue() {
 // simd.SoftmaxInPlace + the top-k loop of moeForwardWithREAP in the reference's order
 // (model/moe.go:226-280; backends/simd/runtime/softmax.go:9-30): one CTA per token; the
 // exponentials are taken in parallel, the sum by one thread in index order, the k rounds of
-// "largest probability not yet picked, lowest id on ties" by a warp.  The last CTA to finish groups
-// the items by expert.
+// "largest probability not yet picked, lowest id on ties" by a warp over shared memory.  The last
+// CTA to finish groups the (token, slot) items by expert into the work list.
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, int norm_topk, int tokens,
                  int max_tokens, MoeTables tb, int* __restrict__ ids, float* __restrict__ wts,
-                 float* __restrict__ probs_scratch, int* __restrict__ lists) {
+                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items) {
+  __shared__ float sp[kMoeMaxExperts];
+  __shared__ int s_cnt[kMoeMaxExperts];
+  __shared__ float s_mx, s_inv;
+  __shared__ int s_ok, s_last, s_n;
   pdl_prologue();
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
   const float* lg = logits + (size_t)t * num_experts;
-  float* p = probs_scratch + (size_t)t * num_experts;
   int* my_ids = ids + (size_t)t * top_k;
   float* my_w = wts + (size_t)t * top_k;
-  __shared__ float s_mx, s_inv;
-  __shared__ int s_ok, s_last;
+  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = lg[i];
+  __syncthreads();
   if (tid < 32) {
     float mx = -INFINITY;
-    for (int i = lane; i < num_experts; i += 32) mx = fmaxf(mx, lg[i]);  // skips NaN, as "x > mx" does
+    for (int i = lane; i < num_experts; i += 32) mx = fmaxf(mx, sp[i]);  // skips NaN, as "x > mx" does
 #pragma unroll
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     // the reference starts from x[0]: if that is NaN every comparison is false and the maximum stays NaN
-    if (isnan(lg[0])) mx = lg[0];
+    if (isnan(sp[0])) mx = sp[0];
     if (lane == 0) s_mx = mx;
   }
   __syncthreads();
-  for (int i = tid; i < num_experts; i += blockDim.x) p[i] = (float)exp((double)(lg[i] - s_mx));
+  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = (float)exp((double)(sp[i] - s_mx));
   __syncthreads();
   if (tid == 0) {
     float sum = 0.f;
-    for (int i = 0; i < num_experts; ++i) sum = __fadd_rn(sum, p[i]);
+    for (int i = 0; i < num_experts; ++i) sum = __fadd_rn(sum, sp[i]);
     s_ok = !(sum == 0.f || isnan(sum) || isinf(sum));  // SoftmaxInPlace fails: no expert runs
     s_inv = __fdiv_rn(1.f, sum);
   }
   __syncthreads();
   if (s_ok)
-    for (int i = tid; i < num_experts; i += blockDim.x) p[i] = __fmul_rn(p[i], s_inv);
+    for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __fmul_rn(sp[i], s_inv);
   __syncthreads();
   if (tid < 32) {
     int n = 0;
     float wsum = 0.f;
     for (int k = 0; k < top_k; ++k) {
       int best = -1;
-      float bs = -1.f;
+      float bs = -1.f;  // probabilities are >= 0; a picked entry is overwritten with -2 and never wins again
       if (s_ok) {
         for (int j = lane; j < num_experts; j += 32) {
-          float v = p[j];
+          float v = sp[j];
           if (v > bs) {
-            bool picked = false;
-            for (int q = 0; q < n; ++q) picked |= my_ids[q] == j;
-            if (!picked) {
-              best = j;
-              bs = v;
-            }
+            best = j;
+            bs = v;
           }
         }
 #pragma unroll
@@ -253,6 +160,7 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
         if (lane == 0) {
           my_ids[n] = best;
           my_w[n] = bs;
+          sp[best] = -2.f;
         }
         wsum = __fadd_rn(wsum, bs);
         ++n;
@@ -272,144 +180,266 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
   }
   __syncthreads();
   if (!s_last) return;
-  // ---- last CTA: group the items by expert ------------------------------------------------
+  // ---- last CTA: group the items by expert.  The order inside a list and of the work entries
+  // depends on scheduling; no result does (every item's arithmetic is the same in any grouping).
   __threadfence();
-  int* n_active = lists + 1;
-  int* active = lists + 2;
-  int* counts = lists + 2 + num_experts;
-  int* items = lists + 2 + 2 * num_experts;
-  const volatile int* vids = ids;
+  for (int e = tid; e < num_experts; e += blockDim.x) s_cnt[e] = 0;
+  if (tid == 0) s_n = 0;
+  __syncthreads();
+  for (int it = tid; it < tokens * top_k; it += blockDim.x) {
+    const int e = __ldcg(ids + it);
+    if (e >= 0 && tb.gate_w[e] != nullptr) items[(size_t)e * max_tokens + atomicAdd(&s_cnt[e], 1)] = it;
+  }
+  __syncthreads();
   for (int e = tid; e < num_experts; e += blockDim.x) {
-    int c = 0;
-    if (tb.gate_w[e] != nullptr)
-      for (int it = 0; it < tokens * top_k; ++it)
-        if (vids[it] == e) items[(size_t)e * max_tokens + c++] = it;  // a token selects an expert at most once
-    counts[e] = c;
+    if (s_cnt[e] > 0) {
+      MoeWork wk;
+      wk.w[0] = tb.gate_w[e];
+      wk.w[1] = tb.up_w[e];
+      wk.w[2] = tb.down_w[e];
+      wk.sb[0] = tb.gate_sb[e];
+      wk.sb[1] = tb.up_sb[e];
+      wk.sb[2] = tb.down_sb[e];
+      wk.expert = e;
+      wk.count = s_cnt[e];
+      wk.pad[0] = wk.pad[1] = 0;
+      work[atomicAdd(&s_n, 1)] = wk;
+    }
   }
   __syncthreads();
   if (tid == 0) {
-    int n = 0;
-    for (int e = 0; e < num_experts; ++e)
-      if (counts[e] > 0) active[n++] = e;
-    *n_active = n;
+    lists[1] = s_n;
     lists[0] = 0;  // ready for the next call
   }
 }
 
-constexpr int kMoeM = 4;  // tokens of one expert handled per pass over its rows
+// Sums N values over the warp with N-1 + 5-log2(N) shuffles: at each of the first log2(N) butterfly
+// steps a lane keeps one half of its values and hands the other half to its partner.  Every value is
+// added in the same lane pairs as a plain xor butterfly, so the result does not depend on N.
+// On return v[0] is the total of value number idx(lane), idx = the lane's bits 4,3,.. read as a number.
+template <int N>
+__device__ __forceinline__ void warp_sum_split(float (&v)[N], int lane) {
+  int o = 16;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1, o >>= 1) {
+    const bool upper = lane & o;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      float keep = upper ? v[i + n / 2] : v[i];
+      float give = upper ? v[i] : v[i + n / 2];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+    }
+  }
+  for (; o; o >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+}
 
-// act[item][r] = silu(gate_e[r] . x_t) * (up_e[r] . x_t) for every item (token t, slot) of expert e.
-template <bool SB_BF16>
-__global__ void __launch_bounds__(kMoeThreads)
-moe_gate_up_kernel(MoeTables tb, const float* __restrict__ x, const int* __restrict__ lists, float* __restrict__ act,
-                   int num_experts, int max_tokens, int hidden, int inter, int top_k, int ug_shift, int groups) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  pdl_prologue();
-  if ((int)blockIdx.y >= lists[1]) return;
-  const int e = lists[2 + blockIdx.y];
-  const int count = lists[2 + num_experts + e];
-  const int* items = lists + 2 + 2 * num_experts + (size_t)e * max_tokens;
-  const int units = hidden / 32, iters = (units + 31) / 32;
-  const int xs_stride = iters * 256, xc_stride = iters * 32;
-  float4* xs = reinterpret_cast<float4*>(smem_raw);
-  float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)kMoeM * xs_stride * 16);
+// The expert kernels.  PHASE 0: rows of gate and up (one row of each per warp task) against the
+// expert's tokens' x, writing silu(g) * u per item; PHASE 1: two adjacent rows of down per task against
+// the items' activations, writing one vector per item.  grid = (row blocks, work entries); a CTA
+// walks its expert's items M at a time: vectors staged in shared memory as [vector][iteration][slot][lane]
+// float4 plus {16*sum, sum} per 32-element unit, each packed word unpacked once and used M times, the
+// next 16-byte units in flight while the current ones are computed.
+template <bool SB_BF16, int PHASE, int M>
+__device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __restrict__ items, int base, int m_now,
+                                                const float* __restrict__ src, float* __restrict__ dst, int in_dim,
+                                                int out_rows, int top_k, int ug_shift, int groups, float4* xs, float2* xc) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int units = in_dim / 32, iters = (units + 31) / 32;
   const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
-  for (int base = 0; base < count; base += kMoeM) {
-    const int m_now = min(kMoeM, count - base);
-    if (base) __syncthreads();
-    for (int m = 0; m < m_now; ++m) moe_stage_values(x + (size_t)(items[base + m] / top_k) * hidden, hidden, xs + m * xs_stride);
-    __syncthreads();
-    for (int m = 0; m < m_now; ++m) moe_stage_consts(hidden, xs + m * xs_stride, xc + m * xc_stride);
-    __syncthreads();
-    for (int r = blockIdx.x * kMoeWarps + warp; r < inter; r += gridDim.x * kMoeWarps) {
-      const MoeRow rows[2] = {{tb.gate_w[e] + (size_t)r * units, reinterpret_cast<const char*>(tb.gate_sb[e]) + r * sb_row},
-                              {tb.up_w[e] + (size_t)r * units, reinterpret_cast<const char*>(tb.up_sb[e]) + r * sb_row}};
-      float g[kMoeM], u[kMoeM];
-      if (m_now == 1) {
-        float acc[2][1];
-        moe_rows_dot<SB_BF16, 2, 1>(rows, units, ug_shift, xs, xc, xs_stride, xc_stride, lane, acc);
-        g[0] = acc[0][0];
-        u[0] = acc[1][0];
+  const int tasks = PHASE == 0 ? out_rows : (out_rows + 1) / 2;
+  const int task_stride = gridDim.x * kMoeWarps;
+  struct Rows {
+    const uint4* w[2];
+    const char* sb[2];
+    int row;
+  };
+  auto open_task = [&](int task, Rows& t) {
+    if (PHASE == 0) {
+      t.row = task;
+      t.w[0] = wk.w[0] + (size_t)task * units;
+      t.w[1] = wk.w[1] + (size_t)task * units;
+      t.sb[0] = reinterpret_cast<const char*>(wk.sb[0]) + task * sb_row;
+      t.sb[1] = reinterpret_cast<const char*>(wk.sb[1]) + task * sb_row;
+    } else {
+      t.row = task * 2;
+      const int r1 = min(t.row + 1, out_rows - 1);
+      t.w[0] = wk.w[2] + (size_t)t.row * units;
+      t.w[1] = wk.w[2] + (size_t)r1 * units;
+      t.sb[0] = reinterpret_cast<const char*>(wk.sb[2]) + t.row * sb_row;
+      t.sb[1] = reinterpret_cast<const char*>(wk.sb[2]) + r1 * sb_row;
+    }
+  };
+  struct Tile {
+    uint4 w[2];
+    uint32_t s[2], b[2];
+  };
+  auto load_tile = [&](const Rows& t, int it, Tile& d) {
+    int unit = it * 32 + lane;
+    if (unit >= units) unit = units - 1;  // the staged vector is zero there
+    const int grp = unit >> ug_shift;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      d.w[r] = ld_stream(t.w[r] + unit);
+      if (SB_BF16) {
+        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(t.sb[r]) + grp);
+        d.s[r] = v << 16;
+        d.b[r] = v & 0xFFFF0000u;
       } else {
-        float acc[2][kMoeM];  // vectors past m_now are stale shared memory; their results are not stored
-        moe_rows_dot<SB_BF16, 2, kMoeM>(rows, units, ug_shift, xs, xc, xs_stride, xc_stride, lane, acc);
-#pragma unroll
-        for (int m = 0; m < kMoeM; ++m) {
-          g[m] = acc[0][m];
-          u[m] = acc[1][m];
-        }
+        float2 v = __ldg(reinterpret_cast<const float2*>(t.sb[r]) + grp);
+        d.s[r] = __float_as_uint(v.x);
+        d.b[r] = __float_as_uint(v.y);
       }
+    }
+  };
+
+  int task = blockIdx.x * kMoeWarps + warp;
+  const bool has_work = task < tasks;
+  Rows cur_rows, nxt_rows;
+  Tile cur, nxt;
+  if (has_work) {  // first weights in flight while the vectors are staged
+    open_task(task, cur_rows);
+    load_tile(cur_rows, 0, cur);
+  }
+  // ---- stage the m_now vectors -----------------------------------------------------------
+  const int per_m = iters * 256;
+  for (int idx = threadIdx.x; idx < M * per_m; idx += kMoeThreads) {
+    const int m = idx / per_m, rem = idx - m * per_m;
+    const int it = rem >> 8, slot = (rem >> 5) & 7, l = rem & 31, unit = it * 32 + l;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < m_now && unit < units) {
+      const int item = items[base + m];
+      const float* p = src + (size_t)(PHASE == 0 ? item / top_k : item) * in_dim + (size_t)unit * 32 + slot * 4;
+      v = *reinterpret_cast<const float4*>(p);
+    }
+    xs[idx] = v;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < M * iters * 32; idx += kMoeThreads) {
+    const int mi = idx >> 5, l = idx & 31;
+    float s = 0.f;
 #pragma unroll
-      for (int m = 0; m < kMoeM; ++m) {
-        if (m < m_now) {
-          float gs = warp_sum(g[m]), us = warp_sum(u[m]);
-          if (lane == 0) {
-            // kernels.SiLU then the multiply (backends/simd/kernels/activation.go:15-24)
-            float sv = __fdiv_rn(gs, __fadd_rn(1.0f, (float)exp((double)(-gs))));
-            act[(size_t)items[base + m] * inter + r] = __fmul_rn(sv, us);
+    for (int k = 0; k < 8; ++k) {
+      float4 v = xs[(mi * 8 + k) * 32 + l];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    xc[idx] = make_float2(16.f * s, s);
+  }
+  __syncthreads();
+  if (!has_work) return;
+
+  float acc[2][M];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+  while (true) {
+    const int ntask = task + task_stride;
+    const bool more = ntask < tasks;
+    for (int it = 0; it < iters; ++it) {
+      if (it + 1 < iters) {
+        load_tile(cur_rows, it + 1, nxt);
+      } else if (more) {
+        open_task(ntask, nxt_rows);
+        load_tile(nxt_rows, 0, nxt);
+      }
+      float2 F[2][M];
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) F[r][m] = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float4 xa[M], xb[M];
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          const float4* bp = xs + ((size_t)(m * iters + it) * 8 + 2 * k) * 32 + lane;
+          xa[m] = bp[0];
+          xb[m] = bp[32];
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint32_t word = k == 0 ? cur.w[r].x : k == 1 ? cur.w[r].y : k == 2 ? cur.w[r].z : cur.w[r].w;
+          float f[8];
+          unpack16(word, f);
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            fma2(F[r][m], make_float2(f[0], f[1]), make_float2(xa[m].x, xa[m].y));
+            fma2(F[r][m], make_float2(f[2], f[3]), make_float2(xa[m].z, xa[m].w));
+            fma2(F[r][m], make_float2(f[4], f[5]), make_float2(xb[m].x, xb[m].y));
+            fma2(F[r][m], make_float2(f[6], f[7]), make_float2(xb[m].z, xb[m].w));
           }
         }
       }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const float2 c = xc[(m * iters + it) * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float dot = (F[r][m].x + F[r][m].y) - c.x;
+          acc[r][m] = fmaf(__uint_as_float(cur.s[r]), dot, acc[r][m]);
+          acc[r][m] = fmaf(__uint_as_float(cur.b[r]), c.y, acc[r][m]);
+        }
+      }
+      cur = nxt;
     }
+    // ---- reduce the 2*M sums; value number 2*m + r ends up in the lanes whose top bits spell it
+    float v[2 * M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      v[2 * m] = acc[0][m];
+      v[2 * m + 1] = acc[1][m];
+      acc[0][m] = acc[1][m] = 0.f;
+    }
+    warp_sum_split<2 * M>(v, lane);
+    constexpr int kLow = 16 / M;              // lane bit that tells row 0 from row 1
+    const int m_of_lane = lane / (2 * kLow);  // lane bits above kLow
+    const int r_of_lane = (lane / kLow) & 1;
+    const float mine = v[0];
+    const float other = __shfl_xor_sync(0xffffffffu, mine, kLow);
+    if ((lane & (kLow - 1)) == 0 && m_of_lane < m_now) {
+      const int item = items[base + m_of_lane];
+      if (PHASE == 0) {
+        if (r_of_lane == 0) {
+          // kernels.SiLU then the multiply (backends/simd/kernels/activation.go:15-24)
+          const float sv = __fdiv_rn(mine, __fadd_rn(1.0f, (float)exp((double)(-mine))));
+          dst[(size_t)item * out_rows + cur_rows.row] = __fmul_rn(sv, other);
+        }
+      } else {
+        const int row = cur_rows.row + r_of_lane;
+        if (row < out_rows) dst[(size_t)item * out_rows + row] = mine;
+      }
+    }
+    if (!more) break;
+    cur_rows = nxt_rows;
+    task = ntask;
   }
 }
 
-// dpart[item][r] = down_e[r] . act[item] for every item of expert e.
-template <bool SB_BF16>
-__global__ void __launch_bounds__(kMoeThreads)
-moe_down_kernel(MoeTables tb, const float* __restrict__ act, const int* __restrict__ lists, float* __restrict__ dpart,
-                int num_experts, int max_tokens, int hidden, int inter, int ug_shift, int groups) {
+template <bool SB_BF16, int PHASE>
+__global__ void __launch_bounds__(kMoeThreads, 2)
+moe_expert_kernel(const MoeWork* __restrict__ work, const int* __restrict__ lists, const int* __restrict__ items_all,
+                  const float* __restrict__ src, float* __restrict__ dst, int max_tokens, int in_dim, int out_rows,
+                  int top_k, int ug_shift, int groups) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_prologue();
   if ((int)blockIdx.y >= lists[1]) return;
-  const int e = lists[2 + blockIdx.y];
-  const int count = lists[2 + num_experts + e];
-  const int* items = lists + 2 + 2 * num_experts + (size_t)e * max_tokens;
-  const int units = inter / 32, iters = (units + 31) / 32;
-  const int xs_stride = iters * 256, xc_stride = iters * 32;
+  const MoeWork wk = work[blockIdx.y];
+  const int* items = items_all + (size_t)wk.expert * max_tokens;
+  const int iters = (in_dim / 32 + 31) / 32;
   float4* xs = reinterpret_cast<float4*>(smem_raw);
-  float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)kMoeM * xs_stride * 16);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
-  for (int base = 0; base < count; base += kMoeM) {
-    const int m_now = min(kMoeM, count - base);
-    if (base) __syncthreads();
-    for (int m = 0; m < m_now; ++m) moe_stage_values(act + (size_t)items[base + m] * inter, inter, xs + m * xs_stride);
-    __syncthreads();
-    for (int m = 0; m < m_now; ++m) moe_stage_consts(inter, xs + m * xs_stride, xc + m * xc_stride);
-    __syncthreads();
-    // two rows per pass: the rows are short, two loads in flight per lane
-    for (int r = (blockIdx.x * kMoeWarps + warp) * 2; r < hidden; r += gridDim.x * kMoeWarps * 2) {
-      const int r1 = min(r + 1, hidden - 1);
-      const MoeRow rows[2] = {{tb.down_w[e] + (size_t)r * units, reinterpret_cast<const char*>(tb.down_sb[e]) + r * sb_row},
-                              {tb.down_w[e] + (size_t)r1 * units, reinterpret_cast<const char*>(tb.down_sb[e]) + r1 * sb_row}};
-      float d0[kMoeM], d1[kMoeM];
-      if (m_now == 1) {
-        float acc[2][1];
-        moe_rows_dot<SB_BF16, 2, 1>(rows, units, ug_shift, xs, xc, xs_stride, xc_stride, lane, acc);
-        d0[0] = acc[0][0];
-        d1[0] = acc[1][0];
-      } else {
-        float acc[2][kMoeM];
-        moe_rows_dot<SB_BF16, 2, kMoeM>(rows, units, ug_shift, xs, xc, xs_stride, xc_stride, lane, acc);
-#pragma unroll
-        for (int m = 0; m < kMoeM; ++m) {
-          d0[m] = acc[0][m];
-          d1[m] = acc[1][m];
-        }
-      }
-#pragma unroll
-      for (int m = 0; m < kMoeM; ++m) {
-        if (m < m_now) {
-          float a0 = warp_sum(d0[m]), a1 = warp_sum(d1[m]);
-          if (lane == 0) {
-            float* o = dpart + (size_t)items[base + m] * hidden;
-            o[r] = a0;
-            if (r + 1 < hidden) o[r + 1] = a1;
-          }
-        }
-      }
+  // M vectors per pass: 1, 2 or 4 by how many items the expert has
+  if (wk.count == 1) {
+    float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)1 * iters * 256 * 16);
+    moe_expert_pass<SB_BF16, PHASE, 1>(wk, items, 0, 1, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc);
+  } else if (wk.count == 2) {
+    float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)2 * iters * 256 * 16);
+    moe_expert_pass<SB_BF16, PHASE, 2>(wk, items, 0, 2, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc);
+  } else {
+    float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)4 * iters * 256 * 16);
+    for (int base = 0; base < wk.count; base += 4) {
+      if (base) __syncthreads();
+      moe_expert_pass<SB_BF16, PHASE, 4>(wk, items, base, min(4, wk.count - base), src, dst, in_dim, out_rows, top_k,
+                                         ug_shift, groups, xs, xc);
     }
   }
 }
@@ -473,6 +503,7 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
   clear_error();
   if (!out) return fail(GOPH_E_INVALID, "goph_moe_create: nil result pointer");
   *out = nullptr;
+  if (num_experts > kMoeMaxExperts) return fail(GOPH_E_UNSUPPORTED, "MoE: at most %d experts per layer, got %d", kMoeMaxExperts, num_experts);
   if (num_experts <= 0 || hidden <= 0 || inter <= 0 || max_tokens <= 0)
     return fail(GOPH_E_INVALID, "invalid MoE dims experts=%d hidden=%d inter=%d tokens=%d", num_experts, hidden, inter, max_tokens);
   if (top_k <= 0) top_k = 8;                      // model/moe.go:209-212
@@ -507,9 +538,10 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
   if (e == cudaSuccess) e = cudaMalloc(&m->wts, (size_t)max_tokens * top_k * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->act, (size_t)max_tokens * top_k * inter * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->dpart, (size_t)max_tokens * top_k * hidden * sizeof(float));
-  const size_t list_ints = 2 + 2 * (size_t)num_experts + (size_t)num_experts * max_tokens;
-  if (e == cudaSuccess) e = cudaMalloc(&m->lists, list_ints * sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(m->lists, 0, list_ints * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&m->lists, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(m->lists, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&m->work, (size_t)num_experts * sizeof(goph::MoeWork));
+  if (e == cudaSuccess) e = cudaMalloc(&m->items, (size_t)num_experts * max_tokens * sizeof(int));
   if (e != cudaSuccess) {
     int rc = fail_cuda(e, "cudaMalloc(MoE layer)");
     m->magic = 0;  // partial allocations are released by the process; the handle is not returned
@@ -582,6 +614,8 @@ GOPH_API int goph_moe_free(goph_moe_layer* m) {
   cudaFree(m->act);
   cudaFree(m->dpart);
   cudaFree(m->lists);
+  cudaFree(m->work);
+  cudaFree(m->items);
   m->magic = 0;
   delete m;
   return GOPH_OK;
@@ -592,37 +626,28 @@ static int moe_run(goph_moe_layer* m, float* out_dev, const float* x_dev, const 
                    cudaStream_t s) {
   if (int rc = moe_upload_tables(m)) return rc;
   const int sms = device_state(m->device).sm_count;
-  float* probs = m->logits + (size_t)m->max_tokens * m->num_experts;
   if (int rc = moe_launch(moe_route_kernel, dim3(tokens), 128, 0, s, logits_dev, m->num_experts, m->top_k, m->norm_topk, tokens,
-                          m->max_tokens, m->dev, m->ids, m->wts, probs, m->lists))
+                          m->max_tokens, m->dev, m->ids, m->wts, m->lists, m->work, m->items))
     return rc;
   int sh = 0;
   while ((32 << sh) < m->group_size) ++sh;
   // at most this many experts can have been selected; CTAs past the actual number return at once
   const int max_active = min(m->num_experts, tokens * m->top_k);
-  const int want_ctas = sms * 8;
-  {
-    const int units = m->hidden / 32, iters = (units + 31) / 32;
-    const size_t smem = (size_t)kMoeM * iters * (256 * 16 + 32 * 8);
-    if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: hidden=%d does not fit shared memory", m->hidden);
-    const int max_blocks = (m->inter + kMoeWarps - 1) / kMoeWarps;
-    int gx = max(1, min(max_blocks, (want_ctas + max_active - 1) / max_active));
-    auto k = m->sb_bf16 ? moe_gate_up_kernel<true> : moe_gate_up_kernel<false>;
+  const int want_ctas = sms * 4;
+  for (int phase = 0; phase < 2; ++phase) {
+    const int in_dim = phase == 0 ? m->hidden : m->inter, out_rows = phase == 0 ? m->inter : m->hidden;
+    const int iters = (in_dim / 32 + 31) / 32;
+    const size_t smem = (size_t)4 * iters * (256 * 16 + 32 * 8);
+    if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: %d columns do not fit shared memory", in_dim);
+    const int tasks = phase == 0 ? out_rows : (out_rows + 1) / 2;
+    const int max_blocks = (tasks + kMoeWarps - 1) / kMoeWarps;
+    const int gx = max(1, min(max_blocks, (want_ctas + max_active - 1) / max_active));
+    auto k = phase == 0 ? (m->sb_bf16 ? moe_expert_kernel<true, 0> : moe_expert_kernel<false, 0>)
+                        : (m->sb_bf16 ? moe_expert_kernel<true, 1> : moe_expert_kernel<false, 1>);
     GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (int rc = moe_launch(k, dim3(gx, max_active), kMoeThreads, smem, s, m->dev, x_dev, m->lists, m->act, m->num_experts,
-                            m->max_tokens, m->hidden, m->inter, m->top_k, sh, m->hidden / m->group_size))
-      return rc;
-  }
-  {
-    const int units = m->inter / 32, iters = (units + 31) / 32;
-    const size_t smem = (size_t)kMoeM * iters * (256 * 16 + 32 * 8);
-    if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: inter=%d does not fit shared memory", m->inter);
-    const int max_blocks = (m->hidden + kMoeWarps * 2 - 1) / (kMoeWarps * 2);
-    int gx = max(1, min(max_blocks, (want_ctas + max_active - 1) / max_active));
-    auto k = m->sb_bf16 ? moe_down_kernel<true> : moe_down_kernel<false>;
-    GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (int rc = moe_launch(k, dim3(gx, max_active), kMoeThreads, smem, s, m->dev, m->act, m->lists, m->dpart, m->num_experts,
-                            m->max_tokens, m->hidden, m->inter, sh, m->inter / m->group_size))
+    if (int rc = moe_launch(k, dim3(gx, max_active), kMoeThreads, smem, s, m->work, m->lists, m->items,
+                            phase == 0 ? x_dev : m->act, phase == 0 ? m->act : m->dpart, m->max_tokens, in_dim, out_rows,
+                            m->top_k, sh, in_dim / m->group_size))
       return rc;
   }
   return moe_launch(moe_combine_kernel, dim3((m->hidden + 255) / 256, tokens), 256, 0, s, m->dev, m->dpart, m->ids, m->wts,
