@@ -34,6 +34,9 @@ LAYER_OPS = [("qkv", [(QDIM, HIDDEN), (KVDIM, HIDDEN), (KVDIM, HIDDEN)]),
              ("o", [(HIDDEN, QDIM)]),
              ("gate_up", [(FFN, HIDDEN), (FFN, HIDDEN)]),
              ("down", [(HIDDEN, FFN)])]
+# DRAM bytes per launch of the dominant kernel from an ncu capture (dram__bytes_read.sum +
+# dram__bytes_write.sum), filled in from profiles/ when a capture of that launch exists.
+TRAFFIC = {"lm_head": None}
 WORKLOAD = "qwen3-0.6b mlx4-g64 decode-step projections (28 layers x q|k|v,o,gate|up,down + LM head 151936x1024)"
 
 
@@ -94,74 +97,112 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def shard_rows(out_dim, rank, world):
-    """Rows [lo, hi) of a projection owned by `rank`: contiguous, split on multiples of 8 rows."""
-    per = (out_dim // 8 + world - 1) // world * 8
-    lo = min(out_dim, rank * per)
-    return lo, min(out_dim, lo + per)
+class _Raw:
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
 
 
 class DecodeStepProjections:
-    """Weights, activations and the launch list of one decode step, (row-sharded for world > 1)."""
+    """Weights, activations and the launch list of one decode step.
 
-    def __init__(self, rt, syn, rank=0, world=1, layers=LAYERS):
+    One GPU: the weights that share an x (q|k|v, gate|up) are separate handles driven by one
+    multi-weight launch.  Several GPUs: the same weights are concatenated by rows, every rank
+    uploads its row shard, and each launch is followed by the peer-memory exchange that leaves the
+    whole output on every rank (`gather="p2p"`), or by an NCCL all-gather (`gather="nccl"`, kept
+    as the library baseline)."""
+
+    def __init__(self, rt, syn, sharding, rank=0, world=1, layers=LAYERS, gather="p2p", shard_min_mb=16.0):
         import torch
-        self.rt, self.torch, self.rank, self.world = rt, torch, rank, world
-        self.ops = []  # (name, [handles], x_tensor, [out_tensors], [(out_dim_shard, in_dim)], [full out_dim])
+        self.rt, self.torch, self.rank, self.world, self.gather_kind = rt, torch, rank, world, gather
+        self.ops = []  # (name, [handles], x_tensor, [out_tensors], [(out_dim_shard, in_dim)], (lo, out_full))
         self.weight_bytes = 0
         self.bytes_per_step = 0.0
         ops = [(l, n, shapes) for l in range(layers) for n, shapes in LAYER_OPS] + [(layers, "lm_head", [(VOCAB, HIDDEN)])]
         for l, name, shapes in ops:
             in_dim = shapes[0][1]
             x = torch.from_numpy(syn.activations(("x", l, name), in_dim)).cuda()
+            # every layer of a random-init model has its own weights; generation is the slow
+            # part on the host, so layers draw from 4 distinct seeds (contents never repeat in L2:
+            # the copies are separate device buffers)
+            parts = [syn.mlx_weight((name, i, l % 4), o, in_dim, GS) for i, (o, _) in enumerate(shapes)]
             hs, outs, dims = [], [], []
-            for i, (out_dim, _) in enumerate(shapes):
-                # every layer of a random-init model has its own weights; generation is the slow
-                # part on the host, so layers draw from 4 distinct seeds (contents never repeat in L2:
-                # the copies are separate device buffers)
-                w, s, b = syn.mlx_weight((name, i, l % 4), out_dim, in_dim, GS)
-                lo, hi = shard_rows(out_dim, rank, world)
-                wpr, gpr = in_dim // 8, in_dim // GS
-                h = rt.UploadMLXWeight(w[lo * wpr:hi * wpr], s[lo * gpr:hi * gpr], b[lo * gpr:hi * gpr],
-                                       in_dim, hi - lo, GS, True)
-                hs.append(h)
+            packed_mb = sum(o for o, _ in shapes) * in_dim * 0.5625 / 1e6
+            if world == 1 or packed_mb < shard_min_mb:
+                # small projections are not worth an exchange: every rank computes them whole
+                for (o, _), (w, s, b) in zip(shapes, parts):
+                    hs.append(rt.UploadMLXWeight(w, s, b, in_dim, o, GS, True))
+                    outs.append(torch.empty(o, dtype=torch.float32, device="cuda"))
+                    dims.append((o, in_dim))
+                span = None
+            else:
+                w, s, b = (np.concatenate([p[k] for p in parts]) for k in range(3))
+                out_full = sum(o for o, _ in shapes)
+                lo, hi = sharding.shard_rows(out_full, rank, world)
+                hs.append(rt.UploadMLXWeight(*sharding.slice_mlx(w, s, b, in_dim, GS, lo, hi), in_dim, hi - lo, GS, True))
                 outs.append(torch.empty(hi - lo, dtype=torch.float32, device="cuda"))
                 dims.append((hi - lo, in_dim))
+                span = (lo, out_full)
+            for h, (o, i) in zip(hs, dims):
                 self.weight_bytes += h.ResidentBytes()
-                self.bytes_per_step += algorithmic_bytes(hi - lo, in_dim)
-            self.ops.append((name, hs, x, outs, dims))
-        self.launches_per_step = len(self.ops)
-        self.logits = self.ops[-1][3][0]
+                # replicated work counts once for the job: rank 0's copy
+                if span is not None or rank == 0:
+                    self.bytes_per_step += algorithmic_bytes(o, i)
+            self.ops.append((name, hs, x, outs, dims, span))
+        self.sharded_ops = sum(1 for op in self.ops if op[5] is not None)
+        self.launches_per_step = len(self.ops) + (self.sharded_ops if gather == "p2p" else 0)
+        self.exchange = None
         if world > 1:
-            self.gathered = [[torch.empty(world * o.numel(), dtype=torch.float32, device="cuda") for o in op[3]]
-                             for op in self.ops]
+            import torch.distributed as dist
+            if gather == "p2p":
+                self.exchange = rt.Gather(rank, world, VOCAB + 64)
+                handles = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
+                mine = torch.tensor(list(self.exchange.Export()), dtype=torch.uint8, device="cuda")
+                dist.all_gather(handles, mine)
+                for r, h in enumerate(handles):
+                    if r != rank:
+                        self.exchange.OpenPeer(r, bytes(h.cpu().tolist()))
+                dist.barrier()
+            else:
+                self.gathered = [torch.empty(world * op[3][0].numel(), dtype=torch.float32, device="cuda") if op[5] else None
+                                 for op in self.ops]
+        self.logits_n = VOCAB
 
-    def _launch(self, op, stream):
+    def _launch(self, k, op, stream):
+        """Returns the device address of the op's complete output on this rank."""
         rt = self.rt
-        _, hs, x, outs, _ = op
+        _, hs, x, outs, _, span = op
         xb = rt.wrap(x.data_ptr(), x.numel() * 4)
+        if span is not None and self.gather_kind == "p2p":
+            return self.exchange.GemmMLX(xb, hs[0], 1, span[0], span[1], stream).Ptr
         obs = [rt.wrap(o.data_ptr(), o.numel() * 4) for o in outs]
         if len(hs) == 1:
             rt.GemvMLX(obs[0], xb, hs[0], stream)
         else:
             rt.GemmMLXMulti(obs, xb, hs, 1, stream)
+        if span is not None:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.gathered[k], outs[0])
+            return self.gathered[k].data_ptr()
+        return outs[-1].data_ptr()
 
-    def step(self, stream, gather=True):
+    def step(self, stream):
+        """One decode step's projections; returns the device address of the logits."""
+        ptr = 0
         for k, op in enumerate(self.ops):
-            self._launch(op, stream)
-            if self.world > 1 and gather:
-                import torch.distributed as dist
-                for o, g in zip(op[3], self.gathered[k]):
-                    dist.all_gather_into_tensor(g, o)
+            ptr = self._launch(k, op, stream)
+        return ptr
+
+    def logits_tensor(self, ptr):
+        return self.torch.as_tensor(_Raw(ptr, self.logits_n), device="cuda")
 
     def timed_launches(self, stream):
         """One eager pass with events around every launch: [(name, bytes, ms)]."""
         torch = self.torch
         evs = []
-        for op in self.ops:
+        for k, op in enumerate(self.ops):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            self._launch(op, stream)
+            self._launch(k, op, stream)
             b.record(stream)
             evs.append((op[0], sum(algorithmic_bytes(o, i) for o, i in op[4]), a, b))
         torch.cuda.synchronize()
@@ -231,8 +272,6 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world != args.gpus:
-        world = int(os.environ.get("WORLD_SIZE", str(1)))
     torch.cuda.set_device(local)
     if world > 1:
         import torch.distributed as dist
@@ -240,9 +279,12 @@ def run_ours(args):
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
     rt.init(local)
-    wl = DecodeStepProjections(rt, syn, rank, world)
+    wl = DecodeStepProjections(rt, syn, pkg.sharding, rank, world, gather=args.gather, shard_min_mb=args.shard_min_mb)
     stream = torch.cuda.Stream()
     hbm_peak, peak_kind = peaks()
+    p2p = world > 1 and args.gather == "p2p"
+    use_graph = bool(args.graph) and (world == 1 or p2p)
+    steps_per_graph = 1
 
     def barrier():
         if world > 1:
@@ -252,21 +294,23 @@ def run_ours(args):
 
     # ---- device-resident throughput: the step replayed as a CUDA graph -------------------
     with torch.cuda.stream(stream):
-        for _ in range(max(3, args.warmup)):
+        for _ in range(2 * max(3, args.warmup)):
             wl.step(stream)
     torch.cuda.synchronize()
-    graph = None
-    if args.graph and world == 1:
+    graph, graph_logits = None, 0
+    if use_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
-            wl.step(torch.cuda.current_stream())
+            for _ in range(steps_per_graph):
+                graph_logits = wl.step(torch.cuda.current_stream())
         for _ in range(3):
             graph.replay()
         torch.cuda.synchronize()
+    timed_steps = (args.steps + steps_per_graph - 1) // steps_per_graph * steps_per_graph if graph is not None else args.steps
 
     def run_steps(k):
         if graph is not None:
-            for _ in range(k):
+            for _ in range(k // steps_per_graph):
                 graph.replay()
         else:
             with torch.cuda.stream(stream):
@@ -278,7 +322,7 @@ def run_ours(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     rec_stream = torch.cuda.current_stream() if graph is not None else stream
     ev0.record(rec_stream)
-    run_steps(args.steps)
+    run_steps(timed_steps)
     ev1.record(rec_stream)
     barrier()
     ms_total = ev0.elapsed_time(ev1)
@@ -294,7 +338,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     with torch.cuda.stream(stream):
-        for _ in range(args.steps):
+        for _ in range(timed_steps):
             wl.step(stream)
     e1.record(stream)
     barrier()
@@ -302,72 +346,83 @@ def run_ours(args):
 
     # ---- end to end: activations from pinned host memory, logits back -------------------
     xs_host = [torch.from_numpy(syn.activations(("x", 0, op[0]), op[2].numel())).pin_memory() for op in wl.ops]
-    logits_host = torch.empty(wl.logits.numel(), dtype=torch.float32).pin_memory()
+    logits_host = torch.empty(wl.logits_n, dtype=torch.float32).pin_memory()
     h2d = sum(x.numel() * 4 for x in xs_host)
     d2h = logits_host.numel() * 4
 
     def e2e_step():
         for op, xh in zip(wl.ops, xs_host):
             op[2].copy_(xh, non_blocking=True)
-        if graph is not None:
+        if graph is not None and steps_per_graph == 1:
             graph.replay()
+            ptr = graph_logits
         else:
-            wl.step(torch.cuda.current_stream())
-        logits_host.copy_(wl.logits, non_blocking=True)
+            ptr = wl.step(torch.cuda.current_stream())
+        logits_host.copy_(wl.logits_tensor(ptr), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for _ in range(3):
+    for _ in range(4):
         e2e_step()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(timed_steps):
         e2e_step()
     barrier()
     ms_e2e = (time.perf_counter() - t0) * 1e3
 
-    # ---- per-launch durations for the roofline of the GEMV kernel -----------------------
+    # ---- per-launch durations for the roofline of the GEMV kernels ----------------------
     with torch.cuda.stream(stream):
         per = []
-        for _ in range(3):
+        for _ in range(4):
             per = wl.timed_launches(stream)
     k_bytes = sum(b for _, b, _ in per)
     k_ms = sum(t for _, _, t in per)
     lm = [p for p in per if p[0] == "lm_head"][0]
+    status = rt.KernelStatus() + (wl.exchange.Status() if wl.exchange is not None else 0)
 
     # max over ranks
-    times = torch.tensor([ms_total, ms_eager, ms_e2e], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms_total, ms_eager, ms_e2e, float(status)], dtype=torch.float64, device="cuda")
     total_bytes = torch.tensor([wl.bytes_per_step], dtype=torch.float64, device="cuda")
     if world > 1:
         import torch.distributed as dist
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
-    ms_total, ms_eager, ms_e2e = [float(t) for t in times.cpu()]
+    ms_total, ms_eager, ms_e2e, status = [float(t) for t in times.cpu()]
     job_bytes = float(total_bytes.cpu()[0])
+    if status != 0:
+        raise SystemExit("a bounded device-side wait gave up (status %d): the numbers are void" % int(status))
 
     if rank == 0:
-        gbs = job_bytes * args.steps / (ms_total * 1e-3) / 1e9
+        gbs = job_bytes * timed_steps / (ms_total * 1e-3) / 1e9
         achieved = k_bytes / (k_ms * 1e-3) / 1e9
+        lm_gbs = lm[1] / (lm[2] * 1e-3) / 1e9
         line = {
             "metric": "quant_gemv_weight_bandwidth", "value": round(gbs, 2), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms_total / args.steps, 4),
+            "steps": timed_steps, "warmup": 2 * max(3, args.warmup), "ms_per_step": round(ms_total / timed_steps, 4),
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch": 1, "launch": "cuda graph replay" if graph is not None else "eager",
                        "l2": "inputs larger than L2 (335 MB of weights per step vs 126 MB L2)",
-                       "parallelism": "row-sharded x%d + all-gather" % world if world > 1 else "single GPU"},
-            "decode_tok_s_projections_only": round(args.steps / (ms_total * 1e-3), 1),
-            "eager": {"value": round(job_bytes * args.steps / (ms_eager * 1e-3) / 1e9, 2), "unit": "GB/s",
-                      "ms_per_step": round(ms_eager / args.steps, 4)},
-            "e2e": {"value": round(job_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 2), "unit": "GB/s",
+                       "parallelism": ("%d of %d projections (those of %g MB or more packed: the LM head) row-sharded x%d, "
+                                       "outputs exchanged through %s; the smaller ones computed whole on every rank and "
+                                       "counted once" % (wl.sharded_ops, len(wl.ops), args.shard_min_mb, world,
+                                                         "peer memory (one launch per exchange)" if p2p else "NCCL all-gather"))
+                       if world > 1 else "single GPU"},
+            "decode_tok_s_projections_only": round(timed_steps / (ms_total * 1e-3), 1),
+            "eager": {"value": round(job_bytes * timed_steps / (ms_eager * 1e-3) / 1e9, 2), "unit": "GB/s",
+                      "ms_per_step": round(ms_eager / timed_steps, 4)},
+            "e2e": {"value": round(job_bytes * timed_steps / (ms_e2e * 1e-3) / 1e9, 2), "unit": "GB/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": round(ms_e2e / args.steps, 4)},
-            "gpu_launches": wl.launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "mlx_gemv_kernel (all %d launches of a step, eager, CUDA events around each)" % len(per),
-                         "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
-                         "frac": round(achieved / hbm_peak, 4), "peak_kind": peak_kind, "traffic": None,
-                         "lm_head_launch": {"bytes": lm[1], "ms": round(lm[2], 5),
-                                            "achieved": round(lm[1] / (lm[2] * 1e-3) / 1e9, 1),
-                                            "frac": round(lm[1] / (lm[2] * 1e-3) / 1e9 / hbm_peak, 4)}},
+                    "ms_per_step": round(ms_e2e / timed_steps, 4)},
+            "gpu_launches": wl.launches_per_step * timed_steps,
+            # dominant kernel by time and bytes: the LM head launch (mlx_mma_kernel, tcgen05 path)
+            "roofline": {"bound": "hbm", "kernel": "mlx_mma_kernel on the LM head %dx%d (CUDA events around the launch, eager)" % (
+                             wl.ops[-1][4][0][0], HIDDEN),
+                         "achieved": round(lm_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
+                         "frac": round(lm_gbs / hbm_peak, 4), "peak_kind": peak_kind, "traffic": TRAFFIC.get("lm_head"),
+                         "bytes": lm[1], "ms": round(lm[2], 5),
+                         "whole_step": {"note": "all %d launches of a step, events around each: small launches are latency-bound" % len(per),
+                                        "achieved": round(achieved, 1), "frac": round(achieved / hbm_peak, 4)}},
             "clocks": clocks,
         }
         if not args.no_cpu and world == 1:
@@ -379,6 +434,7 @@ def run_ours(args):
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -389,6 +445,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--graph", type=int, default=1)
+    ap.add_argument("--shard-min-mb", type=float, default=16.0,
+                    help="N>1: projections below this many MB of packed weights are computed whole on every rank")
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: how the row shards' outputs reach every rank")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -2,23 +2,27 @@
 //
 // The reference has no multi-GPU path; this is the exchange step that row-sharding a projection
 // (or placing MoE experts per GPU) needs: every rank's [M, out/G] block (or partial [T, hidden] sum)
-// must reach every other rank.  The blocks are a few KB, so the cost is latency, not bandwidth:
-// instead of a library collective the producing rank stores its block straight into every peer's
-// result buffer (plain st.global to peer memory mapped through CUDA IPC or peer access), then
-// raises a flag in each peer's memory; one thread per GPU waits — bounded — until every peer's
-// flag for this exchange has arrived.  One launch per exchange, placed behind the product's
-// kernel with programmatic dependent launch.
+// must reach every other rank.  The blocks are a few KB, so the cost is latency, not bandwidth.
+// Instead of a library collective, one kernel per exchange:
+//   push  every value of this rank's block is stored, paired with the exchange number, as one
+//         8-byte word {value, number} straight into every peer's receive area (plain st.global to
+//         peer memory mapped through CUDA IPC or peer access).  An 8-byte store arrives whole, so
+//         the number doubles as the "this word is valid" flag: no fence, no separate signal, no
+//         acknowledgement round trip.
+//   pull  the same kernel then reads its own receive area: each thread spins — bounded — on the
+//         words it is responsible for until they carry this exchange's number, and writes the
+//         values into the rank's plain result buffer.  The own block is copied directly.
+// The kernel sits behind the product's kernel with programmatic dependent launch; kernels launched
+// after it on the stream see the complete result.
 //
-// Memory of one rank's exchange area (one cudaMalloc, exported to the peers):
-//   [0, 256)                 uint32 flags[8]: flags[q] = number of the last exchange rank q completed into this area
-//   [256, 256 + 4*cap)       result buffer for odd exchanges
-//   [256 + 4*cap, ...)       result buffer for even exchanges
-// The exchange number lives in device memory (the kernel advances it), so exchanges can be captured
-// into a CUDA graph; the result buffer alternates with the number's parity, and since the host hands
-// the buffer's address to the readers at capture time, a replayed graph must hold an even number of
-// exchanges per exchange area (the kernel flags a mismatch in the status word).
-// Two result buffers are enough: a rank can only start exchange e+2 after every peer has raised
-// its flag for e+1, which a peer does after (in stream order) its readers of exchange e.
+// Receive area of one rank (one cudaMalloc, exported to the peers): two banks of `cap` 8-byte words;
+// exchange number e uses bank e & 1.  Two banks are enough: a peer can run at most one exchange
+// ahead of this rank (it cannot finish exchange e+1 without this rank's e+1 block), so while this
+// rank reads bank e & 1 a peer writes bank (e+1) & 1 at the latest.  Words are never cleared: a
+// 32-bit exchange number does not come round again within any realistic run.  The number lives in
+// device memory and is advanced by the kernel itself, so a captured CUDA graph can be replayed.
+// The result buffer is private to the rank and single: stream order already separates its readers
+// from the next exchange's writes.
 #include <string.h>
 
 #include "goph_internal.cuh"
@@ -29,76 +33,76 @@ constexpr int kMaxRanks = 8;
 constexpr long long kGatherTimeoutCycles = 4000000000ll;  // ~2 s at the maximum SM clock
 
 struct GatherArgs {
-  unsigned char* peer[kMaxRanks];
+  unsigned long long* peer[kMaxRanks];  // receive areas (peer[rank] is this rank's own)
   int world, rank;
-  int expected_parity;      // parity of the exchange number the host believes this launch has
-  unsigned long long cap_bytes;
-  const float* src;
-  int rows, count;
-  long long dst_off, dst_row_stride;
+  unsigned long long cap;   // words per bank
+  const float* src;         // this rank's block [rows][my_count]
+  float* result;            // [rows][row_stride]
+  int rows;
+  int per;                  // block width of every rank but possibly the last ones
+  long long total;          // valid width of a result row: rank q holds [q*per, min(total, (q+1)*per))
+  long long row_stride;
   int* done;                // arrival counter
   int* status;
-  uint32_t* epoch_dev;      // number of exchanges completed on this rank; the kernel numbers itself from it
+  uint32_t* epoch_dev;      // number of exchanges completed on this rank
 };
 
-__global__ void __launch_bounds__(256) gather_push_kernel(GatherArgs a) {
+__device__ __forceinline__ int block_count(const GatherArgs& a, int q) {
+  long long lo = (long long)q * a.per, hi = lo + a.per;
+  if (hi > a.total) hi = a.total;
+  return hi > lo ? (int)(hi - lo) : 0;
+}
+
+__global__ void __launch_bounds__(256) gather_exchange_kernel(const __grid_constant__ GatherArgs a) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  // The exchange numbers itself on the device, so a captured graph can be replayed.  Every CTA reads
-  // the counter before the last one to arrive advances it.
+  // Every CTA reads the counter before the last one to finish advances it.
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_dev) + 1;
-  const unsigned long long buf_off = 256 + (unsigned long long)(epoch & 1) * a.cap_bytes;
-  const long long total = (long long)a.rows * a.count;
+  const unsigned long long bank = (unsigned long long)(epoch & 1) * a.cap;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, nth = (long long)gridDim.x * blockDim.x;
-  const bool vec = a.count % 4 == 0 && a.dst_off % 4 == 0 && a.dst_row_stride % 4 == 0 && ((uintptr_t)a.src & 15) == 0;
-  for (int p = 0; p < a.world; ++p) {
-    const int q = (a.rank + p) % a.world;  // start with the own copy, then walk the peers in a rank-dependent order
-    float* dst = reinterpret_cast<float*>(a.peer[q] + buf_off) + a.dst_off;
-    if (vec) {
-      const int c4 = a.count / 4;
-      for (long long i = tid; i < total / 4; i += nth) {
-        const long long m = i / c4, j = i - m * c4;
-        float4 v = reinterpret_cast<const float4*>(a.src)[i];
-        *reinterpret_cast<float4*>(dst + m * a.dst_row_stride + j * 4) = v;
-      }
-    } else {
-      for (long long i = tid; i < total; i += nth) {
-        const long long m = i / a.count, j = i - m * a.count;
-        dst[m * a.dst_row_stride + j] = a.src[i];
-      }
+  // ---- push: own block to the own result and, tagged, to every peer's bank ----------------
+  const int my_count = block_count(a, a.rank);
+  const long long my_off = (long long)a.rank * a.per;
+  for (long long i = tid; i < (long long)a.rows * my_count; i += nth) {
+    const long long m = i / my_count, j = i - m * my_count;
+    const float v = a.src[i];
+    const long long at = m * a.row_stride + my_off + j;
+    a.result[at] = v;
+    const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(v);
+    for (int p = 1; p < a.world; ++p) {
+      const int q = (a.rank + p) % a.world;  // each rank walks the peers in its own order
+      a.peer[q][bank + at] = word;
     }
   }
-  __threadfence_system();
+  // ---- pull: the peers' blocks out of the own bank ------------------------------------------
+  const unsigned long long* mine = a.peer[a.rank] + bank;
+  const long long t0 = clock64();
+  bool gave_up = false;
+  for (int p = 1; p < a.world && !gave_up; ++p) {
+    const int q = (a.rank + p) % a.world;
+    const int cnt = block_count(a, q);
+    const long long off = (long long)q * a.per;
+    for (long long i = tid; i < (long long)a.rows * cnt; i += nth) {
+      const long long m = i / cnt, j = i - m * cnt;
+      const long long at = m * a.row_stride + off + j;
+      unsigned long long word;
+      while (true) {
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(word) : "l"(mine + at) : "memory");
+        if ((uint32_t)(word >> 32) == epoch) break;
+        if (clock64() - t0 > kGatherTimeoutCycles) {
+          atomicCAS(a.status, 0, 100 + q);  // rank q's block did not arrive
+          gave_up = true;
+          break;
+        }
+      }
+      if (gave_up) break;
+      a.result[at] = __uint_as_float((uint32_t)word);
+    }
+  }
   __syncthreads();
-  __shared__ int s_last;
-  if (threadIdx.x == 0) s_last = atomicAdd(a.done, 1) == (int)gridDim.x - 1;
-  __syncthreads();
-  if (!s_last || threadIdx.x >= 32) return;
-  // last CTA, first warp: lane q signals rank q and waits for rank q's signal
-  __threadfence_system();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && atomicAdd(a.done, 1) == (int)gridDim.x - 1) {
     *a.done = 0;
     *a.epoch_dev = epoch;
-    // the host handed out the result buffer of the other parity: its count of exchanges is off
-    // (a replayed graph must hold an even number of exchanges)
-    if ((int)(epoch & 1) != a.expected_parity) atomicCAS(a.status, 0, 200);
-  }
-  const int q = threadIdx.x;
-  if (q < a.world) {
-    uint32_t* remote = reinterpret_cast<uint32_t*>(a.peer[q]) + a.rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
-    const uint32_t* local = reinterpret_cast<const uint32_t*>(a.peer[a.rank]) + q;
-    const long long t0 = clock64();
-    while (true) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
-      if ((int)(v - epoch) >= 0) break;
-      if (clock64() - t0 > kGatherTimeoutCycles) {
-        atomicCAS(a.status, 0, 100 + q);  // rank q's block never arrived
-        break;
-      }
-      __nanosleep(100);
-    }
   }
 }
 
@@ -117,13 +121,13 @@ __global__ void gather_sum_kernel(const float* __restrict__ gathered, float* __r
 struct goph_gather {
   uint32_t magic;
   int device, rank, world;
-  uint64_t capacity;  // floats per result buffer
-  unsigned char* area;
-  unsigned char* peer[goph::kMaxRanks];
+  uint64_t capacity;            // floats in a result, words per bank
+  unsigned long long* area;     // receive area: two banks
+  unsigned long long* peer[goph::kMaxRanks];
   int peer_kind[goph::kMaxRanks];  // 0 not connected, 1 opened from an IPC handle, 2 this process's memory
-  uint32_t epoch;
-  int* done;    // [0] arrival counter, [1] status, [2] exchanges completed
-  float* shard; // this rank's block before it is pushed [capacity]
+  int* done;      // [0] arrival counter, [1] status, [2] exchanges completed
+  float* result;  // [capacity]
+  float* shard;   // this rank's block before it is pushed [capacity]
 };
 
 using namespace goph;
@@ -148,7 +152,7 @@ GOPH_API int goph_gather_create(int device, int rank, int world, uint64_t capaci
   clear_error();
   if (!out) return fail(GOPH_E_INVALID, "goph_gather_create: nil result pointer");
   *out = nullptr;
-  if (world <= 0 || world > kMaxRanks || rank < 0 || rank >= world || capacity_floats == 0 || capacity_floats > (1ull << 32))
+  if (world <= 0 || world > kMaxRanks || rank < 0 || rank >= world || capacity_floats == 0 || capacity_floats > (1ull << 30))
     return fail(GOPH_E_INVALID, "goph_gather_create: rank=%d world=%d (max %d) capacity=%llu", rank, world, kMaxRanks,
                 (unsigned long long)capacity_floats);
   if (int rc = use_device(device)) return rc;
@@ -159,16 +163,18 @@ GOPH_API int goph_gather_create(int device, int rank, int world, uint64_t capaci
   g->rank = rank;
   g->world = world;
   g->capacity = capacity_floats;
-  const size_t bytes = 256 + 2 * capacity_floats * sizeof(float);
+  const size_t bytes = 2 * capacity_floats * sizeof(unsigned long long);
   cudaError_t e = cudaMalloc(&g->area, bytes);
-  if (e == cudaSuccess) e = cudaMemset(g->area, 0, bytes);
+  if (e == cudaSuccess) e = cudaMemset(g->area, 0, bytes);  // number 0 is never used by an exchange
   if (e == cudaSuccess) e = cudaMalloc(&g->done, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(g->done, 0, 4 * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&g->result, capacity_floats * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&g->shard, capacity_floats * sizeof(float));
   if (e == cudaSuccess) e = cudaDeviceSynchronize();  // the area is zero before any peer can see it
   if (e != cudaSuccess) {
     cudaFree(g->area);
     cudaFree(g->done);
+    cudaFree(g->result);
     cudaFree(g->shard);
     delete g;
     return fail_cuda(e, "cudaMalloc(exchange area)");
@@ -201,7 +207,7 @@ GOPH_API int goph_gather_open_peer(goph_gather* g, int peer_rank, const unsigned
   memcpy(&h, handle64, 64);
   void* p = nullptr;
   GOPH_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
-  g->peer[peer_rank] = static_cast<unsigned char*>(p);
+  g->peer[peer_rank] = static_cast<unsigned long long*>(p);
   g->peer_kind[peer_rank] = 1;
   return GOPH_OK;
 }
@@ -238,6 +244,7 @@ GOPH_API int goph_gather_free(goph_gather* g) {
     if (g->peer_kind[r] == 1) cudaIpcCloseMemHandle(g->peer[r]);
   cudaFree(g->area);
   cudaFree(g->done);
+  cudaFree(g->result);
   cudaFree(g->shard);
   g->magic = 0;
   delete g;
@@ -259,15 +266,19 @@ GOPH_API int goph_gather_shard_buffer(goph_gather* g, float** shard_dev) {
   return GOPH_OK;
 }
 
-GOPH_API int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int count, int64_t dst_off,
-                             int64_t dst_row_stride, void* stream, float** result_dev) {
+GOPH_API int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int per, int64_t total,
+                             int64_t row_stride, void* stream, float** result_dev) {
   clear_error();
   if (!valid_gather(g)) return fail(GOPH_E_INVALID, "goph_gather_all: invalid handle");
-  if ((!src_dev && count > 0) || rows <= 0 || count < 0 || dst_off < 0 || dst_row_stride < count || !result_dev)
-    return fail(GOPH_E_INVALID, "goph_gather_all: rows=%d count=%d offset=%lld stride=%lld", rows, count, (long long)dst_off,
-                (long long)dst_row_stride);
-  if ((uint64_t)dst_off + (uint64_t)(rows - 1) * (uint64_t)dst_row_stride + (uint64_t)count > g->capacity)
-    return fail(GOPH_E_INVALID, "goph_gather_all: block ends past the exchange capacity of %llu floats", (unsigned long long)g->capacity);
+  if (rows <= 0 || per <= 0 || total < 0 || row_stride < total || total > (int64_t)per * g->world || !result_dev)
+    return fail(GOPH_E_INVALID, "goph_gather_all: rows=%d per=%d total=%lld stride=%lld world=%d", rows, per, (long long)total,
+                (long long)row_stride, g->world);
+  if ((uint64_t)rows * (uint64_t)row_stride > g->capacity)
+    return fail(GOPH_E_INVALID, "goph_gather_all: result [%d x %lld] exceeds the exchange capacity of %llu floats", rows,
+                (long long)row_stride, (unsigned long long)g->capacity);
+  const int64_t my_lo = (int64_t)g->rank * per;
+  const int64_t my_count = my_lo >= total ? 0 : (total - my_lo < per ? total - my_lo : per);
+  if (!src_dev && my_count > 0) return fail(GOPH_E_INVALID, "goph_gather_all: nil block");
   for (int r = 0; r < g->world; ++r)
     if (!g->peer_kind[r]) return fail(GOPH_E_INVALID, "goph_gather_all: rank %d is not connected", r);
   if (int rc = use_device(g->device)) return rc;
@@ -276,21 +287,22 @@ GOPH_API int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int
   for (int r = 0; r < g->world; ++r) a.peer[r] = g->peer[r];
   a.world = g->world;
   a.rank = g->rank;
-  const uint32_t epoch = ++g->epoch;  // host mirror; the device counter is the one the kernels use
-  a.expected_parity = (int)(epoch & 1);
-  a.cap_bytes = g->capacity * sizeof(float);
-  a.epoch_dev = reinterpret_cast<uint32_t*>(g->done + 2);
+  a.cap = g->capacity;
   a.src = src_dev;
+  a.result = g->result;
   a.rows = rows;
-  a.count = count;
-  a.dst_off = dst_off;
-  a.dst_row_stride = dst_row_stride;
+  a.per = per;
+  a.total = total;
+  a.row_stride = row_stride;
   a.done = g->done;
   a.status = g->done + 1;
-  long long total = (long long)rows * count;
-  int grid = (int)((total / 4 + 255) / 256);
+  a.epoch_dev = reinterpret_cast<uint32_t*>(g->done + 2);
+  // enough threads that nobody polls more than a few words in sequence
+  long long elems = (long long)rows * total;
+  int grid = (int)((elems + 256 * 4 - 1) / (256 * 4));
   if (grid < 1) grid = 1;
-  if (grid > 32) grid = 32;
+  const int cap_grid = 2 * device_state(g->device).sm_count;
+  if (grid > cap_grid) grid = cap_grid;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
@@ -301,46 +313,56 @@ GOPH_API int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  GOPH_CUDA(cudaLaunchKernelEx(&cfg, gather_push_kernel, a));
-  *result_dev = reinterpret_cast<float*>(g->area + 256 + (uint64_t)(epoch & 1) * a.cap_bytes);
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, gather_exchange_kernel, a));
+  *result_dev = g->result;
   return GOPH_OK;
 }
 
-static int check_shard(const goph_gather* g, int shard_out, int batch, int row_lo, int out_dim_full) {
+// The partition goph_shard_rows gives: block width and this rank's rows.
+static int check_shard(const goph_gather* g, int shard_out, int batch, int row_lo, int out_dim_full, int* per) {
   if (!valid_gather(g)) return fail(GOPH_E_INVALID, "invalid exchange handle");
-  if (batch <= 0 || row_lo < 0 || shard_out < 0 || (int64_t)row_lo + shard_out > out_dim_full)
-    return fail(GOPH_E_INVALID, "shard rows [%d,%d) do not lie in 0..%d", row_lo, row_lo + shard_out, out_dim_full);
+  if (batch <= 0 || out_dim_full <= 0) return fail(GOPH_E_INVALID, "batch=%d out_dim=%d", batch, out_dim_full);
+  int lo = 0, hi = 0, lo0 = 0, hi0 = 0;
+  if (int rc = goph_shard_rows(out_dim_full, g->rank, g->world, 8, &lo, &hi)) return rc;
+  if (int rc = goph_shard_rows(out_dim_full, 0, g->world, 8, &lo0, &hi0)) return rc;
+  if (row_lo != lo || shard_out != hi - lo)
+    return fail(GOPH_E_INVALID, "shard holds rows [%d,%d); rank %d of %d owns [%d,%d) of %d (goph_shard_rows, align 8)", row_lo,
+                row_lo + shard_out, g->rank, g->world, lo, hi, out_dim_full);
   if ((uint64_t)batch * (uint64_t)out_dim_full > g->capacity)
     return fail(GOPH_E_INVALID, "result [%d x %d] exceeds the exchange capacity of %llu floats", batch, out_dim_full,
                 (unsigned long long)g->capacity);
+  *per = hi0 - lo0;
   return GOPH_OK;
 }
 
 GOPH_API int goph_mlx_gemm_allgather(goph_gather* g, const goph_mlx_weight* shard, const float* x_dev, uint64_t x_len,
                                      int batch, int row_lo, int out_dim_full, void* stream, float** result_dev) {
   clear_error();
-  if (!shard) return fail(GOPH_E_INVALID, "nil weight shard");
-  if (int rc = check_shard(g, shard->out_dim, batch, row_lo, out_dim_full)) return rc;
-  if (int rc = goph_mlx_gemm(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, shard, batch, stream)) return rc;
-  return goph_gather_all(g, g->shard, batch, shard->out_dim, row_lo, out_dim_full, stream, result_dev);
+  int per = 0;
+  if (int rc = check_shard(g, shard ? shard->out_dim : 0, batch, row_lo, out_dim_full, &per)) return rc;
+  if (shard)
+    if (int rc = goph_mlx_gemm(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, shard, batch, stream)) return rc;
+  return goph_gather_all(g, g->shard, batch, per, out_dim_full, out_dim_full, stream, result_dev);
 }
 
 GOPH_API int goph_gguf_project_allgather(goph_gather* g, const goph_gguf_matrix* shard, const float* x_dev, uint64_t x_len,
                                          int batch, int row_lo, int out_dim_full, void* stream, float** result_dev) {
   clear_error();
-  if (!shard) return fail(GOPH_E_INVALID, "nil matrix shard");
-  if (int rc = check_shard(g, shard->out_dim, batch, row_lo, out_dim_full)) return rc;
-  if (int rc = goph_gguf_project(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, batch, shard, stream)) return rc;
-  return goph_gather_all(g, g->shard, batch, shard->out_dim, row_lo, out_dim_full, stream, result_dev);
+  int per = 0;
+  if (int rc = check_shard(g, shard ? shard->out_dim : 0, batch, row_lo, out_dim_full, &per)) return rc;
+  if (shard)
+    if (int rc = goph_gguf_project(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, batch, shard, stream)) return rc;
+  return goph_gather_all(g, g->shard, batch, per, out_dim_full, out_dim_full, stream, result_dev);
 }
 
 GOPH_API int goph_fp8_gemm_allgather(goph_gather* g, const goph_fp8_linear* shard, const float* x_dev, uint64_t x_len,
                                      int batch, int row_lo, int out_dim_full, void* stream, float** result_dev) {
   clear_error();
-  if (!shard) return fail(GOPH_E_INVALID, "nil linear shard");
-  if (int rc = check_shard(g, shard->out_dim, batch, row_lo, out_dim_full)) return rc;
-  if (int rc = goph_fp8_gemm(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, batch, shard, stream)) return rc;
-  return goph_gather_all(g, g->shard, batch, shard->out_dim, row_lo, out_dim_full, stream, result_dev);
+  int per = 0;
+  if (int rc = check_shard(g, shard ? shard->out_dim : 0, batch, row_lo, out_dim_full, &per)) return rc;
+  if (shard)
+    if (int rc = goph_fp8_gemm(g->shard, (uint64_t)batch * shard->out_dim, x_dev, x_len, batch, shard, stream)) return rc;
+  return goph_gather_all(g, g->shard, batch, per, out_dim_full, out_dim_full, stream, result_dev);
 }
 
 GOPH_API int goph_moe_forward_sharded(goph_gather* g, goph_moe_layer* m, float* out_dev, uint64_t out_len,
@@ -349,11 +371,12 @@ GOPH_API int goph_moe_forward_sharded(goph_gather* g, goph_moe_layer* m, float* 
   if (!valid_gather(g)) return fail(GOPH_E_INVALID, "invalid exchange handle");
   if (tokens <= 0 || hidden <= 0) return fail(GOPH_E_INVALID, "tokens=%d hidden=%d", tokens, hidden);
   const uint64_t n = (uint64_t)tokens * hidden;
-  if (n * g->world > g->capacity) return fail(GOPH_E_INVALID, "partial sums [%d x %d x %d] exceed the exchange capacity", g->world, tokens, hidden);
+  if (n * g->world > g->capacity || n > 0x7fffffffull)
+    return fail(GOPH_E_INVALID, "partial sums [%d x %d x %d] exceed the exchange capacity", g->world, tokens, hidden);
   if (!out_dev || out_len < n) return fail(GOPH_E_INVALID, "MoE out length=%llu, want %llu", (unsigned long long)out_len, (unsigned long long)n);
   if (int rc = goph_moe_forward(m, g->shard, n, x_dev, x_len, tokens, stream)) return rc;
   float* gathered = nullptr;
-  if (int rc = goph_gather_all(g, g->shard, 1, (int)n, (int64_t)g->rank * n, (int64_t)n * g->world, stream, &gathered)) return rc;
+  if (int rc = goph_gather_all(g, g->shard, 1, (int)n, (int64_t)n * g->world, (int64_t)n * g->world, stream, &gathered)) return rc;
   int grid = (int)((n + 255) / 256);
   if (grid > 592) grid = 592;
   cudaLaunchAttribute attr;

@@ -537,28 +537,33 @@ class Gather:
     def _result(self, p, n):
         return Buffer(p.value, int(n) * 4, self.device, owned=False)
 
-    def All(self, src, rows, count, dstOff, dstRowStride, stream=None):
+    def All(self, src, rows, per, total, rowStride, stream=None):
+        """Every rank's block [rows x its width] side by side in every rank's result buffer."""
         p = C.c_void_p(0)
-        _check(lib().goph_gather_all(self._h, C.c_void_p(src.Ptr if src is not None else 0), int(rows), int(count),
-                                     C.c_int64(int(dstOff)), C.c_int64(int(dstRowStride)), _stream_ptr(stream), C.byref(p)))
-        return self._result(p, (rows - 1) * dstRowStride + max(dstRowStride, dstOff + count))
+        _check(lib().goph_gather_all(self._h, C.c_void_p(src.Ptr if src is not None else 0), int(rows), int(per),
+                                     C.c_int64(int(total)), C.c_int64(int(rowStride)), _stream_ptr(stream), C.byref(p)))
+        return self._result(p, rows * rowStride)
 
     def GemmMLX(self, x, shard, B, rowLo, outDimFull, stream=None):
-        """GemmMLX for a weight split by rows over the GPUs; returns this rank's [B x outDimFull] buffer."""
+        """GemmMLX for a weight split by rows over the GPUs (shard None: this rank owns no rows);
+        returns this rank's [B x outDimFull] buffer."""
         p = C.c_void_p(0)
-        _check(lib().goph_mlx_gemm_allgather(self._h, _mlx_handle(shard), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(B),
+        _check(lib().goph_mlx_gemm_allgather(self._h, _mlx_handle(shard) if shard is not None else None,
+                                             C.c_void_p(x.Ptr), C.c_uint64(x.n), int(B),
                                              int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
         return self._result(p, B * outDimFull)
 
     def ProjectGGUF(self, x, shard, batch, rowLo, outDimFull, stream=None):
         p = C.c_void_p(0)
-        _check(lib().goph_gguf_project_allgather(self._h, shard._h, C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
+        _check(lib().goph_gguf_project_allgather(self._h, shard._h if shard is not None else None, C.c_void_p(x.Ptr),
+                                                 C.c_uint64(x.n), int(batch),
                                                  int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
         return self._result(p, batch * outDimFull)
 
     def GemmFP8E4M3(self, x, shard, batch, rowLo, outDimFull, stream=None):
         p = C.c_void_p(0)
-        _check(lib().goph_fp8_gemm_allgather(self._h, _fp8_handle(shard), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
+        _check(lib().goph_fp8_gemm_allgather(self._h, _fp8_handle(shard) if shard is not None else None,
+                                             C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
                                              int(rowLo), int(outDimFull), _stream_ptr(stream), C.byref(p)))
         return self._result(p, batch * outDimFull)
 

@@ -243,18 +243,21 @@ int goph_gather_open_peer(goph_gather* g, int peer_rank, const unsigned char* ha
 /* Same-process form: connects g to the area of `peer` (another rank's handle), enabling peer access. */
 int goph_gather_attach_local(goph_gather* g, goph_gather* peer);
 int goph_gather_free(goph_gather* g);
-/* 0, or 100+q if rank q's block did not arrive within the wait limit (~2 s), or 200 if a replayed
- * CUDA graph held an odd number of exchanges.  The waits are bounded; the context stays usable. */
+/* 0, or 100+q if a block of rank q did not arrive within the wait limit (~2 s).  The waits are
+ * bounded; the context stays usable. */
 int goph_gather_status(goph_gather* g, int* out_status);
 /* Device buffer of capacity_floats floats in which a rank may build its block. */
 int goph_gather_shard_buffer(goph_gather* g, float** shard_dev);
-/* Writes this rank's block src[rows][count] to result[m * dst_row_stride + dst_off + j] on EVERY rank
- * and returns, in *result_dev, this rank's result buffer; stream-ordered: kernels launched after it
- * on `stream` see all ranks' blocks.  The buffer stays valid until the exchange after the next one. */
-int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int count, int64_t dst_off,
-                    int64_t dst_row_stride, void* stream, float** result_dev);
-/* Sharded product + exchange: `shard` holds rows [row_lo, row_lo + shard.out_dim) of a projection
- * with out_dim_full rows; *result_dev receives [batch x out_dim_full] on every rank.
+/* All ranks' blocks side by side in every rank's result buffer.  A result row is `total` floats
+ * wide (row_stride >= total apart); rank q owns columns [q*per, min(total, (q+1)*per)) of it and
+ * passes them as src[rows][its width].  *result_dev receives this rank's result buffer
+ * [rows x row_stride]; stream-ordered: kernels launched after the call on `stream` see all ranks'
+ * blocks, and the buffer is rewritten by the next exchange on this handle. */
+int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int per, int64_t total,
+                    int64_t row_stride, void* stream, float** result_dev);
+/* Sharded product + exchange: `shard` holds the rows goph_shard_rows(out_dim_full, rank, world, 8)
+ * gives this rank, starting at row_lo (NULL for a rank that owns no rows); *result_dev receives
+ * [batch x out_dim_full] on every rank.
  * (GemmMLX / ProjectBatchToBuffer / GemmFP8E4M3Buffer for a weight split over GPUs.) */
 int goph_mlx_gemm_allgather(goph_gather* g, const goph_mlx_weight* shard, const float* x_dev, uint64_t x_len,
                             int batch, int row_lo, int out_dim_full, void* stream, float** result_dev);

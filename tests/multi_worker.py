@@ -116,7 +116,7 @@ def run_gpu(rank, world, pkg):
                 res = g.GemmMLX(xb, h, batch, lo, out_dim)
             else:
                 h = None
-                res = g.All(None, batch, 0, lo, out_dim)
+                res = g.GemmMLX(xb, None, batch, lo, out_dim)
             rt.Sync()
             got = res.Download(batch * out_dim)
             want = orc.mlx_gemm(x, batch, w, s, b, out_dim, in_dim, 64, nthreads=8)

@@ -43,7 +43,7 @@ def test_sharded_products_and_exchange_one_rank_per_gpu():
 
 @pytest.mark.gpu
 def test_exchange_single_rank(gpu, pkg):
-    """world = 1: the exchange degenerates to a copy into the own result buffer plus the own flag."""
+    """world = 1: the exchange degenerates to a copy into the own result buffer."""
     import numpy as np
     from oracle import binding as orc
     rt, syn = gpu, pkg.synth
@@ -63,7 +63,7 @@ def test_exchange_single_rank(gpu, pkg):
     with pytest.raises(rt.GophError):
         g.GemmMLX(rt.Malloc(in_dim), h, 1, 8, out_dim)        # rows past the full output
     with pytest.raises(rt.GophError):
-        g.All(rt.Malloc(16), 1, 16, (1 << 16) - 8, 1 << 16)   # past the capacity
+        g.All(rt.Malloc(16), 2, 1 << 16, 1 << 16, 1 << 16)    # past the capacity
     with pytest.raises(rt.GophError):
         rt.Gather(0, 9, 1024)                                 # more ranks than the exchange supports
     h.Free(); g.Free()
