@@ -16,6 +16,7 @@
 //   Q8_0  plane of (q + 128) bytes [out][in], then f16 d [out][in/32].
 #include <string.h>
 
+#include "mlx_mma.cuh"
 #include "stream_gemv.cuh"
 
 namespace goph {
@@ -209,8 +210,8 @@ __global__ void q8_0_dequant_kernel(const uint8_t* __restrict__ plane, const uin
 }
 
 static bool valid_gguf(const goph_gguf_matrix* m) {
-  return m && m->magic == kMagicGGUF && m->data && m->in_dim > 0 && m->out_dim > 0 &&
-         (m->qtype == GOPH_GGUF_Q4_K || (m->qtype == GOPH_GGUF_Q8_0 && m->d16));
+  return m && m->magic == kMagicGGUF && m->in_dim > 0 && m->out_dim > 0 &&
+         (m->tiled || (m->data && (m->qtype == GOPH_GGUF_Q4_K || (m->qtype == GOPH_GGUF_Q8_0 && m->d16))));
 }
 
 static long gguf_row_bytes(int qtype, int in_dim) {
@@ -255,6 +256,7 @@ GOPH_API int goph_gguf_upload(int device, int qtype, const uint8_t* raw, uint64_
     if (rc) {
       cudaFree(h->data);
       cudaFree(h->d16);
+      cudaFree(h->tiled);
       delete h;
     }
     return rc;
@@ -281,6 +283,16 @@ GOPH_API int goph_gguf_upload(int device, int qtype, const uint8_t* raw, uint64_
   UP(cudaGetLastError());
   UP(cudaDeviceSynchronize());
 #undef UP
+  // Large matrices go to the tensor-core layout (the CUDA-core kernels are instruction-bound on
+  // this part); small ones stay in the streaming layout, whose launch is leaner.
+  const bool big = (uint64_t)in_dim * (uint64_t)out_dim >= (8ull << 20);
+  if (gguf_mma_supported(qtype, in_dim) && (options().gguf_layout == 2 || (options().gguf_layout == 0 && big))) {
+    if (int rc = gguf_mma_make_tiled(h)) return bail(rc);
+    cudaFree(h->data);
+    cudaFree(h->d16);
+    h->data = nullptr;
+    h->d16 = nullptr;
+  }
   *out = h;
   return bail(GOPH_OK);
 }
@@ -292,6 +304,7 @@ GOPH_API int goph_gguf_free(goph_gguf_matrix* m) {
   if (int rc = use_device(m->device)) return rc;
   cudaFree(m->data);
   cudaFree(m->d16);
+  cudaFree(m->tiled);
   m->magic = 0;
   delete m;
   return GOPH_OK;
@@ -311,6 +324,7 @@ GOPH_API int goph_gguf_dequant(const goph_gguf_matrix* m, float* out_dev, uint64
   if ((uintptr_t)out_dev % 16) return fail(GOPH_E_INVALID, "dequant out must be 16-byte aligned");
   if (int rc = use_device(m->device)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
+  if (m->tiled) return gguf_mma_dequant(m, out_dev, s);
   if (m->qtype == GOPH_GGUF_Q4_K) {
     size_t nunits = need / 32;
     q4k_dequant_kernel<<<(unsigned)((nunits + 255) / 256), 256, 0, s>>>(m->data, out_dev, nunits);
@@ -333,6 +347,7 @@ GOPH_API int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_
     return fail(GOPH_E_INVALID, "buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
                 (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
   if (int rc = use_device(m->device)) return rc;
+  if (m->tiled) return gguf_mma_launch(m, out_dev, x_dev, batch, options().mlx_digits, (cudaStream_t)stream);
   StreamArgs a;
   memset(&a, 0, sizeof a);
   a.w = m->data;

@@ -57,6 +57,7 @@ struct Options {
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
   int mlx_unpack = 0;
+  int gguf_layout = 0; // as mlx_layout, for Q4_K / Q8_0 matrices
   int mlx_rows = 0, gguf_rows = 0, fp8_rows = 0;
 };
 Options& options();
@@ -96,6 +97,7 @@ struct goph_gguf_matrix {
   int qtype, in_dim, out_dim;
   uint8_t* data;   // Q4_K: blocks; Q8_0: biased int8 plane
   uint16_t* d16;   // Q8_0 only: f16 scales
+  uint8_t* tiled;  // tensor-core layout (data and d16 are then null): one stage per 128 rows x 256 elements
   uint64_t bytes;
 };
 

@@ -45,9 +45,29 @@ namespace {
 
 constexpr int kTileRows = 128;
 constexpr int kChunkK = 256;                  // elements per pipeline stage
-constexpr int kStageWBytes = kTileRows * 128; // packed nibbles of a stage
-constexpr int kStageMBytes = kTileRows * 16;  // {scale,bias} bf16 pairs, 4 groups of 64
-constexpr int kStageBytes = kStageWBytes + kStageMBytes;  // the B tile follows
+constexpr int kStageMBytes = kTileRows * 16;  // 16 bytes of scales per row and stage in every format
+
+// What differs between the weight formats that share this kernel.  A stage is 128 rows x 256
+// elements: the weights as the shared-memory image the tensor core (or the converters) want,
+// then 16 bytes of scale data per row.
+//   MLX4  128 B of nibbles per row (16-byte units XOR-swizzled by row); {scale,bias} bf16 pairs of
+//         the 4 groups of 64.  One accumulator block per group (two K=32 MMAs accumulate).
+//   Q4K   the same nibble image (one 256-element super-block per row and stage); f16 d, f16 dmin and
+//         8 x 12 bits (sc | m << 6).  One accumulator block per 32-element sub-block.
+//   Q80   256 signed bytes per row, stored as K-major 8x16-byte core matrices
+//         [K step][K half][row group][row][16 B] so the MMA reads them from shared memory as they
+//         lie — no conversion at all; 8 f16 block scales.  One accumulator block per 32-element block.
+enum { FMT_MLX4 = 0, FMT_Q4K = 1, FMT_Q80 = 2 };
+template <int FMT>
+struct Fmt {
+  static constexpr bool kConv = FMT != FMT_Q80;                 // nibbles -> bytes through TMEM
+  static constexpr int kBlocks = FMT == FMT_MLX4 ? 4 : 8;       // accumulator blocks per stage
+  static constexpr int kGroup = FMT == FMT_MLX4 ? 64 : 32;      // elements per scale
+  static constexpr int kStageWBytes = kTileRows * (FMT == FMT_Q80 ? 256 : 128);
+  static constexpr int kStageBytes = kStageWBytes + kStageMBytes;  // the B tile follows
+};
+constexpr int kStageWBytes = Fmt<FMT_MLX4>::kStageWBytes;
+constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
 constexpr long long kTimeoutCycles = 4000000000LL;
 
 constexpr int kConvWarps = 8, kEpiWarps = 4;
@@ -143,6 +163,16 @@ __device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
+// The same with A read from shared memory through a descriptor.
+__device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -172,12 +202,12 @@ struct MmaArgs {
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
 // 2 B tiles (8 K-steps x N rows x 32 bytes), per-(row,group) tables {sum x, 2^(E-26), 2^(26-E)},
 // mbarriers, the TMEM base holder.
-template <int N>
+template <int N, int FMT = FMT_MLX4>
 struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
-  static constexpr int kStage = kStageBytes + kBTileBytes;
+  static constexpr int kStage = Fmt<FMT>::kStageBytes + kBTileBytes;
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim) {
-    return (size_t)stages * kStage + (size_t)batch * (in_dim / 64) * 8 + 1024 + 512;
+    return (size_t)stages * kStage + (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512;
   }
 };
 
@@ -207,7 +237,10 @@ struct StageWalk {
 // One block of 64 threads per (activation row, 64-element group): group sum, power-of-two scale,
 // and the base-128 digits of every element written where the tensor core expects them:
 // chunk (256 K) -> K-step (32) -> half (16 bytes) -> 8-row core matrix -> row -> byte.
-template <int DIGITS>
+// G32: sums and scales per 32 elements (one warp each) instead of per 64.  NATURAL: the B bytes of
+// a K step in element order (for A operands that lie in memory in element order) instead of the
+// order the nibble converters produce.
+template <int DIGITS, bool G32 = false, bool NATURAL = false>
 __global__ void __launch_bounds__(64)
 mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, float* __restrict__ xtab, int batch,
                   int in_dim, int N) {
@@ -224,18 +257,26 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
     s += __shfl_xor_sync(0xffffffffu, s, o);
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   }
-  __shared__ float sh[4];
-  if ((t & 31) == 0) {
-    sh[t >> 5] = s;
-    sh[2 + (t >> 5)] = mx;
+  if (!G32) {
+    __shared__ float sh[4];
+    if ((t & 31) == 0) {
+      sh[t >> 5] = s;
+      sh[2 + (t >> 5)] = mx;
+    }
+    __syncthreads();
+    s = sh[0] + sh[1];
+    mx = fmaxf(sh[2], sh[3]);
   }
-  __syncthreads();
-  s = sh[0] + sh[1];
-  mx = fmaxf(sh[2], sh[3]);
   int e = (int)((__float_as_uint(mx) >> 23) & 0xFF);  // mx < 2^(e-126)
   if (e < QBITS + 2) e = QBITS + 2;
   if (e > 254) e = 254;  // inf/nan inputs: results are undefined, not a hang
-  if (t == 0) {
+  if (G32) {
+    if ((t & 31) == 0) {
+      const int g32 = 2 * g + (t >> 5), n32 = 2 * groups;
+      xtab[m * n32 + g32] = s;
+      xtab[(batch + m) * n32 + g32] = __uint_as_float((uint32_t)(e - 126 - QBITS + 127) << 23);
+    }
+  } else if (t == 0) {
     xtab[m * groups + g] = s;
     xtab[(batch + m) * groups + g] = __uint_as_float((uint32_t)(e - 126 - QBITS + 127) << 23);  // 2^(E-QBITS)
   }
@@ -244,7 +285,7 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
   // position of element k inside its chunk's B tile
   const int k = (g & 3) * 64 + t;          // element within the 256-element chunk
   const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
-  const int pos = 8 * w + 4 * (j & 1) + (j >> 1);  // byte along K inside the step (order of the A bytes)
+  const int pos = NATURAL ? (k & 31) : 8 * w + 4 * (j & 1) + (j >> 1);  // byte along K inside the step (order of the A bytes)
   const size_t base = (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
 #pragma unroll
   for (int d = 0; d < DIGITS; ++d) {
@@ -257,19 +298,25 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
 
 // N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
 // MB: activation rows the instantiation can take (MB * DIGITS <= N).
-template <int N, int DIGITS, int MB>
+template <int N, int DIGITS, int MB, int FMT = FMT_MLX4>
 __global__ void __launch_bounds__(kThreads, 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
   static_assert(N == 8 || N == 16 || N == 32, "accumulator blocks of 8, 16 or 32 columns");
-  constexpr int NB = N <= 16 ? 4 : 2;           // depth of the A / accumulator rings in TMEM
-  constexpr uint32_t kCols = 512;               // >= NB * (64 + 4N) columns
-  constexpr int kStage = MmaSmem<N>::kStage;
+  typedef Fmt<FMT> F;
+  constexpr int kBlocks = F::kBlocks;
+  constexpr int kACols = F::kConv ? 64 : 0;     // TMEM columns of one A buffer
+  // depth of the A / accumulator rings in TMEM: NB * (kACols + kBlocks * N) <= 512 columns
+  constexpr int NB = (kACols + kBlocks * N) * 4 <= 512 ? 4 : 2;
+  static_assert(NB * (kACols + kBlocks * N) <= 512, "TMEM plan");
+  constexpr uint32_t kCols = 512;
+  constexpr int kStage = MmaSmem<N, FMT>::kStage;
+  constexpr int kStageBytes = F::kStageBytes, kStageWBytes = F::kStageWBytes;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
   unsigned char* ring = smem;
-  const int groups = a.in_dim / 64;
+  const int groups = a.in_dim / F::kGroup;
   float* xsum = reinterpret_cast<float*>(ring + (size_t)S * kStage);  // [batch][groups] sum of x
   float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
   uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
@@ -284,7 +331,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, kConvThreads + kEpiThreads + 1);  // converters, epilogue (meta), MMA commit (B tile)
+      // converters (conversion formats), epilogue (scale data), MMA commit (B tile, A read from the stage)
+      mbar_init(empty0 + 8 * s, (F::kConv ? kConvThreads : 0) + kEpiThreads + 1);
     }
     for (int b = 0; b < NB; ++b) {
       mbar_init(aready0 + 8 * b, kConvThreads);
@@ -303,7 +351,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NB * 64;  // A: NB x 64 cols; D: NB x 4N cols
+  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NB * kACols;  // A: NB x 64 cols; D: NB x kBlocks*N cols
   bool ok = true;
   StageWalk sw(a);
 
@@ -321,12 +369,18 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
           uint32_t dst = smem_u32(ring + (size_t)i * kStage);
           mbar_expect_tx(full0 + 8 * i, kStage);
-          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, kStageBytes, full0 + 8 * i);
+          const unsigned char* src = a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes;
+          if (a.dbg & 128) {
+            bulk_load_1d(dst, src, 16384, full0 + 8 * i);
+            bulk_load_1d(dst + 16384, src + 16384, kStageBytes - 16384, full0 + 8 * i);
+          } else {
+            bulk_load_1d(dst, src, kStageBytes, full0 + 8 * i);
+          }
         }
         pdl_wait();
         for (int j = 0; j < i; ++j, sw.next(a))
-          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N>::kBTileBytes,
-                       MmaSmem<N>::kBTileBytes, full0 + 8 * j);
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N, FMT>::kBTileBytes,
+                       MmaSmem<N, FMT>::kBTileBytes, full0 + 8 * j);
         nst = i;
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
@@ -336,8 +390,14 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         ++nst;
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
         mbar_expect_tx(full0 + 8 * slot, kStage);
-        bulk_load_1d(dst, a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes, kStageBytes, full0 + 8 * slot);
-        bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N>::kBTileBytes, MmaSmem<N>::kBTileBytes,
+        const unsigned char* src = a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes;
+        if (a.dbg & 128) {
+          bulk_load_1d(dst, src, 16384, full0 + 8 * slot);
+          bulk_load_1d(dst + 16384, src + 16384, kStageBytes - 16384, full0 + 8 * slot);
+        } else {
+          bulk_load_1d(dst, src, kStageBytes, full0 + 8 * slot);
+        }
+        bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N, FMT>::kBTileBytes, MmaSmem<N, FMT>::kBTileBytes,
                      full0 + 8 * slot);
       }
       if (pr) {
@@ -350,37 +410,50 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       const int mi = warp - kWarpMMA;
+      const int istride = (a.dbg & 512) ? 1 : kMmaWarps;  // tuning aid: one issuer takes every stage
       if (mi == 1 && sw.live(a)) sw.next(a);
-      // instruction descriptor: D s32, A u8, B s8, both K-major, N, M=128
-      const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+      // instruction descriptor: D s32, A u8 (nibbles) or s8 (Q8_0 bytes), B s8, both K-major, N, M=128
+      const uint32_t idesc = (2u << 4) | ((FMT == FMT_Q80 ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+      // A from shared memory (Q8_0): K-adjacent core matrices 16 row groups apart, row groups 128 B apart
+      const uint64_t adesc_hi = ((uint64_t)(2048u >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
       constexpr uint32_t kLBO = (N / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
       const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
       const bool pr = a.probe && blockIdx.x == 0 && mi == 0;
       long long w0 = 0, w1 = 0, w2 = 0, tstart = clock64();
-      for (int i = mi; sw.live(a) && ok; i += kMmaWarps) {
+      for (int i = mi; sw.live(a) && ok && !(istride == 1 && mi == 1); i += istride) {
         int b = i % NB, slot = i % S;
-        if (!(a.dbg & 32)) ok = mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 8, pr, w2);
-        if (ok) ok = mbar_wait_t(aready0 + 8 * b, (i / NB) & 1, a.status, 2, pr, w0);
+        // The two issuers take alternate stages, so this one has not itself seen stage i-1 land.
+        // A parity wait can only tell the barrier's current phase from the one before it: if this
+        // issuer ran ahead and asked for round R of a slot whose round R-1 is still in flight, the
+        // wait would pass at once.  Waiting for stage i-1 first makes every earlier stage (in
+        // particular stage i-S, the slot's previous round) complete before stage i is asked for.
+        if (i >= 1) ok = mbar_wait_t(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 9, pr, w2);
+        if (ok && !(a.dbg & 32)) ok = mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 8, pr, w2);
+        if (ok && F::kConv) ok = mbar_wait_t(aready0 + 8 * b, (i / NB) & 1, a.status, 2, pr, w0);
         if (ok && i >= NB) ok = mbar_wait_t(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5, pr, w1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (a.dbg & 256) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage + kStageBytes);
-        const uint32_t dcol = tmemD0 + b * (4 * N), acol = tmemA0 + b * 64;
-        if (a.dbg & 64) {
+        const uint32_t dcol = tmemD0 + b * (kBlocks * N), acol = tmemA0 + b * kACols;
+        if (!(a.dbg & 2)) {
 #pragma unroll
-          for (int step = 0; step < 8; step += 2)
-            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF),
-                       idesc, 0);
-        } else if (!(a.dbg & 2)) {
-#pragma unroll
-          for (int step = 0; step < 8; ++step)  // K = 32 per step; two steps per 64-element group
-            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF),
-                       idesc, step & 1);
+          for (int step = 0; step < 8; ++step) {  // K = 32 per step
+            const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
+            if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
+              umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
+            } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
+              umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
+            } else {
+              const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
+              umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
+            }
+          }
         }
         umma_commit(mdone0 + 8 * b);
         umma_commit(empty0 + 8 * slot);
         sw.next(a);
-        if (sw.live(a)) sw.next(a);
+        if (istride == 2 && sw.live(a)) sw.next(a);
       }
       if (pr) {
         a.probe[8] = clock64() - tstart;
@@ -389,6 +462,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         a.probe[11] = w2;
       }
     }
+  } else if (warp < kConvWarps && !F::kConv) {
+    // nothing to convert: the MMA reads the stage as it lies
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------------ converters
     // Thread = (row r of the tile, half h of the stage's eight 16-byte units).
@@ -473,44 +548,62 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         continue;
       }
       const uint32_t meta[4] = {mv.x, mv.y, mv.z, mv.w};
-      constexpr int NLD = (MB * DIGITS + 15) / 16;  // 16-column loads per group block
-      uint32_t t[4][NLD][16];
+      const int gbase = sw.c * kBlocks;
+      // four accumulator blocks (4N adjacent columns) at a time (register budget); the buffer is
+      // released after the last loads
+      constexpr int NLD = 4 * N / 16;
 #pragma unroll
-      for (int g = 0; g < 4; ++g)
+      for (int hb = 0; hb < kBlocks / 4; ++hb) {
+        uint32_t t[NLD][16];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          // (with N = 8 the load also brings the next block's eight columns, which are ignored)
-          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (4 * N) + g * N + l * 16, t[g][l]);
+          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + hb * 4 * N + l * 16, t[l]);
           else {
 #pragma unroll
-            for (int z = 0; z < 16; ++z) t[g][l][z] = meta[g] + z;
+            for (int z = 0; z < 16; ++z) t[l][z] = meta[l & 3] + z;
           }
         }
 #pragma unroll
-      for (int g = 0; g < 4; ++g)
+        for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[l]);
+        if (hb == kBlocks / 4 - 1) {
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(dfree0 + 8 * b);
+        }
 #pragma unroll
-        for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[g][l]);
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(dfree0 + 8 * b);
-      const int gbase = sw.c * 4;
+        for (int g = 0; g < 4; ++g) {
+          const int blk = hb * 4 + g;
+          // the block's multiplier of the integer dot and of the block's sum of x
+          float sc, bi;
+          if (FMT == FMT_MLX4) {  // {scale, bias} bf16 pair of the 64-element group
+            sc = __uint_as_float(meta[g] << 16);
+            bi = __uint_as_float(meta[g] & 0xFFFF0000u);
+          } else if (FMT == FMT_Q4K) {  // (sc*d) and -(m*dmin), each rounded to f32 as dequantRowQ4KTo does
+            const int bit = 12 * blk, wi = bit >> 5, sh = bit & 31;
+            const uint32_t lo = wi == 0 ? meta[1] : wi == 1 ? meta[2] : meta[3];
+            const uint32_t hi = wi == 0 ? meta[2] : wi == 1 ? meta[3] : 0u;
+            const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+            sc = __fmul_rn((float)(f & 63u), __half2float(__ushort_as_half((unsigned short)(meta[0] & 0xFFFFu))));
+            bi = -__fmul_rn((float)(f >> 6), __half2float(__ushort_as_half((unsigned short)(meta[0] >> 16))));
+          } else {  // f16 block scale
+            sc = __half2float(__ushort_as_half((unsigned short)((meta[blk >> 1] >> (16 * (blk & 1))) & 0xFFFFu)));
+            bi = 0.f;
+          }
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float sc = __uint_as_float(meta[g] << 16), bi = __uint_as_float(meta[g] & 0xFFFF0000u);
-#pragma unroll
-        for (int m = 0; m < MB; ++m) {
-          if (m < a.batch) {
-            auto col = [&](int cidx) { return (int)t[g][cidx >> 4][cidx & 15]; };
-            float dotq;
-            if (DIGITS == 4) {
-              int lo = col(4 * m) + (col(4 * m + 1) << 7), hi = col(4 * m + 2) + (col(4 * m + 3) << 7);
-              dotq = fmaf((float)hi, 16384.f, (float)lo);
-            } else {
-              int lo = col(3 * m) + (col(3 * m + 1) << 7);
-              dotq = fmaf((float)col(3 * m + 2), 16384.f, (float)lo);
+          for (int m = 0; m < MB; ++m) {
+            if (m < a.batch) {
+              auto col = [&](int cidx) { return (int)t[(g * N + cidx) >> 4][(g * N + cidx) & 15]; };
+              float dotq;
+              if (DIGITS == 4) {
+                int lo = col(4 * m) + (col(4 * m + 1) << 7), hi = col(4 * m + 2) + (col(4 * m + 3) << 7);
+                dotq = fmaf((float)hi, 16384.f, (float)lo);
+              } else {
+                int lo = col(3 * m) + (col(3 * m + 1) << 7);
+                dotq = fmaf((float)col(3 * m + 2), 16384.f, (float)lo);
+              }
+              float dot = dotq * xfs[m * groups + gbase + blk];
+              acc[m] = fmaf(sc, dot, acc[m]);
+              if (FMT != FMT_Q80) acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
             }
-            float dot = dotq * xfs[m * groups + gbase + g];
-            acc[m] = fmaf(sc, dot, acc[m]);
-            acc[m] = fmaf(bi, xsum[m * groups + gbase + g], acc[m]);
           }
         }
       }
@@ -640,7 +733,7 @@ constexpr size_t kMaxCounters = 4096;
 // Prepared activations: up to 8 rows of up to 65536 elements (B operand: 32 rows x in_dim bytes).
 constexpr int kMaxPrepIn = 65536;  // mlx_mma_supported's bound on in_dim
 constexpr size_t kPrepXbBytes = (size_t)32 * kMaxPrepIn;
-constexpr size_t kPrepTabFloats = (size_t)2 * 8 * (kMaxPrepIn / 64);
+constexpr size_t kPrepTabFloats = (size_t)2 * 8 * (kMaxPrepIn / 32);
 
 static MmaDeviceBufs* device_bufs(int device) {
   static MmaDeviceBufs bufs[kMaxDevices];
@@ -674,12 +767,18 @@ int mlx_mma_status(int device) {
   return v;
 }
 
-template <int N, int DIGITS, int MB>
-static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t stream, bool prep) {
+// A matrix in one of the tiled layouts, as the launch code sees it.
+struct TiledDesc {
+  const unsigned char* tiled;
+  int device, out_dim, in_dim;
+};
+
+template <int N, int DIGITS, int MB, int FMT>
+static int launch_one(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep) {
   MmaArgs a = a0;
-  DeviceState& st = device_state(w->device);
-  size_t fixed = MmaSmem<N>::bytes(0, a.batch, a.in_dim);
-  int stages = (int)(((size_t)kSmemBudget - fixed) / MmaSmem<N>::kStage);
+  DeviceState& st = device_state(w.device);
+  size_t fixed = MmaSmem<N, FMT>::bytes(0, a.batch, a.in_dim);
+  int stages = (int)(((size_t)kSmemBudget - fixed) / MmaSmem<N, FMT>::kStage);
   if (stages > 8) stages = 8;
   if (stages < 3)
     return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
@@ -695,7 +794,7 @@ static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t 
   while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
   a.splits = splits;
   a.items = a.ntiles * splits;
-  size_t smem = MmaSmem<N>::bytes(stages, a.batch, a.in_dim);
+  size_t smem = MmaSmem<N, FMT>::bytes(stages, a.batch, a.in_dim);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
   // activations -> digits, sums and scales, once per launch
   cudaLaunchAttribute attr;
@@ -709,9 +808,9 @@ static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t 
   cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
   cfg.blockDim = dim3(64);
   if (prep)
-    GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS>, a.x, const_cast<unsigned char*>(a.xb),
-                                 const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
-  auto kern = mlx_mma_kernel<N, DIGITS, MB>;
+    GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80>, a.x,
+                                 const_cast<unsigned char*>(a.xb), const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
+  auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
   cfg.gridDim = dim3(grid);
@@ -721,14 +820,14 @@ static int launch_one(const goph_mlx_weight* w, const MmaArgs& a0, cudaStream_t 
   return GOPH_OK;
 }
 
-int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
-                   bool x_prepared) {
-  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
-  MmaDeviceBufs* bufs = device_bufs(w->device);
+template <int FMT>
+static int tiled_launch(const TiledDesc& w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                        bool x_prepared) {
+  MmaDeviceBufs* bufs = device_bufs(w.device);
   if (!bufs) return fail(GOPH_E_NOMEM, "cannot allocate the tensor-core path's device scratch");
   MmaArgs a;
   memset(&a, 0, sizeof a);
-  a.w = w->tiled;
+  a.w = w.tiled;
   a.status = bufs->status;
   a.scratch = bufs->scratch;
   a.counters = bufs->counters;
@@ -736,27 +835,30 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
   a.xtab = bufs->xtab;
   a.probe = options().mlx_probe ? bufs->probe : nullptr;
   a.dbg = options().mlx_dbg;
-  a.out_dim = w->out_dim;
-  a.in_dim = w->in_dim;
-  a.ntiles = (w->out_dim + kTileRows - 1) / kTileRows;
-  a.nchunks = w->in_dim / kChunkK;
-  const int cap = 8;  // activation rows one launch can take
+  a.out_dim = w.out_dim;
+  a.in_dim = w.in_dim;
+  a.ntiles = (w.out_dim + kTileRows - 1) / kTileRows;
+  a.nchunks = w.in_dim / kChunkK;
+  // activation rows one launch can take: the accumulator blocks of a stage must fit TMEM twice
+  const int cap = FMT == FMT_Q4K ? (digits == 3 ? 5 : 4) : 8;
   for (int b0 = 0; b0 < batch;) {
     int nb = batch - b0 < cap ? batch - b0 : cap;
-    a.x = x + (size_t)b0 * w->in_dim;
-    a.out = out + (size_t)b0 * w->out_dim;
+    a.x = x + (size_t)b0 * w.in_dim;
+    a.out = out + (size_t)b0 * w.out_dim;
     a.batch = nb;
     const bool prep = !(x_prepared && batch <= cap);
     int rc;
     if (digits == 3) {
-      rc = nb <= 2 ? launch_one<8, 3, 2>(w, a, stream, prep)
-         : nb <= 5 ? launch_one<16, 3, 5>(w, a, stream, prep)
-                   : launch_one<32, 3, 8>(w, a, stream, prep);
+      if (nb <= 2) rc = launch_one<8, 3, 2, FMT>(w, a, stream, prep);
+      else if (nb <= 5) rc = launch_one<16, 3, 5, FMT>(w, a, stream, prep);
+      else if (FMT != FMT_Q4K) rc = launch_one<32, 3, 8, FMT == FMT_Q4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
+      else rc = fail(GOPH_E_UNSUPPORTED, "batch slice too wide");
     } else {
-      rc = nb == 1 ? launch_one<8, 4, 1>(w, a, stream, prep)
-         : nb == 2 ? launch_one<8, 4, 2>(w, a, stream, prep)
-         : nb <= 4 ? launch_one<16, 4, 4>(w, a, stream, prep)
-                   : launch_one<32, 4, 8>(w, a, stream, prep);
+      if (nb == 1) rc = launch_one<8, 4, 1, FMT>(w, a, stream, prep);
+      else if (nb == 2) rc = launch_one<8, 4, 2, FMT>(w, a, stream, prep);
+      else if (nb <= 4) rc = launch_one<16, 4, 4, FMT>(w, a, stream, prep);
+      else if (FMT != FMT_Q4K) rc = launch_one<32, 4, 8, FMT == FMT_Q4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
+      else rc = fail(GOPH_E_UNSUPPORTED, "batch slice too wide");
     }
     if (rc) return rc;
     b0 += nb;
@@ -764,6 +866,153 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
   return GOPH_OK;
 }
 
+int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                   bool x_prepared) {
+  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
+  TiledDesc d{w->tiled, w->device, w->out_dim, w->in_dim};
+  return tiled_launch<FMT_MLX4>(d, out, x, batch, digits, stream, x_prepared);
+}
+
+// ---- GGUF Q4_K / Q8_0 in the tiled layouts ------------------------------------------------------
+
+// Device super-blocks {16-byte header, 8 x 16 bytes of nibbles} -> tiled stages; one thread per 16-byte unit.
+__global__ void q4k_tile_kernel(const unsigned char* __restrict__ blocks, unsigned char* __restrict__ tiled, int out_dim,
+                                int ntiles, int nchunks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nstages = (size_t)ntiles * nchunks;
+  if (idx >= nstages * (128 * 9)) return;
+  size_t stg = idx / (128 * 9);
+  int rem = (int)(idx - stg * (128 * 9));
+  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
+  int r = rem / 9, u = rem - r * 9;
+  int row = tile * 128 + r;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  unsigned char* dst = tiled + stg * Fmt<FMT_Q4K>::kStageBytes;
+  const unsigned char* src = blocks + ((size_t)row * nchunks + chunk) * 144;
+  if (u < 8) {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(src + 16 + 16 * u);
+    *reinterpret_cast<uint4*>(dst + r * 128 + ((u ^ (r & 7)) << 4)) = v;
+  } else {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(src);
+    *reinterpret_cast<uint4*>(dst + Fmt<FMT_Q4K>::kStageWBytes + r * 16) = v;
+  }
+}
+
+// Byte plane (q + 128) and f16 scales -> tiled stages of signed bytes; one thread per 16-byte half block.
+__global__ void q80_tile_kernel(const unsigned char* __restrict__ plane, const uint16_t* __restrict__ d16,
+                                unsigned char* __restrict__ tiled, int out_dim, int in_dim, int ntiles, int nchunks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nstages = (size_t)ntiles * nchunks;
+  if (idx >= nstages * (128 * 16)) return;
+  size_t stg = idx / (128 * 16);
+  int rem = (int)(idx - stg * (128 * 16));
+  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
+  int r = rem >> 4, hb = rem & 15, step = hb >> 1, half = hb & 1;
+  int row = tile * 128 + r;
+  unsigned char* dst = tiled + stg * Fmt<FMT_Q80>::kStageBytes;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (row < out_dim) {
+    v = *reinterpret_cast<const uint4*>(plane + (size_t)row * in_dim + chunk * 256 + step * 32 + half * 16);
+    v.x ^= 0x80808080u;
+    v.y ^= 0x80808080u;
+    v.z ^= 0x80808080u;
+    v.w ^= 0x80808080u;
+  }
+  *reinterpret_cast<uint4*>(dst + step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16) = v;
+  if (half == 0) {
+    uint16_t d = row < out_dim ? d16[(size_t)row * (in_dim / 32) + chunk * 8 + step] : (uint16_t)0;
+    *reinterpret_cast<uint16_t*>(dst + Fmt<FMT_Q80>::kStageWBytes + r * 16 + step * 2) = d;
+  }
+}
+
+// dequantRowQ4KTo / dequantRowQ8_0To from the tiled layouts (loader/gguf/quant_matrix.go:138-158, :281-329).
+__global__ void q4k_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, float* __restrict__ out, int out_dim,
+                                         int in_dim, int nchunks) {
+  size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // 32-element unit of the row-major result
+  size_t units_per_row = in_dim / 32;
+  if (u >= (size_t)out_dim * units_per_row) return;
+  int row = (int)(u / units_per_row), unit = (int)(u - (size_t)row * units_per_row);
+  int chunk = unit >> 3, sblk = unit & 7, r = row & 127;
+  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * Fmt<FMT_Q4K>::kStageBytes;
+  uint4 h = *reinterpret_cast<const uint4*>(stg + Fmt<FMT_Q4K>::kStageWBytes + r * 16);
+  uint4 q = *reinterpret_cast<const uint4*>(stg + r * 128 + ((sblk ^ (r & 7)) << 4));
+  int bit = 12 * sblk, wi = bit >> 5, sh = bit & 31;
+  uint32_t lo = wi == 0 ? h.y : wi == 1 ? h.z : h.w, hi = wi == 0 ? h.z : wi == 1 ? h.w : 0u;
+  uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+  float sd = __fmul_rn((float)(f & 63u), __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu))));
+  float md = __fmul_rn((float)(f >> 6), __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
+  float4* o = reinterpret_cast<float4*>(out + u * 32);
+  uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fsub_rn(__fmul_rn(sd, (float)((ws[k] >> (4 * e)) & 0xF)), md);
+    o[2 * k] = make_float4(v[0], v[1], v[2], v[3]);
+    o[2 * k + 1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+__global__ void q80_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, float* __restrict__ out, int out_dim,
+                                         int in_dim, int nchunks) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)out_dim * in_dim) return;
+  int row = (int)(i / in_dim), col = (int)(i - (size_t)row * in_dim);
+  int chunk = col >> 8, k = col & 255, step = k >> 5, half = (k >> 4) & 1, r = row & 127;
+  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * Fmt<FMT_Q80>::kStageBytes;
+  signed char q = (signed char)stg[step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16 + (k & 15)];
+  uint16_t d = *reinterpret_cast<const uint16_t*>(stg + Fmt<FMT_Q80>::kStageWBytes + r * 16 + step * 2);
+  out[i] = __fmul_rn(__half2float(__ushort_as_half(d)), (float)q);
+}
+
+bool gguf_mma_supported(int qtype, int in_dim) {
+  return (qtype == GOPH_GGUF_Q4_K || qtype == GOPH_GGUF_Q8_0) && in_dim % kChunkK == 0 && in_dim <= kMaxPrepIn;
+}
+
+int gguf_mma_make_tiled(goph_gguf_matrix* m) {
+  const int ntiles = (m->out_dim + kTileRows - 1) / kTileRows, nchunks = m->in_dim / kChunkK;
+  const bool q4 = m->qtype == GOPH_GGUF_Q4_K;
+  const size_t stage = q4 ? Fmt<FMT_Q4K>::kStageBytes : Fmt<FMT_Q80>::kStageBytes;
+  const size_t bytes = (size_t)ntiles * nchunks * stage;
+  unsigned char* t = nullptr;
+  GOPH_CUDA(cudaMalloc(&t, bytes));
+  if (q4) {
+    size_t threads = (size_t)ntiles * nchunks * 128 * 9;
+    q4k_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, t, m->out_dim, ntiles, nchunks);
+  } else {
+    size_t threads = (size_t)ntiles * nchunks * 128 * 16;
+    q80_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, m->d16, t, m->out_dim, m->in_dim, ntiles, nchunks);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    cudaFree(t);
+    return fail_cuda(e, "gguf tile kernel");
+  }
+  m->tiled = t;
+  m->bytes = bytes;
+  return GOPH_OK;
+}
+
+int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream) {
+  if (!m->tiled) return fail(GOPH_E_UNSUPPORTED, "matrix is not in the tiled layout");
+  TiledDesc d{m->tiled, m->device, m->out_dim, m->in_dim};
+  return m->qtype == GOPH_GGUF_Q4_K ? tiled_launch<FMT_Q4K>(d, out, x, batch, digits, stream, false)
+                                    : tiled_launch<FMT_Q80>(d, out, x, batch, digits, stream, false);
+}
+
+int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream) {
+  const int nchunks = m->in_dim / kChunkK;
+  if (m->qtype == GOPH_GGUF_Q4_K) {
+    size_t units = (size_t)m->out_dim * (m->in_dim / 32);
+    q4k_dequant_tiled_kernel<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);
+  } else {
+    size_t n = (size_t)m->out_dim * m->in_dim;
+    q80_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);
+  }
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
 
 // ---- GEMV without any allocation ---------------------------------------------------------------
 // Some callers must not allocate device memory when they run a product: a serving loop that has

@@ -31,4 +31,11 @@ int mlx_mma_status(int device);
 // Copies the 32 cycle counters CTA 0 wrote when option mlx_probe is on (tuning aid).
 int mlx_mma_probe(int device, long long* out32);
 
+// GGUF Q4_K / Q8_0 on the same kernel.  make_tiled builds m->tiled from the matrix's device
+// buffers (which the caller then frees); dequant reproduces dequantRowQ4KTo / dequantRowQ8_0To.
+bool gguf_mma_supported(int qtype, int in_dim);
+int gguf_mma_make_tiled(goph_gguf_matrix* m);
+int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream);
+int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream);
+
 }  // namespace goph

@@ -73,6 +73,10 @@ int goph_sm_count(int device);
  *                 scales and biases; the row-major layout feeds the CUDA-core kernels.  0 (default):
  *                 tiled for matrices of 8 Mi weights or more, row-major below; 1: always row-major;
  *                 2: tiled whenever the shape allows
+ *   "gguf_layout" the same choice for goph_gguf_upload (Q4_K and Q8_0; in_dim a multiple of 256):
+ *                 0 (default) tensor-core layout from 8 Mi weights, 1 always the streaming layout,
+ *                 2 tensor-core layout whenever the shape allows.  "mlx_digits" and "mlx_splits"
+ *                 apply to these products as well
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)

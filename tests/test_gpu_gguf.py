@@ -60,6 +60,7 @@ def test_q8_0_reference_formula_blocks(gpu, pkg):
 @pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (4096, 4096), (259, 2816), (2048, 768)])
 def test_gemv_parity(gpu, pkg, qtype, out_dim, in_dim, rows):
     gpu.SetOption("gguf_rows", rows)
+    gpu.SetOption("gguf_layout", 1)   # the CUDA-core streaming kernels
     try:
         raw = make(pkg, qtype, ("gemv", out_dim, in_dim), out_dim, in_dim)
         m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
@@ -75,6 +76,7 @@ def test_gemv_parity(gpu, pkg, qtype, out_dim, in_dim, rows):
             t.Free()
     finally:
         gpu.SetOption("gguf_rows", 0)
+        gpu.SetOption("gguf_layout", 0)
 
 
 @pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
@@ -140,3 +142,133 @@ def test_full_size_against_device_dequant(gpu, pkg, qtype, out_dim, in_dim):
         got = deq[r0 * in_dim:(r0 + 8) * in_dim].cpu().numpy()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     m.Free()
+
+
+# ---- the tensor-core layout (gguf_layout=2: every matrix whose in_dim is a multiple of 256) ----
+
+@pytest.fixture
+def tiled_layout(gpu):
+    gpu.SetOption("gguf_layout", 2)
+    yield
+    gpu.SetOption("gguf_layout", 0)
+    assert gpu.KernelStatus() == 0   # no bounded wait gave up
+
+
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("out_dim,in_dim", [(128, 256), (64, 4096), (300, 512), (259, 2816)])
+def test_tiled_dequant_bit_exact(gpu, pkg, tiled_layout, qtype, out_dim, in_dim):
+    raw = make(pkg, qtype, "deq-t", out_dim, in_dim)
+    m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+    padded = (out_dim + 127) // 128 * 128
+    assert m.ResidentBytes() == raw.size // out_dim * padded   # file bytes per row, rows padded to the 128-row tile
+    out = out_with_canary(gpu, out_dim * in_dim)
+    m.Dequant(out)
+    gpu.Sync()
+    got = read_and_check_canary(out, out_dim * in_dim)
+    want = orc.gguf_dequant(raw, qtype, in_dim, out_dim, nthreads=8).reshape(-1)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    m.Free(); out.Free()
+
+
+@pytest.mark.parametrize("digits", [4, 3])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (4096, 4096), (259, 2816), (2048, 768), (64, 256), (19000, 1024)])
+def test_tiled_gemv_parity(gpu, pkg, tiled_layout, qtype, out_dim, in_dim, digits):
+    gpu.SetOption("mlx_digits", digits)
+    try:
+        raw = make(pkg, qtype, ("gemv-t", out_dim, in_dim), out_dim, in_dim)
+        m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+        # three digits carry 20 bits under the block maximum: meant for bf16-valued activations
+        x = pkg.synth.activations(("gemv-t", in_dim), in_dim, bf16=(digits == 3))
+        xo = gpu.from_numpy(x)
+        out = out_with_canary(gpu, out_dim)
+        m.ProjectBatchToBuffer(out, xo, 1)
+        gpu.Sync()
+        got = read_and_check_canary(out, out_dim)
+        want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, nthreads=8)
+        assert pkg.synth.rel_err(got, want) <= TOL, pkg.synth.rel_err(got, want)
+        out2 = out_with_canary(gpu, out_dim)
+        m.ProjectBatchToBuffer(out2, xo, 1)
+        gpu.Sync()
+        assert np.array_equal(read_and_check_canary(out2, out_dim).view(np.uint32), got.view(np.uint32))  # run-to-run identical
+        for t in (m, xo, out, out2):
+            t.Free()
+    finally:
+        gpu.SetOption("mlx_digits", 4)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 16])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+def test_tiled_k_splits(gpu, pkg, tiled_layout, qtype, splits):
+    out_dim, in_dim = 700, 4096
+    gpu.SetOption("mlx_splits", splits)
+    try:
+        raw = make(pkg, qtype, "split-t", out_dim, in_dim)
+        m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+        x = pkg.synth.activations("split-t", in_dim, bf16=False)
+        xo = gpu.from_numpy(x)
+        out = out_with_canary(gpu, out_dim)
+        m.ProjectBatchToBuffer(out, xo, 1)
+        gpu.Sync()
+        want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, nthreads=8)
+        assert pkg.synth.rel_err(read_and_check_canary(out, out_dim), want) <= TOL
+        for t in (m, xo, out):
+            t.Free()
+    finally:
+        gpu.SetOption("mlx_splits", 0)
+
+
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("batch", [2, 3, 4, 5, 8, 11])
+def test_tiled_batched_projection(gpu, pkg, tiled_layout, qtype, batch):
+    out_dim, in_dim = 777, 2048
+    raw = make(pkg, qtype, "batch-t", out_dim, in_dim)
+    m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+    x = pkg.synth.activations(("batch-t", batch), batch * in_dim, bf16=False)
+    xo = gpu.from_numpy(x)
+    out = out_with_canary(gpu, batch * out_dim)
+    m.ProjectBatchToBuffer(out, xo, batch)
+    gpu.Sync()
+    got = read_and_check_canary(out, batch * out_dim)
+    want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, batch, nthreads=8)
+    assert pkg.synth.rel_err(got, want) <= TOL
+    for t in (m, xo, out):
+        t.Free()
+
+
+def test_tiled_wide_dynamic_range(gpu, pkg, tiled_layout):
+    # activations spanning 2^-20 .. 2^10 inside one block: the integer digits keep 26 bits under the block maximum
+    out_dim, in_dim = 256, 1024
+    rng = pkg.synth.rng("range-t")
+    x = (rng.standard_normal(in_dim) * np.exp2(rng.integers(-20, 11, in_dim))).astype(F)
+    for qtype in (Q8_0, Q4_K):
+        raw = make(pkg, qtype, "range-t", out_dim, in_dim)
+        m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+        xo = gpu.from_numpy(x)
+        out = gpu.Malloc(out_dim)
+        m.ProjectBatchToBuffer(out, xo, 1)
+        gpu.Sync()
+        want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim)
+        assert pkg.synth.rel_err(out.Download(), want) <= TOL
+        for t in (m, xo, out):
+            t.Free()
+
+
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+def test_tiled_product_while_l2_writes_back(gpu, pkg, qtype):
+    """Loads arrive late and out of order when the L2 is full of dirty lines (here: a 600 MB memset
+    right before the launch); the pipeline's waits must hold under that timing too."""
+    out_dim, in_dim = 128256, 4096
+    raw = make(pkg, qtype, ("wb", out_dim), out_dim, in_dim)
+    x = pkg.synth.activations(("wb", in_dim), in_dim, bf16=False)
+    want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, nthreads=16)
+    m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+    xo, out, junk = gpu.from_numpy(x), gpu.Malloc(out_dim), gpu.Malloc(150_000_000)
+    for _ in range(4):
+        junk.Zero()
+        m.ProjectBatchToBuffer(out, xo, 1)
+        gpu.Sync()
+        assert pkg.synth.rel_err(out.Download(), want) <= TOL
+    assert gpu.KernelStatus() == 0
+    for t in (m, xo, out, junk):
+        t.Free()

@@ -304,3 +304,20 @@ def test_full_size_against_device_dequant(gpu, pkg, out_dim, in_dim):
     lin = out[:out_dim] + out[out_dim:]
     assert pkg.synth.rel_err(o1.cpu().numpy(), lin.cpu().numpy()) <= 1e-3
     h.Free()
+
+
+def test_tensor_core_product_while_l2_writes_back(gpu, pkg):
+    """Loads arrive late and out of order when the L2 is full of dirty lines (a 600 MB memset right
+    before each launch); the pipeline's waits must hold under that timing too."""
+    out_dim, in_dim = 128256, 4096
+    h, (w, s, b) = upload(gpu, pkg.synth, ("wb", out_dim, in_dim), out_dim, in_dim)
+    x = pkg.synth.activations(("wb", in_dim), in_dim)
+    want = orc.mlx_gemv(x, w, s, b, out_dim, in_dim, 64, nthreads=16)
+    xo, out, junk = gpu.from_numpy(x), gpu.Malloc(out_dim), gpu.Malloc(150_000_000)
+    for _ in range(4):
+        junk.Zero()
+        gpu.GemvMLX(out, xo, h)
+        gpu.Sync()
+        assert pkg.synth.rel_err(out.Download(), want) <= TOL
+    for t in (h, xo, out, junk):
+        t.Free()
