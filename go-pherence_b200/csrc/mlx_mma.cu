@@ -70,7 +70,7 @@ constexpr int kStageWBytes = Fmt<FMT_MLX4>::kStageWBytes;
 constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
 constexpr long long kTimeoutCycles = 4000000000LL;
 
-constexpr int kConvWarps = 8, kEpiWarps = 4;
+constexpr int kConvWarps = 8, kEpiWarps = 8;  // two epilogue warps per TMEM lane quarter: each takes half of a stage's accumulator blocks
 constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
 constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
 constexpr int kMmaWarps = 2;  // two issuing threads take alternate stages so one's waits hide behind the other's MMAs
@@ -207,7 +207,7 @@ struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
   static constexpr int kStage = Fmt<FMT>::kStageBytes + kBTileBytes;
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim) {
-    return (size_t)stages * kStage + (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512;
+    return (size_t)stages * kStage + (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
   }
 };
 
@@ -323,6 +323,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   // bars: full[S], empty[S], a_ready[NB], mma_done[NB], d_free[NB]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 3 * NB);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* pair = reinterpret_cast<float*>(tmem_holder + 4);  // [MB][128]: the second epilogue half's sums of an item
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
@@ -332,10 +333,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
       // converters (conversion formats), epilogue (scale data), MMA commit (B tile, A read from the stage)
-      mbar_init(empty0 + 8 * s, (F::kConv ? kConvThreads : 0) + kEpiThreads + 1);
+      mbar_init(empty0 + 8 * s, (F::kConv ? kConvThreads / 2 : 0) + kEpiThreads + 1);
     }
     for (int b = 0; b < NB; ++b) {
-      mbar_init(aready0 + 8 * b, kConvThreads);
+      mbar_init(aready0 + 8 * b, kConvThreads / 2);
       mbar_init(mdone0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiThreads);
     }
@@ -466,15 +467,20 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     // nothing to convert: the MMA reads the stage as it lies
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------------ converters
-    // Thread = (row r of the tile, half h of the stage's eight 16-byte units).
-    const int q4 = warp & 3, h = warp >> 2;
+    // Two groups of four warps take alternate stages, so two stages are being converted at any
+    // time and one group's barrier waits and TMEM-store latency hide behind the other's work.
+    // Thread = row r of the tile: the stage's eight 16-byte units of that row.
+    const int q4 = warp & 3, grp = warp >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     const bool pr = a.probe && blockIdx.x == 0 && tid == 0;
     long long w0 = 0, w1 = 0, tstart = clock64();
-    for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
+    if (grp == 1 && sw.live(a)) sw.next(a);
+    for (int i = grp; sw.live(a) && ok; i += 2) {
       int b = i % NB, slot = i % S;
       if (i >= NB) ok = __all_sync(0xffffffffu, mbar_wait_t(mdone0 + 8 * b, ((i - NB) / NB) & 1, a.status, 3, pr, w0));
+      // stage i-1 first: see the note at the MMA issuers' wait (a group skips every other stage)
+      if (ok && i >= 1) ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 10, pr, w1));
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 4, pr, w1));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -482,31 +488,30 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       if (a.dbg & 8) {
         mbar_arrive(aready0 + 8 * b);
         mbar_arrive(empty0 + 8 * slot);
-        continue;
-      }
-      // ---- this row's half of the stage: 128 nibbles -> 128 bytes -> 32 TMEM columns ----
-      uint4 qv[4];
+      } else {
+        // ---- this row of the stage: 256 nibbles -> 256 bytes -> 64 TMEM columns ----
+        uint4 qv[8];
 #pragma unroll
-      for (int uu = 0; uu < 4; ++uu) {
-        int u = h * 4 + uu;
-        qv[uu] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
-      }
+        for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
 #pragma unroll
-      for (int uu = 0; uu < 4; ++uu) {
-        uint32_t ws[4] = {qv[uu].x, qv[uu].y, qv[uu].z, qv[uu].w};
-        uint32_t regs[8];
+        for (int u = 0; u < 8; ++u) {
+          uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+          uint32_t regs[8];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
-          regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
+          for (int w = 0; w < 4; ++w) {
+            regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
+            regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
+          }
+          if (!(a.dbg & 1)) tmem_st8(tmemA0 + lane_base + b * 64 + u * 8, regs);
+          else if (regs[0] == 0x12345678u && regs[7] == 1u) *last_flag = 1;
         }
-        if (!(a.dbg & 1)) tmem_st8(tmemA0 + lane_base + b * 64 + (h * 4 + uu) * 8, regs);
-        else if (regs[0] == 0x12345678u && regs[7] == 1u) *last_flag = 1;
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(aready0 + 8 * b);
+        mbar_arrive(empty0 + 8 * slot);
       }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(aready0 + 8 * b);
-      mbar_arrive(empty0 + 8 * slot);
+      sw.next(a);
+      if (sw.live(a)) sw.next(a);
     }
     if (pr) {
       a.probe[16] = clock64() - tstart;
@@ -515,7 +520,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int q4 = warp & 3;
+    // Two warps per TMEM lane quarter: `half` 0 takes the first half of a stage's accumulator
+    // blocks, `half` 1 the second; each keeps its own running sums and the halves are added when
+    // an item (tile, K range) ends.
+    const int q4 = warp & 3, half = (warp - kConvWarps) >> 2;
     const int r = q4 * 32 + lane;  // row of the tile == TMEM lane
     const int et = tid - kConvThreads;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
@@ -527,6 +535,9 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     const bool pr = a.probe && blockIdx.x == 0 && et == 0;
     long long w0 = 0, w1 = 0, tstart = clock64();
+    constexpr int kHB = kBlocks / 2;                        // blocks of this half
+    constexpr int kSub = kHB * N <= 64 ? kHB : 64 / N;      // blocks per pass (at most 64 columns in registers)
+    constexpr int NLD = kSub * N / 16;                      // 16-column loads per pass
     for (int i = 0; sw.live(a) && ok; ++i) {
       int b = i % NB, slot = i % S;
       ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 6, pr, w0));
@@ -538,26 +549,15 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (a.dbg & 16) {
-        mbar_arrive(dfree0 + 8 * b);
-        acc[0] += __uint_as_float(mv.x);
-        const bool done16 = sw.last_chunk();
-        const int row16 = sw.tile * kTileRows + r;
-        sw.next(a);
-        if (done16 && row16 < a.out_dim) a.out[row16] = acc[0];
-        continue;
-      }
       const uint32_t meta[4] = {mv.x, mv.y, mv.z, mv.w};
       const int gbase = sw.c * kBlocks;
-      // four accumulator blocks (4N adjacent columns) at a time (register budget); the buffer is
-      // released after the last loads
-      constexpr int NLD = 4 * N / 16;
 #pragma unroll
-      for (int hb = 0; hb < kBlocks / 4; ++hb) {
+      for (int sub = 0; sub < kHB / kSub; ++sub) {
+        const int blk0 = half * kHB + sub * kSub;  // first block of this pass
         uint32_t t[NLD][16];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + hb * 4 * N + l * 16, t[l]);
+          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + blk0 * N + l * 16, t[l]);
           else {
 #pragma unroll
             for (int z = 0; z < 16; ++z) t[l][z] = meta[l & 3] + z;
@@ -565,18 +565,19 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         }
 #pragma unroll
         for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[l]);
-        if (hb == kBlocks / 4 - 1) {
+        if (sub == kHB / kSub - 1) {
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           mbar_arrive(dfree0 + 8 * b);
         }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int blk = hb * 4 + g;
+        for (int g = 0; g < kSub; ++g) {
+          const int blk = blk0 + g;
           // the block's multiplier of the integer dot and of the block's sum of x
           float sc, bi;
           if (FMT == FMT_MLX4) {  // {scale, bias} bf16 pair of the 64-element group
-            sc = __uint_as_float(meta[g] << 16);
-            bi = __uint_as_float(meta[g] & 0xFFFF0000u);
+            const uint32_t mw = blk == 0 ? meta[0] : blk == 1 ? meta[1] : blk == 2 ? meta[2] : meta[3];
+            sc = __uint_as_float(mw << 16);
+            bi = __uint_as_float(mw & 0xFFFF0000u);
           } else if (FMT == FMT_Q4K) {  // (sc*d) and -(m*dmin), each rounded to f32 as dequantRowQ4KTo does
             const int bit = 12 * blk, wi = bit >> 5, sh = bit & 31;
             const uint32_t lo = wi == 0 ? meta[1] : wi == 1 ? meta[2] : meta[3];
@@ -585,7 +586,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
             sc = __fmul_rn((float)(f & 63u), __half2float(__ushort_as_half((unsigned short)(meta[0] & 0xFFFFu))));
             bi = -__fmul_rn((float)(f >> 6), __half2float(__ushort_as_half((unsigned short)(meta[0] >> 16))));
           } else {  // f16 block scale
-            sc = __half2float(__ushort_as_half((unsigned short)((meta[blk >> 1] >> (16 * (blk & 1))) & 0xFFFFu)));
+            const uint32_t mw = (blk >> 1) == 0 ? meta[0] : (blk >> 1) == 1 ? meta[1] : (blk >> 1) == 2 ? meta[2] : meta[3];
+            sc = __half2float(__ushort_as_half((unsigned short)((mw >> (16 * (blk & 1))) & 0xFFFFu)));
             bi = 0.f;
           }
 #pragma unroll
@@ -611,27 +613,45 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       const int tile = sw.tile, split = sw.split;
       sw.next(a);
       if (!item_done) continue;
+      // ---- the item is complete: add the two halves' sums (half 1 -> shared memory -> half 0) ----
+      if (half == 1) {
+#pragma unroll
+        for (int m = 0; m < MB; ++m) {
+          pair[m * kTileRows + r] = acc[m];
+          acc[m] = 0.f;
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      if (half == 0) {
+#pragma unroll
+        for (int m = 0; m < MB; ++m) acc[m] += pair[m * kTileRows + r];
+      }
       const int row = tile * kTileRows + r;
       if (a.splits == 1) {
+        if (half == 0) {
 #pragma unroll
-        for (int m = 0; m < MB; ++m) {
-          if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = acc[m];
-          acc[m] = 0.f;
+          for (int m = 0; m < MB; ++m) {
+            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = acc[m];
+            acc[m] = 0.f;
+          }
         }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // pair is free for the next item
       } else {
-        // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds
-        // the partials in split order (so the result does not depend on arrival order) and stores.
-        float* part = a.scratch + ((size_t)tile * a.splits + split) * (MB * kTileRows);
+        // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
+        // partials in split order (so the result does not depend on arrival order) and stores.
+        if (half == 0) {
+          float* part = a.scratch + ((size_t)tile * a.splits + split) * (MB * kTileRows);
 #pragma unroll
-        for (int m = 0; m < MB; ++m) {
-          part[m * kTileRows + r] = acc[m];
-          acc[m] = 0.f;
+          for (int m = 0; m < MB; ++m) {
+            part[m * kTileRows + r] = acc[m];
+            acc[m] = 0.f;
+          }
+          __threadfence();
         }
-        __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         if (et == 0) *last_flag = (atomicAdd(a.counters + tile, 1u) == (unsigned)a.splits - 1) ? 1 : 0;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        if (*last_flag) {
+        if (*last_flag && half == 0) {
           __threadfence();
           const float* base = a.scratch + (size_t)tile * a.splits * (MB * kTileRows);
 #pragma unroll
