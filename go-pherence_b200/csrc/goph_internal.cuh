@@ -55,6 +55,7 @@ struct Options {
   int mlx_dbg = 0;     // tuning aid: leaves out parts of the tensor-core kernel (results are then wrong)
   int mlx_probe = 0;   // 1: CTA 0 of the tensor-core kernel records per-role wait cycles
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
+  int mlx_fuse = 0;    // 1: narrow tensor-core launches make their activation digits themselves (one launch, slower today)
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
   int mlx_unpack = 0;
   int gguf_layout = 0; // as mlx_layout, for Q4_K / Q8_0 matrices

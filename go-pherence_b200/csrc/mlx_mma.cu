@@ -202,12 +202,15 @@ struct MmaArgs {
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
 // 2 B tiles (8 K-steps x N rows x 32 bytes), per-(row,group) tables {sum x, 2^(E-26), 2^(26-E)},
 // mbarriers, the TMEM base holder.
-template <int N, int FMT = FMT_MLX4>
+// FUSED: the activation digits are made by the kernel itself and stay resident for all chunks
+// (in_dim / 256 B tiles after the ring) instead of travelling with every stage.
+template <int N, int FMT = FMT_MLX4, bool FUSED = false>
 struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
-  static constexpr int kStage = Fmt<FMT>::kStageBytes + kBTileBytes;
+  static constexpr int kStage = Fmt<FMT>::kStageBytes + (FUSED ? 0 : kBTileBytes);
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim) {
-    return (size_t)stages * kStage + (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
+    return (size_t)stages * kStage + (FUSED ? (size_t)(in_dim / kChunkK) * kBTileBytes : 0) +
+           (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
   }
 };
 
@@ -296,9 +299,63 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
   }
 }
 
+// The same preparation done by a CTA of the product kernel for itself (all warps, before the
+// pipeline starts): digits into the resident B tiles in shared memory, sums and scales into the
+// tables the epilogue reads.  A warp takes one 64-element group at a time, lane l the elements l
+// and l + 32; the arithmetic and its order are those of mlx_prep_x_kernel.
+template <int DIGITS, bool G32, bool NATURAL, int N>
+__device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int batch, int in_dim, unsigned char* bres,
+                                              float* xsum, float* xfs, int warp, int lane, int nwarps) {
+  constexpr int QBITS = DIGITS == 4 ? 26 : 19;
+  const int groups = in_dim / 64;
+  const int ntab = G32 ? 2 * groups : groups;
+  for (int gi = warp; gi < batch * groups; gi += nwarps) {
+    const int m = gi / groups, g = gi - m * groups;
+    const float* xp = x + (size_t)m * in_dim + g * 64;
+    float v[2] = {xp[lane], xp[32 + lane]};
+    float s[2] = {v[0], v[1]}, mx[2] = {fabsf(v[0]), fabsf(v[1])};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        s[h] += __shfl_xor_sync(0xffffffffu, s[h], o);
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], o));
+      }
+    }
+    if (!G32) {
+      s[0] = s[1] = s[0] + s[1];
+      mx[0] = mx[1] = fmaxf(mx[0], mx[1]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int e = (int)((__float_as_uint(mx[h]) >> 23) & 0xFF);
+      if (e < QBITS + 2) e = QBITS + 2;
+      if (e > 254) e = 254;
+      if (lane == 0 && (G32 || h == 0)) {
+        const int ti = m * ntab + (G32 ? 2 * g + h : g);
+        xsum[ti] = s[h];
+        xfs[ti] = __uint_as_float((uint32_t)(e - 126 - QBITS + 127) << 23);
+      }
+      const float fi = __uint_as_float((uint32_t)(QBITS - (e - 126) + 127) << 23);
+      int q = __float2int_rn(v[h] * fi);
+      const int k = (g & 3) * 64 + h * 32 + lane;  // element within the 256-element chunk
+      const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
+      const int pos = NATURAL ? (k & 31) : 8 * w + 4 * (j & 1) + (j >> 1);
+      unsigned char* base = bres + (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
+#pragma unroll
+      for (int d = 0; d < DIGITS; ++d) {
+        int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
+        q = (q - dig) >> 7;
+        const int n = m * DIGITS + d;
+        base[(n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
+      }
+    }
+  }
+}
+
 // N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
 // MB: activation rows the instantiation can take (MB * DIGITS <= N).
-template <int N, int DIGITS, int MB, int FMT = FMT_MLX4>
+template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false>
 __global__ void __launch_bounds__(kThreads, 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
@@ -310,14 +367,16 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   constexpr int NB = (kACols + kBlocks * N) * 4 <= 512 ? 4 : 2;
   static_assert(NB * (kACols + kBlocks * N) <= 512, "TMEM plan");
   constexpr uint32_t kCols = 512;
-  constexpr int kStage = MmaSmem<N, FMT>::kStage;
+  constexpr int kStage = MmaSmem<N, FMT, FUSED>::kStage;
   constexpr int kStageBytes = F::kStageBytes, kStageWBytes = F::kStageWBytes;
+  constexpr int kBTileBytes = MmaSmem<N, FMT, FUSED>::kBTileBytes;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
   unsigned char* ring = smem;
   const int groups = a.in_dim / F::kGroup;
-  float* xsum = reinterpret_cast<float*>(ring + (size_t)S * kStage);  // [batch][groups] sum of x
+  unsigned char* bres = ring + (size_t)S * kStage;  // FUSED: resident B tiles of every chunk
+  float* xsum = reinterpret_cast<float*>(bres + (FUSED ? (size_t)a.nchunks * kBTileBytes : 0));  // [batch][groups] sum of x
   float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
   uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
   // bars: full[S], empty[S], a_ready[NB], mma_done[NB], d_free[NB]
@@ -356,6 +415,23 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   bool ok = true;
   StageWalk sw(a);
 
+  if (FUSED) {
+    // The weights do not depend on the kernel in front: the producer fills the ring, then every
+    // warp helps to turn the activations into digits, sums and scales.
+    if (warp == kWarpTMA && lane == 0) {
+      StageWalk sw0 = sw;
+      for (int i = 0; i < S && sw0.live(a); ++i, sw0.next(a)) {
+        mbar_expect_tx(full0 + 8 * i, kStageBytes);
+        bulk_load_1d(smem_u32(ring + (size_t)i * kStage), a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes,
+                     kStageBytes, full0 + 8 * i);
+      }
+    }
+    pdl_wait();
+    prep_x_in_cta<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80, N>(a.x, a.batch, a.in_dim, bres, xsum, xfs, warp, lane, kThreads / 32);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the MMA reads the digits through the async proxy
+    __syncthreads();
+  }
+
   if (warp == kWarpTMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -365,23 +441,20 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       // The weights do not depend on the kernel in front: fill the ring with them first, then
       // wait for the activation digits and add the B tiles of those stages.
       int i = 0;
-      {
+      if (FUSED) {
+        for (; i < S && sw.live(a); ++i) sw.next(a);  // filled before the activations were prepared
+        nst = i;
+      } else {
         StageWalk sw0 = sw;
         for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
           uint32_t dst = smem_u32(ring + (size_t)i * kStage);
           mbar_expect_tx(full0 + 8 * i, kStage);
-          const unsigned char* src = a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes;
-          if (a.dbg & 128) {
-            bulk_load_1d(dst, src, 16384, full0 + 8 * i);
-            bulk_load_1d(dst + 16384, src + 16384, kStageBytes - 16384, full0 + 8 * i);
-          } else {
-            bulk_load_1d(dst, src, kStageBytes, full0 + 8 * i);
-          }
+          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, kStageBytes, full0 + 8 * i);
         }
         pdl_wait();
         for (int j = 0; j < i; ++j, sw.next(a))
-          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N, FMT>::kBTileBytes,
-                       MmaSmem<N, FMT>::kBTileBytes, full0 + 8 * j);
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes,
+                       kBTileBytes, full0 + 8 * j);
         nst = i;
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
@@ -392,14 +465,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
         mbar_expect_tx(full0 + 8 * slot, kStage);
         const unsigned char* src = a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes;
-        if (a.dbg & 128) {
-          bulk_load_1d(dst, src, 16384, full0 + 8 * slot);
-          bulk_load_1d(dst + 16384, src + 16384, kStageBytes - 16384, full0 + 8 * slot);
-        } else {
-          bulk_load_1d(dst, src, kStageBytes, full0 + 8 * slot);
-        }
-        bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * MmaSmem<N, FMT>::kBTileBytes, MmaSmem<N, FMT>::kBTileBytes,
-                     full0 + 8 * slot);
+        bulk_load_1d(dst, src, kStageBytes, full0 + 8 * slot);
+        if (!FUSED) bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes, kBTileBytes, full0 + 8 * slot);
       }
       if (pr) {
         a.probe[0] = clock64() - tstart;
@@ -434,8 +501,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         if (ok && i >= NB) ok = mbar_wait_t(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5, pr, w1);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (a.dbg & 256) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage + kStageBytes);
+        const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)sw.c * kBTileBytes) : smem_u32(ring + (size_t)slot * kStage + kStageBytes);
         const uint32_t dcol = tmemD0 + b * (kBlocks * N), acol = tmemA0 + b * kACols;
         if (!(a.dbg & 2)) {
 #pragma unroll
@@ -530,9 +596,11 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     float acc[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-    pdl_wait();  // the tables come from the preparation kernel in front
-    for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
-    asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+    if (!FUSED) {
+      pdl_wait();  // the tables come from the preparation kernel in front
+      for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+    }
     const bool pr = a.probe && blockIdx.x == 0 && et == 0;
     long long w0 = 0, w1 = 0, tstart = clock64();
     constexpr int kHB = kBlocks / 2;                        // blocks of this half
@@ -793,15 +861,13 @@ struct TiledDesc {
   int device, out_dim, in_dim;
 };
 
-template <int N, int DIGITS, int MB, int FMT>
-static int launch_one(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep) {
+constexpr size_t kMmaSmemBudget = 222 * 1024;  // of the 227 KiB a CTA may have
+constexpr int kMaxStages = 10;
+
+template <int N, int DIGITS, int MB, int FMT, bool FUSED>
+static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep, int stages) {
   MmaArgs a = a0;
   DeviceState& st = device_state(w.device);
-  size_t fixed = MmaSmem<N, FMT>::bytes(0, a.batch, a.in_dim);
-  int stages = (int)(((size_t)kSmemBudget - fixed) / MmaSmem<N, FMT>::kStage);
-  if (stages > 8) stages = 8;
-  if (stages < 3)
-    return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
   a.stages = stages;
   // K split: enough (tile, split) items to occupy the SMs, bounded by the chunks and the scratch
   int splits = 1;
@@ -814,9 +880,8 @@ static int launch_one(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream
   while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
   a.splits = splits;
   a.items = a.ntiles * splits;
-  size_t smem = MmaSmem<N, FMT>::bytes(stages, a.batch, a.in_dim);
+  size_t smem = MmaSmem<N, FMT, FUSED>::bytes(stages, a.batch, a.in_dim);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
-  // activations -> digits, sums and scales, once per launch
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
@@ -825,12 +890,14 @@ static int launch_one(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream
   cfg.stream = stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
-  cfg.blockDim = dim3(64);
-  if (prep)
+  if (!FUSED && prep) {
+    // activations -> digits, sums and scales, once per launch
+    cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
+    cfg.blockDim = dim3(64);
     GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80>, a.x,
                                  const_cast<unsigned char*>(a.xb), const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
-  auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT>;
+  }
+  auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT, FUSED>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
   cfg.gridDim = dim3(grid);
@@ -838,6 +905,27 @@ static int launch_one(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream
   cfg.dynamicSmemBytes = smem;
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
+}
+
+template <int N, int DIGITS, int MB, int FMT>
+static int launch_one(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
+  // Option mlx_fuse: narrow launches (one or two activation rows) make their own digits when all
+  // chunks' B tiles fit beside a ring of at least five stages — one launch instead of two.  Off by
+  // default: measured on dependent chains of 4096 x 4096 products it costs 9.6 us per product
+  // against 8.0 us with the separate kernel, whose 64-thread blocks spread over all SMs while a
+  // CTA of the product kernel prepares the whole vector by itself.
+  if (N == 8 && options().mlx_fuse) {
+    size_t fixed = MmaSmem<N, FMT, true>::bytes(0, a.batch, a.in_dim);
+    int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, true>::kStage) : 0;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages >= 5) return launch_impl<N, DIGITS, MB, FMT, N == 8>(w, a, stream, prep, stages);
+  }
+  size_t fixed = MmaSmem<N, FMT, false>::bytes(0, a.batch, a.in_dim);
+  int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, false>::kStage) : 0;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 3)
+    return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
+  return launch_impl<N, DIGITS, MB, FMT, false>(w, a, stream, prep, stages);
 }
 
 template <int FMT>

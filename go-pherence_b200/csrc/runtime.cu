@@ -72,6 +72,8 @@ GOPH_API int goph_set_option(const char* name, int value) {
   bool rows_ok = value == 0 || value == 1 || value == 2 || value == 4;
   if (!strcmp(name, "pdl")) {
     o.pdl = value != 0;
+  } else if (!strcmp(name, "mlx_fuse")) {
+    o.mlx_fuse = value ? 1 : 0;
   } else if (!strcmp(name, "gguf_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "gguf_layout=%d not in 0..2", value);
     o.gguf_layout = value;

@@ -25,7 +25,7 @@ def algorithmic_bytes(fmt, out_dim, in_dim, batch):
     return out_dim * in_dim * per_weight + extra + batch * in_dim * 4 + batch * out_dim * 4
 
 
-def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=10):
+def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=10, chain=False):
     import torch
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
@@ -52,8 +52,23 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     out = torch.empty(batch * out_dim, dtype=torch.float32, device="cuda")
     xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
     stream = torch.cuda.current_stream()
+    if chain:
+        # every launch consumes the output of the one before it (square matrices only), as the
+        # projections of a decode step do: nothing of a launch's activations exists before its
+        # predecessor has finished.  The values overflow after a few dozen launches; the time does not care.
+        if out_dim != in_dim:
+            raise SystemExit("--chain needs out == in")
+        flip = [0]
 
     def launch(h):
+        if chain:
+            i = flip[0]
+            flip[0] ^= 1
+            _launch(h, (xb, ob)[i], (xb, ob)[1 - i])
+        else:
+            _launch(h, xb, ob)
+
+    def _launch(h, xb, ob):
         if fmt == "mlx4":
             rt.GemmMLX(ob, xb, h, batch, stream)
         elif fmt == "fp8":
@@ -86,7 +101,7 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     if os.path.exists(pk):
         peak = float(json.load(open(pk))["hbm_gbs"])
     gbs = nbytes / us / 1e3
-    res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "opts": dict(opts), "copies": copies,
+    res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "opts": dict(opts), "copies": copies, "chain": bool(chain),
            "us_per_launch": round(us, 3), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
            "bytes": nbytes}
     for h in handles:
@@ -169,12 +184,13 @@ def main():
     ap.add_argument("--launches", type=int, default=200)
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
+    ap.add_argument("--chain", action="store_true", help="each launch reads the previous launch's output (out == in)")
     args = ap.parse_args()
     opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts)))
         return
-    print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts)))
+    print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts, chain=args.chain)))
 
 
 if __name__ == "__main__":

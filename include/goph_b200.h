@@ -80,6 +80,8 @@ int goph_sm_count(int device);
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
+ *   "mlx_fuse"    1: tensor-core launches of one or two activation rows prepare the activation digits
+ *                 inside the product kernel (one launch instead of two); 0 (default) separate kernel
  *   "mlx_splits"  CTAs that share the K range of one 128-row tile (0 = chosen by shape)
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion

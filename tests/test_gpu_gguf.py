@@ -272,3 +272,28 @@ def test_tiled_product_while_l2_writes_back(gpu, pkg, qtype):
     assert gpu.KernelStatus() == 0
     for t in (m, xo, out, junk):
         t.Free()
+
+
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (300, 256), (2048, 8192), (640, 14336)])
+def test_tiled_fused_and_separate_preparation_agree(gpu, pkg, tiled_layout, qtype, out_dim, in_dim, batch):
+    raw = make(pkg, qtype, ("fuse-t", out_dim, in_dim), out_dim, in_dim)
+    m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
+    x = pkg.synth.activations(("fuse-t", in_dim, batch), batch * in_dim, bf16=False)
+    xo = gpu.from_numpy(x)
+    want = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, batch, nthreads=8)
+    got = []
+    try:
+        for fuse in (1, 0):
+            gpu.SetOption("mlx_fuse", fuse)
+            out = out_with_canary(gpu, batch * out_dim)
+            m.ProjectBatchToBuffer(out, xo, batch)
+            gpu.Sync()
+            got.append(read_and_check_canary(out, batch * out_dim))
+            out.Free()
+    finally:
+        gpu.SetOption("mlx_fuse", 0)
+    assert pkg.synth.rel_err(got[0], want) <= TOL
+    assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
+    m.Free(); xo.Free()

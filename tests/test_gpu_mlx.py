@@ -321,3 +321,31 @@ def test_tensor_core_product_while_l2_writes_back(gpu, pkg):
         assert pkg.synth.rel_err(out.Download(), want) <= TOL
     for t in (h, xo, out, junk):
         t.Free()
+
+
+@pytest.mark.parametrize("digits", [4, 3])
+@pytest.mark.parametrize("batch", [1, 2])
+@pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (300, 256), (4096, 1024), (2048, 8192), (640, 14336)])
+def test_fused_and_separate_preparation_agree(gpu, pkg, out_dim, in_dim, batch, digits):
+    """With option mlx_fuse narrow launches make the activation digits inside the product kernel
+    (one launch instead of two).  Same arithmetic, same bits."""
+    h, (w, s, b) = upload(gpu, pkg.synth, ("fuse", out_dim, in_dim), out_dim, in_dim)
+    x = pkg.synth.activations(("fuse", in_dim, batch), batch * in_dim, bf16=(digits == 3))
+    xo = gpu.from_numpy(x)
+    want = orc.mlx_gemm(x, batch, w, s, b, out_dim, in_dim, 64, nthreads=8)
+    got = []
+    gpu.SetOption("mlx_digits", digits)
+    try:
+        for fuse in (1, 0):
+            gpu.SetOption("mlx_fuse", fuse)
+            out = out_with_canary(gpu, batch * out_dim)
+            gpu.GemmMLX(out, xo, h, batch)
+            gpu.Sync()
+            got.append(read_and_check_canary(out, batch * out_dim))
+            out.Free()
+    finally:
+        gpu.SetOption("mlx_fuse", 0)
+        gpu.SetOption("mlx_digits", 4)
+    assert pkg.synth.rel_err(got[0], want) <= TOL
+    assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
+    h.Free(); xo.Free()
