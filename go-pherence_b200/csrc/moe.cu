@@ -31,6 +31,8 @@ namespace goph {
 
 constexpr uint32_t kMagicMoE = 0x4d4f4558;  // "MOEX"
 constexpr int kMoeWarps = 8, kMoeThreads = kMoeWarps * 32;
+constexpr int kMoeDepth = 4;             // steps of a warp's weight ring
+constexpr int kMoeStepBytes = 1024 + 512;  // two rows x 32 lanes x 16 B of weights, two rows x 32 lanes x 8 B of scales
 constexpr int kMoeMaxExperts = 1024;  // the routing kernel keeps one float and one int per expert in shared memory
 
 struct MoeTables {
@@ -88,6 +90,103 @@ __device__ __forceinline__ void unpack16(uint32_t w, float (&f)[8]) {
 __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Router logits for every token in one launch: grid (expert blocks of 16, tokens); a CTA stages its
+// token's x and each warp takes two expert rows.  (The batched MLX kernel would run ceil(T/8)
+// launches over the same small matrix.)
+template <bool SB_BF16>
+__global__ void __launch_bounds__(kMoeThreads)
+moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, const float* __restrict__ x,
+                  float* __restrict__ logits, int num_experts, int hidden, int ug_shift, int groups) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int units = hidden / 32, iters = (units + 31) / 32;
+  float4* xs = reinterpret_cast<float4*>(smem_raw);
+  float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)iters * 256 * 16);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.y;
+  const int e0 = (blockIdx.x * kMoeWarps + warp) * 2, e1 = min(e0 + 1, num_experts - 1);
+  const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the weights do not depend on the kernel in front: first units in flight before the wait
+  uint4 q[2];
+  const bool live = e0 < num_experts;
+  const int u0 = min(lane, units - 1);
+  if (live) {
+    q[0] = ld_stream(w + (size_t)e0 * units + u0);
+    q[1] = ld_stream(w + (size_t)e1 * units + u0);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int idx = threadIdx.x; idx < iters * 256; idx += kMoeThreads) {
+    const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (unit < units) v = *reinterpret_cast<const float4*>(x + (size_t)t * hidden + (size_t)unit * 32 + slot * 4);
+    xs[idx] = v;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < iters * 32; idx += kMoeThreads) {
+    const int it = idx >> 5, l = idx & 31;
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float4 v = xs[(it * 8 + k) * 32 + l];
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+    xc[idx] = make_float2(16.f * s, s);
+  }
+  __syncthreads();
+  if (!live) return;
+  float acc[2] = {0.f, 0.f};
+  for (int it = 0; it < iters; ++it) {
+    int unit = it * 32 + lane;
+    const bool valid = unit < units;
+    if (!valid) unit = units - 1;
+    uint4 nq[2] = {q[0], q[1]};
+    if (it + 1 < iters) {
+      const int nu = min((it + 1) * 32 + lane, units - 1);
+      nq[0] = ld_stream(w + (size_t)e0 * units + nu);
+      nq[1] = ld_stream(w + (size_t)e1 * units + nu);
+    }
+    const int grp = unit >> ug_shift;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int e = r ? e1 : e0;
+      float sc, bi;
+      if (SB_BF16) {
+        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(sb) + e * sb_row) + grp);
+        sc = __uint_as_float(v << 16);
+        bi = __uint_as_float(v & 0xFFFF0000u);
+      } else {
+        float2 v = __ldg(reinterpret_cast<const float2*>(reinterpret_cast<const char*>(sb) + e * sb_row) + grp);
+        sc = v.x;
+        bi = v.y;
+      }
+      float2 F = make_float2(0.f, 0.f);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t word = k == 0 ? q[r].x : k == 1 ? q[r].y : k == 2 ? q[r].z : q[r].w;
+        float f[8];
+        unpack16(word, f);
+        const float4 xa = xs[(it * 8 + 2 * k) * 32 + lane], xb = xs[(it * 8 + 2 * k + 1) * 32 + lane];
+        fma2(F, make_float2(f[0], f[1]), make_float2(xa.x, xa.y));
+        fma2(F, make_float2(f[2], f[3]), make_float2(xa.z, xa.w));
+        fma2(F, make_float2(f[4], f[5]), make_float2(xb.x, xb.y));
+        fma2(F, make_float2(f[6], f[7]), make_float2(xb.z, xb.w));
+      }
+      const float2 c = xc[it * 32 + lane];
+      if (valid) {
+        acc[r] = fmaf(sc, (F.x + F.y) - c.x, acc[r]);
+        acc[r] = fmaf(bi, c.y, acc[r]);
+      }
+    }
+    q[0] = nq[0];
+    q[1] = nq[1];
+  }
+  const float a0 = warp_sum(acc[0]), a1 = warp_sum(acc[1]);
+  if (lane == 0) {
+    logits[(size_t)t * num_experts + e0] = a0;
+    if (e0 + 1 < num_experts) logits[(size_t)t * num_experts + e0 + 1] = a1;
+  }
 }
 
 // simd.SoftmaxInPlace + the top-k loop of moeForwardWithREAP in the reference's order
@@ -174,8 +273,12 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
       }
       if (norm_topk && n > 0 && wsum > 0.f)
         for (int k = 0; k < n; ++k) my_w[k] = __fdiv_rn(my_w[k], wsum);
-      __threadfence();
-      s_last = atomicAdd(&lists[0], 1) == tokens - 1;
+      if (tokens > 1) {
+        __threadfence();
+        s_last = atomicAdd(&lists[0], 1) == tokens - 1;
+      } else {
+        s_last = 1;  // the only CTA builds the work list itself
+      }
     }
   }
   __syncthreads();
@@ -207,6 +310,8 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
     }
   }
   __syncthreads();
+  // entries past the selected experts: count 0 tells their CTAs to return
+  for (int y = s_n + tid; y < num_experts; y += blockDim.x) work[y].count = 0;
   if (tid == 0) {
     lists[1] = s_n;
     lists[0] = 0;  // ready for the next call
@@ -242,7 +347,8 @@ __device__ __forceinline__ void warp_sum_split(float (&v)[N], int lane) {
 template <bool SB_BF16, int PHASE, int M>
 __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __restrict__ items, int base, int m_now,
                                                 const float* __restrict__ src, float* __restrict__ dst, int in_dim,
-                                                int out_rows, int top_k, int ug_shift, int groups, float4* xs, float2* xc) {
+                                                int out_rows, int top_k, int ug_shift, int groups, float4* xs, float2* xc,
+                                                unsigned char* ring) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int units = in_dim / 32, iters = (units + 31) / 32;
   const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
@@ -269,37 +375,38 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
       t.sb[1] = reinterpret_cast<const char*>(wk.sb[2]) + r1 * sb_row;
     }
   };
-  struct Tile {
-    uint4 w[2];
-    uint32_t s[2], b[2];
-  };
-  auto load_tile = [&](const Rows& t, int it, Tile& d) {
-    int unit = it * 32 + lane;
-    if (unit >= units) unit = units - 1;  // the staged vector is zero there
-    const int grp = unit >> ug_shift;
+  // Per-warp ring of kMoeDepth steps in shared memory, filled with cp.async: a lane copies the 16-byte
+  // unit and the {scale,bias} entry it will itself consume, so completion of the lane's own copy
+  // group is all the synchronisation a step needs, and kMoeDepth - 1 steps of every warp are in
+  // flight while one is computed.  A step = one 32-lane iteration over the two rows of a task.
+  unsigned char* wring = ring + (size_t)warp * kMoeDepth * kMoeStepBytes;
+  int task = blockIdx.x * kMoeWarps + warp;
+  const int my_tasks = task < tasks ? (tasks - task + task_stride - 1) / task_stride : 0;
+  const int nsteps = my_tasks * iters;
+  auto issue = [&](int q) {
+    if (q < nsteps) {
+      const int j = q / iters, it = q - j * iters;
+      Rows t;
+      open_task(task + j * task_stride, t);
+      int unit = it * 32 + lane;
+      if (unit >= units) unit = units - 1;  // the staged vector is zero there
+      const int grp = unit >> ug_shift;
+      unsigned char* slot = wring + (size_t)(q % kMoeDepth) * kMoeStepBytes;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      d.w[r] = ld_stream(t.w[r] + unit);
-      if (SB_BF16) {
-        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(t.sb[r]) + grp);
-        d.s[r] = v << 16;
-        d.b[r] = v & 0xFFFF0000u;
-      } else {
-        float2 v = __ldg(reinterpret_cast<const float2*>(t.sb[r]) + grp);
-        d.s[r] = __float_as_uint(v.x);
-        d.b[r] = __float_as_uint(v.y);
+      for (int r = 0; r < 2; ++r) {
+        const uint32_t dw = (uint32_t)__cvta_generic_to_shared(slot + r * 512 + lane * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dw), "l"(t.w[r] + unit) : "memory");
+        const uint32_t ds = (uint32_t)__cvta_generic_to_shared(slot + 1024 + r * 256 + lane * 8);
+        if (SB_BF16)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ds), "l"(reinterpret_cast<const uint32_t*>(t.sb[r]) + grp) : "memory");
+        else
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(ds), "l"(reinterpret_cast<const float2*>(t.sb[r]) + grp) : "memory");
       }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // one group per step, empty past the end
   };
-
-  int task = blockIdx.x * kMoeWarps + warp;
-  const bool has_work = task < tasks;
-  Rows cur_rows, nxt_rows;
-  Tile cur, nxt;
-  if (has_work) {  // first weights in flight while the vectors are staged
-    open_task(task, cur_rows);
-    load_tile(cur_rows, 0, cur);
-  }
+#pragma unroll
+  for (int q = 0; q < kMoeDepth - 1; ++q) issue(q);  // first weights in flight while the vectors are staged
   // ---- stage the m_now vectors -----------------------------------------------------------
   const int per_m = iters * 256;
   for (int idx = threadIdx.x; idx < M * per_m; idx += kMoeThreads) {
@@ -325,23 +432,35 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
     xc[idx] = make_float2(16.f * s, s);
   }
   __syncthreads();
-  if (!has_work) return;
 
   float acc[2][M];
 #pragma unroll
   for (int r = 0; r < 2; ++r)
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-  while (true) {
-    const int ntask = task + task_stride;
-    const bool more = ntask < tasks;
-    for (int it = 0; it < iters; ++it) {
-      if (it + 1 < iters) {
-        load_tile(cur_rows, it + 1, nxt);
-      } else if (more) {
-        open_task(ntask, nxt_rows);
-        load_tile(nxt_rows, 0, nxt);
+  Rows cur_rows;
+  for (int q = 0; q < nsteps; ++q) {
+    const int j = q / iters, it = q - j * iters;
+    if (it == 0) open_task(task + j * task_stride, cur_rows);
+    issue(q + kMoeDepth - 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(kMoeDepth - 1) : "memory");
+    const unsigned char* slot = wring + (size_t)(q % kMoeDepth) * kMoeStepBytes;
+    uint4 cw[2];
+    uint32_t cs[2], cb[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      cw[r] = *reinterpret_cast<const uint4*>(slot + r * 512 + lane * 16);
+      if (SB_BF16) {
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(slot + 1024 + r * 256 + lane * 8);
+        cs[r] = v << 16;
+        cb[r] = v & 0xFFFF0000u;
+      } else {
+        const float2 v = *reinterpret_cast<const float2*>(slot + 1024 + r * 256 + lane * 8);
+        cs[r] = __float_as_uint(v.x);
+        cb[r] = __float_as_uint(v.y);
       }
+    }
+    {
       float2 F[2][M];
 #pragma unroll
       for (int r = 0; r < 2; ++r)
@@ -358,7 +477,7 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
         }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const uint32_t word = k == 0 ? cur.w[r].x : k == 1 ? cur.w[r].y : k == 2 ? cur.w[r].z : cur.w[r].w;
+          const uint32_t word = k == 0 ? cw[r].x : k == 1 ? cw[r].y : k == 2 ? cw[r].z : cw[r].w;
           float f[8];
           unpack16(word, f);
 #pragma unroll
@@ -376,12 +495,12 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           const float dot = (F[r][m].x + F[r][m].y) - c.x;
-          acc[r][m] = fmaf(__uint_as_float(cur.s[r]), dot, acc[r][m]);
-          acc[r][m] = fmaf(__uint_as_float(cur.b[r]), c.y, acc[r][m]);
+          acc[r][m] = fmaf(__uint_as_float(cs[r]), dot, acc[r][m]);
+          acc[r][m] = fmaf(__uint_as_float(cb[r]), c.y, acc[r][m]);
         }
       }
-      cur = nxt;
     }
+    if (it != iters - 1) continue;
     // ---- reduce the 2*M sums; value number 2*m + r ends up in the lanes whose top bits spell it
     float v[2 * M];
 #pragma unroll
@@ -409,10 +528,8 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
         if (row < out_rows) dst[(size_t)item * out_rows + row] = mine;
       }
     }
-    if (!more) break;
-    cur_rows = nxt_rows;
-    task = ntask;
   }
+  asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
 template <bool SB_BF16, int PHASE>
@@ -422,24 +539,25 @@ moe_expert_kernel(const MoeWork* __restrict__ work, const int* __restrict__ list
                   int top_k, int ug_shift, int groups) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   pdl_prologue();
-  if ((int)blockIdx.y >= lists[1]) return;
-  const MoeWork wk = work[blockIdx.y];
+  const MoeWork wk = work[blockIdx.y];  // entries past the selected experts carry count 0
+  if (wk.count == 0) return;
   const int* items = items_all + (size_t)wk.expert * max_tokens;
   const int iters = (in_dim / 32 + 31) / 32;
   float4* xs = reinterpret_cast<float4*>(smem_raw);
+  unsigned char* ring = smem_raw + (size_t)4 * iters * (256 * 16 + 32 * 8);  // behind room for four vectors
   // M vectors per pass: 1, 2 or 4 by how many items the expert has
   if (wk.count == 1) {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)1 * iters * 256 * 16);
-    moe_expert_pass<SB_BF16, PHASE, 1>(wk, items, 0, 1, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc);
+    moe_expert_pass<SB_BF16, PHASE, 1>(wk, items, 0, 1, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring);
   } else if (wk.count == 2) {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)2 * iters * 256 * 16);
-    moe_expert_pass<SB_BF16, PHASE, 2>(wk, items, 0, 2, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc);
+    moe_expert_pass<SB_BF16, PHASE, 2>(wk, items, 0, 2, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring);
   } else {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)4 * iters * 256 * 16);
     for (int base = 0; base < wk.count; base += 4) {
       if (base) __syncthreads();
       moe_expert_pass<SB_BF16, PHASE, 4>(wk, items, base, min(4, wk.count - base), src, dst, in_dim, out_rows, top_k,
-                                         ug_shift, groups, xs, xc);
+                                         ug_shift, groups, xs, xc, ring);
     }
   }
 }
@@ -454,10 +572,21 @@ moe_combine_kernel(MoeTables tb, const float* __restrict__ dpart, const int* __r
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= hidden) return;
   float acc = 0.f;
-  for (int k = 0; k < top_k; ++k) {
-    const int e = ids[t * top_k + k];
-    if (e < 0 || tb.down_w[e] == nullptr) continue;
-    acc = __fadd_rn(acc, __fmul_rn(wts[t * top_k + k], dpart[((size_t)t * top_k + k) * hidden + r]));
+  for (int k0 = 0; k0 < top_k; k0 += 8) {  // eight slots at a time: their loads are issued together
+    int e[8];
+    float w[8], d[8];
+    bool on[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[j] = k0 + j < top_k ? ids[t * top_k + k0 + j] : -1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      on[j] = e[j] >= 0 && tb.down_w[e[j]] != nullptr;
+      w[j] = on[j] ? wts[t * top_k + k0 + j] : 0.f;
+      d[j] = on[j] ? dpart[((size_t)t * top_k + k0 + j) * hidden + r] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (on[j]) acc = __fadd_rn(acc, __fmul_rn(w[j], d[j]));
   }
   out[(size_t)t * hidden + r] = acc;
 }
@@ -633,11 +762,13 @@ static int moe_run(goph_moe_layer* m, float* out_dev, const float* x_dev, const 
   while ((32 << sh) < m->group_size) ++sh;
   // at most this many experts can have been selected; CTAs past the actual number return at once
   const int max_active = min(m->num_experts, tokens * m->top_k);
-  const int want_ctas = sms * 4;
+  // two CTAs fit an SM.  One or two tokens: one wave, so the per-CTA staging of the vectors is paid
+  // once; more tokens: two waves' worth of smaller CTAs even out experts with different item counts
+  const int want_ctas = sms * (tokens <= 2 ? 2 : 4);
   for (int phase = 0; phase < 2; ++phase) {
     const int in_dim = phase == 0 ? m->hidden : m->inter, out_rows = phase == 0 ? m->inter : m->hidden;
     const int iters = (in_dim / 32 + 31) / 32;
-    const size_t smem = (size_t)4 * iters * (256 * 16 + 32 * 8);
+    const size_t smem = (size_t)4 * iters * (256 * 16 + 32 * 8) + (size_t)kMoeWarps * kMoeDepth * kMoeStepBytes;
     if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: %d columns do not fit shared memory", in_dim);
     const int tasks = phase == 0 ? out_rows : (out_rows + 1) / 2;
     const int max_blocks = (tasks + kMoeWarps - 1) / kMoeWarps;
@@ -673,7 +804,23 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
   if (int rc = moe_check_io(m, out_dev, out_len, x_dev, x_len, tokens)) return rc;
   if (!m->router) return fail(GOPH_E_INVALID, "MoE layer has no router weight");
   if (int rc = use_device(m->device)) return rc;
-  if (int rc = goph_mlx_gemm(m->logits, (uint64_t)tokens * m->num_experts, x_dev, x_len, m->router, tokens, stream)) return rc;
+  const goph_mlx_weight* rw = m->router;
+  if (rw->qweight && rw->sb && rw->group_size >= 32 && !(rw->group_size & (rw->group_size - 1)) && rw->in_dim % 32 == 0) {
+    // row-major router (the usual case: it is small): one launch for all tokens
+    int sh = 0;
+    while ((32 << sh) < rw->group_size) ++sh;
+    const int iters = (m->hidden / 32 + 31) / 32;
+    const size_t smem = (size_t)iters * (256 * 16 + 32 * 8);
+    if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: hidden=%d does not fit shared memory", m->hidden);
+    auto k = rw->sb_bf16 ? moe_router_kernel<true> : moe_router_kernel<false>;
+    GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (int rc = moe_launch(k, dim3((m->num_experts + 2 * kMoeWarps - 1) / (2 * kMoeWarps), tokens), kMoeThreads, smem,
+                            (cudaStream_t)stream, reinterpret_cast<const uint4*>(rw->qweight), rw->sb, x_dev, m->logits,
+                            m->num_experts, m->hidden, sh, m->hidden / rw->group_size))
+      return rc;
+  } else if (int rc = goph_mlx_gemm(m->logits, (uint64_t)tokens * m->num_experts, x_dev, x_len, rw, tokens, stream)) {
+    return rc;
+  }
   return moe_run(m, out_dev, x_dev, m->logits, tokens, (cudaStream_t)stream);
 }
 
