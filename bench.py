@@ -269,6 +269,38 @@ def run_reference(args):
     }))
 
 
+def extras(wl):
+    """Figures for the other BASELINE configs, measured in the same run with the same harness as
+    go-pherence_b200/microbench.py (device time per launch, CUDA-graph replay, weights rotated
+    through copies larger than the L2).  Reported beside the headline, not part of it."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("goph_microbench", os.path.join(ROOT, "go-pherence_b200", "microbench.py"))
+    mb = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mb)
+    # free the headline workload's weights first
+    for op in wl.ops:
+        for h in op[1]:
+            h.Free()
+    out = {}
+    keep = ("us_per_launch", "GBps", "frac_of_hbm_peak")
+    out["llama3_8b_gemv_batch1"] = {
+        fmt: {"%dx%d" % (o, i): {k: mb.run(fmt, o, i, launches=60)[k] for k in keep}
+              for o, i in ((14336, 4096), (128256, 4096))}
+        for fmt in ("mlx4", "q4k", "q8_0", "fp8")}
+    out["llama3_8b_layer_chain_batch1"] = {
+        fmt: {k: v for k, v in mb.run_layer_chain(fmt, layers=6, reps=3).items() if k in ("us_per_layer", "GBps", "frac_of_hbm_peak")}
+        for fmt in ("mlx4", "q4k", "q8_0")}
+    out["llama3_70b_small_m"] = {
+        fmt: {"8192x8192 M=%d" % m: {k: mb.run(fmt, 8192, 8192, batch=m, launches=20)[k] for k in ("us_per_launch",)}
+              for m in (1, 4, 16, 64)}
+        for fmt in ("mlx4", "fp8")}
+    out["qwen3_30b_a3b_moe_layer"] = {
+        "T=%d" % t: {k: v for k, v in mb.run_moe(t, layers=2, launches=20).items()
+                     if k in ("us_per_call", "GBps", "frac_of_hbm_peak", "distinct_experts_per_call")}
+        for t in (1, 8, 32)}
+    return out
+
+
 def run_ours(args):
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -372,16 +404,44 @@ def run_ours(args):
     barrier()
     ms_e2e = (time.perf_counter() - t0) * 1e3
 
-    # ---- per-launch durations for the roofline of the GEMV kernels ----------------------
-    with torch.cuda.stream(stream):
-        per = []
-        for _ in range(4):
-            per = wl.timed_launches(stream)
-    k_bytes = sum(b for _, b, _ in per)
-    k_ms = sum(t for _, _, t in per)
-    lm = [p for p in per if p[0] == "lm_head"][0]
-    small = [p for p in per if p[0] != "lm_head"]
-    small_bytes, small_ms = sum(p[1] for p in small), sum(p[2] for p in small)
+    # ---- roofline of the two kernels: graph replays of their launches alone, CUDA events around -------
+    # (events around single eager launches would time the host's launch rate, not the kernels)
+    def replay_time(ops_subset, reps):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            cs = torch.cuda.current_stream()
+            for k, op in ops_subset:
+                wl._launch(k, op, cs)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    indexed = list(enumerate(wl.ops))
+    small_ops = [(k, op) for k, op in indexed if op[0] != "lm_head"]
+    lm_ops = [(k, op) for k, op in indexed if op[0] == "lm_head"]
+    small_bytes = sum(sum(algorithmic_bytes(o, i) for o, i in op[4]) for _, op in small_ops)
+    lm_bytes = sum(sum(algorithmic_bytes(o, i) for o, i in op[4]) for _, op in lm_ops)
+    if use_graph:
+        small_ms = replay_time(small_ops, 50)
+        # the LM head by difference: replayed alone its 88 MB would stay in the 126 MB L2
+        lm_ms = max(ms_total / timed_steps - small_ms, 1e-6)
+    else:
+        with torch.cuda.stream(stream):
+            per = []
+            for _ in range(4):
+                per = wl.timed_launches(stream)
+        small_ms = sum(t for n, _, t in per if n != "lm_head")
+        lm_ms = sum(t for n, _, t in per if n == "lm_head")
+    lm = ("lm_head", lm_bytes, lm_ms)
+    small = small_ops
+    k_bytes, k_ms = small_bytes + lm_bytes, small_ms + lm_ms
     status = rt.KernelStatus() + (wl.exchange.Status() if wl.exchange is not None else 0)
 
     # max over ranks
@@ -423,7 +483,7 @@ def run_ours(args):
             # dominant kernel by time (95 % of the step's kernel time in the ncu launch list): the
             # CUDA-core GEMV behind the layer projections; the LM head's tensor-core launch beside it
             "roofline": {"bound": "hbm",
-                         "kernel": "mlx_gemv_kernel (the %d layer-projection launches of a step, CUDA events around each, eager)" % len(small),
+                         "kernel": "mlx_gemv_kernel (the %d layer-projection launches of a step replayed as a CUDA graph, CUDA events around the replays)" % len(small),
                          "achieved": round(small_gbs, 1), "peak": hbm_peak, "unit": "GB/s",
                          "frac": round(small_gbs / hbm_peak, 4), "peak_kind": peak_kind,
                          "bytes_per_launch": round(small_bytes / len(small)),
@@ -436,6 +496,8 @@ def run_ours(args):
                          "whole_step": {"achieved": round(achieved, 1), "frac": round(achieved / hbm_peak, 4)}},
             "clocks": clocks,
         }
+        if not args.no_extra and world == 1:
+            line["extra"] = extras(wl)
         if not args.no_cpu and world == 1:
             from oracle import binding as orc
             gbs_cpu, ms_cpu, cores = time_cpu(orc, syn, 3, 1, 4)
@@ -461,6 +523,7 @@ def main():
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: how the row shards' outputs reach every rank")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the per-format / MoE / small-M figures beside the headline")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -109,7 +109,7 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     return res
 
 
-def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, launches=40, opts=()):
+def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, launches=40, opts=(), keep_alive=None):
     """Selected-expert projection at the Qwen3-30B-A3B layer shape: `layers` distinct layers are walked
     so consecutive calls do not find their experts in L2.  Bytes counted: the router plus three matrices
     of every distinct expert the call's tokens selected."""
@@ -174,9 +174,94 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
 
 
+def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts=()):
+    """The projections of decoder layers at Llama-3-8B shapes as one dependent chain, batch 1:
+    q|k|v (hidden+2kv x hidden) -> o (hidden x hidden, fed by the first `hidden` outputs) ->
+    gate|up (2 ffn x hidden) -> down (hidden x ffn, fed by the first `ffn` outputs) -> next layer.
+    Every launch reads what the launch before it wrote, as in a decode step; `layers` layers have
+    their own device copies of the weights (more than the L2 holds), replayed as a CUDA graph."""
+    import numpy as np
+    import torch
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(0)
+    for k, v in opts:
+        rt.SetOption(k, v)
+    shapes = [(hidden + 2 * kv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
+    host = []
+    for o, i in shapes:
+        if fmt == "mlx4":
+            host.append(syn.mlx_weight(("chain", o, i), o, i, 64))
+        elif fmt == "q4k":
+            host.append(syn.q4k_matrix(("chain", o, i), o, i))
+        elif fmt == "q8_0":
+            host.append(syn.q8_0_matrix(("chain", o, i), o, i))
+        else:
+            w = torch.randn(o, i).clamp_(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy().reshape(-1)
+            host.append((w, np.full(o, 1.0 / np.sqrt(i), dtype=np.float32)))
+    handles, nbytes = [], 0.0
+    for _ in range(layers):
+        hs = []
+        for (o, i), hw in zip(shapes, host):
+            if fmt == "mlx4":
+                hs.append(rt.UploadMLXWeight(*hw, i, o, 64, True))
+            elif fmt in ("q4k", "q8_0"):
+                hs.append(rt.UploadGGUFMatrix(rt.GGUF_Q4_K if fmt == "q4k" else rt.GGUF_Q8_0, hw, i, o))
+            else:
+                hs.append(rt.UploadFP8E4M3Linear(hw[0], hw[1], None, o, i))
+            nbytes += algorithmic_bytes(fmt, o, i, 1)
+        handles.append(hs)
+    bufs = [torch.zeros(max(2 * ffn, hidden + 2 * kv), dtype=torch.float32, device="cuda") for _ in range(2)]
+    bufs[0][:hidden] = torch.from_numpy(syn.activations("chain", hidden)).cuda()
+    wrap = lambda t: rt.wrap(t.data_ptr(), t.numel() * 4)
+
+    def launch(h, x, out, stream):
+        if fmt == "mlx4":
+            rt.GemvMLX(out, x, h, stream)
+        elif fmt == "fp8":
+            rt.GemvFP8E4M3Buffer(out, x, h, stream)
+        else:
+            h.ProjectBatchToBuffer(out, x, 1, stream)
+
+    def step(stream):
+        cur = 0
+        for hs in handles:
+            for h in hs:
+                launch(h, wrap(bufs[cur]), wrap(bufs[1 - cur]), stream)
+                cur ^= 1
+
+    step(torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step(torch.cuda.current_stream())
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    peak = 6650.0
+    pk = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = float(json.load(open(pk))["hbm_gbs"])
+    gbs = nbytes / us / 1e3
+    for hs in handles:
+        for h in hs:
+            h.Free()
+    return {"format": fmt, "workload": "%d decoder layers of projections at Llama-3-8B shapes, dependent chain, batch 1" % layers,
+            "launches": 4 * layers, "us_per_layer": round(us / layers, 2), "GBps": round(gbs, 1),
+            "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--layer-chain", action="store_true", help="decoder-layer projections at Llama-3-8B shapes as a dependent chain")
     ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q8_0", "fp8", "moe"])
     ap.add_argument("--out", type=int, default=4096)
     ap.add_argument("--in", dest="in_dim", type=int, default=4096)
@@ -187,6 +272,9 @@ def main():
     ap.add_argument("--chain", action="store_true", help="each launch reads the previous launch's output (out == in)")
     args = ap.parse_args()
     opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
+    if args.layer_chain:
+        print(json.dumps(run_layer_chain(args.format, opts=opts)))
+        return
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts)))
         return
