@@ -5,5 +5,6 @@ the C ABI of libgoph_b200.so; `build` compiles that library in-tree.
 """
 from . import build  # noqa: F401
 from . import runtime  # noqa: F401
+from . import decode  # noqa: F401
 from . import sharding  # noqa: F401
 from . import synth  # noqa: F401

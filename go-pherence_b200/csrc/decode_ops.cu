@@ -1,0 +1,335 @@
+// The operations of a decode step that are not matrix products: RMSNorm (with the residual add in
+// front of it), per-head QK RMSNorm + RoPE + KV append, grouped-query attention over the KV cache,
+// SiLU*up, argmax, embedding lookup from the tied 4-bit LM head, position bookkeeping.
+//
+// Replaces the decode-step kernels of GPUModel.Generate (model/gpu_forward.go:993-1357: rms_norm,
+// rope, attention_score / softmax / attention_out, silu_mul, add, argmax); arithmetic specification:
+// runLegacyCPUToken (model/llama.go:899-1441) with simd.RMSNorm, kernels.ApplyRoPE,
+// simd.GQAAttentionScaleInto, kernels.SiLU and ArgmaxLogits (model/inference_helpers.go:248-261).
+// The position and the current token live in device memory (`pos_dev`, `tok_dev`) and the kernels
+// read them there, so one captured CUDA graph serves every step of a generation.
+// Every kernel starts with the programmatic-dependent-launch prologue used across the library.
+#include <math_constants.h>
+#include <string.h>
+
+#include "goph_internal.cuh"
+#include "mlx_mma.cuh"
+
+namespace goph {
+
+__device__ __forceinline__ void pdl_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += sh[i];
+  return t;
+}
+
+// hidden = a (+ b); normed = (hidden * inv) * w, inv = 1/sqrt(sum(hidden^2)/n + eps).  One CTA per row.
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* hidden, float* __restrict__ normed, const float* a, const float* __restrict__ b,
+                   const float* __restrict__ w, int n, float eps) {
+  __shared__ float sh[8];
+  pdl_begin();
+  const size_t row = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = a[row * n + i];
+    if (b) v = __fadd_rn(v, b[row * n + i]);
+    if (hidden) hidden[row * n + i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, sh);
+  const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)n), eps)));
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v;
+    if (hidden) {
+      v = hidden[row * n + i];  // written above by this thread (hidden may be the same buffer as a)
+    } else {
+      v = a[row * n + i];
+      if (b) v = __fadd_rn(v, b[row * n + i]);
+    }
+    normed[row * n + i] = __fmul_rn(__fmul_rn(v, inv), w[i]);
+  }
+}
+
+// Per head (q heads then k heads): optional RMSNorm with the head-dim weight, RoPE on the pairs
+// (i, i + d/2) with the table row of *pos_dev; q in place, k into the cache row, v copied into its
+// cache row.  One CTA of head_dim/2 threads per head; head_dim <= 512.
+__global__ void __launch_bounds__(256)
+qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                           const float* __restrict__ qw, const float* __restrict__ kw,
+                           const float* __restrict__ table, const int* __restrict__ pos_dev,
+                           float* __restrict__ kcache, float* __restrict__ vcache, int heads, int kv_heads,
+                           int head_dim, float eps) {
+  __shared__ float sh[8];
+  pdl_begin();
+  const int pos = *pos_dev, half = head_dim / 2, i = threadIdx.x;
+  const bool is_q = (int)blockIdx.x < heads;
+  const int head = is_q ? blockIdx.x : blockIdx.x - heads;
+  const float* src = (is_q ? q : k) + (size_t)head * head_dim;
+  float x0 = src[i], x1 = src[i + half];
+  const float* w = is_q ? qw : kw;
+  if (w) {
+    float ss = block_sum(fmaf(x0, x0, x1 * x1), sh);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)head_dim), eps)));
+    x0 = __fmul_rn(__fmul_rn(x0, inv), w[i]);
+    x1 = __fmul_rn(__fmul_rn(x1, inv), w[i + half]);
+  }
+  const float c = table[((size_t)pos * half + i) * 2], s = table[((size_t)pos * half + i) * 2 + 1];
+  const float y0 = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+  const float y1 = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
+  const size_t kvd = (size_t)kv_heads * head_dim;
+  if (is_q) {
+    q[(size_t)head * head_dim + i] = y0;
+    q[(size_t)head * head_dim + i + half] = y1;
+  } else {
+    float* kd = kcache + (size_t)pos * kvd + (size_t)head * head_dim;
+    kd[i] = y0;
+    kd[i + half] = y1;
+    float* vd = vcache + (size_t)pos * kvd + (size_t)head * head_dim;
+    const float* vs = v + (size_t)head * head_dim;
+    vd[i] = vs[i];
+    vd[i + half] = vs[i + half];
+  }
+}
+
+// One CTA per query head: scores over positions 0..pos (a warp per position), softmax with f64 exp,
+// out = sum_t p_t v_t.  Scores live in dynamic shared memory (max_seq floats).
+__global__ void __launch_bounds__(256)
+attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ kcache,
+                   const float* __restrict__ vcache, const int* __restrict__ pos_dev, int heads, int kv_heads,
+                   int head_dim, float scale) {
+  extern __shared__ float scores[];
+  __shared__ float sh[8];
+  __shared__ float part[256];
+  pdl_begin();
+  const int seq = *pos_dev + 1;
+  const int head = blockIdx.x, kvh = head / (heads / kv_heads);
+  const size_t kvd = (size_t)kv_heads * head_dim;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const float* qh = q + (size_t)head * head_dim;
+  for (int t = warp; t < seq; t += nw) {
+    const float* kh = kcache + (size_t)t * kvd + (size_t)kvh * head_dim;
+    float d = 0.f;
+    for (int i = lane; i < head_dim; i += 32) d = fmaf(qh[i], kh[i], d);
+    d = warp_sum(d);
+    if (lane == 0) scores[t] = __fmul_rn(d, scale);
+  }
+  __syncthreads();
+  float mx = -CUDART_INF_F;
+  for (int t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, scores[t]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) sh[warp] = mx;
+  __syncthreads();
+  mx = sh[0];
+  for (int i = 1; i < nw; ++i) mx = fmaxf(mx, sh[i]);
+  float sum = 0.f;
+  for (int t = threadIdx.x; t < seq; t += blockDim.x) {
+    const float e = (float)exp((double)(scores[t] - mx));
+    scores[t] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, sh);
+  const float inv = __fdiv_rn(1.f, sum);
+  // out[d]: the threads split the positions in blockDim/head_dim interleaved groups, then add up
+  const int groups = blockDim.x / head_dim > 0 ? blockDim.x / head_dim : 1;
+  const int d = threadIdx.x % head_dim, g = threadIdx.x / head_dim;
+  float acc = 0.f;
+  if (g < groups)
+    for (int t = g; t < seq; t += groups)
+      acc = fmaf(__fmul_rn(scores[t], inv), vcache[(size_t)t * kvd + (size_t)kvh * head_dim + d], acc);
+  part[threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.x < head_dim) {
+    float r = 0.f;
+    for (int j = 0; j < groups; ++j) r += part[j * head_dim + threadIdx.x];
+    out[(size_t)head * head_dim + threadIdx.x] = r;
+  }
+}
+
+// out[i] = silu(gate[i]) * up[i]; gate and up are the two halves of one fused projection output.
+__global__ void silu_mul_kernel(float* __restrict__ out, const float* __restrict__ gate, const float* __restrict__ up, int n) {
+  pdl_begin();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float g = gate[i];
+  out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, (float)exp((double)(-g)))), up[i]);
+}
+
+// First maximum of logits[0..n): one CTA; the winner becomes the current token and the position
+// advances by one (the bookkeeping of the greedy loop, model/llama.go:826-895).
+__global__ void __launch_bounds__(1024)
+argmax_advance_kernel(const float* __restrict__ logits, int n, int* __restrict__ tok_dev, int* __restrict__ pos_dev,
+                      int* __restrict__ history, const int* __restrict__ forced, int history_cap) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_begin();
+  float best = -CUDART_INF_F;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best) {  // strided ascending scan: within a thread the first maximum wins
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    sv[warp] = best;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
+        best = sv[w];
+        bi = si[w];
+      }
+    if (bi == 0x7fffffff) bi = 0;  // all NaN: ArgmaxLogits keeps index 0
+    const int pos = *pos_dev;
+    // while the prompt is being fed the next token is given, not chosen
+    if (forced && pos + 1 < history_cap && forced[pos + 1] >= 0) bi = forced[pos + 1];
+    *tok_dev = bi;
+    if (history && pos + 1 < history_cap) history[pos + 1] = bi;
+    *pos_dev = pos + 1;
+  }
+}
+
+// hidden = dequantised row *tok_dev of an MLX weight (the tied LM head used as embedding table,
+// LlamaModel.TokenEmbeddingInto), either layout.
+__global__ void embed_mlx_kernel(float* __restrict__ out, const uint32_t* __restrict__ qweight, const void* __restrict__ sb,
+                                 const unsigned char* __restrict__ tiled, const int* __restrict__ tok_dev, int in_dim,
+                                 int group_size, int sb_bf16) {
+  pdl_begin();
+  const int row = *tok_dev;
+  const int word = blockIdx.x * blockDim.x + threadIdx.x;  // packed word index within the row
+  if (word >= in_dim / 8) return;
+  const int col = word * 8, groups = in_dim / group_size, g = col / group_size;
+  uint32_t w;
+  float sc, bi;
+  if (tiled) {
+    const int nchunks = in_dim / kMlxChunkK;
+    w = *reinterpret_cast<const uint32_t*>(tiled + mlx_tiled_word_offset(row, col, nchunks));
+    const uint32_t m = *reinterpret_cast<const uint32_t*>(tiled + mlx_tiled_meta_offset(row, col, nchunks));
+    sc = __uint_as_float(m << 16);
+    bi = __uint_as_float(m & 0xFFFF0000u);
+  } else {
+    w = qweight[(size_t)row * (in_dim / 8) + word];
+    if (sb_bf16) {
+      const uint32_t m = reinterpret_cast<const uint32_t*>(sb)[(size_t)row * groups + g];
+      sc = __uint_as_float(m << 16);
+      bi = __uint_as_float(m & 0xFFFF0000u);
+    } else {
+      const float2 m = reinterpret_cast<const float2*>(sb)[(size_t)row * groups + g];
+      sc = m.x;
+      bi = m.y;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[col + e] = __fadd_rn(__fmul_rn((float)((w >> (4 * e)) & 0xF), sc), bi);
+}
+
+template <typename... KArgs, typename... Args>
+static int op_launch(void (*k)(KArgs...), dim3 grid, int threads, size_t smem, void* stream, Args... args) {
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = (cudaStream_t)stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, k, KArgs(args)...));
+  return GOPH_OK;
+}
+
+}  // namespace goph
+
+using namespace goph;
+
+GOPH_API int goph_add_rmsnorm(int device, float* hidden_dev, float* normed_dev, const float* a_dev, const float* b_dev,
+                              const float* weight_dev, int n, int rows, float eps, void* stream) {
+  clear_error();
+  if (!normed_dev || !a_dev || !weight_dev || n <= 0 || rows <= 0) return fail(GOPH_E_INVALID, "goph_add_rmsnorm: n=%d rows=%d", n, rows);
+  if (int rc = use_device(device)) return rc;
+  return op_launch(add_rmsnorm_kernel, dim3(rows), 256, 0, stream, hidden_dev, normed_dev, a_dev, b_dev, weight_dev, n, eps);
+}
+
+GOPH_API int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_dev, const float* v_dev,
+                                      const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
+                                      const int* pos_dev, float* kcache_dev, float* vcache_dev, int heads, int kv_heads,
+                                      int head_dim, float eps, void* stream) {
+  clear_error();
+  if (!q_dev || !k_dev || !v_dev || !rope_table_dev || !pos_dev || !kcache_dev || !vcache_dev)
+    return fail(GOPH_E_INVALID, "goph_qk_norm_rope_append: nil buffer");
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim < 64 || head_dim > 512 || head_dim % 64)
+    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim a multiple of 64 up to 512)", heads,
+                kv_heads, head_dim);
+  if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fail(GOPH_E_INVALID, "QNorm without KNorm");
+  if (int rc = use_device(device)) return rc;
+  return op_launch(qk_norm_rope_append_kernel, dim3(heads + kv_heads), head_dim / 2, 0, stream, q_dev, k_dev, v_dev, q_norm_dev,
+                   k_norm_dev, rope_table_dev, pos_dev, kcache_dev, vcache_dev, heads, kv_heads, head_dim, eps);
+}
+
+GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
+                              const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,
+                              int head_dim, float scale, void* stream) {
+  clear_error();
+  if (!out_dev || !q_dev || !kcache_dev || !vcache_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_attn_decode: nil buffer");
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim <= 0 || head_dim > 256 || 256 % head_dim)
+    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim a divisor of 256)", heads, kv_heads,
+                head_dim);
+  if (max_seq <= 0 || (size_t)max_seq * 4 > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "max_seq=%d scores do not fit shared memory", max_seq);
+  if (int rc = use_device(device)) return rc;
+  GOPH_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_seq * 4));
+  return op_launch(attn_decode_kernel, dim3(heads), 256, (size_t)max_seq * 4, stream, out_dev, q_dev, kcache_dev, vcache_dev, pos_dev,
+                   heads, kv_heads, head_dim, scale);
+}
+
+GOPH_API int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float* up_dev, int n, void* stream) {
+  clear_error();
+  if (!out_dev || !gate_dev || !up_dev || n <= 0) return fail(GOPH_E_INVALID, "goph_silu_mul: n=%d", n);
+  if (int rc = use_device(device)) return rc;
+  return op_launch(silu_mul_kernel, dim3((n + 255) / 256), 256, 0, stream, out_dev, gate_dev, up_dev, n);
+}
+
+GOPH_API int goph_argmax_advance(int device, const float* logits_dev, int n, int* tok_dev, int* pos_dev, int* history_dev,
+                                 const int* forced_dev, int history_cap, void* stream) {
+  clear_error();
+  if (!logits_dev || n <= 0 || !tok_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_argmax_advance: n=%d", n);
+  if (int rc = use_device(device)) return rc;
+  return op_launch(argmax_advance_kernel, dim3(1), 1024, 0, stream, logits_dev, n, tok_dev, pos_dev, history_dev, forced_dev,
+                   history_cap);
+}
+
+GOPH_API int goph_mlx_embed(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, const int* tok_dev, void* stream) {
+  clear_error();
+  if (!w || w->magic != kMagicMLX) return fail(GOPH_E_INVALID, "invalid MLX weight handle");
+  if (!out_dev || out_len < (uint64_t)w->in_dim || !tok_dev) return fail(GOPH_E_INVALID, "goph_mlx_embed: buffers");
+  if (int rc = use_device(w->device)) return rc;
+  const int words = w->in_dim / 8;
+  return op_launch(embed_mlx_kernel, dim3((words + 127) / 128), 128, 0, stream, out_dev, (const uint32_t*)w->qweight,
+                   (const void*)w->sb, (const unsigned char*)w->tiled, tok_dev, w->in_dim, w->group_size, w->sb_bf16);
+}

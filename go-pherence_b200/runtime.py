@@ -32,6 +32,7 @@ EXPORTS = [
     "goph_fp8_gemm_host",
     "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
     "goph_moe_forward_logits", "goph_moe_last_routing",
+    "goph_add_rmsnorm", "goph_qk_norm_rope_append", "goph_attn_decode", "goph_silu_mul", "goph_argmax_advance", "goph_mlx_embed",
     "goph_shard_rows", "goph_gather_create", "goph_gather_export", "goph_gather_open_peer", "goph_gather_attach_local",
     "goph_gather_free", "goph_gather_status", "goph_gather_shard_buffer", "goph_gather_all",
     "goph_mlx_gemm_allgather", "goph_gguf_project_allgather", "goph_fp8_gemm_allgather", "goph_moe_forward_sharded",
@@ -576,3 +577,38 @@ class Gather:
         if self._h:
             _check(lib().goph_gather_free(self._h))
             self._h = None
+
+
+# ------------------------------------------------------------------------------ decode-step operations
+def _ptr(b):
+    return C.c_void_p(b.Ptr if b is not None else 0)
+
+
+def AddRMSNorm(hidden, normed, a, b, weight, n, rows=1, eps=1e-6, stream=None):
+    """hidden = a (+ b); normed = RMSNorm(hidden) * weight (simd.RMSNorm after the residual add)."""
+    _check(lib().goph_add_rmsnorm(_device, _ptr(hidden), _ptr(normed), _ptr(a), _ptr(b), _ptr(weight), int(n), int(rows),
+                                  C.c_float(eps), _stream_ptr(stream)))
+
+
+def QKNormRoPEAppend(q, k, v, qNorm, kNorm, ropeTable, pos, kCache, vCache, heads, kvHeads, headDim, eps=1e-6, stream=None):
+    _check(lib().goph_qk_norm_rope_append(_device, _ptr(q), _ptr(k), _ptr(v), _ptr(qNorm), _ptr(kNorm), _ptr(ropeTable),
+                                          _ptr(pos), _ptr(kCache), _ptr(vCache), int(heads), int(kvHeads), int(headDim),
+                                          C.c_float(eps), _stream_ptr(stream)))
+
+
+def AttnDecode(out, q, kCache, vCache, pos, maxSeq, heads, kvHeads, headDim, scale, stream=None):
+    _check(lib().goph_attn_decode(_device, _ptr(out), _ptr(q), _ptr(kCache), _ptr(vCache), _ptr(pos), int(maxSeq), int(heads),
+                                  int(kvHeads), int(headDim), C.c_float(scale), _stream_ptr(stream)))
+
+
+def SiLUMul(out, gate, up, n, stream=None):
+    _check(lib().goph_silu_mul(_device, _ptr(out), _ptr(gate), _ptr(up), int(n), _stream_ptr(stream)))
+
+
+def ArgmaxAdvance(logits, n, tok, pos, history, forced, historyCap, stream=None):
+    _check(lib().goph_argmax_advance(_device, _ptr(logits), int(n), _ptr(tok), _ptr(pos), _ptr(history), _ptr(forced),
+                                     int(historyCap), _stream_ptr(stream)))
+
+
+def EmbedMLX(out, w, tok, stream=None):
+    _check(lib().goph_mlx_embed(_ptr(out), C.c_uint64(out.n), _mlx_handle(w), _ptr(tok), _stream_ptr(stream)))

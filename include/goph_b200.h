@@ -232,6 +232,38 @@ int goph_moe_forward_logits(goph_moe_layer* m, float* out_dev, uint64_t out_len,
 /* Expert ids (-1 = none) and weights [tokens x top_k] chosen by the last forward call. */
 int goph_moe_last_routing(goph_moe_layer* m, int tokens, int* ids_host, float* weights_host);
 
+/* ---- the other operations of a decode step ----------------------------------------------
+ * The kernels GPUModel.Generate launches between the projections (model/gpu_forward.go:993-1357),
+ * with the arithmetic of runLegacyCPUToken (model/llama.go:899-1441).  The position and the current
+ * token are read from device memory, so one captured CUDA graph serves every step. */
+
+/* hidden = a (+ b when b is not NULL; hidden may be NULL); normed = RMSNorm(hidden) * weight, per row
+ * of n (simd.RMSNorm, backends/simd/runtime/vec_amd64.s:280-375; the residual add of
+ * model/llama.go:1213-1216 in front of it). */
+int goph_add_rmsnorm(int device, float* hidden_dev, float* normed_dev, const float* a_dev, const float* b_dev,
+                     const float* weight_dev, int n, int rows, float eps, void* stream);
+/* Per head: optional QK RMSNorm (Qwen3, model/llama.go:1105-1127), RoPE with the table row of
+ * *pos_dev (kernels.ApplyRoPE, backends/simd/kernels/rope.go:29-44; table [max_seq][head_dim/2][cos,sin]
+ * as simd.BuildRoPEFreqs makes it); q in place, k and v into row *pos_dev of the caches
+ * [max_seq][kv_heads*head_dim] (model/llama.go:1150-1160). */
+int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_dev, const float* v_dev,
+                             const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
+                             const int* pos_dev, float* kcache_dev, float* vcache_dev, int heads, int kv_heads,
+                             int head_dim, float eps, void* stream);
+/* simd.GQAAttentionScaleInto over positions 0..*pos_dev (backends/simd/runtime/attention.go:82-113). */
+int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
+                     const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,
+                     int head_dim, float scale, void* stream);
+/* simd.VecSiLUMul (backends/simd/kernels/activation.go:15-24). */
+int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float* up_dev, int n, void* stream);
+/* ArgmaxLogits (model/inference_helpers.go:248-261: the first maximum) and the bookkeeping of the
+ * greedy loop: *tok_dev = the winner (or forced_dev[*pos_dev + 1] when that is >= 0: prompt tokens),
+ * history_dev[*pos_dev + 1] = it, *pos_dev += 1. */
+int goph_argmax_advance(int device, const float* logits_dev, int n, int* tok_dev, int* pos_dev, int* history_dev,
+                        const int* forced_dev, int history_cap, void* stream);
+/* LlamaModel.TokenEmbeddingInto for a tied MLX LM head: dequantised row *tok_dev (model/inference_helpers.go:20-44). */
+int goph_mlx_embed(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, const int* tok_dev, void* stream);
+
 /* ---- row-sharded products across the GPUs of one box ----------------------------------------
  * The reference is single-GPU.  A projection [out x in] is split by rows: rank r of `world` uploads
  * rows [lo, hi) as an ordinary weight handle (rows are contiguous in every format), computes

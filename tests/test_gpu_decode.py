@@ -1,0 +1,168 @@
+"""GPU parity of the decode-step operations and of greedy decoding against the CPU restatement
+(oracle/decode.py, pinned by the reference's frozen token sequences), through the C ABI.
+
+Operations are compared within f32 rounding of the restatement; the decode gate is token identity
+over the generated sequence on random-init models (the reference's gate for MLX checkpoints)."""
+import numpy as np
+import pytest
+
+from gpu_util import F
+from oracle import binding as orc
+from oracle import decode as od
+
+pytestmark = pytest.mark.gpu
+
+
+def test_add_rmsnorm(gpu, pkg):
+    g = pkg.synth.rng("rms")
+    n = 1024
+    a, b, w = (g.standard_normal(n, dtype=F) for _ in range(3))
+    A, B, W = gpu.from_numpy(a), gpu.from_numpy(b), gpu.from_numpy(w)
+    hid, nrm = gpu.Malloc(n), gpu.Malloc(n)
+    gpu.AddRMSNorm(hid, nrm, A, B, W, n, 1, 1e-6)
+    gpu.Sync()
+    assert np.array_equal(hid.Download(), a + b)
+    assert np.allclose(nrm.Download(), od.rmsnorm(a + b, w, 1e-6), rtol=2e-6, atol=1e-7)
+    gpu.AddRMSNorm(None, nrm, A, None, W, n, 1, 1e-6)      # no residual, no hidden output
+    gpu.Sync()
+    assert np.allclose(nrm.Download(), od.rmsnorm(a, w, 1e-6), rtol=2e-6, atol=1e-7)
+    gpu.AddRMSNorm(A, nrm, A, B, W, n, 1, 1e-6)            # in place on the residual stream
+    gpu.Sync()
+    assert np.array_equal(A.Download(), a + b)
+    assert np.allclose(nrm.Download(), od.rmsnorm(a + b, w, 1e-6), rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,qk_norm", [(16, 8, 128, True), (4, 2, 64, False), (8, 8, 128, True)])
+def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, qk_norm):
+    g = pkg.synth.rng("attn", heads, head_dim)
+    max_seq, kvd = 96, kv_heads * head_dim
+    table = od.rope_table(max_seq, head_dim, 1e6)
+    T = gpu.from_numpy(table.reshape(-1))
+    qn = g.standard_normal(head_dim, dtype=F) if qk_norm else None
+    kn = g.standard_normal(head_dim, dtype=F) if qk_norm else None
+    QN = gpu.from_numpy(qn) if qk_norm else None
+    KN = gpu.from_numpy(kn) if qk_norm else None
+    kc, vc = gpu.Malloc(max_seq * kvd), gpu.Malloc(max_seq * kvd)
+    kc.Zero(); vc.Zero()
+    ref_k, ref_v = np.zeros((max_seq, kvd), dtype=F), np.zeros((max_seq, kvd), dtype=F)
+    pos_buf = gpu.MallocBytes(4)
+    out = gpu.Malloc(heads * head_dim)
+    scale = 1.0 / np.sqrt(head_dim)
+    for pos in range(70):
+        q = g.standard_normal(heads * head_dim, dtype=F)
+        k = g.standard_normal(kvd, dtype=F)
+        v = g.standard_normal(kvd, dtype=F)
+        pos_buf.UploadBytes(np.array([pos], dtype=np.int32).view(np.uint8))
+        Q, K, V = gpu.from_numpy(q), gpu.from_numpy(k), gpu.from_numpy(v)
+        gpu.QKNormRoPEAppend(Q, K, V, QN, KN, T, pos_buf, kc, vc, heads, kv_heads, head_dim, 1e-6)
+        gpu.AttnDecode(out, Q, kc, vc, pos_buf, max_seq, heads, kv_heads, head_dim, scale)
+        gpu.Sync()
+        rq, rk = q.copy(), k.copy()
+        if qk_norm:
+            rq = np.concatenate([od.rmsnorm(rq[h * head_dim:(h + 1) * head_dim], qn, 1e-6) for h in range(heads)]).astype(F)
+            rk = np.concatenate([od.rmsnorm(rk[h * head_dim:(h + 1) * head_dim], kn, 1e-6) for h in range(kv_heads)]).astype(F)
+        od.apply_rope(rq, table, pos, heads, head_dim)
+        od.apply_rope(rk, table, pos, kv_heads, head_dim)
+        ref_k[pos], ref_v[pos] = rk, v
+        if pos in (0, 1, 31, 32, 69):
+            assert np.allclose(Q.Download(), rq, rtol=1e-5, atol=1e-6)
+            assert np.allclose(kc.Download()[pos * kvd:(pos + 1) * kvd], rk, rtol=1e-5, atol=1e-6)
+            assert np.array_equal(vc.Download()[pos * kvd:(pos + 1) * kvd], v)
+            want = od.attention(rq, ref_k, ref_v, pos + 1, heads, kv_heads, head_dim, scale)
+            assert np.allclose(out.Download(), want, rtol=1e-4, atol=2e-5)
+        for t in (Q, K, V):
+            t.Free()
+
+
+def test_silu_mul_argmax_embed(gpu, pkg):
+    g = pkg.synth.rng("misc")
+    n = 3072
+    a, b = g.standard_normal(n, dtype=F) * F(3), g.standard_normal(n, dtype=F)
+    out = gpu.Malloc(n)
+    gpu.SiLUMul(out, gpu.from_numpy(a), gpu.from_numpy(b), n)
+    gpu.Sync()
+    assert np.allclose(out.Download(), od.silu_mul(a, b), rtol=2e-6, atol=1e-7)
+    # argmax: first maximum, history and position bookkeeping, forced tokens
+    logits = g.standard_normal(151936, dtype=F)
+    logits[[77, 5000, 150000]] = logits.max() + F(1)
+    ints = gpu.MallocBytes(8 + 8 * 16)
+    host = np.full(2 + 32, -1, dtype=np.int32)
+    host[0], host[1] = 3, 4
+    host[2 + 16 + 6] = 999                                     # forced[6]
+    ints.UploadBytes(host.view(np.uint8))
+    tok, pos = gpu.wrap(ints.Ptr, 4), gpu.wrap(ints.Ptr + 4, 4)
+    hist, forced = gpu.wrap(ints.Ptr + 8, 64), gpu.wrap(ints.Ptr + 8 + 64, 64)
+    L = gpu.from_numpy(logits)
+    gpu.ArgmaxAdvance(L, logits.size, tok, pos, hist, forced, 16)
+    gpu.ArgmaxAdvance(L, logits.size, tok, pos, hist, forced, 16)
+    gpu.Sync()
+    got = ints.Download(2 + 32, dtype=np.int32)
+    assert got[0] == 999 and got[1] == 6 and got[2 + 5] == 77 and got[2 + 6] == 999
+    # embedding = dequantised row of the tied LM head, both layouts
+    for layout, (rows, cols) in ((1, (300, 256)), (2, (300, 256)), (0, (8192, 1024))):
+        w, s, b2 = pkg.synth.mlx_weight(("emb", layout), rows, cols, 64)
+        gpu.SetOption("mlx_layout", layout)
+        h = gpu.UploadMLXWeight(w, s, b2, cols, rows, 64, True)
+        gpu.SetOption("mlx_layout", 0)
+        want = orc.mlx_dequant(w, s, b2, rows, cols, 64).reshape(rows, cols)
+        e = gpu.Malloc(cols)
+        for t in (0, 129, rows - 1):
+            ints.UploadBytes(np.array([t], dtype=np.int32).view(np.uint8))
+            gpu.EmbedMLX(e, h, tok)
+            gpu.Sync()
+            assert np.array_equal(e.Download().view(np.uint32), want[t].view(np.uint32))
+        h.Free()
+
+
+def build_model(pkg, cfg, key):
+    syn = pkg.synth
+    g = syn.rng("decode", key)
+    shapes = {"q": (cfg.heads * cfg.head_dim, cfg.hidden), "k": (cfg.kv_heads * cfg.head_dim, cfg.hidden),
+              "v": (cfg.kv_heads * cfg.head_dim, cfg.hidden), "o": (cfg.hidden, cfg.heads * cfg.head_dim),
+              "gate": (cfg.inter, cfg.hidden), "up": (cfg.inter, cfg.hidden), "down": (cfg.hidden, cfg.inter)}
+    layers_gpu, layers_orc = [], []
+    for l in range(cfg.layers):
+        dg, do = {}, {}
+        for name, (o, i) in shapes.items():
+            w = syn.mlx_weight((key, name, l % 4), o, i, 64)   # four distinct sets of layer weights
+            dg[name] = w
+            do[name] = (w, o, i)
+        for name, n in (("input_norm", cfg.hidden), ("post_norm", cfg.hidden), ("q_norm", cfg.head_dim), ("k_norm", cfg.head_dim)):
+            v = (F(1) + F(0.1) * g.standard_normal(n, dtype=F)).astype(F)   # norm weights 1 + small noise
+            dg[name] = do[name] = v
+        layers_gpu.append(dg)
+        layers_orc.append(do)
+    lm = syn.mlx_weight((key, "lm"), cfg.vocab, cfg.hidden, 64)
+    final_norm = (F(1) + F(0.1) * g.standard_normal(cfg.hidden, dtype=F)).astype(F)
+    return layers_gpu, layers_orc, lm, final_norm
+
+
+def run_gate(gpu, pkg, cfg, key, prompt_len, max_new):
+    layers_gpu, layers_orc, lm, final_norm = build_model(pkg, cfg, key)
+    prompt = [int(t) for t in pkg.synth.rng("prompt", key).integers(0, cfg.vocab, prompt_len)]
+    oracle = od.OracleDecoder(cfg, od.MLXWeights(orc, cfg, layers_orc, lm, final_norm, nthreads=16))
+    trace = []
+    want = oracle.generate(prompt, max_new, trace=trace)
+    dec = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta))
+    got = dec.generate(prompt, max_new)
+    margins = [m for _, m, _ in trace]
+    assert gpu.KernelStatus() == 0
+    return want, got, margins, dec
+
+
+def test_greedy_tokens_small_model(gpu, pkg):
+    cfg = od.DecodeConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, inter=1024, vocab=4096, max_seq=64)
+    want, got, margins, dec = run_gate(gpu, pkg, cfg, "small", 12, 40)
+    assert got == want, (got, want, min(margins))
+    again = dec.generate(want[:12], 40, use_graph=False)     # plain launches give the same tokens as the graph
+    assert again == want
+
+
+def test_greedy_tokens_qwen3_0_6b(gpu, pkg):
+    """BASELINE config 1: random-init Qwen3-0.6B architecture in MLX 4-bit, 128-token random prompt,
+    64 greedy tokens identical to the restatement of the reference's CPU loop."""
+    cfg = od.DecodeConfig(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
+                          eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
+    want, got, margins, _ = run_gate(gpu, pkg, cfg, "qwen3-0.6b", 128, 64)
+    print("top-2 logit margins of the 64 chosen tokens: min %.3e median %.3e" % (min(margins), float(np.median(margins))))
+    assert got == want, ([i for i, (a, b) in enumerate(zip(got, want)) if a != b][:3], min(margins))
