@@ -269,6 +269,54 @@ def run_reference(args):
     }))
 
 
+def decode_rate(rt, syn, pkg):
+    """Greedy decode of the random-init Qwen3-0.6B MLX-4bit model (BASELINE config 1): every operation
+    of a token step on the GPU, the step captured once as a CUDA graph; 128 prompt tokens are fed
+    one by one, then 64 tokens are generated and those 64 steps are timed with CUDA events."""
+    import math
+    import types
+    import torch
+    F = np.float32
+    cfg = types.SimpleNamespace(hidden=HIDDEN, layers=LAYERS, heads=16, kv_heads=8, head_dim=128, inter=FFN, vocab=VOCAB,
+                                eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
+    shapes = {"q": (QDIM, HIDDEN), "k": (KVDIM, HIDDEN), "v": (KVDIM, HIDDEN), "o": (HIDDEN, QDIM),
+              "gate": (FFN, HIDDEN), "up": (FFN, HIDDEN), "down": (HIDDEN, FFN)}
+    g = syn.rng("bench-decode")
+    base = [{n: syn.mlx_weight(("dec", n, k), o, i, GS) for n, (o, i) in shapes.items()} for k in range(4)]
+    layers = []
+    for l in range(LAYERS):
+        d = dict(base[l % 4])
+        for n, sz in (("input_norm", HIDDEN), ("post_norm", HIDDEN), ("q_norm", 128), ("k_norm", 128)):
+            d[n] = (F(1) + F(0.1) * g.standard_normal(sz, dtype=F)).astype(F)
+        layers.append(d)
+    lm = syn.mlx_weight(("dec", "lm"), VOCAB, HIDDEN, GS)
+    half = 64
+    table = np.empty((cfg.max_seq, half, 2), dtype=F)
+    for i in range(half):
+        ang = np.arange(cfg.max_seq, dtype=np.float64) * (1.0 / math.pow(cfg.theta, 2.0 * i / 128.0))
+        table[:, i, 0], table[:, i, 1] = np.cos(ang).astype(F), np.sin(ang).astype(F)
+    dec = pkg.decode.MLXDecoder(rt, cfg, layers, lm, (F(1) + F(0.1) * g.standard_normal(HIDDEN, dtype=F)).astype(F), table)
+    prompt = [int(t) for t in g.integers(0, VOCAB, 128)]
+    dec.reset(prompt)
+    dec.capture()
+    dec.reset(prompt)
+    for _ in range(127):
+        dec.graph.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(64):
+        dec.graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / 64
+    weight_bytes = 335241216
+    return {"tok_s": round(1e3 / ms, 1), "ms_per_token": round(ms, 4), "launches_per_token": dec.launches_per_step,
+            "positions": "128..191 after a 128-token prompt fed token by token", "batch": 1,
+            "weight_GBps": round(weight_bytes / ms / 1e6, 1),
+            "gate": "64 greedy tokens identical to the CPU restatement (tests/test_gpu_decode.py::test_greedy_tokens_qwen3_0_6b)"}
+
+
 def extras(wl):
     """Figures for the other BASELINE configs, measured in the same run with the same harness as
     go-pherence_b200/microbench.py (device time per launch, CUDA-graph replay, weights rotated
@@ -498,6 +546,7 @@ def run_ours(args):
         }
         if not args.no_extra and world == 1:
             line["extra"] = extras(wl)
+            line["decode"] = decode_rate(rt, syn, pkg)
         if not args.no_cpu and world == 1:
             from oracle import binding as orc
             gbs_cpu, ms_cpu, cores = time_cpu(orc, syn, 3, 1, 4)

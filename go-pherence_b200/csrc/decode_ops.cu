@@ -33,31 +33,61 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
   return t;
 }
 
-// hidden = a (+ b); normed = (hidden * inv) * w, inv = 1/sqrt(sum(hidden^2)/n + eps).  One CTA per row.
+// hidden = a (+ b); normed = (hidden * inv) * w, inv = 1/sqrt(sum(hidden^2)/n + eps).  One CTA per
+// row; rows of up to 2048 elements stay in registers between the two passes.
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(float* hidden, float* __restrict__ normed, const float* a, const float* __restrict__ b,
                    const float* __restrict__ w, int n, float eps) {
   __shared__ float sh[8];
   pdl_begin();
   const size_t row = blockIdx.x;
+  constexpr int kKeep = 8;
+  const bool keep = n <= 256 * kKeep;
+  float v[kKeep];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v = a[row * n + i];
-    if (b) v = __fadd_rn(v, b[row * n + i]);
-    if (hidden) hidden[row * n + i] = v;
-    ss = fmaf(v, v, ss);
+  if (keep) {
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = threadIdx.x + j * 256;
+      v[j] = 0.f;
+      if (i < n) {
+        v[j] = a[row * n + i];
+        if (b) v[j] = __fadd_rn(v[j], b[row * n + i]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < n && hidden) hidden[row * n + i] = v[j];
+      ss = fmaf(v[j], v[j], ss);
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float x = a[row * n + i];
+      if (b) x = __fadd_rn(x, b[row * n + i]);
+      if (hidden) hidden[row * n + i] = x;
+      ss = fmaf(x, x, ss);
+    }
   }
   ss = block_sum(ss, sh);
   const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)n), eps)));
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    float v;
-    if (hidden) {
-      v = hidden[row * n + i];  // written above by this thread (hidden may be the same buffer as a)
-    } else {
-      v = a[row * n + i];
-      if (b) v = __fadd_rn(v, b[row * n + i]);
+  if (keep) {
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < n) normed[row * n + i] = __fmul_rn(__fmul_rn(v[j], inv), w[i]);
     }
-    normed[row * n + i] = __fmul_rn(__fmul_rn(v, inv), w[i]);
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float x;
+      if (hidden) {
+        x = hidden[row * n + i];  // written above by this thread (hidden may be the same buffer as a)
+      } else {
+        x = a[row * n + i];
+        if (b) x = __fadd_rn(x, b[row * n + i]);
+      }
+      normed[row * n + i] = __fmul_rn(__fmul_rn(x, inv), w[i]);
+    }
   }
 }
 
@@ -102,59 +132,132 @@ qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, c
   }
 }
 
-// One CTA per query head: scores over positions 0..pos (a warp per position), softmax with f64 exp,
-// out = sum_t p_t v_t.  Scores live in dynamic shared memory (max_seq floats).
-__global__ void __launch_bounds__(256)
+// Grid (query heads, position splits): a CTA of 8 warps takes every split-th block of positions
+// of its head.  Scores: a warp takes positions four at a time so their loads are in flight
+// together; the CTA's softmax numerators use its own maximum (f64 exp); a warp accumulates
+// e_t * v_t for all of head_dim (lane d, d+32, ...).  Each CTA leaves {max, sum, vector} in global
+// scratch and the last CTA of a head to arrive merges the splits: out = sum_s a_s v_s / sum_s a_s l_s
+// with a_s = exp(m_s - m).  Scores live in dynamic shared memory (max_seq floats).
+constexpr int kAttnWarps = 8, kAttnMaxEPL = 8, kAttnMaxSplits = 16, kAttnMaxHeads = 256;
+__global__ void __launch_bounds__(kAttnWarps * 32)
 attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ kcache,
                    const float* __restrict__ vcache, const int* __restrict__ pos_dev, int heads, int kv_heads,
-                   int head_dim, float scale) {
+                   int head_dim, float scale, float* __restrict__ scratch, unsigned int* __restrict__ counters) {
   extern __shared__ float scores[];
-  __shared__ float sh[8];
-  __shared__ float part[256];
+  __shared__ float sh[kAttnWarps];
+  __shared__ float part[kAttnWarps][256];
+  __shared__ int s_last;
   pdl_begin();
   const int seq = *pos_dev + 1;
   const int head = blockIdx.x, kvh = head / (heads / kv_heads);
+  const int splits = gridDim.y, split = blockIdx.y;
   const size_t kvd = (size_t)kv_heads * head_dim;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const float* qh = q + (size_t)head * head_dim;
-  for (int t = warp; t < seq; t += nw) {
-    const float* kh = kcache + (size_t)t * kvd + (size_t)kvh * head_dim;
-    float d = 0.f;
-    for (int i = lane; i < head_dim; i += 32) d = fmaf(qh[i], kh[i], d);
-    d = warp_sum(d);
-    if (lane == 0) scores[t] = __fmul_rn(d, scale);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int epl = head_dim / 32;  // elements per lane
+  const float* kbase = kcache + (size_t)kvh * head_dim;
+  const float* vbase = vcache + (size_t)kvh * head_dim;
+  // this CTA's positions: split, split + splits, ... in units of kAttnWarps*4 positions, i.e. local
+  // index i -> position t(i) = ((i / B) * splits + split) * B + i % B with B = 4 * kAttnWarps
+  constexpr int B = 4 * kAttnWarps;
+  const int nblocks = (seq + B - 1) / B;
+  const int my_blocks = nblocks > split ? (nblocks - split + splits - 1) / splits : 0;
+  auto pos_of = [&](int i) { return ((i / B) * splits + split) * B + (i % B); };
+  const int nloc = my_blocks * B;  // local indices (some past seq in the last block)
+  float qr[kAttnMaxEPL];
+#pragma unroll
+  for (int e = 0; e < kAttnMaxEPL; ++e) qr[e] = e < epl ? q[(size_t)head * head_dim + lane + 32 * e] : 0.f;
+  for (int i0 = warp; i0 < nloc; i0 += B) {
+    float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = pos_of(i0 + j * kAttnWarps);
+      if (t < seq) {
+#pragma unroll
+        for (int e = 0; e < kAttnMaxEPL; ++e)
+          if (e < epl) d[j] = fmaf(qr[e], kbase[(size_t)t * kvd + lane + 32 * e], d[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float r = warp_sum(d[j]);
+      const int i = i0 + j * kAttnWarps;
+      if (lane == 0) scores[i] = pos_of(i) < seq ? __fmul_rn(r, scale) : -CUDART_INF_F;
+    }
   }
   __syncthreads();
   float mx = -CUDART_INF_F;
-  for (int t = threadIdx.x; t < seq; t += blockDim.x) mx = fmaxf(mx, scores[t]);
+  for (int i = threadIdx.x; i < nloc; i += blockDim.x) mx = fmaxf(mx, scores[i]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   if (lane == 0) sh[warp] = mx;
   __syncthreads();
   mx = sh[0];
-  for (int i = 1; i < nw; ++i) mx = fmaxf(mx, sh[i]);
+  for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, sh[i]);
   float sum = 0.f;
-  for (int t = threadIdx.x; t < seq; t += blockDim.x) {
-    const float e = (float)exp((double)(scores[t] - mx));
-    scores[t] = e;
+  for (int i = threadIdx.x; i < nloc; i += blockDim.x) {
+    const float e = scores[i] == -CUDART_INF_F ? 0.f : (float)exp((double)(scores[i] - mx));
+    scores[i] = e;
     sum += e;
   }
   sum = block_sum(sum, sh);
-  const float inv = __fdiv_rn(1.f, sum);
-  // out[d]: the threads split the positions in blockDim/head_dim interleaved groups, then add up
-  const int groups = blockDim.x / head_dim > 0 ? blockDim.x / head_dim : 1;
-  const int d = threadIdx.x % head_dim, g = threadIdx.x / head_dim;
-  float acc = 0.f;
-  if (g < groups)
-    for (int t = g; t < seq; t += groups)
-      acc = fmaf(__fmul_rn(scores[t], inv), vcache[(size_t)t * kvd + (size_t)kvh * head_dim + d], acc);
-  part[threadIdx.x] = acc;
-  __syncthreads();
-  if (threadIdx.x < head_dim) {
-    float r = 0.f;
-    for (int j = 0; j < groups; ++j) r += part[j * head_dim + threadIdx.x];
-    out[(size_t)head * head_dim + threadIdx.x] = r;
+  float acc[kAttnMaxEPL];
+#pragma unroll
+  for (int e = 0; e < kAttnMaxEPL; ++e) acc[e] = 0.f;
+  for (int i0 = warp; i0 < nloc; i0 += B) {
+    float vv[4][kAttnMaxEPL], p[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + j * kAttnWarps, t = pos_of(i);
+      p[j] = scores[i];
+#pragma unroll
+      for (int e = 0; e < kAttnMaxEPL; ++e) vv[j][e] = (t < seq && e < epl) ? vbase[(size_t)t * kvd + lane + 32 * e] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < kAttnMaxEPL; ++e) acc[e] = fmaf(p[j], vv[j][e], acc[e]);
   }
+#pragma unroll
+  for (int e = 0; e < kAttnMaxEPL; ++e)
+    if (e < epl) part[warp][lane + 32 * e] = acc[e];
+  __syncthreads();
+  // ---- this split's {max, sum, vector} to scratch; the head's last CTA merges -------------------
+  const int stride = 2 + 256;
+  float* mine = scratch + ((size_t)head * kAttnMaxSplits + split) * stride;
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float r = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) r += part[w][d];
+    mine[2 + d] = r;
+  }
+  if (threadIdx.x == 0) {
+    mine[0] = mx;
+    mine[1] = sum;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(counters + head, 1u) == (unsigned)splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* base = scratch + (size_t)head * kAttnMaxSplits * stride;
+  float m = -CUDART_INF_F;
+  for (int s2 = 0; s2 < splits; ++s2) m = fmaxf(m, __ldcg(base + s2 * stride));
+  float total = 0.f;
+  for (int s2 = 0; s2 < splits; ++s2) {
+    const float ms = __ldcg(base + s2 * stride);
+    if (ms != -CUDART_INF_F) total = fmaf(__ldcg(base + s2 * stride + 1), (float)exp((double)(ms - m)), total);
+  }
+  const float inv = __fdiv_rn(1.f, total);
+  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+    float r = 0.f;
+    for (int s2 = 0; s2 < splits; ++s2) {
+      const float ms = __ldcg(base + s2 * stride);
+      if (ms != -CUDART_INF_F) r = fmaf(__ldcg(base + s2 * stride + 2 + d), (float)exp((double)(ms - m)), r);
+    }
+    out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
+  }
+  if (threadIdx.x == 0) counters[head] = 0;
 }
 
 // out[i] = silu(gate[i]) * up[i]; gate and up are the two halves of one fused projection output.
@@ -166,44 +269,60 @@ __global__ void silu_mul_kernel(float* __restrict__ out, const float* __restrict
   out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, (float)exp((double)(-g)))), up[i]);
 }
 
-// First maximum of logits[0..n): one CTA; the winner becomes the current token and the position
-// advances by one (the bookkeeping of the greedy loop, model/llama.go:826-895).
-__global__ void __launch_bounds__(1024)
+// First maximum of logits[0..n): kArgmaxCtas CTAs reduce a slice each; the last one to arrive
+// reduces their results, and the winner becomes the current token and the position advances by one
+// (the bookkeeping of the greedy loop, model/llama.go:826-895).  scratch: kArgmaxCtas {value, index}
+// pairs and an arrival counter that the last CTA leaves at zero.
+constexpr int kArgmaxCtas = 64;
+__device__ __forceinline__ void argmax_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) {
+    best = ov;
+    bi = oi;
+  }
+}
+__global__ void __launch_bounds__(512)
 argmax_advance_kernel(const float* __restrict__ logits, int n, int* __restrict__ tok_dev, int* __restrict__ pos_dev,
-                      int* __restrict__ history, const int* __restrict__ forced, int history_cap) {
-  __shared__ float sv[32];
-  __shared__ int si[32];
+                      int* __restrict__ history, const int* __restrict__ forced, int history_cap,
+                      float* __restrict__ part_val, int* __restrict__ part_idx, unsigned int* __restrict__ counter) {
+  __shared__ float sv[16];
+  __shared__ int si[16];
+  __shared__ int s_last;
   pdl_begin();
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * per, hi = min(n, lo + per);
   float best = -CUDART_INF_F;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = logits[i];
-    if (v > best) {  // strided ascending scan: within a thread the first maximum wins
+    if (v > best) {  // ascending scan: within a thread the first maximum wins
       best = v;
       bi = i;
     }
   }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
 #pragma unroll
-  for (int o = 16; o; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
-  }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = 16; o; o >>= 1) argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
   if (lane == 0) {
     sv[warp] = best;
     si[warp] = bi;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-      if (sv[w] > best || (sv[w] == best && si[w] < bi)) {
-        best = sv[w];
-        bi = si[w];
-      }
+    for (int w = 1; w < nw; ++w) argmax_merge(best, bi, sv[w], si[w]);
+    part_val[blockIdx.x] = best;
+    part_idx[blockIdx.x] = bi;
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last || threadIdx.x >= 32) return;
+  __threadfence();
+  best = -CUDART_INF_F;
+  bi = 0x7fffffff;
+  for (int c = lane; c < (int)gridDim.x; c += 32) argmax_merge(best, bi, __ldcg(part_val + c), __ldcg(part_idx + c));
+#pragma unroll
+  for (int o = 16; o; o >>= 1) argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if (lane == 0) {
     if (bi == 0x7fffffff) bi = 0;  // all NaN: ArgmaxLogits keeps index 0
     const int pos = *pos_dev;
     // while the prompt is being fed the next token is given, not chosen
@@ -211,6 +330,7 @@ argmax_advance_kernel(const float* __restrict__ logits, int n, int* __restrict__
     *tok_dev = bi;
     if (history && pos + 1 < history_cap) history[pos + 1] = bi;
     *pos_dev = pos + 1;
+    *counter = 0;
   }
 }
 
@@ -298,14 +418,30 @@ GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, co
                               int head_dim, float scale, void* stream) {
   clear_error();
   if (!out_dev || !q_dev || !kcache_dev || !vcache_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_attn_decode: nil buffer");
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim <= 0 || head_dim > 256 || 256 % head_dim)
-    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim a divisor of 256)", heads, kv_heads,
-                head_dim);
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim < 32 || head_dim > 256 || head_dim % 32)
+    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim a multiple of 32 up to 256)", heads,
+                kv_heads, head_dim);
+  if ((size_t)max_seq * 4 > 160 * 1024) return fail(GOPH_E_UNSUPPORTED, "max_seq=%d scores do not fit shared memory", max_seq);
   if (max_seq <= 0 || (size_t)max_seq * 4 > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "max_seq=%d scores do not fit shared memory", max_seq);
   if (int rc = use_device(device)) return rc;
-  GOPH_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_seq * 4));
-  return op_launch(attn_decode_kernel, dim3(heads), 256, (size_t)max_seq * 4, stream, out_dev, q_dev, kcache_dev, vcache_dev, pos_dev,
-                   heads, kv_heads, head_dim, scale);
+  if (heads > kAttnMaxHeads) return fail(GOPH_E_UNSUPPORTED, "at most %d query heads", kAttnMaxHeads);
+  static float* scratch[kMaxDevices] = {};
+  static unsigned int* counters[kMaxDevices] = {};
+  if (!counters[device]) {
+    GOPH_CUDA(cudaMalloc(&scratch[device], (size_t)kAttnMaxHeads * kAttnMaxSplits * (2 + 256) * sizeof(float)));
+    GOPH_CUDA(cudaMalloc(&counters[device], kAttnMaxHeads * sizeof(unsigned int)));
+    GOPH_CUDA(cudaMemset(counters[device], 0, kAttnMaxHeads * sizeof(unsigned int)));
+  }
+  // enough CTAs that every warp has about one round of positions at the longest sequence
+  int splits = (max_seq + 4 * kAttnWarps - 1) / (4 * kAttnWarps);
+  const int want = (2 * device_state(device).sm_count + heads - 1) / heads;
+  if (splits > want) splits = want;
+  if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
+  if (splits < 1) splits = 1;
+  const size_t smem = ((size_t)max_seq + 4 * kAttnWarps) * 4;
+  GOPH_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  return op_launch(attn_decode_kernel, dim3(heads, splits), kAttnWarps * 32, smem, stream, out_dev, q_dev, kcache_dev, vcache_dev,
+                   pos_dev, heads, kv_heads, head_dim, scale, scratch[device], counters[device]);
 }
 
 GOPH_API int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float* up_dev, int n, void* stream) {
@@ -320,8 +456,19 @@ GOPH_API int goph_argmax_advance(int device, const float* logits_dev, int n, int
   clear_error();
   if (!logits_dev || n <= 0 || !tok_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_argmax_advance: n=%d", n);
   if (int rc = use_device(device)) return rc;
-  return op_launch(argmax_advance_kernel, dim3(1), 1024, 0, stream, logits_dev, n, tok_dev, pos_dev, history_dev, forced_dev,
-                   history_cap);
+  // per-device scratch of the two-level reduction, allocated once
+  static float* part_val[kMaxDevices] = {};
+  static int* part_idx[kMaxDevices] = {};
+  static unsigned int* counter[kMaxDevices] = {};
+  if (!counter[device]) {
+    GOPH_CUDA(cudaMalloc(&part_val[device], kArgmaxCtas * sizeof(float)));
+    GOPH_CUDA(cudaMalloc(&part_idx[device], kArgmaxCtas * sizeof(int)));
+    GOPH_CUDA(cudaMalloc(&counter[device], sizeof(unsigned int)));
+    GOPH_CUDA(cudaMemset(counter[device], 0, sizeof(unsigned int)));
+  }
+  const int ctas = n >= 64 * 512 ? kArgmaxCtas : 1;
+  return op_launch(argmax_advance_kernel, dim3(ctas), 512, 0, stream, logits_dev, n, tok_dev, pos_dev, history_dev, forced_dev,
+                   history_cap, part_val[device], part_idx[device], counter[device]);
 }
 
 GOPH_API int goph_mlx_embed(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, const int* tok_dev, void* stream) {
