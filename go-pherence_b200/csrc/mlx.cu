@@ -116,6 +116,15 @@ struct MlxArgs {
   int groups;       // in_dim / group_size
   int ug_shift;     // log2(group_size / 32)
   int x_aligned;    // x is 16-byte aligned
+  // Operation applied to x while it is staged (batch 1, 16-byte aligned vectors):
+  //   1  v = x (+ pre_b); CTA 0 stores v to pre_hidden (which must not alias x or pre_b);
+  //      staged x = (v * inv) * pre_w, inv = 1/sqrt(sum(v^2)/n + pre_eps)  — residual add + RMSNorm
+  //   2  staged x = silu(x) * pre_b                                          — SiLU(gate) * up
+  int pre_op;
+  const float* pre_b;
+  const float* pre_w;
+  float* pre_hidden;
+  float pre_eps;
 };
 
 // Shared memory: float4 xs[M][iters][8][32]; float2 xc[M][iters][32].
@@ -146,6 +155,69 @@ __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2
   const int nsum = M * a.iters * 32;
   for (int idx = threadIdx.x; idx < nsum; idx += kThreads) {
     int mi = idx >> 5, l = idx & 31;  // mi = m*iters + it
+    float se = 0.f, so = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      float4 v = xs[(mi * 8 + s) * 32 + l];
+      se += v.x + v.z;
+      so += v.y + v.w;
+    }
+    xc[idx] = make_float2(Unpack<MODE>::kOffEven * se + Unpack<MODE>::kOffOdd * so, se + so);
+  }
+  __syncthreads();
+}
+
+// Staging with the operation a.pre_op in front (see MlxArgs); batch 1.
+template <int MODE>
+__device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, float2* xc) {
+  __shared__ float red[kWarps];
+  const int total = a.iters * 256;
+  float ss = 0.f;
+  for (int idx = threadIdx.x; idx < total; idx += kThreads) {
+    const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (unit < a.units) {
+      const size_t e0 = (size_t)unit * 32 + slot * 4;
+      v = *reinterpret_cast<const float4*>(a.x + e0);
+      if (a.pre_op == 1) {
+        if (a.pre_b) {
+          const float4 b = *reinterpret_cast<const float4*>(a.pre_b + e0);
+          v = make_float4(__fadd_rn(v.x, b.x), __fadd_rn(v.y, b.y), __fadd_rn(v.z, b.z), __fadd_rn(v.w, b.w));
+        }
+        if (a.pre_hidden && blockIdx.x == 0) *reinterpret_cast<float4*>(a.pre_hidden + e0) = v;
+        ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+      } else {
+        const float4 u = *reinterpret_cast<const float4*>(a.pre_b + e0);
+        v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.f, (float)exp((double)(-v.x)))), u.x);
+        v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.f, (float)exp((double)(-v.y)))), u.y);
+        v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.f, (float)exp((double)(-v.z)))), u.z);
+        v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.f, (float)exp((double)(-v.w)))), u.w);
+      }
+    }
+    xs[idx] = v;
+  }
+  if (a.pre_op == 1) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) t += red[w];
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.in_dim), a.pre_eps)));
+    for (int idx = threadIdx.x; idx < total; idx += kThreads) {
+      const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
+      if (unit < a.units) {
+        const float4 w = *reinterpret_cast<const float4*>(a.pre_w + (size_t)unit * 32 + slot * 4);
+        float4 v = xs[idx];
+        v = make_float4(__fmul_rn(__fmul_rn(v.x, inv), w.x), __fmul_rn(__fmul_rn(v.y, inv), w.y),
+                        __fmul_rn(__fmul_rn(v.z, inv), w.z), __fmul_rn(__fmul_rn(v.w, inv), w.w));
+        xs[idx] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < a.iters * 32; idx += kThreads) {
+    const int mi = idx >> 5, l = idx & 31;
     float se = 0.f, so = 0.f;
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
@@ -231,7 +303,11 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
     load_tile(cur_rows, 0, cur);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  mlx_stage_x<M, MODE>(a, xs, xc);
+  if (M == 1 && a.pre_op != 0) {
+    mlx_stage_x_pre<MODE>(a, xs, xc);
+  } else {
+    mlx_stage_x<M, MODE>(a, xs, xc);
+  }
   if (!has_work) return;
 
   float acc[R][M];
@@ -453,8 +529,16 @@ static bool fast_path_ok(const goph_mlx_weight* w) {
 }
 
 // One launch of the streaming kernel for up to kMaxSeg weights sharing x, batch <= 8.
+struct MlxPre {
+  int op = 0;
+  const float* b = nullptr;
+  const float* w = nullptr;
+  float* hidden = nullptr;
+  float eps = 0.f;
+};
+
 static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, int n, const float* x,
-                         int batch, cudaStream_t stream) {
+                         int batch, cudaStream_t stream, const MlxPre* pre = nullptr) {
   const goph_mlx_weight* w0 = ws[0];
   DeviceState& st = device_state(w0->device);
   MlxArgs a;
@@ -470,6 +554,13 @@ static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, i
   while ((1 << sh) < upg) ++sh;
   a.ug_shift = sh;
   a.x_aligned = ((uintptr_t)x % 16) == 0;
+  if (pre) {
+    a.pre_op = pre->op;
+    a.pre_b = pre->b;
+    a.pre_w = pre->w;
+    a.pre_hidden = pre->hidden;
+    a.pre_eps = pre->eps;
+  }
 
   int M = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
   long total_rows = 0;
@@ -822,4 +913,31 @@ GOPH_API int goph_mlx_gemm_host(float* out_host, uint64_t out_len, const float* 
   cudaFree(dx);
   cudaFree(dout);
   return rc;
+}
+
+
+// out = W . f(x): the operation in front of a projection folded into the kernel that stages x
+// (one launch instead of two in the decode step).  pre_op 1: v = x (+ b); hidden_out = v;
+// f = RMSNorm(v) * norm_w.  pre_op 2: f = silu(x) * b.  Row-major weights of the CUDA-core kernel,
+// batch 1; anything else is GOPH_E_UNSUPPORTED and the caller runs the two operations separately.
+GOPH_API int goph_mlx_gemv_pre(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, int pre_op, const float* x_dev,
+                               const float* b_dev, const float* norm_w_dev, float* hidden_out_dev, float eps, void* stream) {
+  clear_error();
+  if (!valid_handle(w)) return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: invalid weight handle");
+  if (pre_op != 1 && pre_op != 2) return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: pre_op=%d", pre_op);
+  if (!out_dev || out_len < (uint64_t)w->out_dim || !x_dev) return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: buffers");
+  if ((pre_op == 1 && !norm_w_dev) || (pre_op == 2 && !b_dev)) return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: missing operand");
+  if (pre_op == 1 && hidden_out_dev && (hidden_out_dev == x_dev || hidden_out_dev == b_dev))
+    return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: hidden_out must not alias an input (every CTA reads the inputs)");
+  if (w->tiled || !fast_path_ok(w)) return fail(GOPH_E_UNSUPPORTED, "goph_mlx_gemv_pre: row-major weights with group size >= 32 only");
+  const uintptr_t al = (uintptr_t)x_dev | (uintptr_t)b_dev | (uintptr_t)norm_w_dev | (uintptr_t)hidden_out_dev;
+  if (al % 16) return fail(GOPH_E_INVALID, "goph_mlx_gemv_pre: vectors must be 16-byte aligned");
+  if (int rc = use_device(w->device)) return rc;
+  MlxPre pre;
+  pre.op = pre_op;
+  pre.b = b_dev;
+  pre.w = norm_w_dev;
+  pre.hidden = hidden_out_dev;
+  pre.eps = eps;
+  return launch_stream(&w, &out_dev, 1, x_dev, 1, (cudaStream_t)stream, &pre);
 }

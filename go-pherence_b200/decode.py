@@ -14,7 +14,7 @@ import numpy as np
 
 
 class MLXDecoder:
-    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64):
+    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64, fuse=True):
         """cfg: an object with hidden, layers, heads, kv_heads, head_dim, inter, vocab, eps, qk_norm, max_seq.
         layers[l]: dict with "q","k","v","o","gate","up","down" -> (words, scales, biases) in the MLX
         layout, and "input_norm","post_norm" (+ "q_norm","k_norm") f32 vectors.  lm_head: the tied
@@ -41,7 +41,12 @@ class MLXDecoder:
         self.lm = rt.UploadMLXWeight(*lm_head, c.hidden, c.vocab, group_size, True)
         self.final_norm = rt.from_numpy(np.asarray(final_norm, dtype=np.float32))
         self.table = rt.from_numpy(np.ascontiguousarray(rope_table, dtype=np.float32).reshape(-1))
-        self.hidden, self.normed = rt.Malloc(c.hidden), rt.Malloc(c.hidden)
+        self.hidden, self.hidden2, self.normed = rt.Malloc(c.hidden), rt.Malloc(c.hidden), rt.Malloc(c.hidden)
+        self.proj2 = rt.Malloc(c.hidden)
+        # the fused launches need the row-major layout (the library keeps projections under 8 Mi weights in it)
+        big = 8 << 20
+        self.fused = fuse and group_size >= 32 and c.hidden % 32 == 0 and c.inter % 32 == 0 and max(
+            (qd + 2 * kvd) * c.hidden, 2 * c.inter * c.hidden, c.inter * c.hidden) < big
         self.qkv, self.attn = rt.Malloc(qd + 2 * kvd), rt.Malloc(qd)
         self.proj, self.gu, self.act = rt.Malloc(c.hidden), rt.Malloc(2 * c.inter), rt.Malloc(c.inter)
         self.logits = rt.Malloc(c.vocab)
@@ -58,27 +63,46 @@ class MLXDecoder:
         return self.rt.wrap(buf.Ptr + 4 * off, 4 * n)
 
     def step(self, stream=None):
-        """One token: embed the current token, the layer stack, logits, pick and advance."""
+        """One token: embed the current token, the layer stack, logits, pick and advance.  Where the
+        weights allow it (row-major layout: projections under 8 Mi weights) the residual add + RMSNorm
+        in front of q|k|v and gate|up and the SiLU*up in front of down run inside the product's launch
+        (goph_mlx_gemv_pre); otherwise as separate launches."""
         rt, c = self.rt, self.cfg
         n = 0
-        rt.EmbedMLX(self.hidden, self.lm, self.tok, stream); n += 1
+        cur, other = self.hidden, self.hidden2
+        rt.EmbedMLX(cur, self.lm, self.tok, stream); n += 1
         prev = None   # the projection output still to be added to the residual stream
         for e in self.L:
-            # residual add of the previous block fused with this block's input norm
-            rt.AddRMSNorm(self.hidden if prev is not None else None, self.normed, self.hidden, prev, e["input_norm"], c.hidden, 1, c.eps, stream)
-            rt.GemvMLX(self.qkv, self.normed, e["qkv"], stream)
+            if self.fused:
+                # v = cur (+ prev) -> other; q|k|v = W . RMSNorm(v)
+                rt.GemvMLXPre(self.qkv, e["qkv"], 1, cur, prev, e["input_norm"], other if prev is not None else None, c.eps, stream)
+                if prev is not None:
+                    cur, other = other, cur
+                n += 1
+            else:
+                rt.AddRMSNorm(cur if prev is not None else None, self.normed, cur, prev, e["input_norm"], c.hidden, 1, c.eps, stream)
+                rt.GemvMLX(self.qkv, self.normed, e["qkv"], stream)
+                n += 2
             q, k, v = self._sub(self.qkv, 0, self.qd), self._sub(self.qkv, self.qd, self.kvd), self._sub(self.qkv, self.qd + self.kvd, self.kvd)
             rt.QKNormRoPEAppend(q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.heads, c.kv_heads,
                                 c.head_dim, c.eps, stream)
             rt.AttnDecode(self.attn, q, e["kc"], e["vc"], self.pos, c.max_seq, c.heads, c.kv_heads, c.head_dim, self.scale, stream)
             rt.GemvMLX(self.proj, self.attn, e["o"], stream)
-            rt.AddRMSNorm(self.hidden, self.normed, self.hidden, self.proj, e["post_norm"], c.hidden, 1, c.eps, stream)
-            rt.GemvMLX(self.gu, self.normed, e["gate_up"], stream)
-            rt.SiLUMul(self.act, self._sub(self.gu, 0, c.inter), self._sub(self.gu, c.inter, c.inter), c.inter, stream)
-            rt.GemvMLX(self.proj, self.act, e["down"], stream)
-            prev = self.proj
-            n += 9
-        rt.AddRMSNorm(self.hidden, self.normed, self.hidden, prev, self.final_norm, c.hidden, 1, c.eps, stream)
+            n += 3
+            gate, up = self._sub(self.gu, 0, c.inter), self._sub(self.gu, c.inter, c.inter)
+            if self.fused:
+                rt.GemvMLXPre(self.gu, e["gate_up"], 1, cur, self.proj, e["post_norm"], other, c.eps, stream)
+                cur, other = other, cur
+                rt.GemvMLXPre(self.proj2, e["down"], 2, gate, up, None, None, c.eps, stream)
+                n += 2
+            else:
+                rt.AddRMSNorm(cur, self.normed, cur, self.proj, e["post_norm"], c.hidden, 1, c.eps, stream)
+                rt.GemvMLX(self.gu, self.normed, e["gate_up"], stream)
+                rt.SiLUMul(self.act, gate, up, c.inter, stream)
+                rt.GemvMLX(self.proj2, self.act, e["down"], stream)
+                n += 4
+            prev = self.proj2
+        rt.AddRMSNorm(None, self.normed, cur, prev, self.final_norm, c.hidden, 1, c.eps, stream)
         rt.GemvMLX(self.logits, self.normed, self.lm, stream)
         rt.ArgmaxAdvance(self.logits, c.vocab, self.tok, self.pos, self.history, self.forced, c.max_seq, stream)
         self.launches_per_step = n + 3 + (1 if self.lm.OutDim * self.lm.InDim >= (8 << 20) else 0)

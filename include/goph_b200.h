@@ -261,6 +261,14 @@ int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float
  * history_dev[*pos_dev + 1] = it, *pos_dev += 1. */
 int goph_argmax_advance(int device, const float* logits_dev, int n, int* tok_dev, int* pos_dev, int* history_dev,
                         const int* forced_dev, int history_cap, void* stream);
+/* out = W . f(x) with the operation in front of the projection folded into the product's launch:
+ *   pre_op 1  v = x (+ b when not NULL); hidden_out = v (optional; must not alias x or b);
+ *             f = RMSNorm(v) * norm_w            (residual add + norm + q|k|v or gate|up projection)
+ *   pre_op 2  f = silu(x) * b                    (activation + down projection)
+ * Row-major MLX weights (group size >= 32), batch 1, 16-byte aligned vectors; otherwise
+ * GOPH_E_UNSUPPORTED and the caller issues the operations separately. */
+int goph_mlx_gemv_pre(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, int pre_op, const float* x_dev,
+                      const float* b_dev, const float* norm_w_dev, float* hidden_out_dev, float eps, void* stream);
 /* LlamaModel.TokenEmbeddingInto for a tied MLX LM head: dequantised row *tok_dev (model/inference_helpers.go:20-44). */
 int goph_mlx_embed(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, const int* tok_dev, void* stream);
 

@@ -156,6 +156,46 @@ def test_greedy_tokens_small_model(gpu, pkg):
     assert got == want, (got, want, min(margins))
     again = dec.generate(want[:12], 40, use_graph=False)     # plain launches give the same tokens as the graph
     assert again == want
+    # the same model with norm / activation as separate launches instead of inside the products
+    layers_gpu, _, lm, final_norm = build_model(pkg, cfg, "small")
+    plain = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta), fuse=False)
+    assert dec.fused and not plain.fused and plain.launches_per_step == 0
+    assert plain.generate(want[:12], 40) == want
+    assert plain.launches_per_step > dec.launches_per_step
+
+
+def test_gemv_with_operation_in_front(gpu, pkg):
+    """goph_mlx_gemv_pre against the separate operations of the oracle."""
+    out_dim, in_dim = 768, 1024
+    w, s, b = pkg.synth.mlx_weight("pre", out_dim, in_dim, 64)
+    gpu.SetOption("mlx_layout", 1)
+    h = gpu.UploadMLXWeight(w, s, b, in_dim, out_dim, 64, True)
+    gpu.SetOption("mlx_layout", 0)
+    g = pkg.synth.rng("pre")
+    x, r, nw = (g.standard_normal(in_dim, dtype=F) for _ in range(3))
+    X, R, NW = gpu.from_numpy(x), gpu.from_numpy(r), gpu.from_numpy(nw)
+    out, hid = gpu.Malloc(out_dim), gpu.Malloc(in_dim)
+    gpu.GemvMLXPre(out, h, 1, X, R, NW, hid, 1e-6)
+    gpu.Sync()
+    assert np.array_equal(hid.Download(), x + r)
+    want = orc.mlx_gemv(od.rmsnorm(x + r, nw, 1e-6).astype(F), w, s, b, out_dim, in_dim, 64)
+    assert pkg.synth.rel_err(out.Download(), want) <= 2e-3
+    gpu.GemvMLXPre(out, h, 1, X, None, NW, None, 1e-6)           # no residual, no hidden output
+    gpu.Sync()
+    assert pkg.synth.rel_err(out.Download(), orc.mlx_gemv(od.rmsnorm(x, nw, 1e-6).astype(F), w, s, b, out_dim, in_dim, 64)) <= 2e-3
+    gpu.GemvMLXPre(out, h, 2, X, R, None, None)                   # silu(x) * r
+    gpu.Sync()
+    assert pkg.synth.rel_err(out.Download(), orc.mlx_gemv(od.silu_mul(x, r).astype(F), w, s, b, out_dim, in_dim, 64)) <= 2e-3
+    with pytest.raises(gpu.GophError):
+        gpu.GemvMLXPre(out, h, 1, X, R, NW, X)                    # hidden_out aliasing an input
+    with pytest.raises(gpu.GophError):
+        gpu.GemvMLXPre(out, h, 3, X, R, NW, None)
+    gpu.SetOption("mlx_layout", 2)
+    ht = gpu.UploadMLXWeight(w, s, b, in_dim, out_dim, 64, True)
+    gpu.SetOption("mlx_layout", 0)
+    with pytest.raises(gpu.GophError):
+        gpu.GemvMLXPre(out, ht, 1, X, R, NW, hid)                 # tiled weights: not supported, the caller splits
+    h.Free(); ht.Free()
 
 
 def test_greedy_tokens_qwen3_0_6b(gpu, pkg):
