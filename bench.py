@@ -269,7 +269,7 @@ def run_reference(args):
     }))
 
 
-def decode_rate(rt, syn, pkg):
+def decode_rate(rt, syn, pkg, cpu=False):
     """Greedy decode of the random-init Qwen3-0.6B MLX-4bit model (BASELINE config 1): every operation
     of a token step on the GPU, the step captured once as a CUDA graph; 128 prompt tokens are fed
     one by one, then 64 tokens are generated and those 64 steps are timed with CUDA events."""
@@ -311,7 +311,22 @@ def decode_rate(rt, syn, pkg):
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / 64
     weight_bytes = 335241216
-    return {"tok_s": round(1e3 / ms, 1), "ms_per_token": round(ms, 4), "launches_per_token": dec.launches_per_step,
+    cpu_tok_s = None
+    if cpu:
+        # the same model through the CPU restatement of the reference's loop, a few tokens on all cores
+        from oracle import binding as orc
+        from oracle import decode as od
+        ocfg = od.DecodeConfig(hidden=HIDDEN, layers=LAYERS, heads=16, kv_heads=8, head_dim=128, inter=FFN, vocab=VOCAB,
+                               eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
+        lo = [{**{n: (d[n], *shapes[n]) for n in shapes}, **{n: d[n] for n in ("input_norm", "post_norm", "q_norm", "k_norm")}}
+              for d in layers]
+        oracle = od.OracleDecoder(ocfg, od.MLXWeights(orc, ocfg, lo, lm, np.ones(HIDDEN, dtype=F), nthreads=os.cpu_count() or 1))
+        oracle.step(prompt[0], 0)
+        t0 = time.perf_counter()
+        for p in range(1, 5):
+            oracle.step(prompt[p], p)
+        cpu_tok_s = round(4 / (time.perf_counter() - t0), 2)
+    return {"tok_s": round(1e3 / ms, 1), "cpu_restatement_tok_s": cpu_tok_s, "cpu_cores": (os.cpu_count() or 1) if cpu else None, "ms_per_token": round(ms, 4), "launches_per_token": dec.launches_per_step,
             "positions": "128..191 after a 128-token prompt fed token by token", "batch": 1,
             "weight_GBps": round(weight_bytes / ms / 1e6, 1),
             "gate": "64 greedy tokens identical to the CPU restatement (tests/test_gpu_decode.py::test_greedy_tokens_qwen3_0_6b)"}
@@ -546,7 +561,7 @@ def run_ours(args):
         }
         if not args.no_extra and world == 1:
             line["extra"] = extras(wl)
-            line["decode"] = decode_rate(rt, syn, pkg)
+            line["decode"] = decode_rate(rt, syn, pkg, cpu=not args.no_cpu)
         if not args.no_cpu and world == 1:
             from oracle import binding as orc
             gbs_cpu, ms_cpu, cores = time_cpu(orc, syn, 3, 1, 4)
