@@ -195,7 +195,9 @@ attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const f
   for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, sh[i]);
   float sum = 0.f;
   for (int i = threadIdx.x; i < nloc; i += blockDim.x) {
-    const float e = scores[i] == -CUDART_INF_F ? 0.f : (float)exp((double)(scores[i] - mx));
+    // single-precision exp (2 ulp) where the reference rounds an f64 exp to f32: the FP64 pipe of
+    // this part is too slow for a per-position operation
+    const float e = scores[i] == -CUDART_INF_F ? 0.f : expf(scores[i] - mx);
     scores[i] = e;
     sum += e;
   }
@@ -241,20 +243,27 @@ attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const f
   if (!s_last) return;
   __threadfence();
   const float* base = scratch + (size_t)head * kAttnMaxSplits * stride;
-  float m = -CUDART_INF_F;
-  for (int s2 = 0; s2 < splits; ++s2) m = fmaxf(m, __ldcg(base + s2 * stride));
-  float total = 0.f;
-  for (int s2 = 0; s2 < splits; ++s2) {
-    const float ms = __ldcg(base + s2 * stride);
-    if (ms != -CUDART_INF_F) total = fmaf(__ldcg(base + s2 * stride + 1), (float)exp((double)(ms - m)), total);
+  // the splits' rescaling factors a_s = exp(m_s - m), computed once
+  __shared__ float fac[kAttnMaxSplits];
+  __shared__ float s_inv;
+  if (threadIdx.x < 32) {
+    float m = -CUDART_INF_F;
+    for (int s2 = 0; s2 < splits; ++s2) m = fmaxf(m, __ldcg(base + s2 * stride));
+    float mine_f = 0.f;
+    if (lane < splits) {
+      const float ms = __ldcg(base + lane * stride);
+      mine_f = ms == -CUDART_INF_F ? 0.f : expf(ms - m);
+      fac[lane] = mine_f;
+    }
+    float total = lane < splits ? __fmul_rn(__ldcg(base + lane * stride + 1), mine_f) : 0.f;
+    total = warp_sum(total);
+    if (lane == 0) s_inv = __fdiv_rn(1.f, total);
   }
-  const float inv = __fdiv_rn(1.f, total);
+  __syncthreads();
+  const float inv = s_inv;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float r = 0.f;
-    for (int s2 = 0; s2 < splits; ++s2) {
-      const float ms = __ldcg(base + s2 * stride);
-      if (ms != -CUDART_INF_F) r = fmaf(__ldcg(base + s2 * stride + 2 + d), (float)exp((double)(ms - m)), r);
-    }
+    for (int s2 = 0; s2 < splits; ++s2) r = fmaf(__ldcg(base + s2 * stride + 2 + d), fac[s2], r);
     out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
   }
   if (threadIdx.x == 0) counters[head] = 0;
@@ -266,7 +275,7 @@ __global__ void silu_mul_kernel(float* __restrict__ out, const float* __restrict
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float g = gate[i];
-  out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, (float)exp((double)(-g)))), up[i]);
+  out[i] = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.f, expf(-g))), up[i]);  // expf: see attn_decode_kernel
 }
 
 // First maximum of logits[0..n): kArgmaxCtas CTAs reduce a slice each; the last one to arrive

@@ -187,11 +187,13 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
         if (a.pre_hidden && blockIdx.x == 0) *reinterpret_cast<float4*>(a.pre_hidden + e0) = v;
         ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
       } else {
+        // single-precision exp (2 ulp) where the reference rounds an f64 exp to f32: every CTA
+        // repeats this for the whole vector and the FP64 pipe of this part is slow
         const float4 u = *reinterpret_cast<const float4*>(a.pre_b + e0);
-        v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.f, (float)exp((double)(-v.x)))), u.x);
-        v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.f, (float)exp((double)(-v.y)))), u.y);
-        v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.f, (float)exp((double)(-v.z)))), u.z);
-        v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.f, (float)exp((double)(-v.w)))), u.w);
+        v.x = __fmul_rn(__fdiv_rn(v.x, __fadd_rn(1.f, expf(-v.x))), u.x);
+        v.y = __fmul_rn(__fdiv_rn(v.y, __fadd_rn(1.f, expf(-v.y))), u.y);
+        v.z = __fmul_rn(__fdiv_rn(v.z, __fadd_rn(1.f, expf(-v.z))), u.z);
+        v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.f, expf(-v.w))), u.w);
       }
     }
     xs[idx] = v;

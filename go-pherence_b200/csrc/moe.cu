@@ -520,7 +520,8 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
       if (PHASE == 0) {
         if (r_of_lane == 0) {
           // kernels.SiLU then the multiply (backends/simd/kernels/activation.go:15-24)
-          const float sv = __fdiv_rn(mine, __fadd_rn(1.0f, (float)exp((double)(-mine))));
+          // single-precision exp (2 ulp) where the reference rounds an f64 exp: the FP64 pipe is slow
+          const float sv = __fdiv_rn(mine, __fadd_rn(1.0f, expf(-mine)));
           dst[(size_t)item * out_rows + cur_rows.row] = __fmul_rn(sv, other);
         }
       } else {
