@@ -132,100 +132,170 @@ qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, c
   }
 }
 
-// Grid (query heads, position splits): a CTA of 8 warps takes every split-th block of positions
-// of its head.  Scores: a warp takes positions four at a time so their loads are in flight
-// together; the CTA's softmax numerators use its own maximum (f64 exp); a warp accumulates
-// e_t * v_t for all of head_dim (lane d, d+32, ...).  Each CTA leaves {max, sum, vector} in global
-// scratch and the last CTA of a head to arrive merges the splits: out = sum_s a_s v_s / sum_s a_s l_s
-// with a_s = exp(m_s - m).  Scores live in dynamic shared memory (max_seq floats).
-constexpr int kAttnWarps = 8, kAttnMaxEPL = 8, kAttnMaxSplits = 16, kAttnMaxHeads = 256;
+// Grid (query heads, position splits): a CTA of kAttnWarps warps takes every split-th block of
+// kAttnWarps*4 positions of its head.  Scores: a warp takes four positions at a time so their K and V
+// rows are all in flight together (the V rows are requested before the softmax); the CTA's softmax
+// numerators use its own maximum; a warp accumulates e_t * v_t for all of head_dim (lane d, d+32, ..).
+// One split (sequences up to a few hundred positions): the CTA writes the head's output.  Several
+// splits: each leaves {max, sum, vector} in global scratch and the head's last CTA merges them,
+// out = sum_s a_s v_s / sum_s a_s l_s with a_s = exp(m_s - m).
+// FUSED: the kernel also does what qk_norm_rope_append_kernel does — every warp norms and rotates
+// its head's q for itself; the warp that owns the current position norms and rotates the new k,
+// uses it and the new v from the projection output instead of the cache, and (for the first head
+// of a KV group) writes both into the cache rows.  No CTA reads the cache row being written.
+constexpr int kAttnWarps = 32, kAttnMaxSplits = 16, kAttnMaxHeads = 256;
+
+template <int EPL>
+__device__ __forceinline__ void norm_rope_head(float (&x)[EPL], const float* __restrict__ w, const float* __restrict__ trow,
+                                               int head_dim, float eps, int lane) {
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) ss = fmaf(x[e], x[e], ss);
+    ss = warp_sum(ss);
+    const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)head_dim), eps)));
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) x[e] = __fmul_rn(__fmul_rn(x[e], inv), w[lane + 32 * e]);
+  }
+#pragma unroll
+  for (int e = 0; e < EPL / 2; ++e) {  // pairs (i, i + head_dim/2) sit in the same lane
+    const int i = lane + 32 * e;
+    const float c = trow[2 * i], sn = trow[2 * i + 1];
+    const float x0 = x[e], x1 = x[e + EPL / 2];
+    x[e] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, sn));
+    x[e + EPL / 2] = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, c));
+  }
+}
+
+struct AttnArgs {
+  float* out;
+  const float* q;        // FUSED: raw projection output; else already normed and rotated
+  const float* k_new;    // FUSED: raw k and v of the current position
+  const float* v_new;
+  const float* q_norm;   // FUSED: head-dim RMSNorm weights or null
+  const float* k_norm;
+  const float* table;    // FUSED: RoPE table [max_seq][head_dim/2][2]
+  float* kcache;
+  float* vcache;
+  const int* pos_dev;
+  int heads, kv_heads, head_dim;
+  float scale, eps;
+  float* scratch;
+  unsigned int* counters;
+};
+
+template <int EPL, bool FUSED>
 __global__ void __launch_bounds__(kAttnWarps * 32)
-attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const float* __restrict__ kcache,
-                   const float* __restrict__ vcache, const int* __restrict__ pos_dev, int heads, int kv_heads,
-                   int head_dim, float scale, float* __restrict__ scratch, unsigned int* __restrict__ counters) {
+attn_decode_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ float scores[];
   __shared__ float sh[kAttnWarps];
-  __shared__ float part[kAttnWarps][256];
+  __shared__ float part[kAttnWarps][EPL * 32];
   __shared__ int s_last;
   pdl_begin();
-  const int seq = *pos_dev + 1;
-  const int head = blockIdx.x, kvh = head / (heads / kv_heads);
+  const int pos = *a.pos_dev, seq = pos + 1;
+  const int heads = a.heads, kv_heads = a.kv_heads, head_dim = a.head_dim;
+  const int head = blockIdx.x, per = heads / kv_heads, kvh = head / per;
   const int splits = gridDim.y, split = blockIdx.y;
   const size_t kvd = (size_t)kv_heads * head_dim;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int epl = head_dim / 32;  // elements per lane
-  const float* kbase = kcache + (size_t)kvh * head_dim;
-  const float* vbase = vcache + (size_t)kvh * head_dim;
-  // this CTA's positions: split, split + splits, ... in units of kAttnWarps*4 positions, i.e. local
-  // index i -> position t(i) = ((i / B) * splits + split) * B + i % B with B = 4 * kAttnWarps
+  const float* kbase = a.kcache + (size_t)kvh * head_dim;
+  const float* vbase = a.vcache + (size_t)kvh * head_dim;
   constexpr int B = 4 * kAttnWarps;
   const int nblocks = (seq + B - 1) / B;
   const int my_blocks = nblocks > split ? (nblocks - split + splits - 1) / splits : 0;
   auto pos_of = [&](int i) { return ((i / B) * splits + split) * B + (i % B); };
   const int nloc = my_blocks * B;  // local indices (some past seq in the last block)
-  float qr[kAttnMaxEPL];
+  float qr[EPL];
 #pragma unroll
-  for (int e = 0; e < kAttnMaxEPL; ++e) qr[e] = e < epl ? q[(size_t)head * head_dim + lane + 32 * e] : 0.f;
-  for (int i0 = warp; i0 < nloc; i0 += B) {
-    float d[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int e = 0; e < EPL; ++e) qr[e] = a.q[(size_t)head * head_dim + lane + 32 * e];
+  if (FUSED) norm_rope_head<EPL>(qr, a.q_norm, a.table + (size_t)pos * head_dim, head_dim, a.eps, lane);
+  float acc[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
+  // One block of positions per iteration; with several iterations the accumulators are rescaled to
+  // the running maximum (the usual single-pass softmax); the common case is one iteration.
+  float run_max = -CUDART_INF_F, run_sum = 0.f;
+  for (int blk = 0; blk < my_blocks; ++blk) {
+    float kv_k[4][EPL], kv_v[4][EPL];
+    int tt[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int t = pos_of(i0 + j * kAttnWarps);
-      if (t < seq) {
+      const int t = pos_of(blk * B + warp + j * kAttnWarps);
+      tt[j] = t;
+      const bool cur = FUSED && t == pos;
 #pragma unroll
-        for (int e = 0; e < kAttnMaxEPL; ++e)
-          if (e < epl) d[j] = fmaf(qr[e], kbase[(size_t)t * kvd + lane + 32 * e], d[j]);
+      for (int e = 0; e < EPL; ++e) {
+        const size_t off = (size_t)t * kvd + lane + 32 * e;
+        kv_k[j][e] = t < seq ? (cur ? a.k_new[(size_t)kvh * head_dim + lane + 32 * e] : kbase[off]) : 0.f;
+        kv_v[j][e] = t < seq ? (cur ? a.v_new[(size_t)kvh * head_dim + lane + 32 * e] : vbase[off]) : 0.f;
       }
     }
+    float sc[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float r = warp_sum(d[j]);
-      const int i = i0 + j * kAttnWarps;
-      if (lane == 0) scores[i] = pos_of(i) < seq ? __fmul_rn(r, scale) : -CUDART_INF_F;
-    }
-  }
-  __syncthreads();
-  float mx = -CUDART_INF_F;
-  for (int i = threadIdx.x; i < nloc; i += blockDim.x) mx = fmaxf(mx, scores[i]);
+      if (FUSED && tt[j] == pos) {  // the new position: norm, rotate, and (one warp per KV head) append
+        norm_rope_head<EPL>(kv_k[j], a.k_norm, a.table + (size_t)pos * head_dim, head_dim, a.eps, lane);
+        if (head % per == 0) {
 #pragma unroll
-  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if (lane == 0) sh[warp] = mx;
-  __syncthreads();
-  mx = sh[0];
-  for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, sh[i]);
-  float sum = 0.f;
-  for (int i = threadIdx.x; i < nloc; i += blockDim.x) {
+          for (int e = 0; e < EPL; ++e) {
+            a.kcache[(size_t)pos * kvd + (size_t)kvh * head_dim + lane + 32 * e] = kv_k[j][e];
+            a.vcache[(size_t)pos * kvd + (size_t)kvh * head_dim + lane + 32 * e] = kv_v[j][e];
+          }
+        }
+      }
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) d = fmaf(qr[e], kv_k[j][e], d);
+      d = warp_sum(d);
+      sc[j] = tt[j] < seq ? __fmul_rn(d, a.scale) : -CUDART_INF_F;
+    }
+    // block maximum
+    float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+    if (lane == 0) sh[warp] = mx;
+    __syncthreads();
+    mx = sh[0];
+#pragma unroll
+    for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, sh[i]);
+    const float new_max = fmaxf(run_max, mx);
     // single-precision exp (2 ulp) where the reference rounds an f64 exp to f32: the FP64 pipe of
     // this part is too slow for a per-position operation
-    const float e = scores[i] == -CUDART_INF_F ? 0.f : expf(scores[i] - mx);
-    scores[i] = e;
-    sum += e;
-  }
-  sum = block_sum(sum, sh);
-  float acc[kAttnMaxEPL];
+    const float rescale = run_max == -CUDART_INF_F ? 0.f : expf(run_max - new_max);
+    float local = 0.f;
 #pragma unroll
-  for (int e = 0; e < kAttnMaxEPL; ++e) acc[e] = 0.f;
-  for (int i0 = warp; i0 < nloc; i0 += B) {
-    float vv[4][kAttnMaxEPL], p[4];
+    for (int e = 0; e < EPL; ++e) acc[e] *= rescale;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int i = i0 + j * kAttnWarps, t = pos_of(i);
-      p[j] = scores[i];
+      const float p = sc[j] == -CUDART_INF_F ? 0.f : expf(sc[j] - new_max);
+      local += p;
 #pragma unroll
-      for (int e = 0; e < kAttnMaxEPL; ++e) vv[j][e] = (t < seq && e < epl) ? vbase[(size_t)t * kvd + lane + 32 * e] : 0.f;
+      for (int e = 0; e < EPL; ++e) acc[e] = fmaf(p, kv_v[j][e], acc[e]);
     }
+    __syncthreads();  // sh is reused
+    if (lane == 0) sh[warp] = local;   // every lane of the warp holds the same four p: one copy per warp
+    __syncthreads();
+    float bsum = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int e = 0; e < kAttnMaxEPL; ++e) acc[e] = fmaf(p[j], vv[j][e], acc[e]);
+    for (int i = 0; i < kAttnWarps; ++i) bsum += sh[i];
+    run_sum = fmaf(run_sum, rescale, bsum);
+    run_max = new_max;
+    __syncthreads();
   }
 #pragma unroll
-  for (int e = 0; e < kAttnMaxEPL; ++e)
-    if (e < epl) part[warp][lane + 32 * e] = acc[e];
+  for (int e = 0; e < EPL; ++e) part[warp][lane + 32 * e] = acc[e];
   __syncthreads();
+  if (splits == 1) {
+    const float inv = __fdiv_rn(1.f, run_sum);
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+      float r = 0.f;
+#pragma unroll
+      for (int w = 0; w < kAttnWarps; ++w) r += part[w][d];
+      a.out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
+    }
+    return;
+  }
   // ---- this split's {max, sum, vector} to scratch; the head's last CTA merges -------------------
   const int stride = 2 + 256;
-  float* mine = scratch + ((size_t)head * kAttnMaxSplits + split) * stride;
+  float* mine = a.scratch + ((size_t)head * kAttnMaxSplits + split) * stride;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float r = 0.f;
 #pragma unroll
@@ -233,16 +303,16 @@ attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const f
     mine[2 + d] = r;
   }
   if (threadIdx.x == 0) {
-    mine[0] = mx;
-    mine[1] = sum;
+    mine[0] = run_max;
+    mine[1] = run_sum;
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(counters + head, 1u) == (unsigned)splits - 1;
+  if (threadIdx.x == 0) s_last = atomicAdd(a.counters + head, 1u) == (unsigned)splits - 1;
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const float* base = scratch + (size_t)head * kAttnMaxSplits * stride;
+  const float* base = a.scratch + (size_t)head * kAttnMaxSplits * stride;
   // the splits' rescaling factors a_s = exp(m_s - m), computed once
   __shared__ float fac[kAttnMaxSplits];
   __shared__ float s_inv;
@@ -264,9 +334,9 @@ attn_decode_kernel(float* __restrict__ out, const float* __restrict__ q, const f
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float r = 0.f;
     for (int s2 = 0; s2 < splits; ++s2) r = fmaf(__ldcg(base + s2 * stride + 2 + d), fac[s2], r);
-    out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
+    a.out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
   }
-  if (threadIdx.x == 0) counters[head] = 0;
+  if (threadIdx.x == 0) a.counters[head] = 0;
 }
 
 // out[i] = silu(gate[i]) * up[i]; gate and up are the two halves of one fused projection output.
@@ -422,18 +492,14 @@ GOPH_API int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_d
                    k_norm_dev, rope_table_dev, pos_dev, kcache_dev, vcache_dev, heads, kv_heads, head_dim, eps);
 }
 
-GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
-                              const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,
-                              int head_dim, float scale, void* stream) {
-  clear_error();
-  if (!out_dev || !q_dev || !kcache_dev || !vcache_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_attn_decode: nil buffer");
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim < 32 || head_dim > 256 || head_dim % 32)
-    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim a multiple of 32 up to 256)", heads,
-                kv_heads, head_dim);
-  if ((size_t)max_seq * 4 > 160 * 1024) return fail(GOPH_E_UNSUPPORTED, "max_seq=%d scores do not fit shared memory", max_seq);
-  if (max_seq <= 0 || (size_t)max_seq * 4 > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "max_seq=%d scores do not fit shared memory", max_seq);
+static int attn_launch(int device, AttnArgs& a, int max_seq, bool fused, void* stream) {
+  if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.head_dim < 64 || a.head_dim > 256 || a.head_dim % 64)
+    return fail(GOPH_E_UNSUPPORTED, "attention dims heads=%d kv_heads=%d head_dim=%d (head_dim 64, 128 or 256)", a.heads,
+                a.kv_heads, a.head_dim);
+  if (a.head_dim == 192) return fail(GOPH_E_UNSUPPORTED, "head_dim 192");
+  if (a.heads > kAttnMaxHeads) return fail(GOPH_E_UNSUPPORTED, "at most %d query heads", kAttnMaxHeads);
+  if (max_seq <= 0) return fail(GOPH_E_INVALID, "max_seq=%d", max_seq);
   if (int rc = use_device(device)) return rc;
-  if (heads > kAttnMaxHeads) return fail(GOPH_E_UNSUPPORTED, "at most %d query heads", kAttnMaxHeads);
   static float* scratch[kMaxDevices] = {};
   static unsigned int* counters[kMaxDevices] = {};
   if (!counters[device]) {
@@ -441,16 +507,67 @@ GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, co
     GOPH_CUDA(cudaMalloc(&counters[device], kAttnMaxHeads * sizeof(unsigned int)));
     GOPH_CUDA(cudaMemset(counters[device], 0, kAttnMaxHeads * sizeof(unsigned int)));
   }
-  // enough CTAs that every warp has about one round of positions at the longest sequence
-  int splits = (max_seq + 4 * kAttnWarps - 1) / (4 * kAttnWarps);
-  const int want = (2 * device_state(device).sm_count + heads - 1) / heads;
-  if (splits > want) splits = want;
+  a.scratch = scratch[device];
+  a.counters = counters[device];
+  // one CTA per head takes two blocks of 128 positions without help; longer caches are split
+  int splits = (max_seq + 8 * kAttnWarps - 1) / (8 * kAttnWarps);
   if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
   if (splits < 1) splits = 1;
-  const size_t smem = ((size_t)max_seq + 4 * kAttnWarps) * 4;
-  GOPH_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  return op_launch(attn_decode_kernel, dim3(heads, splits), kAttnWarps * 32, smem, stream, out_dev, q_dev, kcache_dev, vcache_dev,
-                   pos_dev, heads, kv_heads, head_dim, scale, scratch[device], counters[device]);
+  const dim3 grid(a.heads, splits);
+  const int threads = kAttnWarps * 32;
+  if (a.head_dim == 64) return fused ? op_launch(attn_decode_kernel<2, true>, grid, threads, 0, stream, a)
+                                     : op_launch(attn_decode_kernel<2, false>, grid, threads, 0, stream, a);
+  if (a.head_dim == 128) return fused ? op_launch(attn_decode_kernel<4, true>, grid, threads, 0, stream, a)
+                                      : op_launch(attn_decode_kernel<4, false>, grid, threads, 0, stream, a);
+  return fused ? op_launch(attn_decode_kernel<8, true>, grid, threads, 0, stream, a)
+               : op_launch(attn_decode_kernel<8, false>, grid, threads, 0, stream, a);
+}
+
+GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
+                              const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,
+                              int head_dim, float scale, void* stream) {
+  clear_error();
+  if (!out_dev || !q_dev || !kcache_dev || !vcache_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_attn_decode: nil buffer");
+  AttnArgs a;
+  memset(&a, 0, sizeof a);
+  a.out = out_dev;
+  a.q = q_dev;
+  a.kcache = const_cast<float*>(kcache_dev);
+  a.vcache = const_cast<float*>(vcache_dev);
+  a.pos_dev = pos_dev;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.scale = scale;
+  return attn_launch(device, a, max_seq, false, stream);
+}
+
+GOPH_API int goph_attn_decode_fused(int device, float* out_dev, const float* q_dev, const float* k_dev, const float* v_dev,
+                                    const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
+                                    const int* pos_dev, float* kcache_dev, float* vcache_dev, int max_seq, int heads,
+                                    int kv_heads, int head_dim, float scale, float eps, void* stream) {
+  clear_error();
+  if (!out_dev || !q_dev || !k_dev || !v_dev || !rope_table_dev || !kcache_dev || !vcache_dev || !pos_dev)
+    return fail(GOPH_E_INVALID, "goph_attn_decode_fused: nil buffer");
+  if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fail(GOPH_E_INVALID, "QNorm without KNorm");
+  AttnArgs a;
+  memset(&a, 0, sizeof a);
+  a.out = out_dev;
+  a.q = q_dev;
+  a.k_new = k_dev;
+  a.v_new = v_dev;
+  a.q_norm = q_norm_dev;
+  a.k_norm = k_norm_dev;
+  a.table = rope_table_dev;
+  a.kcache = kcache_dev;
+  a.vcache = vcache_dev;
+  a.pos_dev = pos_dev;
+  a.heads = heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.scale = scale;
+  a.eps = eps;
+  return attn_launch(device, a, max_seq, true, stream);
 }
 
 GOPH_API int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float* up_dev, int n, void* stream) {

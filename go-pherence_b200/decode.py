@@ -3,7 +3,8 @@
 Host-side mirror of GPUModel.Generate (model/gpu_forward.go:993-1357) over the C ABI: the seven
 projections of a layer run as four fused products (q|k|v, o, gate|up, down) through goph_mlx_gemv,
 everything between them through the decode-step operations (goph_add_rmsnorm,
-goph_qk_norm_rope_append, goph_attn_decode, goph_silu_mul, goph_argmax_advance, goph_mlx_embed).
+goph_qk_norm_rope_append, goph_attn_decode, goph_silu_mul, goph_argmax_advance, goph_mlx_embed) or
+their fused forms (goph_mlx_gemv_pre, goph_attn_decode_fused: five launches per layer).
 The position, the current token, the prompt and the produced tokens live in device memory, so the
 whole step is captured once as a CUDA graph and replayed per token — prompt tokens included (they
 are fed one by one, as the reference's sequential loop does).  torch is used for stream capture only.
@@ -84,11 +85,17 @@ class MLXDecoder:
                 rt.GemvMLX(self.qkv, self.normed, e["qkv"], stream)
                 n += 2
             q, k, v = self._sub(self.qkv, 0, self.qd), self._sub(self.qkv, self.qd, self.kvd), self._sub(self.qkv, self.qd + self.kvd, self.kvd)
-            rt.QKNormRoPEAppend(q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.heads, c.kv_heads,
-                                c.head_dim, c.eps, stream)
-            rt.AttnDecode(self.attn, q, e["kc"], e["vc"], self.pos, c.max_seq, c.heads, c.kv_heads, c.head_dim, self.scale, stream)
+            if self.fused:
+                rt.AttnDecodeFused(self.attn, q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.max_seq,
+                                   c.heads, c.kv_heads, c.head_dim, self.scale, c.eps, stream)
+                n += 1
+            else:
+                rt.QKNormRoPEAppend(q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.heads, c.kv_heads,
+                                    c.head_dim, c.eps, stream)
+                rt.AttnDecode(self.attn, q, e["kc"], e["vc"], self.pos, c.max_seq, c.heads, c.kv_heads, c.head_dim, self.scale, stream)
+                n += 2
             rt.GemvMLX(self.proj, self.attn, e["o"], stream)
-            n += 3
+            n += 1
             gate, up = self._sub(self.gu, 0, c.inter), self._sub(self.gu, c.inter, c.inter)
             if self.fused:
                 rt.GemvMLXPre(self.gu, e["gate_up"], 1, cur, self.proj, e["post_norm"], other, c.eps, stream)

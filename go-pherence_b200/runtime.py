@@ -32,7 +32,7 @@ EXPORTS = [
     "goph_fp8_gemm_host",
     "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
     "goph_moe_forward_logits", "goph_moe_last_routing",
-    "goph_add_rmsnorm", "goph_qk_norm_rope_append", "goph_attn_decode", "goph_silu_mul", "goph_argmax_advance", "goph_mlx_embed", "goph_mlx_gemv_pre",
+    "goph_add_rmsnorm", "goph_qk_norm_rope_append", "goph_attn_decode", "goph_attn_decode_fused", "goph_silu_mul", "goph_argmax_advance", "goph_mlx_embed", "goph_mlx_gemv_pre",
     "goph_shard_rows", "goph_gather_create", "goph_gather_export", "goph_gather_open_peer", "goph_gather_attach_local",
     "goph_gather_free", "goph_gather_status", "goph_gather_shard_buffer", "goph_gather_all",
     "goph_mlx_gemm_allgather", "goph_gguf_project_allgather", "goph_fp8_gemm_allgather", "goph_moe_forward_sharded",
@@ -618,3 +618,11 @@ def GemvMLXPre(out, w, preOp, x, b, normW, hiddenOut, eps=1e-6, stream=None):
     """out = W . f(x): preOp 1 = RMSNorm(x (+ b)) * normW with hiddenOut = x (+ b); preOp 2 = silu(x) * b."""
     _check(lib().goph_mlx_gemv_pre(_ptr(out), C.c_uint64(out.n), _mlx_handle(w), int(preOp), _ptr(x), _ptr(b), _ptr(normW),
                                    _ptr(hiddenOut), C.c_float(eps), _stream_ptr(stream)))
+
+
+def AttnDecodeFused(out, q, k, v, qNorm, kNorm, ropeTable, pos, kCache, vCache, maxSeq, heads, kvHeads, headDim, scale,
+                    eps=1e-6, stream=None):
+    """QKNormRoPEAppend + AttnDecode in one launch (q, k, v: raw projection outputs of the current position)."""
+    _check(lib().goph_attn_decode_fused(_device, _ptr(out), _ptr(q), _ptr(k), _ptr(v), _ptr(qNorm), _ptr(kNorm), _ptr(ropeTable),
+                                        _ptr(pos), _ptr(kCache), _ptr(vCache), int(maxSeq), int(heads), int(kvHeads),
+                                        int(headDim), C.c_float(scale), C.c_float(eps), _stream_ptr(stream)))

@@ -254,6 +254,12 @@ int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_dev, const
 int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
                      const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,
                      int head_dim, float scale, void* stream);
+/* goph_qk_norm_rope_append and goph_attn_decode in one launch: q_dev, k_dev, v_dev are the raw
+ * projection outputs of the current position; the new k and v are also written into their cache rows. */
+int goph_attn_decode_fused(int device, float* out_dev, const float* q_dev, const float* k_dev, const float* v_dev,
+                           const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
+                           const int* pos_dev, float* kcache_dev, float* vcache_dev, int max_seq, int heads,
+                           int kv_heads, int head_dim, float scale, float eps, void* stream);
 /* simd.VecSiLUMul (backends/simd/kernels/activation.go:15-24). */
 int goph_silu_mul(int device, float* out_dev, const float* gate_dev, const float* up_dev, int n, void* stream);
 /* ArgmaxLogits (model/inference_helpers.go:248-261: the first maximum) and the bookkeeping of the

@@ -32,10 +32,14 @@ def test_add_rmsnorm(gpu, pkg):
     assert np.allclose(nrm.Download(), od.rmsnorm(a + b, w, 1e-6), rtol=2e-6, atol=1e-7)
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,qk_norm", [(16, 8, 128, True), (4, 2, 64, False), (8, 8, 128, True)])
-def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, qk_norm):
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,qk_norm,max_seq,steps", [
+    (16, 8, 128, True, 96, 70), (4, 2, 64, False, 96, 70), (8, 8, 128, True, 96, 70), (4, 1, 256, True, 96, 40),
+    (8, 4, 128, True, 1024, 600),     # long cache: the positions are split over several CTAs per head
+])
+def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, qk_norm, max_seq, steps, fused):
     g = pkg.synth.rng("attn", heads, head_dim)
-    max_seq, kvd = 96, kv_heads * head_dim
+    kvd = kv_heads * head_dim
     table = od.rope_table(max_seq, head_dim, 1e6)
     T = gpu.from_numpy(table.reshape(-1))
     qn = g.standard_normal(head_dim, dtype=F) if qk_norm else None
@@ -48,15 +52,20 @@ def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, 
     pos_buf = gpu.MallocBytes(4)
     out = gpu.Malloc(heads * head_dim)
     scale = 1.0 / np.sqrt(head_dim)
-    for pos in range(70):
+    checks = {0, 1, 31, 32, 127, 128, 129, 255, 256, 257, steps - 1}
+    for pos in range(steps):
         q = g.standard_normal(heads * head_dim, dtype=F)
         k = g.standard_normal(kvd, dtype=F)
         v = g.standard_normal(kvd, dtype=F)
         pos_buf.UploadBytes(np.array([pos], dtype=np.int32).view(np.uint8))
         Q, K, V = gpu.from_numpy(q), gpu.from_numpy(k), gpu.from_numpy(v)
-        gpu.QKNormRoPEAppend(Q, K, V, QN, KN, T, pos_buf, kc, vc, heads, kv_heads, head_dim, 1e-6)
-        gpu.AttnDecode(out, Q, kc, vc, pos_buf, max_seq, heads, kv_heads, head_dim, scale)
-        gpu.Sync()
+        if fused:
+            gpu.AttnDecodeFused(out, Q, K, V, QN, KN, T, pos_buf, kc, vc, max_seq, heads, kv_heads, head_dim, scale, 1e-6)
+        else:
+            gpu.QKNormRoPEAppend(Q, K, V, QN, KN, T, pos_buf, kc, vc, heads, kv_heads, head_dim, 1e-6)
+            gpu.AttnDecode(out, Q, kc, vc, pos_buf, max_seq, heads, kv_heads, head_dim, scale)
+        if pos in checks:
+            gpu.Sync()
         rq, rk = q.copy(), k.copy()
         if qk_norm:
             rq = np.concatenate([od.rmsnorm(rq[h * head_dim:(h + 1) * head_dim], qn, 1e-6) for h in range(heads)]).astype(F)
@@ -64,8 +73,9 @@ def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, 
         od.apply_rope(rq, table, pos, heads, head_dim)
         od.apply_rope(rk, table, pos, kv_heads, head_dim)
         ref_k[pos], ref_v[pos] = rk, v
-        if pos in (0, 1, 31, 32, 69):
-            assert np.allclose(Q.Download(), rq, rtol=1e-5, atol=1e-6)
+        if pos in checks:
+            if not fused:
+                assert np.allclose(Q.Download(), rq, rtol=1e-5, atol=1e-6)
             assert np.allclose(kc.Download()[pos * kvd:(pos + 1) * kvd], rk, rtol=1e-5, atol=1e-6)
             assert np.array_equal(vc.Download()[pos * kvd:(pos + 1) * kvd], v)
             want = od.attention(rq, ref_k, ref_v, pos + 1, heads, kv_heads, head_dim, scale)
