@@ -96,8 +96,8 @@ struct goph_gguf_matrix {
   uint32_t magic;
   int device;
   int qtype, in_dim, out_dim;
-  uint8_t* data;   // Q4_K: blocks; Q8_0: biased int8 plane
-  uint16_t* d16;   // Q8_0 only: f16 scales
+  uint8_t* data;   // Q4_K, Q5_K: blocks; Q8_0: biased int8 plane; Q6_K: low-nibble plane
+  uint16_t* d16;   // Q8_0: f16 scales; Q6_K: two-bit highs, int8 scales and f16 d, one plane after another
   uint8_t* tiled;  // tensor-core layout (data and d16 are then null): one stage per 128 rows x 256 elements
   uint64_t bytes;
 };

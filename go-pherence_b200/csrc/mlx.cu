@@ -816,10 +816,12 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   return GOPH_OK;
 }
 
-// Not part of the public header: tuning aid used by the in-tree microbenchmarks.
+// Tuning aid: the cycle counters CTA 0 of the tensor-core kernel wrote under option mlx_probe.
 GOPH_API int goph_debug_probe(int device, long long* out32) {
-  if (use_device(device)) return -1;
-  return mlx_mma_probe(device, out32);
+  clear_error();
+  if (!out32) return fail(GOPH_E_INVALID, "goph_debug_probe: nil result pointer");
+  if (int rc = use_device(device)) return rc;
+  return mlx_mma_probe(device, out32) == 0 ? GOPH_OK : fail(GOPH_E_CUDA, "goph_debug_probe: copy failed");
 }
 
 GOPH_API uint64_t goph_mlx_resident_bytes(const goph_mlx_weight* w) {

@@ -20,7 +20,7 @@ from __graft_entry__ import load_package  # noqa: E402
 
 
 def algorithmic_bytes(fmt, out_dim, in_dim, batch):
-    per_weight = {"mlx4": 0.5625, "q4k": 0.5625, "q8_0": 1.0625, "fp8": 1.0}[fmt]
+    per_weight = {"mlx4": 0.5625, "q4k": 0.5625, "q5k": 0.6875, "q6k": 0.8203125, "q8_0": 1.0625, "fp8": 1.0}[fmt]
     extra = 4 * out_dim if fmt == "fp8" else 0
     return out_dim * in_dim * per_weight + extra + batch * in_dim * 4 + batch * out_dim * 4
 
@@ -40,9 +40,9 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     if fmt == "mlx4":
         w, s, b = syn.mlx_weight("mb", out_dim, in_dim, 64)
         handles = [rt.UploadMLXWeight(w, s, b, in_dim, out_dim, 64, True) for _ in range(copies)]
-    elif fmt in ("q4k", "q8_0"):
-        qt = rt.GGUF_Q4_K if fmt == "q4k" else rt.GGUF_Q8_0
-        raw = (syn.q4k_matrix if fmt == "q4k" else syn.q8_0_matrix)("mb", out_dim, in_dim)
+    elif fmt in ("q4k", "q5k", "q6k", "q8_0"):
+        qt = {"q4k": rt.GGUF_Q4_K, "q5k": rt.GGUF_Q5_K, "q6k": rt.GGUF_Q6_K, "q8_0": rt.GGUF_Q8_0}[fmt]
+        raw = {"q4k": syn.q4k_matrix, "q5k": syn.q5k_matrix, "q6k": syn.q6k_matrix, "q8_0": syn.q8_0_matrix}[fmt]("mb", out_dim, in_dim)
         handles = [rt.UploadGGUFMatrix(qt, raw, in_dim, out_dim) for _ in range(copies)]
     else:
         w = torch.randn(out_dim, in_dim).clamp_(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8).numpy().reshape(-1)
@@ -262,7 +262,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1)
     ap.add_argument("--layer-chain", action="store_true", help="decoder-layer projections at Llama-3-8B shapes as a dependent chain")
-    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q8_0", "fp8", "moe"])
+    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q5k", "q6k", "q8_0", "fp8", "moe"])
     ap.add_argument("--out", type=int, default=4096)
     ap.add_argument("--in", dest="in_dim", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1)

@@ -18,10 +18,12 @@ LIB_PATH = os.path.join(_HERE, "libgoph_b200.so")
 
 GGUF_Q8_0 = 8   # loader/gguf/gguf.go:51
 GGUF_Q4_K = 12  # loader/gguf/gguf.go:54
+GGUF_Q5_K = 13  # loader/gguf/gguf.go:55
+GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 
 # Every symbol include/goph_b200.h declares.
 EXPORTS = [
-    "goph_init", "goph_set_option", "goph_kernel_status", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_init", "goph_set_option", "goph_kernel_status", "goph_debug_probe", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
     "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
@@ -363,6 +365,45 @@ def GemvQ4KBatchToBuffer(out, x, batch, m, stream=None):
 
 
 GemvQ8_0BatchToBuffer = GemvQ4KBatchToBuffer  # runtime/q8.go:225
+
+
+def UploadQ5KMatrixRows(raw, inDim, outDim):
+    """nvidia.UploadQ5KMatrixRows (runtime/qk.go:51): 176-byte super-blocks of 256 elements."""
+    return _upload_gguf(GGUF_Q5_K, raw, inDim, outDim)
+
+
+def UploadQ6KMatrixRows(raw, inDim, outDim):
+    """nvidia.UploadQ6KMatrixRows (runtime/qk.go:55): 210-byte super-blocks of 256 elements."""
+    return _upload_gguf(GGUF_Q6_K, raw, inDim, outDim)
+
+
+def _want_qtype(m, qtype, name):
+    if not isinstance(m, GPUGGUFMatrix) or not m._h or m.QType != qtype:
+        raise GophError(1, "invalid %s matrix" % name)
+
+
+def GemvQ5KBatch(x, batch, m):
+    """nvidia.GemvQ5KBatch (runtime/qk.go:392) with host slices; returns out."""
+    _want_qtype(m, GGUF_Q5_K, "Q5_K")
+    return _gguf_host(x, batch, m)
+
+
+def GemvQ6KBatch(x, batch, m):
+    """nvidia.GemvQ6KBatch (runtime/qk.go:396) with host slices; returns out."""
+    _want_qtype(m, GGUF_Q6_K, "Q6_K")
+    return _gguf_host(x, batch, m)
+
+
+def GemvQ5KBatchToBuffer(out, x, batch, m, stream=None):
+    """nvidia.GemvQ5KBatchToBuffer (runtime/qk.go:229)."""
+    _want_qtype(m, GGUF_Q5_K, "Q5_K")
+    m.ProjectBatchToBuffer(out, x, batch, stream)
+
+
+def GemvQ6KBatchToBuffer(out, x, batch, m, stream=None):
+    """nvidia.GemvQ6KBatchToBuffer (runtime/qk.go:285)."""
+    _want_qtype(m, GGUF_Q6_K, "Q6_K")
+    m.ProjectBatchToBuffer(out, x, batch, stream)
 
 
 # ------------------------------------------------------------------------------- FP8

@@ -7,6 +7,7 @@ points.  The reference is single-GPU and has no counterpart."""
 import numpy as np
 
 Q8_0_BLOCK, Q4_K_BLOCK = (32, 34), (256, 144)   # (elements, bytes) per block; loader/gguf/quant_matrix.go:26-60
+Q5_K_BLOCK, Q6_K_BLOCK = (256, 176), (256, 210)  # loader/gguf/quant_matrix.go:331-426
 
 
 def shard_rows(out_dim, rank, world, align=8):
@@ -26,7 +27,7 @@ def slice_mlx(weight, scales, biases, in_dim, group_size, lo, hi):
 
 
 def slice_gguf(raw, block, in_dim, lo, hi):
-    """block: Q8_0_BLOCK or Q4_K_BLOCK."""
+    """block: Q8_0_BLOCK, Q4_K_BLOCK, Q5_K_BLOCK or Q6_K_BLOCK."""
     row_bytes = in_dim // block[0] * block[1]
     return np.ascontiguousarray(raw[lo * row_bytes:hi * row_bytes])
 

@@ -60,6 +60,28 @@ def q4k_matrix(key, out_dim, in_dim):
     return raw.reshape(-1)
 
 
+def q5k_matrix(key, out_dim, in_dim):
+    """176-byte super-blocks: f16 d, dmin ~ U(0.001,0.02); 12 scale bytes, 32 fifth-bit bytes and 128 nibble bytes uniform bits."""
+    g = rng("q5_k", key, out_dim, in_dim)
+    nb = out_dim * (in_dim // 256)
+    raw = np.empty((nb, 176), dtype=np.uint8)
+    raw[:, 0:4] = g.uniform(0.001, 0.02, (nb, 2)).astype(np.float16).view(np.uint8).reshape(nb, 4)
+    raw[:, 4:] = g.integers(0, 256, size=(nb, 172), dtype=np.uint8)
+    return raw.reshape(-1)
+
+
+def q6k_matrix(key, out_dim, in_dim):
+    """210-byte super-blocks: 128 nibble bytes and 64 two-bit bytes uniform bits, 16 int8 scales ~ U[-127,127],
+    f16 d ~ U(0.0005,0.005)."""
+    g = rng("q6_k", key, out_dim, in_dim)
+    nb = out_dim * (in_dim // 256)
+    raw = np.empty((nb, 210), dtype=np.uint8)
+    raw[:, 0:192] = g.integers(0, 256, size=(nb, 192), dtype=np.uint8)
+    raw[:, 192:208] = g.integers(-127, 128, size=(nb, 16), dtype=np.int8).view(np.uint8)
+    raw[:, 208:210] = g.uniform(0.0005, 0.005, nb).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    return raw.reshape(-1)
+
+
 def e4m3_table():
     """Value of every E4M3FN code (bias 7, subnormals, 0x7f/0xff NaN)."""
     t = np.zeros(256, dtype=F)

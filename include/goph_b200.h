@@ -42,8 +42,10 @@ enum {
   GOPH_E_NOMEM = 5
 };
 
-/* GGUF tensor type ids accepted by goph_gguf_upload (loader/gguf/gguf.go:51,54). */
-enum { GOPH_GGUF_Q8_0 = 8, GOPH_GGUF_Q4_K = 12 };
+/* GGUF tensor type ids accepted by goph_gguf_upload (loader/gguf/gguf.go:51-56).  Q5_K and Q6_K
+   (176- and 210-byte super-blocks of 256 elements; loader/gguf/quant_matrix.go:331-426) go through
+   the CUDA-core streaming kernel only. */
+enum { GOPH_GGUF_Q8_0 = 8, GOPH_GGUF_Q4_K = 12, GOPH_GGUF_Q5_K = 13, GOPH_GGUF_Q6_K = 14 };
 
 typedef struct goph_mlx_weight goph_mlx_weight;   /* nvidia.GPUMLXWeight      (runtime/mlx.go:21-32)   */
 typedef struct goph_gguf_matrix goph_gguf_matrix; /* nvidia.GPUGGUFMatrix / GPUQ4KMatrix / GPUQ8_0Matrix
@@ -95,6 +97,12 @@ int goph_set_option(const char* name, int value);
  * after every launch under GO_PHERENCE_CUDA_LAUNCH_CHECK, runtime/runtime.go:687-694.)
  * Synchronises with the device. */
 int goph_kernel_status(int device, int* out_status);
+/* Tuning aids of the tensor-core kernel, compiled in (a few predicated instructions): with option
+ * "mlx_probe" = 1, CTA 0 records per-role cycle counters (total and time spent in each barrier
+ * wait) that this call copies out as 32 int64 values; option "mlx_dbg" leaves out parts of the
+ * kernel for ablation timing (bit 0 TMEM stores, 1 MMAs, 2 TMEM loads, 3 conversion) — results are
+ * then meaningless.  Neither is used by the library's own paths or tests of results. */
+int goph_debug_probe(int device, long long* out32);
 
 /* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
 int goph_malloc(int device, uint64_t bytes, void** out_dev);

@@ -15,6 +15,8 @@ _lib = None
 
 Q8_0 = 8   # loader/gguf/gguf.go:51
 Q4_K = 12  # loader/gguf/gguf.go:54
+Q5_K = 13  # loader/gguf/gguf.go:55
+Q6_K = 14  # loader/gguf/gguf.go:56
 
 
 def lib():

@@ -280,17 +280,95 @@ void q4k_dequant_row(float* dst, const uint8_t* raw, int n) {
   }
 }
 
-enum { GGUF_Q8_0 = 8, GGUF_Q4_K = 12 };  // ggml type ids (loader/gguf/types)
+// loader/gguf/quant_matrix.go:331-384 — Q5_K: 176-byte super-blocks {f16 d, f16 dmin, 12 scale
+// bytes (the Q4_K packing), 32 bytes of fifth bits, 128 bytes of low nibbles}; groups of 64
+// elements share 32 nibble bytes (low / high nibble) and two bits of each qh byte.
+void q5k_dequant_row(float* dst, const uint8_t* raw, int n) {
+  for (int b = 0; b < n / 256; ++b) {
+    const uint8_t* blk = raw + (size_t)b * 176;
+    float d = f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+    float dmin = f16_to_f32((uint16_t)(blk[2] | (blk[3] << 8)));
+    const uint8_t* sc = blk + 4;
+    const uint8_t* qh = blk + 16;
+    const uint8_t* ql = blk + 48;
+    float scales[8], mins[8];
+    for (int j = 0; j < 4; ++j) {
+      scales[j] = (float)(sc[j] & 63) * d;
+      mins[j] = (float)(sc[j + 4] & 63) * dmin;
+    }
+    for (int j = 4; j < 8; ++j) {
+      int k = j - 4;
+      scales[j] = (float)((sc[j + 4] & 0x0f) | ((sc[k] >> 6) << 4)) * d;
+      mins[j] = (float)((sc[j + 4] >> 4) | ((sc[k + 4] >> 6) << 4)) * dmin;
+    }
+    int is = 0;
+    uint8_t u1 = 1, u2 = 2;
+    for (int group = 0; group < 4; ++group) {
+      float d1 = scales[is], m1 = mins[is], d2 = scales[is + 1], m2 = mins[is + 1];
+      for (int i = 0; i < 32; ++i) {
+        int q1 = ql[i] & 0x0f;
+        if (qh[i] & u1) q1 += 16;
+        int q2 = ql[i] >> 4;
+        if (qh[i] & u2) q2 += 16;
+        dst[b * 256 + group * 64 + i] = d1 * (float)q1 - m1;
+        dst[b * 256 + group * 64 + 32 + i] = d2 * (float)q2 - m2;
+      }
+      ql += 32;
+      is += 2;
+      u1 = (uint8_t)(u1 << 2);
+      u2 = (uint8_t)(u2 << 2);
+    }
+  }
+}
+
+// loader/gguf/quant_matrix.go:386-426 — Q6_K: 210-byte super-blocks {128 bytes of low nibbles,
+// 64 bytes of two-bit highs, 16 int8 scales, f16 d}; value = d * scale * (q - 32), the product
+// d * scale rounded to f32 first.
+void q6k_dequant_row(float* dst, const uint8_t* raw, int n) {
+  for (int b = 0; b < n / 256; ++b) {
+    const uint8_t* blk = raw + (size_t)b * 210;
+    const uint8_t* ql = blk;
+    const uint8_t* qh = blk + 128;
+    const int8_t* sc = reinterpret_cast<const int8_t*>(blk + 192);
+    float d = f16_to_f32((uint16_t)(blk[208] | (blk[209] << 8)));
+    float* y = dst + (size_t)b * 256;
+    for (int half = 0; half < 2; ++half) {
+      for (int l = 0; l < 32; ++l) {
+        int is = l / 16;
+        int q1 = (int8_t)((ql[l] & 0x0F) | (((qh[l] >> 0) & 3) << 4)) - 32;
+        int q2 = (int8_t)((ql[l + 32] & 0x0F) | (((qh[l] >> 2) & 3) << 4)) - 32;
+        int q3 = (int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+        int q4 = (int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+        y[l] = d * (float)sc[is + 0] * (float)q1;
+        y[l + 32] = d * (float)sc[is + 2] * (float)q2;
+        y[l + 64] = d * (float)sc[is + 4] * (float)q3;
+        y[l + 96] = d * (float)sc[is + 6] * (float)q4;
+      }
+      y += 128;
+      ql += 64;
+      qh += 32;
+      sc += 8;
+    }
+  }
+}
+
+enum { GGUF_Q8_0 = 8, GGUF_Q4_K = 12, GGUF_Q5_K = 13, GGUF_Q6_K = 14 };  // ggml type ids (loader/gguf/gguf.go:51-56)
 
 int gguf_row_bytes(int qtype, int in_dim) {
   if (qtype == GGUF_Q8_0) return in_dim % 32 ? -1 : in_dim / 32 * 34;
   if (qtype == GGUF_Q4_K) return in_dim % 256 ? -1 : in_dim / 256 * 144;
+  if (qtype == GGUF_Q5_K) return in_dim % 256 ? -1 : in_dim / 256 * 176;
+  if (qtype == GGUF_Q6_K) return in_dim % 256 ? -1 : in_dim / 256 * 210;
   return -1;
 }
 
 void gguf_dequant_row(float* dst, const uint8_t* raw, int qtype, int n) {
   if (qtype == GGUF_Q8_0)
     q8_0_dequant_row(dst, raw, n);
+  else if (qtype == GGUF_Q5_K)
+    q5k_dequant_row(dst, raw, n);
+  else if (qtype == GGUF_Q6_K)
+    q6k_dequant_row(dst, raw, n);
   else
     q4k_dequant_row(dst, raw, n);
 }

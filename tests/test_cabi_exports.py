@@ -70,6 +70,9 @@ def test_upload_validation_happens_before_device_use(pkg):
     raw = np.zeros(144, dtype=np.uint8)
     assert L.goph_gguf_upload(7, 12, vp(raw), C.c_uint64(144), 255, 1, C.byref(h)) == 1   # not a multiple of 256
     assert L.goph_gguf_upload(7, 8, vp(raw), C.c_uint64(33), 32, 1, C.byref(h)) == 1      # short raw
-    assert L.goph_gguf_upload(7, 14, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 4   # Q6_K unsupported
+    assert L.goph_gguf_upload(7, 10, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 4   # Q2_K unsupported
+    assert L.goph_gguf_upload(7, 13, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 1   # Q5_K wants 176 bytes
+    assert L.goph_gguf_upload(7, 14, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 1   # Q6_K wants 210 bytes
+    assert L.goph_gguf_upload(7, 14, vp(raw), C.c_uint64(105), 128, 1, C.byref(h)) == 1   # not a multiple of 256
     assert L.goph_fp8_upload(7, vp(raw), C.c_uint64(6), vp(s), 3, None, 0, 2, 3, C.byref(h)) == 1  # scale len 3
     assert L.goph_fp8_upload(7, vp(raw), C.c_uint64(5), vp(s), 1, None, 0, 2, 3, C.byref(h)) == 1  # weight bytes

@@ -1,23 +1,26 @@
-"""GPU parity of the GGUF Q8_0 / Q4_K path against the CPU oracle, through the C ABI."""
+"""GPU parity of the GGUF Q8_0 / Q4_K / Q5_K / Q6_K path against the CPU oracle, through the C ABI."""
 import numpy as np
 import pytest
 
 from gpu_util import F, TOL, out_with_canary, read_and_check_canary
 from oracle import binding as orc
-from test_oracle_pins import q4k_test_rows, q8_0_test_rows
+from test_oracle_pins import q4k_test_rows, q8_0_test_rows, qk_test_rows
 
 pytestmark = pytest.mark.gpu
 
-Q8_0, Q4_K = orc.Q8_0, orc.Q4_K
+Q8_0, Q4_K, Q5_K, Q6_K = orc.Q8_0, orc.Q4_K, orc.Q5_K, orc.Q6_K
 
 
 def make(pkg, qtype, key, out_dim, in_dim):
-    gen = pkg.synth.q8_0_matrix if qtype == Q8_0 else pkg.synth.q4k_matrix
+    gen = {Q8_0: pkg.synth.q8_0_matrix, Q4_K: pkg.synth.q4k_matrix, Q5_K: pkg.synth.q5k_matrix,
+           Q6_K: pkg.synth.q6k_matrix}[qtype]
     return gen(key, out_dim, in_dim)
 
 
 @pytest.mark.parametrize("qtype,out_dim,in_dim", [(Q8_0, 64, 4096), (Q8_0, 3, 32), (Q8_0, 17, 96),
-                                                   (Q4_K, 64, 4096), (Q4_K, 2, 256), (Q4_K, 9, 2816)])
+                                                   (Q4_K, 64, 4096), (Q4_K, 2, 256), (Q4_K, 9, 2816),
+                                                   (Q5_K, 64, 4096), (Q5_K, 2, 256), (Q5_K, 9, 2816),
+                                                   (Q6_K, 64, 4096), (Q6_K, 2, 256), (Q6_K, 9, 2816)])
 def test_dequant_bit_exact(gpu, pkg, qtype, out_dim, in_dim):
     raw = make(pkg, qtype, "deq", out_dim, in_dim)
     m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
@@ -55,8 +58,30 @@ def test_q8_0_reference_formula_blocks(gpu, pkg):
     m.Free()
 
 
+@pytest.mark.parametrize("kind", [5, 6])
+def test_q5k_q6k_reference_formula_blocks(gpu, pkg, kind):
+    # backends/nvidia/runtime/qk_test.go:11-75: GemvQ5KBatch / GemvQ6KBatch at batch 3 vs the indexed
+    # dequantisation times x, within 2e-4 * max(1, |want|); the device dequantisation bit for bit
+    raw, x, in_dim, out_dim = qk_test_rows(kind)
+    qtype = Q5_K if kind == 5 else Q6_K
+    m = (gpu.UploadQ5KMatrixRows if kind == 5 else gpu.UploadQ6KMatrixRows)(raw, in_dim, out_dim)
+    assert m.ResidentBytes() == raw.size
+    got = (gpu.GemvQ5KBatch if kind == 5 else gpu.GemvQ6KBatch)(x, 3, m).reshape(3, out_dim)
+    deq = orc.gguf_dequant(raw, qtype, in_dim, out_dim)
+    for b in range(3):
+        want = deq.astype(np.float64) @ x[b * in_dim:(b + 1) * in_dim].astype(np.float64)
+        assert np.all(np.abs(got[b] - want) <= 2e-4 * np.maximum(1.0, np.abs(want)))
+    out = out_with_canary(gpu, out_dim * in_dim)
+    m.Dequant(out)
+    gpu.Sync()
+    assert np.array_equal(read_and_check_canary(out, out_dim * in_dim).view(np.uint32), deq.reshape(-1).view(np.uint32))
+    with pytest.raises(gpu.GophError):  # the other kind's entry point refuses this matrix (qk.go:403-405)
+        (gpu.GemvQ6KBatch if kind == 5 else gpu.GemvQ5KBatch)(x, 3, m)
+    m.Free(); out.Free()
+
+
 @pytest.mark.parametrize("rows", [0, 1, 2, 4])
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (4096, 4096), (259, 2816), (2048, 768)])
 def test_gemv_parity(gpu, pkg, qtype, out_dim, in_dim, rows):
     gpu.SetOption("gguf_rows", rows)
@@ -79,7 +104,7 @@ def test_gemv_parity(gpu, pkg, qtype, out_dim, in_dim, rows):
         gpu.SetOption("gguf_layout", 0)
 
 
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("batch", [2, 3, 4, 5, 8, 11])
 def test_batched_projection(gpu, pkg, qtype, batch):
     out_dim, in_dim = 1024, 2048
@@ -104,7 +129,11 @@ def test_malformed_calls_raise(gpu, pkg):
     with pytest.raises(gpu.GophError):
         gpu.UploadQ4KMatrixRaw(raw[:-1], 256, 4)
     with pytest.raises(gpu.GophError):
-        gpu.UploadGGUFMatrix(14, raw, 256, 4)  # Q6_K is not on this path
+        gpu.UploadGGUFMatrix(10, raw, 256, 4)  # Q2_K is not on this path
+    with pytest.raises(gpu.GophError):
+        gpu.UploadQ5KMatrixRows(raw, 256, 4)   # 144-byte blocks where 176 are due
+    with pytest.raises(gpu.GophError):
+        gpu.UploadQ6KMatrixRows(make(pkg, Q6_K, "bad", 4, 256), 128, 4)
     m = gpu.UploadQ4KMatrixRaw(raw, 256, 4)
     x = gpu.Malloc(256); out = out_with_canary(gpu, 4)
     with pytest.raises(gpu.GophError):
@@ -119,7 +148,7 @@ def test_malformed_calls_raise(gpu, pkg):
     x.Free(); out.Free()
 
 
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("out_dim,in_dim", [(14336, 4096), (4096, 14336), (128256, 4096)])
 def test_full_size_against_device_dequant(gpu, pkg, qtype, out_dim, in_dim):
     """Llama-3-8B shapes: fused projection vs bit-exact device dequantisation and an f64 product."""

@@ -388,3 +388,100 @@ def test_moe_route_strict_greater_and_renorm():
     ids2, wts2 = orc.moe_route(logits, 3, norm_topk=False)
     p = orc.softmax(logits)
     assert list(ids2) == [1, 2, 0] and np.array_equal(wts2, p[[1, 2, 0]])
+
+
+# ---- Q5_K / Q6_K (backends/nvidia/runtime/qk_test.go) ---------------------------------------------
+
+def qk_test_rows(kind):
+    """The formula-built blocks and input of TestGemvQ5KBatchMatchesIndependentDequant /
+    TestGemvQ6KBatchMatchesIndependentDequant (qk_test.go:11-75, :96-113)."""
+    f16 = lambda v: np.array([v], dtype=np.float32).astype(np.float16).view(np.uint8)
+    if kind == 5:
+        in_dim, out_dim, bs = 512, 7, 176
+    else:
+        in_dim, out_dim, bs = 512, 5, 210
+    blocks = in_dim // 256
+    raw = np.zeros((out_dim, blocks, bs), dtype=np.uint8)
+    for row in range(out_dim):
+        for block in range(blocks):
+            blk = raw[row, block]
+            if kind == 5:
+                blk[0:2] = f16(np.float32(0.025) + np.float32(row + block) * np.float32(0.002))
+                blk[2:4] = f16(np.float32(0.004) + np.float32((row + block) % 3) * np.float32(0.001))
+                for i in range(12):
+                    blk[4 + i] = (row * 11 + block * 7 + i * 13 + 3) & 0xFF
+                for i in range(32):
+                    blk[16 + i] = (row * 5 + block * 3 + i * 17 + 1) & 0xFF
+                for i in range(128):
+                    blk[48 + i] = (row * 19 + block * 23 + i * 29 + 9) & 0xFF
+            else:
+                for i in range(128):
+                    blk[i] = (row * 13 + block * 7 + i * 19 + 5) & 0xFF
+                for i in range(64):
+                    blk[128 + i] = (row * 17 + block * 11 + i * 23 + 3) & 0xFF
+                for i in range(16):
+                    blk[192 + i] = np.int8((row * 5 + block * 3 + i * 7) % 31 - 15).view(np.uint8)
+                blk[208:210] = f16(np.float32(0.017) + np.float32(row + block) * np.float32(0.001))
+    x = np.array([np.float32((i * 17) % 37 - 18) * np.float32(0.013) for i in range(3 * in_dim)], dtype=np.float32)
+    return raw.reshape(-1), x, in_dim, out_dim
+
+
+def dequant_q5k_indexed(raw, n):
+    """dequantQ5KTest (qk_test.go:135-167): the indexed form, independent of the streaming decoder."""
+    out = np.zeros(n, dtype=np.float32)
+    for b in range(n // 256):
+        blk = raw[b * 176:(b + 1) * 176]
+        d = blk[0:2].copy().view(np.float16)[0].astype(np.float32)
+        dmin = blk[2:4].copy().view(np.float16)[0].astype(np.float32)
+        sc, qh, ql = blk[4:16], blk[16:48], blk[48:176]
+        scales, mins = np.zeros(8, np.float32), np.zeros(8, np.float32)
+        for j in range(4):
+            scales[j], mins[j] = np.float32(sc[j] & 63) * d, np.float32(sc[j + 4] & 63) * dmin
+        for j in range(4, 8):
+            k = j - 4
+            scales[j] = np.float32((sc[j + 4] & 15) | ((sc[k] >> 6) << 4)) * d
+            mins[j] = np.float32((sc[j + 4] >> 4) | ((sc[k + 4] >> 6) << 4)) * dmin
+        for group in range(4):
+            for i in range(32):
+                q0, q1 = int(ql[group * 32 + i] & 15), int(ql[group * 32 + i] >> 4)
+                if qh[i] & (1 << (group * 2)):
+                    q0 += 16
+                if qh[i] & (1 << (group * 2 + 1)):
+                    q1 += 16
+                base = b * 256 + group * 64
+                out[base + i] = scales[group * 2] * np.float32(q0) - mins[group * 2]
+                out[base + 32 + i] = scales[group * 2 + 1] * np.float32(q1) - mins[group * 2 + 1]
+    return out
+
+
+def dequant_q6k_indexed(raw, n):
+    """dequantQ6KTest (qk_test.go:169-190)."""
+    out = np.zeros(n, dtype=np.float32)
+    for b in range(n // 256):
+        blk = raw[b * 210:(b + 1) * 210]
+        ql, qh, sc = blk[:128], blk[128:192], blk[192:208].view(np.int8)
+        d = blk[208:210].copy().view(np.float16)[0].astype(np.float32)
+        for i in range(256):
+            hb, group, lane = i // 128, (i % 128) // 32, i % 32
+            qb = int(ql[hb * 64 + (group % 2) * 32 + lane])
+            low = qb >> 4 if group >= 2 else qb & 15
+            high = (int(qh[hb * 32 + lane]) >> (group * 2)) & 3
+            q = np.int8(low | (high << 4)).astype(np.int32) - 32
+            out[b * 256 + i] = d * np.float32(sc[hb * 8 + lane // 16 + group * 2]) * np.float32(q)
+    return out
+
+
+@pytest.mark.parametrize("kind,qtype,indexed", [(5, orc.Q5_K, dequant_q5k_indexed), (6, orc.Q6_K, dequant_q6k_indexed)])
+def test_q5k_q6k_reference_formula_blocks(kind, qtype, indexed):
+    raw, x, in_dim, out_dim = qk_test_rows(kind)
+    rb = orc.gguf_row_bytes(qtype, in_dim)
+    assert rb == in_dim // 256 * (176 if kind == 5 else 210)
+    deq = orc.gguf_dequant(raw, qtype, in_dim, out_dim)
+    for r in range(out_dim):
+        want = indexed(raw[r * rb:(r + 1) * rb], in_dim)
+        assert np.array_equal(deq[r].view(np.uint32), want.view(np.uint32)), r
+    got = orc.gguf_gemv(x, raw, qtype, in_dim, out_dim, batch=3).reshape(3, out_dim)
+    for b in range(3):
+        want = deq.astype(np.float64) @ x[b * in_dim:(b + 1) * in_dim].astype(np.float64)
+        assert np.all(np.abs(got[b] - want) <= 2e-4 * np.maximum(1.0, np.abs(want)))
+    assert orc.gguf_row_bytes(orc.Q5_K, 255) == -1 and orc.gguf_row_bytes(orc.Q6_K, 300) == -1
