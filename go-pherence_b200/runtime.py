@@ -25,6 +25,8 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 EXPORTS = [
     "goph_init", "goph_set_option", "goph_kernel_status", "goph_debug_probe", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
+    "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
+    "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
     "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
     "goph_mlx_gemm_host",
@@ -60,7 +62,7 @@ def lib():
                                 "there is no CPU or PyTorch fallback")
         L = C.CDLL(LIB_PATH)
         L.goph_last_error.restype = C.c_char_p
-        for name in ("goph_mlx_resident_bytes", "goph_gguf_resident_bytes", "goph_fp8_resident_bytes"):
+        for name in ("goph_mlx_resident_bytes", "goph_gguf_resident_bytes", "goph_fp8_resident_bytes", "goph_gptq_resident_bytes"):
             getattr(L, name).restype = C.c_uint64
             getattr(L, name).argtypes = [C.c_void_p]
         _lib = L
@@ -404,6 +406,57 @@ def GemvQ6KBatchToBuffer(out, x, batch, m, stream=None):
     """nvidia.GemvQ6KBatchToBuffer (runtime/qk.go:285)."""
     _want_qtype(m, GGUF_Q6_K, "Q6_K")
     m.ProjectBatchToBuffer(out, x, batch, stream)
+
+
+# ------------------------------------------------------------------------------- GPTQ
+class GPUQuantWeight:
+    """nvidia.GPUQuantWeight (runtime/q4.go:18-26)."""
+
+    def __init__(self, handle, in_dim, out_dim, groups):
+        self._h, self.InDim, self.OutDim, self.Groups = handle, in_dim, out_dim, groups
+
+    def ResidentBytes(self):
+        return int(lib().goph_gptq_resident_bytes(self._h)) if self._h else 0
+
+    def UsesMLXKernels(self):
+        return bool(lib().goph_gptq_uses_mlx_kernels(self._h)) if self._h else False
+
+    def Dequant(self, out, stream=None):
+        if not self._h:
+            raise GophError(1, "nil or freed GPUQuantWeight")
+        _check(lib().goph_gptq_dequant(self._h, C.c_void_p(out.Ptr), C.c_uint64(out.n), _stream_ptr(stream)))
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_gptq_free(self._h))
+            self._h = None
+
+
+def UploadQuantWeight(qweight, gIdx, scales, inDim, outDim):
+    """nvidia.UploadQuantWeight (runtime/q4.go:29-102)."""
+    qweight = np.ascontiguousarray(qweight, dtype=np.int32)
+    gIdx = np.ascontiguousarray(gIdx, dtype=np.int32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    h = C.c_void_p(0)
+    _check(lib().goph_gptq_upload(_device, _vp(qweight), C.c_uint64(qweight.size), _vp(gIdx), C.c_uint64(gIdx.size),
+                                  _vp(scales), C.c_uint64(scales.size), int(inDim), int(outDim), C.byref(h)))
+    return GPUQuantWeight(h, int(inDim), int(outDim), scales.size // int(outDim))
+
+
+def GemmQ4(out, x, w, B, stream=None):
+    """nvidia.GemmQ4 (runtime/gemm_q4.go:24) on device buffers; raises where the reference would fall back to the CPU."""
+    if not isinstance(w, GPUQuantWeight) or not w._h:
+        raise GophError(1, "nil or freed GPUQuantWeight")
+    _check(lib().goph_gptq_gemm(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(B), w._h,
+                                _stream_ptr(stream)))
+
+
+def GemvQ4(out, x, w, stream=None):
+    """nvidia.GemvQ4 (runtime/q4.go:149)."""
+    GemmQ4(out, x, w, 1, stream)
+
+
+GemvQ4OrGemm = GemmQ4  # nvidia.GemvQ4OrGemm (runtime/gemm_q4.go:113): one entry point serves every batch
 
 
 # ------------------------------------------------------------------------------- FP8

@@ -82,6 +82,21 @@ def q6k_matrix(key, out_dim, in_dim):
     return raw.reshape(-1)
 
 
+def gptq_weight(key, out_dim, in_dim, gs=128, act_order=False, f16_scales=True):
+    """GPTQ symmetric INT4 in checkpoint layout: qweight [in/8][out] int32 of uniform nibbles, scales
+    [in/gs][out] ~ U(0.002,0.02) (rounded to f16 as checkpoints store them unless f16_scales is False),
+    g_idx = i // gs, or under act_order that pattern scattered by a random permutation of the inputs."""
+    g = rng("gptq", key, out_dim, in_dim, gs, act_order)
+    qw = g.integers(0, 2 ** 32, size=(in_dim // 8) * out_dim, dtype=np.uint64).astype(np.uint32).view(np.int32)
+    sc = g.uniform(0.002, 0.02, (in_dim // gs) * out_dim).astype(np.float32)
+    if f16_scales:
+        sc = sc.astype(np.float16).astype(np.float32)
+    gidx = (np.arange(in_dim) // gs).astype(np.int32)
+    if act_order:
+        gidx = gidx[g.permutation(in_dim)]
+    return qw, gidx, sc
+
+
 def e4m3_table():
     """Value of every E4M3FN code (bias 7, subnormals, 0x7f/0xff NaN)."""
     t = np.zeros(256, dtype=F)

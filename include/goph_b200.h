@@ -191,6 +191,33 @@ int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint
 int goph_gguf_project_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
                            int batch, const goph_gguf_matrix* m);
 
+/* ---- GPTQ symmetric INT4 weights (backends/simd/quant/q4, runtime/q4.go, gemm_q4.go) ---- */
+
+typedef struct goph_gptq_weight goph_gptq_weight; /* nvidia.GPUQuantWeight (runtime/q4.go:18-26) */
+
+/* nvidia.UploadQuantWeight (runtime/q4.go:29-102): qweight [in_dim/8, out_dim] int32 (input 8p+k in
+ * bits 4k..4k+3 of row p), g_idx [in_dim], scales [groups, out_dim] with groups = scales_len / out_dim;
+ * weight = scale * (q - 8).  Same rejections as the reference: in_dim not a multiple of 8, short
+ * buffers, scales_len not a positive multiple of out_dim, g_idx outside [0, groups).
+ * A g_idx of equal consecutive groups (group size a multiple of 8) is served by the MLX kernels
+ * (q*s - 8*s is that format's affine form), any other g_idx by a row kernel with per-input scale
+ * lookup. */
+int goph_gptq_upload(int device, const int32_t* qweight, uint64_t qweight_len, const int32_t* g_idx,
+                     uint64_t g_idx_len, const float* scales, uint64_t scales_len, int in_dim, int out_dim,
+                     goph_gptq_weight** out);
+/* GPUQuantWeight.Free (runtime/q4.go:104-120); NULL is a no-op. */
+int goph_gptq_free(goph_gptq_weight* w);
+uint64_t goph_gptq_resident_bytes(const goph_gptq_weight* w);
+/* 1 when the weight is held in the MLX layouts (regular g_idx), 0 otherwise. */
+int goph_gptq_uses_mlx_kernels(const goph_gptq_weight* w);
+/* nvidia.GemvQ4 (batch 1; runtime/q4.go:149-182) and nvidia.GemmQ4 (runtime/gemm_q4.go:24-68) on device
+ * buffers: x [batch,in_dim] f32 -> out [batch,out_dim].  No CPU fallback. */
+int goph_gptq_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
+                   const goph_gptq_weight* w, void* stream);
+/* q4.DequantSymTo (backends/simd/quant/q4/dequant.go:134-197): [out_dim, in_dim] row-major f32,
+ * bit-exact (scale * float32(q - 8)). */
+int goph_gptq_dequant(const goph_gptq_weight* w, float* out_dev, uint64_t out_len, void* stream);
+
 /* ---- FP8 E4M3 linears (backends/simd/quant/fp8, runtime/fp8.go) ---------------------- */
 
 /* nvidia.UploadFP8E4M3Linear (runtime/fp8.go:48): weight [out_dim,in_dim] E4M3FN bytes,

@@ -118,6 +118,30 @@ def gguf_gemv(x, raw, qtype, in_dim, out_dim, batch=1, nthreads=1):
     return out if rc == 0 else None
 
 
+# --------------------------------------------------------------------- GPTQ
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def gptq_dequant_sym(qweight, gidx, scales, in_dim, out_dim):
+    """q4.DequantSym (backends/simd/quant/q4/dequant.go:114-197): [out, in] row-major, or None when rejected."""
+    qweight, gidx, scales = _i32(qweight), _i32(gidx), _f32(scales)
+    out = np.empty(max(0, out_dim * in_dim), dtype=np.float32)
+    rc = lib().orc_gptq_dequant_sym(_p(out), C.c_long(out.size), _p(qweight), C.c_long(qweight.size), _p(gidx),
+                                    C.c_long(gidx.size), _p(scales), C.c_long(scales.size), in_dim, out_dim)
+    return out.reshape(out_dim, in_dim) if rc == 0 else None
+
+
+def gptq_gemm_sym(x, batch, qweight, gidx, scales, in_dim, out_dim):
+    """q4.GemvSym / q4.GemmSym (gemv.go:76-94, gemm_sym_portable.go:7-150); None when rejected."""
+    x, qweight, gidx, scales = _f32(x), _i32(qweight), _i32(gidx), _f32(scales)
+    out = np.empty(max(0, batch * out_dim), dtype=np.float32)
+    rc = lib().orc_gptq_gemm_sym(_p(out), C.c_long(out.size), _p(x), C.c_long(x.size), batch, _p(qweight),
+                                 C.c_long(qweight.size), _p(gidx), C.c_long(gidx.size), _p(scales),
+                                 C.c_long(scales.size), in_dim, out_dim)
+    return out if rc == 0 else None
+
+
 # --------------------------------------------------------------------- FP8
 def e4m3_decode(code):
     return lib().orc_e4m3_decode(int(code) & 0xFF)

@@ -593,6 +593,70 @@ ORC_API int orc_gguf_gemv(float* out, long out_len, const float* x, long x_len, 
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// GPTQ symmetric INT4 (backends/simd/quant/q4): qweight [in/8][out] int32 (input 8p+k in bits
+// 4k..4k+3 of row p), g_idx [in], scales [groups][out]; weight = scale * (q - 8).
+// ---------------------------------------------------------------------------
+
+// validate.go:32-75 — dims, lengths, g_idx non-negative, scales cover max(g_idx)+1 groups.
+int gptq_validate_sym(long qw_len, const int32_t* gidx, long g_len, long s_len, int in_dim, int out_dim) {
+  if (in_dim <= 0 || out_dim <= 0 || in_dim % 8 != 0) return 1;
+  if (qw_len < (long)(in_dim / 8) * out_dim || g_len < in_dim) return 2;
+  int max_group = -1;
+  for (int i = 0; i < in_dim; ++i) {
+    if (gidx[i] < 0) return 3;
+    if (gidx[i] > max_group) max_group = gidx[i];
+  }
+  if (s_len < (long)(max_group + 1) * out_dim) return 4;
+  return 0;
+}
+
+// dequant.go:181-197 — out[j*in + i] = scale[g(i)][j] * float32(q - 8).
+ORC_API int orc_gptq_dequant_sym(float* out, long out_len, const int32_t* qw, long qw_len, const int32_t* gidx,
+                                 long g_len, const float* sc, long s_len, int in_dim, int out_dim) {
+  if (int rc = gptq_validate_sym(qw_len, gidx, g_len, s_len, in_dim, out_dim)) return rc;
+  if (out_len < (long)in_dim * out_dim) return 5;
+  for (int p = 0; p < in_dim / 8; ++p)
+    for (int bit = 0; bit < 8; ++bit) {
+      int i = p * 8 + bit;
+      const float* srow = sc + (size_t)gidx[i] * out_dim;
+      for (int j = 0; j < out_dim; ++j) {
+        int q = (int)(((uint32_t)qw[(size_t)p * out_dim + j] >> (4 * bit)) & 0xF);
+        out[(size_t)j * in_dim + i] = srow[j] * (float)(q - 8);
+      }
+    }
+  return 0;
+}
+
+// gemv.go:76-94 and gemm_sym_portable.go:7-150 — activation rows in tiles of up to four; a tile of
+// one adds (x*scale)*(q-8), larger tiles form w = scale*(q-8) once and add x*w per row.
+ORC_API int orc_gptq_gemm_sym(float* out, long out_len, const float* x, long x_len, int batch, const int32_t* qw,
+                              long qw_len, const int32_t* gidx, long g_len, const float* sc, long s_len, int in_dim,
+                              int out_dim) {
+  if (int rc = gptq_validate_sym(qw_len, gidx, g_len, s_len, in_dim, out_dim)) return rc;
+  if (batch <= 0 || out_len < (long)batch * out_dim || x_len < (long)batch * in_dim) return 5;
+  for (long k = 0; k < (long)batch * out_dim; ++k) out[k] = 0.f;
+  for (int b = 0; b < batch; b += 4) {
+    int rem = std::min(4, batch - b);
+    for (int p = 0; p < in_dim / 8; ++p)
+      for (int bit = 0; bit < 8; ++bit) {
+        int i = p * 8 + bit;
+        const float* srow = sc + (size_t)gidx[i] * out_dim;
+        for (int j = 0; j < out_dim; ++j) {
+          float q = (float)((int)(((uint32_t)qw[(size_t)p * out_dim + j] >> (4 * bit)) & 0xF) - 8);
+          if (rem == 1) {
+            float xs = x[(size_t)b * in_dim + i] * srow[j];
+            out[(size_t)b * out_dim + j] += xs * q;
+          } else {
+            float wv = srow[j] * q;
+            for (int r = 0; r < rem; ++r) out[(size_t)(b + r) * out_dim + j] += x[(size_t)(b + r) * in_dim + i] * wv;
+          }
+        }
+      }
+  }
+  return 0;
+}
+
 ORC_API float orc_e4m3_decode(uint8_t code) { return e4m3_decode(code); }
 
 // Linear.DequantRowTo over all rows (fp8.go:181-198): lut[w]*scale.

@@ -74,5 +74,16 @@ def test_upload_validation_happens_before_device_use(pkg):
     assert L.goph_gguf_upload(7, 13, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 1   # Q5_K wants 176 bytes
     assert L.goph_gguf_upload(7, 14, vp(raw), C.c_uint64(144), 256, 1, C.byref(h)) == 1   # Q6_K wants 210 bytes
     assert L.goph_gguf_upload(7, 14, vp(raw), C.c_uint64(105), 128, 1, C.byref(h)) == 1   # not a multiple of 256
+    # UploadQuantWeight validation (backends/nvidia/runtime/q4.go:30-56)
+    qw, gi = np.zeros(32, dtype=np.int32), np.zeros(64, dtype=np.int32)
+    sc = np.ones(4, dtype=np.float32)
+    gptq = lambda nq, ng, ns, i, o: L.goph_gptq_upload(7, vp(qw), C.c_uint64(nq), vp(gi), C.c_uint64(ng), vp(sc),
+                                                        C.c_uint64(ns), i, o, C.byref(h))
+    assert gptq(32, 64, 4, 60, 4) == 1 and gptq(31, 64, 4, 64, 4) == 1 and gptq(32, 63, 4, 64, 4) == 1
+    assert gptq(32, 64, 3, 64, 4) == 1 and gptq(32, 64, 0, 64, 4) == 1
+    gi[5] = 1
+    assert gptq(32, 64, 4, 64, 4) == 1      # g_idx names group 1 of 1
+    gi[5] = 0
+    assert gptq(32, 64, 4, 64, 4) == 3      # well-formed, device 7 not initialised
     assert L.goph_fp8_upload(7, vp(raw), C.c_uint64(6), vp(s), 3, None, 0, 2, 3, C.byref(h)) == 1  # scale len 3
     assert L.goph_fp8_upload(7, vp(raw), C.c_uint64(5), vp(s), 1, None, 0, 2, 3, C.byref(h)) == 1  # weight bytes

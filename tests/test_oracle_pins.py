@@ -485,3 +485,80 @@ def test_q5k_q6k_reference_formula_blocks(kind, qtype, indexed):
         want = deq.astype(np.float64) @ x[b * in_dim:(b + 1) * in_dim].astype(np.float64)
         assert np.all(np.abs(got[b] - want) <= 2e-4 * np.maximum(1.0, np.abs(want)))
     assert orc.gguf_row_bytes(orc.Q5_K, 255) == -1 and orc.gguf_row_bytes(orc.Q6_K, 300) == -1
+
+
+# ---- GPTQ symmetric INT4 (backends/simd/quant/q4) -------------------------------------------
+
+def pack_nibbles(vals):
+    """packNibbles (known_values_test.go:5-11)."""
+    out = 0
+    for i, v in enumerate(vals):
+        out |= (int(v) & 0xF) << (4 * i)
+    return np.array([out], dtype=np.uint32).view(np.int32)[0]
+
+
+def gptq_test_case_irregular():
+    """Inputs of TestGemvSymMatchesDequantSymReference (known_values_test.go:62-109): g_idx out of order."""
+    in_dim, out_dim = 16, 5
+    x = np.array([1, -2, 3, -4, 5, -6, 7, -8, 9, -10, 11, -12, 13, -14, 15, -16], dtype=np.float32)
+    qw = np.zeros((in_dim // 8) * out_dim, dtype=np.int32)
+    for pack in range(in_dim // 8):
+        for j in range(out_dim):
+            qw[pack * out_dim + j] = pack_nibbles([(pack * 3 + j * 5 + bit) & 0xF for bit in range(8)])
+    gidx = np.array([0, 0, 0, 0, 1, 1, 1, 1, 2, 2, 2, 2, 1, 1, 0, 0], dtype=np.int32)
+    scales = np.array([0.25, 0.5, 0.75, 1, 1.25, 1.5, 1.75, 2, 2.25, 2.5, -0.5, -0.25, 0.125, 0.375, 0.625], dtype=np.float32)
+    return qw, gidx, scales, x, in_dim, out_dim
+
+
+def gptq_test_case_known():
+    """Inputs of TestGemvSymKnownValues (known_values_test.go:111-132)."""
+    qw = np.array([pack_nibbles([8, 9, 10, 11, 12, 13, 14, 15]), pack_nibbles([7, 6, 5, 4, 3, 2, 1, 0])], dtype=np.int32)
+    gidx = np.array([0, 0, 0, 0, 1, 1, 1, 1], dtype=np.int32)
+    scales = np.array([1, 2, 10, 20], dtype=np.float32)
+    x = np.arange(1, 9, dtype=np.float32)
+    return qw, gidx, scales, x, 8, 2
+
+
+def test_gptq_sym_reference_known_values():
+    qw, gidx, scales, x, in_dim, out_dim = gptq_test_case_known()
+    got = orc.gptq_gemm_sym(x, 1, qw, gidx, scales, in_dim, out_dim)
+    want = np.zeros(2, dtype=np.float32)
+    for i in range(in_dim):
+        g = int(gidx[i])
+        want[0] = want[0] + np.float32(x[i] * scales[g * out_dim + 0]) * np.float32(i)
+        want[1] = want[1] + np.float32(x[i] * scales[g * out_dim + 1]) * np.float32(-1 - i)
+    assert np.array_equal(got, want)
+
+    qw, gidx, scales, x, in_dim, out_dim = gptq_test_case_irregular()
+    deq = orc.gptq_dequant_sym(qw, gidx, scales, in_dim, out_dim)
+    for j in range(out_dim):          # the closed form, element by element
+        for i in range(in_dim):
+            q = ((i // 8) * 3 + j * 5 + i % 8) & 0xF
+            assert deq[j, i] == scales[gidx[i] * out_dim + j] * np.float32(q - 8)
+    got = orc.gptq_gemm_sym(x, 1, qw, gidx, scales, in_dim, out_dim)
+    want = np.zeros(out_dim, dtype=np.float32)
+    for j in range(out_dim):
+        for i in range(in_dim):
+            want[j] = want[j] + deq[j, i] * x[i]
+    assert np.array_equal(got, want)   # exact: every product in the test is a small dyadic number
+    # batches go through tiles of four; every row equals the single-row product here (exact arithmetic)
+    for batch in (2, 3, 4, 5):
+        xb = np.concatenate([x * np.float32(k + 1) for k in range(batch)])
+        gb = orc.gptq_gemm_sym(xb, batch, qw, gidx, scales, in_dim, out_dim).reshape(batch, out_dim)
+        for k in range(batch):
+            assert np.array_equal(gb[k], want * np.float32(k + 1))
+
+
+def test_gptq_sym_rejects_malformed():
+    # validate_test.go / gemv_validate_test.go: bad dims, short buffers, negative or uncovered groups
+    qw, gidx, scales, x, in_dim, out_dim = gptq_test_case_irregular()
+    assert orc.gptq_gemm_sym(x, 1, qw, gidx, scales, 12, out_dim) is None
+    assert orc.gptq_gemm_sym(x, 1, qw[:-1], gidx, scales, in_dim, out_dim) is None
+    assert orc.gptq_gemm_sym(x, 1, qw, gidx[:-1], scales, in_dim, out_dim) is None
+    assert orc.gptq_gemm_sym(x, 1, qw, gidx, scales[:-1], in_dim, out_dim) is None
+    bad = gidx.copy(); bad[3] = -1
+    assert orc.gptq_gemm_sym(x, 1, qw, bad, scales, in_dim, out_dim) is None
+    bad[3] = 3
+    assert orc.gptq_dequant_sym(qw, bad, scales, in_dim, out_dim) is None
+    assert orc.gptq_gemm_sym(x[:-1], 1, qw, gidx, scales, in_dim, out_dim) is None
+    assert orc.gptq_gemm_sym(x, 0, qw, gidx, scales, in_dim, out_dim) is None
