@@ -127,6 +127,13 @@ struct MlxArgs {
   float pre_eps;
 };
 
+// c1 = sum over a unit of (offset * x), c2 = sum of x, from the sums over the unit's even and odd
+// elements; one definition so that every kernel rounds alike.
+template <int MODE>
+__device__ __forceinline__ float2 mlx_unit_consts(float se, float so) {
+  return make_float2(__fmaf_rn(Unpack<MODE>::kOffEven, se, __fmul_rn(Unpack<MODE>::kOffOdd, so)), __fadd_rn(se, so));
+}
+
 // Shared memory: float4 xs[M][iters][8][32]; float2 xc[M][iters][32].
 __host__ __device__ inline size_t mlx_smem_bytes(int M, int iters) {
   return (size_t)M * iters * (8 * 32 * 16 + 32 * 8);
@@ -134,22 +141,32 @@ __host__ __device__ inline size_t mlx_smem_bytes(int M, int iters) {
 
 template <int M, int MODE>
 __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2* xc) {
-  const int per_m = a.iters * 256;
-  const int total = M * per_m;
-  for (int idx = threadIdx.x; idx < total; idx += kThreads) {
-    int m = idx / per_m, rem = idx - m * per_m;
-    int it = rem >> 8, slot = (rem >> 5) & 7, l = rem & 31;
-    int unit = it * 32 + l;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (m < a.batch && unit < a.units) {
-      const float* p = a.x + (size_t)m * a.in_dim + (size_t)unit * 32 + slot * 4;
-      if (a.x_aligned) {
-        v = __ldg(reinterpret_cast<const float4*>(p));
-      } else {
-        v = make_float4(__ldg(p), __ldg(p + 1), __ldg(p + 2), __ldg(p + 3));
+  // thread t fills xs[j*256 + t] for j < M*iters (j = m*iters + it; slot = warp, lane = lane); four
+  // loads are in flight before the first store
+  const int n = M * a.iters;
+  const int slot = (threadIdx.x >> 5) & 7, l = threadIdx.x & 31;
+  for (int j0 = 0; j0 < n; j0 += 4) {
+    float4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = j0 + u;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (j < n) {
+        const int m = M == 1 ? 0 : j / a.iters, it = j - m * a.iters, unit = it * 32 + l;
+        if (m < a.batch && unit < a.units) {
+          // plain (coherent) loads: inside a product list x may have been written earlier in this launch
+          const float* p = a.x + (size_t)m * a.in_dim + (size_t)unit * 32 + slot * 4;
+          if (a.x_aligned) {
+            v[u] = *reinterpret_cast<const float4*>(p);
+          } else {
+            v[u] = make_float4(p[0], p[1], p[2], p[3]);
+          }
+        }
       }
     }
-    xs[idx] = v;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u < n) xs[(j0 + u) * 256 + threadIdx.x] = v[u];
   }
   __syncthreads();
   const int nsum = M * a.iters * 32;
@@ -162,14 +179,14 @@ __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2
       se += v.x + v.z;
       so += v.y + v.w;
     }
-    xc[idx] = make_float2(Unpack<MODE>::kOffEven * se + Unpack<MODE>::kOffOdd * so, se + so);
+    xc[idx] = mlx_unit_consts<MODE>(se, so);
   }
   __syncthreads();
 }
 
 // Staging with the operation a.pre_op in front (see MlxArgs); batch 1.
 template <int MODE>
-__device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, float2* xc) {
+__device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, float2* xc, int cta) {
   __shared__ float red[kWarps];
   const int total = a.iters * 256;
   float ss = 0.f;
@@ -184,7 +201,7 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
           const float4 b = *reinterpret_cast<const float4*>(a.pre_b + e0);
           v = make_float4(__fadd_rn(v.x, b.x), __fadd_rn(v.y, b.y), __fadd_rn(v.z, b.z), __fadd_rn(v.w, b.w));
         }
-        if (a.pre_hidden && blockIdx.x == 0) *reinterpret_cast<float4*>(a.pre_hidden + e0) = v;
+        if (a.pre_hidden && cta == 0) *reinterpret_cast<float4*>(a.pre_hidden + e0) = v;
         ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
       } else {
         // single-precision exp (2 ulp) where the reference rounds an f64 exp to f32: every CTA
@@ -227,21 +244,23 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
       se += v.x + v.z;
       so += v.y + v.w;
     }
-    xc[idx] = make_float2(Unpack<MODE>::kOffEven * se + Unpack<MODE>::kOffOdd * so, se + so);
+    xc[idx] = mlx_unit_consts<MODE>(se, so);
   }
   __syncthreads();
 }
 
-template <int R, int M, int MODE, bool SB_BF16>
-__global__ void __launch_bounds__(kThreads)
-mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// The streaming product for one launch's worth of work, as CTA `cta` of `nctas`.  `wait` runs on
+// every thread after the first weight loads are issued and before x is read: it is where the
+// producer of x is waited for.
+template <int R, int M, int MODE, bool SB_BF16, class Wait>
+__device__ __forceinline__ void mlx_gemv_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait,
+                                              long long* staged_at = nullptr) {
   float4* xs = reinterpret_cast<float4*>(smem_raw);
   float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)M * a.iters * 8 * 32 * 16);
 
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int task_stride = gridDim.x * kWarps;
+  const int task_stride = nctas * kWarps;
   const int iters = a.iters;
   const int units = a.units;
   typedef typename std::conditional<SB_BF16, uint32_t, float2>::type SbT;
@@ -272,7 +291,7 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
   };
   struct Tile {
     uint4 w[R];
-    uint32_t s[R], b[R];  // scale, bias as f32 bit patterns
+    SbT sb[R];  // as loaded: nothing is computed from a tile before its step, so a load never blocks the issue of the next
   };
   auto load_tile = [&](const Rows& t, int it, Tile& d) {
     int unit = it * 32 + lane;
@@ -281,36 +300,48 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       d.w[r] = ld_stream(t.w[r] + unit);
-      if (SB_BF16) {
-        uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(t.sb[r]) + grp);
-        d.s[r] = v << 16;
-        d.b[r] = v & 0xFFFF0000u;
-      } else {
-        float2 v = __ldg(reinterpret_cast<const float2*>(t.sb[r]) + grp);
-        d.s[r] = __float_as_uint(v.x);
-        d.b[r] = __float_as_uint(v.y);
-      }
+      d.sb[r] = __ldg(t.sb[r] + grp);
     }
   };
+  auto tile_scale = [](const SbT& v) -> float {
+    if constexpr (SB_BF16) return __uint_as_float(v << 16);
+    else return v.x;
+  };
+  auto tile_bias = [](const SbT& v) -> float {
+    if constexpr (SB_BF16) return __uint_as_float(v & 0xFFFF0000u);
+    else return v.y;
+  };
 
-  // The weights do not depend on the kernel in front: issue the first loads, then wait for it
-  // (programmatic dependent launch) and stage x.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  Rows cur_rows, nxt_rows;
-  Tile cur, nxt;
-  int task = blockIdx.x * kWarps + warp;
-  const bool has_work = task < a.tasks;
-  if (has_work) {
-    open_task(task, cur_rows);
-    load_tile(cur_rows, 0, cur);
-  }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // A warp's work is a sequence of steps (task, iteration); the tiles of the next D steps are in
+  // flight in a ring of registers.  The weights do not depend on the producer of x: the ring is
+  // filled first, then the producer is waited for and x is staged.
+  constexpr int D = R == 1 ? 4 : 2;
+  const int first_task = cta * kWarps + warp;
+  const int my_tasks = first_task < a.tasks ? (a.tasks - 1 - first_task) / task_stride + 1 : 0;
+  const int nsteps = my_tasks * iters;
+  Rows ld_rows, cp_rows;
+  Tile ring[D];
+  int ld_step = 0, ld_task = first_task, ld_it = 0;
+  auto issue = [&](Tile& d) {
+    if (ld_step >= nsteps) return;
+    if (ld_it == 0) open_task(ld_task, ld_rows);
+    load_tile(ld_rows, ld_it, d);
+    ++ld_step;
+    if (++ld_it == iters) {
+      ld_it = 0;
+      ld_task += task_stride;
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < D; ++j) issue(ring[j]);
+  wait();
   if (M == 1 && a.pre_op != 0) {
-    mlx_stage_x_pre<MODE>(a, xs, xc);
+    mlx_stage_x_pre<MODE>(a, xs, xc, cta);
   } else {
     mlx_stage_x<M, MODE>(a, xs, xc);
   }
-  if (!has_work) return;
+  if (staged_at && threadIdx.x == 0) *staged_at = clock64();
+  if (nsteps == 0) return;
 
   float acc[R][M];
 #pragma unroll
@@ -318,17 +349,15 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
 
-  while (true) {
-    const int ntask = task + task_stride;
-    const bool more_tasks = ntask < a.tasks;
-    for (int it = 0; it < iters; ++it) {
-      // next tile in flight while this one is computed
-      if (it + 1 < iters) {
-        load_tile(cur_rows, it + 1, nxt);
-      } else if (more_tasks) {
-        open_task(ntask, nxt_rows);
-        load_tile(nxt_rows, 0, nxt);
-      }
+  int cp_task = first_task, cp_it = 0;
+  open_task(cp_task, cp_rows);
+  for (int s0 = 0; s0 < nsteps; s0 += D) {
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+      if (s0 + j >= nsteps) break;
+      const Tile cur = ring[j];
+      issue(ring[j]);  // the slot's next occupant: step s0 + j + D
+      const int it = cp_it;
       float2 F[R][M];
 #pragma unroll
       for (int r = 0; r < R; ++r)
@@ -363,25 +392,261 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           float dot = (F[r][m].x + F[r][m].y) - c.x;
-          acc[r][m] = fmaf(__uint_as_float(cur.s[r]), dot, acc[r][m]);
-          acc[r][m] = fmaf(__uint_as_float(cur.b[r]), c.y, acc[r][m]);
+          acc[r][m] = fmaf(tile_scale(cur.sb[r]), dot, acc[r][m]);
+          acc[r][m] = fmaf(tile_bias(cur.sb[r]), c.y, acc[r][m]);
         }
       }
-      cur = nxt;
-    }
+      if (++cp_it == iters) {  // the task's rows are complete
 #pragma unroll
-    for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float v = warp_sum(acc[r][m]);
-        acc[r][m] = 0.f;
-        if (lane == 0 && cur_rows.row0 + r < cur_rows.rows && m < a.batch)
-          cur_rows.out[(size_t)m * cur_rows.rows + cur_rows.row0 + r] = v;
+          for (int m = 0; m < M; ++m) {
+            float v = warp_sum(acc[r][m]);
+            acc[r][m] = 0.f;
+            if (lane == 0 && cp_rows.row0 + r < cp_rows.rows && m < a.batch)
+              cp_rows.out[(size_t)m * cp_rows.rows + cp_rows.row0 + r] = v;
+          }
+        cp_it = 0;
+        cp_task += task_stride;
+        if (s0 + j + 1 < nsteps) open_task(cp_task, cp_rows);
       }
-    if (!more_tasks) break;
-    cur_rows = nxt_rows;
-    task = ntask;
+    }
   }
+}
+
+// The product of a list entry (one row per warp task, batch 1), arranged so that as little as
+// possible is left to do once x exists: the tiles of a warp's first four steps are loaded and the
+// nibbles of its first two steps are already turned into floats while the producer of x is
+// awaited; x is staged with one pass and one barrier, each lane forming its unit's two constants
+// from the values it reads anyway.  Same arithmetic, in the same order, as mlx_gemv_body.
+template <int MODE, bool SB_BF16, class Wait>
+__device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait,
+                                              long long* staged_at) {
+  float4* xs = reinterpret_cast<float4*>(smem_raw);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int task_stride = nctas * kWarps, iters = a.iters, units = a.units;
+  typedef typename std::conditional<SB_BF16, uint32_t, float2>::type SbT;
+  constexpr int D = 4, P = 2;
+  struct Row {
+    const uint4* w;
+    const SbT* sb;
+    float* out;  // where this task's result goes, or nullptr
+  };
+  struct Tile {
+    uint4 w;
+    SbT sb;
+  };
+  auto open_task = [&](int task, Row& t) {
+    int seg = 0;
+#pragma unroll
+    for (int s = 1; s < kMaxSeg; ++s)
+      if (s < a.nseg && task >= a.seg[s].task0) seg = s;
+    const MlxSeg& sg = a.seg[seg];
+    const int row = task - sg.task0;
+    t.w = sg.w + (size_t)row * units;
+    t.sb = reinterpret_cast<const SbT*>(sg.sb) + (size_t)row * a.groups;
+    t.out = sg.out + row;
+  };
+  const int first_task = cta * kWarps + warp;
+  const int my_tasks = first_task < a.tasks ? (a.tasks - 1 - first_task) / task_stride + 1 : 0;
+  const int nsteps = my_tasks * iters;
+  Row ld_row, cp_row;
+  Tile ring[D];
+  int ld_step = 0, ld_task = first_task, ld_it = 0;
+  auto issue = [&](Tile& d) {
+    if (ld_step >= nsteps) return;
+    if (ld_it == 0) open_task(ld_task, ld_row);
+    int unit = ld_it * 32 + lane;
+    if (unit >= units) unit = units - 1;  // x is zero there; any finite weight will do
+    d.w = ld_stream(ld_row.w + unit);
+    d.sb = __ldg(ld_row.sb + (unit >> a.ug_shift));
+    ++ld_step;
+    if (++ld_it == iters) {
+      ld_it = 0;
+      ld_task += task_stride;
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < D; ++j) issue(ring[j]);
+  float pf[P][32];
+#pragma unroll
+  for (int p = 0; p < P; ++p)
+    if (p < nsteps) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t word = k == 0 ? ring[p].w.x : k == 1 ? ring[p].w.y : k == 2 ? ring[p].w.z : ring[p].w.w;
+        float f[8];
+        Unpack<MODE>::run(word, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pf[p][8 * k + e] = f[e];
+      }
+    }
+  wait();
+  {  // x -> shared memory, [iteration][slot = warp][lane]; plain (coherent) loads
+    const int slot = warp & 7;
+    for (int j0 = 0; j0 < iters; j0 += 4) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int unit = (j0 + u) * 32 + lane;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j0 + u < iters && unit < units) v[u] = *reinterpret_cast<const float4*>(a.x + (size_t)unit * 32 + slot * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (j0 + u < iters) xs[(j0 + u) * 256 + threadIdx.x] = v[u];
+    }
+  }
+  __syncthreads();
+  if (staged_at && threadIdx.x == 0) *staged_at = clock64();
+  if (nsteps == 0) return;
+
+  float acc = 0.f;
+  int cp_task = first_task, cp_it = 0;
+  open_task(cp_task, cp_row);
+  // one step: F = sum (offset + nibble) * x over the lane's unit, then the scale and bias terms
+  auto step = [&](auto&& nibbles, const SbT sb, int s) {
+    float se = 0.f, so = 0.f;
+    float2 F = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float4 xa = xs[(cp_it * 8 + 2 * k) * 32 + lane], xb = xs[(cp_it * 8 + 2 * k + 1) * 32 + lane];
+      se += xa.x + xa.z;
+      so += xa.y + xa.w;
+      se += xb.x + xb.z;
+      so += xb.y + xb.w;
+      float f[8];
+      nibbles(k, f);
+      fma2(F, make_float2(f[0], f[1]), make_float2(xa.x, xa.y));
+      fma2(F, make_float2(f[2], f[3]), make_float2(xa.z, xa.w));
+      fma2(F, make_float2(f[4], f[5]), make_float2(xb.x, xb.y));
+      fma2(F, make_float2(f[6], f[7]), make_float2(xb.z, xb.w));
+    }
+    const float2 c = mlx_unit_consts<MODE>(se, so);
+    const float dot = (F.x + F.y) - c.x;
+    float sc, bi;
+    if constexpr (SB_BF16) {
+      sc = __uint_as_float(sb << 16);
+      bi = __uint_as_float(sb & 0xFFFF0000u);
+    } else {
+      sc = sb.x;
+      bi = sb.y;
+    }
+    acc = fmaf(sc, dot, acc);
+    acc = fmaf(bi, c.y, acc);
+    if (++cp_it == iters) {  // the task's row is complete
+      const float v = warp_sum(acc);
+      acc = 0.f;
+      if (lane == 0) *cp_row.out = v;
+      cp_it = 0;
+      cp_task += task_stride;
+      if (s + 1 < nsteps) open_task(cp_task, cp_row);
+    }
+  };
+#pragma unroll
+  for (int p = 0; p < P; ++p)
+    if (p < nsteps) {
+      const SbT sb = ring[p].sb;
+      issue(ring[p]);  // the slot's next occupant: step p + D
+      step([&](int k, float (&f)[8]) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = pf[p][8 * k + e];
+      }, sb, p);
+    }
+  for (int s0 = P; s0 < nsteps; s0 += D) {
+#pragma unroll
+    for (int j = 0; j < D; ++j) {
+      if (s0 + j >= nsteps) break;
+      const Tile cur = ring[(P + j) % D];
+      issue(ring[(P + j) % D]);
+      step([&](int k, float (&f)[8]) {
+        const uint32_t word = k == 0 ? cur.w.x : k == 1 ? cur.w.y : k == 2 ? cur.w.z : cur.w.w;
+        Unpack<MODE>::run(word, f);
+      }, cur.sb, s0 + j);
+    }
+  }
+}
+
+// One product per launch; x may come from the kernel in front (programmatic dependent launch).
+template <int R, int M, int MODE, bool SB_BF16>
+__global__ void __launch_bounds__(kThreads)
+mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  mlx_gemv_body<R, M, MODE, SB_BF16>(a, smem_raw, blockIdx.x, gridDim.x,
+                                     [] { asm volatile("griddepcontrol.wait;" ::: "memory"); });
+}
+
+// A list of products in one cooperative launch: every CTA works through the list, and a barrier
+// over the whole grid stands between consecutive products (product k+1 may read what product k
+// wrote).  Each CTA issues its first weight loads of product k+1 before it waits at the barrier,
+// and fetches the next product's arguments while it computes.  The barrier is a counter in global
+// memory that only grows: launch number L of a list of n products on G CTAs starts at L*(n-1)*G
+// (L is read from launches[0] before a CTA's first arrival and advanced by CTA 0 after the last
+// barrier, when every CTA has read it).  A wait gives up after about a second: the CTA records
+// 200 + the product's index in *status and leaves the list, and so do the others.
+constexpr long long kBarrierTimeoutCycles = 2000000000ll;
+
+template <int MODE, bool SB_BF16>
+__global__ void __launch_bounds__(kThreads, 2)
+mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter, unsigned* launches, int* status,
+                   long long* probe) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ __align__(16) MlxArgs args[2];
+  __shared__ unsigned s_base;
+  __shared__ int s_abort;
+  constexpr int kArgWords = sizeof(MlxArgs) / 4;
+  static_assert(sizeof(MlxArgs) % 4 == 0, "MlxArgs is copied word by word");
+  for (int i = threadIdx.x; i < kArgWords; i += kThreads)
+    reinterpret_cast<uint32_t*>(&args[0])[i] = reinterpret_cast<const uint32_t*>(&ops[0])[i];
+  if (threadIdx.x == 0) {
+    s_base = *reinterpret_cast<volatile unsigned*>(launches) * (unsigned)(nops - 1) * gridDim.x;
+    s_abort = 0;
+  }
+  __syncthreads();
+  // tuning aid (option mlx_probe): CTA 0 and the last CTA record clock64 at six points of products 8..11
+  long long tp[6] = {0, 0, 0, 0, 0, 0};
+  const bool probing = probe && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && threadIdx.x == 0;
+  for (int op = 0; op < nops; ++op) {
+    if (probing) tp[0] = clock64();
+    mlx_list_body<MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, [&] {
+      if (probing) tp[1] = clock64();
+      // the next product's arguments, fetched by the upper half of the CTA while thread 0 polls;
+      // they become visible to all with the barriers inside the staging of x
+      if (op + 1 < nops && threadIdx.x >= 128) {
+        for (int i = threadIdx.x - 128; i < kArgWords; i += kThreads - 128)
+          reinterpret_cast<uint32_t*>(&args[(op + 1) & 1])[i] = reinterpret_cast<const uint32_t*>(&ops[op + 1])[i];
+      }
+      if (op == 0) return;
+      if (threadIdx.x == 0) {
+        const unsigned target = s_base + (unsigned)op * gridDim.x;
+        const long long t0 = clock64();
+        unsigned seen;
+        while (true) {
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+          if ((int)(seen - target) >= 0) break;
+          if (clock64() - t0 > kBarrierTimeoutCycles) {
+            s_abort = 1;
+            atomicExch(status, 200 + op);
+            break;
+          }
+        }
+        if (probing) tp[2] = clock64();
+      }
+      __syncthreads();
+    }, probing ? &tp[3] : nullptr);
+    if (probing) tp[4] = clock64();
+    __syncthreads();  // every warp is done with x in shared memory and has stored its rows
+    if (s_abort) return;
+    if (op + 1 < nops && threadIdx.x == 0)
+      asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(counter), "r"(1u) : "memory");
+    if (probing) {
+      tp[5] = clock64();
+      if (op >= 8 && op < 12)
+        for (int i = 0; i < 6; ++i) probe[((blockIdx.x ? 4 : 0) + (op - 8)) * 6 + i] = tp[i];
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && nops > 1) atomicAdd(launches, 1u);
 }
 
 // Any group size / ragged in_dim: one warp per row, plain conversions, x from global.
@@ -676,9 +941,164 @@ static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const*
   return GOPH_OK;
 }
 
+typedef void (*MlxProgramKernel)(const MlxArgs*, int, unsigned*, unsigned*, int*, long long*);
+
+static MlxProgramKernel pick_program_kernel(int mode, bool bf16) {
+  if (mode == UNPACK_PAIR) return bf16 ? mlx_program_kernel<UNPACK_PAIR, true> : mlx_program_kernel<UNPACK_PAIR, false>;
+  if (mode == UNPACK_CVT) return bf16 ? mlx_program_kernel<UNPACK_CVT, true> : mlx_program_kernel<UNPACK_CVT, false>;
+  return bf16 ? mlx_program_kernel<UNPACK_EXACT, true> : mlx_program_kernel<UNPACK_EXACT, false>;
+}
+
 }  // namespace goph
 
+// A fixed list of batch-1 products launched as one cooperative kernel (see mlx_program_kernel).
+struct goph_mlx_program {
+  uint32_t magic;
+  int device;
+  int nops;
+  int grid;
+  size_t smem;
+  goph::MlxProgramKernel kernel;
+  goph::MlxArgs* ops;   // device
+  unsigned* words;      // device: [0] barrier counter, [1] launches so far, [2] status; from byte 64: 48 probe timestamps
+};
+
 using namespace goph;
+
+constexpr uint32_t kMagicProgram = 0x4d50524f;  // "MPRO"
+
+GOPH_API int goph_mlx_program_create(int device, int n_ops, const int* weights_per_op,
+                                     const goph_mlx_weight* const* ws, float* const* outs_dev,
+                                     const float* const* xs_dev, goph_mlx_program** out) {
+  clear_error();
+  if (!out) return fail(GOPH_E_INVALID, "goph_mlx_program_create: nil result pointer");
+  *out = nullptr;
+  if (n_ops <= 0 || !weights_per_op || !ws || !outs_dev || !xs_dev)
+    return fail(GOPH_E_INVALID, "goph_mlx_program_create: empty list or nil array");
+  std::vector<MlxArgs> ops((size_t)n_ops);
+  int k = 0, max_iters = 1;
+  const goph_mlx_weight* first = ws[0];
+  for (int o = 0; o < n_ops; ++o) {
+    const int n = weights_per_op[o];
+    if (n <= 0 || n > kMaxSeg) return fail(GOPH_E_INVALID, "product %d: %d weights (1..%d allowed)", o, n, kMaxSeg);
+    MlxArgs& a = ops[o];
+    memset(&a, 0, sizeof a);
+    const goph_mlx_weight* w0 = ws[k];
+    for (int i = 0; i < n; ++i) {
+      const goph_mlx_weight* w = ws[k + i];
+      if (!valid_handle(w)) return fail(GOPH_E_INVALID, "product %d: invalid weight handle", o);
+      if (w->device != device) return fail(GOPH_E_INVALID, "product %d: weight lives on device %d", o, w->device);
+      if (w->tiled || !fast_path_ok(w))
+        return fail(GOPH_E_UNSUPPORTED, "product %d: only row-major weights with a power-of-two group size >= 32 "
+                                        "and in_dim %% 32 == 0 can join a product list", o);
+      if (w->in_dim != w0->in_dim || w->group_size != w0->group_size)
+        return fail(GOPH_E_INVALID, "product %d: its weights do not share x (in_dim/group size differ)", o);
+      if (!first || w->sb_bf16 != first->sb_bf16)
+        return fail(GOPH_E_UNSUPPORTED, "product %d: scale tables of one list must share a format", o);
+      if (!outs_dev[k + i]) return fail(GOPH_E_INVALID, "product %d: nil output", o);
+      a.seg[i].w = reinterpret_cast<const uint4*>(w->qweight);
+      a.seg[i].sb = w->sb;
+      a.seg[i].out = outs_dev[k + i];
+      a.seg[i].rows = w->out_dim;
+      a.seg[i].task0 = a.tasks;
+      a.tasks += w->out_dim;  // one row per warp task
+    }
+    if (!xs_dev[o] || (uintptr_t)xs_dev[o] % 16) return fail(GOPH_E_INVALID, "product %d: x is nil or not 16-byte aligned", o);
+    a.nseg = n;
+    a.x = xs_dev[o];
+    a.batch = 1;
+    a.in_dim = w0->in_dim;
+    a.units = w0->in_dim / 32;
+    a.iters = (a.units + 31) / 32;
+    a.groups = w0->groups;
+    int upg = w0->group_size / 32, sh = 0;
+    while ((1 << sh) < upg) ++sh;
+    a.ug_shift = sh;
+    a.x_aligned = 1;
+    if (a.iters > max_iters) max_iters = a.iters;
+    k += n;
+  }
+  const size_t smem = mlx_smem_bytes(1, max_iters);
+  if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "product list: in_dim too large for shared memory");
+  if (int rc = use_device(device)) return rc;
+  DeviceState& st = device_state(device);
+  MlxProgramKernel kern = pick_program_kernel(options().mlx_unpack, first->sb_bf16 != 0);
+  GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int per_sm = 0;
+  GOPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
+  if (per_sm < 1) return fail(GOPH_E_UNSUPPORTED, "product list kernel does not fit (smem %zu)", smem);
+  if (per_sm > 2) per_sm = 2;  // 16 warps per SM keep the loads in flight; more CTAs only lengthen the barrier
+  auto* p = new goph_mlx_program();
+  p->magic = kMagicProgram;
+  p->device = device;
+  p->nops = n_ops;
+  p->grid = st.sm_count * per_sm;
+  p->smem = smem;
+  p->kernel = kern;
+  cudaError_t e = cudaMalloc(&p->ops, ops.size() * sizeof(MlxArgs));
+  if (e == cudaSuccess) e = cudaMalloc(&p->words, 64 + 48 * 8);
+  if (e == cudaSuccess) e = cudaMemcpy(p->ops, ops.data(), ops.size() * sizeof(MlxArgs), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemset(p->words, 0, 64 + 48 * 8);
+  if (e != cudaSuccess) {
+    cudaFree(p->ops);
+    cudaFree(p->words);
+    delete p;
+    return fail_cuda(e, "goph_mlx_program_create");
+  }
+  *out = p;
+  return GOPH_OK;
+}
+
+GOPH_API int goph_mlx_program_run(goph_mlx_program* p, void* stream) {
+  clear_error();
+  if (!p || p->magic != kMagicProgram) return fail(GOPH_E_INVALID, "invalid product list handle");
+  if (int rc = use_device(p->device)) return rc;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeCooperative;
+  attr.val.cooperative = 1;  // every CTA resident at once: the barrier between products needs it
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(p->grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = p->smem;
+  cfg.stream = (cudaStream_t)stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  long long* probe = options().mlx_probe ? reinterpret_cast<long long*>(p->words + 16) : nullptr;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, p->kernel, (const MlxArgs*)p->ops, p->nops, p->words, p->words + 1,
+                               reinterpret_cast<int*>(p->words + 2), probe));
+  return GOPH_OK;
+}
+
+/* Tuning aid: the 48 timestamps recorded under option "mlx_probe" (see mlx_program_kernel). */
+GOPH_API int goph_mlx_program_probe(goph_mlx_program* p, long long* out48) {
+  clear_error();
+  if (!p || p->magic != kMagicProgram || !out48) return fail(GOPH_E_INVALID, "goph_mlx_program_probe: bad arguments");
+  if (int rc = use_device(p->device)) return rc;
+  GOPH_CUDA(cudaMemcpy(out48, p->words + 16, 48 * 8, cudaMemcpyDeviceToHost));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_mlx_program_status(goph_mlx_program* p, int* out_status) {
+  clear_error();
+  if (!p || p->magic != kMagicProgram) return fail(GOPH_E_INVALID, "invalid product list handle");
+  if (!out_status) return fail(GOPH_E_INVALID, "goph_mlx_program_status: nil result pointer");
+  if (int rc = use_device(p->device)) return rc;
+  GOPH_CUDA(cudaMemcpy(out_status, p->words + 2, 4, cudaMemcpyDeviceToHost));
+  return GOPH_OK;
+}
+
+GOPH_API int goph_mlx_program_free(goph_mlx_program* p) {
+  clear_error();
+  if (!p) return GOPH_OK;
+  if (p->magic != kMagicProgram) return fail(GOPH_E_INVALID, "goph_mlx_program_free: not a product list handle");
+  if (int rc = use_device(p->device)) return rc;
+  cudaFree(p->ops);
+  cudaFree(p->words);
+  p->magic = 0;
+  delete p;
+  return GOPH_OK;
+}
 
 static int mlx_upload_common(int device, const uint32_t* weight, const float* scales, const float* biases,
                              bool on_device, int in_dim, int out_dim, int gs, goph_mlx_weight** out) {

@@ -25,6 +25,7 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 EXPORTS = [
     "goph_init", "goph_set_option", "goph_kernel_status", "goph_debug_probe", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
+    "goph_mlx_program_create", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free", "goph_mlx_program_probe",
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
@@ -406,6 +407,46 @@ def GemvQ6KBatchToBuffer(out, x, batch, m, stream=None):
     """nvidia.GemvQ6KBatchToBuffer (runtime/qk.go:285)."""
     _want_qtype(m, GGUF_Q6_K, "Q6_K")
     m.ProjectBatchToBuffer(out, x, batch, stream)
+
+
+class MLXProgram:
+    """A list of batch-1 MLX products run as one cooperative launch (goph_mlx_program_*).
+    ops: [(x Buffer, [weights], [out Buffers])]; product k+1 may read what product k wrote."""
+
+    def __init__(self, ops):
+        ws, outs, xs, counts = [], [], [], []
+        for x, hs, os_ in ops:
+            if len(hs) != len(os_) or not hs:
+                raise GophError(1, "product needs as many outputs as weights")
+            counts.append(len(hs)); xs.append(x.Ptr)
+            ws += [_mlx_handle(h) for h in hs]; outs += [o.Ptr for o in os_]
+        self._keep = ops
+        self.n = len(ops)
+        h = C.c_void_p(0)
+        _check(lib().goph_mlx_program_create(_device, len(ops), (C.c_int * len(counts))(*counts),
+                                             (C.c_void_p * len(ws))(*ws),
+                                             (C.c_void_p * len(outs))(*outs), (C.c_void_p * len(xs))(*xs), C.byref(h)))
+        self._h = h
+
+    def Run(self, stream=None):
+        if not self._h:
+            raise GophError(1, "freed product list")
+        _check(lib().goph_mlx_program_run(self._h, _stream_ptr(stream)))
+
+    def Status(self):
+        st = C.c_int(0)
+        _check(lib().goph_mlx_program_status(self._h, C.byref(st)))
+        return st.value
+
+    def Probe(self):
+        out = (C.c_longlong * 48)()
+        _check(lib().goph_mlx_program_probe(self._h, out))
+        return np.array(out[:], dtype=np.int64).reshape(2, 4, 6)
+
+    def Free(self):
+        if self._h:
+            _check(lib().goph_mlx_program_free(self._h))
+            self._h = None
 
 
 # ------------------------------------------------------------------------------- GPTQ

@@ -191,6 +191,33 @@ int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint
 int goph_gguf_project_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
                            int batch, const goph_gguf_matrix* m);
 
+/* ---- product lists: many batch-1 MLX products in one launch -------------------------------
+ * The reference launches one kernel per projection (runtime/mlx.go:287-321); at batch 1 the small
+ * projections of a decode step are bound by launch latency, not by memory.  A product list is
+ * created once from the weights, outputs and activation vectors of consecutive projections and
+ * then run as ONE cooperative kernel: every CTA works through the list, with a grid-wide barrier
+ * between products, so product k+1 may read (as its x) what product k wrote.  Results are those
+ * of goph_mlx_gemv on the same arguments, bit for bit. */
+typedef struct goph_mlx_program goph_mlx_program;
+
+/* n_ops products; product o multiplies xs_dev[o] (in_dim f32, 16-byte aligned) with
+ * weights_per_op[o] weights (1..8, sharing in_dim and group size; ws and outs_dev are the
+ * concatenation over products).  Weights must be in the row-major layout (upload with option
+ * "mlx_layout" = 1 or under 8 Mi weights), group size a power of two >= 32, one scale-table
+ * format per list.  The buffers are borrowed: they must outlive the list. */
+int goph_mlx_program_create(int device, int n_ops, const int* weights_per_op, const goph_mlx_weight* const* ws,
+                            float* const* outs_dev, const float* const* xs_dev, goph_mlx_program** out);
+/* Runs the list on `stream` (capturable into a CUDA graph).  Runs of one list must not overlap. */
+int goph_mlx_program_run(goph_mlx_program* p, void* stream);
+/* 0, or 200 + k when a CTA gave up waiting (about a second) at the barrier in front of product k;
+ * the list must then be freed.  Synchronises with the device. */
+int goph_mlx_program_status(goph_mlx_program* p, int* out_status);
+int goph_mlx_program_free(goph_mlx_program* p);
+/* Tuning aid: with option "mlx_probe" set, the first and the last CTA record clock64 at six points
+ * (product entered, first loads issued, barrier passed, x staged, rows stored, arrival posted) of
+ * products 8..11; this copies the 2 x 4 x 6 values out. */
+int goph_mlx_program_probe(goph_mlx_program* p, long long* out48);
+
 /* ---- GPTQ symmetric INT4 weights (backends/simd/quant/q4, runtime/q4.go, gemm_q4.go) ---- */
 
 typedef struct goph_gptq_weight goph_gptq_weight; /* nvidia.GPUQuantWeight (runtime/q4.go:18-26) */

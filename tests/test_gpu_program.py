@@ -1,0 +1,112 @@
+"""Product lists (goph_mlx_program_*): many dependent batch-1 products in one cooperative launch."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def chain(gpu, pkg, dims, gs=64):
+    """dims: [(in, [outs])]; the first output of a product is the next product's x."""
+    syn = pkg.synth
+    x0 = gpu.from_numpy(syn.activations("prog", dims[0][0], bf16=False))
+    ops, x = [], x0
+    for k, (in_dim, outs) in enumerate(dims):
+        hs = [gpu.UploadMLXWeight(*syn.mlx_weight(("prog", k, i), o, in_dim, gs), in_dim, o, gs, True) for i, o in enumerate(outs)]
+        os_ = [gpu.Malloc(o) for o in outs]
+        ops.append((x, hs, os_))
+        x = os_[0]
+    return x0, ops
+
+
+def run_separately(gpu, ops):
+    for x, hs, os_ in ops:
+        if len(hs) == 1:
+            gpu.GemvMLX(os_[0], x, hs[0])
+        else:
+            gpu.GemmMLXMulti(os_, x, hs, 1)
+    gpu.Sync()
+    return [o.Download() for _, _, os_ in ops for o in os_]
+
+
+DIMS = [(1024, [2048]), (2048, [1024, 512, 96]), (1024, [3072]), (3072, [1024]), (1024, [40])]
+
+
+def test_list_equals_separate_launches_bit_for_bit(gpu, pkg):
+    x0, ops = chain(gpu, pkg, DIMS)
+    want = run_separately(gpu, ops)
+    for _, _, os_ in ops:
+        for o in os_:
+            o.Upload(np.full(o.n, 7.0, dtype=np.float32))
+    prog = gpu.MLXProgram(ops)
+    for rep in range(3):   # the barrier counter carries over from launch to launch
+        prog.Run()
+        gpu.Sync()
+        got = [o.Download() for _, _, os_ in ops for o in os_]
+        for g, w in zip(got, want):
+            assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), rep
+        assert prog.Status() == 0
+    prog.Free(); prog.Free()
+    with pytest.raises(gpu.GophError):
+        prog.Run()
+
+
+def test_list_replays_in_a_cuda_graph_with_new_inputs(gpu, pkg):
+    import torch
+    x0, ops = chain(gpu, pkg, DIMS)
+    prog = gpu.MLXProgram(ops)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        prog.Run(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        prog.Run(torch.cuda.current_stream())
+    for k in range(4):
+        x0.Upload(pkg.synth.activations(("prog-x", k), DIMS[0][0], bf16=False))
+        g.replay()
+        torch.cuda.synchronize()
+        got = [o.Download() for _, _, os_ in ops for o in os_]
+        want = run_separately(gpu, ops)
+        for a, b in zip(got, want):
+            assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), k
+    assert prog.Status() == 0
+    prog.Free()
+
+
+def test_single_product_and_group_size_128(gpu, pkg):
+    x0, ops = chain(gpu, pkg, [(2048, [300, 7])], gs=128)
+    want = run_separately(gpu, ops)
+    for o in ops[0][2]:
+        o.Upload(np.zeros(o.n, dtype=np.float32))
+    prog = gpu.MLXProgram(ops)
+    prog.Run(); prog.Run()
+    gpu.Sync()
+    for o, w in zip(ops[0][2], want):
+        assert np.array_equal(o.Download().view(np.uint32), w.view(np.uint32))
+    prog.Free()
+
+
+def test_malformed_lists_raise(gpu, pkg):
+    syn = pkg.synth
+    x0, ops = chain(gpu, pkg, [(1024, [64]), (64, [32])])
+    with pytest.raises(gpu.GophError):
+        gpu.MLXProgram([])
+    with pytest.raises(gpu.GophError):
+        gpu.MLXProgram([(x0, ops[0][1], [])])
+    with pytest.raises(gpu.GophError):      # weights of one product must share x
+        gpu.MLXProgram([(x0, [ops[0][1][0], ops[1][1][0]], [ops[0][2][0], ops[1][2][0]])])
+    with pytest.raises(gpu.GophError):      # more than eight weights in one product
+        gpu.MLXProgram([(x0, ops[0][1] * 9, ops[0][2] * 9)])
+    gpu.SetOption("mlx_layout", 2)
+    try:
+        tiled = gpu.UploadMLXWeight(*syn.mlx_weight("prog-t", 256, 1024, 64), 1024, 256, 64, True)
+    finally:
+        gpu.SetOption("mlx_layout", 0)
+    with pytest.raises(gpu.GophError):      # tensor-core layout
+        gpu.MLXProgram([(x0, [tiled], [gpu.Malloc(256)])])
+    odd = gpu.wrap(x0.Ptr + 4, 4 * 1020)
+    with pytest.raises(gpu.GophError):      # x not 16-byte aligned
+        gpu.MLXProgram([(odd, ops[0][1], ops[0][2])])
+    ops[0][1][0].Free()
+    with pytest.raises(gpu.GophError):
+        gpu.MLXProgram(ops)
