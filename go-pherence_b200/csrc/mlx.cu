@@ -1004,6 +1004,11 @@ GOPH_API int goph_mlx_program_create(int device, int n_ops, const int* weights_p
       a.tasks += w->out_dim;  // one row per warp task
     }
     if (!xs_dev[o] || (uintptr_t)xs_dev[o] % 16) return fail(GOPH_E_INVALID, "product %d: x is nil or not 16-byte aligned", o);
+    for (int i = 0; i < n; ++i) {  // the barrier orders products against each other, not a product against itself
+      const uintptr_t o0 = (uintptr_t)outs_dev[k + i], o1 = (uintptr_t)(outs_dev[k + i] + ws[k + i]->out_dim);
+      const uintptr_t x0 = (uintptr_t)xs_dev[o], x1 = (uintptr_t)(xs_dev[o] + w0->in_dim);
+      if (o0 < x1 && x0 < o1) return fail(GOPH_E_INVALID, "product %d: an output overlaps its x", o);
+    }
     a.nseg = n;
     a.x = xs_dev[o];
     a.batch = 1;

@@ -174,9 +174,9 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
 
 
-def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts=()):
-    """The projections of decoder layers at Llama-3-8B shapes as one dependent chain, batch 1:
-    q|k|v (hidden+2kv x hidden) -> o (hidden x hidden, fed by the first `hidden` outputs) ->
+def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts=(), qdim=0, as_list=False):
+    """The projections of decoder layers (Llama-3-8B shapes by default) as one dependent chain, batch 1:
+    q|k|v (qdim+2kv x hidden) -> o (hidden x qdim, fed by the first `qdim` outputs) ->
     gate|up (2 ffn x hidden) -> down (hidden x ffn, fed by the first `ffn` outputs) -> next layer.
     Every launch reads what the launch before it wrote, as in a decode step; `layers` layers have
     their own device copies of the weights (more than the L2 holds), replayed as a CUDA graph."""
@@ -187,7 +187,8 @@ def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts
     rt.init(0)
     for k, v in opts:
         rt.SetOption(k, v)
-    shapes = [(hidden + 2 * kv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
+    qdim = qdim or hidden
+    shapes = [(qdim + 2 * kv, hidden), (hidden, qdim), (2 * ffn, hidden), (hidden, ffn)]
     host = []
     for o, i in shapes:
         if fmt == "mlx4":
@@ -211,7 +212,7 @@ def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts
                 hs.append(rt.UploadFP8E4M3Linear(hw[0], hw[1], None, o, i))
             nbytes += algorithmic_bytes(fmt, o, i, 1)
         handles.append(hs)
-    bufs = [torch.zeros(max(2 * ffn, hidden + 2 * kv), dtype=torch.float32, device="cuda") for _ in range(2)]
+    bufs = [torch.zeros(max(2 * ffn, qdim + 2 * kv), dtype=torch.float32, device="cuda") for _ in range(2)]
     bufs[0][:hidden] = torch.from_numpy(syn.activations("chain", hidden)).cuda()
     wrap = lambda t: rt.wrap(t.data_ptr(), t.numel() * 4)
 
@@ -223,7 +224,21 @@ def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts
         else:
             h.ProjectBatchToBuffer(out, x, 1, stream)
 
+    program = None
+    if as_list:   # the same chain as one product list (one cooperative launch)
+        if fmt != "mlx4":
+            raise SystemExit("--list needs --format mlx4")
+        ops, cur = [], 0
+        for hs in handles:
+            for h in hs:
+                ops.append((wrap(bufs[cur]), [h], [wrap(bufs[1 - cur])]))
+                cur ^= 1
+        program = rt.MLXProgram(ops)
+
     def step(stream):
+        if program is not None:
+            program.Run(stream)
+            return
         cur = 0
         for hs in handles:
             for h in hs:
@@ -253,8 +268,11 @@ def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts
     for hs in handles:
         for h in hs:
             h.Free()
-    return {"format": fmt, "workload": "%d decoder layers of projections at Llama-3-8B shapes, dependent chain, batch 1" % layers,
-            "launches": 4 * layers, "us_per_layer": round(us / layers, 2), "GBps": round(gbs, 1),
+    if program is not None:
+        program.Free()
+    return {"format": fmt, "workload": "%d decoder layers of projections (hidden %d, q %d, kv %d, ffn %d), dependent chain, batch 1"
+                                       % (layers, hidden, qdim, kv, ffn),
+            "launches": 1 if as_list else 4 * layers, "us_per_product": round(us / (4 * layers), 3), "us_per_layer": round(us / layers, 2), "GBps": round(gbs, 1),
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
 
 
@@ -270,10 +288,17 @@ def main():
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
     ap.add_argument("--chain", action="store_true", help="each launch reads the previous launch's output (out == in)")
+    ap.add_argument("--list", action="store_true", help="--layer-chain as one product list (one cooperative launch)")
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--qdim", type=int, default=0)
+    ap.add_argument("--kv", type=int, default=1024)
+    ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--layers", type=int, default=8)
     args = ap.parse_args()
     opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
     if args.layer_chain:
-        print(json.dumps(run_layer_chain(args.format, opts=opts)))
+        print(json.dumps(run_layer_chain(args.format, args.hidden, args.ffn, args.kv, args.layers, opts=opts, qdim=args.qdim,
+                                         as_list=args.list)))
         return
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts)))

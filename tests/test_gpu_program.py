@@ -73,6 +73,59 @@ def test_list_replays_in_a_cuda_graph_with_new_inputs(gpu, pkg):
     prog.Free()
 
 
+def test_ping_pong_buffers_and_independent_products(gpu, pkg):
+    """Two buffers used alternately (every product overwrites the x of the product before it), then
+    products that do not depend on each other but share memory: the list must order them as
+    separate launches on one stream would."""
+    syn = pkg.synth
+    n = 1024
+    bufs = [gpu.Malloc(n), gpu.Malloc(n)]
+    bufs[0].Upload(syn.activations("pp", n, bf16=False))
+    ws = [gpu.UploadMLXWeight(*syn.mlx_weight(("pp", k), n, n, 64), n, n, 64, True) for k in range(6)]
+    ops = [(bufs[k & 1], [ws[k]], [bufs[1 - (k & 1)]]) for k in range(6)]
+    # an unrelated product that overwrites the very first x while the chain may still be reading it,
+    # and one more reading that result through a sub-range that straddles nothing (whole buffer)
+    ext, side = gpu.from_numpy(syn.activations("pp-ext", n, bf16=False)), gpu.Malloc(n)
+    ops.append((ext, [ws[0]], [bufs[0]]))
+    ops.append((bufs[0], [ws[1]], [side]))
+    x0 = bufs[0].Download()
+    want = run_separately(gpu, ops)
+    final = [b.Download() for b in bufs] + [side.Download()]
+    prog = gpu.MLXProgram(ops)
+    for rep in range(3):
+        bufs[0].Upload(x0)
+        prog.Run()
+        gpu.Sync()
+        got = [b.Download() for b in bufs] + [side.Download()]
+        for g, w in zip(got, final):
+            assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), rep
+        assert prog.Status() == 0
+    prog.Free()
+    with pytest.raises(gpu.GophError):      # a product may not overwrite its own x
+        gpu.MLXProgram([(bufs[0], [ws[0]], [bufs[0]])])
+
+
+def test_x_straddling_two_outputs_waits_for_both(gpu, pkg):
+    syn = pkg.synth
+    both = gpu.Malloc(1024)
+    lo, hi = gpu.wrap(both.Ptr, 4 * 512), gpu.wrap(both.Ptr + 4 * 512, 4 * 512)
+    x = gpu.from_numpy(syn.activations("st", 256, bf16=False))
+    wa = gpu.UploadMLXWeight(*syn.mlx_weight("st-a", 512, 256, 64), 256, 512, 64, True)
+    wb = gpu.UploadMLXWeight(*syn.mlx_weight("st-b", 512, 256, 64), 256, 512, 64, True)
+    wc = gpu.UploadMLXWeight(*syn.mlx_weight("st-c", 300, 1024, 64), 1024, 300, 64, True)
+    out = gpu.Malloc(300)
+    ops = [(x, [wa], [lo]), (x, [wb], [hi]), (both, [wc], [out])]
+    want = run_separately(gpu, ops)[-1]
+    out.Upload(np.zeros(300, dtype=np.float32))
+    prog = gpu.MLXProgram(ops)
+    for _ in range(2):
+        prog.Run()
+    gpu.Sync()
+    assert np.array_equal(out.Download().view(np.uint32), want.view(np.uint32))
+    assert prog.Status() == 0
+    prog.Free()
+
+
 def test_single_product_and_group_size_128(gpu, pkg):
     x0, ops = chain(gpu, pkg, [(2048, [300, 7])], gs=128)
     want = run_separately(gpu, ops)
