@@ -36,9 +36,10 @@ LAYER_OPS = [("qkv", [(QDIM, HIDDEN), (KVDIM, HIDDEN), (KVDIM, HIDDEN)]),
              ("down", [(HIDDEN, FFN)])]
 # dram__bytes_read.sum + dram__bytes_write.sum over algorithmic bytes, from the ncu captures
 # summarised under profiles/ (mlx_gemv_kernel on 3072x1024: 1.787 MB against 1.786 MB;
+# mlx_program_kernel on the 112-product chain: 252.3 MB against 249.9 MB;
 # mlx_mma_kernel on 65536x4096: 151.08 + 4.8 MB against 151.27 MB).  Traffic grows with the bytes
 # streamed, so a launch's traffic is its algorithmic bytes times this ratio.
-TRAFFIC_RATIO = {"mlx_gemv_kernel": 1.001, "mlx_program_kernel": 1.001, "mlx_mma_kernel": 1.031}
+TRAFFIC_RATIO = {"mlx_gemv_kernel": 1.001, "mlx_program_kernel": 1.010, "mlx_mma_kernel": 1.031}
 WORKLOAD = "qwen3-0.6b mlx4-g64 decode-step projections (28 layers x q|k|v,o,gate|up,down + LM head 151936x1024)"
 
 
