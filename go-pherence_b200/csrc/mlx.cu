@@ -482,7 +482,10 @@ __device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* s
       }
     }
   wait();
-  {  // x -> shared memory, [iteration][slot = warp][lane]; plain (coherent) loads
+  if (a.pre_op != 0) {
+    // residual add + RMSNorm, or SiLU(x) * b, applied while x is staged (as in goph_mlx_gemv_pre)
+    mlx_stage_x_pre<MODE>(a, xs, reinterpret_cast<float2*>(smem_raw + (size_t)iters * 8 * 32 * 16), cta);
+  } else {  // x -> shared memory, [iteration][slot = warp][lane]; plain (coherent) loads
     const int slot = warp & 7;
     for (int j0 = 0; j0 < iters; j0 += 4) {
       float4 v[4];
@@ -496,8 +499,8 @@ __device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* s
       for (int u = 0; u < 4; ++u)
         if (j0 + u < iters) xs[(j0 + u) * 256 + threadIdx.x] = v[u];
     }
+    __syncthreads();
   }
-  __syncthreads();
   if (staged_at && threadIdx.x == 0) *staged_at = clock64();
   if (nsteps == 0) return;
 
@@ -967,9 +970,24 @@ using namespace goph;
 
 constexpr uint32_t kMagicProgram = 0x4d50524f;  // "MPRO"
 
+GOPH_API int goph_mlx_program_create_pre(int device, int n_ops, const int* weights_per_op,
+                                         const goph_mlx_weight* const* ws, float* const* outs_dev,
+                                         const float* const* xs_dev, const int* pre_ops, const float* const* pre_b,
+                                         const float* const* pre_w, float* const* pre_hidden, const float* pre_eps,
+                                         goph_mlx_program** out);
+
 GOPH_API int goph_mlx_program_create(int device, int n_ops, const int* weights_per_op,
                                      const goph_mlx_weight* const* ws, float* const* outs_dev,
                                      const float* const* xs_dev, goph_mlx_program** out) {
+  return goph_mlx_program_create_pre(device, n_ops, weights_per_op, ws, outs_dev, xs_dev, nullptr, nullptr, nullptr, nullptr,
+                                     nullptr, out);
+}
+
+GOPH_API int goph_mlx_program_create_pre(int device, int n_ops, const int* weights_per_op,
+                                         const goph_mlx_weight* const* ws, float* const* outs_dev,
+                                         const float* const* xs_dev, const int* pre_ops, const float* const* pre_b,
+                                         const float* const* pre_w, float* const* pre_hidden, const float* pre_eps,
+                                         goph_mlx_program** out) {
   clear_error();
   if (!out) return fail(GOPH_E_INVALID, "goph_mlx_program_create: nil result pointer");
   *out = nullptr;
@@ -1004,11 +1022,33 @@ GOPH_API int goph_mlx_program_create(int device, int n_ops, const int* weights_p
       a.tasks += w->out_dim;  // one row per warp task
     }
     if (!xs_dev[o] || (uintptr_t)xs_dev[o] % 16) return fail(GOPH_E_INVALID, "product %d: x is nil or not 16-byte aligned", o);
-    for (int i = 0; i < n; ++i) {  // the barrier orders products against each other, not a product against itself
-      const uintptr_t o0 = (uintptr_t)outs_dev[k + i], o1 = (uintptr_t)(outs_dev[k + i] + ws[k + i]->out_dim);
-      const uintptr_t x0 = (uintptr_t)xs_dev[o], x1 = (uintptr_t)(xs_dev[o] + w0->in_dim);
-      if (o0 < x1 && x0 < o1) return fail(GOPH_E_INVALID, "product %d: an output overlaps its x", o);
+    // the barrier orders products against each other, not a product against itself: what a product
+    // writes (outputs, the hidden vector of operation 1) must not meet what it reads
+    const int pre_op = pre_ops ? pre_ops[o] : 0;
+    const float* pb = pre_op && pre_b ? pre_b[o] : nullptr;
+    const float* pw = pre_op && pre_w ? pre_w[o] : nullptr;
+    float* ph = pre_op == 1 && pre_hidden ? pre_hidden[o] : nullptr;
+    if (pre_op < 0 || pre_op > 2) return fail(GOPH_E_INVALID, "product %d: pre_op=%d", o, pre_op);
+    if ((pre_op == 1 && !pw) || (pre_op == 2 && !pb)) return fail(GOPH_E_INVALID, "product %d: missing operand of its operation", o);
+    if (((uintptr_t)pb | (uintptr_t)pw | (uintptr_t)ph) % 16) return fail(GOPH_E_INVALID, "product %d: vectors must be 16-byte aligned", o);
+    {
+      typedef std::pair<uintptr_t, uintptr_t> Range;
+      auto range = [](const float* p, int n) { return Range((uintptr_t)p, (uintptr_t)(p + n)); };
+      auto meet = [](Range p, Range q) { return p.first && q.first && p.first < q.second && q.first < p.second; };
+      std::vector<Range> reads = {range(xs_dev[o], w0->in_dim), range(pb, w0->in_dim)}, writes = {range(ph, w0->in_dim)};
+      for (int i = 0; i < n; ++i) writes.push_back(range(outs_dev[k + i], ws[k + i]->out_dim));
+      for (const Range& wr : writes)
+        for (const Range& rd : reads)
+          if (meet(wr, rd)) return fail(GOPH_E_INVALID, "product %d: an output overlaps its x", o);
+      for (size_t i = 0; i < writes.size(); ++i)
+        for (size_t j = i + 1; j < writes.size(); ++j)
+          if (meet(writes[i], writes[j])) return fail(GOPH_E_INVALID, "product %d: two of its outputs overlap", o);
     }
+    a.pre_op = pre_op;
+    a.pre_b = pb;
+    a.pre_w = pw;
+    a.pre_hidden = ph;
+    a.pre_eps = pre_eps ? pre_eps[o] : 0.f;
     a.nseg = n;
     a.x = xs_dev[o];
     a.batch = 1;

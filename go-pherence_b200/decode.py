@@ -4,7 +4,10 @@ Host-side mirror of GPUModel.Generate (model/gpu_forward.go:993-1357) over the C
 projections of a layer run as four fused products (q|k|v, o, gate|up, down) through goph_mlx_gemv,
 everything between them through the decode-step operations (goph_add_rmsnorm,
 goph_qk_norm_rope_append, goph_attn_decode, goph_silu_mul, goph_argmax_advance, goph_mlx_embed) or
-their fused forms (goph_mlx_gemv_pre, goph_attn_decode_fused: five launches per layer).
+their fused forms (goph_mlx_gemv_pre, goph_attn_decode_fused: five launches per layer), or — with
+product lists (goph_mlx_program_create_pre) — everything between two attentions (o, add + norm,
+gate|up, SiLU * up, down, add + norm, the next layer's q|k|v) as one cooperative launch: two launches
+per layer.
 The position, the current token, the prompt and the produced tokens live in device memory, so the
 whole step is captured once as a CUDA graph and replayed per token — prompt tokens included (they
 are fed one by one, as the reference's sequential loop does).  torch is used for stream capture only.
@@ -15,7 +18,7 @@ import numpy as np
 
 
 class MLXDecoder:
-    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64, fuse=True):
+    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64, fuse=True, lists=True):
         """cfg: an object with hidden, layers, heads, kv_heads, head_dim, inter, vocab, eps, qk_norm, max_seq.
         layers[l]: dict with "q","k","v","o","gate","up","down" -> (words, scales, biases) in the MLX
         layout, and "input_norm","post_norm" (+ "q_norm","k_norm") f32 vectors.  lm_head: the tied
@@ -59,6 +62,29 @@ class MLXDecoder:
         self.scale = 1.0 / math.sqrt(c.head_dim)
         self.graph = None
         self.launches_per_step = 0
+        self.lists = self._build_lists() if (self.fused and lists) else None
+
+    def _build_lists(self):
+        """The fused step's products grouped between the attentions: [q|k|v of layer 0], then per layer
+        [o, gate|up, down, q|k|v of the next layer] (the last without a next).  The buffers rotate exactly
+        as in step(); they are the same every token, so the lists are built once."""
+        rt, c = self.rt, self.cfg
+        cur, other = self.hidden, self.hidden2
+        gate, up = self._sub(self.gu, 0, c.inter), self._sub(self.gu, c.inter, c.inter)
+        lists, ops, pre, prev = [], [], [], None
+        for e in self.L:
+            ops.append((cur, [e["qkv"]], [self.qkv]))
+            pre.append(dict(op=1, b=prev, w=e["input_norm"], hidden=other if prev is not None else None, eps=c.eps))
+            if prev is not None:
+                cur, other = other, cur
+            lists.append(rt.MLXProgram(ops, pre))
+            ops = [(self.attn, [e["o"]], [self.proj]), (cur, [e["gate_up"]], [self.gu]), (gate, [e["down"]], [self.proj2])]
+            pre = [None, dict(op=1, b=self.proj, w=e["post_norm"], hidden=other, eps=c.eps), dict(op=2, b=up)]
+            cur, other = other, cur
+            prev = self.proj2
+        lists.append(rt.MLXProgram(ops, pre))
+        self._final = (cur, prev)
+        return lists
 
     def _sub(self, buf, off, n):
         return self.rt.wrap(buf.Ptr + 4 * off, 4 * n)
@@ -72,6 +98,20 @@ class MLXDecoder:
         n = 0
         cur, other = self.hidden, self.hidden2
         rt.EmbedMLX(cur, self.lm, self.tok, stream); n += 1
+        if self.lists is not None:
+            q, k, v = self._sub(self.qkv, 0, self.qd), self._sub(self.qkv, self.qd, self.kvd), self._sub(self.qkv, self.qd + self.kvd, self.kvd)
+            for li, e in enumerate(self.L):
+                self.lists[li].Run(stream)
+                rt.AttnDecodeFused(self.attn, q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.max_seq,
+                                   c.heads, c.kv_heads, c.head_dim, self.scale, c.eps, stream)
+                n += 2
+            self.lists[-1].Run(stream)
+            cur, prev = self._final
+            rt.AddRMSNorm(None, self.normed, cur, prev, self.final_norm, c.hidden, 1, c.eps, stream)
+            rt.GemvMLX(self.logits, self.normed, self.lm, stream)
+            rt.ArgmaxAdvance(self.logits, c.vocab, self.tok, self.pos, self.history, self.forced, c.max_seq, stream)
+            self.launches_per_step = n + 4 + (1 if self.lm.OutDim * self.lm.InDim >= (8 << 20) else 0)
+            return
         prev = None   # the projection output still to be added to the residual stream
         for e in self.L:
             if self.fused:

@@ -25,7 +25,7 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 EXPORTS = [
     "goph_init", "goph_set_option", "goph_kernel_status", "goph_debug_probe", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
-    "goph_mlx_program_create", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free", "goph_mlx_program_probe",
+    "goph_mlx_program_create", "goph_mlx_program_create_pre", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free", "goph_mlx_program_probe",
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
@@ -411,21 +411,30 @@ def GemvQ6KBatchToBuffer(out, x, batch, m, stream=None):
 
 class MLXProgram:
     """A list of batch-1 MLX products run as one cooperative launch (goph_mlx_program_*).
-    ops: [(x Buffer, [weights], [out Buffers])]; product k+1 may read what product k wrote."""
+    ops: [(x Buffer, [weights], [out Buffers])]; product k+1 may read what product k wrote.
+    pre: optional list, one entry per product: None, or a dict with "op" (1: residual add + RMSNorm,
+    2: SiLU(x) * b) and the operands "b", "w", "hidden" (Buffers or None) and "eps"."""
 
-    def __init__(self, ops):
+    def __init__(self, ops, pre=None):
         ws, outs, xs, counts = [], [], [], []
         for x, hs, os_ in ops:
             if len(hs) != len(os_) or not hs:
                 raise GophError(1, "product needs as many outputs as weights")
             counts.append(len(hs)); xs.append(x.Ptr)
             ws += [_mlx_handle(h) for h in hs]; outs += [o.Ptr for o in os_]
-        self._keep = ops
+        self._keep = (ops, pre)
         self.n = len(ops)
         h = C.c_void_p(0)
-        _check(lib().goph_mlx_program_create(_device, len(ops), (C.c_int * len(counts))(*counts),
-                                             (C.c_void_p * len(ws))(*ws),
-                                             (C.c_void_p * len(outs))(*outs), (C.c_void_p * len(xs))(*xs), C.byref(h)))
+        n = len(ops)
+        if pre is not None and len(pre) != n:
+            raise GophError(1, "one pre entry per product")
+        ptr = lambda b: b.Ptr if b is not None else None
+        pick = lambda key: (C.c_void_p * n)(*[ptr(p.get(key)) if p else None for p in pre]) if pre is not None and n else None
+        pre_ops = (C.c_int * n)(*[int(p["op"]) if p else 0 for p in pre]) if pre is not None and n else None
+        pre_eps = (C.c_float * n)(*[float(p.get("eps", 0.0)) if p else 0.0 for p in pre]) if pre is not None and n else None
+        _check(lib().goph_mlx_program_create_pre(_device, n, (C.c_int * len(counts))(*counts), (C.c_void_p * len(ws))(*ws),
+                                                 (C.c_void_p * len(outs))(*outs), (C.c_void_p * len(xs))(*xs), pre_ops,
+                                                 pick("b"), pick("w"), pick("hidden"), pre_eps, C.byref(h)))
         self._h = h
 
     def Run(self, stream=None):

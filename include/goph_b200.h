@@ -207,6 +207,15 @@ typedef struct goph_mlx_program goph_mlx_program;
  * format per list.  The buffers are borrowed: they must outlive the list. */
 int goph_mlx_program_create(int device, int n_ops, const int* weights_per_op, const goph_mlx_weight* const* ws,
                             float* const* outs_dev, const float* const* xs_dev, goph_mlx_program** out);
+/* The same with an operation applied to a product's x while it is staged, as goph_mlx_gemv_pre does for
+ * a single launch (arrays of n_ops entries, or NULL for none): pre_ops[o] = 0 none; 1 v = x (+ pre_b[o]),
+ * stored to pre_hidden[o] when not NULL, x' = RMSNorm(v) * pre_w[o] with pre_eps[o]; 2 x' = SiLU(x) * pre_b[o].
+ * A product's outputs and hidden vector must not overlap what it reads.  With these a decoder layer's
+ * o -> (add, norm) gate|up -> (SiLU, mul) down -> (add, norm) next q|k|v is one launch. */
+int goph_mlx_program_create_pre(int device, int n_ops, const int* weights_per_op, const goph_mlx_weight* const* ws,
+                                float* const* outs_dev, const float* const* xs_dev, const int* pre_ops,
+                                const float* const* pre_b, const float* const* pre_w, float* const* pre_hidden,
+                                const float* pre_eps, goph_mlx_program** out);
 /* Runs the list on `stream` (capturable into a CUDA graph).  Runs of one list must not overlap. */
 int goph_mlx_program_run(goph_mlx_program* p, void* stream);
 /* 0, or 200 + k when a CTA gave up waiting (about a second) at the barrier in front of product k;

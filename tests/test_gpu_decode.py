@@ -216,3 +216,24 @@ def test_greedy_tokens_qwen3_0_6b(gpu, pkg):
     want, got, margins, _ = run_gate(gpu, pkg, cfg, "qwen3-0.6b", 128, 64)
     print("top-2 logit margins of the 64 chosen tokens: min %.3e median %.3e" % (min(margins), float(np.median(margins))))
     assert got == want, ([i for i, (a, b) in enumerate(zip(got, want)) if a != b][:3], min(margins))
+
+
+def test_product_lists_change_nothing(gpu, pkg):
+    """The step with everything between two attentions as one cooperative launch (two launches per
+    layer) against the same step as five launches per layer: same tokens, same logits bit for bit."""
+    cfg = od.DecodeConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, inter=1024, vocab=4096, max_seq=40)
+    layers_gpu, _, lm, final_norm = build_model(pkg, cfg, "lists")
+    table = od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta)
+    with_lists = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table)
+    without = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table, lists=False)
+    assert with_lists.lists is not None and len(with_lists.lists) == cfg.layers + 1 and without.lists is None
+    prompt = [5, 17, 3, 99, 1024, 7]
+    la, lb = [], []
+    a = with_lists.generate(prompt, 12, use_graph=True, logits_at=la)
+    b = without.generate(prompt, 12, use_graph=True, logits_at=lb)
+    assert a == b
+    for x, y in zip(la, lb):
+        assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+    assert with_lists.launches_per_step < without.launches_per_step
+    assert all(p.Status() == 0 for p in with_lists.lists)
+    assert with_lists.generate(prompt, 12, use_graph=False) == a

@@ -163,3 +163,40 @@ def test_malformed_lists_raise(gpu, pkg):
     ops[0][1][0].Free()
     with pytest.raises(gpu.GophError):
         gpu.MLXProgram(ops)
+
+
+def test_list_with_operations_in_front_equals_single_launches(gpu, pkg):
+    """o -> (add, norm) gate|up -> (SiLU, mul) down -> (add, norm) q|k|v as one list against
+    goph_mlx_gemv / goph_mlx_gemv_pre launches, bit for bit (hidden vectors included)."""
+    syn = pkg.synth
+    hid, inter, qd = 512, 1024, 768
+    g = syn.rng("list-pre")
+    f = lambda n: gpu.from_numpy(g.standard_normal(n, dtype=np.float32))
+    mk = lambda key, o, i: gpu.UploadMLXWeight(*syn.mlx_weight(("list-pre", key), o, i, 64), i, o, 64, True)
+    w_o, w_gu, w_down, w_qkv = mk("o", hid, qd), mk("gu", 2 * inter, hid), mk("down", hid, inter), mk("qkv", qd, hid)
+    attn, resid, n1, n2 = f(qd), f(hid), f(hid), f(hid)
+
+    def buffers():
+        gu = gpu.Malloc(2 * inter)
+        return dict(proj=gpu.Malloc(hid), gu=gu, gate=gpu.wrap(gu.Ptr, 4 * inter), up=gpu.wrap(gu.Ptr + 4 * inter, 4 * inter),
+                    proj2=gpu.Malloc(hid), h1=gpu.Malloc(hid), h2=gpu.Malloc(hid), qkv=gpu.Malloc(qd))
+
+    A, B = buffers(), buffers()
+    gpu.GemvMLX(A["proj"], attn, w_o)
+    gpu.GemvMLXPre(A["gu"], w_gu, 1, resid, A["proj"], n1, A["h1"], 1e-6)
+    gpu.GemvMLXPre(A["proj2"], w_down, 2, A["gate"], A["up"], None, None)
+    gpu.GemvMLXPre(A["qkv"], w_qkv, 1, A["h1"], A["proj2"], n2, A["h2"], 1e-6)
+    prog = gpu.MLXProgram([(attn, [w_o], [B["proj"]]), (resid, [w_gu], [B["gu"]]), (B["gate"], [w_down], [B["proj2"]]),
+                           (B["h1"], [w_qkv], [B["qkv"]])],
+                          [None, dict(op=1, b=B["proj"], w=n1, hidden=B["h1"], eps=1e-6), dict(op=2, b=B["up"]),
+                           dict(op=1, b=B["proj2"], w=n2, hidden=B["h2"], eps=1e-6)])
+    prog.Run(); prog.Run()
+    gpu.Sync()
+    for k in ("proj", "gu", "proj2", "h1", "h2", "qkv"):
+        assert np.array_equal(A[k].Download().view(np.uint32), B[k].Download().view(np.uint32)), k
+    assert prog.Status() == 0
+    prog.Free()
+    with pytest.raises(gpu.GophError):      # the hidden vector of operation 1 must not be one of its inputs
+        gpu.MLXProgram([(resid, [w_gu], [B["gu"]])], [dict(op=1, b=B["proj"], w=n1, hidden=resid, eps=1e-6)])
+    with pytest.raises(gpu.GophError):      # operation 2 needs its second operand
+        gpu.MLXProgram([(B["gate"], [w_down], [B["proj2"]])], [dict(op=2)])
