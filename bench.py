@@ -408,6 +408,8 @@ def run_ours(args):
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
     rt.init(local)
+    for o in args.opt:   # tuning: library options (goph_set_option) for this run
+        rt.SetOption(o.split("=")[0], int(o.split("=")[1]))
     wl = DecodeStepProjections(rt, syn, pkg.sharding, rank, world, gather=args.gather, shard_min_mb=args.shard_min_mb,
                                product_list=bool(args.list))
     stream = torch.cuda.Stream()
@@ -628,6 +630,7 @@ def main():
                     help="N>1: projections below this many MB of packed weights are computed whole on every rank")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: how the row shards' outputs reach every rank")
+    ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option (tuning)")
     ap.add_argument("--list", type=int, default=1,
                     help="1: the layer projections run as one product list (a cooperative launch); 0: one launch each")
     ap.add_argument("--no-cpu", action="store_true")

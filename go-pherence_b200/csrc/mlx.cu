@@ -141,10 +141,11 @@ __host__ __device__ inline size_t mlx_smem_bytes(int M, int iters) {
 
 template <int M, int MODE>
 __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2* xc) {
-  // thread t fills xs[j*256 + t] for j < M*iters (j = m*iters + it; slot = warp, lane = lane); four
-  // loads are in flight before the first store
+  // Consecutive threads read consecutive 16 bytes of x (a warp asks the L2 for four lines, not for a
+  // piece of thirty-two): float4 number t + 256*i of row m holds slot t%8 of unit (t + 256*i)/8 and goes
+  // to xs[((m*iters + unit/32)*8 + slot)*32 + unit%32].  Four loads are in flight before the first store.
   const int n = M * a.iters;
-  const int slot = (threadIdx.x >> 5) & 7, l = threadIdx.x & 31;
+  const int slot = threadIdx.x & 7, u0 = threadIdx.x >> 3;  // unit = it*32 + u0
   for (int j0 = 0; j0 < n; j0 += 4) {
     float4 v[4];
 #pragma unroll
@@ -152,7 +153,7 @@ __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2
       const int j = j0 + u;
       v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (j < n) {
-        const int m = M == 1 ? 0 : j / a.iters, it = j - m * a.iters, unit = it * 32 + l;
+        const int m = M == 1 ? 0 : j / a.iters, it = j - m * a.iters, unit = it * 32 + u0;
         if (m < a.batch && unit < a.units) {
           // plain (coherent) loads: inside a product list x may have been written earlier in this launch
           const float* p = a.x + (size_t)m * a.in_dim + (size_t)unit * 32 + slot * 4;
@@ -166,7 +167,7 @@ __device__ __forceinline__ void mlx_stage_x(const MlxArgs& a, float4* xs, float2
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u)
-      if (j0 + u < n) xs[(j0 + u) * 256 + threadIdx.x] = v[u];
+      if (j0 + u < n) xs[((j0 + u) * 8 + slot) * 32 + u0] = v[u];
   }
   __syncthreads();
   const int nsum = M * a.iters * 32;
@@ -190,8 +191,10 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
   __shared__ float red[kWarps];
   const int total = a.iters * 256;
   float ss = 0.f;
+  // consecutive threads take consecutive 16 bytes of the vectors (see mlx_stage_x); xs keeps its layout
+  auto at = [](int idx) { return (((idx >> 8) * 8 + (idx & 7)) * 32) + ((idx >> 3) & 31); };
   for (int idx = threadIdx.x; idx < total; idx += kThreads) {
-    const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
+    const int slot = idx & 7, unit = idx >> 3;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (unit < a.units) {
       const size_t e0 = (size_t)unit * 32 + slot * 4;
@@ -213,7 +216,7 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
         v.w = __fmul_rn(__fdiv_rn(v.w, __fadd_rn(1.f, expf(-v.w))), u.w);
       }
     }
-    xs[idx] = v;
+    xs[at(idx)] = v;
   }
   if (a.pre_op == 1) {
     ss = warp_sum(ss);
@@ -224,13 +227,13 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
     for (int w = 0; w < kWarps; ++w) t += red[w];
     const float inv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(t, (float)a.in_dim), a.pre_eps)));
     for (int idx = threadIdx.x; idx < total; idx += kThreads) {
-      const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
+      const int slot = idx & 7, unit = idx >> 3;
       if (unit < a.units) {
         const float4 w = *reinterpret_cast<const float4*>(a.pre_w + (size_t)unit * 32 + slot * 4);
-        float4 v = xs[idx];
+        float4 v = xs[at(idx)];
         v = make_float4(__fmul_rn(__fmul_rn(v.x, inv), w.x), __fmul_rn(__fmul_rn(v.y, inv), w.y),
                         __fmul_rn(__fmul_rn(v.z, inv), w.z), __fmul_rn(__fmul_rn(v.w, inv), w.w));
-        xs[idx] = v;
+        xs[at(idx)] = v;
       }
     }
   }
@@ -485,19 +488,19 @@ __device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* s
   if (a.pre_op != 0) {
     // residual add + RMSNorm, or SiLU(x) * b, applied while x is staged (as in goph_mlx_gemv_pre)
     mlx_stage_x_pre<MODE>(a, xs, reinterpret_cast<float2*>(smem_raw + (size_t)iters * 8 * 32 * 16), cta);
-  } else {  // x -> shared memory, [iteration][slot = warp][lane]; plain (coherent) loads
-    const int slot = warp & 7;
+  } else {  // x -> shared memory, [iteration][slot][lane]; plain (coherent) loads
+    const int slot = threadIdx.x & 7, u0 = threadIdx.x >> 3;  // consecutive threads, consecutive 16 bytes (see mlx_stage_x)
     for (int j0 = 0; j0 < iters; j0 += 4) {
       float4 v[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int unit = (j0 + u) * 32 + lane;
+        const int unit = (j0 + u) * 32 + u0;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (j0 + u < iters && unit < units) v[u] = *reinterpret_cast<const float4*>(a.x + (size_t)unit * 32 + slot * 4);
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u)
-        if (j0 + u < iters) xs[(j0 + u) * 256 + threadIdx.x] = v[u];
+        if (j0 + u < iters) xs[((j0 + u) * 8 + slot) * 32 + u0] = v[u];
     }
     __syncthreads();
   }
@@ -590,7 +593,7 @@ mlx_gemv_kernel(const __grid_constant__ MlxArgs a) {
 // 200 + the product's index in *status and leaves the list, and so do the others.
 constexpr long long kBarrierTimeoutCycles = 2000000000ll;
 
-template <int MODE, bool SB_BF16>
+template <int R, int MODE, bool SB_BF16>
 __global__ void __launch_bounds__(kThreads, 2)
 mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter, unsigned* launches, int* status,
                    long long* probe) {
@@ -612,7 +615,7 @@ mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter,
   const bool probing = probe && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && threadIdx.x == 0;
   for (int op = 0; op < nops; ++op) {
     if (probing) tp[0] = clock64();
-    mlx_list_body<MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, [&] {
+    auto wait = [&] {
       if (probing) tp[1] = clock64();
       // the next product's arguments, fetched by the upper half of the CTA while thread 0 polls;
       // they become visible to all with the barriers inside the staging of x
@@ -637,7 +640,11 @@ mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter,
         if (probing) tp[2] = clock64();
       }
       __syncthreads();
-    }, probing ? &tp[3] : nullptr);
+    };
+    // R rows per warp task: one row at a time with the nibbles unpacked ahead (R == 1), or R rows
+    // sharing every load of x (the streaming kernel's loop)
+    if constexpr (R == 1) mlx_list_body<MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait, probing ? &tp[3] : nullptr);
+    else mlx_gemv_body<R, 1, MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait, probing ? &tp[3] : nullptr);
     if (probing) tp[4] = clock64();
     __syncthreads();  // every warp is done with x in shared memory and has stored its rows
     if (s_abort) return;
@@ -835,11 +842,19 @@ static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, i
   int M = batch <= 1 ? 1 : batch <= 2 ? 2 : batch <= 4 ? 4 : 8;
   long total_rows = 0;
   for (int i = 0; i < n; ++i) total_rows += ws[i]->out_dim;
-  // Rows per warp: as many as keep every SM's 16 resident warps busy for two rounds.
+  // Rows per warp.  Batches: as many as keep every SM's 16 resident warps busy for two rounds.
+  // Batch 1 is latency-bound (every CTA stages the whole x, and a launch costs by the CTA): two rows per
+  // warp from 512 rows on.  Measured on the Qwen3-0.6B decode step (145 dependent launches per token,
+  // prompt positions): 1250 tok/s with one row per warp, 1400-1440 with two, 1330 with four, 1190 with
+  // four for the wide and two for the deep projections.
   int R = options().mlx_rows;
   if (R != 1 && R != 2 && R != 4) {
-    long want = (long)st.sm_count * 2 * kWarps * 2;
-    R = total_rows / 4 >= want ? 4 : total_rows / 2 >= want ? 2 : 1;
+    if (M == 1) {
+      R = total_rows >= 512 ? 2 : 1;
+    } else {
+      long want = (long)st.sm_count * 2 * kWarps * 2;
+      R = total_rows / 4 >= want ? 4 : total_rows / 2 >= want ? 2 : 1;
+    }
   }
   if (M == 8 && R == 4) R = 2;
   int tasks = 0;
@@ -861,6 +876,7 @@ static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, i
   GOPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, kThreads, smem));
   if (per_sm < 1) return fail(GOPH_E_UNSUPPORTED, "MLX GEMV kernel does not fit (smem %zu)", smem);
   int grid = (tasks + kWarps - 1) / kWarps;
+  if (options().mlx_ctas_per_sm > 0 && per_sm > options().mlx_ctas_per_sm) per_sm = options().mlx_ctas_per_sm;
   int cap = st.sm_count * per_sm;
   if (grid > cap) grid = cap;
   cudaLaunchAttribute attr;
@@ -946,10 +962,16 @@ static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const*
 
 typedef void (*MlxProgramKernel)(const MlxArgs*, int, unsigned*, unsigned*, int*, long long*);
 
-static MlxProgramKernel pick_program_kernel(int mode, bool bf16) {
-  if (mode == UNPACK_PAIR) return bf16 ? mlx_program_kernel<UNPACK_PAIR, true> : mlx_program_kernel<UNPACK_PAIR, false>;
-  if (mode == UNPACK_CVT) return bf16 ? mlx_program_kernel<UNPACK_CVT, true> : mlx_program_kernel<UNPACK_CVT, false>;
-  return bf16 ? mlx_program_kernel<UNPACK_EXACT, true> : mlx_program_kernel<UNPACK_EXACT, false>;
+template <int R>
+static MlxProgramKernel pick_program_kernel_r(int mode, bool bf16) {
+  if (mode == UNPACK_PAIR) return bf16 ? mlx_program_kernel<R, UNPACK_PAIR, true> : mlx_program_kernel<R, UNPACK_PAIR, false>;
+  if (mode == UNPACK_CVT) return bf16 ? mlx_program_kernel<R, UNPACK_CVT, true> : mlx_program_kernel<R, UNPACK_CVT, false>;
+  return bf16 ? mlx_program_kernel<R, UNPACK_EXACT, true> : mlx_program_kernel<R, UNPACK_EXACT, false>;
+}
+
+static MlxProgramKernel pick_program_kernel(int rows, int mode, bool bf16) {
+  return rows == 1 ? pick_program_kernel_r<1>(mode, bf16) : rows == 2 ? pick_program_kernel_r<2>(mode, bf16)
+                                                                      : pick_program_kernel_r<4>(mode, bf16);
 }
 
 }  // namespace goph
@@ -995,6 +1017,9 @@ GOPH_API int goph_mlx_program_create_pre(int device, int n_ops, const int* weigh
     return fail(GOPH_E_INVALID, "goph_mlx_program_create: empty list or nil array");
   std::vector<MlxArgs> ops((size_t)n_ops);
   int k = 0, max_iters = 1;
+  // rows per warp task: one (the list's own loop with the nibbles unpacked ahead; measured best), or two
+  // or four through option "mlx_rows" (the streaming kernel's loop: rows share every load of x)
+  const int R = options().mlx_rows == 2 || options().mlx_rows == 4 ? options().mlx_rows : 1;
   const goph_mlx_weight* first = ws[0];
   for (int o = 0; o < n_ops; ++o) {
     const int n = weights_per_op[o];
@@ -1019,7 +1044,7 @@ GOPH_API int goph_mlx_program_create_pre(int device, int n_ops, const int* weigh
       a.seg[i].out = outs_dev[k + i];
       a.seg[i].rows = w->out_dim;
       a.seg[i].task0 = a.tasks;
-      a.tasks += w->out_dim;  // one row per warp task
+      a.tasks += (w->out_dim + R - 1) / R;
     }
     if (!xs_dev[o] || (uintptr_t)xs_dev[o] % 16) return fail(GOPH_E_INVALID, "product %d: x is nil or not 16-byte aligned", o);
     // the barrier orders products against each other, not a product against itself: what a product
@@ -1067,12 +1092,13 @@ GOPH_API int goph_mlx_program_create_pre(int device, int n_ops, const int* weigh
   if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "product list: in_dim too large for shared memory");
   if (int rc = use_device(device)) return rc;
   DeviceState& st = device_state(device);
-  MlxProgramKernel kern = pick_program_kernel(options().mlx_unpack, first->sb_bf16 != 0);
+  MlxProgramKernel kern = pick_program_kernel(R, options().mlx_unpack, first->sb_bf16 != 0);
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int per_sm = 0;
   GOPH_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem));
   if (per_sm < 1) return fail(GOPH_E_UNSUPPORTED, "product list kernel does not fit (smem %zu)", smem);
   if (per_sm > 2) per_sm = 2;  // 16 warps per SM keep the loads in flight; more CTAs only lengthen the barrier
+  if (options().mlx_ctas_per_sm > 0 && per_sm > options().mlx_ctas_per_sm) per_sm = options().mlx_ctas_per_sm;
   auto* p = new goph_mlx_program();
   p->magic = kMagicProgram;
   p->device = device;

@@ -74,6 +74,9 @@ GOPH_API int goph_set_option(const char* name, int value) {
     o.pdl = value != 0;
   } else if (!strcmp(name, "mlx_fuse")) {
     o.mlx_fuse = value ? 1 : 0;
+  } else if (!strcmp(name, "mlx_ctas_per_sm")) {
+    if (value < 0 || value > 8) return fail(GOPH_E_INVALID, "mlx_ctas_per_sm=%d not in 0..8", value);
+    o.mlx_ctas_per_sm = value;
   } else if (!strcmp(name, "gguf_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "gguf_layout=%d not in 0..2", value);
     o.gguf_layout = value;

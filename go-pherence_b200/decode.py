@@ -18,7 +18,7 @@ import numpy as np
 
 
 class MLXDecoder:
-    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64, fuse=True, lists=True):
+    def __init__(self, rt, cfg, layers, lm_head, final_norm, rope_table, group_size=64, fuse=True, lists=False):
         """cfg: an object with hidden, layers, heads, kv_heads, head_dim, inter, vocab, eps, qk_norm, max_seq.
         layers[l]: dict with "q","k","v","o","gate","up","down" -> (words, scales, biases) in the MLX
         layout, and "input_norm","post_norm" (+ "q_norm","k_norm") f32 vectors.  lm_head: the tied

@@ -224,8 +224,8 @@ def test_product_lists_change_nothing(gpu, pkg):
     cfg = od.DecodeConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, inter=1024, vocab=4096, max_seq=40)
     layers_gpu, _, lm, final_norm = build_model(pkg, cfg, "lists")
     table = od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta)
-    with_lists = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table)
-    without = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table, lists=False)
+    with_lists = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table, lists=True)
+    without = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, table)
     assert with_lists.lists is not None and len(with_lists.lists) == cfg.layers + 1 and without.lists is None
     prompt = [5, 17, 3, 99, 1024, 7]
     la, lb = [], []
