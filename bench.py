@@ -9,7 +9,7 @@ step streams them from HBM again).  Data is synthetic and seeded.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints ONE JSON line (see DESIGN.md for the fields).  `value` is GB/s of algorithmic bytes
+Prints ONE JSON line.  `value` is GB/s of algorithmic bytes
 with inputs resident in HBM; `e2e` is the same step with the activations copied from pinned
 host memory and the logits copied back inside the timed region.
 """

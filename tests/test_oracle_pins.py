@@ -291,7 +291,9 @@ def test_q4k_dequant_and_gemv_formula_blocks():
         assert abs(float(got[r]) - float(want)) <= 1e-3
 
 
-REF_TESTDATA = "/root/reference/loader/gguf/testdata"
+# the reference checkout, when one sits beside this repository (or where GOPH_REFERENCE_DIR points)
+REF_TESTDATA = os.path.join(os.environ.get("GOPH_REFERENCE_DIR") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"), "loader", "gguf", "testdata")
 
 
 @pytest.mark.skipif(not os.path.exists(REF_TESTDATA), reason="reference checkout not present")
