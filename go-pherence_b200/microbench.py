@@ -276,6 +276,42 @@ def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
 
 
+def run_decode_tokens(steps=3, position=150, opts=()):
+    """A few greedy steps of the Qwen3-0.6B-shaped MLX 4-bit decoder at a given position, as plain
+    launches (for a profiler's launch list; the timing figure is bench.py's `decode`)."""
+    import types
+    import numpy as np
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(0)
+    for k, v in opts:
+        rt.SetOption(k, v)
+    F = np.float32
+    cfg = types.SimpleNamespace(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
+                                eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
+    shapes = {"q": (2048, 1024), "k": (1024, 1024), "v": (1024, 1024), "o": (1024, 2048), "gate": (3072, 1024),
+              "up": (3072, 1024), "down": (1024, 3072)}
+    base = [{n: syn.mlx_weight(("dec", n, k), o, i, 64) for n, (o, i) in shapes.items()} for k in range(4)]
+    layers = []
+    for l in range(cfg.layers):
+        d = dict(base[l % 4])
+        for n, sz in (("input_norm", 1024), ("post_norm", 1024), ("q_norm", 128), ("k_norm", 128)):
+            d[n] = np.ones(sz, dtype=F)
+        layers.append(d)
+    lm = syn.mlx_weight(("dec", "lm"), cfg.vocab, cfg.hidden, 64)
+    table = np.zeros((cfg.max_seq, cfg.head_dim // 2, 2), dtype=F)
+    table[:, :, 0] = 1
+    dec = pkg.decode.MLXDecoder(rt, cfg, layers, lm, np.ones(1024, dtype=F), table)
+    ints = np.full(2 + 2 * cfg.max_seq, -1, dtype=np.int32)
+    ints[0], ints[1] = 5, position   # current token and position: the cache rows before it are zeros
+    dec.ints.UploadBytes(ints.view(np.uint8))
+    for _ in range(steps):
+        dec.step(None)
+    rt.Sync()
+    return {"workload": "qwen3-0.6b mlx4 decode, %d eager steps from position %d" % (steps, position),
+            "launches_per_token": dec.launches_per_step}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1)
@@ -289,6 +325,7 @@ def main():
     ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
     ap.add_argument("--chain", action="store_true", help="each launch reads the previous launch's output (out == in)")
     ap.add_argument("--list", action="store_true", help="--layer-chain as one product list (one cooperative launch)")
+    ap.add_argument("--decode-tokens", type=int, default=0, help="run this many eager decoder steps (for a launch list)")
     ap.add_argument("--hidden", type=int, default=4096)
     ap.add_argument("--qdim", type=int, default=0)
     ap.add_argument("--kv", type=int, default=1024)
@@ -296,6 +333,9 @@ def main():
     ap.add_argument("--layers", type=int, default=8)
     args = ap.parse_args()
     opts = [(o.split("=")[0], int(o.split("=")[1])) for o in args.opt]
+    if args.decode_tokens:
+        print(json.dumps(run_decode_tokens(args.decode_tokens, opts=opts)))
+        return
     if args.layer_chain:
         print(json.dumps(run_layer_chain(args.format, args.hidden, args.ffn, args.kv, args.layers, opts=opts, qdim=args.qdim,
                                          as_list=args.list)))
