@@ -132,8 +132,8 @@ qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, c
   }
 }
 
-// Grid (query heads, position splits): a CTA of kAttnWarps warps takes every split-th block of
-// kAttnWarps*4 positions of its head.  Scores: a warp takes four positions at a time so their K and V
+// Grid (query heads, position splits): a CTA of W warps takes every split-th block of
+// W*4 positions of its head.  Scores: a warp takes four positions at a time so their K and V
 // rows are all in flight together (the V rows are requested before the softmax); the CTA's softmax
 // numerators use its own maximum; a warp accumulates e_t * v_t for all of head_dim (lane d, d+32, ..).
 // One split (sequences up to a few hundred positions): the CTA writes the head's output.  Several
@@ -143,7 +143,7 @@ qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, c
 // its head's q for itself; the warp that owns the current position norms and rotates the new k,
 // uses it and the new v from the projection output instead of the cache, and (for the first head
 // of a KV group) writes both into the cache rows.  No CTA reads the cache row being written.
-constexpr int kAttnWarps = 32, kAttnMaxSplits = 16, kAttnMaxHeads = 256;
+constexpr int kAttnMaxSplits = 16, kAttnMaxHeads = 256;
 
 template <int EPL>
 __device__ __forceinline__ void norm_rope_head(float (&x)[EPL], const float* __restrict__ w, const float* __restrict__ trow,
@@ -184,12 +184,12 @@ struct AttnArgs {
   unsigned int* counters;
 };
 
-template <int EPL, bool FUSED>
-__global__ void __launch_bounds__(kAttnWarps * 32)
+template <int EPL, bool FUSED, int W>
+__global__ void __launch_bounds__(W * 32)
 attn_decode_kernel(const __grid_constant__ AttnArgs a) {
   extern __shared__ float scores[];
-  __shared__ float sh[kAttnWarps];
-  __shared__ float part[kAttnWarps][EPL * 32];
+  __shared__ float sh[W];
+  __shared__ float part[W][EPL * 32];
   __shared__ int s_last;
   pdl_begin();
   const int pos = *a.pos_dev, seq = pos + 1;
@@ -200,7 +200,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* kbase = a.kcache + (size_t)kvh * head_dim;
   const float* vbase = a.vcache + (size_t)kvh * head_dim;
-  constexpr int B = 4 * kAttnWarps;
+  constexpr int B = 4 * W;
   const int nblocks = (seq + B - 1) / B;
   const int my_blocks = nblocks > split ? (nblocks - split + splits - 1) / splits : 0;
   auto pos_of = [&](int i) { return ((i / B) * splits + split) * B + (i % B); };
@@ -220,7 +220,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
     int tt[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int t = pos_of(blk * B + warp + j * kAttnWarps);
+      const int t = pos_of(blk * B + warp + j * W);
       tt[j] = t;
       const bool cur = FUSED && t == pos;
 #pragma unroll
@@ -255,7 +255,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
     __syncthreads();
     mx = sh[0];
 #pragma unroll
-    for (int i = 1; i < kAttnWarps; ++i) mx = fmaxf(mx, sh[i]);
+    for (int i = 1; i < W; ++i) mx = fmaxf(mx, sh[i]);
     const float new_max = fmaxf(run_max, mx);
     // single-precision exp (2 ulp) where the reference rounds an f64 exp to f32: the FP64 pipe of
     // this part is too slow for a per-position operation
@@ -275,7 +275,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
     __syncthreads();
     float bsum = 0.f;
 #pragma unroll
-    for (int i = 0; i < kAttnWarps; ++i) bsum += sh[i];
+    for (int i = 0; i < W; ++i) bsum += sh[i];
     run_sum = fmaf(run_sum, rescale, bsum);
     run_max = new_max;
     __syncthreads();
@@ -288,7 +288,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
       float r = 0.f;
 #pragma unroll
-      for (int w = 0; w < kAttnWarps; ++w) r += part[w][d];
+      for (int w = 0; w < W; ++w) r += part[w][d];
       a.out[(size_t)head * head_dim + d] = __fmul_rn(r, inv);
     }
     return;
@@ -299,7 +299,7 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float r = 0.f;
 #pragma unroll
-    for (int w = 0; w < kAttnWarps; ++w) r += part[w][d];
+    for (int w = 0; w < W; ++w) r += part[w][d];
     mine[2 + d] = r;
   }
   if (threadIdx.x == 0) {
@@ -509,18 +509,25 @@ static int attn_launch(int device, AttnArgs& a, int max_seq, bool fused, void* s
   }
   a.scratch = scratch[device];
   a.counters = counters[device];
-  // one CTA per head takes two blocks of 128 positions without help; longer caches are split
-  int splits = (max_seq + 8 * kAttnWarps - 1) / (8 * kAttnWarps);
+  // Short caches (the latency-bound case): CTAs of 4 warps, one block of 16 positions each, so that they
+  // fit beside the projection kernels' CTAs and start under programmatic dependent launch (measured on
+  // the Qwen3-0.6B step at positions 128-191: 1318 tok/s against 1249 with 32-warp CTAs).  Long caches:
+  // CTAs of 32 warps, two blocks of 128 positions each without help, more through splits.
+  const bool small = max_seq <= 16 * kAttnMaxSplits;
+  const int per_cta = small ? 16 : 256;
+  int splits = (max_seq + per_cta - 1) / per_cta;
   if (splits > kAttnMaxSplits) splits = kAttnMaxSplits;
   if (splits < 1) splits = 1;
   const dim3 grid(a.heads, splits);
-  const int threads = kAttnWarps * 32;
-  if (a.head_dim == 64) return fused ? op_launch(attn_decode_kernel<2, true>, grid, threads, 0, stream, a)
-                                     : op_launch(attn_decode_kernel<2, false>, grid, threads, 0, stream, a);
-  if (a.head_dim == 128) return fused ? op_launch(attn_decode_kernel<4, true>, grid, threads, 0, stream, a)
-                                      : op_launch(attn_decode_kernel<4, false>, grid, threads, 0, stream, a);
-  return fused ? op_launch(attn_decode_kernel<8, true>, grid, threads, 0, stream, a)
-               : op_launch(attn_decode_kernel<8, false>, grid, threads, 0, stream, a);
+#define GOPH_ATTN(EPL)                                                                                          \
+  return small ? (fused ? op_launch(attn_decode_kernel<EPL, true, 4>, grid, 4 * 32, 0, stream, a)               \
+                        : op_launch(attn_decode_kernel<EPL, false, 4>, grid, 4 * 32, 0, stream, a))             \
+               : (fused ? op_launch(attn_decode_kernel<EPL, true, 32>, grid, 32 * 32, 0, stream, a)             \
+                        : op_launch(attn_decode_kernel<EPL, false, 32>, grid, 32 * 32, 0, stream, a))
+  if (a.head_dim == 64) GOPH_ATTN(2);
+  if (a.head_dim == 128) GOPH_ATTN(4);
+  GOPH_ATTN(8);
+#undef GOPH_ATTN
 }
 
 GOPH_API int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,

@@ -35,7 +35,9 @@ def test_add_rmsnorm(gpu, pkg):
 @pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,qk_norm,max_seq,steps", [
     (16, 8, 128, True, 96, 70), (4, 2, 64, False, 96, 70), (8, 8, 128, True, 96, 70), (4, 1, 256, True, 96, 40),
-    (8, 4, 128, True, 1024, 600),     # long cache: the positions are split over several CTAs per head
+    (8, 4, 128, True, 1024, 600),     # long cache: CTAs of 32 warps, the positions split over several per head
+    (8, 4, 128, True, 256, 250),      # the longest cache the 4-warp CTAs take (16 splits of 16 positions)
+    (4, 2, 64, True, 272, 270),       # the shortest the 32-warp CTAs take
 ])
 def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, qk_norm, max_seq, steps, fused):
     g = pkg.synth.rng("attn", heads, head_dim)
