@@ -179,7 +179,10 @@ class DecodeStepProjections:
                                               for _, hs, x, outs, _, _ in self.ops[:self.listed]])
             else:
                 self.listed = 0
-        self.launches_per_step = (len(self.ops) - self.listed + (1 if self.program else 0)
+        # launches of this library per step: the list, one per remaining product, one more for every
+        # product on the tensor-core path (its activation digits are a launch of their own), the exchanges
+        tensor_core = sum(1 for op in self.ops[self.listed:] if any(o * i >= (8 << 20) for o, i in op[4]))
+        self.launches_per_step = (len(self.ops) - self.listed + (1 if self.program else 0) + tensor_core
                                   + (self.sharded_ops if gather == "p2p" else 0))
         self.exchange = None
         if world > 1:
