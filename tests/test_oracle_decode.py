@@ -5,6 +5,9 @@ synthetic models whose weights come from a linear congruential generator
 (model/cpu_prefill_test.go:10-28, :33-100).  The models are rebuilt here by the same formula and the
 restatement must emit the same tokens; that pins RMSNorm, QK-norm, RoPE, grouped-query attention,
 SiLU and the residual order at the token level."""
+import json
+import os
+
 import numpy as np
 import pytest
 
@@ -50,14 +53,14 @@ def build_prefill_test_model(qk_norm):
     return cfg, od.DenseWeights(embed, norm, lm, L)
 
 
-@pytest.mark.parametrize("qk_norm,want", [
-    (False, [1, 5, 9, 2, 7, 3, 21, 29, 7, 17, 17, 17]),   # llama_plain
-    (True, [1, 5, 9, 2, 7, 3, 21, 29, 7, 17, 17, 17]),    # qwen3_qknorm
-])
-def test_decode_loop_golden_tokens(qk_norm, want):
+GOLDEN = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decode_golden_tokens.json")))
+
+
+@pytest.mark.parametrize("qk_norm,name", [(False, "llama_plain"), (True, "qwen3_qknorm")])
+def test_decode_loop_golden_tokens(qk_norm, name):
     cfg, w = build_prefill_test_model(qk_norm)
-    got = od.OracleDecoder(cfg, w).generate([1, 5, 9, 2, 7, 3], 6)
-    assert got == want
+    got = od.OracleDecoder(cfg, w).generate(GOLDEN["prompt"], 6)
+    assert got == GOLDEN[name]
 
 
 def test_rope_table_and_rotation():
