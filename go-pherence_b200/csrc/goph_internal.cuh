@@ -52,8 +52,6 @@ inline bool mul_ok(uint64_t a, uint64_t b, uint64_t* out) {
 struct Options {
   int pdl = 1;         // launch kernels with programmatic stream serialization
   int mlx_layout = 0;  // layout chosen at upload: 0 by size, 1 always row-major, 2 tiled whenever the shape allows
-  int mlx_dbg = 0;     // tuning aid: leaves out parts of the tensor-core kernel (results are then wrong)
-  int mlx_probe = 0;   // 1: CTA 0 of the tensor-core kernel records per-role wait cycles
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
   int mlx_fuse = 0;    // 1: narrow tensor-core launches make their activation digits themselves (one launch, slower today)
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)

@@ -256,8 +256,7 @@ __device__ __forceinline__ void mlx_stage_x_pre(const MlxArgs& a, float4* xs, fl
 // every thread after the first weight loads are issued and before x is read: it is where the
 // producer of x is waited for.
 template <int R, int M, int MODE, bool SB_BF16, class Wait>
-__device__ __forceinline__ void mlx_gemv_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait,
-                                              long long* staged_at = nullptr) {
+__device__ __forceinline__ void mlx_gemv_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait) {
   float4* xs = reinterpret_cast<float4*>(smem_raw);
   float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)M * a.iters * 8 * 32 * 16);
 
@@ -343,7 +342,6 @@ __device__ __forceinline__ void mlx_gemv_body(const MlxArgs& a, unsigned char* s
   } else {
     mlx_stage_x<M, MODE>(a, xs, xc);
   }
-  if (staged_at && threadIdx.x == 0) *staged_at = clock64();
   if (nsteps == 0) return;
 
   float acc[R][M];
@@ -423,8 +421,7 @@ __device__ __forceinline__ void mlx_gemv_body(const MlxArgs& a, unsigned char* s
 // awaited; x is staged with one pass and one barrier, each lane forming its unit's two constants
 // from the values it reads anyway.  Same arithmetic, in the same order, as mlx_gemv_body.
 template <int MODE, bool SB_BF16, class Wait>
-__device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait,
-                                              long long* staged_at) {
+__device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* smem_raw, int cta, int nctas, Wait wait) {
   float4* xs = reinterpret_cast<float4*>(smem_raw);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int task_stride = nctas * kWarps, iters = a.iters, units = a.units;
@@ -504,7 +501,6 @@ __device__ __forceinline__ void mlx_list_body(const MlxArgs& a, unsigned char* s
     }
     __syncthreads();
   }
-  if (staged_at && threadIdx.x == 0) *staged_at = clock64();
   if (nsteps == 0) return;
 
   float acc = 0.f;
@@ -595,8 +591,7 @@ constexpr long long kBarrierTimeoutCycles = 2000000000ll;
 
 template <int R, int MODE, bool SB_BF16>
 __global__ void __launch_bounds__(kThreads, 2)
-mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter, unsigned* launches, int* status,
-                   long long* probe) {
+mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter, unsigned* launches, int* status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ __align__(16) MlxArgs args[2];
   __shared__ unsigned s_base;
@@ -610,13 +605,8 @@ mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter,
     s_abort = 0;
   }
   __syncthreads();
-  // tuning aid (option mlx_probe): CTA 0 and the last CTA record clock64 at six points of products 8..11
-  long long tp[6] = {0, 0, 0, 0, 0, 0};
-  const bool probing = probe && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1) && threadIdx.x == 0;
   for (int op = 0; op < nops; ++op) {
-    if (probing) tp[0] = clock64();
     auto wait = [&] {
-      if (probing) tp[1] = clock64();
       // the next product's arguments, fetched by the upper half of the CTA while thread 0 polls;
       // they become visible to all with the barriers inside the staging of x
       if (op + 1 < nops && threadIdx.x >= 128) {
@@ -637,24 +627,17 @@ mlx_program_kernel(const MlxArgs* __restrict__ ops, int nops, unsigned* counter,
             break;
           }
         }
-        if (probing) tp[2] = clock64();
       }
       __syncthreads();
     };
     // R rows per warp task: one row at a time with the nibbles unpacked ahead (R == 1), or R rows
     // sharing every load of x (the streaming kernel's loop)
-    if constexpr (R == 1) mlx_list_body<MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait, probing ? &tp[3] : nullptr);
-    else mlx_gemv_body<R, 1, MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait, probing ? &tp[3] : nullptr);
-    if (probing) tp[4] = clock64();
+    if constexpr (R == 1) mlx_list_body<MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait);
+    else mlx_gemv_body<R, 1, MODE, SB_BF16>(args[op & 1], smem_raw, blockIdx.x, gridDim.x, wait);
     __syncthreads();  // every warp is done with x in shared memory and has stored its rows
     if (s_abort) return;
     if (op + 1 < nops && threadIdx.x == 0)
       asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(counter), "r"(1u) : "memory");
-    if (probing) {
-      tp[5] = clock64();
-      if (op >= 8 && op < 12)
-        for (int i = 0; i < 6; ++i) probe[((blockIdx.x ? 4 : 0) + (op - 8)) * 6 + i] = tp[i];
-    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0 && nops > 1) atomicAdd(launches, 1u);
 }
@@ -960,7 +943,7 @@ static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const*
   return GOPH_OK;
 }
 
-typedef void (*MlxProgramKernel)(const MlxArgs*, int, unsigned*, unsigned*, int*, long long*);
+typedef void (*MlxProgramKernel)(const MlxArgs*, int, unsigned*, unsigned*, int*);
 
 template <int R>
 static MlxProgramKernel pick_program_kernel_r(int mode, bool bf16) {
@@ -985,7 +968,7 @@ struct goph_mlx_program {
   size_t smem;
   goph::MlxProgramKernel kernel;
   goph::MlxArgs* ops;   // device
-  unsigned* words;      // device: [0] barrier counter, [1] launches so far, [2] status; from byte 64: 48 probe timestamps
+  unsigned* words;      // device: [0] barrier counter, [1] launches so far, [2] status
 };
 
 using namespace goph;
@@ -1135,18 +1118,8 @@ GOPH_API int goph_mlx_program_run(goph_mlx_program* p, void* stream) {
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  long long* probe = options().mlx_probe ? reinterpret_cast<long long*>(p->words + 16) : nullptr;
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, p->kernel, (const MlxArgs*)p->ops, p->nops, p->words, p->words + 1,
-                               reinterpret_cast<int*>(p->words + 2), probe));
-  return GOPH_OK;
-}
-
-/* Tuning aid: the 48 timestamps recorded under option "mlx_probe" (see mlx_program_kernel). */
-GOPH_API int goph_mlx_program_probe(goph_mlx_program* p, long long* out48) {
-  clear_error();
-  if (!p || p->magic != kMagicProgram || !out48) return fail(GOPH_E_INVALID, "goph_mlx_program_probe: bad arguments");
-  if (int rc = use_device(p->device)) return rc;
-  GOPH_CUDA(cudaMemcpy(out48, p->words + 16, 48 * 8, cudaMemcpyDeviceToHost));
+                               reinterpret_cast<int*>(p->words + 2)));
   return GOPH_OK;
 }
 
@@ -1305,14 +1278,6 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   if (int rc = use_device(device)) return rc;
   *out_status = mlx_mma_status(device);
   return GOPH_OK;
-}
-
-// Tuning aid: the cycle counters CTA 0 of the tensor-core kernel wrote under option mlx_probe.
-GOPH_API int goph_debug_probe(int device, long long* out32) {
-  clear_error();
-  if (!out32) return fail(GOPH_E_INVALID, "goph_debug_probe: nil result pointer");
-  if (int rc = use_device(device)) return rc;
-  return mlx_mma_probe(device, out32) == 0 ? GOPH_OK : fail(GOPH_E_CUDA, "goph_debug_probe: copy failed");
 }
 
 GOPH_API uint64_t goph_mlx_resident_bytes(const goph_mlx_weight* w) {

@@ -36,10 +36,15 @@
 // the CTA winds down (copies drained, TMEM returned) instead of spinning.
 #include <string.h>
 
+#include <mutex>
+
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
+#include "tc_common.cuh"
 
 namespace goph {
+
+using namespace tc;
 
 namespace {
 
@@ -68,7 +73,6 @@ struct Fmt {
 };
 constexpr int kStageWBytes = Fmt<FMT_MLX4>::kStageWBytes;
 constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
-constexpr long long kTimeoutCycles = 4000000000LL;
 
 constexpr int kConvWarps = 8, kEpiWarps = 8;  // two epilogue warps per TMEM lane quarter: each takes half of a stage's accumulator blocks
 constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
@@ -76,106 +80,6 @@ constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
 constexpr int kMmaWarps = 2;  // two issuing threads take alternate stages so one's waits hide behind the other's MMAs
 constexpr int kThreads = (kWarpMMA + kMmaWarps) * 32;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait: false after ~2 s, with `code` left in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kTimeoutCycles) {
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-// mbar_wait that also adds the cycles spent waiting to acc when probing is on.
-__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, int* status, int code, bool probing,
-                                            long long& acc) {
-  if (!probing) return mbar_wait(bar, parity, status, code);
-  long long t0 = clock64();
-  bool r = mbar_wait(bar, parity, status, code);
-  acc += clock64() - t0;
-  return r;
-}
-
-// Programmatic dependent launch: let the next kernel in the stream start its prologue now /
-// wait until every kernel this one depends on has completed and its writes are visible.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
-               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-// Waits for the loads above; the registers are listed so no use of them can move before it.
-__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-               :
-               : "memory");
-}
-
-// D[tmem] (+)= A[tmem] * B[smem descriptor], 8-bit integers, int32 accumulate; one thread issues.
-__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-// The same with A read from shared memory through a descriptor.
-__device__ __forceinline__ void umma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                           uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 
 }  // namespace
 
@@ -188,8 +92,6 @@ struct MmaArgs {
   int* status;             // device word: 0 ok, otherwise the first wait that gave up
   float* scratch;          // split-K partial sums [item][batch][128]
   unsigned int* counters;  // per-tile arrival counters, zero between launches
-  long long* probe;        // optional [4 roles][8] cycle counters of CTA 0 (tuning aid), or nullptr
-  int dbg;                 // tuning aid: bit0 skip tcgen05.st, bit1 skip tcgen05.mma, bit2 skip tcgen05.ld
   int out_dim, in_dim;
   int batch;               // activation rows of this launch (<= MB of the instantiation)
   int ntiles;              // ceil(out_dim / 128)
@@ -392,12 +294,13 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
       // converters (conversion formats), epilogue (scale data), MMA commit (B tile, A read from the stage)
-      mbar_init(empty0 + 8 * s, (F::kConv ? kConvThreads / 2 : 0) + kEpiThreads + 1);
+      // (one arrival per warp: a warp's lanes meet first and one of them arrives for all)
+      mbar_init(empty0 + 8 * s, (F::kConv ? kConvWarps / 2 : 0) + kEpiWarps + 1);
     }
     for (int b = 0; b < NB; ++b) {
-      mbar_init(aready0 + 8 * b, kConvThreads / 2);
+      mbar_init(aready0 + 8 * b, kConvWarps / 2);
       mbar_init(mdone0 + 8 * b, 1);
-      mbar_init(dfree0 + 8 * b, kEpiThreads);
+      mbar_init(dfree0 + 8 * b, kEpiWarps);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -435,15 +338,11 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   if (warp == kWarpTMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      const bool pr = a.probe && blockIdx.x == 0;
-      long long w0 = 0, tstart = clock64();
-      int nst = 0;
       // The weights do not depend on the kernel in front: fill the ring with them first, then
       // wait for the activation digits and add the B tiles of those stages.
       int i = 0;
       if (FUSED) {
         for (; i < S && sw.live(a); ++i) sw.next(a);  // filled before the activations were prepared
-        nst = i;
       } else {
         StageWalk sw0 = sw;
         for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
@@ -455,30 +354,22 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         for (int j = 0; j < i; ++j, sw.next(a))
           bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes,
                        kBTileBytes, full0 + 8 * j);
-        nst = i;
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
         int slot = i % S, round = i / S;
-        ok = mbar_wait_t(empty0 + 8 * slot, (round - 1) & 1, a.status, 1, pr, w0);
+        ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 1);
         if (!ok) break;
-        ++nst;
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
         mbar_expect_tx(full0 + 8 * slot, kStage);
         const unsigned char* src = a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes;
         bulk_load_1d(dst, src, kStageBytes, full0 + 8 * slot);
         if (!FUSED) bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes, kBTileBytes, full0 + 8 * slot);
       }
-      if (pr) {
-        a.probe[0] = clock64() - tstart;
-        a.probe[1] = w0;
-        a.probe[2] = nst;
-      }
     }
   } else if (warp >= kWarpMMA) {
     // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
       const int mi = warp - kWarpMMA;
-      const int istride = (a.dbg & 512) ? 1 : kMmaWarps;  // tuning aid: one issuer takes every stage
       if (mi == 1 && sw.live(a)) sw.next(a);
       // instruction descriptor: D s32, A u8 (nibbles) or s8 (Q8_0 bytes), B s8, both K-major, N, M=128
       const uint32_t idesc = (2u << 4) | ((FMT == FMT_Q80 ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
@@ -486,47 +377,37 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       const uint64_t adesc_hi = ((uint64_t)(2048u >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
       constexpr uint32_t kLBO = (N / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
       const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
-      const bool pr = a.probe && blockIdx.x == 0 && mi == 0;
-      long long w0 = 0, w1 = 0, w2 = 0, tstart = clock64();
-      for (int i = mi; sw.live(a) && ok && !(istride == 1 && mi == 1); i += istride) {
+      for (int i = mi; sw.live(a) && ok; i += kMmaWarps) {
         int b = i % NB, slot = i % S;
         // The two issuers take alternate stages, so this one has not itself seen stage i-1 land.
         // A parity wait can only tell the barrier's current phase from the one before it: if this
         // issuer ran ahead and asked for round R of a slot whose round R-1 is still in flight, the
         // wait would pass at once.  Waiting for stage i-1 first makes every earlier stage (in
         // particular stage i-S, the slot's previous round) complete before stage i is asked for.
-        if (i >= 1) ok = mbar_wait_t(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 9, pr, w2);
-        if (ok && !(a.dbg & 32)) ok = mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 8, pr, w2);
-        if (ok && F::kConv) ok = mbar_wait_t(aready0 + 8 * b, (i / NB) & 1, a.status, 2, pr, w0);
-        if (ok && i >= NB) ok = mbar_wait_t(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5, pr, w1);
+        if (i >= 1) ok = mbar_wait(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 9);
+        if (ok) ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 8);
+        if (ok && F::kConv) ok = mbar_wait(aready0 + 8 * b, (i / NB) & 1, a.status, 2);
+        if (ok && i >= NB) ok = mbar_wait(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)sw.c * kBTileBytes) : smem_u32(ring + (size_t)slot * kStage + kStageBytes);
         const uint32_t dcol = tmemD0 + b * (kBlocks * N), acol = tmemA0 + b * kACols;
-        if (!(a.dbg & 2)) {
 #pragma unroll
-          for (int step = 0; step < 8; ++step) {  // K = 32 per step
-            const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
-            if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
-              umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
-            } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
-              umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
-            } else {
-              const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
-              umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
-            }
+        for (int step = 0; step < 8; ++step) {  // K = 32 per step
+          const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
+          if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
+            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
+          } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
+            umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
+          } else {
+            const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
+            umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
           }
         }
         umma_commit(mdone0 + 8 * b);
         umma_commit(empty0 + 8 * slot);
         sw.next(a);
-        if (istride == 2 && sw.live(a)) sw.next(a);
-      }
-      if (pr) {
-        a.probe[8] = clock64() - tstart;
-        a.probe[9] = w0;
-        a.probe[10] = w1;
-        a.probe[11] = w2;
+        if (sw.live(a)) sw.next(a);
       }
     }
   } else if (warp < kConvWarps && !F::kConv) {
@@ -539,50 +420,43 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     const int q4 = warp & 3, grp = warp >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-    const bool pr = a.probe && blockIdx.x == 0 && tid == 0;
-    long long w0 = 0, w1 = 0, tstart = clock64();
     if (grp == 1 && sw.live(a)) sw.next(a);
     for (int i = grp; sw.live(a) && ok; i += 2) {
       int b = i % NB, slot = i % S;
-      if (i >= NB) ok = __all_sync(0xffffffffu, mbar_wait_t(mdone0 + 8 * b, ((i - NB) / NB) & 1, a.status, 3, pr, w0));
+      if (i >= NB) ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, ((i - NB) / NB) & 1, a.status, 3));
       // stage i-1 first: see the note at the MMA issuers' wait (a group skips every other stage)
-      if (ok && i >= 1) ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 10, pr, w1));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 4, pr, w1));
+      if (ok && i >= 1) ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 10));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 4));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const unsigned char* st = ring + (size_t)slot * kStage;
-      if (a.dbg & 8) {
-        mbar_arrive(aready0 + 8 * b);
-        mbar_arrive(empty0 + 8 * slot);
-      } else {
-        // ---- this row of the stage: 256 nibbles -> 256 bytes -> 64 TMEM columns ----
-        uint4 qv[8];
+      // ---- this row of the stage: 256 nibbles -> 256 bytes -> 64 TMEM columns ----
+      uint4 qv[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
+      for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
-          uint32_t regs[8];
+      for (int u = 0; u < 8; ++u) {
+        uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+        uint32_t regs[8];
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
-            regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
-          }
-          if (!(a.dbg & 1)) tmem_st8(tmemA0 + lane_base + b * 64 + u * 8, regs);
-          else if (regs[0] == 0x12345678u && regs[7] == 1u) *last_flag = 1;
+        for (int w = 0; w < 4; ++w) {
+          regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
+          regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        tmem_st8(tmemA0 + lane_base + b * 64 + u * 8, regs);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      // One arrival per warp: 128 arrivals on one mbarrier serialise in the shared-memory atomic
+      // unit and cost more than the conversion itself.  The lanes meet (which also orders their
+      // shared-memory reads and TMEM stores before the elected lane's releasing arrival).
+      __syncwarp();
+      if (lane == 0) {
         mbar_arrive(aready0 + 8 * b);
         mbar_arrive(empty0 + 8 * slot);
       }
       sw.next(a);
       if (sw.live(a)) sw.next(a);
-    }
-    if (pr) {
-      a.probe[16] = clock64() - tstart;
-      a.probe[17] = w0;
-      a.probe[18] = w1;
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -601,19 +475,20 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     }
-    const bool pr = a.probe && blockIdx.x == 0 && et == 0;
-    long long w0 = 0, w1 = 0, tstart = clock64();
     constexpr int kHB = kBlocks / 2;                        // blocks of this half
     constexpr int kSub = kHB * N <= 64 ? kHB : 64 / N;      // blocks per pass (at most 64 columns in registers)
     constexpr int NLD = kSub * N / 16;                      // 16-column loads per pass
     for (int i = 0; sw.live(a) && ok; ++i) {
       int b = i % NB, slot = i % S;
-      ok = __all_sync(0xffffffffu, mbar_wait_t(full0 + 8 * slot, (i / S) & 1, a.status, 6, pr, w0));
+      ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
       uint4 mv = make_uint4(0, 0, 0, 0);
       if (ok) {
         mv = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStage + kStageWBytes + r * 16);
-        mbar_arrive(empty0 + 8 * slot);
-        ok = __all_sync(0xffffffffu, mbar_wait_t(mdone0 + 8 * b, (i / NB) & 1, a.status, 7, pr, w1));
+        // the scale data is in registers: one lane releases the stage for the warp (the value is
+        // consumed by the shuffle, so every lane's load has completed before the arrival)
+        const uint32_t seen = __reduce_or_sync(0xffffffffu, mv.x | 1u);
+        if (lane == 0 && seen) mbar_arrive(empty0 + 8 * slot);
+        ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, (i / NB) & 1, a.status, 7));
       }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -625,17 +500,14 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         uint32_t t[NLD][16];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          if (!(a.dbg & 4)) tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + blk0 * N + l * 16, t[l]);
-          else {
-#pragma unroll
-            for (int z = 0; z < 16; ++z) t[l][z] = meta[l & 3] + z;
-          }
+          tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + blk0 * N + l * 16, t[l]);
         }
 #pragma unroll
         for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[l]);
         if (sub == kHB / kSub - 1) {
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          mbar_arrive(dfree0 + 8 * b);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dfree0 + 8 * b);
         }
 #pragma unroll
         for (int g = 0; g < kSub; ++g) {
@@ -733,11 +605,6 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
     }
-    if (pr) {
-      a.probe[24] = clock64() - tstart;
-      a.probe[25] = w0;
-      a.probe[26] = w1;
-    }
   }
 
   // ---- wind down: everyone meets, outstanding copies are drained, TMEM is returned ----
@@ -809,7 +676,6 @@ int mlx_mma_make_tiled(goph_mlx_weight* w) {
 struct MmaDeviceBufs {
   unsigned char* xb = nullptr;  // prepared B operand of the launch in flight
   float* xtab = nullptr;        // prepared per-(row, group) tables
-  long long* probe = nullptr;
   int* status = nullptr;
   float* scratch = nullptr;
   unsigned int* counters = nullptr;
@@ -823,29 +689,36 @@ constexpr int kMaxPrepIn = 65536;  // mlx_mma_supported's bound on in_dim
 constexpr size_t kPrepXbBytes = (size_t)32 * kMaxPrepIn;
 constexpr size_t kPrepTabFloats = (size_t)2 * 8 * (kMaxPrepIn / 32);
 
+// The buffers of a device are allocated on first use.  Nothing is published until every
+// allocation has succeeded (a failure frees what it got and the next call tries again), and
+// first calls from several threads are serialised.
 static MmaDeviceBufs* device_bufs(int device) {
   static MmaDeviceBufs bufs[kMaxDevices];
-  MmaDeviceBufs& b = bufs[device];
-  if (!b.status) {
-    if (cudaMalloc(&b.status, sizeof(int)) != cudaSuccess) return nullptr;
-    if (cudaMalloc(&b.scratch, kScratchFloats * sizeof(float)) != cudaSuccess) return nullptr;
-    if (cudaMalloc(&b.counters, kMaxCounters * sizeof(unsigned int)) != cudaSuccess) return nullptr;
-    if (cudaMalloc(&b.probe, 32 * sizeof(long long)) != cudaSuccess) return nullptr;
-    if (cudaMalloc(&b.xb, kPrepXbBytes) != cudaSuccess) return nullptr;
-    if (cudaMalloc(&b.xtab, kPrepTabFloats * sizeof(float)) != cudaSuccess) return nullptr;
-    cudaMemset(b.xb, 0, kPrepXbBytes);
-    cudaMemset(b.probe, 0, 32 * sizeof(long long));
-    cudaMemset(b.status, 0, sizeof(int));
-    cudaMemset(b.counters, 0, kMaxCounters * sizeof(unsigned int));
-    cudaDeviceSynchronize();
+  static bool ready[kMaxDevices] = {};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ready[device]) return &bufs[device];
+  MmaDeviceBufs b;
+  bool ok = cudaMalloc(&b.status, sizeof(int)) == cudaSuccess &&
+            cudaMalloc(&b.scratch, kScratchFloats * sizeof(float)) == cudaSuccess &&
+            cudaMalloc(&b.counters, kMaxCounters * sizeof(unsigned int)) == cudaSuccess &&
+            cudaMalloc(&b.xb, kPrepXbBytes) == cudaSuccess &&
+            cudaMalloc(&b.xtab, kPrepTabFloats * sizeof(float)) == cudaSuccess;
+  ok = ok && cudaMemset(b.xb, 0, kPrepXbBytes) == cudaSuccess && cudaMemset(b.status, 0, sizeof(int)) == cudaSuccess &&
+       cudaMemset(b.counters, 0, kMaxCounters * sizeof(unsigned int)) == cudaSuccess &&
+       cudaDeviceSynchronize() == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    cudaFree(b.status);
+    cudaFree(b.scratch);
+    cudaFree(b.counters);
+    cudaFree(b.xb);
+    cudaFree(b.xtab);
+    return nullptr;
   }
-  return &b;
-}
-
-int mlx_mma_probe(int device, long long* out32) {
-  MmaDeviceBufs* b = device_bufs(device);
-  if (!b) return -1;
-  return cudaMemcpy(out32, b->probe, 32 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+  bufs[device] = b;
+  ready[device] = true;
+  return &bufs[device];
 }
 
 int mlx_mma_status(int device) {
@@ -941,8 +814,6 @@ static int tiled_launch(const TiledDesc& w, float* out, const float* x, int batc
   a.counters = bufs->counters;
   a.xb = bufs->xb;
   a.xtab = bufs->xtab;
-  a.probe = options().mlx_probe ? bufs->probe : nullptr;
-  a.dbg = options().mlx_dbg;
   a.out_dim = w.out_dim;
   a.in_dim = w.in_dim;
   a.ntiles = (w.out_dim + kTileRows - 1) / kTileRows;

@@ -83,10 +83,6 @@ GOPH_API int goph_set_option(const char* name, int value) {
   } else if (!strcmp(name, "mlx_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_layout=%d not in 0..2", value);
     o.mlx_layout = value;
-  } else if (!strcmp(name, "mlx_dbg")) {
-    o.mlx_dbg = value;
-  } else if (!strcmp(name, "mlx_probe")) {
-    o.mlx_probe = value != 0;
   } else if (!strcmp(name, "mlx_splits")) {
     if (value < 0 || value > 64) return fail(GOPH_E_INVALID, "mlx_splits=%d not in 0..64", value);
     o.mlx_splits = value;

@@ -23,9 +23,9 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 
 # Every symbol include/goph_b200.h declares.
 EXPORTS = [
-    "goph_init", "goph_set_option", "goph_kernel_status", "goph_debug_probe", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_init", "goph_set_option", "goph_kernel_status", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
-    "goph_mlx_program_create", "goph_mlx_program_create_pre", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free", "goph_mlx_program_probe",
+    "goph_mlx_program_create", "goph_mlx_program_create_pre", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free",
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
@@ -446,11 +446,6 @@ class MLXProgram:
         st = C.c_int(0)
         _check(lib().goph_mlx_program_status(self._h, C.byref(st)))
         return st.value
-
-    def Probe(self):
-        out = (C.c_longlong * 48)()
-        _check(lib().goph_mlx_program_probe(self._h, out))
-        return np.array(out[:], dtype=np.int64).reshape(2, 4, 6)
 
     def Free(self):
         if self._h:

@@ -97,13 +97,6 @@ int goph_set_option(const char* name, int value);
  * after every launch under GO_PHERENCE_CUDA_LAUNCH_CHECK, runtime/runtime.go:687-694.)
  * Synchronises with the device. */
 int goph_kernel_status(int device, int* out_status);
-/* Tuning aids of the tensor-core kernel, compiled in (a few predicated instructions): with option
- * "mlx_probe" = 1, CTA 0 records per-role cycle counters (total and time spent in each barrier
- * wait) that this call copies out as 32 int64 values; option "mlx_dbg" leaves out parts of the
- * kernel for ablation timing (bit 0 TMEM stores, 1 MMAs, 2 TMEM loads, 3 conversion) — results are
- * then meaningless.  Neither is used by the library's own paths or tests of results. */
-int goph_debug_probe(int device, long long* out32);
-
 /* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
 int goph_malloc(int device, uint64_t bytes, void** out_dev);
 int goph_free(int device, void* dev);
@@ -222,11 +215,6 @@ int goph_mlx_program_run(goph_mlx_program* p, void* stream);
  * the list must then be freed.  Synchronises with the device. */
 int goph_mlx_program_status(goph_mlx_program* p, int* out_status);
 int goph_mlx_program_free(goph_mlx_program* p);
-/* Tuning aid: with option "mlx_probe" set, the first and the last CTA record clock64 at six points
- * (product entered, first loads issued, barrier passed, x staged, rows stored, arrival posted) of
- * products 8..11; this copies the 2 x 4 x 6 values out. */
-int goph_mlx_program_probe(goph_mlx_program* p, long long* out48);
-
 /* ---- GPTQ symmetric INT4 weights (backends/simd/quant/q4, runtime/q4.go, gemm_q4.go) ---- */
 
 typedef struct goph_gptq_weight goph_gptq_weight; /* nvidia.GPUQuantWeight (runtime/q4.go:18-26) */
