@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include "stream_gemv.cuh"
+#include "tc_gemm.cuh"
 
 namespace goph {
 
@@ -94,7 +95,7 @@ __global__ void fp8_fill_scale_kernel(float* __restrict__ dst, const float* __re
 }
 
 static bool valid_fp8(const goph_fp8_linear* w) {
-  return w && w->magic == kMagicFP8 && w->weight && w->scale && w->in_dim > 0 && w->out_dim > 0;
+  return w && w->magic == kMagicFP8 && (w->weight || w->tiled) && w->scale && w->in_dim > 0 && w->out_dim > 0;
 }
 
 }  // namespace goph
@@ -132,6 +133,7 @@ GOPH_API int goph_fp8_upload(int device, const uint8_t* weight, uint64_t weight_
     cudaFree(tmp);
     if (rc) {
       cudaFree(h->weight);
+      cudaFree(h->tiled);
       cudaFree(h->scale);
       cudaFree(h->bias);
       delete h;
@@ -161,6 +163,19 @@ GOPH_API int goph_fp8_upload(int device, const uint8_t* weight, uint64_t weight_
   UP(cudaDeviceSynchronize());
 #undef UP
   h->bytes = want + (uint64_t)out_dim * 4 * (bias ? 2 : 1);
+  // Tensor-core layout for matrices large enough to amortise that kernel's fixed cost; a matrix
+  // holding one of the two NaN codes stays row-major (the converter of the tensor-core kernel maps
+  // them to +-480, the CUDA-core kernels keep them NaN as the reference's table does).
+  const bool big = want >= (8u << 20);
+  if (tc_fp8_supported(in_dim) && (options().fp8_layout == 2 || (options().fp8_layout == 0 && big))) {
+    int has_nan = 0;
+    if (int rc = tc_fp8_make_tiled(h, &has_nan)) return bail(rc);
+    if (h->tiled) {
+      cudaFree(h->weight);
+      h->weight = nullptr;
+      h->bytes = (uint64_t)((out_dim + 127) / 128) * 128 * in_dim + (uint64_t)out_dim * 4 * (bias ? 2 : 1);
+    }
+  }
   *out = h;
   return bail(GOPH_OK);
 }
@@ -171,6 +186,7 @@ GOPH_API int goph_fp8_free(goph_fp8_linear* w) {
   if (w->magic != kMagicFP8) return fail(GOPH_E_INVALID, "goph_fp8_free: not an FP8 linear handle");
   if (int rc = use_device(w->device)) return rc;
   cudaFree(w->weight);
+  cudaFree(w->tiled);
   cudaFree(w->scale);
   cudaFree(w->bias);
   w->magic = 0;
@@ -190,6 +206,7 @@ GOPH_API int goph_fp8_dequant(const goph_fp8_linear* w, float* out_dev, uint64_t
     return fail(GOPH_E_INVALID, "dequant out length=%llu, want at least %llu", (unsigned long long)out_len,
                 (unsigned long long)need);
   if (int rc = use_device(w->device)) return rc;
+  if (w->tiled) return tc_fp8_dequant_tiled(w, out_dev, (cudaStream_t)stream);
   fp8_dequant_kernel<<<(unsigned)((need + 255) / 256), 256, 0, (cudaStream_t)stream>>>(w->weight, w->scale, out_dev,
                                                                                        need, w->in_dim);
   GOPH_CUDA(cudaGetLastError());
@@ -209,6 +226,7 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
                 (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
   if (int rc = use_device(w->device)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
+  if (w->tiled) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
   if (w->in_dim % 16 != 0) {
     fp8_gemv_ragged_kernel<<<(w->out_dim + kGWarps - 1) / kGWarps, kGThreads, 0, s>>>(
         w->weight, w->scale, w->bias, x_dev, out_dev, w->out_dim, w->in_dim, batch);
@@ -228,6 +246,25 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
   a.row_bytes = w->in_dim;
   const int force_rows = options().fp8_rows;
   return stream_launch<FP8Fmt>(a, w->device, batch, s, force_rows);
+}
+
+GOPH_API int goph_fp8_gemm_bf16(float* out_dev, uint64_t out_len, const uint16_t* x_bf16_dev, uint64_t x_len, int batch,
+                                const goph_fp8_linear* w, void* stream) {
+  clear_error();
+  if (!valid_fp8(w)) return fail(GOPH_E_INVALID, "invalid FP8 linear handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_x, need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)w->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)w->out_dim, &need_o))
+    return fail(GOPH_E_INVALID, "fp8 batch size overflow batch=%d in=%d out=%d", batch, w->in_dim, w->out_dim);
+  if (!x_bf16_dev || x_len < need_x || !out_dev || out_len < need_o)
+    return fail(GOPH_E_INVALID, "fp8 batch buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
+                (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
+  if (!w->tiled)
+    return fail(GOPH_E_UNSUPPORTED,
+                "goph_fp8_gemm_bf16 needs a linear in the tensor-core layout (in_dim a multiple of 256, no NaN codes, "
+                "uploaded with fp8_layout 0 or 2)");
+  if (int rc = use_device(w->device)) return rc;
+  return tc_gemm_fp8(w, out_dev, x_bf16_dev, true, batch, (cudaStream_t)stream);
 }
 
 GOPH_API int goph_fp8_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len, int batch,

@@ -57,6 +57,7 @@ struct Options {
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
   int mlx_unpack = 0;
   int gguf_layout = 0; // as mlx_layout, for Q4_K / Q8_0 matrices
+  int fp8_layout = 0;  // as mlx_layout, for FP8 linears
   int mlx_rows = 0, gguf_rows = 0, fp8_rows = 0;
   int mlx_ctas_per_sm = 0;  // tuning aid: cap on resident CTAs per SM of the MLX streaming kernel and of product lists (0 = by shape)
 };
@@ -108,7 +109,9 @@ struct goph_fp8_linear {
   int device;
   int in_dim, out_dim;
   int scale_len;      // what the caller passed (1 or out_dim)
-  uint8_t* weight;    // [out_dim][in_dim]
+  uint8_t* weight;    // [out_dim][in_dim] (row-major layout) or nullptr
+  uint8_t* tiled;     // tensor-core layout or nullptr: one 32 KiB block per 128 rows x 256 bytes, blocks
+                      // ordered [tile][chunk], 16-byte unit u of row r at r*256 + ((u&8)|((u&7)^(r&7)))*16
   float* scale;       // [out_dim]
   float* bias;        // [out_dim] or nullptr
   uint64_t bytes;

@@ -30,6 +30,7 @@
 
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
+#include "tc_gemm.cuh"
 
 namespace goph {
 
@@ -902,7 +903,11 @@ static int mlx_products(int n, float* const* outs, const goph_mlx_weight* const*
       const goph_mlx_weight* one = ws[i];
       float* o = outs[i];
       int rc;
-      if (one->tiled) {
+      if (one->tiled && batch > 8) {
+        // more rows than one pass of the integer kernel takes: bf16 operands, weights streamed once
+        // per 16 rows (general f32 activations are split into three exact bf16 pieces)
+        rc = tc_gemm_mlx(one, o, x, false, batch, stream);
+      } else if (one->tiled) {
         rc = mlx_mma_launch(one, o, x, batch, options().mlx_digits, stream, prepared);
         prepared = true;
       } else {
@@ -1277,6 +1282,7 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   if (!out_status) return fail(GOPH_E_INVALID, "goph_kernel_status: nil result pointer");
   if (int rc = use_device(device)) return rc;
   *out_status = mlx_mma_status(device);
+  if (*out_status == 0) *out_status = tc_gemm_status(device);
   return GOPH_OK;
 }
 
@@ -1336,6 +1342,25 @@ GOPH_API int goph_mlx_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
     return fail(GOPH_E_INVALID, "out length=%llu, want at least %llu", (unsigned long long)out_len,
                 (unsigned long long)((uint64_t)batch * w->out_dim));
   return goph_mlx_gemm_multi(1, &out_dev, &w, x_dev, x_len, batch, stream);
+}
+
+GOPH_API int goph_mlx_gemm_bf16(float* out_dev, uint64_t out_len, const uint16_t* x_bf16_dev, uint64_t x_len,
+                                const goph_mlx_weight* w, int batch, void* stream) {
+  clear_error();
+  if (!valid_handle(w)) return fail(GOPH_E_INVALID, "invalid MLX weight handle");
+  if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+  uint64_t need_x, need_o;
+  if (!mul_ok((uint64_t)batch, (uint64_t)w->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)w->out_dim, &need_o))
+    return fail(GOPH_E_INVALID, "batch size overflow");
+  if (!x_bf16_dev || x_len < need_x || !out_dev || out_len < need_o)
+    return fail(GOPH_E_INVALID, "buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len, (unsigned long long)need_x,
+                (unsigned long long)out_len, (unsigned long long)need_o);
+  if (!w->tiled)
+    return fail(GOPH_E_UNSUPPORTED,
+                "goph_mlx_gemm_bf16 needs a weight in the tiled layout (group size 64, in_dim a multiple of 256, "
+                "uploaded with mlx_layout 0 or 2); this one is row-major");
+  if (int rc = use_device(w->device)) return rc;
+  return tc_gemm_mlx(w, out_dev, x_bf16_dev, true, batch, (cudaStream_t)stream);
 }
 
 GOPH_API int goph_mlx_gemv(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,

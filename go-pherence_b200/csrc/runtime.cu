@@ -80,6 +80,9 @@ GOPH_API int goph_set_option(const char* name, int value) {
   } else if (!strcmp(name, "gguf_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "gguf_layout=%d not in 0..2", value);
     o.gguf_layout = value;
+  } else if (!strcmp(name, "fp8_layout")) {
+    if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "fp8_layout=%d not in 0..2", value);
+    o.fp8_layout = value;
   } else if (!strcmp(name, "mlx_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_layout=%d not in 0..2", value);
     o.mlx_layout = value;

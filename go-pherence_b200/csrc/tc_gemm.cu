@@ -1,0 +1,797 @@
+// Small-batch products on the 5th-generation tensor cores: bf16 operands, f32 accumulators in TMEM,
+// the weights streamed ONCE per pass of up to 64 activation rows.
+//
+// Stands behind nvidia.GemmMLX (backends/nvidia/runtime/mlx.go:395-431; kernel text
+// backends/nvidia/ptx/mlx/mlx.go:179-308, which re-reads the weights for every batch row) and
+// nvidia.GemmFP8E4M3Buffer (backends/nvidia/runtime/fp8.go:271-320; ptx/fp8/fp8.go:154-309) for
+// prefill chunks and verifier batches.
+//
+// Arithmetic
+//   * A operand (weights, M = 128 rows of a tile): written to TMEM as bf16 by converter warps.
+//       MLX 4-bit: nibble n becomes the bf16 16 + n (bits 0x4180 | n << 3: two shifts-and-masks per
+//       pair of nibbles, exact).  The 16 is taken out again through the group's sum of x.
+//       FP8 E4M3:  the byte's exponent and mantissa are placed into a bf16 and multiplied by 2^120
+//       (one packed bf16 multiply per two weights) — exact for normals and subnormals alike.
+//   * B operand (activations, N = 16/32/64 columns): bf16.  Activations that are bf16 values go in
+//       as they are (one piece); general f32 activations are split into three bf16 pieces
+//       hi + mid + lo = x exactly, and the three products accumulate into the same columns.
+//   * Every product n * x_piece is exact in f32; the tensor core accumulates in f32.
+//   * MLX: one accumulator block per 64-element group (four K = 16 instructions accumulate);
+//       the epilogue forms scale * (D - 16 * sum x) + bias * sum x = scale * D + (bias - 16 scale) * sum x
+//       per (row, group) in f32 and keeps running sums in registers — mlx.GemvTo's expression
+//       (backends/mlx/gemv.go:178-209) with the dot product taken by the tensor core.
+//     FP8: one accumulator block per 256-element stage; the epilogue adds the stages in f32 and
+//       applies the row scale and bias once at the end (fp8.Linear.GemvTo,
+//       backends/simd/quant/fp8/fp8.go:219-239).
+//
+// Pipeline of one CTA (18 warps, one persistent CTA per SM, walking (128-row tile, K split,
+// 256-element chunk) stages):
+//   producer warp    one bulk copy of the weight block (the tiled layouts store a stage's
+//                    shared-memory image contiguously), one of the chunk's B tile(s), one of the
+//                    chunk's sums of x (MLX), into a ring guarded by full/empty mbarriers; weight
+//                    copies of the first ring are issued before the kernel in front has finished.
+//   8 converter warps  two groups on alternate stages, thread = row: swizzled LDS.128 -> bf16 pairs
+//                    -> tcgen05.st into the group's own 128-column A buffer.
+//   MMA thread       16 (x pieces) tcgen05.mma kind::f16 M128 x N x K16 per stage, A from TMEM, B
+//                    through a shared-memory descriptor; tcgen05.commit releases the A buffer, the
+//                    stage and (per group block / per item) the accumulator to the epilogue.
+//   8 epilogue warps two per TMEM lane quarter, each owning half of the columns: tcgen05.ld,
+//                    scales from the staged block, running sums in registers.  K splits write
+//                    partial sums to scratch; the CTA arriving last adds them in split order.
+// mbarrier arrivals are one per warp.  Every wait is bounded (~2 s); a waiter that gives up
+// records a code (300+) in the status word and the CTA winds down.
+#include <string.h>
+
+#include <mutex>
+
+#include "goph_internal.cuh"
+#include "tc_common.cuh"
+#include "tc_gemm.cuh"
+
+namespace goph {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kTileRows = 128;
+constexpr int kChunkK = 256;
+enum { G_MLX4 = 0, G_FP8 = 1 };
+
+constexpr int kConvWarps = 8, kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
+constexpr int kThreads = (kWarpMMA + 1) * 32;
+constexpr int kMlxWBytes = kTileRows * 128 + kTileRows * 16;  // nibbles + {scale,bias} pairs of a stage
+constexpr int kFp8WBytes = kTileRows * 256;
+
+struct GemmArgs {
+  const unsigned char* w;    // tiled weight blocks [tile][chunk]
+  const unsigned char* xb;   // B tiles [chunk][piece][K step 16][K half 2][NC/8][8 rows][16 B]
+  const float* xtab;         // MLX: [chunk][4 groups][NC] sums of x
+  const float* scale;        // FP8: [out_dim]
+  const float* bias;         // FP8: [out_dim] or nullptr
+  float* out;                // [batch][out_dim]
+  int* status;
+  float* scratch;            // split-K partial sums [tile][split][NC][128]
+  unsigned int* counters;    // per-tile arrival counters, zero between launches
+  int out_dim, in_dim, batch;
+  int ntiles, nchunks, splits, items, stages;
+};
+
+// Walks the (tile, chunk) stages of this CTA's work items in the order every role uses.
+struct StageWalk {
+  int w, tile, split, c, c0, c1;
+  __device__ __forceinline__ void open(const GemmArgs& a) {
+    tile = w / a.splits;
+    split = w - tile * a.splits;
+    c0 = c = split * a.nchunks / a.splits;
+    c1 = (split + 1) * a.nchunks / a.splits;
+  }
+  __device__ __forceinline__ StageWalk(const GemmArgs& a) : w(blockIdx.x) {
+    if (w < a.items) open(a);
+  }
+  __device__ __forceinline__ bool live(const GemmArgs& a) const { return w < a.items; }
+  __device__ __forceinline__ bool last_chunk() const { return c + 1 == c1; }
+  __device__ __forceinline__ void next(const GemmArgs& a) {
+    if (++c == c1) {
+      w += gridDim.x;
+      if (w < a.items) open(a);
+    }
+  }
+};
+
+template <int NC, int P, int FMT>
+struct GemmSmem {
+  static constexpr int kWBytes = FMT == G_MLX4 ? kMlxWBytes : kFp8WBytes;
+  static constexpr int kBBytes = P * NC * 512;                  // 256 K x NC rows of bf16 per piece
+  static constexpr int kXBytes = FMT == G_MLX4 ? NC * 16 : 0;   // 4 groups x NC sums
+  static constexpr int kStage = kWBytes + kBBytes + kXBytes;
+  static __host__ __device__ size_t bytes(int stages) { return (size_t)stages * kStage + 1024 + 512; }
+};
+
+// Element order along K inside a 16-element MMA step, as the converters emit it.  A thread of the
+// preparation kernel owns 8 consecutive elements (one 16-byte row of a core matrix) and places
+// element j of them at position pos8(j).
+//   MLX4: a packed word's nibbles j and j+4 share a register (low / high half).
+//   FP8:  a word's bytes 0,2 and 1,3 share a register.
+template <int FMT>
+__host__ __device__ inline int pos8(int j) {
+  return FMT == G_MLX4 ? 2 * (j & 3) + (j >> 2) : 4 * (j >> 2) + (((j & 1) << 1) | ((j >> 1) & 1));
+}
+
+__device__ __forceinline__ uint32_t bf16_bits_rn(float v) {
+  return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+// ---- activation preparation -----------------------------------------------------------------
+// Grid (chunk, 8-row block of the NC columns); block of 256 threads = 8 rows x 32 octets of the
+// chunk.  Thread: 8 consecutive elements of one activation row -> one 16-byte core-matrix row per
+// piece.  Rows past `batch` are written as zeros.  MLX: the sums of x per 64-element group.
+template <int NC, int P, int FMT, bool XBF16>
+__global__ void __launch_bounds__(256)
+tc_prep_x_kernel(const void* __restrict__ xv, unsigned char* __restrict__ xb, float* __restrict__ xtab, int batch,
+                 int in_dim) {
+  const int c = blockIdx.x, m = blockIdx.y * 8 + (threadIdx.x >> 5), o = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();  // x may be the output of the kernel in front; the tiles may still be read by it
+  float v[8];
+  if (m < batch) {
+    if (XBF16) {
+      const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(xv) + (size_t)m * in_dim + c * kChunkK + o * 8);
+      const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[2 * k] = __uint_as_float(ws[k] << 16);
+        v[2 * k + 1] = __uint_as_float(ws[k] & 0xFFFF0000u);
+      }
+    } else {
+      const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(xv) + (size_t)m * in_dim + c * kChunkK + o * 8);
+      const float4 a = p[0], b = p[1];
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+      v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  }
+  if (FMT == G_MLX4) {
+    float s = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    if ((o & 7) == 0) xtab[((size_t)c * 4 + (o >> 3)) * NC + m] = s;
+  }
+  // K step = o >> 1, K half = o & 1; the 8 elements fill one core-matrix row of that half
+  unsigned char* dst = xb + (size_t)c * (P * NC * 512) + (o >> 1) * (NC * 32) + (o & 1) * ((NC / 8) * 128) + (m >> 3) * 128 +
+                       (m & 7) * 16;
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      h[j] = bf16_bits_rn(v[j]);
+      v[j] -= __uint_as_float(h[j] << 16);  // exact: the remainder of a round-to-nearest fits f32
+    }
+    uint32_t e[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) e[pos8<FMT>(j)] = h[j];
+    *reinterpret_cast<uint4*>(dst + (size_t)p * (NC * 512)) =
+        make_uint4(e[0] | (e[1] << 16), e[2] | (e[3] << 16), e[4] | (e[5] << 16), e[6] | (e[7] << 16));
+  }
+}
+
+// HC (8, 16 or 32) consecutive accumulator columns of this warp's 32 lanes into registers.
+template <int HC>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&t)[HC]) {
+  static_assert(HC == 8 || HC == 16 || HC == 32, "8, 16 or 32 columns");
+  if constexpr (HC == 8) {
+    tmem_ld8(taddr, t);
+    tmem_wait_ld(t);
+  } else if constexpr (HC == 16) {
+    tmem_ld16(taddr, t);
+    tmem_wait_ld(t);
+  } else {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]), "=r"(t[4]), "=r"(t[5]), "=r"(t[6]), "=r"(t[7]), "=r"(t[8]),
+          "=r"(t[9]), "=r"(t[10]), "=r"(t[11]), "=r"(t[12]), "=r"(t[13]), "=r"(t[14]), "=r"(t[15]), "=r"(t[16]),
+          "=r"(t[17]), "=r"(t[18]), "=r"(t[19]), "=r"(t[20]), "=r"(t[21]), "=r"(t[22]), "=r"(t[23]), "=r"(t[24]),
+          "=r"(t[25]), "=r"(t[26]), "=r"(t[27]), "=r"(t[28]), "=r"(t[29]), "=r"(t[30]), "=r"(t[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]),
+                   "+r"(t[9]), "+r"(t[10]), "+r"(t[11]), "+r"(t[12]), "+r"(t[13]), "+r"(t[14]), "+r"(t[15]), "+r"(t[16]),
+                   "+r"(t[17]), "+r"(t[18]), "+r"(t[19]), "+r"(t[20]), "+r"(t[21]), "+r"(t[22]), "+r"(t[23]), "+r"(t[24]),
+                   "+r"(t[25]), "+r"(t[26]), "+r"(t[27]), "+r"(t[28]), "+r"(t[29]), "+r"(t[30]), "+r"(t[31])
+                 :
+                 : "memory");
+  }
+}
+
+// ---- the product kernel -----------------------------------------------------------------------
+template <int NC, int P, int FMT>
+__global__ void __launch_bounds__(kThreads, 1)
+tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
+  static_assert(NC == 16 || NC == 32 || NC == 64, "accumulator blocks of 16, 32 or 64 columns");
+  typedef GemmSmem<NC, P, FMT> SM;
+  constexpr int kWBytes = SM::kWBytes, kBBytes = SM::kBBytes, kXBytes = SM::kXBytes, kStage = SM::kStage;
+  constexpr bool kMLX = FMT == G_MLX4;
+  constexpr int NA = 2;                                        // A buffers of 128 columns, one per converter group
+  constexpr int ND = 256 / NC > 8 ? 8 : 256 / NC;              // accumulator blocks of NC columns
+  constexpr int UPS = kMLX ? 4 : 1;                            // accumulator blocks per stage (MLX: one per 64-element group)
+  constexpr int KPU = 16 / UPS;                                // K = 16 instructions per block and piece
+  constexpr int HC = NC / 2;                                   // columns an epilogue warp owns
+  constexpr uint32_t kCols = 512;
+  static_assert(NA * 128 + ND * NC <= 512, "TMEM plan");
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  const int S = a.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)S * kStage);
+  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
+  const uint32_t aready0 = smem_u32(bars + 2 * S), afree0 = aready0 + 8 * NA;
+  const uint32_t dfull0 = afree0 + 8 * NA, dfree0 = dfull0 + 8 * ND;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      // one converter group, the epilogue (MLX: scale data and sums of x), the MMA commit (B tile)
+      mbar_init(empty0 + 8 * s, kConvWarps / 2 + (kMLX ? kEpiWarps : 0) + 1);
+    }
+    for (int b = 0; b < NA; ++b) {
+      mbar_init(aready0 + 8 * b, kConvWarps / 2);
+      mbar_init(afree0 + 8 * b, 1);
+    }
+    for (int b = 0; b < ND; ++b) {
+      mbar_init(dfull0 + 8 * b, 1);
+      mbar_init(dfree0 + 8 * b, kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kWarpMMA) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)), "r"(kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * 128;
+  bool ok = true;
+  StageWalk sw(a);
+
+  if (warp == kWarpTMA) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      auto load_w = [&](int slot, const StageWalk& s) {
+        bulk_load_1d(smem_u32(ring + (size_t)slot * kStage), a.w + ((size_t)s.tile * a.nchunks + s.c) * kWBytes, kWBytes,
+                     full0 + 8 * slot);
+      };
+      auto load_x = [&](int slot, const StageWalk& s) {
+        const uint32_t dst = smem_u32(ring + (size_t)slot * kStage) + kWBytes;
+        bulk_load_1d(dst, a.xb + (size_t)s.c * kBBytes, kBBytes, full0 + 8 * slot);
+        if (kMLX) bulk_load_1d(dst + kBBytes, a.xtab + (size_t)s.c * (4 * NC), kXBytes, full0 + 8 * slot);
+      };
+      // The weights do not depend on the kernel in front: fill the ring with them first, then wait
+      // for the prepared activations and add the B tiles of those stages.
+      int i = 0;
+      StageWalk sw0 = sw;
+      for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
+        mbar_expect_tx(full0 + 8 * i, kStage);
+        load_w(i, sw0);
+      }
+      pdl_wait();
+      for (int j = 0; j < i; ++j, sw.next(a)) load_x(j, sw);
+      for (; sw.live(a) && ok; ++i, sw.next(a)) {
+        const int slot = i % S, round = i / S;
+        ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 301);
+        if (!ok) break;
+        mbar_expect_tx(full0 + 8 * slot, kStage);
+        load_w(slot, sw);
+        load_x(slot, sw);
+      }
+    }
+  } else if (warp == kWarpMMA) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D f32, A bf16, B bf16, both K-major, N = NC, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NC >> 3) << 17) | ((128u >> 4) << 24);
+      constexpr uint32_t kLBO = (NC / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
+      const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
+      int du = 0;  // accumulator blocks handed to the epilogue so far
+      for (int i = 0; sw.live(a) && ok; ++i) {
+        const int slot = i % S, ab = i % NA;
+        ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 302);
+        if (ok) ok = mbar_wait(aready0 + 8 * ab, (i / NA) & 1, a.status, 303);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage) + kWBytes;
+        const uint32_t acol = tmemA0 + ab * 128;
+#pragma unroll
+        for (int u = 0; u < UPS; ++u, ++du) {
+          const int ds = du % ND;
+          if (du >= ND) {
+            ok = mbar_wait(dfree0 + 8 * ds, (du / ND - 1) & 1, a.status, 304);
+            if (!ok) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int p = 0; p < P; ++p) {
+#pragma unroll
+            for (int k = 0; k < KPU; ++k) {
+              const int ks = KPU * u + k;
+              const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + p * (NC * 512) + ks * (NC * 32)) >> 4) & 0x3FFF);
+              umma_bf16_ts(tmemD0 + ds * NC, acol + ks * 8, bdesc, idesc, (p | k) != 0);
+            }
+          }
+          umma_commit(dfull0 + 8 * ds);
+        }
+        if (!ok) break;
+        umma_commit(afree0 + 8 * ab);
+        umma_commit(empty0 + 8 * slot);
+        sw.next(a);
+      }
+    }
+  } else if (warp < kConvWarps) {
+    // ------------------------------------------------------------------ converters
+    // Two groups of four warps convert alternate stages into their own A buffer; both follow
+    // every stage's full barrier so that no barrier phase is ever skipped.  Thread = row r.
+    const int q4 = warp & 3, grp = warp >> 2;
+    const int r = q4 * 32 + lane;
+    const uint32_t abuf = tmemA0 + ((uint32_t)(q4 * 32) << 16) + grp * 128;
+    for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
+      const int slot = i % S;
+      ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 305));
+      if (!ok) break;
+      if ((i & 1) != grp) continue;
+      if (i >= NA) ok = __all_sync(0xffffffffu, mbar_wait(afree0 + 8 * grp, ((i / NA) - 1) & 1, a.status, 306));
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned char* st = ring + (size_t)slot * kStage;
+      if (kMLX) {
+        // 256 nibbles of the row -> 256 bf16 (16 + n) -> 128 TMEM columns
+        uint4 qv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+#pragma unroll
+          for (int s2 = 0; s2 < 2; ++s2) {  // a K = 16 step is two packed words
+            uint32_t regs[8];
+#pragma unroll
+            for (int wi = 0; wi < 2; ++wi) {
+              const uint32_t w = ws[2 * s2 + wi];
+              regs[4 * wi + 0] = ((w << 3) & 0x00780078u) | 0x41804180u;  // nibbles 0 and 4
+              regs[4 * wi + 1] = ((w >> 1) & 0x00780078u) | 0x41804180u;  // nibbles 1 and 5
+              regs[4 * wi + 2] = ((w >> 5) & 0x00780078u) | 0x41804180u;  // nibbles 2 and 6
+              regs[4 * wi + 3] = ((w >> 9) & 0x00780078u) | 0x41804180u;  // nibbles 3 and 7
+            }
+            tmem_st8(abuf + (2 * u + s2) * 8, regs);
+          }
+        }
+      } else {
+        // 256 E4M3 bytes of the row -> 256 bf16 -> 128 TMEM columns, four 16-byte units at a time
+#pragma unroll
+        for (int ub = 0; ub < 16; ub += 4) {
+          uint4 qv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            qv[u] = *reinterpret_cast<const uint4*>(st + r * 256 + ((((ub + u) & 8) | (((ub + u) & 7) ^ (r & 7))) << 4));
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+            uint32_t regs[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t w = ws[k];
+              // bytes 0,2 / 1,3: sign to bit 15, exponent and mantissa to bits 10..4, times 2^120
+              const uint32_t a02 = ((w << 4) & 0x07F007F0u) | ((w << 8) & 0x80008000u);
+              const uint32_t a13 = ((w >> 4) & 0x07F007F0u) | (w & 0x80008000u);
+              asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(regs[2 * k]) : "r"(a02), "r"(0x7B807B80u));
+              asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(regs[2 * k + 1]) : "r"(a13), "r"(0x7B807B80u));
+            }
+            tmem_st8(abuf + (ub + u) * 8, regs);
+          }
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(aready0 + 8 * grp);
+        mbar_arrive(empty0 + 8 * slot);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    // Warp (q4, h): rows 32 q4 .. +31 of the tile, columns h * HC .. + HC - 1 of every block.
+    const int q4 = warp & 3, h = (warp - kConvWarps) >> 2;
+    const int r = q4 * 32 + lane;
+    const int et = tid - kConvWarps * 32;
+    const uint32_t dbase = tmemD0 + ((uint32_t)(q4 * 32) << 16) + h * HC;
+    const int mcols = a.batch - h * HC;  // columns of this warp that hold activation rows
+    float2 acc[HC / 2];
+#pragma unroll
+    for (int j = 0; j < HC / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+    int du = 0;
+    auto load_block = [&](int ds, uint32_t (&t)[HC]) { tmem_ld_cols<HC>(dbase + ds * NC, t); };
+    for (int i = 0; sw.live(a) && ok; ++i) {
+      const int slot = i % S;
+      const unsigned char* st = ring + (size_t)slot * kStage;
+      uint32_t meta[4] = {0, 0, 0, 0};
+      if (kMLX) {
+        ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 307));
+        if (!ok) break;
+        const uint4 mv = *reinterpret_cast<const uint4*>(st + kTileRows * 128 + r * 16);
+        meta[0] = mv.x, meta[1] = mv.y, meta[2] = mv.z, meta[3] = mv.w;
+      }
+      const float4* xs = reinterpret_cast<const float4*>(st + kWBytes + kBBytes) + h * (HC / 4);
+#pragma unroll
+      for (int u = 0; u < UPS; ++u, ++du) {
+        const int ds = du % ND;
+        ok = __all_sync(0xffffffffu, mbar_wait(dfull0 + 8 * ds, (du / ND) & 1, a.status, 308));
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t t[HC];
+        load_block(ds, t);
+        tc_fence_before();
+        warp_arrive(dfree0 + 8 * ds, lane);
+        if (kMLX) {
+          const float sc = __uint_as_float(meta[u] << 16), bi = __uint_as_float(meta[u] & 0xFFFF0000u);
+          const float b16 = fmaf(-16.f, sc, bi);  // the 16 added to every nibble comes out through sum x
+          const float2 sc2 = make_float2(sc, sc), bi2 = make_float2(b16, b16);
+#pragma unroll
+          for (int j = 0; j < HC / 4; ++j) {
+            if (4 * j < mcols) {
+              const float4 xv = xs[u * (NC / 4) + j];
+              fma2(acc[2 * j], sc2, make_float2(__uint_as_float(t[4 * j]), __uint_as_float(t[4 * j + 1])));
+              fma2(acc[2 * j + 1], sc2, make_float2(__uint_as_float(t[4 * j + 2]), __uint_as_float(t[4 * j + 3])));
+              fma2(acc[2 * j], bi2, make_float2(xv.x, xv.y));
+              fma2(acc[2 * j + 1], bi2, make_float2(xv.z, xv.w));
+            }
+          }
+        } else {
+          // FP8: the tensor core sums one stage (256 elements); the stages are added here in f32
+#pragma unroll
+          for (int j = 0; j < HC / 2; ++j) {
+            acc[j].x += __uint_as_float(t[2 * j]);
+            acc[j].y += __uint_as_float(t[2 * j + 1]);
+          }
+        }
+      }
+      if (!ok) break;
+      if (kMLX) warp_arrive(empty0 + 8 * slot, lane);  // scale data and sums of x are no longer needed
+      const bool item_done = sw.last_chunk();
+      const int tile = sw.tile, split = sw.split;
+      sw.next(a);
+      if (!item_done) continue;
+      // ---- the item is complete ----
+      const int row = tile * kTileRows + r;
+      float rs = 1.f, rb = 0.f;
+      if (!kMLX && row < a.out_dim) {
+        rs = a.scale[row];
+        if (a.bias) rb = a.bias[row];
+      }
+      auto finish = [&](float v) { return kMLX ? v : (a.bias ? __fadd_rn(__fmul_rn(v, rs), rb) : __fmul_rn(v, rs)); };
+      if (a.splits == 1) {
+#pragma unroll
+        for (int j = 0; j < HC / 2; ++j) {
+          const int m = h * HC + 2 * j;
+          if (row < a.out_dim) {
+            if (m < a.batch) a.out[(size_t)m * a.out_dim + row] = finish(acc[j].x);
+            if (m + 1 < a.batch) a.out[(size_t)(m + 1) * a.out_dim + row] = finish(acc[j].y);
+          }
+          acc[j] = make_float2(0.f, 0.f);
+        }
+      } else {
+        // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
+        // partials in split order (so the result does not depend on arrival order) and stores.
+        float* part = a.scratch + ((size_t)tile * a.splits + split) * (NC * kTileRows);
+#pragma unroll
+        for (int j = 0; j < HC / 2; ++j) {
+          const int m = h * HC + 2 * j;
+          if (m < a.batch) part[m * kTileRows + r] = acc[j].x;
+          if (m + 1 < a.batch) part[(m + 1) * kTileRows + r] = acc[j].y;
+          acc[j] = make_float2(0.f, 0.f);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (et == 0) *last_flag = (atomicAdd(a.counters + tile, 1u) == (unsigned)a.splits - 1) ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* base = a.scratch + (size_t)tile * a.splits * (NC * kTileRows);
+          for (int m = h * HC; m < h * HC + HC && m < a.batch; ++m) {
+            float sum = 0.f;
+            for (int s2 = 0; s2 < a.splits; ++s2) sum += __ldcg(base + (size_t)s2 * (NC * kTileRows) + m * kTileRows + r);
+            if (row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum);
+          }
+          if (et == 0) a.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      }
+    }
+  }
+
+  // ---- wind down: everyone meets, outstanding copies are drained, TMEM is returned ----
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kWarpTMA && lane == 0 && *reinterpret_cast<volatile int*>(a.status) != 0) {
+    // a waiter gave up: copies may still be in flight; give each ring slot a bounded chance to land
+    for (int s = 0; s < S; ++s) {
+      long long t0 = clock64();
+      while (!mbar_try_wait(full0 + 8 * s, 0) && !mbar_try_wait(full0 + 8 * s, 1) && clock64() - t0 < kTimeoutCycles / 8) {
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == kWarpMMA) {
+    __syncwarp();
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kCols) : "memory");
+  }
+}
+
+// ---- host side --------------------------------------------------------------------------------
+
+constexpr int kMaxIn = 65536;
+constexpr size_t kXbBytes = (size_t)128 * kMaxIn;          // 64 columns x 1 piece or 16 x 3, 2 bytes each
+constexpr size_t kXtabFloats = (size_t)kMaxIn;             // (in/64) groups x 64 columns
+constexpr int kMaxItems = 320;                             // (tile, split) items with partial sums at once
+constexpr size_t kScratchFloats = (size_t)kMaxItems * kTileRows * 64;
+constexpr size_t kMaxCounters = 4096;
+constexpr size_t kSmemBudget2 = 222 * 1024;
+
+struct GemmBufs {
+  unsigned char* xb = nullptr;
+  float* xtab = nullptr;
+  int* status = nullptr;
+  float* scratch = nullptr;
+  unsigned int* counters = nullptr;
+};
+
+// Allocated on a device's first small-batch product; published only when complete.
+GemmBufs* gemm_bufs(int device, bool allocate = true) {
+  static GemmBufs bufs[kMaxDevices];
+  static bool ready[kMaxDevices] = {};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (ready[device]) return &bufs[device];
+  if (!allocate) return nullptr;
+  GemmBufs b;
+  bool ok = cudaMalloc(&b.xb, kXbBytes) == cudaSuccess && cudaMalloc(&b.xtab, kXtabFloats * 4) == cudaSuccess &&
+            cudaMalloc(&b.status, 256) == cudaSuccess && cudaMalloc(&b.scratch, kScratchFloats * 4) == cudaSuccess &&
+            cudaMalloc(&b.counters, kMaxCounters * 4) == cudaSuccess;
+  ok = ok && cudaMemset(b.status, 0, 256) == cudaSuccess && cudaMemset(b.counters, 0, kMaxCounters * 4) == cudaSuccess &&
+       cudaDeviceSynchronize() == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    cudaFree(b.xb);
+    cudaFree(b.xtab);
+    cudaFree(b.status);
+    cudaFree(b.scratch);
+    cudaFree(b.counters);
+    return nullptr;
+  }
+  bufs[device] = b;
+  ready[device] = true;
+  return &bufs[device];
+}
+
+}  // namespace
+
+// K splits per tile: the split whose busiest CTA spends the least time (items are dealt to the
+// CTAs round-robin), in units of one stage; fix_cost is what writing and re-reading one item's
+// partial sums costs in those units.
+int tc_choose_splits(int ntiles, int nchunks, int sms, int max_items, float fix_cost) {
+  int best = 1;
+  float best_cost = -1.f;
+  for (int s = 1; s <= 8 && s <= nchunks; ++s) {
+    const long items = (long)ntiles * s;
+    if (items > max_items && s > 1) break;
+    const int grid = items < sms ? (int)items : sms;
+    const long per_cta = (items + grid - 1) / grid;
+    const float cost = per_cta * ((nchunks + s - 1) / s + (s > 1 ? fix_cost : 0.f));
+    if (best_cost < 0.f || cost < best_cost) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+namespace {
+
+struct GemmDesc {
+  const unsigned char* tiled;
+  const float* scale;
+  const float* bias;
+  int device, out_dim, in_dim;
+};
+
+template <int NC, int P, int FMT, bool XBF16>
+int launch_pass(const GemmDesc& w, float* out, const void* x, int nb, GemmBufs* bufs, cudaStream_t stream) {
+  typedef GemmSmem<NC, P, FMT> SM;
+  DeviceState& st = device_state(w.device);
+  GemmArgs a;
+  memset(&a, 0, sizeof a);
+  a.w = w.tiled;
+  a.xb = bufs->xb;
+  a.xtab = bufs->xtab;
+  a.scale = w.scale;
+  a.bias = w.bias;
+  a.out = out;
+  a.status = bufs->status;
+  a.scratch = bufs->scratch;
+  a.counters = bufs->counters;
+  a.out_dim = w.out_dim;
+  a.in_dim = w.in_dim;
+  a.batch = nb;
+  a.ntiles = (w.out_dim + kTileRows - 1) / kTileRows;
+  a.nchunks = w.in_dim / kChunkK;
+  int max_items = (int)(kScratchFloats / ((size_t)NC * kTileRows));
+  if (a.ntiles > (int)kMaxCounters) max_items = 0;
+  a.splits = options().mlx_splits > 0 ? (options().mlx_splits < a.nchunks ? options().mlx_splits : a.nchunks)
+                                      : tc_choose_splits(a.ntiles, a.nchunks, st.sm_count, max_items, NC / 32.f);
+  while (a.splits > 1 && (long)a.ntiles * a.splits > max_items) --a.splits;
+  a.items = a.ntiles * a.splits;
+  int stages = (int)((kSmemBudget2 - SM::bytes(0)) / SM::kStage);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return fail(GOPH_E_UNSUPPORTED, "small-batch tensor-core path: a stage of %d bytes leaves no room for a ring", SM::kStage);
+  a.stages = stages;
+  size_t smem = SM::bytes(stages);
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM (the kernel owns all of TMEM)
+
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.stream = stream;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(a.nchunks, NC / 8);
+  cfg.blockDim = dim3(256);
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, tc_prep_x_kernel<NC, P, FMT, XBF16>, x, bufs->xb, bufs->xtab, nb, w.in_dim));
+  auto kern = tc_gemm_kernel<NC, P, FMT>;
+  GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  return GOPH_OK;
+}
+
+// Passes of up to 64 rows (bf16 activations, one piece) or 16 rows (f32 activations, three pieces).
+template <int FMT>
+int run_passes(const GemmDesc& w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
+  if (w.in_dim % kChunkK != 0 || w.in_dim > kMaxIn)
+    return fail(GOPH_E_UNSUPPORTED, "small-batch tensor-core path: in_dim=%d is not a multiple of 256 up to %d", w.in_dim, kMaxIn);
+  if ((uintptr_t)x % 16) return fail(GOPH_E_INVALID, "x must be 16-byte aligned");
+  GemmBufs* bufs = gemm_bufs(w.device);
+  if (!bufs) return fail(GOPH_E_NOMEM, "cannot allocate the small-batch tensor-core path's device scratch");
+  const int cap = x_bf16 ? 64 : 16;
+  const size_t xstride = (size_t)w.in_dim * (x_bf16 ? 2 : 4);
+  for (int b0 = 0; b0 < batch;) {
+    const int nb = batch - b0 < cap ? batch - b0 : cap;
+    const void* xp = static_cast<const unsigned char*>(x) + (size_t)b0 * xstride;
+    float* op = out + (size_t)b0 * w.out_dim;
+    int rc;
+    if (!x_bf16) rc = launch_pass<16, 3, FMT, false>(w, op, xp, nb, bufs, stream);
+    else if (nb <= 16) rc = launch_pass<16, 1, FMT, true>(w, op, xp, nb, bufs, stream);
+    else if (nb <= 32) rc = launch_pass<32, 1, FMT, true>(w, op, xp, nb, bufs, stream);
+    else rc = launch_pass<64, 1, FMT, true>(w, op, xp, nb, bufs, stream);
+    if (rc) return rc;
+    b0 += nb;
+  }
+  return GOPH_OK;
+}
+
+// Row-major bytes -> tiled stages (16-byte unit u of row r at r*256 + ((u & 8) | ((u & 7) ^ (r & 7))) * 16);
+// one thread per 16-byte unit.  Flags the two NaN codes.
+__global__ void fp8_tile_kernel(const unsigned char* __restrict__ w, unsigned char* __restrict__ tiled, int out_dim, int in_dim,
+                                int ntiles, int nchunks, int* nan_flag) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nstages = (size_t)ntiles * nchunks;
+  if (idx >= nstages * (128 * 16)) return;
+  size_t stg = idx / (128 * 16);
+  int rem = (int)(idx - stg * (128 * 16));
+  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
+  int r = rem >> 4, u = rem & 15, row = tile * 128 + r;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (row < out_dim) {
+    v = *reinterpret_cast<const uint4*>(w + (size_t)row * in_dim + chunk * 256 + u * 16);
+    const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
+    bool nan = false;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t m = ws[k] & 0x7F7F7F7Fu;
+      nan = nan || (m & 0xFFu) == 0x7Fu || (m & 0xFF00u) == 0x7F00u || (m & 0xFF0000u) == 0x7F0000u || (m >> 24) == 0x7Fu;
+    }
+    if (nan) *nan_flag = 1;
+  }
+  *reinterpret_cast<uint4*>(tiled + stg * kFp8WBytes + r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4)) = v;
+}
+
+__global__ void fp8_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, const float* __restrict__ scale,
+                                         float* __restrict__ out, int out_dim, int in_dim, int nchunks) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)out_dim * in_dim) return;
+  int row = (int)(i / in_dim), col = (int)(i - (size_t)row * in_dim);
+  int chunk = col >> 8, k = col & 255, u = k >> 4, r = row & 127;
+  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * kFp8WBytes;
+  unsigned char b = stg[r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4) + (k & 15)];
+  __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+  out[i] = __fmul_rn(__half2float(*reinterpret_cast<__half*>(&hr)), scale[row]);
+}
+
+}  // namespace
+
+int tc_gemm_mlx(const goph_mlx_weight* w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
+  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
+  GemmDesc d{w->tiled, nullptr, nullptr, w->device, w->out_dim, w->in_dim};
+  return run_passes<G_MLX4>(d, out, x, x_bf16, batch, stream);
+}
+
+int tc_gemm_fp8(const goph_fp8_linear* w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
+  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "FP8 linear is not in the tiled layout");
+  GemmDesc d{w->tiled, w->scale, w->bias, w->device, w->out_dim, w->in_dim};
+  return run_passes<G_FP8>(d, out, x, x_bf16, batch, stream);
+}
+
+bool tc_fp8_supported(int in_dim) { return in_dim % kChunkK == 0 && in_dim <= kMaxIn; }
+
+int tc_fp8_make_tiled(goph_fp8_linear* w, int* has_nan) {
+  const int ntiles = (w->out_dim + kTileRows - 1) / kTileRows, nchunks = w->in_dim / kChunkK;
+  const size_t bytes = (size_t)ntiles * nchunks * kFp8WBytes;
+  unsigned char* t = nullptr;
+  int* flag = nullptr;
+  GOPH_CUDA(cudaMalloc(&t, bytes));
+  cudaError_t e = cudaMalloc(&flag, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(flag, 0, sizeof(int));
+  if (e == cudaSuccess) {
+    size_t threads = (size_t)ntiles * nchunks * 128 * 16;
+    fp8_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(w->weight, t, w->out_dim, w->in_dim, ntiles, nchunks, flag);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaMemcpy(has_nan, flag, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(flag);
+  if (e != cudaSuccess) {
+    cudaFree(t);
+    return fail_cuda(e, "fp8_tile_kernel");
+  }
+  if (*has_nan) {
+    cudaFree(t);
+    return GOPH_OK;
+  }
+  w->tiled = t;
+  return GOPH_OK;
+}
+
+int tc_fp8_dequant_tiled(const goph_fp8_linear* w, float* out, cudaStream_t stream) {
+  size_t n = (size_t)w->out_dim * w->in_dim;
+  fp8_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w->tiled, w->scale, out, w->out_dim, w->in_dim,
+                                                                            w->in_dim / kChunkK);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+int tc_gemm_status(int device) {
+  GemmBufs* b = gemm_bufs(device, false);
+  if (!b) return 0;  // no small-batch product has run on this device
+  int v = -1;
+  cudaMemcpy(&v, b->status, sizeof(int), cudaMemcpyDeviceToHost);
+  return v;
+}
+
+}  // namespace goph

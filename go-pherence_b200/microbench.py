@@ -25,7 +25,7 @@ def algorithmic_bytes(fmt, out_dim, in_dim, batch):
     return out_dim * in_dim * per_weight + extra + batch * in_dim * 4 + batch * out_dim * 4
 
 
-def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=10, chain=False):
+def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=10, chain=False, xbf16=False):
     import torch
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
@@ -51,6 +51,9 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     x = torch.from_numpy(syn.activations("mb", batch * in_dim)).cuda()
     out = torch.empty(batch * out_dim, dtype=torch.float32, device="cuda")
     xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
+    if xbf16:  # the activations as bf16 in device memory (the bf16 entry points, tensor-core layouts only)
+        x16 = x.to(torch.bfloat16)
+        xb = rt.wrap(x16.data_ptr(), x16.numel() * 2)
     stream = torch.cuda.current_stream()
     if chain:
         # every launch consumes the output of the one before it (square matrices only), as the
@@ -69,7 +72,11 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
             _launch(h, xb, ob)
 
     def _launch(h, xb, ob):
-        if fmt == "mlx4":
+        if fmt == "mlx4" and xbf16:
+            rt.GemmMLXBF16(ob, xb, h, batch, stream)
+        elif fmt == "fp8" and xbf16:
+            rt.GemmFP8E4M3BF16Buffer(ob, xb, batch, h, stream)
+        elif fmt == "mlx4":
             rt.GemmMLX(ob, xb, h, batch, stream)
         elif fmt == "fp8":
             rt.GemmFP8E4M3Buffer(ob, xb, batch, h, stream)
@@ -101,7 +108,8 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     if os.path.exists(pk):
         peak = float(json.load(open(pk))["hbm_gbs"])
     gbs = nbytes / us / 1e3
-    res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "opts": dict(opts), "copies": copies, "chain": bool(chain),
+    tflops = 2.0 * out_dim * in_dim * batch / us / 1e6
+    res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "x": "bf16" if xbf16 else "f32", "tflops": round(tflops, 1), "opts": dict(opts), "copies": copies, "chain": bool(chain),
            "us_per_launch": round(us, 3), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
            "bytes": nbytes}
     for h in handles:
@@ -141,6 +149,9 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
     x = torch.from_numpy(syn.activations("moe-bench", tokens * hidden)).cuda()
     out = torch.empty(tokens * hidden, dtype=torch.float32, device="cuda")
     xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
+    if xbf16:  # the activations as bf16 in device memory (the bf16 entry points, tensor-core layouts only)
+        x16 = x.to(torch.bfloat16)
+        xb = rt.wrap(x16.data_ptr(), x16.numel() * 2)
     stream = torch.cuda.current_stream()
     distinct = []
     for m in mods:
@@ -323,6 +334,7 @@ def main():
     ap.add_argument("--launches", type=int, default=200)
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--opt", action="append", default=[], help="name=value for goph_set_option")
+    ap.add_argument("--xbf16", action="store_true", help="activations held as bf16 (the bf16 entry points)")
     ap.add_argument("--chain", action="store_true", help="each launch reads the previous launch's output (out == in)")
     ap.add_argument("--list", action="store_true", help="--layer-chain as one product list (one cooperative launch)")
     ap.add_argument("--decode-tokens", type=int, default=0, help="run this many eager decoder steps (for a launch list)")
@@ -343,7 +355,7 @@ def main():
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts)))
         return
-    print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts, chain=args.chain)))
+    print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts, chain=args.chain, xbf16=args.xbf16)))
 
 
 if __name__ == "__main__":

@@ -29,11 +29,11 @@ EXPORTS = [
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
-    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
+    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_bf16", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
     "goph_mlx_gemm_host",
     "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
     "goph_gguf_project", "goph_gguf_project_host",
-    "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm",
+    "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm", "goph_fp8_gemm_bf16",
     "goph_fp8_gemm_host",
     "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
     "goph_moe_forward_logits", "goph_moe_last_routing",
@@ -262,6 +262,21 @@ def GemmMLX(out, input, w, B, stream=None):
         raise GophError(1, "nil buffer")
     _check(lib().goph_mlx_gemm(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(input.Ptr),
                                C.c_uint64(input.n), _mlx_handle(w), int(B), _stream_ptr(stream)))
+
+
+def to_bf16_bits(a):
+    """f32 array -> uint16 bf16 bit patterns (round to nearest even)."""
+    b = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return ((b + np.uint32(0x7FFF) + ((b >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def GemmMLXBF16(out, input, w, B, stream=None):
+    """nvidia.GemmMLX (runtime/mlx.go:395) with the activations held as bf16: `input` is a Buffer of
+    B * inDim bf16 bit patterns (2 bytes each)."""
+    if out is None or input is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_mlx_gemm_bf16(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(input.Ptr),
+                                    C.c_uint64(input.Size // 2), _mlx_handle(w), int(B), _stream_ptr(stream)))
 
 
 def GemmMLXMulti(outs, x, weights, B=1, stream=None):
@@ -546,6 +561,15 @@ def GemmFP8E4M3Buffer(out, x, batch, w, stream=None):
         raise GophError(1, "nil buffer")
     _check(lib().goph_fp8_gemm(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
                                int(batch), _fp8_handle(w), _stream_ptr(stream)))
+
+
+def GemmFP8E4M3BF16Buffer(out, x, batch, w, stream=None):
+    """nvidia.GemmFP8E4M3Buffer (runtime/fp8.go:271) with the activations held as bf16: `x` is a Buffer
+    of batch * inDim bf16 bit patterns."""
+    if out is None or x is None:
+        raise GophError(1, "nil buffer")
+    _check(lib().goph_fp8_gemm_bf16(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.Size // 2),
+                                    int(batch), _fp8_handle(w), _stream_ptr(stream)))
 
 
 def GemvFP8E4M3Buffer(out, x, w, stream=None):

@@ -79,6 +79,9 @@ int goph_sm_count(int device);
  *                 0 (default) tensor-core layout from 8 Mi weights, 1 always the streaming layout,
  *                 2 tensor-core layout whenever the shape allows.  "mlx_digits" and "mlx_splits"
  *                 apply to these products as well
+ *   "fp8_layout"  the same choice for goph_fp8_upload (in_dim a multiple of 256, no NaN codes in the
+ *                 weight): the tensor-core layout serves every batch size through the bf16
+ *                 tensor-core kernel, the row-major layout the CUDA-core kernels
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
@@ -134,9 +137,18 @@ int goph_mlx_dequant(const goph_mlx_weight* w, float* out_dev, uint64_t out_len,
 /* nvidia.GemvMLX / GemvMLXDirect (runtime/mlx.go:287-350, :455-488): out = W·x. */
 int goph_mlx_gemv(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
                   const goph_mlx_weight* w, void* stream);
-/* nvidia.GemmMLX (runtime/mlx.go:395-431): x [batch,in] → out [batch,out]. */
+/* nvidia.GemmMLX (runtime/mlx.go:395-431): x [batch,in] → out [batch,out].  Tiled weights: up to
+ * 8 rows run on the integer tensor-core kernel; more rows on the bf16 tensor-core kernel, which
+ * streams the weights once per 16 rows (every f32 activation is split into three bf16 pieces
+ * that add up to it exactly, so the result is as exact as the 8-row path's). */
 int goph_mlx_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
                   const goph_mlx_weight* w, int batch, void* stream);
+/* nvidia.GemmMLX (runtime/mlx.go:395-431) for activations held as bf16 (prefill chunks and verifier
+ * batches of models whose activations are bf16): x_bf16_dev is [batch,in] bf16 bit patterns,
+ * 16-byte aligned; x_len counts elements.  The weights are streamed once per 64 rows.  Tiled
+ * weights only (GOPH_E_UNSUPPORTED otherwise). */
+int goph_mlx_gemm_bf16(float* out_dev, uint64_t out_len, const uint16_t* x_bf16_dev, uint64_t x_len,
+                       const goph_mlx_weight* w, int batch, void* stream);
 /* mlx.Gemv2To generalised (backends/mlx/gemv.go:32-60): n ≤ 8 weights with equal in_dim and
  * group size share one x [batch,in]; outs_dev[i] is [batch, out_dim_i].  One launch. */
 int goph_mlx_gemm_multi(int n, float* const* outs_dev, const goph_mlx_weight* const* ws,
@@ -256,6 +268,11 @@ int goph_fp8_dequant(const goph_fp8_linear* w, float* out_dev, uint64_t out_len,
 /* nvidia.GemvFP8E4M3Buffer / GemmFP8E4M3Buffer (runtime/fp8.go:995, :271). */
 int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
                   const goph_fp8_linear* w, void* stream);
+/* nvidia.GemmFP8E4M3Buffer (runtime/fp8.go:271-320) for activations held as bf16: x_bf16_dev is
+ * [batch,in] bf16 bit patterns, 16-byte aligned; the weights are streamed once per 64 rows.
+ * Linears in the tensor-core layout only (GOPH_E_UNSUPPORTED otherwise). */
+int goph_fp8_gemm_bf16(float* out_dev, uint64_t out_len, const uint16_t* x_bf16_dev, uint64_t x_len, int batch,
+                       const goph_fp8_linear* w, void* stream);
 /* nvidia.GemvFP8E4M3 / GemmFP8E4M3 with Go slices (runtime/fp8.go:158, :180). */
 int goph_fp8_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
                        int batch, const goph_fp8_linear* w);
