@@ -11,13 +11,18 @@ from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-OBJ = os.path.join(HERE, "build")
-LIB = os.path.join(HERE, "libgoph_b200.so")
+# GOPH_TUNING=1 builds a second library with the kernels' cycle probes compiled in (tuning only;
+# nothing in the package loads it unless GOPH_B200_LIB points at it)
+TUNING = os.environ.get("GOPH_TUNING") == "1"
+OBJ = os.path.join(HERE, "build_tuning" if TUNING else "build")
+LIB = os.path.join(HERE, "libgoph_b200_tuning.so" if TUNING else "libgoph_b200.so")
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "--use_fast_math=false"]
 FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]  # precise math only
+if TUNING:
+    FLAGS.append("-DGOPH_TUNING")
 
 
 def _sources():

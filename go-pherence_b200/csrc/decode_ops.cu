@@ -91,6 +91,11 @@ add_rmsnorm_kernel(float* hidden, float* __restrict__ normed, const float* a, co
   }
 }
 
+// Set when a kernel found the position word outside [0, max_seq): 401 the KV append, 402 attention.
+// Such a kernel touches neither the caches nor its output (a step replayed once more than the cache
+// holds, or a stale position word, must not write out of bounds).  Read through goph_kernel_status.
+__device__ int g_decode_status;
+
 // Per head (q heads then k heads): optional RMSNorm with the head-dim weight, RoPE on the pairs
 // (i, i + d/2) with the table row of *pos_dev; q in place, k into the cache row, v copied into its
 // cache row.  One CTA of head_dim/2 threads per head; head_dim <= 512.
@@ -99,10 +104,14 @@ qk_norm_rope_append_kernel(float* __restrict__ q, const float* __restrict__ k, c
                            const float* __restrict__ qw, const float* __restrict__ kw,
                            const float* __restrict__ table, const int* __restrict__ pos_dev,
                            float* __restrict__ kcache, float* __restrict__ vcache, int heads, int kv_heads,
-                           int head_dim, float eps) {
+                           int head_dim, float eps, int max_seq) {
   __shared__ float sh[8];
   pdl_begin();
   const int pos = *pos_dev, half = head_dim / 2, i = threadIdx.x;
+  if (pos < 0 || pos >= max_seq) {
+    if (i == 0) atomicCAS(&g_decode_status, 0, 401);
+    return;
+  }
   const bool is_q = (int)blockIdx.x < heads;
   const int head = is_q ? blockIdx.x : blockIdx.x - heads;
   const float* src = (is_q ? q : k) + (size_t)head * head_dim;
@@ -179,6 +188,7 @@ struct AttnArgs {
   float* vcache;
   const int* pos_dev;
   int heads, kv_heads, head_dim;
+  int max_seq;           // rows of the caches and of the RoPE table
   float scale, eps;
   float* scratch;
   unsigned int* counters;
@@ -193,6 +203,10 @@ attn_decode_kernel(const __grid_constant__ AttnArgs a) {
   __shared__ int s_last;
   pdl_begin();
   const int pos = *a.pos_dev, seq = pos + 1;
+  if (pos < 0 || pos >= a.max_seq) {
+    if (threadIdx.x == 0) atomicCAS(&g_decode_status, 0, 402);
+    return;
+  }
   const int heads = a.heads, kv_heads = a.kv_heads, head_dim = a.head_dim;
   const int head = blockIdx.x, per = heads / kv_heads, kvh = head / per;
   const int splits = gridDim.y, split = blockIdx.y;
@@ -466,6 +480,17 @@ static int op_launch(void (*k)(KArgs...), dim3 grid, int threads, size_t smem, v
 
 }  // namespace goph
 
+namespace goph {
+int decode_ops_status() {
+  int v = 0;
+  return cudaMemcpyFromSymbol(&v, g_decode_status, sizeof(int)) == cudaSuccess ? v : -1;
+}
+void decode_ops_status_clear() {
+  const int zero = 0;
+  cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int));
+}
+}  // namespace goph
+
 using namespace goph;
 
 GOPH_API int goph_add_rmsnorm(int device, float* hidden_dev, float* normed_dev, const float* a_dev, const float* b_dev,
@@ -478,9 +503,10 @@ GOPH_API int goph_add_rmsnorm(int device, float* hidden_dev, float* normed_dev, 
 
 GOPH_API int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_dev, const float* v_dev,
                                       const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
-                                      const int* pos_dev, float* kcache_dev, float* vcache_dev, int heads, int kv_heads,
-                                      int head_dim, float eps, void* stream) {
+                                      const int* pos_dev, float* kcache_dev, float* vcache_dev, int max_seq, int heads,
+                                      int kv_heads, int head_dim, float eps, void* stream) {
   clear_error();
+  if (max_seq <= 0) return fail(GOPH_E_INVALID, "max_seq=%d", max_seq);
   if (!q_dev || !k_dev || !v_dev || !rope_table_dev || !pos_dev || !kcache_dev || !vcache_dev)
     return fail(GOPH_E_INVALID, "goph_qk_norm_rope_append: nil buffer");
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || head_dim < 64 || head_dim > 512 || head_dim % 64)
@@ -489,7 +515,7 @@ GOPH_API int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_d
   if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fail(GOPH_E_INVALID, "QNorm without KNorm");
   if (int rc = use_device(device)) return rc;
   return op_launch(qk_norm_rope_append_kernel, dim3(heads + kv_heads), head_dim / 2, 0, stream, q_dev, k_dev, v_dev, q_norm_dev,
-                   k_norm_dev, rope_table_dev, pos_dev, kcache_dev, vcache_dev, heads, kv_heads, head_dim, eps);
+                   k_norm_dev, rope_table_dev, pos_dev, kcache_dev, vcache_dev, heads, kv_heads, head_dim, eps, max_seq);
 }
 
 static int attn_launch(int device, AttnArgs& a, int max_seq, bool fused, void* stream) {
@@ -509,6 +535,7 @@ static int attn_launch(int device, AttnArgs& a, int max_seq, bool fused, void* s
   }
   a.scratch = scratch[device];
   a.counters = counters[device];
+  a.max_seq = max_seq;
   // Short caches (the latency-bound case): CTAs of 4 warps, one block of 16 positions each, so that they
   // fit beside the projection kernels' CTAs and start under programmatic dependent launch (measured on
   // the Qwen3-0.6B step at positions 128-191: 1318 tok/s against 1249 with 32-warp CTAs).  Long caches:

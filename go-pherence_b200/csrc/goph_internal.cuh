@@ -63,6 +63,11 @@ struct Options {
 };
 Options& options();
 
+// Status word of the decode-step kernels on the current device (0, or 401 / 402 when a kernel found
+// the position word outside [0, max_seq)).
+int decode_ops_status();
+void decode_ops_status_clear();
+
 // Largest dynamic shared-memory request the GEMV kernels make.
 constexpr int kSmemBudget = 200 * 1024;
 

@@ -721,6 +721,11 @@ static MmaDeviceBufs* device_bufs(int device) {
   return &bufs[device];
 }
 
+void mlx_mma_status_clear(int device) {
+  MmaDeviceBufs* b = device_bufs(device);
+  if (b) cudaMemset(b->status, 0, sizeof(int));
+}
+
 int mlx_mma_status(int device) {
   MmaDeviceBufs* b = device_bufs(device);
   int v = -1;

@@ -28,6 +28,7 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
                    bool x_prepared = false);
 // Reads the device status word (0 = every wait completed); synchronises the copy stream.
 int mlx_mma_status(int device);
+void mlx_mma_status_clear(int device);
 
 // GGUF Q4_K / Q8_0 on the same kernel.  make_tiled builds m->tiled from the matrix's device
 // buffers (which the caller then frees); dequant reproduces dequantRowQ4KTo / dequantRowQ8_0To.

@@ -119,12 +119,29 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[8]) {
                :
                : "memory");
 }
+// One lane waits for the whole warp (32 lanes polling the same barrier only crowd the shared-memory
+// pipeline); the shuffle hands the outcome to the others and orders their later accesses behind it.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int* status, int code, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 // One arrival for the whole warp: the lanes meet (which orders their shared-memory reads and, with
 // the tcgen05 fence each lane has executed, their TMEM accesses before the releasing arrival).
 // A per-thread arrival would serialise 32 shared-memory atomics per warp on one barrier.
 __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
   __syncwarp();
   if (lane == 0) mbar_arrive(bar);
+}
+// True in exactly one lane of the (converged) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

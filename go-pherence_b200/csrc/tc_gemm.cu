@@ -54,14 +54,33 @@ using namespace tc;
 
 namespace {
 
+// Tuning build only (-DGOPH_TUNING): CTA 0 adds up, per role, the cycles spent in each barrier wait
+// and in each phase of its loop; goph_tuning_probe copies the counters out.  The shipped library
+// is built without it.
+#ifdef GOPH_TUNING
+__device__ unsigned long long g_tc_span[4];  // globaltimer ns: min CTA entry, max CTA set-up done, max CTA exit, min set-up done
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ long long g_tc_trace[8][64];  // [event][stage] clock64 of one CTA in the middle of the grid
+#define TP(...) __VA_ARGS__
+#define DBG(bit) (a.dbg & (bit))
+#else
+#define TP(...)
+#define DBG(bit) 0
+#endif
+
 constexpr int kTileRows = 128;
 constexpr int kChunkK = 256;
 enum { G_MLX4 = 0, G_FP8 = 1 };
 
-constexpr int kConvWarps = 8, kEpiWarps = 8;
+constexpr int kConvWarps = 8, kEpiWarps = 16;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
-constexpr int kThreads = (kWarpMMA + 1) * 32;
+constexpr int kMmaWarps = 1;
+constexpr int kThreads = (kWarpMMA + kMmaWarps) * 32;
 constexpr int kMlxWBytes = kTileRows * 128 + kTileRows * 16;  // nibbles + {scale,bias} pairs of a stage
 constexpr int kFp8WBytes = kTileRows * 256;
 
@@ -77,6 +96,8 @@ struct GemmArgs {
   unsigned int* counters;    // per-tile arrival counters, zero between launches
   int out_dim, in_dim, batch;
   int ntiles, nchunks, splits, items, stages;
+  int rotate;                // 1: every tile starts its K range at a different chunk (see StageWalk::chunk)
+  int dbg;                   // tuning build only: parts of the kernel left out (results are then wrong)
 };
 
 // Walks the (tile, chunk) stages of this CTA's work items in the order every role uses.
@@ -93,6 +114,14 @@ struct StageWalk {
   }
   __device__ __forceinline__ bool live(const GemmArgs& a) const { return w < a.items; }
   __device__ __forceinline__ bool last_chunk() const { return c + 1 == c1; }
+  // The chunk to load at this step.  The CTAs of a wave walk their K ranges in step; starting each
+  // tile at a different chunk keeps them from all asking the L2 for the same activation tile at
+  // the same moment.  (The sum over chunks is taken in this order; it is fixed per tile.)
+  __device__ __forceinline__ int chunk(const GemmArgs& a) const {
+    if (!a.rotate) return c;
+    const int len = c1 - c0;
+    return c0 + (c - c0 + tile * 5) % len;
+  }
   __device__ __forceinline__ void next(const GemmArgs& a) {
     if (++c == c1) {
       w += gridDim.x;
@@ -181,33 +210,28 @@ tc_prep_x_kernel(const void* __restrict__ xv, unsigned char* __restrict__ xb, fl
   }
 }
 
-// HC (8, 16 or 32) consecutive accumulator columns of this warp's 32 lanes into registers.
+// HC (4, 8 or 16) consecutive accumulator columns of this warp's 32 lanes into registers: the
+// load is issued, and waited for separately so that other work can go in between.
 template <int HC>
-__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&t)[HC]) {
-  static_assert(HC == 8 || HC == 16 || HC == 32, "8, 16 or 32 columns");
-  if constexpr (HC == 8) {
-    tmem_ld8(taddr, t);
-    tmem_wait_ld(t);
-  } else if constexpr (HC == 16) {
-    tmem_ld16(taddr, t);
-    tmem_wait_ld(t);
-  } else {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]), "=r"(t[4]), "=r"(t[5]), "=r"(t[6]), "=r"(t[7]), "=r"(t[8]),
-          "=r"(t[9]), "=r"(t[10]), "=r"(t[11]), "=r"(t[12]), "=r"(t[13]), "=r"(t[14]), "=r"(t[15]), "=r"(t[16]),
-          "=r"(t[17]), "=r"(t[18]), "=r"(t[19]), "=r"(t[20]), "=r"(t[21]), "=r"(t[22]), "=r"(t[23]), "=r"(t[24]),
-          "=r"(t[25]), "=r"(t[26]), "=r"(t[27]), "=r"(t[28]), "=r"(t[29]), "=r"(t[30]), "=r"(t[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]),
-                   "+r"(t[9]), "+r"(t[10]), "+r"(t[11]), "+r"(t[12]), "+r"(t[13]), "+r"(t[14]), "+r"(t[15]), "+r"(t[16]),
-                   "+r"(t[17]), "+r"(t[18]), "+r"(t[19]), "+r"(t[20]), "+r"(t[21]), "+r"(t[22]), "+r"(t[23]), "+r"(t[24]),
-                   "+r"(t[25]), "+r"(t[26]), "+r"(t[27]), "+r"(t[28]), "+r"(t[29]), "+r"(t[30]), "+r"(t[31])
-                 :
+__device__ __forceinline__ void tmem_ld_issue(uint32_t taddr, uint32_t (&t)[HC]) {
+  static_assert(HC == 4 || HC == 8 || HC == 16, "4, 8 or 16 columns");
+  if constexpr (HC == 4) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3])
+                 : "r"(taddr)
                  : "memory");
+  } else if constexpr (HC == 8) {
+    tmem_ld8(taddr, t);
+  } else {
+    tmem_ld16(taddr, t);
+  }
+}
+template <int HC>
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&t)[HC]) {
+  if constexpr (HC == 4) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]) : : "memory");
+  } else {
+    tmem_wait_ld(t);
   }
 }
 
@@ -220,12 +244,16 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   constexpr int kWBytes = SM::kWBytes, kBBytes = SM::kBBytes, kXBytes = SM::kXBytes, kStage = SM::kStage;
   constexpr bool kMLX = FMT == G_MLX4;
   constexpr int NA = 2;                                        // A buffers of 128 columns, one per converter group
-  constexpr int ND = 256 / NC > 8 ? 8 : 256 / NC;              // accumulator blocks of NC columns
-  constexpr int UPS = kMLX ? 4 : 1;                            // accumulator blocks per stage (MLX: one per 64-element group)
-  constexpr int KPU = 16 / UPS;                                // K = 16 instructions per block and piece
-  constexpr int HC = NC / 2;                                   // columns an epilogue warp owns
+  // A stage is handed from the MMA warp to the epilogue in two units of 128 elements; a unit is
+  // two accumulator blocks of NC columns (one per 64 elements, an MLX group).  Every hand-over
+  // costs each side a few hundred cycles of waits, fences and arrivals, so it is not done per block.
+  constexpr int UPS = 2;                                       // units per stage
+  constexpr int UC = 2 * NC;                                   // accumulator columns of a unit
+  constexpr int ND = 256 / UC > 4 ? 4 : 256 / UC;              // units in the accumulator ring
+  constexpr int HC = NC / 4;                                   // columns an epilogue warp owns
   constexpr uint32_t kCols = 512;
-  static_assert(NA * 128 + ND * NC <= 512, "TMEM plan");
+  static_assert(NA * 128 + ND * UC <= 512, "TMEM plan");
+  TP(if (threadIdx.x == 0) atomicMin(&g_tc_span[0], gtime());)
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
@@ -242,12 +270,12 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(full0 + 8 * s, 1);
-      // one converter group, the epilogue (MLX: scale data and sums of x), the MMA commit (B tile)
-      mbar_init(empty0 + 8 * s, kConvWarps / 2 + (kMLX ? kEpiWarps : 0) + 1);
+      // the converters, the epilogue (MLX: scale data and sums of x), the MMA commits (B tile)
+      mbar_init(empty0 + 8 * s, kConvWarps + (kMLX ? kEpiWarps : 0) + kMmaWarps);
     }
     for (int b = 0; b < NA; ++b) {
-      mbar_init(aready0 + 8 * b, kConvWarps / 2);
-      mbar_init(afree0 + 8 * b, 1);
+      mbar_init(aready0 + 8 * b, kConvWarps);
+      mbar_init(afree0 + 8 * b, kMmaWarps);
     }
     for (int b = 0; b < ND; ++b) {
       mbar_init(dfull0 + 8 * b, 1);
@@ -268,102 +296,130 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * 128;
   bool ok = true;
   StageWalk sw(a);
+  TP(const bool tr = blockIdx.x == gridDim.x / 2; if (tr && tid == 0) g_tc_trace[7][0] = clock64();)
+  TP(if (tid == 0) { const unsigned long long g = gtime(); atomicMax(&g_tc_span[1], g); atomicMin(&g_tc_span[3], g); })
 
   if (warp == kWarpTMA) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       auto load_w = [&](int slot, const StageWalk& s) {
-        bulk_load_1d(smem_u32(ring + (size_t)slot * kStage), a.w + ((size_t)s.tile * a.nchunks + s.c) * kWBytes, kWBytes,
+        bulk_load_1d(smem_u32(ring + (size_t)slot * kStage), a.w + ((size_t)s.tile * a.nchunks + s.chunk(a)) * kWBytes, kWBytes,
                      full0 + 8 * slot);
       };
       auto load_x = [&](int slot, const StageWalk& s) {
         const uint32_t dst = smem_u32(ring + (size_t)slot * kStage) + kWBytes;
-        bulk_load_1d(dst, a.xb + (size_t)s.c * kBBytes, kBBytes, full0 + 8 * slot);
-        if (kMLX) bulk_load_1d(dst + kBBytes, a.xtab + (size_t)s.c * (4 * NC), kXBytes, full0 + 8 * slot);
+        const int c = s.chunk(a);
+        if (DBG(2)) return;  // tuning: no activation traffic
+        bulk_load_1d(dst, a.xb + (size_t)c * kBBytes, kBBytes, full0 + 8 * slot);
+        if (kMLX) bulk_load_1d(dst + kBBytes, a.xtab + (size_t)c * (4 * NC), kXBytes, full0 + 8 * slot);
       };
       // The weights do not depend on the kernel in front: fill the ring with them first, then wait
       // for the prepared activations and add the B tiles of those stages.
       int i = 0;
       StageWalk sw0 = sw;
       for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
-        mbar_expect_tx(full0 + 8 * i, kStage);
+        mbar_expect_tx(full0 + 8 * i, DBG(2) ? kWBytes : kStage);
         load_w(i, sw0);
       }
       pdl_wait();
-      for (int j = 0; j < i; ++j, sw.next(a)) load_x(j, sw);
+      TP(if (tr) g_tc_trace[7][2] = clock64();)
+      for (int j = 0; j < i; ++j, sw.next(a)) {
+        load_x(j, sw);
+        TP(if (tr && j < 64) g_tc_trace[0][j] = clock64();)
+      }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
         const int slot = i % S, round = i / S;
         ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 301);
         if (!ok) break;
-        mbar_expect_tx(full0 + 8 * slot, kStage);
+        mbar_expect_tx(full0 + 8 * slot, DBG(2) ? kWBytes : kStage);
         load_w(slot, sw);
         load_x(slot, sw);
+        TP(if (tr && i < 64) g_tc_trace[0][i] = clock64();)
       }
     }
   } else if (warp == kWarpMMA) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // instruction descriptor: D f32, A bf16, B bf16, both K-major, N = NC, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NC >> 3) << 17) | ((128u >> 4) << 24);
-      constexpr uint32_t kLBO = (NC / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
-      const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
-      int du = 0;  // accumulator blocks handed to the epilogue so far
-      for (int i = 0; sw.live(a) && ok; ++i) {
-        const int slot = i % S, ab = i % NA;
-        ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 302);
-        if (ok) ok = mbar_wait(aready0 + 8 * ab, (i / NA) & 1, a.status, 303);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage) + kWBytes;
-        const uint32_t acol = tmemA0 + ab * 128;
+    // The whole warp walks the stages and waits; one elected lane issues.  (Everything the
+    // instructions need is the same in all lanes, which lets it live in uniform registers.)
+    // instruction descriptor: D f32, A bf16, B bf16, both K-major, N = NC, M = 128
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NC >> 3) << 17) | ((128u >> 4) << 24);
+    constexpr uint32_t kLBO = (NC / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
+    const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
+    int du = 0;  // units handed to the epilogue so far
+    for (int i = 0; sw.live(a) && ok; ++i) {
+      const int slot = i % S, ab = i % NA;
+      ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 302);
+      if (ok) ok = mbar_wait(aready0 + 8 * ab, (i / NA) & 1, a.status, 303);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      TP(if (tr && lane == 0 && i < 64) g_tc_trace[1][i] = clock64();)
+      const uint32_t bbase = smem_u32(ring + (size_t)slot * kStage) + kWBytes;
+      const uint32_t acol = tmemA0 + ab * 128;
 #pragma unroll
-        for (int u = 0; u < UPS; ++u, ++du) {
-          const int ds = du % ND;
-          if (du >= ND) {
-            ok = mbar_wait(dfree0 + 8 * ds, (du / ND - 1) & 1, a.status, 304);
-            if (!ok) break;
-            tc_fence_after();
-          }
+      for (int u = 0; u < UPS; ++u, ++du) {
+        const int ds = du % ND;
+        if (du >= ND) {
+          ok = __all_sync(0xffffffffu, mbar_wait(dfree0 + 8 * ds, (du / ND - 1) & 1, a.status, 304));
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (elect_one()) {
+          if (!DBG(4)) {
 #pragma unroll
-          for (int p = 0; p < P; ++p) {
+            for (int p = 0; p < P; ++p) {
 #pragma unroll
-            for (int k = 0; k < KPU; ++k) {
-              const int ks = KPU * u + k;
-              const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + p * (NC * 512) + ks * (NC * 32)) >> 4) & 0x3FFF);
-              umma_bf16_ts(tmemD0 + ds * NC, acol + ks * 8, bdesc, idesc, (p | k) != 0);
+              for (int k = 0; k < 8; ++k) {  // K steps 8u .. 8u+7: the first four into block 0, the others into block 1
+                const int ks = 8 * u + k;
+                const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + p * (NC * 512) + ks * (NC * 32)) >> 4) & 0x3FFF);
+                umma_bf16_ts(tmemD0 + ds * UC + (k >> 2) * NC, acol + ks * 8, bdesc, idesc, (p | (k & 3)) != 0);
+              }
             }
           }
           umma_commit(dfull0 + 8 * ds);
         }
-        if (!ok) break;
+        __syncwarp();
+      }
+      if (!ok) break;
+      if (elect_one()) {
         umma_commit(afree0 + 8 * ab);
         umma_commit(empty0 + 8 * slot);
-        sw.next(a);
       }
+      __syncwarp();
+      TP(if (tr && lane == 0 && i < 64) g_tc_trace[2][i] = clock64();)
+      sw.next(a);
     }
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------------ converters
-    // Two groups of four warps convert alternate stages into their own A buffer; both follow
-    // every stage's full barrier so that no barrier phase is ever skipped.  Thread = row r.
-    const int q4 = warp & 3, grp = warp >> 2;
+    // All eight warps convert every stage, into the A buffer of the stage's parity (the MMAs of one
+    // stage read one buffer while the next stage is written into the other).  Thread = row r of
+    // the tile and one half of the stage's K range.
+    const int q4 = warp & 3, kh = warp >> 2;
     const int r = q4 * 32 + lane;
-    const uint32_t abuf = tmemA0 + ((uint32_t)(q4 * 32) << 16) + grp * 128;
     for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
-      const int slot = i % S;
+      const int slot = i % S, ab = i & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 305));
-      if (!ok) break;
-      if ((i & 1) != grp) continue;
-      if (i >= NA) ok = __all_sync(0xffffffffu, mbar_wait(afree0 + 8 * grp, ((i / NA) - 1) & 1, a.status, 306));
+      if (ok && i >= NA) ok = __all_sync(0xffffffffu, mbar_wait(afree0 + 8 * ab, ((i / NA) - 1) & 1, a.status, 306));
       if (!ok) break;
       tc_fence_after();
+      TP(if (tr && warp == 0 && lane == 0 && i < 64) g_tc_trace[3][i] = clock64();)
       const unsigned char* st = ring + (size_t)slot * kStage;
+      const uint32_t abuf = tmemA0 + ((uint32_t)(q4 * 32) << 16) + ab * 128 + kh * 64;
+      if (DBG(8)) {  // tuning: nothing converted
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(aready0 + 8 * ab);
+          mbar_arrive(empty0 + 8 * slot);
+        }
+        continue;
+      }
       if (kMLX) {
-        // 256 nibbles of the row -> 256 bf16 (16 + n) -> 128 TMEM columns
-        uint4 qv[8];
+        // 128 nibbles of the row -> 128 bf16 (16 + n) -> 64 TMEM columns
+        uint4 qv[4];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
+        for (int u = 0; u < 4; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + (((4 * kh + u) ^ (r & 7)) << 4));
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 4; ++u) {
           const uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
 #pragma unroll
           for (int s2 = 0; s2 < 2; ++s2) {  // a K = 16 step is two packed words
@@ -380,13 +436,13 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
           }
         }
       } else {
-        // 256 E4M3 bytes of the row -> 256 bf16 -> 128 TMEM columns, four 16-byte units at a time
+        // 128 E4M3 bytes of the row -> 128 bf16 -> 64 TMEM columns, four 16-byte units at a time
 #pragma unroll
-        for (int ub = 0; ub < 16; ub += 4) {
+        for (int ub = 0; ub < 8; ub += 4) {
           uint4 qv[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            qv[u] = *reinterpret_cast<const uint4*>(st + r * 256 + ((((ub + u) & 8) | (((ub + u) & 7) ^ (r & 7))) << 4));
+            qv[u] = *reinterpret_cast<const uint4*>(st + r * 256 + (((8 * kh) | ((ub + u) ^ (r & 7))) << 4));
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
@@ -408,23 +464,24 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(aready0 + 8 * grp);
+        mbar_arrive(aready0 + 8 * ab);
         mbar_arrive(empty0 + 8 * slot);
       }
+      TP(if (tr && warp == 0 && lane == 0 && i < 64) g_tc_trace[4][i] = clock64();)
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    // Warp (q4, h): rows 32 q4 .. +31 of the tile, columns h * HC .. + HC - 1 of every block.
-    const int q4 = warp & 3, h = (warp - kConvWarps) >> 2;
+    // Warp (q4, cq): rows 32 q4 .. +31 of the tile, columns cq * HC .. + HC - 1 of every block.
+    // The TMEM load of a stage's next block is in flight while the current one is added up.
+    const int q4 = warp & 3, cq = (warp - kConvWarps) >> 2;
     const int r = q4 * 32 + lane;
     const int et = tid - kConvWarps * 32;
-    const uint32_t dbase = tmemD0 + ((uint32_t)(q4 * 32) << 16) + h * HC;
-    const int mcols = a.batch - h * HC;  // columns of this warp that hold activation rows
+    const uint32_t dbase = tmemD0 + ((uint32_t)(q4 * 32) << 16) + cq * HC;
+    const int mcols = a.batch - cq * HC;  // columns of this warp that hold activation rows
     float2 acc[HC / 2];
 #pragma unroll
     for (int j = 0; j < HC / 2; ++j) acc[j] = make_float2(0.f, 0.f);
     int du = 0;
-    auto load_block = [&](int ds, uint32_t (&t)[HC]) { tmem_ld_cols<HC>(dbase + ds * NC, t); };
     for (int i = 0; sw.live(a) && ok; ++i) {
       const int slot = i % S;
       const unsigned char* st = ring + (size_t)slot * kStage;
@@ -435,42 +492,51 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         const uint4 mv = *reinterpret_cast<const uint4*>(st + kTileRows * 128 + r * 16);
         meta[0] = mv.x, meta[1] = mv.y, meta[2] = mv.z, meta[3] = mv.w;
       }
-      const float4* xs = reinterpret_cast<const float4*>(st + kWBytes + kBBytes) + h * (HC / 4);
+      const float* xs = reinterpret_cast<const float*>(st + kWBytes + kBBytes) + cq * HC;
 #pragma unroll
       for (int u = 0; u < UPS; ++u, ++du) {
         const int ds = du % ND;
         ok = __all_sync(0xffffffffu, mbar_wait(dfull0 + 8 * ds, (du / ND) & 1, a.status, 308));
         if (!ok) break;
         tc_fence_after();
-        uint32_t t[HC];
-        load_block(ds, t);
+        TP(if (tr && et == 0 && u == 0 && i < 64) g_tc_trace[5][i] = clock64();)
+        uint32_t t[2][HC];  // this warp's columns of the unit's two blocks, both loads in flight together
+        tmem_ld_issue<HC>(dbase + ds * UC, t[0]);
+        tmem_ld_issue<HC>(dbase + ds * UC + NC, t[1]);
+        tmem_ld_wait<HC>(t[0]);
+        tmem_ld_wait<HC>(t[1]);
         tc_fence_before();
         warp_arrive(dfree0 + 8 * ds, lane);
-        if (kMLX) {
-          const float sc = __uint_as_float(meta[u] << 16), bi = __uint_as_float(meta[u] & 0xFFFF0000u);
-          const float b16 = fmaf(-16.f, sc, bi);  // the 16 added to every nibble comes out through sum x
-          const float2 sc2 = make_float2(sc, sc), bi2 = make_float2(b16, b16);
 #pragma unroll
-          for (int j = 0; j < HC / 4; ++j) {
-            if (4 * j < mcols) {
-              const float4 xv = xs[u * (NC / 4) + j];
-              fma2(acc[2 * j], sc2, make_float2(__uint_as_float(t[4 * j]), __uint_as_float(t[4 * j + 1])));
-              fma2(acc[2 * j + 1], sc2, make_float2(__uint_as_float(t[4 * j + 2]), __uint_as_float(t[4 * j + 3])));
-              fma2(acc[2 * j], bi2, make_float2(xv.x, xv.y));
-              fma2(acc[2 * j + 1], bi2, make_float2(xv.z, xv.w));
+        for (int b = 0; b < 2; ++b) {
+          const int g = 2 * u + b;  // 64-element group of the stage
+          if (kMLX) {
+            const float sc = __uint_as_float(meta[g] << 16), bi = __uint_as_float(meta[g] & 0xFFFF0000u);
+            const float b16 = fmaf(-16.f, sc, bi);  // the 16 added to every nibble comes out through sum x
+            const float2 sc2 = make_float2(sc, sc), bi2 = make_float2(b16, b16);
+#pragma unroll
+            for (int j = 0; j < HC / 4; ++j) {
+              if (4 * j < mcols) {
+                const float4 xv = *reinterpret_cast<const float4*>(xs + g * NC + 4 * j);
+                fma2(acc[2 * j], sc2, make_float2(__uint_as_float(t[b][4 * j]), __uint_as_float(t[b][4 * j + 1])));
+                fma2(acc[2 * j + 1], sc2, make_float2(__uint_as_float(t[b][4 * j + 2]), __uint_as_float(t[b][4 * j + 3])));
+                fma2(acc[2 * j], bi2, make_float2(xv.x, xv.y));
+                fma2(acc[2 * j + 1], bi2, make_float2(xv.z, xv.w));
+              }
             }
-          }
-        } else {
-          // FP8: the tensor core sums one stage (256 elements); the stages are added here in f32
+          } else {
+            // FP8: the tensor core sums 64 elements per block; the blocks are added here in f32
 #pragma unroll
-          for (int j = 0; j < HC / 2; ++j) {
-            acc[j].x += __uint_as_float(t[2 * j]);
-            acc[j].y += __uint_as_float(t[2 * j + 1]);
+            for (int j = 0; j < HC / 2; ++j) {
+              acc[j].x += __uint_as_float(t[b][2 * j]);
+              acc[j].y += __uint_as_float(t[b][2 * j + 1]);
+            }
           }
         }
       }
       if (!ok) break;
       if (kMLX) warp_arrive(empty0 + 8 * slot, lane);  // scale data and sums of x are no longer needed
+      TP(if (tr && et == 0 && i < 64) g_tc_trace[6][i] = clock64();)
       const bool item_done = sw.last_chunk();
       const int tile = sw.tile, split = sw.split;
       sw.next(a);
@@ -486,7 +552,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       if (a.splits == 1) {
 #pragma unroll
         for (int j = 0; j < HC / 2; ++j) {
-          const int m = h * HC + 2 * j;
+          const int m = cq * HC + 2 * j;
           if (row < a.out_dim) {
             if (m < a.batch) a.out[(size_t)m * a.out_dim + row] = finish(acc[j].x);
             if (m + 1 < a.batch) a.out[(size_t)(m + 1) * a.out_dim + row] = finish(acc[j].y);
@@ -499,7 +565,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         float* part = a.scratch + ((size_t)tile * a.splits + split) * (NC * kTileRows);
 #pragma unroll
         for (int j = 0; j < HC / 2; ++j) {
-          const int m = h * HC + 2 * j;
+          const int m = cq * HC + 2 * j;
           if (m < a.batch) part[m * kTileRows + r] = acc[j].x;
           if (m + 1 < a.batch) part[(m + 1) * kTileRows + r] = acc[j].y;
           acc[j] = make_float2(0.f, 0.f);
@@ -511,7 +577,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         if (*last_flag) {
           __threadfence();
           const float* base = a.scratch + (size_t)tile * a.splits * (NC * kTileRows);
-          for (int m = h * HC; m < h * HC + HC && m < a.batch; ++m) {
+          for (int m = cq * HC; m < cq * HC + HC && m < a.batch; ++m) {
             float sum = 0.f;
             for (int s2 = 0; s2 < a.splits; ++s2) sum += __ldcg(base + (size_t)s2 * (NC * kTileRows) + m * kTileRows + r);
             if (row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum);
@@ -522,7 +588,8 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       }
     }
   }
-
+  TP(if (tr && tid == 0) g_tc_trace[7][1] = clock64();)
+  TP(if (tid == 0) atomicMax(&g_tc_span[2], gtime());)
   // ---- wind down: everyone meets, outstanding copies are drained, TMEM is returned ----
   tc_fence_before();
   __syncthreads();
@@ -612,6 +679,9 @@ int tc_choose_splits(int ntiles, int nchunks, int sms, int max_items, float fix_
 
 namespace {
 
+int g_rotate = 1;  // see StageWalk::chunk
+int g_dbg = 0;     // tuning build only
+
 struct GemmDesc {
   const unsigned char* tiled;
   const float* scale;
@@ -649,6 +719,8 @@ int launch_pass(const GemmDesc& w, float* out, const void* x, int nb, GemmBufs* 
   if (stages > 8) stages = 8;
   if (stages < 2) return fail(GOPH_E_UNSUPPORTED, "small-batch tensor-core path: a stage of %d bytes leaves no room for a ring", SM::kStage);
   a.stages = stages;
+  a.rotate = g_rotate;
+  a.dbg = g_dbg;
   size_t smem = SM::bytes(stages);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM (the kernel owns all of TMEM)
 
@@ -786,6 +858,28 @@ int tc_fp8_dequant_tiled(const goph_fp8_linear* w, float* out, cudaStream_t stre
   return GOPH_OK;
 }
 
+#ifdef GOPH_TUNING
+void tc_gemm_tuning_set(int dbg, int rotate) {
+  g_dbg = dbg;
+  g_rotate = rotate;
+}
+int tc_gemm_span(unsigned long long* out4, int reset) {
+  if (reset) {
+    const unsigned long long init[4] = {~0ull, 0ull, 0ull, ~0ull};
+    return cudaMemcpyToSymbol(g_tc_span, init, sizeof init) == cudaSuccess ? 0 : -1;
+  }
+  return cudaMemcpyFromSymbol(out4, g_tc_span, 4 * sizeof(unsigned long long)) == cudaSuccess ? 0 : -1;
+}
+int tc_gemm_probe(long long* out64) {
+  return cudaMemcpyFromSymbol(out64, g_tc_trace, 8 * 64 * sizeof(long long)) == cudaSuccess ? 0 : -1;
+}
+#endif
+
+void tc_gemm_status_clear(int device) {
+  GemmBufs* b = gemm_bufs(device, false);
+  if (b) cudaMemset(b->status, 0, sizeof(int));
+}
+
 int tc_gemm_status(int device) {
   GemmBufs* b = gemm_bufs(device, false);
   if (!b) return 0;  // no small-batch product has run on this device
@@ -795,3 +889,12 @@ int tc_gemm_status(int device) {
 }
 
 }  // namespace goph
+
+#ifdef GOPH_TUNING
+GOPH_API int goph_tuning_probe(long long* out64) { return goph::tc_gemm_probe(out64); }
+GOPH_API int goph_tuning_span(unsigned long long* out4, int reset) { return goph::tc_gemm_span(out4, reset); }
+GOPH_API int goph_tuning_set(int dbg, int rotate) {
+  goph::tc_gemm_tuning_set(dbg, rotate);
+  return 0;
+}
+#endif

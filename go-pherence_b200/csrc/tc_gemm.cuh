@@ -25,5 +25,6 @@ int tc_fp8_dequant_tiled(const goph_fp8_linear* w, float* out, cudaStream_t stre
 int tc_choose_splits(int ntiles, int nchunks, int sms, int max_items, float fix_cost);
 // Device status word of the small-batch kernels (0 = every wait completed).
 int tc_gemm_status(int device);
+void tc_gemm_status_clear(int device);
 
 }  // namespace goph

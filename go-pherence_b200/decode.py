@@ -89,8 +89,12 @@ class MLXDecoder:
     def _sub(self, buf, off, n):
         return self.rt.wrap(buf.Ptr + 4 * off, 4 * n)
 
-    def step(self, stream=None):
-        """One token: embed the current token, the layer stack, logits, pick and advance.  Where the
+    def step(self, stream=None, dump=None):
+        """dump: optional list (plain launches only, not inside a graph capture) that receives
+        ("layer<l>.hidden", f32 array) after every layer -- the labelled-tensor hook the reference's
+        loop has for layer-by-layer comparison (debugLayerHook, model/gpu_forward.go:883-1542).
+
+        One token: embed the current token, the layer stack, logits, pick and advance.  Where the
         weights allow it (row-major layout: projections under 8 Mi weights) the residual add + RMSNorm
         in front of q|k|v and gate|up and the SiLU*up in front of down run inside the product's launch
         (goph_mlx_gemv_pre); otherwise as separate launches."""
@@ -130,7 +134,7 @@ class MLXDecoder:
                                    c.heads, c.kv_heads, c.head_dim, self.scale, c.eps, stream)
                 n += 1
             else:
-                rt.QKNormRoPEAppend(q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.heads, c.kv_heads,
+                rt.QKNormRoPEAppend(q, k, v, e["q_norm"], e["k_norm"], self.table, self.pos, e["kc"], e["vc"], c.max_seq, c.heads, c.kv_heads,
                                     c.head_dim, c.eps, stream)
                 rt.AttnDecode(self.attn, q, e["kc"], e["vc"], self.pos, c.max_seq, c.heads, c.kv_heads, c.head_dim, self.scale, stream)
                 n += 2
@@ -149,6 +153,11 @@ class MLXDecoder:
                 rt.GemvMLX(self.proj2, self.act, e["down"], stream)
                 n += 4
             prev = self.proj2
+            if dump is not None:
+                # the residual stream after this layer is cur + prev (the add itself runs inside the
+                # next layer's first launch); an f32 add on the host gives the same bits
+                rt.Sync()
+                dump.append(("layer%d.hidden" % len(dump), cur.Download(c.hidden) + prev.Download(c.hidden)))
         rt.AddRMSNorm(None, self.normed, cur, prev, self.final_norm, c.hidden, 1, c.eps, stream)
         rt.GemvMLX(self.logits, self.normed, self.lm, stream)
         rt.ArgmaxAdvance(self.logits, c.vocab, self.tok, self.pos, self.history, self.forced, c.max_seq, stream)
@@ -173,9 +182,10 @@ class MLXDecoder:
             self.step(torch.cuda.current_stream())
         return self.graph
 
-    def generate(self, prompt, max_new, use_graph=True, logits_at=None):
+    def generate(self, prompt, max_new, use_graph=True, logits_at=None, logits_all=None):
         """Returns prompt + max_new greedy tokens.  logits_at: optional list that receives the logits
-        (numpy) that chose each generated token."""
+        (numpy) that chose each generated token; logits_all: the logits of every position, prompt
+        positions included."""
         c = self.cfg
         total = len(prompt) + max_new
         if total > c.max_seq:
@@ -192,6 +202,9 @@ class MLXDecoder:
             if logits_at is not None and i >= len(prompt) - 1:
                 self.rt.Sync()
                 logits_at.append(self.logits.Download())
+            if logits_all is not None:
+                self.rt.Sync()
+                logits_all.append(self.logits.Download())
         self.rt.Sync()
         hist = self.history.Download(c.max_seq, dtype=np.int32)
         return [int(t) for t in hist[:total]]

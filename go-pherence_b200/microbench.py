@@ -30,6 +30,10 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
     rt.init(0)
+    tune = dict((k, v) for k, v in opts if k.startswith("tune_"))
+    opts = [(k, v) for k, v in opts if not k.startswith("tune_")]
+    if tune:  # tuning build only: parts of the small-batch kernel left out / chunk rotation off
+        rt.lib().goph_tuning_set(int(tune.get("tune_dbg", 0)), int(tune.get("tune_rotate", 1)))
     for k, v in opts:
         rt.SetOption(k, v)
     nbytes = algorithmic_bytes(fmt, out_dim, in_dim, batch)
@@ -112,6 +116,15 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     res = {"format": fmt, "out": out_dim, "in": in_dim, "batch": batch, "x": "bf16" if xbf16 else "f32", "tflops": round(tflops, 1), "opts": dict(opts), "copies": copies, "chain": bool(chain),
            "us_per_launch": round(us, 3), "GBps": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peak, 4),
            "bytes": nbytes}
+    if hasattr(rt.lib(), "goph_tuning_probe"):  # tuning build: clock64 timeline of one CTA's last launch
+        import ctypes
+        buf = (ctypes.c_longlong * 512)()
+        rt.lib().goph_tuning_probe(buf)
+        t0 = buf[7 * 64]
+        names = ["loads_issued", "mma_sees_stage", "mma_issued", "conv_starts", "conv_done", "epi_sees_unit0", "epi_done"]
+        res["trace"] = {"end": buf[7 * 64 + 1] - t0, "pdl_wait_done": buf[7 * 64 + 2] - t0}
+        for e, n in enumerate(names):
+            res["trace"][n] = [buf[e * 64 + i] - t0 for i in range(20) if buf[e * 64 + i]]
     for h in handles:
         h.Free()
     return res
@@ -149,9 +162,6 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
     x = torch.from_numpy(syn.activations("moe-bench", tokens * hidden)).cuda()
     out = torch.empty(tokens * hidden, dtype=torch.float32, device="cuda")
     xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
-    if xbf16:  # the activations as bf16 in device memory (the bf16 entry points, tensor-core layouts only)
-        x16 = x.to(torch.bfloat16)
-        xb = rt.wrap(x16.data_ptr(), x16.numel() * 2)
     stream = torch.cuda.current_stream()
     distinct = []
     for m in mods:

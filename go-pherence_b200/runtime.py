@@ -23,7 +23,7 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 
 # Every symbol include/goph_b200.h declares.
 EXPORTS = [
-    "goph_init", "goph_set_option", "goph_kernel_status", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_init", "goph_set_option", "goph_kernel_status", "goph_kernel_status_clear", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
     "goph_mlx_program_create", "goph_mlx_program_create_pre", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free",
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
@@ -58,10 +58,11 @@ def lib():
     """The loaded C-ABI library.  Raises if it has not been built: there is no fallback."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("GOPH_B200_LIB") or LIB_PATH  # the tuning build of the same library, when asked for
+        if not os.path.exists(path):
             raise GophError(-1, "libgoph_b200.so is not built (run __graft_entry__.build()); "
                                 "there is no CPU or PyTorch fallback")
-        L = C.CDLL(LIB_PATH)
+        L = C.CDLL(path)
         L.goph_last_error.restype = C.c_char_p
         for name in ("goph_mlx_resident_bytes", "goph_gguf_resident_bytes", "goph_fp8_resident_bytes", "goph_gptq_resident_bytes"):
             getattr(L, name).restype = C.c_uint64
@@ -109,6 +110,10 @@ def KernelStatus():
     v = C.c_int(0)
     _check(lib().goph_kernel_status(_device, C.byref(v)))
     return v.value
+
+
+def KernelStatusClear():
+    _check(lib().goph_kernel_status_clear(_device))
 
 
 def SMCount():
@@ -753,9 +758,9 @@ def AddRMSNorm(hidden, normed, a, b, weight, n, rows=1, eps=1e-6, stream=None):
                                   C.c_float(eps), _stream_ptr(stream)))
 
 
-def QKNormRoPEAppend(q, k, v, qNorm, kNorm, ropeTable, pos, kCache, vCache, heads, kvHeads, headDim, eps=1e-6, stream=None):
+def QKNormRoPEAppend(q, k, v, qNorm, kNorm, ropeTable, pos, kCache, vCache, maxSeq, heads, kvHeads, headDim, eps=1e-6, stream=None):
     _check(lib().goph_qk_norm_rope_append(_device, _ptr(q), _ptr(k), _ptr(v), _ptr(qNorm), _ptr(kNorm), _ptr(ropeTable),
-                                          _ptr(pos), _ptr(kCache), _ptr(vCache), int(heads), int(kvHeads), int(headDim),
+                                          _ptr(pos), _ptr(kCache), _ptr(vCache), int(maxSeq), int(heads), int(kvHeads), int(headDim),
                                           C.c_float(eps), _stream_ptr(stream)))
 
 

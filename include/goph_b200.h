@@ -100,6 +100,9 @@ int goph_set_option(const char* name, int value);
  * after every launch under GO_PHERENCE_CUDA_LAUNCH_CHECK, runtime/runtime.go:687-694.)
  * Synchronises with the device. */
 int goph_kernel_status(int device, int* out_status);
+/* Sets the device's status words back to 0 after the caller has dealt with a non-zero status
+ * (the reference has no counterpart: it tears the context down).  Synchronises with the device. */
+int goph_kernel_status_clear(int device);
 /* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
 int goph_malloc(int device, uint64_t bytes, void** out_dev);
 int goph_free(int device, void* dev);
@@ -321,11 +324,13 @@ int goph_add_rmsnorm(int device, float* hidden_dev, float* normed_dev, const flo
 /* Per head: optional QK RMSNorm (Qwen3, model/llama.go:1105-1127), RoPE with the table row of
  * *pos_dev (kernels.ApplyRoPE, backends/simd/kernels/rope.go:29-44; table [max_seq][head_dim/2][cos,sin]
  * as simd.BuildRoPEFreqs makes it); q in place, k and v into row *pos_dev of the caches
- * [max_seq][kv_heads*head_dim] (model/llama.go:1150-1160). */
+ * [max_seq][kv_heads*head_dim] (model/llama.go:1150-1160).  A position outside [0, max_seq) leaves
+ * q and the caches untouched and sets the device status word (goph_kernel_status) to 401; the
+ * attention entry points below do the same with 402. */
 int goph_qk_norm_rope_append(int device, float* q_dev, const float* k_dev, const float* v_dev,
                              const float* q_norm_dev, const float* k_norm_dev, const float* rope_table_dev,
-                             const int* pos_dev, float* kcache_dev, float* vcache_dev, int heads, int kv_heads,
-                             int head_dim, float eps, void* stream);
+                             const int* pos_dev, float* kcache_dev, float* vcache_dev, int max_seq, int heads,
+                             int kv_heads, int head_dim, float eps, void* stream);
 /* simd.GQAAttentionScaleInto over positions 0..*pos_dev (backends/simd/runtime/attention.go:82-113). */
 int goph_attn_decode(int device, float* out_dev, const float* q_dev, const float* kcache_dev,
                      const float* vcache_dev, const int* pos_dev, int max_seq, int heads, int kv_heads,

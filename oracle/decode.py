@@ -154,8 +154,10 @@ class OracleDecoder:
         self.vc = [np.zeros((cfg.max_seq, kvd), dtype=F) for _ in range(cfg.layers)]
         self.scale = F(1.0 / math.sqrt(cfg.head_dim))
 
-    def step(self, tok, pos):
-        """One token through the stack; returns the logits."""
+    def step(self, tok, pos, dump=None):
+        """One token through the stack; returns the logits.  dump: optional list that receives
+        (label, f32 array) after every layer, the labelled-tensor hook of the reference's loop
+        (debugLayerHook, model/llama.go:933-1437)."""
         c, w = self.cfg, self.w
         hidden = w.embedding(tok).astype(F)
         for l in range(c.layers):
@@ -176,15 +178,20 @@ class OracleDecoder:
             hidden = rmsnorm(hidden, w.norm(l, "post_norm"), c.eps)
             act = silu_mul(w.proj(l, "gate", hidden), w.proj(l, "up", hidden))
             hidden = residual + w.proj(l, "down", act.astype(F))
+            if dump is not None:
+                dump.append(("layer%d.hidden" % l, hidden.astype(F).copy()))
         hidden = rmsnorm(hidden, w.final_norm, c.eps)
         return w.logits(hidden.astype(F))
 
-    def generate(self, prompt, max_new, trace=None):
-        """LlamaModel.Generate with Tok == nil: prompt tokens one by one, then greedy tokens."""
+    def generate(self, prompt, max_new, trace=None, all_logits=None):
+        """LlamaModel.Generate with Tok == nil: prompt tokens one by one, then greedy tokens.
+        all_logits: optional list that receives the logits of every position, prompt included."""
         out = list(prompt)
         logits = None
         for pos, tok in enumerate(prompt):
             logits = self.step(tok, pos)
+            if all_logits is not None:
+                all_logits.append(logits.copy())
         for i in range(max_new):
             nxt = argmax_first(logits)
             if trace is not None:
@@ -193,4 +200,6 @@ class OracleDecoder:
             out.append(nxt)
             if i + 1 < max_new:
                 logits = self.step(nxt, len(out) - 1)
+                if all_logits is not None:
+                    all_logits.append(logits.copy())
         return out

@@ -64,7 +64,7 @@ def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, 
         if fused:
             gpu.AttnDecodeFused(out, Q, K, V, QN, KN, T, pos_buf, kc, vc, max_seq, heads, kv_heads, head_dim, scale, 1e-6)
         else:
-            gpu.QKNormRoPEAppend(Q, K, V, QN, KN, T, pos_buf, kc, vc, heads, kv_heads, head_dim, 1e-6)
+            gpu.QKNormRoPEAppend(Q, K, V, QN, KN, T, pos_buf, kc, vc, max_seq, heads, kv_heads, head_dim, 1e-6)
             gpu.AttnDecode(out, Q, kc, vc, pos_buf, max_seq, heads, kv_heads, head_dim, scale)
         if pos in checks:
             gpu.Sync()
@@ -84,6 +84,41 @@ def test_qk_norm_rope_append_and_attention(gpu, pkg, heads, kv_heads, head_dim, 
             assert np.allclose(out.Download(), want, rtol=1e-4, atol=2e-5)
         for t in (Q, K, V):
             t.Free()
+
+
+@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("bad_pos", [16, -1, 1 << 20])
+def test_position_outside_the_cache_is_refused(gpu, pkg, fused, bad_pos):
+    """A step replayed once more than the cache holds (or a stale position word) must not write out of
+    bounds: the kernels leave q, the caches and out untouched and record 401 / 402 in the status word."""
+    heads, kv_heads, head_dim, max_seq = 4, 2, 64, 16
+    kvd = kv_heads * head_dim
+    g = pkg.synth.rng("badpos")
+    T = gpu.from_numpy(od.rope_table(max_seq, head_dim, 1e6).reshape(-1))
+    kc, vc = gpu.Malloc(max_seq * kvd + 64), gpu.Malloc(max_seq * kvd + 64)
+    sentinel = np.full(max_seq * kvd + 64, 123.0, dtype=F)
+    kc.Upload(sentinel); vc.Upload(sentinel)
+    q = g.standard_normal(heads * head_dim, dtype=F)
+    Q, K, V = gpu.from_numpy(q), gpu.from_numpy(g.standard_normal(kvd, dtype=F)), gpu.from_numpy(g.standard_normal(kvd, dtype=F))
+    out = gpu.Malloc(heads * head_dim)
+    out.Upload(np.full(heads * head_dim, 7.0, dtype=F))
+    pos_buf = gpu.from_numpy(np.array([bad_pos], dtype=np.int32))
+    assert gpu.KernelStatus() == 0
+    try:
+        if fused:
+            gpu.AttnDecodeFused(out, Q, K, V, None, None, T, pos_buf, kc, vc, max_seq, heads, kv_heads, head_dim, 0.125, 1e-6)
+        else:
+            gpu.QKNormRoPEAppend(Q, K, V, None, None, T, pos_buf, kc, vc, max_seq, heads, kv_heads, head_dim, 1e-6)
+            gpu.AttnDecode(out, Q, kc, vc, pos_buf, max_seq, heads, kv_heads, head_dim, 0.125)
+        gpu.Sync()
+        assert gpu.KernelStatus() == (402 if fused else 401)
+        assert np.array_equal(kc.Download(), sentinel) and np.array_equal(vc.Download(), sentinel)
+        assert np.array_equal(Q.Download(), q) and np.all(out.Download() == 7.0)
+    finally:
+        gpu.KernelStatusClear()
+    assert gpu.KernelStatus() == 0
+    for t in (T, kc, vc, Q, K, V, out, pos_buf):
+        t.Free()
 
 
 def test_silu_mul_argmax_embed(gpu, pkg):
@@ -126,17 +161,21 @@ def test_silu_mul_argmax_embed(gpu, pkg):
         h.Free()
 
 
-def build_model(pkg, cfg, key):
+def build_model(pkg, cfg, key, centred=False):
     syn = pkg.synth
     g = syn.rng("decode", key)
     shapes = {"q": (cfg.heads * cfg.head_dim, cfg.hidden), "k": (cfg.kv_heads * cfg.head_dim, cfg.hidden),
               "v": (cfg.kv_heads * cfg.head_dim, cfg.hidden), "o": (cfg.hidden, cfg.heads * cfg.head_dim),
               "gate": (cfg.inter, cfg.hidden), "up": (cfg.inter, cfg.hidden), "down": (cfg.hidden, cfg.inter)}
+    def mlx(wsb):
+        # centred: bias = -7.5 * scale (bf16) instead of -8 * scale, i.e. weights of zero mean
+        return (wsb[0], wsb[1], syn.bf16_round(F(-7.5) * wsb[1])) if centred else wsb
+
     layers_gpu, layers_orc = [], []
     for l in range(cfg.layers):
         dg, do = {}, {}
         for name, (o, i) in shapes.items():
-            w = syn.mlx_weight((key, name, l % 4), o, i, 64)   # four distinct sets of layer weights
+            w = mlx(syn.mlx_weight((key, name, l % 4), o, i, 64))   # four distinct sets of layer weights
             dg[name] = w
             do[name] = (w, o, i)
         for name, n in (("input_norm", cfg.hidden), ("post_norm", cfg.hidden), ("q_norm", cfg.head_dim), ("k_norm", cfg.head_dim)):
@@ -144,28 +183,76 @@ def build_model(pkg, cfg, key):
             dg[name] = do[name] = v
         layers_gpu.append(dg)
         layers_orc.append(do)
-    lm = syn.mlx_weight((key, "lm"), cfg.vocab, cfg.hidden, 64)
+    lm = mlx(syn.mlx_weight((key, "lm"), cfg.vocab, cfg.hidden, 64))
     final_norm = (F(1) + F(0.1) * g.standard_normal(cfg.hidden, dtype=F)).astype(F)
     return layers_gpu, layers_orc, lm, final_norm
 
 
-def run_gate(gpu, pkg, cfg, key, prompt_len, max_new):
-    layers_gpu, layers_orc, lm, final_norm = build_model(pkg, cfg, key)
+LOGIT_TOL = 2e-3   # max |logit_gpu - logit_oracle| / max |logit_oracle| allowed at any position
+
+
+def run_gate(gpu, pkg, cfg, key, prompt_len, max_new, centred=False):
+    """Greedy decode on the GPU against the restated CPU loop: tokens, and the logits of EVERY
+    position (prompt positions included).  Returns the statistics the assertions and the report use."""
+    layers_gpu, layers_orc, lm, final_norm = build_model(pkg, cfg, key, centred)
     prompt = [int(t) for t in pkg.synth.rng("prompt", key).integers(0, cfg.vocab, prompt_len)]
     oracle = od.OracleDecoder(cfg, od.MLXWeights(orc, cfg, layers_orc, lm, final_norm, nthreads=16))
-    trace = []
-    want = oracle.generate(prompt, max_new, trace=trace)
+    trace, ref_logits, got_logits = [], [], []
+    want = oracle.generate(prompt, max_new, trace=trace, all_logits=ref_logits)
     dec = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta))
-    got = dec.generate(prompt, max_new)
-    margins = [m for _, m, _ in trace]
+    got = dec.generate(prompt, max_new, logits_all=got_logits)
     assert gpu.KernelStatus() == 0
-    return want, got, margins, dec
+    assert len(got_logits) == len(ref_logits) == prompt_len + max_new - 1
+    margins = [m for _, m, _ in trace]
+    # positions whose inputs are the same on both sides: everything up to the first differing token
+    same = next((i for i, (x, y) in enumerate(zip(got, want)) if x != y), len(want))
+    npos = min(len(ref_logits), same)
+    errs, top5_bad = [], 0
+    for p in range(npos):
+        r, g = ref_logits[p], got_logits[p]
+        d = float(np.max(np.abs(g - r)))
+        errs.append(d / float(np.max(np.abs(r))))
+        t6 = np.sort(np.partition(r, -6)[-6:])
+        if t6[1] - t6[0] > 4 * d:   # the 5th and 6th largest are further apart than the error
+            top5_bad += set(np.argpartition(r, -5)[-5:].tolist()) != set(np.argpartition(g, -5)[-5:].tolist())
+    stats = {"positions_compared": npos, "max_logit_err": max(errs), "min_margin": min(margins),
+             "median_margin": float(np.median(margins)), "distinct_generated": len(set(want[prompt_len:])),
+             "first_difference": None if same == len(want) else same, "top5_mismatches": top5_bad}
+    print("decode gate %s%s: %s" % (key, " (centred)" if centred else "", stats))
+    assert stats["max_logit_err"] <= LOGIT_TOL, stats
+    assert top5_bad == 0, stats
+    if same < len(want):
+        # a different token is only acceptable at a near tie: the oracle's margin at that step within
+        # four times the logit error measured there
+        step = same - prompt_len
+        r, g = ref_logits[same - 1], got_logits[same - 1]
+        assert margins[step] <= 4 * float(np.max(np.abs(g - r))), (stats, margins[step])
+    return want, got, stats, dec
+
+
+def layer_states(gpu, pkg, cfg, key, prompt_len, pos, centred=False):
+    """The residual stream after every layer at position `pos` of the prompt, GPU against the restated
+    CPU loop: the layer-by-layer comparison the reference does with its labelled-tensor hooks."""
+    layers_gpu, layers_orc, lm, final_norm = build_model(pkg, cfg, key, centred)
+    prompt = [int(t) for t in pkg.synth.rng("prompt", key).integers(0, cfg.vocab, prompt_len)]
+    oracle = od.OracleDecoder(cfg, od.MLXWeights(orc, cfg, layers_orc, lm, final_norm, nthreads=16))
+    ref = []
+    for p in range(pos + 1):
+        oracle.step(prompt[p], p, dump=ref if p == pos else None)
+    dec = pkg.decode.MLXDecoder(gpu, cfg, layers_gpu, lm, final_norm, od.rope_table(cfg.max_seq, cfg.head_dim, cfg.theta))
+    dec.reset(prompt)
+    got = []
+    for p in range(pos + 1):
+        dec.step(None, dump=got if p == pos else None)
+    gpu.Sync()
+    assert [n for n, _ in got] == [n for n, _ in ref] and len(ref) == cfg.layers
+    return [float(np.max(np.abs(g - r)) / np.max(np.abs(r))) for (_, g), (_, r) in zip(got, ref)]
 
 
 def test_greedy_tokens_small_model(gpu, pkg):
     cfg = od.DecodeConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, inter=1024, vocab=4096, max_seq=64)
-    want, got, margins, dec = run_gate(gpu, pkg, cfg, "small", 12, 40)
-    assert got == want, (got, want, min(margins))
+    want, got, stats, dec = run_gate(gpu, pkg, cfg, "small", 12, 40)
+    assert got == want, stats
     again = dec.generate(want[:12], 40, use_graph=False)     # plain launches give the same tokens as the graph
     assert again == want
     # the same model with norm / activation as separate launches instead of inside the products
@@ -174,6 +261,18 @@ def test_greedy_tokens_small_model(gpu, pkg):
     assert dec.fused and not plain.fused and plain.launches_per_step == 0
     assert plain.generate(want[:12], 40) == want
     assert plain.launches_per_step > dec.launches_per_step
+
+
+def test_greedy_tokens_vary_small_model(gpu, pkg):
+    """Biases of -7.5 * scale centre the weights, and the greedy sequence then changes from step to step
+    with top-2 margins of a few hundredths: a decoder that is off by more than rounding fails here."""
+    cfg = od.DecodeConfig(hidden=512, layers=3, heads=8, kv_heads=4, head_dim=64, inter=1024, vocab=4096, max_seq=64)
+    want, got, stats, _ = run_gate(gpu, pkg, cfg, "small", 12, 40, centred=True)
+    assert stats["distinct_generated"] >= 16, stats
+    assert got == want or stats["first_difference"] is not None
+    errs = layer_states(gpu, pkg, cfg, "small", 12, 9, centred=True)
+    print("residual stream after each layer at position 9, max relative difference:", ["%.2e" % e for e in errs])
+    assert max(errs) <= 1e-3, errs
 
 
 def test_gemv_with_operation_in_front(gpu, pkg):
@@ -210,14 +309,31 @@ def test_gemv_with_operation_in_front(gpu, pkg):
     h.Free(); ht.Free()
 
 
+QWEN3_0_6B = dict(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
+                  eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
+
+
 def test_greedy_tokens_qwen3_0_6b(gpu, pkg):
-    """BASELINE config 1: random-init Qwen3-0.6B architecture in MLX 4-bit, 128-token random prompt,
-    64 greedy tokens identical to the restatement of the reference's CPU loop."""
-    cfg = od.DecodeConfig(hidden=1024, layers=28, heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
-                          eps=1e-6, theta=1e6, qk_norm=True, max_seq=192)
-    want, got, margins, _ = run_gate(gpu, pkg, cfg, "qwen3-0.6b", 128, 64)
-    print("top-2 logit margins of the 64 chosen tokens: min %.3e median %.3e" % (min(margins), float(np.median(margins))))
-    assert got == want, ([i for i, (a, b) in enumerate(zip(got, want)) if a != b][:3], min(margins))
+    """Random-init Qwen3-0.6B architecture in MLX 4-bit g64 (bias = -8 * scale), 128-token random
+    prompt, 64 greedy tokens: identical to the restatement of the reference's CPU loop, and the logits
+    of all 191 positions within LOGIT_TOL of its logits."""
+    cfg = od.DecodeConfig(**QWEN3_0_6B)
+    want, got, stats, _ = run_gate(gpu, pkg, cfg, "qwen3-0.6b", 128, 64)
+    assert got == want, stats
+    assert stats["positions_compared"] == 191
+
+
+def test_greedy_tokens_vary_qwen3_0_6b(gpu, pkg):
+    """The same architecture with centred weights (bias = -7.5 * scale): the 64 greedy tokens vary, the
+    logits of every position are compared, and the residual stream after each of the 28 layers at a
+    mid-prompt position is compared layer by layer."""
+    cfg = od.DecodeConfig(**QWEN3_0_6B)
+    want, got, stats, _ = run_gate(gpu, pkg, cfg, "qwen3-0.6b", 128, 64, centred=True)
+    assert stats["distinct_generated"] >= 16, stats
+    errs = layer_states(gpu, pkg, cfg, "qwen3-0.6b", 128, 40, centred=True)
+    print("residual stream after each layer at position 40, max relative difference: first %.2e last %.2e max %.2e"
+          % (errs[0], errs[-1], max(errs)))
+    assert max(errs) <= 1e-3, errs
 
 
 def test_product_lists_change_nothing(gpu, pkg):
