@@ -38,10 +38,10 @@ HIDDEN, LAYERS, VOCAB, FFN, QKV, GS = 4096, 32, 128256, 14336, 6144, 64
 LAYER_OPS = [("qkv", QKV, HIDDEN), ("o", HIDDEN, HIDDEN), ("gate_up", 2 * FFN, HIDDEN), ("down", HIDDEN, FFN)]
 WORKLOAD = ("llama-3-8b mlx4-g64 decode-step projections as a dependent chain (32 layers x q|k|v 6144x4096, o 4096x4096, "
             "gate|up 28672x4096, down 4096x14336 + LM head 128256x4096), batch 1")
-# Share of the step's kernel time spent in mlx_mma_kernel (the rest is its activation-preparation
-# launch), and DRAM bytes over algorithmic bytes of that kernel, both from the ncu captures
-# summarised under profiles/.
-MMA_SHARE = 0.93
+# Share of the step's kernel time spent in mlx_mma_kernel (it prepares its own activation digits,
+# so a product is this one launch), and DRAM bytes over algorithmic bytes of that kernel, both from
+# the ncu captures summarised under profiles/.
+MMA_SHARE = 1.0
 MMA_TRAFFIC_RATIO = 1.031
 
 
@@ -114,12 +114,13 @@ def chain_ops(layers):
 def chain_weight(syn, name, l, out_dim, in_dim):
     """Every layer of a random-init model has its own weights; generation is the slow part on the
     host, so layers draw from 4 distinct seeds per projection (contents never repeat in L2: the
-    copies are separate device buffers).  Scales and biases are quartered (exactly: they are bf16
-    values) so that the chained activations stay finite."""
+    copies are separate device buffers).  Scales and biases are divided by 8 or 16 (exactly: they
+    are bf16 values) so that the chained activations neither overflow nor vanish over 129 products."""
     key = (name, l % 4)
     if key not in chain_weight.cache:
         w, s, b = syn.mlx_weight(("chain",) + key, out_dim, in_dim, GS)
-        chain_weight.cache[key] = (w, s * np.float32(0.25), b * np.float32(0.25))
+        m = np.float32(0.125 if in_dim <= 4096 else 0.0625)  # keeps a layer's gain a little under one
+        chain_weight.cache[key] = (w, s * m, b * m)
     return chain_weight.cache[key]
 
 
@@ -155,12 +156,12 @@ class DecodeStepProjections:
             self.bytes_per_step += algorithmic_bytes(hi - lo, in_dim)
             self.ops.append((name, h, x, out, (hi - lo, in_dim), (lo, out_dim)))
             prev_out = out
-        self.launches_per_step = len(self.ops) * (2 + (1 if world > 1 and gather == "p2p" else 0))
+        self.launches_per_step = len(self.ops) * (1 + (1 if world > 1 and gather == "p2p" else 0))
         self.exchange = None
         if world > 1:
             import torch.distributed as dist
             if gather == "p2p":
-                self.exchange = rt.Gather(rank, world, VOCAB + 64)
+                self.exchange = rt.Gather(rank, world, max(VOCAB + 64, world * 32 * 2048))  # logits, or the MoE partial sums of 32 tokens
                 handles = [torch.zeros(64, dtype=torch.uint8, device="cuda") for _ in range(world)]
                 mine = torch.tensor(list(self.exchange.Export()), dtype=torch.uint8, device="cuda")
                 dist.all_gather(handles, mine)
@@ -575,7 +576,10 @@ def run_ours(args):
     if world > 1 and p2p and not args.no_extra:
         for op in wl.ops:  # make room: the chain's weights are not needed any more
             op[1].Free()
-        moe = moe_sharded(rt, syn, pkg.sharding, wl.exchange, rank, world, dist)
+        try:
+            moe = moe_sharded(rt, syn, pkg.sharding, wl.exchange, rank, world, dist)
+        except Exception as e:  # the headline stands without it
+            moe = {"error": str(e)[:200]}
 
     if rank == 0:
         gbs = job_bytes * timed_steps / (ms_total * 1e-3) / 1e9

@@ -23,6 +23,10 @@ FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std
 FLAGS = [f for f in FLAGS if f != "--use_fast_math=false"]  # precise math only
 if TUNING:
     FLAGS.append("-DGOPH_TUNING")
+    if os.environ.get("GOPH_SPIN_NS"):
+        FLAGS.append("-DGOPH_SPIN_NS=" + os.environ["GOPH_SPIN_NS"])
+        OBJ += "_spin"
+        LIB = LIB.replace("_tuning", "_tuning_spin")
 
 
 def _sources():
@@ -62,7 +66,7 @@ def build(force=False, verbose=False):
     objs = [o for o, _ in results]
     if any(changed for _, changed in results) or not os.path.exists(LIB):
         cmd = [NVCC, "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-o", LIB, *objs]
+               "-o", LIB, *objs, "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))

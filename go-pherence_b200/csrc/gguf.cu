@@ -644,6 +644,32 @@ GOPH_API int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_
   return stream_launch<Q80Fmt>(a, m->device, batch, (cudaStream_t)stream, force_rows);
 }
 
+GOPH_API int goph_gguf_project_pair(float* out_a_dev, uint64_t out_a_len, float* out_b_dev, uint64_t out_b_len,
+                                    const float* x_dev, uint64_t x_len, int batch, const goph_gguf_matrix* a,
+                                    const goph_gguf_matrix* b, void* stream) {
+  clear_error();
+  if (!valid_gguf(a) || !valid_gguf(b)) return fail(GOPH_E_INVALID, "invalid GGUF matrix handle");
+  if (a->device != b->device || a->in_dim != b->in_dim)
+    return fail(GOPH_E_INVALID, "pair projection: matrices differ in device or inDim (%d vs %d)", a->in_dim, b->in_dim);
+  if (a->tiled && b->tiled && a->qtype == b->qtype) {
+    // both on the tensor-core path: validated like a single projection, x prepared once
+    if (batch <= 0) return fail(GOPH_E_INVALID, "batch=%d", batch);
+    uint64_t need_x, need_a, need_b;
+    if (!mul_ok((uint64_t)batch, (uint64_t)a->in_dim, &need_x) || !mul_ok((uint64_t)batch, (uint64_t)a->out_dim, &need_a) ||
+        !mul_ok((uint64_t)batch, (uint64_t)b->out_dim, &need_b))
+      return fail(GOPH_E_INVALID, "batch size overflow");
+    if (!x_dev || x_len < need_x || !out_a_dev || out_a_len < need_a || !out_b_dev || out_b_len < need_b)
+      return fail(GOPH_E_INVALID, "buffers x=%llu/%llu outA=%llu/%llu outB=%llu/%llu", (unsigned long long)x_len,
+                  (unsigned long long)need_x, (unsigned long long)out_a_len, (unsigned long long)need_a,
+                  (unsigned long long)out_b_len, (unsigned long long)need_b);
+    if (int rc = use_device(a->device)) return rc;
+    if (int rc = gguf_mma_launch(a, out_a_dev, x_dev, batch, options().mlx_digits, (cudaStream_t)stream, false)) return rc;
+    return gguf_mma_launch(b, out_b_dev, x_dev, batch, options().mlx_digits, (cudaStream_t)stream, true);
+  }
+  if (int rc = goph_gguf_project(out_a_dev, out_a_len, x_dev, x_len, batch, a, stream)) return rc;
+  return goph_gguf_project(out_b_dev, out_b_len, x_dev, x_len, batch, b, stream);
+}
+
 GOPH_API int goph_gguf_project_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
                                     int batch, const goph_gguf_matrix* m) {
   clear_error();

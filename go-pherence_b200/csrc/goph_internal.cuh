@@ -53,7 +53,7 @@ struct Options {
   int pdl = 1;         // launch kernels with programmatic stream serialization
   int mlx_layout = 0;  // layout chosen at upload: 0 by size, 1 always row-major, 2 tiled whenever the shape allows
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
-  int mlx_fuse = 0;    // 1: narrow tensor-core launches make their activation digits themselves (one launch, slower today)
+  int mlx_fuse = 1;    // 1: narrow tensor-core launches make the activation digits of their own K range themselves (one launch)
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
   int mlx_unpack = 0;
   int gguf_layout = 0; // as mlx_layout, for Q4_K / Q8_0 matrices

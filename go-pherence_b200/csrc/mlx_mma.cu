@@ -99,19 +99,21 @@ struct MmaArgs {
   int splits;              // CTAs sharing the K range of one tile
   int items;               // ntiles * splits
   int stages;              // depth of the shared-memory ring
+  int cmax;                // FUSED: most chunks an item has (resident B tiles)
 };
 
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
 // 2 B tiles (8 K-steps x N rows x 32 bytes), per-(row,group) tables {sum x, 2^(E-26), 2^(26-E)},
 // mbarriers, the TMEM base holder.
-// FUSED: the activation digits are made by the kernel itself and stay resident for all chunks
-// (in_dim / 256 B tiles after the ring) instead of travelling with every stage.
+// FUSED: the activation digits are made by the kernel itself, for the K range of the CTA's items
+// only (at most `cmax` chunks), and stay resident after the ring instead of travelling with every
+// stage.
 template <int N, int FMT = FMT_MLX4, bool FUSED = false>
 struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
   static constexpr int kStage = Fmt<FMT>::kStageBytes + (FUSED ? 0 : kBTileBytes);
-  static __host__ __device__ size_t bytes(int stages, int batch, int in_dim) {
-    return (size_t)stages * kStage + (FUSED ? (size_t)(in_dim / kChunkK) * kBTileBytes : 0) +
+  static __host__ __device__ size_t bytes(int stages, int batch, int in_dim, int cmax = 0) {
+    return (size_t)stages * kStage + (FUSED ? (size_t)cmax * kBTileBytes : 0) +
            (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
   }
 };
@@ -207,12 +209,13 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
 // and l + 32; the arithmetic and its order are those of mlx_prep_x_kernel.
 template <int DIGITS, bool G32, bool NATURAL, int N>
 __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int batch, int in_dim, unsigned char* bres,
-                                              float* xsum, float* xfs, int warp, int lane, int nwarps) {
+                                              float* xsum, float* xfs, int warp, int lane, int nwarps, int cbegin, int cend) {
   constexpr int QBITS = DIGITS == 4 ? 26 : 19;
   const int groups = in_dim / 64;
   const int ntab = G32 ? 2 * groups : groups;
-  for (int gi = warp; gi < batch * groups; gi += nwarps) {
-    const int m = gi / groups, g = gi - m * groups;
+  const int gbegin = 4 * cbegin, gcount = 4 * (cend - cbegin);  // the 64-element groups of chunks [cbegin, cend)
+  for (int gi = warp; gi < batch * gcount; gi += nwarps) {
+    const int m = gi / gcount, g = gbegin + (gi - m * gcount);
     const float* xp = x + (size_t)m * in_dim + g * 64;
     float v[2] = {xp[lane], xp[32 + lane]};
     float s[2] = {v[0], v[1]}, mx[2] = {fabsf(v[0]), fabsf(v[1])};
@@ -243,7 +246,7 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
       const int k = (g & 3) * 64 + h * 32 + lane;  // element within the 256-element chunk
       const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
       const int pos = NATURAL ? (k & 31) : 8 * w + 4 * (j & 1) + (j >> 1);
-      unsigned char* base = bres + (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
+      unsigned char* base = bres + (size_t)((g >> 2) - cbegin) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
 #pragma unroll
       for (int d = 0; d < DIGITS; ++d) {
         int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
@@ -278,7 +281,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   unsigned char* ring = smem;
   const int groups = a.in_dim / F::kGroup;
   unsigned char* bres = ring + (size_t)S * kStage;  // FUSED: resident B tiles of every chunk
-  float* xsum = reinterpret_cast<float*>(bres + (FUSED ? (size_t)a.nchunks * kBTileBytes : 0));  // [batch][groups] sum of x
+  float* xsum = reinterpret_cast<float*>(bres + (FUSED ? (size_t)a.cmax * kBTileBytes : 0));  // [batch][groups] sum of x
   float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
   uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
   // bars: full[S], empty[S], a_ready[NB], mma_done[NB], d_free[NB]
@@ -317,6 +320,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NB * kACols;  // A: NB x 64 cols; D: NB x kBlocks*N cols
   bool ok = true;
   StageWalk sw(a);
+  const int cbase = sw.live(a) ? sw.c : 0;  // first chunk of this CTA's K range
 
   if (FUSED) {
     // The weights do not depend on the kernel in front: the producer fills the ring, then every
@@ -330,7 +334,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       }
     }
     pdl_wait();
-    prep_x_in_cta<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80, N>(a.x, a.batch, a.in_dim, bres, xsum, xfs, warp, lane, kThreads / 32);
+    // every item of this CTA covers the same K range (the grid is a multiple of the K splits)
+    if (sw.live(a))
+      prep_x_in_cta<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80, N>(a.x, a.batch, a.in_dim, bres, xsum, xfs, warp, lane, kThreads / 32,
+                                                                 sw.c, sw.c1);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the MMA reads the digits through the async proxy
     __syncthreads();
   }
@@ -390,7 +397,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         if (ok && i >= NB) ok = mbar_wait(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)sw.c * kBTileBytes) : smem_u32(ring + (size_t)slot * kStage + kStageBytes);
+        const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)(sw.c - cbase) * kBTileBytes) : smem_u32(ring + (size_t)slot * kStage + kStageBytes);
         const uint32_t dcol = tmemD0 + b * (kBlocks * N), acol = tmemA0 + b * kACols;
 #pragma unroll
         for (int step = 0; step < 8; ++step) {  // K = 32 per step
@@ -742,23 +749,29 @@ struct TiledDesc {
 constexpr size_t kMmaSmemBudget = 222 * 1024;  // of the 227 KiB a CTA may have
 constexpr int kMaxStages = 10;
 
-template <int N, int DIGITS, int MB, int FMT, bool FUSED>
-static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep, int stages) {
-  MmaArgs a = a0;
-  DeviceState& st = device_state(w.device);
-  a.stages = stages;
-  // K split: enough (tile, split) items to occupy the SMs, bounded by the chunks and the scratch
+// K split: enough (tile, split) items to occupy the SMs, bounded by the chunks and the scratch.
+template <int MB>
+static int choose_splits(const MmaArgs& a, int sm_count) {
   int splits = 1;
-  if (a.ntiles < st.sm_count) {
-    splits = st.sm_count / a.ntiles;
+  if (a.ntiles < sm_count) {
+    splits = sm_count / a.ntiles;
     if (splits > a.nchunks) splits = a.nchunks;
     if (splits < 1) splits = 1;
   }
   if (options().mlx_splits > 0) splits = options().mlx_splits < a.nchunks ? options().mlx_splits : a.nchunks;
   while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
+  return splits;
+}
+
+template <int N, int DIGITS, int MB, int FMT, bool FUSED>
+static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep, int stages, int splits) {
+  MmaArgs a = a0;
+  DeviceState& st = device_state(w.device);
+  a.stages = stages;
   a.splits = splits;
   a.items = a.ntiles * splits;
-  size_t smem = MmaSmem<N, FMT, FUSED>::bytes(stages, a.batch, a.in_dim);
+  a.cmax = (a.nchunks + splits - 1) / splits;
+  size_t smem = MmaSmem<N, FMT, FUSED>::bytes(stages, a.batch, a.in_dim, a.cmax);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -778,6 +791,9 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT, FUSED>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
+  // FUSED: a CTA prepares the activations of one K range, so all its items must be of one split:
+  // item w is split w % splits, and a grid that is a multiple of the splits keeps that fixed per CTA
+  if (FUSED && a.items > grid) grid -= grid % splits;
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
@@ -787,23 +803,27 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
 
 template <int N, int DIGITS, int MB, int FMT>
 static int launch_one(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
-  // Option mlx_fuse: narrow launches (one or two activation rows) make their own digits when all
-  // chunks' B tiles fit beside a ring of at least five stages — one launch instead of two.  Off by
-  // default: measured on dependent chains of 4096 x 4096 products it costs 9.6 us per product
-  // against 8.0 us with the separate kernel, whose 64-thread blocks spread over all SMs while a
-  // CTA of the product kernel prepares the whole vector by itself.
-  if (N == 8 && options().mlx_fuse) {
-    size_t fixed = MmaSmem<N, FMT, true>::bytes(0, a.batch, a.in_dim);
+  const int sms = device_state(w.device).sm_count;
+  const int splits = choose_splits<MB>(a, sms);
+  const int cmax = (a.nchunks + splits - 1) / splits;
+  // Narrow launches (one or two activation rows) whose items are short (at most four chunks: the
+  // matrices that are split over K to fill the SMs) make the digits of their own K range inside
+  // the product kernel: one launch instead of two (measured 7.3 against 7.6 us for 4096 x 4096 in
+  // a dependent chain).  Longer items are served better by the separate kernel, whose small
+  // blocks prepare the vector once for all CTAs (14336 x 4096: 14.1 against 15.2 us).
+  // Option mlx_fuse = 0 always keeps the separate preparation kernel.
+  if (N == 8 && options().mlx_fuse && splits <= sms && cmax <= 4) {
+    size_t fixed = MmaSmem<N, FMT, true>::bytes(0, a.batch, a.in_dim, cmax);
     int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, true>::kStage) : 0;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages >= 5) return launch_impl<N, DIGITS, MB, FMT, N == 8>(w, a, stream, prep, stages);
+    if (stages >= 5) return launch_impl<N, DIGITS, MB, FMT, N == 8>(w, a, stream, prep, stages, splits);
   }
   size_t fixed = MmaSmem<N, FMT, false>::bytes(0, a.batch, a.in_dim);
   int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, false>::kStage) : 0;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages < 3)
     return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
-  return launch_impl<N, DIGITS, MB, FMT, false>(w, a, stream, prep, stages);
+  return launch_impl<N, DIGITS, MB, FMT, false>(w, a, stream, prep, stages, splits);
 }
 
 template <int FMT>
@@ -978,11 +998,12 @@ int gguf_mma_make_tiled(goph_gguf_matrix* m) {
   return GOPH_OK;
 }
 
-int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream) {
+int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                    bool x_prepared) {
   if (!m->tiled) return fail(GOPH_E_UNSUPPORTED, "matrix is not in the tiled layout");
   TiledDesc d{m->tiled, m->device, m->out_dim, m->in_dim};
-  return m->qtype == GOPH_GGUF_Q4_K ? tiled_launch<FMT_Q4K>(d, out, x, batch, digits, stream, false)
-                                    : tiled_launch<FMT_Q80>(d, out, x, batch, digits, stream, false);
+  return m->qtype == GOPH_GGUF_Q4_K ? tiled_launch<FMT_Q4K>(d, out, x, batch, digits, stream, x_prepared)
+                                    : tiled_launch<FMT_Q80>(d, out, x, batch, digits, stream, x_prepared);
 }
 
 int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream) {
@@ -1067,9 +1088,12 @@ static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, 
   while (splits > 1 && a.ntiles * splits > kNoAllocMaxItems) --splits;
   a.splits = splits;
   a.items = a.ntiles * splits;
-  // The array keeps whatever the last call left: the status word and the tile counters have to
-  // start at zero (the digits, tables and partial sums are fully rewritten before they are read).
-  GOPH_CUDA(cudaMemsetAsync(base, 0, kNaTabOff, stream));
+  a.cmax = 0;
+  // The array keeps whatever the last call left: the tile counters have to start at zero (the
+  // digits, tables and partial sums are fully rewritten before they are read).  The status word is
+  // left alone: it is zero when the library is loaded and sticky once a wait has given up, like the
+  // allocated path's; goph_mlx_gemv_noalloc_status reads it.
+  GOPH_CUDA(cudaMemsetAsync(base + kNaCountersOff, 0, kNaTabOff - kNaCountersOff, stream));
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr.val.programmaticStreamSerializationAllowed = 0;  // plain stream order behind the memset
@@ -1096,6 +1120,16 @@ static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, 
 }  // namespace goph
 
 using namespace goph;
+
+GOPH_API int goph_mlx_gemv_noalloc_status(int device, int* out_status) {
+  clear_error();
+  if (!out_status) return fail(GOPH_E_INVALID, "goph_mlx_gemv_noalloc_status: nil result pointer");
+  if (int rc = use_device(device)) return rc;
+  unsigned char* base = nullptr;
+  if (int rc = noalloc_base(device, &base)) return rc;
+  GOPH_CUDA(cudaMemcpy(out_status, base + kNaStatusOff, sizeof(int), cudaMemcpyDeviceToHost));
+  return GOPH_OK;
+}
 
 GOPH_API int goph_mlx_gemv_noalloc(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
                                    const goph_mlx_weight* w, void* stream) {

@@ -34,7 +34,10 @@ void mlx_mma_status_clear(int device);
 // buffers (which the caller then frees); dequant reproduces dequantRowQ4KTo / dequantRowQ8_0To.
 bool gguf_mma_supported(int qtype, int in_dim);
 int gguf_mma_make_tiled(goph_gguf_matrix* m);
-int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream);
+// x_prepared: the launch in front on this stream prepared the same x for a matrix of the same type
+// (same batch, same in_dim): the preparation kernel is skipped.
+int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int batch, int digits, cudaStream_t stream,
+                    bool x_prepared = false);
 int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream);
 
 }  // namespace goph

@@ -1,6 +1,7 @@
 // Runtime part of the C ABI: device binding, buffers, copies, error text.
 // Stands where backends/nvidia/runtime/runtime.go stands in the reference (Init,
 // EnsureContext, Malloc, Buffer.Upload/Download/Free, Sync).
+#include <dlfcn.h>
 #include <stdarg.h>
 #include <string.h>
 
@@ -12,6 +13,29 @@ static DeviceState g_dev[kMaxDevices];
 static thread_local char g_err[512] = "";
 
 static Options g_opt;
+
+// Driver contexts adopted through goph_init_current_context (nullptr: the device's primary
+// context, bound through the runtime).  The reference creates its own context with cuCtxCreate
+// (backends/nvidia/runtime/runtime.go:247) and allocates every buffer in it, so a drop-in has to
+// launch in that context and leave it current on the calling thread.
+static void* g_ctx[kMaxDevices] = {};
+typedef int (*CtxGetCurrent)(void**);
+typedef int (*CtxSetCurrent)(void*);
+typedef int (*CtxGetDevice)(int*);
+static CtxGetCurrent p_ctx_get_current = nullptr;
+static CtxSetCurrent p_ctx_set_current = nullptr;
+static CtxGetDevice p_ctx_get_device = nullptr;
+
+// The driver library is opened at run time (no link-time dependency, as the reference's purego binding).
+static bool load_driver() {
+  if (p_ctx_set_current) return true;
+  void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return false;
+  p_ctx_get_current = (CtxGetCurrent)dlsym(h, "cuCtxGetCurrent");
+  p_ctx_get_device = (CtxGetDevice)dlsym(h, "cuCtxGetDevice");
+  p_ctx_set_current = (CtxSetCurrent)dlsym(h, "cuCtxSetCurrent");
+  return p_ctx_get_current && p_ctx_get_device && p_ctx_set_current;
+}
 
 DeviceState& device_state(int device) { return g_dev[device]; }
 Options& options() { return g_opt; }
@@ -36,6 +60,12 @@ int fail_cuda(cudaError_t e, const char* what) {
 int use_device(int device) {
   if (device < 0 || device >= kMaxDevices) return fail(GOPH_E_INVALID, "device %d out of range", device);
   if (!g_dev[device].ready) return fail(GOPH_E_NOINIT, "goph_init(%d) has not been called", device);
+  if (g_ctx[device]) {
+    // an adopted context: make it current (calls may come from any OS thread), the runtime follows it
+    int rc = p_ctx_set_current(g_ctx[device]);
+    if (rc != 0) return fail(GOPH_E_CUDA, "cuCtxSetCurrent failed with CUresult %d", rc);
+    return GOPH_OK;
+  }
   GOPH_CUDA(cudaSetDevice(device));
   return GOPH_OK;
 }
@@ -50,9 +80,11 @@ GOPH_API int goph_init(int device) {
   int n = 0;
   GOPH_CUDA(cudaGetDeviceCount(&n));
   if (device >= n) return fail(GOPH_E_INVALID, "device %d not present (%d visible)", device, n);
+  DeviceState& st = device_state(device);
+  if (st.ready && g_ctx[device])
+    return fail(GOPH_E_INVALID, "device %d is already bound to an adopted context (goph_init_current_context)", device);
   GOPH_CUDA(cudaSetDevice(device));
   GOPH_CUDA(cudaFree(0));
-  DeviceState& st = device_state(device);
   if (st.ready) return GOPH_OK;
   cudaDeviceProp prop;
   GOPH_CUDA(cudaGetDeviceProperties(&prop, device));
@@ -62,6 +94,39 @@ GOPH_API int goph_init(int device) {
   st.sm_count = prop.multiProcessorCount;
   st.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
   st.ready = true;
+  return GOPH_OK;
+}
+
+GOPH_API int goph_init_current_context(int* out_device) {
+  clear_error();
+  if (!out_device) return fail(GOPH_E_INVALID, "goph_init_current_context: nil result pointer");
+  *out_device = -1;
+  if (!load_driver()) return fail(GOPH_E_CUDA, "goph_init_current_context: libcuda.so.1 cannot be opened");
+  void* ctx = nullptr;
+  int rc = p_ctx_get_current(&ctx);
+  if (rc != 0 || !ctx)
+    return fail(GOPH_E_INVALID, "goph_init_current_context: no driver context is current on this thread (CUresult %d)", rc);
+  int device = -1;
+  rc = p_ctx_get_device(&device);
+  if (rc != 0 || device < 0 || device >= kMaxDevices)
+    return fail(GOPH_E_INVALID, "goph_init_current_context: cuCtxGetDevice gave device %d (CUresult %d)", device, rc);
+  DeviceState& st = device_state(device);
+  if (st.ready && g_ctx[device] != ctx)
+    return fail(GOPH_E_INVALID, "device %d is already bound to %s context: a device serves one context per process", device,
+                g_ctx[device] ? "another adopted" : "its primary");
+  if (st.ready) {
+    *out_device = device;
+    return GOPH_OK;
+  }
+  cudaDeviceProp prop;
+  GOPH_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(GOPH_E_UNSUPPORTED, "device %d is sm_%d%d; this library holds sm_100a code only", device, prop.major, prop.minor);
+  st.sm_count = prop.multiProcessorCount;
+  st.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+  g_ctx[device] = ctx;
+  st.ready = true;
+  *out_device = device;
   return GOPH_OK;
 }
 

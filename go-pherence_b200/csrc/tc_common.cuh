@@ -36,6 +36,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
+#if defined(GOPH_SPIN_NS)
+    asm volatile("nanosleep.u32 %0;" ::"r"((unsigned)GOPH_SPIN_NS));  // tuning: back off between polls
+#endif
     if (clock64() - t0 > kTimeoutCycles) {
       atomicCAS(status, 0, code);
       return false;

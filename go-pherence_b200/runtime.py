@@ -23,16 +23,16 @@ GGUF_Q6_K = 14  # loader/gguf/gguf.go:56
 
 # Every symbol include/goph_b200.h declares.
 EXPORTS = [
-    "goph_init", "goph_set_option", "goph_kernel_status", "goph_kernel_status_clear", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
+    "goph_init", "goph_init_current_context", "goph_set_option", "goph_kernel_status", "goph_kernel_status_clear", "goph_last_error", "goph_sm_count", "goph_malloc", "goph_free", "goph_upload",
     "goph_download", "goph_memset", "goph_sync",
     "goph_mlx_program_create", "goph_mlx_program_create_pre", "goph_mlx_program_run", "goph_mlx_program_status", "goph_mlx_program_free",
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
-    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_bf16", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc",
+    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_bf16", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc", "goph_mlx_gemv_noalloc_status",
     "goph_mlx_gemm_host",
     "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
-    "goph_gguf_project", "goph_gguf_project_host",
+    "goph_gguf_project", "goph_gguf_project_pair", "goph_gguf_project_host",
     "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm", "goph_fp8_gemm_bf16",
     "goph_fp8_gemm_host",
     "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
@@ -94,6 +94,16 @@ def init(device=0):
     _check(lib().goph_init(int(device)))
     _device = int(device)
     return True
+
+
+def InitCurrentContext():
+    """Binds the library to the driver context that is current on this thread (the reference creates its
+    own with cuCtxCreate, runtime/runtime.go:247) instead of the device's primary context."""
+    global _device
+    d = C.c_int(-1)
+    _check(lib().goph_init_current_context(C.byref(d)))
+    _device = d.value
+    return _device
 
 
 def device():
@@ -258,6 +268,13 @@ def GemvMLXNoAlloc(out, x, w, stream=None):
                                        _mlx_handle(w), _stream_ptr(stream)))
 
 
+def GemvMLXNoAllocStatus():
+    """Status word of the allocation-free entry point's kernels on this device (0 = every wait completed)."""
+    v = C.c_int(0)
+    _check(lib().goph_mlx_gemv_noalloc_status(_device, C.byref(v)))
+    return v.value
+
+
 GemvMLXDirect = GemvMLX  # nvidia.GemvMLXDirect (runtime/mlx.go:455): same kernel here.
 
 
@@ -331,6 +348,14 @@ class GPUGGUFMatrix:
         if self._h:
             _check(lib().goph_gguf_free(self._h))
             self._h = None
+
+
+def ProjectQ4PairToBuffers(outA, outB, x, batch, a, b, stream=None):
+    """nvidia.ProjectQ4PairToBuffers (runtime/gguf_matrix.go:82-111): gate and up on one x."""
+    if outA is None or outB is None or x is None or a is None or b is None:
+        raise GophError(1, "nil buffer or matrix")
+    _check(lib().goph_gguf_project_pair(C.c_void_p(outA.Ptr), C.c_uint64(outA.n), C.c_void_p(outB.Ptr), C.c_uint64(outB.n),
+                                        C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch), a._h, b._h, _stream_ptr(stream)))
 
 
 def _upload_gguf(qtype, raw, inDim, outDim):

@@ -61,6 +61,15 @@ typedef struct goph_fp8_linear goph_fp8_linear;   /* nvidia.GPUFP8E4M3Linear  (r
 /* nvidia.Init + EnsureContext (runtime/runtime.go:142-274): bind `device`, create the
  * primary context, read the SM count.  Idempotent per device. */
 int goph_init(int device);
+/* nvidia.EnsureContext for a caller that owns its driver context, as the reference does: it creates
+ * one with cuCtxCreate and allocates every buffer in it (runtime/runtime.go:226-274).  Call this
+ * with that context current on the thread, INSTEAD of goph_init: the library then makes that context
+ * current at the top of every entry point (calls may come from any OS thread, runtime.go:258-274),
+ * launches its kernels in it, allocates its own scratch in it, and leaves it current on return, so
+ * buffers from the caller's cuMemAlloc are valid arguments.  *out_device receives the device
+ * ordinal of the context, which is the `device` argument of the other entry points.  A device
+ * serves one context per process: mixing goph_init and this call on one device is refused. */
+int goph_init_current_context(int* out_device);
 /* Text of the last error on the calling thread ("" if none). */
 const char* goph_last_error(void);
 /* nvidia.SMCount (runtime/runtime.go:285); 0 if the device is not initialised. */
@@ -85,8 +94,9 @@ int goph_sm_count(int device);
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
- *   "mlx_fuse"    1: tensor-core launches of one or two activation rows prepare the activation digits
- *                 inside the product kernel (one launch instead of two); 0 (default) separate kernel
+ *   "mlx_fuse"    1 (default): tensor-core launches of one or two activation rows make the activation
+ *                 digits of their own K range inside the product kernel (one launch per product);
+ *                 0: a separate preparation kernel in front of every product
  *   "mlx_splits"  CTAs that share the K range of one 128-row tile (0 = chosen by shape)
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion
@@ -167,13 +177,18 @@ int goph_mlx_gemm_multi(int n, float* const* outs_dev, const goph_mlx_weight* co
  * Limits: in_dim <= 16384, out_dim <= 524288, batch 1, tiled layout only (group size 64, in_dim a
  * multiple of 256, bf16-valued scales/biases, uploaded with "mlx_layout" 0 or 2) — anything else
  * is rejected with GOPH_E_UNSUPPORTED and a text that names the limit.  x_dev must be 16-byte aligned.
- * The first call on a device resolves the array's device address (cudaGetSymbolAddress); make that
- * first call before any stream capture begins.  All calls on a device share the one array: calls
- * that can overlap on the GPU (different streams without an ordering between them) race on it, so
- * keep them in one stream or order them with events.  The array keeps the previous call's contents;
- * the entry point clears the parts that must start at zero with a memset on `stream`. */
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress) and makes
+ * the driver load the kernels it launches; make that first call before any stream capture begins.
+ * All calls on a device share the one array: calls that can overlap on the GPU (different streams
+ * without an ordering between them) race on it, so keep them in one stream or order them with
+ * events.  The array keeps the previous call's contents; the entry point clears the tile counters,
+ * which must start at zero, with a memset on `stream`.  Its health word (see goph_kernel_status) is
+ * part of the array, sticky, and read with goph_mlx_gemv_noalloc_status, which allocates nothing. */
 int goph_mlx_gemv_noalloc(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
                           const goph_mlx_weight* w, void* stream);
+/* No counterpart in the reference.  0, or the code of the first bounded wait that gave up inside a
+ * goph_mlx_gemv_noalloc kernel on this device.  Synchronises with the device; allocates nothing. */
+int goph_mlx_gemv_noalloc_status(int device, int* out_status);
 /* Host-slice form, as nvidia.GemvQ4K/GemmFP8E4M3 take Go slices (runtime/q4k.go:571,
  * fp8.go:180): copies x in, runs, copies out back, synchronises. */
 int goph_mlx_gemm_host(float* out_host, uint64_t out_len, const float* x_host, uint64_t x_len,
@@ -190,6 +205,12 @@ int goph_gguf_free(goph_gguf_matrix* m);
 uint64_t goph_gguf_resident_bytes(const goph_gguf_matrix* m);
 /* QuantMatrix.DequantRowTo for every row (loader/gguf/quant_matrix.go:42-60), bit-exact. */
 int goph_gguf_dequant(const goph_gguf_matrix* m, float* out_dev, uint64_t out_len, void* stream);
+/* nvidia.ProjectQ4PairToBuffers (runtime/gguf_matrix.go:82-111): two matrices of one inDim (gate and
+ * up) applied to the same x [batch,in]; on the tensor-core path the activations are prepared once
+ * for both.  Results equal two goph_gguf_project calls bit for bit. */
+int goph_gguf_project_pair(float* out_a_dev, uint64_t out_a_len, float* out_b_dev, uint64_t out_b_len,
+                           const float* x_dev, uint64_t x_len, int batch, const goph_gguf_matrix* a,
+                           const goph_gguf_matrix* b, void* stream);
 /* GPUGGUFMatrix.ProjectBatchToBuffer / GemvQ4KBatchToBuffer / GemvQ8_0BatchToBuffer
  * (runtime/gguf_matrix.go:121-135, q4k.go:351, q8.go:225): x [batch,in] f32 → out [batch,out]. */
 int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,

@@ -326,3 +326,37 @@ def test_tiled_fused_and_separate_preparation_agree(gpu, pkg, tiled_layout, qtyp
     assert pkg.synth.rel_err(got[0], want) <= TOL
     assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
     m.Free(); xo.Free()
+
+
+@pytest.mark.parametrize("qname,layout", [("q4k", 2), ("q4k", 1), ("q8_0", 2)])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_pair_projection_shares_x(gpu, pkg, qname, layout, batch):
+    # nvidia.ProjectQ4PairToBuffers (runtime/gguf_matrix.go:82-111): gate and up on one x equal two
+    # single projections bit for bit, and the oracle within the product tolerance
+    in_dim, out_a, out_b = 1024, 768, 512
+    qt = gpu.GGUF_Q4_K if qname == "q4k" else gpu.GGUF_Q8_0
+    gen = pkg.synth.q4k_matrix if qname == "q4k" else pkg.synth.q8_0_matrix
+    ra, rb = gen(("pair", "a"), out_a, in_dim), gen(("pair", "b"), out_b, in_dim)
+    gpu.SetOption("gguf_layout", layout)
+    try:
+        ma, mb = gpu.UploadGGUFMatrix(qt, ra, in_dim, out_a), gpu.UploadGGUFMatrix(qt, rb, in_dim, out_b)
+    finally:
+        gpu.SetOption("gguf_layout", 0)
+    x = pkg.synth.activations(("pair", batch), batch * in_dim, bf16=False)
+    xo = gpu.from_numpy(x)
+    oa, ob = out_with_canary(gpu, batch * out_a), out_with_canary(gpu, batch * out_b)
+    gpu.ProjectQ4PairToBuffers(oa, ob, xo, batch, ma, mb)
+    gpu.Sync()
+    ga, gb = read_and_check_canary(oa, batch * out_a), read_and_check_canary(ob, batch * out_b)
+    sa, sb = out_with_canary(gpu, batch * out_a), out_with_canary(gpu, batch * out_b)
+    ma.ProjectBatchToBuffer(sa, xo, batch)
+    mb.ProjectBatchToBuffer(sb, xo, batch)
+    gpu.Sync()
+    assert np.array_equal(ga.view(np.uint32), read_and_check_canary(sa, batch * out_a).view(np.uint32))
+    assert np.array_equal(gb.view(np.uint32), read_and_check_canary(sb, batch * out_b).view(np.uint32))
+    assert pkg.synth.rel_err(ga, orc.gguf_gemv(x, ra, qt, in_dim, out_a, batch, nthreads=8)) <= TOL
+    assert pkg.synth.rel_err(gb, orc.gguf_gemv(x, rb, qt, in_dim, out_b, batch, nthreads=8)) <= TOL
+    with pytest.raises(gpu.GophError):
+        gpu.ProjectQ4PairToBuffers(oa, ob, xo, batch, ma, None)
+    for t_ in (ma, mb, xo, oa, ob, sa, sb):
+        t_.Free()

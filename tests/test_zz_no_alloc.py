@@ -26,6 +26,9 @@ def tiled_weight(gpu, pkg, key, out_dim, in_dim):
 
 @pytest.mark.parametrize("out_dim,in_dim", [(4096, 4096), (1000, 1024), (18944, 2048)])
 def test_noalloc_matches_regular_entry_point_twice(gpu, pkg, out_dim, in_dim):
+    import torch
+    from oracle import binding as orc
+    w, s, b = pkg.synth.mlx_weight(("na", out_dim, in_dim), out_dim, in_dim, 64)
     h = tiled_weight(gpu, pkg, ("na", out_dim, in_dim), out_dim, in_dim)
     x1 = pkg.synth.activations(("na", in_dim, 1), in_dim, bf16=False)
     x2 = pkg.synth.activations(("na", in_dim, 2), in_dim, bf16=False)
@@ -36,10 +39,18 @@ def test_noalloc_matches_regular_entry_point_twice(gpu, pkg, out_dim, in_dim):
         gpu.Sync()
         want = read_and_check_canary(ref, out_dim)
         out = out_with_canary(gpu, out_dim)
+        gpu.GemvMLXNoAlloc(out, xo, h)   # the first call on the device resolves the scratch address and loads the kernels
+        gpu.Sync()
+        # the entry point's one promise: the device's free memory is the same before and after a call
+        free_before = torch.cuda.mem_get_info()[0]
         gpu.GemvMLXNoAlloc(out, xo, h)
         gpu.Sync()
+        assert torch.cuda.mem_get_info()[0] == free_before
         got = read_and_check_canary(out, out_dim)
-        assert pkg.synth.rel_err(got, want) <= TOL
+        # the same kernel on the same digits: the regular entry point's bits, and the oracle's answer
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        assert pkg.synth.rel_err(got, orc.mlx_gemv(x, w, s, b, out_dim, in_dim, 64, nthreads=8)) <= TOL
+        assert gpu.GemvMLXNoAllocStatus() == 0
         for t in (xo, ref, out):
             t.Free()
     h.Free()
