@@ -48,6 +48,17 @@ using namespace tc;
 
 namespace {
 
+// Tuning build only (-DGOPH_TUNING): one CTA in the middle of the grid records clock64 at the
+// hand-over points of its first 64 stages; goph_tuning_probe_gemv copies the timeline out.
+#ifdef GOPH_TUNING
+__device__ long long g_mma_trace[8][64];
+#define TP(...) __VA_ARGS__
+#define DBG(bit) (a.dbg & (bit))  // parts of the kernel left out (results are then wrong)
+#else
+#define TP(...)
+#define DBG(bit) 0
+#endif
+
 constexpr int kTileRows = 128;
 constexpr int kChunkK = 256;                  // elements per pipeline stage
 constexpr int kStageMBytes = kTileRows * 16;  // 16 bytes of scales per row and stage in every format
@@ -77,7 +88,12 @@ constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
 constexpr int kConvWarps = 8, kEpiWarps = 8;  // two epilogue warps per TMEM lane quarter: each takes half of a stage's accumulator blocks
 constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
 constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
-constexpr int kMmaWarps = 2;  // two issuing threads take alternate stages so one's waits hide behind the other's MMAs
+constexpr int kMmaWarps = 1;  // the whole warp walks the stages, one elected lane issues
+// Stages whose copies are issued at once when a CTA starts.  If every CTA of the grid asked for its
+// whole ring at that moment (tens of MB), the memory system would serve those requests interleaved
+// and the first stage of every CTA would land last, microseconds late; the rest of the ring is
+// asked for when the first stage has arrived.
+constexpr int kFirstStages = 2;
 constexpr int kThreads = (kWarpMMA + kMmaWarps) * 32;
 
 
@@ -100,6 +116,7 @@ struct MmaArgs {
   int items;               // ntiles * splits
   int stages;              // depth of the shared-memory ring
   int cmax;                // FUSED: most chunks an item has (resident B tiles)
+  int dbg;                 // tuning build only
 };
 
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
@@ -108,10 +125,13 @@ struct MmaArgs {
 // FUSED: the activation digits are made by the kernel itself, for the K range of the CTA's items
 // only (at most `cmax` chunks), and stay resident after the ring instead of travelling with every
 // stage.
-template <int N, int FMT = FMT_MLX4, bool FUSED = false>
+// C: chunks of 256 elements per stage.  The nibble formats take two: what a stage costs every role
+// in waits, fences and arrivals is then paid once per 36 KiB instead of once per 18 KiB.  A stage's
+// layout is [C weight blocks][C B tiles].
+template <int N, int FMT = FMT_MLX4, bool FUSED = false, int C = 1>
 struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
-  static constexpr int kStage = Fmt<FMT>::kStageBytes + (FUSED ? 0 : kBTileBytes);
+  static constexpr int kStage = C * (Fmt<FMT>::kStageBytes + (FUSED ? 0 : kBTileBytes));
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim, int cmax = 0) {
     return (size_t)stages * kStage + (FUSED ? (size_t)cmax * kBTileBytes : 0) +
            (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
@@ -121,19 +141,23 @@ struct MmaSmem {
 // Walks the (tile, chunk) stages of this CTA's work items in the order every role uses.
 struct StageWalk {
   int w, tile, split, c, c1;
+  int cps;  // chunks per stage
   __device__ __forceinline__ void open(const MmaArgs& a) {
     tile = w / a.splits;
     split = w - tile * a.splits;
     c = split * a.nchunks / a.splits;
     c1 = (split + 1) * a.nchunks / a.splits;
   }
-  __device__ __forceinline__ StageWalk(const MmaArgs& a) : w(blockIdx.x) {
+  __device__ __forceinline__ StageWalk(const MmaArgs& a, int chunks_per_stage = 1) : w(blockIdx.x), cps(chunks_per_stage) {
     if (w < a.items) open(a);
   }
   __device__ __forceinline__ bool live(const MmaArgs& a) const { return w < a.items; }
-  __device__ __forceinline__ bool last_chunk() const { return c + 1 == c1; }
+  // chunks of the current stage (an item with an odd number of chunks ends on a stage of one)
+  __device__ __forceinline__ int nc() const { return c1 - c < cps ? c1 - c : cps; }
+  __device__ __forceinline__ bool last_chunk() const { return c + nc() == c1; }
   __device__ __forceinline__ void next(const MmaArgs& a) {
-    if (++c == c1) {
+    c += nc();
+    if (c == c1) {
       w += gridDim.x;
       if (w < a.items) open(a);
     }
@@ -260,21 +284,27 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
 
 // N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
 // MB: activation rows the instantiation can take (MB * DIGITS <= N).
-template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false>
+template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false, int C = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
   static_assert(N == 8 || N == 16 || N == 32, "accumulator blocks of 8, 16 or 32 columns");
   typedef Fmt<FMT> F;
   constexpr int kBlocks = F::kBlocks;
-  constexpr int kACols = F::kConv ? 64 : 0;     // TMEM columns of one A buffer
-  // depth of the A / accumulator rings in TMEM: NB * (kACols + kBlocks * N) <= 512 columns
-  constexpr int NB = (kACols + kBlocks * N) * 4 <= 512 ? 4 : 2;
-  static_assert(NB * (kACols + kBlocks * N) <= 512, "TMEM plan");
+  constexpr int kACols = F::kConv ? 64 * C : 0;  // TMEM columns of one A buffer (a stage)
+  constexpr int kDCols = C * kBlocks * N;        // accumulator columns of a stage
+  // Depths of the A ring and of the accumulator ring in TMEM (512 columns).  A third A buffer lets
+  // the converters start stage i+2 while the MMAs of stage i still run; where the columns do not
+  // allow four of each, the accumulators, which the epilogue drains quickly, get the shallower ring.
+  constexpr int NA = (kACols + kDCols) * 4 <= 512 ? 4 : (3 * kACols + 2 * kDCols <= 512 ? 3 : 2);
+  constexpr int ND = (kACols + kDCols) * 4 <= 512 ? 4 : 2;
+  static_assert(NA * kACols + ND * kDCols <= 512, "TMEM plan");
+  static_assert(C == 1 || F::kConv, "two chunks per stage are for the formats that convert");
   constexpr uint32_t kCols = 512;
-  constexpr int kStage = MmaSmem<N, FMT, FUSED>::kStage;
+  constexpr int kStage = MmaSmem<N, FMT, FUSED, C>::kStage;
   constexpr int kStageBytes = F::kStageBytes, kStageWBytes = F::kStageWBytes;
-  constexpr int kBTileBytes = MmaSmem<N, FMT, FUSED>::kBTileBytes;
+  constexpr int kBTileBytes = MmaSmem<N, FMT, FUSED, C>::kBTileBytes;
+  constexpr int kStageLoad = kStageBytes + (FUSED ? 0 : kBTileBytes);  // bytes a chunk brings into a stage
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
@@ -284,14 +314,15 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   float* xsum = reinterpret_cast<float*>(bres + (FUSED ? (size_t)a.cmax * kBTileBytes : 0));  // [batch][groups] sum of x
   float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
   uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
-  // bars: full[S], empty[S], a_ready[NB], mma_done[NB], d_free[NB]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 3 * NB);
+  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   float* pair = reinterpret_cast<float*>(tmem_holder + 4);  // [MB][128]: the second epilogue half's sums of an item
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
-  const uint32_t aready0 = smem_u32(bars + 2 * S), mdone0 = smem_u32(bars + 2 * S + NB), dfree0 = smem_u32(bars + 2 * S + 2 * NB);
+  const uint32_t aready0 = smem_u32(bars + 2 * S), afree0 = aready0 + 8 * NA;
+  const uint32_t mdone0 = afree0 + 8 * NA, dfree0 = mdone0 + 8 * ND;  // mdone: a stage's accumulators are complete
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -300,8 +331,11 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       // (one arrival per warp: a warp's lanes meet first and one of them arrives for all)
       mbar_init(empty0 + 8 * s, (F::kConv ? kConvWarps / 2 : 0) + kEpiWarps + 1);
     }
-    for (int b = 0; b < NB; ++b) {
+    for (int b = 0; b < NA; ++b) {
       mbar_init(aready0 + 8 * b, kConvWarps / 2);
+      mbar_init(afree0 + 8 * b, 1);
+    }
+    for (int b = 0; b < ND; ++b) {
       mbar_init(mdone0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiWarps);
     }
@@ -317,9 +351,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NB * kACols;  // A: NB x 64 cols; D: NB x kBlocks*N cols
+  const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * kACols;  // A: NA x kACols; D: ND x kDCols
   bool ok = true;
-  StageWalk sw(a);
+  StageWalk sw(a, C);
+  TP(const bool tr = blockIdx.x == gridDim.x / 2; if (tr && tid == 0) g_mma_trace[7][0] = clock64();)
   const int cbase = sw.live(a) ? sw.c : 0;  // first chunk of this CTA's K range
 
   if (FUSED) {
@@ -327,10 +362,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     // warp helps to turn the activations into digits, sums and scales.
     if (warp == kWarpTMA && lane == 0) {
       StageWalk sw0 = sw;
-      for (int i = 0; i < S && sw0.live(a); ++i, sw0.next(a)) {
-        mbar_expect_tx(full0 + 8 * i, kStageBytes);
+      for (int i = 0; i < S && i < kFirstStages && sw0.live(a); ++i, sw0.next(a)) {
+        mbar_expect_tx(full0 + 8 * i, sw0.nc() * kStageBytes);
         bulk_load_1d(smem_u32(ring + (size_t)i * kStage), a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes,
-                     kStageBytes, full0 + 8 * i);
+                     sw0.nc() * kStageBytes, full0 + 8 * i);
       }
     }
     pdl_wait();
@@ -349,108 +384,132 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       // wait for the activation digits and add the B tiles of those stages.
       int i = 0;
       if (FUSED) {
-        for (; i < S && sw.live(a); ++i) sw.next(a);  // filled before the activations were prepared
+        for (; i < S && i < kFirstStages && sw.live(a); ++i) sw.next(a);  // asked for before the activations were prepared
       } else {
         StageWalk sw0 = sw;
-        for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
+        for (; i < S && i < kFirstStages && sw0.live(a); ++i, sw0.next(a)) {
           uint32_t dst = smem_u32(ring + (size_t)i * kStage);
-          mbar_expect_tx(full0 + 8 * i, kStage);
-          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, kStageBytes, full0 + 8 * i);
+          mbar_expect_tx(full0 + 8 * i, sw0.nc() * kStageLoad);
+          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, sw0.nc() * kStageBytes, full0 + 8 * i);
         }
         pdl_wait();
         for (int j = 0; j < i; ++j, sw.next(a))
-          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes,
-                       kBTileBytes, full0 + 8 * j);
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + C * kStageBytes, a.xb + (size_t)sw.c * kBTileBytes,
+                       sw.nc() * kBTileBytes, full0 + 8 * j);
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
         int slot = i % S, round = i / S;
-        ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 1);
+        if (round > 0) ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 1);
+        else if (i == kFirstStages) ok = mbar_wait(full0, 0, a.status, 11);  // the first stage is in: the rest of the ring may follow
         if (!ok) break;
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
-        mbar_expect_tx(full0 + 8 * slot, kStage);
+        mbar_expect_tx(full0 + 8 * slot, sw.nc() * kStageLoad);
         const unsigned char* src = a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes;
-        bulk_load_1d(dst, src, kStageBytes, full0 + 8 * slot);
-        if (!FUSED) bulk_load_1d(dst + kStageBytes, a.xb + (size_t)sw.c * kBTileBytes, kBTileBytes, full0 + 8 * slot);
+        bulk_load_1d(dst, src, sw.nc() * kStageBytes, full0 + 8 * slot);
+        if (!FUSED) bulk_load_1d(dst + C * kStageBytes, a.xb + (size_t)sw.c * kBTileBytes, sw.nc() * kBTileBytes, full0 + 8 * slot);
+        TP(if (tr && i < 64) g_mma_trace[0][i] = clock64();)
       }
     }
   } else if (warp >= kWarpMMA) {
     // ------------------------------------------------------------------ MMA issuers
-    if (lane == 0) {
-      const int mi = warp - kWarpMMA;
-      if (mi == 1 && sw.live(a)) sw.next(a);
+    // The whole warp walks its stages and waits; one elected lane issues.  (What the instructions
+    // need is the same in all lanes and can live in uniform registers, which roughly halves the
+    // cycles an issue costs against a single diverged thread.)
+    {
       // instruction descriptor: D s32, A u8 (nibbles) or s8 (Q8_0 bytes), B s8, both K-major, N, M=128
       const uint32_t idesc = (2u << 4) | ((FMT == FMT_Q80 ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
       // A from shared memory (Q8_0): K-adjacent core matrices 16 row groups apart, row groups 128 B apart
       const uint64_t adesc_hi = ((uint64_t)(2048u >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
       constexpr uint32_t kLBO = (N / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
       const uint64_t desc_hi = ((uint64_t)(kLBO >> 4) << 16) | ((uint64_t)(kSBO >> 4) << 32) | (1ull << 46);
-      for (int i = mi; sw.live(a) && ok; i += kMmaWarps) {
-        int b = i % NB, slot = i % S;
-        // The two issuers take alternate stages, so this one has not itself seen stage i-1 land.
-        // A parity wait can only tell the barrier's current phase from the one before it: if this
-        // issuer ran ahead and asked for round R of a slot whose round R-1 is still in flight, the
-        // wait would pass at once.  Waiting for stage i-1 first makes every earlier stage (in
-        // particular stage i-S, the slot's previous round) complete before stage i is asked for.
-        if (i >= 1) ok = mbar_wait(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 9);
-        if (ok) ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 8);
-        if (ok && F::kConv) ok = mbar_wait(aready0 + 8 * b, (i / NB) & 1, a.status, 2);
-        if (ok && i >= NB) ok = mbar_wait(dfree0 + 8 * b, ((i - NB) / NB) & 1, a.status, 5);
+      // Every role sees every stage in order, so no barrier phase is ever skipped (a parity wait
+      // can only tell the current phase from the one before it).
+      for (int i = 0; sw.live(a) && ok; ++i) {
+        const int ba = i % NA, b = i % ND, slot = i % S;
+        ok = mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 8);
+        if (ok && F::kConv) ok = mbar_wait(aready0 + 8 * ba, (i / NA) & 1, a.status, 2);
+        if (ok && i >= ND) ok = mbar_wait(dfree0 + 8 * b, ((i - ND) / ND) & 1, a.status, 5);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)(sw.c - cbase) * kBTileBytes) : smem_u32(ring + (size_t)slot * kStage + kStageBytes);
-        const uint32_t dcol = tmemD0 + b * (kBlocks * N), acol = tmemA0 + b * kACols;
+        TP(if (tr && lane == 0 && i < 64) g_mma_trace[1][i] = clock64();)
+        const int nc = sw.nc();
+        if (elect_one()) {
 #pragma unroll
-        for (int step = 0; step < 8; ++step) {  // K = 32 per step
-          const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
-          if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
-            umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
-          } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
-            umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
-          } else {
-            const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
-            umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
+        for (int cc = 0; cc < C; ++cc) {
+          if (cc < nc) {
+            const uint32_t bbase = FUSED ? smem_u32(bres + (size_t)(sw.c - cbase + cc) * kBTileBytes)
+                                         : smem_u32(ring + (size_t)slot * kStage + C * kStageBytes + cc * kBTileBytes);
+            const uint32_t dcol = tmemD0 + b * kDCols + cc * (kBlocks * N), acol = tmemA0 + ba * kACols + cc * 64;
+#pragma unroll
+            for (int step = 0; step < 8; ++step) {  // K = 32 per step
+              const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
+              if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
+                umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
+              } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
+                umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
+              } else {
+                const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
+                umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
+              }
+            }
           }
         }
         umma_commit(mdone0 + 8 * b);
+        if (F::kConv) umma_commit(afree0 + 8 * ba);
         umma_commit(empty0 + 8 * slot);
+        }
+        __syncwarp();
+        TP(if (tr && lane == 0 && i < 64) g_mma_trace[2][i] = clock64();)
         sw.next(a);
-        if (sw.live(a)) sw.next(a);
       }
     }
   } else if (warp < kConvWarps && !F::kConv) {
     // nothing to convert: the MMA reads the stage as it lies
   } else if (warp < kConvWarps) {
     // ------------------------------------------------------------------ converters
-    // Two groups of four warps take alternate stages, so two stages are being converted at any
-    // time and one group's barrier waits and TMEM-store latency hide behind the other's work.
-    // Thread = row r of the tile: the stage's eight 16-byte units of that row.
+    // Two groups of four warps convert alternate stages (thread = row r of the tile), so two stages
+    // are in conversion at any time: a stage's conversion is a fixed latency of well over a
+    // thousand cycles whatever its size, and what counts is how many run side by side.  Both groups
+    // follow every stage's barriers in order, also those of the stages they do not convert, so no
+    // barrier phase is ever skipped (a parity wait can only tell the current phase from the one
+    // before it).
     const int q4 = warp & 3, grp = warp >> 2;
     const int r = q4 * 32 + lane;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
-    if (grp == 1 && sw.live(a)) sw.next(a);
-    for (int i = grp; sw.live(a) && ok; i += 2) {
-      int b = i % NB, slot = i % S;
-      if (i >= NB) ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, ((i - NB) / NB) & 1, a.status, 3));
-      // stage i-1 first: see the note at the MMA issuers' wait (a group skips every other stage)
-      if (ok && i >= 1) ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * ((i - 1) % S), ((i - 1) / S) & 1, a.status, 10));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 4));
+    for (int i = 0; sw.live(a) && ok; ++i, sw.next(a)) {
+      const int ba = i % NA, slot = i % S;
+      ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 4));
+      if (ok && i >= NA) ok = __all_sync(0xffffffffu, mbar_wait(afree0 + 8 * ba, ((i - NA) / NA) & 1, a.status, 3));
       if (!ok) break;
+      if ((i & 1) != grp) continue;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      TP(if (tr && q4 == 0 && lane == 0 && i < 64) g_mma_trace[3][i] = clock64();)
       const unsigned char* st = ring + (size_t)slot * kStage;
-      // ---- this row of the stage: 256 nibbles -> 256 bytes -> 64 TMEM columns ----
-      uint4 qv[8];
+      // ---- this row of each chunk of the stage: 256 nibbles -> 256 bytes -> 64 TMEM columns ----
+      const int nc = sw.nc();
 #pragma unroll
-      for (int u = 0; u < 8; ++u) qv[u] = *reinterpret_cast<const uint4*>(st + r * 128 + ((u ^ (r & 7)) << 4));
+      for (int cc = 0; cc < C; ++cc) {
+        if (cc < nc) {
+          uint4 qv[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
-        uint32_t regs[8];
+          for (int u = 0; u < 8; ++u) {
+            if (DBG(2)) qv[u] = make_uint4(r, u, cc, i);  // tuning: no shared-memory loads
+            else qv[u] = *reinterpret_cast<const uint4*>(st + cc * kStageBytes + r * 128 + ((u ^ (r & 7)) << 4));
+          }
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
-          regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
+          for (int u = 0; u < 8; ++u) {
+            uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
+            uint32_t regs[8];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              regs[2 * w + 0] = ws[w] & 0x0F0F0F0Fu;         // elements 0,2,4,6 of the word
+              regs[2 * w + 1] = (ws[w] >> 4) & 0x0F0F0F0Fu;  // elements 1,3,5,7
+            }
+            if (!DBG(1)) tmem_st8(tmemA0 + lane_base + ba * kACols + cc * 64 + u * 8, regs);
+            else if ((regs[0] ^ regs[3] ^ regs[5] ^ regs[7]) == 0x12345678u) *last_flag = 1;  // tuning: no TMEM stores
+          }
         }
-        tmem_st8(tmemA0 + lane_base + b * 64 + u * 8, regs);
       }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -459,11 +518,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       // shared-memory reads and TMEM stores before the elected lane's releasing arrival).
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(aready0 + 8 * b);
+        mbar_arrive(aready0 + 8 * ba);
         mbar_arrive(empty0 + 8 * slot);
       }
-      sw.next(a);
-      if (sw.live(a)) sw.next(a);
+      TP(if (tr && q4 == 0 && lane == 0 && i < 64) g_mma_trace[4][i] = clock64();)
     }
   } else {
     // ------------------------------------------------------------------ epilogue
@@ -486,32 +544,43 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     constexpr int kSub = kHB * N <= 64 ? kHB : 64 / N;      // blocks per pass (at most 64 columns in registers)
     constexpr int NLD = kSub * N / 16;                      // 16-column loads per pass
     for (int i = 0; sw.live(a) && ok; ++i) {
-      int b = i % NB, slot = i % S;
+      int b = i % ND, slot = i % S;
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
-      uint4 mv = make_uint4(0, 0, 0, 0);
+      uint4 mvs[C];
+      const int nc = sw.nc();
       if (ok) {
-        mv = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStage + kStageWBytes + r * 16);
-        // the scale data is in registers: one lane releases the stage for the warp (the value is
-        // consumed by the shuffle, so every lane's load has completed before the arrival)
-        const uint32_t seen = __reduce_or_sync(0xffffffffu, mv.x | 1u);
+        uint32_t seen = 1u;
+#pragma unroll
+        for (int cc = 0; cc < C; ++cc) {
+          mvs[cc] = make_uint4(0, 0, 0, 0);
+          if (cc < nc) mvs[cc] = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStage + cc * kStageBytes + kStageWBytes + r * 16);
+          seen |= mvs[cc].x;
+        }
+        // the scale data is in registers: one lane releases the stage for the warp (the values are
+        // consumed by the shuffle, so every lane's loads have completed before the arrival)
+        seen = __reduce_or_sync(0xffffffffu, seen);
         if (lane == 0 && seen) mbar_arrive(empty0 + 8 * slot);
-        ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, (i / NB) & 1, a.status, 7));
+        ok = __all_sync(0xffffffffu, mbar_wait(mdone0 + 8 * b, (i / ND) & 1, a.status, 7));
       }
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t meta[4] = {mv.x, mv.y, mv.z, mv.w};
-      const int gbase = sw.c * kBlocks;
+      TP(if (tr && et == 0 && i < 64) g_mma_trace[5][i] = clock64();)
+#pragma unroll
+      for (int cc = 0; cc < C; ++cc) {
+      if (cc < nc) {
+      const uint32_t meta[4] = {mvs[cc].x, mvs[cc].y, mvs[cc].z, mvs[cc].w};
+      const int gbase = (sw.c + cc) * kBlocks;
 #pragma unroll
       for (int sub = 0; sub < kHB / kSub; ++sub) {
         const int blk0 = half * kHB + sub * kSub;  // first block of this pass
         uint32_t t[NLD][16];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          tmem_ld16(tmemD0 + lane_base + b * (kBlocks * N) + blk0 * N + l * 16, t[l]);
+          tmem_ld16(tmemD0 + lane_base + b * kDCols + cc * (kBlocks * N) + blk0 * N + l * 16, t[l]);
         }
 #pragma unroll
         for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[l]);
-        if (sub == kHB / kSub - 1) {
+        if (sub == kHB / kSub - 1 && cc == nc - 1) {  // the stage's last load: its accumulators are free
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
           if (lane == 0) mbar_arrive(dfree0 + 8 * b);
@@ -556,6 +625,9 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
           }
         }
       }
+      }  // cc < nc
+      }  // chunks of the stage
+      TP(if (tr && et == 0 && i < 64) g_mma_trace[6][i] = clock64();)
       const bool item_done = sw.last_chunk();
       const int tile = sw.tile, split = sw.split;
       sw.next(a);
@@ -614,6 +686,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     }
   }
 
+  TP(if (tr && tid == 0) g_mma_trace[7][1] = clock64();)
   // ---- wind down: everyone meets, outstanding copies are drained, TMEM is returned ----
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -763,15 +836,18 @@ static int choose_splits(const MmaArgs& a, int sm_count) {
   return splits;
 }
 
-template <int N, int DIGITS, int MB, int FMT, bool FUSED>
+int g_mma_dbg = 0;  // tuning build only
+
+template <int N, int DIGITS, int MB, int FMT, bool FUSED, int C>
 static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep, int stages, int splits) {
   MmaArgs a = a0;
+  a.dbg = g_mma_dbg;
   DeviceState& st = device_state(w.device);
   a.stages = stages;
   a.splits = splits;
   a.items = a.ntiles * splits;
   a.cmax = (a.nchunks + splits - 1) / splits;
-  size_t smem = MmaSmem<N, FMT, FUSED>::bytes(stages, a.batch, a.in_dim, a.cmax);
+  size_t smem = MmaSmem<N, FMT, FUSED, C>::bytes(stages, a.batch, a.in_dim, a.cmax);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -788,7 +864,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
     GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80>, a.x,
                                  const_cast<unsigned char*>(a.xb), const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
   }
-  auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT, FUSED>;
+  auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT, FUSED, C>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   int grid = a.items < st.sm_count ? a.items : st.sm_count;
   // FUSED: a CTA prepares the activations of one K range, so all its items must be of one split:
@@ -801,8 +877,15 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   return GOPH_OK;
 }
 
-template <int N, int DIGITS, int MB, int FMT>
-static int launch_one(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
+// Chunks per stage: two for the formats that convert, when a stage's A buffer and accumulators fit
+// the tensor memory twice.
+template <int N, int FMT>
+constexpr int stage_chunks() {
+  return (Fmt<FMT>::kConv && 2 * (2 * 64 + 2 * Fmt<FMT>::kBlocks * N) <= 512) ? 2 : 1;
+}
+
+template <int N, int DIGITS, int MB, int FMT, int C>
+static int launch_with_chunks(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
   const int sms = device_state(w.device).sm_count;
   const int splits = choose_splits<MB>(a, sms);
   const int cmax = (a.nchunks + splits - 1) / splits;
@@ -813,17 +896,26 @@ static int launch_one(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream,
   // blocks prepare the vector once for all CTAs (14336 x 4096: 14.1 against 15.2 us).
   // Option mlx_fuse = 0 always keeps the separate preparation kernel.
   if (N == 8 && options().mlx_fuse && splits <= sms && cmax <= 4) {
-    size_t fixed = MmaSmem<N, FMT, true>::bytes(0, a.batch, a.in_dim, cmax);
-    int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, true>::kStage) : 0;
+    size_t fixed = MmaSmem<N, FMT, true, C>::bytes(0, a.batch, a.in_dim, cmax);
+    int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, true, C>::kStage) : 0;
     if (stages > kMaxStages) stages = kMaxStages;
-    if (stages >= 5) return launch_impl<N, DIGITS, MB, FMT, N == 8>(w, a, stream, prep, stages, splits);
+    if (stages >= 3) return launch_impl<N, DIGITS, MB, FMT, N == 8, C>(w, a, stream, prep, stages, splits);
   }
-  size_t fixed = MmaSmem<N, FMT, false>::bytes(0, a.batch, a.in_dim);
-  int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, false>::kStage) : 0;
+  size_t fixed = MmaSmem<N, FMT, false, C>::bytes(0, a.batch, a.in_dim);
+  int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT, false, C>::kStage) : 0;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages < 3)
+  if (stages < 3) {
+    if (C > 1) return launch_with_chunks<N, DIGITS, MB, FMT, 1>(w, a, stream, prep);
     return fail(GOPH_E_UNSUPPORTED, "tensor-core path: activations of %d x %d leave no room for the ring", a.batch, a.in_dim);
-  return launch_impl<N, DIGITS, MB, FMT, false>(w, a, stream, prep, stages, splits);
+  }
+  return launch_impl<N, DIGITS, MB, FMT, false, C>(w, a, stream, prep, stages, splits);
+}
+
+template <int N, int DIGITS, int MB, int FMT>
+static int launch_one(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
+  constexpr int C = stage_chunks<N, FMT>();
+  if (C > 1 && options().mlx_chunks != 1) return launch_with_chunks<N, DIGITS, MB, FMT, C>(w, a, stream, prep);
+  return launch_with_chunks<N, DIGITS, MB, FMT, 1>(w, a, stream, prep);
 }
 
 template <int FMT>
@@ -1120,6 +1212,16 @@ static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, 
 }  // namespace goph
 
 using namespace goph;
+
+#ifdef GOPH_TUNING
+GOPH_API int goph_tuning_set_gemv(int dbg) {
+  goph::g_mma_dbg = dbg;
+  return 0;
+}
+GOPH_API int goph_tuning_probe_gemv(long long* out512) {
+  return cudaMemcpyFromSymbol(out512, g_mma_trace, 8 * 64 * sizeof(long long)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 GOPH_API int goph_mlx_gemv_noalloc_status(int device, int* out_status) {
   clear_error();

@@ -32,8 +32,9 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     rt.init(0)
     tune = dict((k, v) for k, v in opts if k.startswith("tune_"))
     opts = [(k, v) for k, v in opts if not k.startswith("tune_")]
-    if tune:  # tuning build only: parts of the small-batch kernel left out / chunk rotation off
+    if tune:  # tuning build only: parts of the kernels left out / chunk rotation off
         rt.lib().goph_tuning_set(int(tune.get("tune_dbg", 0)), int(tune.get("tune_rotate", 1)))
+        rt.lib().goph_tuning_set_gemv(int(tune.get("tune_gemv", 0)))
     for k, v in opts:
         rt.SetOption(k, v)
     nbytes = algorithmic_bytes(fmt, out_dim, in_dim, batch)
@@ -119,12 +120,12 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     if hasattr(rt.lib(), "goph_tuning_probe"):  # tuning build: clock64 timeline of one CTA's last launch
         import ctypes
         buf = (ctypes.c_longlong * 512)()
-        rt.lib().goph_tuning_probe(buf)
+        (rt.lib().goph_tuning_probe if batch > 8 or fmt == "fp8" else rt.lib().goph_tuning_probe_gemv)(buf)
         t0 = buf[7 * 64]
         names = ["loads_issued", "mma_sees_stage", "mma_issued", "conv_starts", "conv_done", "epi_sees_unit0", "epi_done"]
         res["trace"] = {"end": buf[7 * 64 + 1] - t0, "pdl_wait_done": buf[7 * 64 + 2] - t0}
         for e, n in enumerate(names):
-            res["trace"][n] = [buf[e * 64 + i] - t0 for i in range(20) if buf[e * 64 + i]]
+            res["trace"][n] = [buf[e * 64 + i] - t0 for i in range(40) if buf[e * 64 + i]]
     for h in handles:
         h.Free()
     return res
