@@ -57,6 +57,18 @@ struct FP8Fmt {
   }
 };
 
+// The same product on the tensor-core layout (one 32 KiB block per 128 rows x 256 bytes, 16-byte
+// units swizzled inside a block row): only the address of a unit differs.  A warp's 32 units of a
+// row are two runs of 256 contiguous bytes.  Used for the batches of up to 8 rows, which the
+// CUDA cores serve better than the tensor-core kernel's three-piece activations.
+struct FP8TiledFmt : FP8Fmt {
+  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
+    const int r = row & 127, u = unit & 15;
+    const size_t blk = (size_t)(row >> 7) * a.nchunks + (unit >> 4);
+    t.q = ld_stream(reinterpret_cast<const uint4*>(a.w + blk * 32768 + r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4)));
+  }
+};
+
 // Rows whose length is not a multiple of 16 bytes cannot be read as aligned 16-byte units:
 // one warp per row, byte loads.
 __global__ void __launch_bounds__(kGThreads)
@@ -226,8 +238,8 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
                 (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
   if (int rc = use_device(w->device)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (w->tiled) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
-  if (w->in_dim % 16 != 0) {
+  if (w->tiled && batch > 8) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
+  if (!w->tiled && w->in_dim % 16 != 0) {
     fp8_gemv_ragged_kernel<<<(w->out_dim + kGWarps - 1) / kGWarps, kGThreads, 0, s>>>(
         w->weight, w->scale, w->bias, x_dev, out_dev, w->out_dim, w->in_dim, batch);
     GOPH_CUDA(cudaGetLastError());
@@ -235,7 +247,8 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
   }
   StreamArgs a;
   memset(&a, 0, sizeof a);
-  a.w = w->weight;
+  a.w = w->tiled ? w->tiled : w->weight;
+  a.nchunks = w->in_dim / 256;
   a.aux = w->scale;
   a.bias = w->bias;
   a.out = out_dev;
@@ -245,6 +258,7 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
   a.units = w->in_dim / 16;
   a.row_bytes = w->in_dim;
   const int force_rows = options().fp8_rows;
+  if (w->tiled) return stream_launch<FP8TiledFmt>(a, w->device, batch, s, force_rows);
   return stream_launch<FP8Fmt>(a, w->device, batch, s, force_rows);
 }
 

@@ -19,19 +19,26 @@
 //     exact integers, one fused multiply-add), scales by 2^(E-26) and forms
 //     s_g * dot + b_g * sum(x)  in f32 — mlx.GemvTo's expression (backends/mlx/gemv.go:178-209).
 //
-// Pipeline of one CTA (448 threads, persistent over (128-row tile, K range) items):
-//   TMA producer warp: per 256-element chunk one bulk copy of the weight's 18 KiB block (the
-//     tiled layout stores exactly the shared-memory image of a stage, so every copy is one
-//     sequential burst) into a ring of up to 8 stages guarded by full/empty mbarriers.
-//     A third copy brings the chunk's B tile (the digits of x, laid out for the tensor core by
-//     mlx_prep_x_kernel, which runs once per launch in front of this kernel).
-//   8 converter warps: thread = (row, half chunk): swizzled LDS.128 -> bytes -> tcgen05.st into
-//     a four-deep ring of A buffers in TMEM.
-//   MMA thread: 8 tcgen05.mma (M128 x N x K32, A from TMEM, B straight from the stage) per
-//     chunk, tcgen05.commit to the accumulator's and the stage's mbarriers.
-//   4 epilogue warps: tcgen05.ld of the four group blocks, scales, running sums in registers;
-//     at the end of an item either store, or (K split) write partials to scratch and let the
-//     CTA that arrives last add them in split order (result independent of arrival order).
+// Pipeline of one CTA (18 warps; persistent over
+// (128-row tile, K range) items; a stage is one 256-element chunk of the tile, or two chunks for
+// the nibble formats when tensor memory has the columns):
+//   TMA producer warp: one bulk copy per stage of the weight's blocks (the tiled layout stores
+//     exactly the shared-memory image of a stage, so every copy is one sequential burst) into a
+//     ring of up to 8 stages guarded by full/empty mbarriers, and one of the stage's B tiles
+//     (the digits of x, laid out for the tensor core by mlx_prep_x_kernel in front of this
+//     kernel, or by this CTA itself for short K ranges).  The first two stages are asked for at
+//     once, the rest of the ring when the first has landed.
+//   8 converter warps in two groups that take alternate stages, thread = row of the tile:
+//     swizzled LDS.128 -> bytes -> tcgen05.st into a ring of A buffers in TMEM (two to four
+//     deep, as the 512 columns allow).  Both groups follow every stage's barriers.
+//   MMA warp: waits as a warp, one elected lane issues 8 tcgen05.mma (M128 x N x K32, A from
+//     TMEM, B straight from the stage) per chunk and commits to the accumulators', the A
+//     buffer's and the stage's mbarriers.  Q8_0 reads A from the stage as it lies (no converters).
+//   Epilogue warps, two per TMEM lane quarter, each with its share of a
+//     stage's accumulator blocks: tcgen05.ld, scales, running sums in registers; at the end of
+//     an item the parts are added through shared memory and either stored, or (K split) written
+//     to scratch, where the CTA that arrives last adds them in split order (result independent
+//     of arrival order).
 // Every wait is bounded (~2 s): a waiter that gives up records a code in the status word and
 // the CTA winds down (copies drained, TMEM returned) instead of spinning.
 #include <string.h>
@@ -77,7 +84,11 @@ enum { FMT_MLX4 = 0, FMT_Q4K = 1, FMT_Q80 = 2 };
 template <int FMT>
 struct Fmt {
   static constexpr bool kConv = FMT != FMT_Q80;                 // nibbles -> bytes through TMEM
-  static constexpr int kBlocks = FMT == FMT_MLX4 ? 4 : 8;       // accumulator blocks per stage
+  // accumulator blocks per 256-element chunk.  Q4_K: one block per PAIR of 32-element sub-blocks;
+  // the two sub-blocks keep their sums apart inside the block because the activation digits of
+  // the even sub-block stand in the first half of the B rows (zeros in the odd K steps) and those
+  // of the odd sub-block in the second half: accumulator columns [0, N/2) and [N/2, N)
+  static constexpr int kBlocks = FMT == FMT_Q80 ? 8 : 4;
   static constexpr int kGroup = FMT == FMT_MLX4 ? 64 : 32;      // elements per scale
   static constexpr int kStageWBytes = kTileRows * (FMT == FMT_Q80 ? 256 : 128);
   static constexpr int kStageBytes = kStageWBytes + kStageMBytes;  // the B tile follows
@@ -85,16 +96,27 @@ struct Fmt {
 constexpr int kStageWBytes = Fmt<FMT_MLX4>::kStageWBytes;
 constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
 
-constexpr int kConvWarps = 8, kEpiWarps = 8;  // two epilogue warps per TMEM lane quarter: each takes half of a stage's accumulator blocks
-constexpr int kConvThreads = kConvWarps * 32, kEpiThreads = kEpiWarps * 32;
-constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
+constexpr int kConvWarps = 8;
+constexpr int kConvThreads = kConvWarps * 32;
 constexpr int kMmaWarps = 1;  // the whole warp walks the stages, one elected lane issues
+// Epilogue warps per TMEM lane quarter; each takes an equal part of a stage's accumulator blocks.
+// Two for every format.  (Four were tried for Q4_K, whose epilogue is the slowest role of its
+// pipeline, 1300 cycles of arithmetic a stage against 500 for MLX: the eight extra warps made every
+// role slower and the LM-head product went from 66 to 74 us.)
+template <int N, int FMT>
+__host__ __device__ constexpr int epi_parts() {
+  return 2;
+}
+template <int N, int FMT>
+__host__ __device__ constexpr int mma_threads() {
+  return (kConvWarps + 4 * epi_parts<N, FMT>() + 1 + kMmaWarps) * 32;
+}
 // Stages whose copies are issued at once when a CTA starts.  If every CTA of the grid asked for its
 // whole ring at that moment (tens of MB), the memory system would serve those requests interleaved
 // and the first stage of every CTA would land last, microseconds late; the rest of the ring is
 // asked for when the first stage has arrived.
 constexpr int kFirstStages = 2;
-constexpr int kThreads = (kWarpMMA + kMmaWarps) * 32;
+constexpr int kThreads = mma_threads<8, FMT_MLX4>();  // of the instantiation the allocation-free entry point launches
 
 
 }  // namespace
@@ -176,6 +198,7 @@ __global__ void __launch_bounds__(64)
 mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, float* __restrict__ xtab, int batch,
                   int in_dim, int N) {
   constexpr int QBITS = DIGITS == 4 ? 26 : 19;  // |q| <= 2^QBITS keeps the top digit within a signed byte
+  constexpr bool PAIRED = G32 && !NATURAL;      // Q4_K: see Fmt::kPaired
   const int groups = in_dim / 64;
   const int m = blockIdx.x / groups, g = blockIdx.x - m * groups;
   const int t = threadIdx.x;
@@ -218,11 +241,17 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
   const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
   const int pos = NATURAL ? (k & 31) : 8 * w + 4 * (j & 1) + (j >> 1);  // byte along K inside the step (order of the A bytes)
   const size_t base = (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
+  const int db = N / 2;
 #pragma unroll
   for (int d = 0; d < DIGITS; ++d) {
     int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
     q = (q - dig) >> 7;
     int n = m * DIGITS + d;
+    if (PAIRED) {  // the other sub-block's half of the rows holds zeros at this K position
+      const int other = n + ((step & 1) ? 0 : db);
+      n += (step & 1) ? db : 0;
+      xb[base + (other >> 3) * 128 + (other & 7) * 16] = 0;
+    }
     xb[base + (n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
   }
 }
@@ -235,6 +264,8 @@ template <int DIGITS, bool G32, bool NATURAL, int N>
 __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int batch, int in_dim, unsigned char* bres,
                                               float* xsum, float* xfs, int warp, int lane, int nwarps, int cbegin, int cend) {
   constexpr int QBITS = DIGITS == 4 ? 26 : 19;
+  constexpr bool PAIRED = G32 && !NATURAL;
+  constexpr int db = N / 2;
   const int groups = in_dim / 64;
   const int ntab = G32 ? 2 * groups : groups;
   const int gbegin = 4 * cbegin, gcount = 4 * (cend - cbegin);  // the 64-element groups of chunks [cbegin, cend)
@@ -275,7 +306,12 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
       for (int d = 0; d < DIGITS; ++d) {
         int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
         q = (q - dig) >> 7;
-        const int n = m * DIGITS + d;
+        int n = m * DIGITS + d;
+        if (PAIRED) {
+          const int other = n + ((step & 1) ? 0 : db);
+          n += (step & 1) ? db : 0;
+          base[(other >> 3) * 128 + (other & 7) * 16] = 0;
+        }
         base[(n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
       }
     }
@@ -285,9 +321,13 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
 // N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
 // MB: activation rows the instantiation can take (MB * DIGITS <= N).
 template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false, int C = 1>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__((mma_threads<N, FMT>()), 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
-  static_assert(MB * DIGITS <= N, "the digits of the activation rows must fit the N columns");
+  constexpr int EP = epi_parts<N, FMT>();
+  constexpr int kEpiWarps = 4 * EP, kEpiThreads = kEpiWarps * 32;
+  constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
+  constexpr int kThreads = mma_threads<N, FMT>();
+  static_assert(MB * DIGITS * (FMT == FMT_Q4K ? 2 : 1) <= N, "the digits of the activation rows must fit the N columns");
   static_assert(N == 8 || N == 16 || N == 32, "accumulator blocks of 8, 16 or 32 columns");
   typedef Fmt<FMT> F;
   constexpr int kBlocks = F::kBlocks;
@@ -317,7 +357,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND]
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  float* pair = reinterpret_cast<float*>(tmem_holder + 4);  // [MB][128]: the second epilogue half's sums of an item
+  float* pair = reinterpret_cast<float*>(tmem_holder + 4);  // [EP-1][MB][128]: the sums of an item from the epilogue parts above 0
+  static_assert((EP - 1) * MB <= 8, "room for the parts' sums");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
@@ -444,10 +485,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
 #pragma unroll
             for (int step = 0; step < 8; ++step) {  // K = 32 per step
               const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
-              if (FMT == FMT_MLX4) {  // two steps accumulate into the block of their 64-element group
+              if (FMT != FMT_Q80) {  // two steps accumulate into the block of their 64 elements
                 umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
-              } else if (FMT == FMT_Q4K) {  // one block per 32-element sub-block
-                umma_i8_ts(dcol + step * N, acol + step * 8, bdesc, idesc, 0);
               } else {
                 const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
                 umma_i8_ss(dcol + step * N, adesc_hi | (uint64_t)((abase >> 4) & 0x3FFF), bdesc, idesc, 0);
@@ -525,10 +564,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    // Two warps per TMEM lane quarter: `half` 0 takes the first half of a stage's accumulator
-    // blocks, `half` 1 the second; each keeps its own running sums and the halves are added when
-    // an item (tile, K range) ends.
-    const int q4 = warp & 3, half = (warp - kConvWarps) >> 2;
+    // EP warps per TMEM lane quarter: part p takes the p-th share of a stage's accumulator
+    // blocks; each keeps its own running sums and the parts are added, in order, when an item
+    // (tile, K range) ends.
+    const int q4 = warp & 3, half = (warp - kConvWarps) >> 2;  // half: the part, 0 .. EP-1
     const int r = q4 * 32 + lane;  // row of the tile == TMEM lane
     const int et = tid - kConvThreads;
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
@@ -540,9 +579,10 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     }
-    constexpr int kHB = kBlocks / 2;                        // blocks of this half
+    constexpr int kHB = kBlocks / EP;                       // blocks of this part
     constexpr int kSub = kHB * N <= 64 ? kHB : 64 / N;      // blocks per pass (at most 64 columns in registers)
-    constexpr int NLD = kSub * N / 16;                      // 16-column loads per pass
+    constexpr bool kNarrow = kSub * N == 8;                 // a pass of one 8-column block: one 8-column load
+    constexpr int NLD = kNarrow ? 1 : kSub * N / 16;        // 16-column loads per pass
     for (int i = 0; sw.live(a) && ok; ++i) {
       int b = i % ND, slot = i % S;
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
@@ -576,10 +616,16 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         uint32_t t[NLD][16];
 #pragma unroll
         for (int l = 0; l < NLD; ++l) {
-          tmem_ld16(tmemD0 + lane_base + b * kDCols + cc * (kBlocks * N) + blk0 * N + l * 16, t[l]);
+          const uint32_t taddr = tmemD0 + lane_base + b * kDCols + cc * (kBlocks * N) + blk0 * N + l * 16;
+          if (kNarrow) tmem_ld8(taddr, *reinterpret_cast<uint32_t(*)[8]>(&t[l][0]));
+          else tmem_ld16(taddr, t[l]);
         }
 #pragma unroll
-        for (int l = 0; l < NLD; ++l) tmem_wait_ld(t[l]);
+        for (int l = 0; l < NLD; ++l) {
+          if (kNarrow) tmem_wait_ld(*reinterpret_cast<uint32_t(*)[8]>(&t[l][0]));
+          else tmem_wait_ld(t[l]);
+        }
+        TP(if (tr && et == 0 && i == 2) g_mma_trace[7][12 + 2 * cc] = clock64();)
         if (sub == kHB / kSub - 1 && cc == nc - 1) {  // the stage's last load: its accumulators are free
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
           __syncwarp();
@@ -588,43 +634,73 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
 #pragma unroll
         for (int g = 0; g < kSub; ++g) {
           const int blk = blk0 + g;
-          // the block's multiplier of the integer dot and of the block's sum of x
-          float sc, bi;
-          if (FMT == FMT_MLX4) {  // {scale, bias} bf16 pair of the 64-element group
-            const uint32_t mw = blk == 0 ? meta[0] : blk == 1 ? meta[1] : blk == 2 ? meta[2] : meta[3];
-            sc = __uint_as_float(mw << 16);
-            bi = __uint_as_float(mw & 0xFFFF0000u);
-          } else if (FMT == FMT_Q4K) {  // (sc*d) and -(m*dmin), each rounded to f32 as dequantRowQ4KTo does
-            const int bit = 12 * blk, wi = bit >> 5, sh = bit & 31;
-            const uint32_t lo = wi == 0 ? meta[1] : wi == 1 ? meta[2] : meta[3];
-            const uint32_t hi = wi == 0 ? meta[2] : wi == 1 ? meta[3] : 0u;
-            const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
-            sc = __fmul_rn((float)(f & 63u), __half2float(__ushort_as_half((unsigned short)(meta[0] & 0xFFFFu))));
-            bi = -__fmul_rn((float)(f >> 6), __half2float(__ushort_as_half((unsigned short)(meta[0] >> 16))));
-          } else {  // f16 block scale
-            const uint32_t mw = (blk >> 1) == 0 ? meta[0] : (blk >> 1) == 1 ? meta[1] : (blk >> 1) == 2 ? meta[2] : meta[3];
-            sc = __half2float(__ushort_as_half((unsigned short)((mw >> (16 * (blk & 1))) & 0xFFFFu)));
-            bi = 0.f;
-          }
+          auto col = [&](int cidx) { return (int)t[(g * N + cidx) >> 4][(g * N + cidx) & 15]; };
+          auto digits_dot = [&](int c0) {  // the integer dot of the DIGITS columns from c0
+            if (DIGITS == 4) {
+              int lo = col(c0) + (col(c0 + 1) << 7), hi = col(c0 + 2) + (col(c0 + 3) << 7);
+              return fmaf((float)hi, 16384.f, (float)lo);
+            }
+            int lo = col(c0) + (col(c0 + 1) << 7);
+            return fmaf((float)col(c0 + 2), 16384.f, (float)lo);
+          };
+          if (FMT == FMT_Q4K) {
+            // the block holds two 32-element sub-blocks: columns [0, N/2) and [N/2, N); their
+            // multipliers (sc*d) and -(m*dmin), each rounded to f32 as dequantRowQ4KTo does
+            constexpr int db = N / 2;
+            const float d16 = __half2float(__ushort_as_half((unsigned short)(meta[0] & 0xFFFFu)));
+            const float dmin16 = __half2float(__ushort_as_half((unsigned short)(meta[0] >> 16)));
 #pragma unroll
-          for (int m = 0; m < MB; ++m) {
-            if (m < a.batch) {
-              auto col = [&](int cidx) { return (int)t[(g * N + cidx) >> 4][(g * N + cidx) & 15]; };
-              float dotq;
-              if (DIGITS == 4) {
-                int lo = col(4 * m) + (col(4 * m + 1) << 7), hi = col(4 * m + 2) + (col(4 * m + 3) << 7);
-                dotq = fmaf((float)hi, 16384.f, (float)lo);
-              } else {
-                int lo = col(3 * m) + (col(3 * m + 1) << 7);
-                dotq = fmaf((float)col(3 * m + 2), 16384.f, (float)lo);
+            for (int hh = 0; hh < 2; ++hh) {
+              const int sub = 2 * blk + hh, bit = 12 * sub, wi = bit >> 5, sh = bit & 31;
+              const uint32_t lo = wi == 0 ? meta[1] : wi == 1 ? meta[2] : meta[3];
+              const uint32_t hi = wi == 0 ? meta[2] : wi == 1 ? meta[3] : 0u;
+              const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+              // Integer -> float through the exponent trick (an add and a subtract on the full-rate
+              // pipes; eight sub-blocks a chunk would otherwise queue on the conversion unit).  Exact
+              // while |v| < 2^22: the 6-bit fields trivially, and a column sums 32 products of a
+              // nibble and a digit in [-64, 63], so |c0 + 128 c1| <= 30720 * 129 < 2^22.
+              auto small_f = [](uint32_t v) { return __uint_as_float(0x4B000000u | v) - 8388608.f; };
+              auto int_f = [](int v) { return __int_as_float(0x4B400000 + v) - 12582912.f; };
+              const float sc = __fmul_rn(small_f(f & 63u), d16), bi = -__fmul_rn(small_f(f >> 6), dmin16);
+              const int ti = 2 * gbase + sub;  // the sub-block's entry of the per-32 tables
+              auto paired_dot = [&](int c0) {
+                const float lo = int_f(col(c0) + (col(c0 + 1) << 7));
+                const float hi = DIGITS == 4 ? int_f(col(c0 + 2) + (col(c0 + 3) << 7)) : int_f(col(c0 + 2));
+                return fmaf(hi, 16384.f, lo);
+              };
+#pragma unroll
+              for (int m = 0; m < MB; ++m) {
+                if (MB == 1 || m < a.batch) {
+                  const float dot = paired_dot(hh * db + DIGITS * m) * xfs[m * groups + ti];
+                  acc[m] = fmaf(sc, dot, acc[m]);
+                  acc[m] = fmaf(bi, xsum[m * groups + ti], acc[m]);
+                }
               }
-              float dot = dotq * xfs[m * groups + gbase + blk];
-              acc[m] = fmaf(sc, dot, acc[m]);
-              if (FMT != FMT_Q80) acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
+            }
+          } else {
+            // the block's multiplier of the integer dot and of the block's sum of x
+            float sc, bi;
+            if (FMT == FMT_MLX4) {  // {scale, bias} bf16 pair of the 64-element group
+              const uint32_t mw = blk == 0 ? meta[0] : blk == 1 ? meta[1] : blk == 2 ? meta[2] : meta[3];
+              sc = __uint_as_float(mw << 16);
+              bi = __uint_as_float(mw & 0xFFFF0000u);
+            } else {  // f16 block scale
+              const uint32_t mw = (blk >> 1) == 0 ? meta[0] : (blk >> 1) == 1 ? meta[1] : (blk >> 1) == 2 ? meta[2] : meta[3];
+              sc = __half2float(__ushort_as_half((unsigned short)((mw >> (16 * (blk & 1))) & 0xFFFFu)));
+              bi = 0.f;
+            }
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+              if (MB == 1 || m < a.batch) {
+                const float dot = digits_dot(DIGITS * m) * xfs[m * groups + gbase + blk];
+                acc[m] = fmaf(sc, dot, acc[m]);
+                if (FMT != FMT_Q80) acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
+              }
             }
           }
         }
       }
+      TP(if (tr && et == 0 && i == 2) g_mma_trace[7][13 + 2 * cc] = clock64() + (long long)(__float_as_int(acc[0]) & 1);)
       }  // cc < nc
       }  // chunks of the stage
       TP(if (tr && et == 0 && i < 64) g_mma_trace[6][i] = clock64();)
@@ -632,18 +708,23 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       const int tile = sw.tile, split = sw.split;
       sw.next(a);
       if (!item_done) continue;
-      // ---- the item is complete: add the two halves' sums (half 1 -> shared memory -> half 0) ----
-      if (half == 1) {
+      // ---- the item is complete: add the parts' sums (parts above 0 -> shared memory -> part 0) ----
+      if (half != 0) {
 #pragma unroll
         for (int m = 0; m < MB; ++m) {
-          pair[m * kTileRows + r] = acc[m];
+          pair[((half - 1) * MB + m) * kTileRows + r] = acc[m];
           acc[m] = 0.f;
         }
       }
+      TP(if (tr && et == 0 && i < 16) g_mma_trace[7][8] = clock64();)
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      TP(if (tr && et == 0 && i < 16) g_mma_trace[7][9] = clock64();)
       if (half == 0) {
 #pragma unroll
-        for (int m = 0; m < MB; ++m) acc[m] += pair[m * kTileRows + r];
+        for (int m = 0; m < MB; ++m) {
+#pragma unroll
+          for (int p = 0; p < EP - 1; ++p) acc[m] += pair[(p * MB + m) * kTileRows + r];
+        }
       }
       const int row = tile * kTileRows + r;
       if (a.splits == 1) {
@@ -654,7 +735,9 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
             acc[m] = 0.f;
           }
         }
+        TP(if (tr && et == 0 && i < 16) g_mma_trace[7][10] = clock64();)
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // pair is free for the next item
+        TP(if (tr && et == 0 && i < 16) g_mma_trace[7][11] = clock64();)
       } else {
         // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
         // partials in split order (so the result does not depend on arrival order) and stores.
@@ -871,7 +954,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   // item w is split w % splits, and a grid that is a multiple of the splits keeps that fixed per CTA
   if (FUSED && a.items > grid) grid -= grid % splits;
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(mma_threads<N, FMT>());
   cfg.dynamicSmemBytes = smem;
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
@@ -936,7 +1019,8 @@ static int tiled_launch(const TiledDesc& w, float* out, const float* x, int batc
   a.ntiles = (w.out_dim + kTileRows - 1) / kTileRows;
   a.nchunks = w.in_dim / kChunkK;
   // activation rows one launch can take: the accumulator blocks of a stage must fit TMEM twice
-  const int cap = FMT == FMT_Q4K ? (digits == 3 ? 5 : 4) : 8;
+  const int cap = FMT == FMT_Q4K ? (digits == 3 ? 5 : 4) : 8;  // Q4_K needs two columns per digit
+  constexpr bool kQ4K = FMT == FMT_Q4K;
   for (int b0 = 0; b0 < batch;) {
     int nb = batch - b0 < cap ? batch - b0 : cap;
     a.x = x + (size_t)b0 * w.in_dim;
@@ -945,15 +1029,16 @@ static int tiled_launch(const TiledDesc& w, float* out, const float* x, int batc
     const bool prep = !(x_prepared && batch <= cap);
     int rc;
     if (digits == 3) {
-      if (nb <= 2) rc = launch_one<8, 3, 2, FMT>(w, a, stream, prep);
-      else if (nb <= 5) rc = launch_one<16, 3, 5, FMT>(w, a, stream, prep);
-      else if (FMT != FMT_Q4K) rc = launch_one<32, 3, 8, FMT == FMT_Q4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
+      if (kQ4K && nb == 1) rc = launch_one<8, 3, 1, FMT>(w, a, stream, prep);
+      else if (nb <= 2) rc = launch_one<kQ4K ? 16 : 8, 3, 2, FMT>(w, a, stream, prep);
+      else if (nb <= 5) rc = launch_one<kQ4K ? 32 : 16, 3, 5, FMT>(w, a, stream, prep);
+      else if (!kQ4K) rc = launch_one<32, 3, 8, kQ4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
       else rc = fail(GOPH_E_UNSUPPORTED, "batch slice too wide");
     } else {
       if (nb == 1) rc = launch_one<8, 4, 1, FMT>(w, a, stream, prep);
-      else if (nb == 2) rc = launch_one<8, 4, 2, FMT>(w, a, stream, prep);
-      else if (nb <= 4) rc = launch_one<16, 4, 4, FMT>(w, a, stream, prep);
-      else if (FMT != FMT_Q4K) rc = launch_one<32, 4, 8, FMT == FMT_Q4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
+      else if (nb == 2) rc = launch_one<kQ4K ? 16 : 8, 4, 2, FMT>(w, a, stream, prep);
+      else if (nb <= 4) rc = launch_one<kQ4K ? 32 : 16, 4, 4, FMT>(w, a, stream, prep);
+      else if (!kQ4K) rc = launch_one<32, 4, 8, kQ4K ? FMT_MLX4 : FMT>(w, a, stream, prep);
       else rc = fail(GOPH_E_UNSUPPORTED, "batch slice too wide");
     }
     if (rc) return rc;

@@ -315,9 +315,11 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       };
       // The weights do not depend on the kernel in front: fill the ring with them first, then wait
       // for the prepared activations and add the B tiles of those stages.
+      // (Only the first two stages at once: a grid that asked for all its rings at the same moment
+      // would see every CTA's first stage land last.  The rest follows when the first stage is in.)
       int i = 0;
       StageWalk sw0 = sw;
-      for (; i < S && sw0.live(a); ++i, sw0.next(a)) {
+      for (; i < S && i < 2 && sw0.live(a); ++i, sw0.next(a)) {
         mbar_expect_tx(full0 + 8 * i, DBG(2) ? kWBytes : kStage);
         load_w(i, sw0);
       }
@@ -329,7 +331,8 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
         const int slot = i % S, round = i / S;
-        ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 301);
+        if (round > 0) ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 301);
+        else if (i == 2) ok = mbar_wait(full0, 0, a.status, 309);
         if (!ok) break;
         mbar_expect_tx(full0 + 8 * slot, DBG(2) ? kWBytes : kStage);
         load_w(slot, sw);

@@ -124,6 +124,7 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
         t0 = buf[7 * 64]
         names = ["loads_issued", "mma_sees_stage", "mma_issued", "conv_starts", "conv_done", "epi_sees_unit0", "epi_done"]
         res["trace"] = {"end": buf[7 * 64 + 1] - t0, "pdl_wait_done": buf[7 * 64 + 2] - t0}
+        res["trace"]["item_end"] = [buf[7 * 64 + k] - t0 for k in range(8, 16) if buf[7 * 64 + k]]
         for e, n in enumerate(names):
             res["trace"][n] = [buf[e * 64 + i] - t0 for i in range(40) if buf[e * 64 + i]]
     for h in handles:
