@@ -474,6 +474,7 @@ static int op_launch(void (*k)(KArgs...), dim3 grid, int threads, size_t smem, v
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, k, KArgs(args)...));
   return GOPH_OK;
 }

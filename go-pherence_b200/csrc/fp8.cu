@@ -238,8 +238,13 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
                 (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
   if (int rc = use_device(w->device)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  if (w->tiled && batch > 8) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
+  // Tensor-core layout: two rows and more go to the small-batch GEMM (one pass over the weights for
+  // up to 16 f32 rows; measured 8192 x 8192, 4 rows: 26 us against 79 us for the CUDA-core kernel),
+  // and so does a single row against a long K (8192 x 28672: 69 against 146 us); a single row of
+  // ordinary length is served best by the CUDA-core streaming kernel (128256 x 4096: 0.88 of the copy rate).
+  if (w->tiled && (batch > 1 || w->in_dim > 16384)) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
   if (!w->tiled && w->in_dim % 16 != 0) {
+    note_launch();
     fp8_gemv_ragged_kernel<<<(w->out_dim + kGWarps - 1) / kGWarps, kGThreads, 0, s>>>(
         w->weight, w->scale, w->bias, x_dev, out_dev, w->out_dim, w->in_dim, batch);
     GOPH_CUDA(cudaGetLastError());

@@ -313,6 +313,7 @@ GOPH_API int goph_gather_all(goph_gather* g, const float* src_dev, int rows, int
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, gather_exchange_kernel, a));
   *result_dev = g->result;
   return GOPH_OK;
@@ -389,6 +390,7 @@ GOPH_API int goph_moe_forward_sharded(goph_gather* g, goph_moe_layer* m, float* 
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, gather_sum_kernel, (const float*)gathered, out_dev, (long long)n, g->world));
   return GOPH_OK;
 }

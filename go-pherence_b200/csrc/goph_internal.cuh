@@ -64,6 +64,9 @@ struct Options {
 };
 Options& options();
 
+// Counts a compute-kernel launch made for the caller (goph_launch_count reads the total).
+void note_launch();
+
 // Status word of the decode-step kernels on the current device (0, or 401 / 402 when a kernel found
 // the position word outside [0, max_seq)).
 int decode_ops_status();

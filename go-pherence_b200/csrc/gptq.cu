@@ -109,6 +109,7 @@ void release(goph_gptq_weight* w) {
 
 template <int M>
 void launch_rows(const goph_gptq_weight* w, const float* x, float* out, cudaStream_t s) {
+  note_launch();
   gptq_rows_kernel<M><<<(w->out_dim + kWarps - 1) / kWarps, kWarps * 32, 0, s>>>(w->words, w->scales, w->gidx, x, out,
                                                                                w->in_dim, w->out_dim, w->groups);
 }

@@ -874,12 +874,14 @@ static int launch_stream(const goph_mlx_weight* const* ws, float* const* outs, i
   cfg.stream = stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, k, a));
   return GOPH_OK;
 }
 
 static int launch_generic(const goph_mlx_weight* w, float* out, const float* x, int batch, cudaStream_t stream) {
   int grid = (w->out_dim + kWarps - 1) / kWarps;
+  note_launch();
   if (w->sb_bf16)
     mlx_gemv_generic_kernel<true><<<grid, kThreads, 0, stream>>>(w->qweight, w->sb, x, out, w->out_dim, w->in_dim,
                                                                  w->group_size, w->groups, batch);
@@ -1123,6 +1125,7 @@ GOPH_API int goph_mlx_program_run(goph_mlx_program* p, void* stream) {
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, p->kernel, (const MlxArgs*)p->ops, p->nops, p->words, p->words + 1,
                                reinterpret_cast<int*>(p->words + 2)));
   return GOPH_OK;

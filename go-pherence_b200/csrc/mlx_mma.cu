@@ -944,6 +944,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
     // activations -> digits, sums and scales, once per launch
     cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
     cfg.blockDim = dim3(64);
+    note_launch();
     GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80>, a.x,
                                  const_cast<unsigned char*>(a.xb), const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
   }
@@ -956,6 +957,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(mma_threads<N, FMT>());
   cfg.dynamicSmemBytes = smem;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
 }
@@ -1281,6 +1283,7 @@ static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, 
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(a.in_dim / 64);
   cfg.blockDim = dim3(64);
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS>, a.x, const_cast<unsigned char*>(a.xb),
                                const_cast<float*>(a.xtab), 1, a.in_dim, N));
   size_t smem = MmaSmem<N>::bytes(stages, 1, a.in_dim);
@@ -1290,6 +1293,7 @@ static int launch_noalloc(const goph_mlx_weight* w, float* out, const float* x, 
   cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
 }

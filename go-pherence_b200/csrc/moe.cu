@@ -605,6 +605,7 @@ static int moe_launch(void (*k)(KArgs...), dim3 grid, int threads, size_t smem, 
   cfg.stream = s;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, k, KArgs(args)...));
   return GOPH_OK;
 }

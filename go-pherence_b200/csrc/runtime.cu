@@ -5,6 +5,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "goph_internal.cuh"
 
 namespace goph {
@@ -38,6 +40,9 @@ static bool load_driver() {
 }
 
 DeviceState& device_state(int device) { return g_dev[device]; }
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 Options& options() { return g_opt; }
 
 void clear_error() { g_err[0] = 0; }
@@ -127,6 +132,13 @@ GOPH_API int goph_init_current_context(int* out_device) {
   g_ctx[device] = ctx;
   st.ready = true;
   *out_device = device;
+  return GOPH_OK;
+}
+
+GOPH_API int goph_launch_count(uint64_t* out_count) {
+  clear_error();
+  if (!out_count) return fail(GOPH_E_INVALID, "goph_launch_count: null result");
+  *out_count = g_launches.load(std::memory_order_relaxed);
   return GOPH_OK;
 }
 

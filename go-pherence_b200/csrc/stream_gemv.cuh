@@ -205,6 +205,7 @@ static int stream_launch(StreamArgs a, int device, int batch, cudaStream_t strea
     int tasks = (a.rows + R - 1) / R;
     int grid = (tasks + kGWarps - 1) / kGWarps;
     if (grid > st.sm_count * per_sm) grid = st.sm_count * per_sm;
+    note_launch();
     k<<<grid, kGThreads, smem, stream>>>(a);
     GOPH_CUDA(cudaGetLastError());
   }

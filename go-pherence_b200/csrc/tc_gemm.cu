@@ -737,12 +737,14 @@ int launch_pass(const GemmDesc& w, float* out, const void* x, int nb, GemmBufs* 
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(a.nchunks, NC / 8);
   cfg.blockDim = dim3(256);
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, tc_prep_x_kernel<NC, P, FMT, XBF16>, x, bufs->xb, bufs->xtab, nb, w.in_dim));
   auto kern = tc_gemm_kernel<NC, P, FMT>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
+  note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
 }

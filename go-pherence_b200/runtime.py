@@ -29,7 +29,7 @@ EXPORTS = [
     "goph_gptq_upload", "goph_gptq_free", "goph_gptq_resident_bytes", "goph_gptq_uses_mlx_kernels", "goph_gptq_gemm",
     "goph_gptq_dequant",
     "goph_mlx_upload", "goph_mlx_upload_dev", "goph_mlx_free", "goph_mlx_resident_bytes",
-    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_bf16", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc", "goph_mlx_gemv_noalloc_status",
+    "goph_mlx_dequant", "goph_mlx_gemv", "goph_mlx_gemm", "goph_mlx_gemm_bf16", "goph_mlx_gemm_multi", "goph_mlx_gemv_noalloc", "goph_mlx_gemv_noalloc_status", "goph_launch_count",
     "goph_mlx_gemm_host",
     "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
     "goph_gguf_project", "goph_gguf_project_pair", "goph_gguf_project_host",
@@ -266,6 +266,13 @@ def GemvMLXNoAlloc(out, x, w, stream=None):
         raise GophError(1, "nil buffer")
     _check(lib().goph_mlx_gemv_noalloc(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
                                        _mlx_handle(w), _stream_ptr(stream)))
+
+
+def LaunchCount():
+    """Compute kernels launched through the library by this process so far (goph_launch_count)."""
+    v = C.c_uint64(0)
+    _check(lib().goph_launch_count(C.byref(v)))
+    return v.value
 
 
 def GemvMLXNoAllocStatus():

@@ -89,14 +89,19 @@ int goph_sm_count(int device);
  *                 2 tensor-core layout whenever the shape allows.  "mlx_digits" and "mlx_splits"
  *                 apply to these products as well
  *   "fp8_layout"  the same choice for goph_fp8_upload (in_dim a multiple of 256, no NaN codes in the
- *                 weight): the tensor-core layout serves every batch size through the bf16
- *                 tensor-core kernel, the row-major layout the CUDA-core kernels
+ *                 weight): the tensor-core layout serves two activation rows and more (and a single
+ *                 row against more than 16384 inputs) through the bf16 tensor-core kernel and a
+ *                 single row through a CUDA-core streaming kernel; the row-major layout is served
+ *                 by the CUDA-core kernels alone
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
  *   "mlx_fuse"    1 (default): tensor-core launches of one or two activation rows make the activation
  *                 digits of their own K range inside the product kernel (one launch per product);
  *                 0: a separate preparation kernel in front of every product
+ *   "mlx_chunks"  256-element chunks per pipeline stage of the tensor-core GEMV: 0 (default) two for
+ *                 the nibble formats where tensor memory has the columns (up to 4 activation rows
+ *                 for MLX 4-bit, 2 for Q4_K), 1 always one
  *   "mlx_splits"  CTAs that share the K range of one 128-row tile (0 = chosen by shape)
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion
@@ -113,6 +118,12 @@ int goph_kernel_status(int device, int* out_status);
 /* Sets the device's status words back to 0 after the caller has dealt with a non-zero status
  * (the reference has no counterpart: it tears the context down).  Synchronises with the device. */
 int goph_kernel_status_clear(int device);
+/* No counterpart in the reference.  Number of compute kernels this process has launched through the
+ * library so far (products, their activation preparation, exchanges, decode-step operations; not
+ * the kernels of uploads and dequantisation).  A benchmark reads it before and after one step made
+ * of plain launches to know how many kernels a step is; launches replayed by a CUDA graph are
+ * counted when they are captured, not when the graph runs. */
+int goph_launch_count(uint64_t* out_count);
 /* nvidia.Malloc / MallocBytes / Buffer.Free (runtime/runtime.go:297-359, q8.go:166-177). */
 int goph_malloc(int device, uint64_t bytes, void** out_dev);
 int goph_free(int device, void* dev);
