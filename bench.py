@@ -112,16 +112,23 @@ def chain_ops(layers):
     return [(l, n, o, i) for l in range(layers) for n, o, i in LAYER_OPS] + [(layers, "lm_head", VOCAB, HIDDEN)]
 
 
+# Exact (power-of-two) factors on the scales that keep the chain's values in range: the gain of a
+# product is sqrt(in_dim * E[(n - 7.5)^2] * E[scale^2]) = 0.77 (in 4096) or 1.44 (in 14336) at
+# 0.125 and twice that at 0.25; a layer's four products then multiply to 1.3, 32 layers to ~5e3.
+CHAIN_GAIN = {"qkv": 0.125, "o": 0.25, "gate_up": 0.125, "down": 0.125, "lm_head": 0.125}
+
+
 def chain_weight(syn, name, l, out_dim, in_dim):
     """Every layer of a random-init model has its own weights; generation is the slow part on the
     host, so layers draw from 4 distinct seeds per projection (contents never repeat in L2: the
-    copies are separate device buffers).  Scales and biases are divided by 8 or 16 (exactly: they
-    are bf16 values) so that the chained activations neither overflow nor vanish over 129 products."""
+    copies are separate device buffers).  The biases are -7.5 x scale (rounded to bf16), so a weight
+    has mean zero and a product does not amplify the mean of its input — with the generator's -8 x
+    scale the mean grew fourfold per product and the chain overflowed after a few layers."""
     key = (name, l % 4)
     if key not in chain_weight.cache:
-        w, s, b = syn.mlx_weight(("chain",) + key, out_dim, in_dim, GS)
-        m = np.float32(0.125 if in_dim <= 4096 else 0.0625)  # keeps a layer's gain a little under one
-        chain_weight.cache[key] = (w, s * m, b * m)
+        w, s, _ = syn.mlx_weight(("chain",) + key, out_dim, in_dim, GS)
+        s = s * np.float32(CHAIN_GAIN[name])
+        chain_weight.cache[key] = (w, s, syn.bf16_round(np.float32(-7.5) * s))
     return chain_weight.cache[key]
 
 
@@ -220,6 +227,8 @@ class DecodeStepProjections:
                 rt.GemvMLX(oo, xo, full)
                 rt.Sync()
                 want = oo.Download()
+                if not (np.isfinite(got).all() and np.isfinite(want).all()):
+                    return float("inf")  # a chain that overflowed proves nothing
                 worst = max(worst, syn.rel_err(got, want))
                 for t in (full, xo, oo):
                     t.Free()
@@ -489,9 +498,13 @@ def run_ours(args):
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
             n0 = rt.LaunchCount()
-            wl.step(stream)
+            logits_ptr = wl.step(stream)
             wl.launches_per_step = rt.LaunchCount() - n0  # kernels of one step, counted by the library
     torch.cuda.synchronize()
+    lg = wl.logits_tensor(logits_ptr)
+    if not bool(torch.isfinite(lg).all()) or float(lg.abs().max()) == 0.0:
+        raise SystemExit("the chained activations overflowed or vanished: the step's logits are not finite, non-zero values")
+    logit_absmax = float(lg.abs().max())
     graph, graph_logits = None, 0
     if use_graph:
         graph = torch.cuda.CUDAGraph()
@@ -601,6 +614,7 @@ def run_ours(args):
                        "packed_weight_bytes_per_step": int(sum(0.5625 * o * i for _, _, o, i in chain_ops(args.layers))),
                        "launch": "cuda graph replay" if graph is not None else "eager",
                        "l2": "inputs larger than L2 (4.2 GB of weights per step vs 126 MB L2)",
+                       "logits_absmax": float("%.3g" % logit_absmax),
                        "parallelism": ("every projection row-sharded x%d, outputs exchanged through %s" % (
                            world, "peer memory (one launch per exchange)" if p2p else "NCCL all-gather"))
                        if world > 1 else "single GPU"},

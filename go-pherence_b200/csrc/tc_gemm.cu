@@ -24,20 +24,26 @@
 //       applies the row scale and bias once at the end (fp8.Linear.GemvTo,
 //       backends/simd/quant/fp8/fp8.go:219-239).
 //
-// Pipeline of one CTA (18 warps, one persistent CTA per SM, walking (128-row tile, K split,
-// 256-element chunk) stages):
+// Pipeline of one CTA (26 warps, one persistent CTA per SM, walking (128-row tile, K split,
+// 256-element chunk) stages; a stage is handed from role to role in two units of half its K steps,
+// so the MMAs of the first unit run while the second is still being converted):
 //   producer warp    one bulk copy of the weight block (the tiled layouts store a stage's
 //                    shared-memory image contiguously), one of the chunk's B tile(s), one of the
 //                    chunk's sums of x (MLX), into a ring guarded by full/empty mbarriers; weight
-//                    copies of the first ring are issued before the kernel in front has finished.
-//   8 converter warps  two groups on alternate stages, thread = row: swizzled LDS.128 -> bf16 pairs
-//                    -> tcgen05.st into the group's own 128-column A buffer.
-//   MMA thread       16 (x pieces) tcgen05.mma kind::f16 M128 x N x K16 per stage, A from TMEM, B
-//                    through a shared-memory descriptor; tcgen05.commit releases the A buffer, the
-//                    stage and (per group block / per item) the accumulator to the epilogue.
-//   8 epilogue warps two per TMEM lane quarter, each owning half of the columns: tcgen05.ld,
-//                    scales from the staged block, running sums in registers.  K splits write
-//                    partial sums to scratch; the CTA arriving last adds them in split order.
+//                    copies are issued before the kernel in front has finished, the first two
+//                    stages at once and the rest of the ring when the first has landed.  The
+//                    chunk order rotates from tile to tile, so CTAs that run side by side do not
+//                    all ask for the same activation tile at the same moment.
+//   8 converter warps  all on every stage, thread = (row, K half): swizzled LDS.128 -> bf16 pairs
+//                    -> tcgen05.st into one of two 128-column A buffers.
+//   MMA warp         waits as a warp, one elected lane issues the stage's tcgen05.mma kind::f16
+//                    (M128 x N x K16, A from TMEM, B through a shared-memory descriptor) unit by
+//                    unit; tcgen05.commit releases the A buffer, the stage and (per group block /
+//                    per item) the accumulators to the epilogue.
+//   16 epilogue warps four per TMEM lane quarter, each owning a quarter of the columns:
+//                    tcgen05.ld, scales from the staged block, running sums in registers.  K
+//                    splits write partial sums to scratch; the CTA arriving last adds them in
+//                    split order.
 // mbarrier arrivals are one per warp.  Every wait is bounded (~2 s); a waiter that gives up
 // records a code (300+) in the status word and the CTA winds down.
 #include <string.h>
@@ -475,7 +481,6 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   } else {
     // ------------------------------------------------------------------ epilogue
     // Warp (q4, cq): rows 32 q4 .. +31 of the tile, columns cq * HC .. + HC - 1 of every block.
-    // The TMEM load of a stage's next block is in flight while the current one is added up.
     const int q4 = warp & 3, cq = (warp - kConvWarps) >> 2;
     const int r = q4 * 32 + lane;
     const int et = tid - kConvWarps * 32;

@@ -4,6 +4,7 @@ allocated by the caller's cuMemAlloc in that context.  Prints "ok" and exits 0 o
 import ctypes as C
 import os
 import sys
+import threading
 
 import numpy as np
 
@@ -47,8 +48,21 @@ def main():
         canary = np.full(out_dim + 64, 123.0, dtype=np.float32)
         check(cu.cuMemcpyHtoD_v2(xd, x.ctypes.data_as(C.c_void_p), C.c_size_t(x.nbytes)), "cuMemcpyHtoD")
         check(cu.cuMemcpyHtoD_v2(od, canary.ctypes.data_as(C.c_void_p), C.c_size_t(canary.nbytes)), "cuMemcpyHtoD")
-        rt.GemvMLX(rt.wrap(od.value, out_dim * 4), rt.wrap(xd.value, in_dim * 4), h)
-        rt.Sync()
+        # the product is issued from a thread that has never had a context current (goroutines
+        # migrate between OS threads, runtime/runtime.go:258-274): the library binds its own
+        failure = []
+
+        def product():
+            try:
+                rt.GemvMLX(rt.wrap(od.value, out_dim * 4), rt.wrap(xd.value, in_dim * 4), h)
+                rt.Sync()
+            except Exception as e:  # noqa: BLE001 - reported to the parent thread
+                failure.append(e)
+
+        t = threading.Thread(target=product)
+        t.start()
+        t.join()
+        assert not failure, failure
         cur = C.c_void_p(0)
         check(cu.cuCtxGetCurrent(C.byref(cur)), "cuCtxGetCurrent")
         assert cur.value == ctx.value, "the library left another context current"

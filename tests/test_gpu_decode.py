@@ -188,7 +188,7 @@ def build_model(pkg, cfg, key, centred=False):
     return layers_gpu, layers_orc, lm, final_norm
 
 
-LOGIT_TOL = 2e-3   # max |logit_gpu - logit_oracle| / max |logit_oracle| allowed at any position
+LOGIT_TOL = 2e-4   # (measured 1.2e-5) max |logit_gpu - logit_oracle| / max |logit_oracle| allowed at any position
 
 
 def run_gate(gpu, pkg, cfg, key, prompt_len, max_new, centred=False):
