@@ -12,6 +12,8 @@
 #include <math_constants.h>
 #include <string.h>
 
+#include <mutex>
+
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
 
@@ -527,15 +529,31 @@ static int attn_launch(int device, AttnArgs& a, int max_seq, bool fused, void* s
   if (a.heads > kAttnMaxHeads) return fail(GOPH_E_UNSUPPORTED, "at most %d query heads", kAttnMaxHeads);
   if (max_seq <= 0) return fail(GOPH_E_INVALID, "max_seq=%d", max_seq);
   if (int rc = use_device(device)) return rc;
+  // Per-device scratch, allocated once.  Calls may come from any thread: the first calls are
+  // serialised, and the pointers are published only when every allocation and the clearing of the
+  // counters have succeeded (a failed first call leaves nothing half-made for the next one).
+  static std::mutex mu;
   static float* scratch[kMaxDevices] = {};
   static unsigned int* counters[kMaxDevices] = {};
-  if (!counters[device]) {
-    GOPH_CUDA(cudaMalloc(&scratch[device], (size_t)kAttnMaxHeads * kAttnMaxSplits * (2 + 256) * sizeof(float)));
-    GOPH_CUDA(cudaMalloc(&counters[device], kAttnMaxHeads * sizeof(unsigned int)));
-    GOPH_CUDA(cudaMemset(counters[device], 0, kAttnMaxHeads * sizeof(unsigned int)));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!counters[device]) {
+      float* s = nullptr;
+      unsigned int* c = nullptr;
+      if (cudaMalloc(&s, (size_t)kAttnMaxHeads * kAttnMaxSplits * (2 + 256) * sizeof(float)) != cudaSuccess ||
+          cudaMalloc(&c, kAttnMaxHeads * sizeof(unsigned int)) != cudaSuccess ||
+          cudaMemset(c, 0, kAttnMaxHeads * sizeof(unsigned int)) != cudaSuccess) {
+        cudaFree(s);
+        cudaFree(c);
+        cudaGetLastError();
+        return fail(GOPH_E_NOMEM, "cannot allocate the attention kernel's device scratch");
+      }
+      scratch[device] = s;
+      counters[device] = c;
+    }
+    a.scratch = scratch[device];
+    a.counters = counters[device];
   }
-  a.scratch = scratch[device];
-  a.counters = counters[device];
   a.max_seq = max_seq;
   // Short caches (the latency-bound case): CTAs of 4 warps, one block of 16 positions each, so that they
   // fit beside the projection kernels' CTAs and start under programmatic dependent launch (measured on
@@ -618,18 +636,38 @@ GOPH_API int goph_argmax_advance(int device, const float* logits_dev, int n, int
   if (!logits_dev || n <= 0 || !tok_dev || !pos_dev) return fail(GOPH_E_INVALID, "goph_argmax_advance: n=%d", n);
   if (int rc = use_device(device)) return rc;
   // per-device scratch of the two-level reduction, allocated once
+  static std::mutex mu;
   static float* part_val[kMaxDevices] = {};
   static int* part_idx[kMaxDevices] = {};
   static unsigned int* counter[kMaxDevices] = {};
-  if (!counter[device]) {
-    GOPH_CUDA(cudaMalloc(&part_val[device], kArgmaxCtas * sizeof(float)));
-    GOPH_CUDA(cudaMalloc(&part_idx[device], kArgmaxCtas * sizeof(int)));
-    GOPH_CUDA(cudaMalloc(&counter[device], sizeof(unsigned int)));
-    GOPH_CUDA(cudaMemset(counter[device], 0, sizeof(unsigned int)));
+  float* pv;
+  int* pi;
+  unsigned int* cnt;
+  {
+    std::lock_guard<std::mutex> lock(mu);  // as for the attention scratch: complete or not at all
+    if (!counter[device]) {
+      float* v = nullptr;
+      int* i = nullptr;
+      unsigned int* c = nullptr;
+      if (cudaMalloc(&v, kArgmaxCtas * sizeof(float)) != cudaSuccess || cudaMalloc(&i, kArgmaxCtas * sizeof(int)) != cudaSuccess ||
+          cudaMalloc(&c, sizeof(unsigned int)) != cudaSuccess || cudaMemset(c, 0, sizeof(unsigned int)) != cudaSuccess) {
+        cudaFree(v);
+        cudaFree(i);
+        cudaFree(c);
+        cudaGetLastError();
+        return fail(GOPH_E_NOMEM, "cannot allocate the argmax kernel's device scratch");
+      }
+      part_val[device] = v;
+      part_idx[device] = i;
+      counter[device] = c;
+    }
+    pv = part_val[device];
+    pi = part_idx[device];
+    cnt = counter[device];
   }
   const int ctas = n >= 64 * 512 ? kArgmaxCtas : 1;
   return op_launch(argmax_advance_kernel, dim3(ctas), 512, 0, stream, logits_dev, n, tok_dev, pos_dev, history_dev, forced_dev,
-                   history_cap, part_val[device], part_idx[device], counter[device]);
+                   history_cap, pv, pi, cnt);
 }
 
 GOPH_API int goph_mlx_embed(float* out_dev, uint64_t out_len, const goph_mlx_weight* w, const int* tok_dev, void* stream) {

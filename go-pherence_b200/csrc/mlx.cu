@@ -1125,6 +1125,9 @@ GOPH_API int goph_mlx_program_run(goph_mlx_program* p, void* stream) {
   cfg.stream = (cudaStream_t)stream;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
+  // the attribute belongs to the kernel, not to the list: a list created later on the same
+  // instantiation with a smaller request would otherwise leave this one without its shared memory
+  GOPH_CUDA(cudaFuncSetAttribute(p->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p->smem));
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, p->kernel, (const MlxArgs*)p->ops, p->nops, p->words, p->words + 1,
                                reinterpret_cast<int*>(p->words + 2)));

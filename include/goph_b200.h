@@ -21,6 +21,11 @@
  *   - Calls may come from any OS thread; the library sets the device it needs on every
  *     call and keeps no thread-local state besides the error text.  Like the reference
  *     (global cudaMu, runtime.go:134-139) callers serialise calls that share a handle.
+ *   - The tensor-core products (tiled layouts), the attention kernel and the argmax kernel keep
+ *     one scratch area per device (activation digits, split-K partial sums, counters).  Calls
+ *     on one device whose kernels could overlap on the GPU — different streams with no ordering
+ *     between them — must be ordered by the caller (one stream, or events), whatever handles
+ *     they use.  The reference launches everything on one stream, which satisfies this.
  *   - Matrices are row-major; x is [batch, in_dim], out is [batch, out_dim], both f32.
  */
 #ifndef GOPH_B200_H

@@ -67,7 +67,7 @@ def test_dequant_bit_exact_f32_scales(gpu, pkg):
 @pytest.mark.parametrize("digits", [4, 3])
 @pytest.mark.parametrize("out_dim,in_dim", QWEN3_LAYER)
 def test_gemv_qwen3_layer_shapes_tensor_cores(gpu, pkg, out_dim, in_dim, digits):
-    # BASELINE config 0 on the tcgen05 path; bf16-valued activations, 4 or 3 base-128 digits
+    # the Qwen3-0.6B projection shapes on the tcgen05 path; bf16-valued activations, 4 or 3 base-128 digits
     gpu.SetOption("mlx_digits", digits)
     try:
         h, (w, s, b) = upload(gpu, pkg.synth, ("cfg0", out_dim, in_dim), out_dim, in_dim)
