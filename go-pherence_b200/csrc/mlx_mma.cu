@@ -43,7 +43,9 @@
 // the CTA winds down (copies drained, TMEM returned) instead of spinning.
 #include <string.h>
 
+#include <map>
 #include <mutex>
+#include <tuple>
 
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
@@ -139,6 +141,10 @@ struct MmaArgs {
   int stages;              // depth of the shared-memory ring
   int cmax;                // FUSED: most chunks an item has (resident B tiles)
   int dbg;                 // tuning build only
+  // 1: the CTAs that share a tile (one per K split) form a thread-block cluster, every CTA has
+  // exactly one item, and the partial sums travel through the shared memory of the cluster's first
+  // CTA instead of global scratch and an atomic counter
+  int cluster;
 };
 
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
@@ -150,13 +156,16 @@ struct MmaArgs {
 // C: chunks of 256 elements per stage.  The nibble formats take two: what a stage costs every role
 // in waits, fences and arrivals is then paid once per 36 KiB instead of once per 18 KiB.  A stage's
 // layout is [C weight blocks][C B tiles].
+// Rows of 128 partial sums the first CTA of a cluster can receive: (splits - 1) x activation rows.
+constexpr int kClusterRecvRows = 7;
+
 template <int N, int FMT = FMT_MLX4, bool FUSED = false, int C = 1>
 struct MmaSmem {
   static constexpr int kBTileBytes = 8 * N * 32;  // 256 K-bytes for each of N rows
   static constexpr int kStage = C * (Fmt<FMT>::kStageBytes + (FUSED ? 0 : kBTileBytes));
   static __host__ __device__ size_t bytes(int stages, int batch, int in_dim, int cmax = 0) {
     return (size_t)stages * kStage + (FUSED ? (size_t)cmax * kBTileBytes : 0) +
-           (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4;
+           (size_t)batch * (in_dim / Fmt<FMT>::kGroup) * 8 + 1024 + 512 + 8 * kTileRows * 4 + kClusterRecvRows * kTileRows * 4;
   }
 };
 
@@ -354,16 +363,18 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   float* xsum = reinterpret_cast<float*>(bres + (FUSED ? (size_t)a.cmax * kBTileBytes : 0));  // [batch][groups] sum of x
   float* xfs = xsum + (size_t)a.batch * groups;                        // [batch][groups] 2^(E-QBITS)
   uint64_t* bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(xfs + (size_t)a.batch * groups) + 15) & ~uintptr_t(15));
-  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND);
+  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND], cluster
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   float* pair = reinterpret_cast<float*>(tmem_holder + 4);  // [EP-1][MB][128]: the sums of an item from the epilogue parts above 0
   static_assert((EP - 1) * MB <= 8, "room for the parts' sums");
+  float* recv = pair + 8 * kTileRows;  // [splits-1][MB][128]: partial sums from the cluster's other CTAs (first CTA only)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
   const uint32_t aready0 = smem_u32(bars + 2 * S), afree0 = aready0 + 8 * NA;
   const uint32_t mdone0 = afree0 + 8 * NA, dfree0 = mdone0 + 8 * ND;  // mdone: a stage's accumulators are complete
+  const uint32_t clbar = dfree0 + 8 * ND;  // cluster launches: the other CTAs' partial sums have arrived (one arrival per warp)
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -380,6 +391,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       mbar_init(mdone0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiWarps);
     }
+    if (a.cluster) mbar_init(clbar, 4 * (a.splits - 1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kWarpMMA) {
@@ -391,6 +403,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (a.cluster) cluster_sync_all();  // the first CTA's barrier is initialised before any peer can arrive on it
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * kACols;  // A: NA x kACols; D: ND x kDCols
   bool ok = true;
@@ -727,7 +740,34 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         }
       }
       const int row = tile * kTileRows + r;
-      if (a.splits == 1) {
+      if (a.cluster) {
+        // The K splits of this tile are the CTAs of this cluster (rank == split) and each has this one
+        // item.  Ranks above 0 put their sums into rank 0's shared memory and arrive on its barrier
+        // (one releasing arrival per warp, after the warp's lanes have met); rank 0 waits, adds the
+        // sums in split order — the same order as the scratch path, so the same bits — and stores.
+        if (half == 0) {
+          if (split != 0) {
+#pragma unroll
+            for (int m = 0; m < MB; ++m)
+              if (m < a.batch) cluster_store_f32(cluster_map(smem_u32(recv + ((split - 1) * MB + m) * kTileRows + r), 0), acc[m]);
+            __syncwarp();
+            if (lane == 0) cluster_arrive_release(cluster_map(clbar, 0));
+          } else {
+            ok = __all_sync(0xffffffffu, mbar_wait_cluster(clbar, 0, a.status, 12));
+            if (ok) {
+#pragma unroll
+              for (int m = 0; m < MB; ++m) {
+                float sum = acc[m];
+                for (int s2 = 1; s2 < a.splits; ++s2) sum += recv[((s2 - 1) * MB + m) * kTileRows + r];
+                if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = sum;
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < MB; ++m) acc[m] = 0.f;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      } else if (a.splits == 1) {
         if (half == 0) {
 #pragma unroll
           for (int m = 0; m < MB; ++m) {
@@ -932,13 +972,13 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   a.cmax = (a.nchunks + splits - 1) / splits;
   size_t smem = MmaSmem<N, FMT, FUSED, C>::bytes(stages, a.batch, a.in_dim, a.cmax);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.stream = stream;
-  cfg.attrs = &attr;
+  cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (!FUSED && prep) {
     // activations -> digits, sums and scales, once per launch
@@ -957,6 +997,36 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(mma_threads<N, FMT>());
   cfg.dynamicSmemBytes = smem;
+  // K splits whose CTAs all run at once, one item each: the CTAs of a tile form a cluster and add
+  // their partial sums through the first CTA's shared memory (no scratch, fence or atomic).  Only
+  // when the device can hold every cluster of the grid at the same time — a second wave of clusters
+  // would cost far more than the fix-up saves.
+  if (options().mlx_cluster && splits > 1 && splits <= 8 && a.items == grid && (splits - 1) * MB <= kClusterRecvRows) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, size_t, int>, int> fits;  // (kernel, splits, smem, device) -> clusters resident at once
+    const auto key = std::make_tuple((const void*)kern, splits, smem, w.device);
+    int resident = -1;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      auto it = fits.find(key);
+      if (it != fits.end()) resident = it->second;
+    }
+    if (resident < 0) {
+      if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        resident = 0;
+      }
+      std::lock_guard<std::mutex> lock(mu);
+      fits[key] = resident;
+    }
+    if (resident * splits >= grid) a.cluster = 1;
+    else cfg.numAttrs = 1;
+  }
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;

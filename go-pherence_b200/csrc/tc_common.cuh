@@ -47,6 +47,48 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   return true;
 }
 
+// ---- thread-block clusters: a peer CTA's shared memory and mbarriers ----------------------------
+// Address of `local` (an address in this CTA's shared memory) inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t remote, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+// Arrival on a peer CTA's mbarrier that publishes this thread's earlier writes to the cluster.
+__device__ __forceinline__ void cluster_arrive_release(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait on an mbarrier of this CTA whose arrivals come from peer CTAs of the cluster.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  long long t0 = clock64();
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if (clock64() - t0 > kTimeoutCycles) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+// Every thread of every CTA of the cluster meets here (all of them must call it).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its prologue now /
 // wait until every kernel this one depends on has completed and its writes are visible.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -108,6 +108,9 @@ int goph_sm_count(int device);
  *                 the nibble formats where tensor memory has the columns (up to 4 activation rows
  *                 for MLX 4-bit, 2 for Q4_K), 1 always one
  *   "mlx_splits"  CTAs that share the K range of one 128-row tile (0 = chosen by shape)
+ *   "mlx_cluster" 1 (default): K splits that all run at once are launched as thread-block clusters and
+ *                 add their partial sums through shared memory; 0: always through device scratch
+ *                 and an atomic counter.  Same bits either way
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion
  *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
