@@ -41,6 +41,8 @@
 //     of arrival order).
 // Every wait is bounded (~2 s): a waiter that gives up records a code in the status word and
 // the CTA winds down (copies drained, TMEM returned) instead of spinning.
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <map>
@@ -945,14 +947,29 @@ struct TiledDesc {
 constexpr size_t kMmaSmemBudget = 222 * 1024;  // of the 227 KiB a CTA may have
 constexpr int kMaxStages = 10;
 
+// Clusters of `size` CTAs of the tensor-core GEMV that the device can hold at once (every such CTA
+// takes a whole SM, so this is a property of how the SMs are grouped); asked once per device.
+static int cluster_room(int device, int size);
+
 // K split: enough (tile, split) items to occupy the SMs, bounded by the chunks and the scratch.
 template <int MB>
-static int choose_splits(const MmaArgs& a, int sm_count) {
+static int choose_splits(const MmaArgs& a, int sm_count, int device) {
   int splits = 1;
   if (a.ntiles < sm_count) {
     splits = sm_count / a.ntiles;
     if (splits > a.nchunks) splits = a.nchunks;
     if (splits < 1) splits = 1;
+    // The cheap way to add the splits' partial sums needs all clusters of `splits` CTAs resident at
+    // once.  Where that many do not fit (48 tiles x 3: room for 45), fewer splits that do fit are the
+    // better trade (6144 x 4096: 7.7 us with 2 splits in clusters against 8.3 us with 3 through scratch).
+    if (options().mlx_cluster && splits > 2 && splits <= 8 && cluster_room(device, splits) < a.ntiles) {
+      for (int s2 = splits - 1; s2 >= 2; --s2) {
+        if (cluster_room(device, s2) >= a.ntiles) {
+          splits = s2;
+          break;
+        }
+      }
+    }
   }
   if (options().mlx_splits > 0) splits = options().mlx_splits < a.nchunks ? options().mlx_splits : a.nchunks;
   while (splits > 1 && ((size_t)a.ntiles * splits * kTileRows * MB > kScratchFloats || (size_t)a.ntiles > kMaxCounters)) --splits;
@@ -960,6 +977,41 @@ static int choose_splits(const MmaArgs& a, int sm_count) {
 }
 
 int g_mma_dbg = 0;  // tuning build only
+
+static int cluster_room(int device, int size) {
+  static std::mutex mu;
+  static int room[kMaxDevices][9];
+  static bool known[kMaxDevices] = {};
+  if (device < 0 || device >= kMaxDevices || size < 2 || size > 8) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!known[device]) {
+    auto kern = mlx_mma_kernel<8, 4, 1, FMT_MLX4, false, 2>;
+    const size_t smem = 200 * 1024;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    for (int sz = 2; sz <= 8; ++sz) {
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = sz;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof cfg);
+      cfg.gridDim = dim3(sz * 64);
+      cfg.blockDim = dim3(mma_threads<8, FMT_MLX4>());
+      cfg.dynamicSmemBytes = smem;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+      }
+      room[device][sz] = n;
+    }
+    known[device] = true;
+  }
+  return room[device][size];
+}
 
 template <int N, int DIGITS, int MB, int FMT, bool FUSED, int C>
 static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t stream, bool prep, int stages, int splits) {
@@ -997,6 +1049,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(mma_threads<N, FMT>());
   cfg.dynamicSmemBytes = smem;
+  int cluster_room = -1;
   // K splits whose CTAs all run at once, one item each: the CTAs of a tile form a cluster and add
   // their partial sums through the first CTA's shared memory (no scratch, fence or atomic).  Only
   // when the device can hold every cluster of the grid at the same time — a second wave of clusters
@@ -1026,7 +1079,13 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
     }
     if (resident * splits >= grid) a.cluster = 1;
     else cfg.numAttrs = 1;
+    cluster_room = resident;
   }
+  // GOPH_TRACE_LAUNCH=1 in the environment: one line per tensor-core product with its launch plan
+  static const bool trace = getenv("GOPH_TRACE_LAUNCH") != nullptr;
+  if (trace)
+    fprintf(stderr, "goph: mlx_mma_kernel fmt=%d out=%d in=%d rows=%d grid=%d splits=%d stages=%d chunks/stage=%d fused=%d cluster=%d (room for %d clusters)\n",
+            FMT, a.out_dim, a.in_dim, a.batch, grid, splits, stages, C, (int)FUSED, a.cluster, cluster_room);
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
@@ -1042,7 +1101,7 @@ constexpr int stage_chunks() {
 template <int N, int DIGITS, int MB, int FMT, int C>
 static int launch_with_chunks(const TiledDesc& w, const MmaArgs& a, cudaStream_t stream, bool prep) {
   const int sms = device_state(w.device).sm_count;
-  const int splits = choose_splits<MB>(a, sms);
+  const int splits = choose_splits<MB>(a, sms, w.device);
   const int cmax = (a.nchunks + splits - 1) / splits;
   // Narrow launches (one or two activation rows) whose items are short (at most four chunks: the
   // matrices that are split over K to fill the SMs) make the digits of their own K range inside
