@@ -57,17 +57,6 @@ struct FP8Fmt {
   }
 };
 
-// The same product on the tensor-core layout (one 32 KiB block per 128 rows x 256 bytes, 16-byte
-// units swizzled inside a block row): only the address of a unit differs.  A warp's 32 units of a
-// row are two runs of 256 contiguous bytes.  Used for the batches of up to 8 rows, which the
-// CUDA cores serve better than the tensor-core kernel's three-piece activations.
-struct FP8TiledFmt : FP8Fmt {
-  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
-    const int r = row & 127, u = unit & 15;
-    const size_t blk = (size_t)(row >> 7) * a.nchunks + (unit >> 4);
-    t.q = ld_stream(reinterpret_cast<const uint4*>(a.w + blk * 32768 + r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4)));
-  }
-};
 
 // Rows whose length is not a multiple of 16 bytes cannot be read as aligned 16-byte units:
 // one warp per row, byte loads.
@@ -175,9 +164,10 @@ GOPH_API int goph_fp8_upload(int device, const uint8_t* weight, uint64_t weight_
   UP(cudaDeviceSynchronize());
 #undef UP
   h->bytes = want + (uint64_t)out_dim * 4 * (bias ? 2 : 1);
-  // Tensor-core layout for matrices large enough to amortise that kernel's fixed cost; a matrix
-  // holding one of the two NaN codes stays row-major (the converter of the tensor-core kernel maps
-  // them to +-480, the CUDA-core kernels keep them NaN as the reference's table does).
+  // Tensor-core layout for matrices large enough to amortise that path's fixed cost; a matrix
+  // holding one of the two NaN codes stays row-major (the kernel that serves large bf16 batches
+  // turns the bytes into bf16 and would map those codes to +-480; the CUDA-core kernels keep them
+  // NaN as the reference's table does).
   const bool big = want >= (8u << 20);
   if (tc_fp8_supported(in_dim) && (options().fp8_layout == 2 || (options().fp8_layout == 0 && big))) {
     int has_nan = 0;
@@ -238,11 +228,9 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
                 (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
   if (int rc = use_device(w->device)) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  // Tensor-core layout: two rows and more go to the small-batch GEMM (one pass over the weights for
-  // up to 16 f32 rows; measured 8192 x 8192, 4 rows: 26 us against 79 us for the CUDA-core kernel),
-  // and so does a single row against a long K (8192 x 28672: 69 against 146 us); a single row of
-  // ordinary length is served best by the CUDA-core streaming kernel (128256 x 4096: 0.88 of the copy rate).
-  if (w->tiled && (batch > 1 || w->in_dim > 16384)) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
+  // Tensor-core layout: every batch size goes to the kernel that feeds the e4m3 bytes to the MMA as
+  // they lie (fp8_mma.cu); the row-major layout is served by the CUDA-core kernels below.
+  if (w->tiled) return tc_gemm_fp8(w, out_dev, x_dev, false, batch, s);
   if (!w->tiled && w->in_dim % 16 != 0) {
     note_launch();
     fp8_gemv_ragged_kernel<<<(w->out_dim + kGWarps - 1) / kGWarps, kGThreads, 0, s>>>(
@@ -252,8 +240,7 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
   }
   StreamArgs a;
   memset(&a, 0, sizeof a);
-  a.w = w->tiled ? w->tiled : w->weight;
-  a.nchunks = w->in_dim / 256;
+  a.w = w->weight;
   a.aux = w->scale;
   a.bias = w->bias;
   a.out = out_dev;
@@ -263,7 +250,6 @@ GOPH_API int goph_fp8_gemm(float* out_dev, uint64_t out_len, const float* x_dev,
   a.units = w->in_dim / 16;
   a.row_bytes = w->in_dim;
   const int force_rows = options().fp8_rows;
-  if (w->tiled) return stream_launch<FP8TiledFmt>(a, w->device, batch, s, force_rows);
   return stream_launch<FP8Fmt>(a, w->device, batch, s, force_rows);
 }
 

@@ -121,7 +121,8 @@ struct goph_fp8_linear {
   int scale_len;      // what the caller passed (1 or out_dim)
   uint8_t* weight;    // [out_dim][in_dim] (row-major layout) or nullptr
   uint8_t* tiled;     // tensor-core layout or nullptr: one 32 KiB block per 128 rows x 256 bytes, blocks
-                      // ordered [tile][chunk], 16-byte unit u of row r at r*256 + ((u&8)|((u&7)^(r&7)))*16
+                      // ordered [tile][chunk], 16-byte unit u of row r at (u/2)*4096 + (u%2)*2048 + (r/8)*128 + (r%8)*16
+                      // (the K-major 8 x 16-byte core matrices the MMA reads from shared memory)
   float* scale;       // [out_dim]
   float* bias;        // [out_dim] or nullptr
   uint64_t bytes;

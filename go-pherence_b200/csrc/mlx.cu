@@ -1289,6 +1289,7 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   if (int rc = use_device(device)) return rc;
   *out_status = mlx_mma_status(device);
   if (*out_status == 0) *out_status = tc_gemm_status(device);
+  if (*out_status == 0) *out_status = fp8_mma_status(device);
   if (*out_status == 0) *out_status = decode_ops_status();
   return GOPH_OK;
 }
@@ -1299,6 +1300,7 @@ GOPH_API int goph_kernel_status_clear(int device) {
   GOPH_CUDA(cudaDeviceSynchronize());
   mlx_mma_status_clear(device);
   tc_gemm_status_clear(device);
+  fp8_mma_status_clear(device);
   decode_ops_status_clear();
   return GOPH_OK;
 }

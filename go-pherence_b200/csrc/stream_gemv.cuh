@@ -35,7 +35,7 @@ struct StreamArgs {
   int iters;            // ceil(units / 32)
   int x_aligned;
   int row_bytes;
-  int nchunks;          // FP8 tensor-core layout: 256-byte chunks per row
+
 };
 
 template <class F>

@@ -450,8 +450,12 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         for (int ub = 0; ub < 8; ub += 4) {
           uint4 qv[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            qv[u] = *reinterpret_cast<const uint4*>(st + r * 256 + (((8 * kh) | ((ub + u) ^ (r & 7))) << 4));
+          for (int u = 0; u < 4; ++u) {
+            // 16-byte unit U of row r in the block of K-major core matrices (see fp8_mma.cu):
+            // [K step U / 2][half U % 2][row group r / 8][row r % 8]; a warp's 32 rows read 512 contiguous bytes
+            const int U = 8 * kh + ub + u;
+            qv[u] = *reinterpret_cast<const uint4*>(st + (U >> 1) * 4096 + (U & 1) * 2048 + (r >> 3) * 128 + (r & 7) * 16);
+          }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const uint32_t ws[4] = {qv[u].x, qv[u].y, qv[u].z, qv[u].w};
@@ -779,93 +783,18 @@ int run_passes(const GemmDesc& w, float* out, const void* x, bool x_bf16, int ba
   return GOPH_OK;
 }
 
-// Row-major bytes -> tiled stages (16-byte unit u of row r at r*256 + ((u & 8) | ((u & 7) ^ (r & 7))) * 16);
-// one thread per 16-byte unit.  Flags the two NaN codes.
-__global__ void fp8_tile_kernel(const unsigned char* __restrict__ w, unsigned char* __restrict__ tiled, int out_dim, int in_dim,
-                                int ntiles, int nchunks, int* nan_flag) {
-  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  size_t nstages = (size_t)ntiles * nchunks;
-  if (idx >= nstages * (128 * 16)) return;
-  size_t stg = idx / (128 * 16);
-  int rem = (int)(idx - stg * (128 * 16));
-  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
-  int r = rem >> 4, u = rem & 15, row = tile * 128 + r;
-  uint4 v = make_uint4(0, 0, 0, 0);
-  if (row < out_dim) {
-    v = *reinterpret_cast<const uint4*>(w + (size_t)row * in_dim + chunk * 256 + u * 16);
-    const uint32_t ws[4] = {v.x, v.y, v.z, v.w};
-    bool nan = false;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t m = ws[k] & 0x7F7F7F7Fu;
-      nan = nan || (m & 0xFFu) == 0x7Fu || (m & 0xFF00u) == 0x7F00u || (m & 0xFF0000u) == 0x7F0000u || (m >> 24) == 0x7Fu;
-    }
-    if (nan) *nan_flag = 1;
-  }
-  *reinterpret_cast<uint4*>(tiled + stg * kFp8WBytes + r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4)) = v;
-}
-
-__global__ void fp8_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, const float* __restrict__ scale,
-                                         float* __restrict__ out, int out_dim, int in_dim, int nchunks) {
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (size_t)out_dim * in_dim) return;
-  int row = (int)(i / in_dim), col = (int)(i - (size_t)row * in_dim);
-  int chunk = col >> 8, k = col & 255, u = k >> 4, r = row & 127;
-  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * kFp8WBytes;
-  unsigned char b = stg[r * 256 + (((u & 8) | ((u & 7) ^ (r & 7))) << 4) + (k & 15)];
-  __half_raw hr = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-  out[i] = __fmul_rn(__half2float(*reinterpret_cast<__half*>(&hr)), scale[row]);
-}
-
 }  // namespace
+
+int tc_gemm_fp8_converted(const goph_fp8_linear* w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
+  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "FP8 linear is not in the tensor-core layout");
+  GemmDesc d{w->tiled, w->scale, w->bias, w->device, w->out_dim, w->in_dim};
+  return run_passes<G_FP8>(d, out, x, x_bf16, batch, stream);
+}
 
 int tc_gemm_mlx(const goph_mlx_weight* w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
   if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
   GemmDesc d{w->tiled, nullptr, nullptr, w->device, w->out_dim, w->in_dim};
   return run_passes<G_MLX4>(d, out, x, x_bf16, batch, stream);
-}
-
-int tc_gemm_fp8(const goph_fp8_linear* w, float* out, const void* x, bool x_bf16, int batch, cudaStream_t stream) {
-  if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "FP8 linear is not in the tiled layout");
-  GemmDesc d{w->tiled, w->scale, w->bias, w->device, w->out_dim, w->in_dim};
-  return run_passes<G_FP8>(d, out, x, x_bf16, batch, stream);
-}
-
-bool tc_fp8_supported(int in_dim) { return in_dim % kChunkK == 0 && in_dim <= kMaxIn; }
-
-int tc_fp8_make_tiled(goph_fp8_linear* w, int* has_nan) {
-  const int ntiles = (w->out_dim + kTileRows - 1) / kTileRows, nchunks = w->in_dim / kChunkK;
-  const size_t bytes = (size_t)ntiles * nchunks * kFp8WBytes;
-  unsigned char* t = nullptr;
-  int* flag = nullptr;
-  GOPH_CUDA(cudaMalloc(&t, bytes));
-  cudaError_t e = cudaMalloc(&flag, sizeof(int));
-  if (e == cudaSuccess) e = cudaMemset(flag, 0, sizeof(int));
-  if (e == cudaSuccess) {
-    size_t threads = (size_t)ntiles * nchunks * 128 * 16;
-    fp8_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(w->weight, t, w->out_dim, w->in_dim, ntiles, nchunks, flag);
-    e = cudaGetLastError();
-  }
-  if (e == cudaSuccess) e = cudaMemcpy(has_nan, flag, sizeof(int), cudaMemcpyDeviceToHost);
-  cudaFree(flag);
-  if (e != cudaSuccess) {
-    cudaFree(t);
-    return fail_cuda(e, "fp8_tile_kernel");
-  }
-  if (*has_nan) {
-    cudaFree(t);
-    return GOPH_OK;
-  }
-  w->tiled = t;
-  return GOPH_OK;
-}
-
-int tc_fp8_dequant_tiled(const goph_fp8_linear* w, float* out, cudaStream_t stream) {
-  size_t n = (size_t)w->out_dim * w->in_dim;
-  fp8_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(w->tiled, w->scale, out, w->out_dim, w->in_dim,
-                                                                            w->in_dim / kChunkK);
-  GOPH_CUDA(cudaGetLastError());
-  return GOPH_OK;
 }
 
 #ifdef GOPH_TUNING

@@ -94,10 +94,9 @@ int goph_sm_count(int device);
  *                 2 tensor-core layout whenever the shape allows.  "mlx_digits" and "mlx_splits"
  *                 apply to these products as well
  *   "fp8_layout"  the same choice for goph_fp8_upload (in_dim a multiple of 256, no NaN codes in the
- *                 weight): the tensor-core layout serves two activation rows and more (and a single
- *                 row against more than 16384 inputs) through the bf16 tensor-core kernel and a
- *                 single row through a CUDA-core streaming kernel; the row-major layout is served
- *                 by the CUDA-core kernels alone
+ *                 weight): the tensor-core layout serves every batch size on the tensor cores (the
+ *                 e4m3 bytes go to the MMA as they lie; f32 activations as six e4m3 pieces, exact,
+ *                 bf16 activations as two); the row-major layout is served by the CUDA-core kernels
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
