@@ -78,11 +78,11 @@ struct Fp8Args {
   float* scratch;           // split-K partial sums [tile][split][MP][128]
   unsigned int* counters;   // per-tile arrival counters, zero between launches
   int out_dim, in_dim, batch;
-  int ntiles, nks, splits, items, stages;  // nks: stages along K (in_dim / KS)
+  int ntiles, nks, splits, items, stages;  // nks: stages along K (in_dim / KS); items = row-tile groups x splits
 };
 
 struct ItemWalk {
-  int w, tile, split, k, k1;
+  int w, tile, split, k, k1;  // tile: the item's group of TT consecutive row tiles
   __device__ __forceinline__ void open(const Fp8Args& a) {
     tile = w / a.splits;
     split = w - tile * a.splits;
@@ -267,18 +267,22 @@ __device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uin
 // KS: K bytes of a pipeline stage, 256 (a whole block) or 128 (half a block, for wide B tiles).  The
 // MMA warp spends some 70 cycles per instruction and 300 per stage on waits and commits, so the
 // longer stage is what lets a single SM keep up with its share of the HBM rate.
-template <int N, int P, int MP, int KS>
+// TT: row tiles per item (1 or 2).  With a wide B tile (64 activation rows in two pieces are 128 B
+// rows: 16 KiB of activations per 16 KiB of weights, re-read from the L2 for every row tile) two row
+// tiles share each B tile: half the L2 traffic and twice the MMAs per wait and commit.
+template <int N, int P, int MP, int KS, int TT>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
   static_assert(KS == 128 || KS == 256, "a stage is a block or half a block");
+  static_assert(TT == 1 || (TT == 2 && 4 * N <= 512), "two accumulator buffers of TT x N columns");
   constexpr int kABytes = kTileRows * KS;
   static_assert(N % 16 == 0 && N >= 16 && N <= 256 && P * MP <= N, "B rows: P pieces of MP activation rows (the rows past P * MP are unused)");
   constexpr int HM = MP / 2;           // rows of one epilogue warp
   constexpr int G = HM >= 16 ? 16 : HM;  // rows per register group
   static_assert(MP >= 2 && MP % 2 == 0 && HM % G == 0, "rows split over two epilogue warps in groups");
   constexpr int kBBytes = N * KS;
-  constexpr int kStage = kABytes + kBBytes;
-  constexpr int ND = 2;                // accumulator buffers of N columns
+  constexpr int kStage = TT * kABytes + kBBytes;  // [TT weight tiles][B tile]
+  constexpr int ND = 2;                // accumulator buffers of TT x N columns
   constexpr float kPieceScale[3] = {1.f, 1.f / 256.f, 1.f / 65536.f};  // pieces 2p and 2p+1 were written 2^(8p) up
   constexpr uint32_t kCols = 512;
   extern __shared__ unsigned char smem_dyn[];
@@ -317,10 +321,12 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      auto a_src = [&](const ItemWalk& q) {
-        return KS == 256 ? a.w + ((size_t)q.tile * nchunks + q.k) * kBlockBytes
-                         : a.w + ((size_t)q.tile * nchunks + (q.k >> 1)) * kBlockBytes + (q.k & 1) * kABytes;
+      auto a_src = [&](const ItemWalk& q, int t) {
+        const size_t tile = (size_t)q.tile * TT + t;
+        return KS == 256 ? a.w + (tile * nchunks + q.k) * kBlockBytes : a.w + (tile * nchunks + (q.k >> 1)) * kBlockBytes + (q.k & 1) * kABytes;
       };
+      // row tiles of the item that exist (the last group of an odd tile count has one)
+      auto tiles_of = [&](const ItemWalk& q) { return q.tile * TT + TT <= a.ntiles ? TT : a.ntiles - q.tile * TT; };
       auto b_src = [&](const ItemWalk& q) {
         return KS == 256 ? a.xb + (size_t)q.k * (N * kChunkK) : a.xb + (size_t)(q.k >> 1) * (N * kChunkK) + (q.k & 1) * kBBytes;
       };
@@ -329,21 +335,24 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
         // the weights do not depend on the kernel in front: the first stages' copies go out at once
         ItemWalk q = wk;
         for (; i < S && i < 2 && q.live(a); ++i, q.next(a)) {
-          mbar_expect_tx(full0 + 8 * i, kStage);
-          bulk_load_1d(smem_u32(ring + (size_t)i * kStage), a_src(q), kABytes, full0 + 8 * i);
+          const int nt = tiles_of(q);
+          mbar_expect_tx(full0 + 8 * i, nt * kABytes + kBBytes);
+          for (int t = 0; t < nt; ++t)
+            bulk_load_1d(smem_u32(ring + (size_t)i * kStage) + t * kABytes, a_src(q, t), kABytes, full0 + 8 * i);
         }
         pdl_wait();
         for (int j = 0; j < i; ++j, wk.next(a))
-          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + kABytes, b_src(wk), kBBytes, full0 + 8 * j);
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + TT * kABytes, b_src(wk), kBBytes, full0 + 8 * j);
       }
       for (; wk.live(a) && ok; ++i, wk.next(a)) {
         const int slot = i % S, round = i / S;
         if (round > 0) ok = mbar_wait(empty0 + 8 * slot, (round - 1) & 1, a.status, 501);
         if (!ok) break;
         const uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
-        mbar_expect_tx(full0 + 8 * slot, kStage);
-        bulk_load_1d(dst, a_src(wk), kABytes, full0 + 8 * slot);
-        bulk_load_1d(dst + kABytes, b_src(wk), kBBytes, full0 + 8 * slot);
+        const int nt = tiles_of(wk);
+        mbar_expect_tx(full0 + 8 * slot, nt * kABytes + kBBytes);
+        for (int t = 0; t < nt; ++t) bulk_load_1d(dst + t * kABytes, a_src(wk, t), kABytes, full0 + 8 * slot);
+        bulk_load_1d(dst + TT * kABytes, b_src(wk), kBBytes, full0 + 8 * slot);
       }
     }
   } else if (warp == 1) {
@@ -367,13 +376,19 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const bool last = wk.last_stage();
+        const int nt = wk.tile * TT + TT <= a.ntiles ? TT : a.ntiles - wk.tile * TT;
         if (elect_one()) {
-          const uint32_t abase = smem_u32(ring + (size_t)slot * kStage), bbase = abase + kABytes;
+          const uint32_t abase = smem_u32(ring + (size_t)slot * kStage), bbase = abase + TT * kABytes;
 #pragma unroll
-          for (int st = 0; st < KS / 32; ++st) {
-            const uint64_t adesc = adesc_hi | (uint64_t)(((abase + st * 4096) >> 4) & 0x3FFF);
-            const uint64_t bdesc = bdesc_hi | (uint64_t)(((bbase + st * (N * 32)) >> 4) & 0x3FFF);
-            umma_f8_ss(tmem_base + b * N, adesc, bdesc, idesc, (first && st == 0) ? 0u : 1u);
+          for (int t = 0; t < TT; ++t) {
+            if (t < nt) {
+#pragma unroll
+              for (int st = 0; st < KS / 32; ++st) {
+                const uint64_t adesc = adesc_hi | (uint64_t)(((abase + t * kABytes + st * 4096) >> 4) & 0x3FFF);
+                const uint64_t bdesc = bdesc_hi | (uint64_t)(((bbase + st * (N * 32)) >> 4) & 0x3FFF);
+                umma_f8_ss(tmem_base + b * (TT * N) + t * N, adesc, bdesc, idesc, (first && st == 0) ? 0u : 1u);
+              }
+            }
           }
           umma_commit(empty0 + 8 * slot);
           if (last) umma_commit(dfull0 + 8 * b);
@@ -395,65 +410,81 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
     const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     pdl_wait();  // the row scales of x come from the preparation kernel in front
     for (int it = 0; wk.live(a) && ok; ++it) {
-      const int b = it % ND, tile = wk.tile, split = wk.split;
+      const int b = it % ND, group = wk.tile, split = wk.split;
+      const int nt = group * TT + TT <= a.ntiles ? TT : a.ntiles - group * TT;
       // this role takes no part in the stages: on to the item's end
       wk.k = wk.k1 - 1;
       wk.next(a);
       ok = __all_sync(0xffffffffu, mbar_wait(dfull0 + 8 * b, (it / ND) & 1, a.status, 504));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      float dot[HM];
+      float dot[TT][HM];
 #pragma unroll
-      for (int g = 0; g < HM / G; ++g) {
-        float part[G];
+      for (int t = 0; t < TT; ++t) {
 #pragma unroll
-        for (int j = 0; j < G; ++j) part[j] = 0.f;
+        for (int g = 0; g < HM / G; ++g) {
+          float part[G];
 #pragma unroll
-        for (int p = P - 1; p >= 0; --p) {  // the smallest pieces first
-          uint32_t t[G];
-          tmem_ld_cols<G>(tmem_base + lane_base + b * N + p * MP + hf * HM + g * G, t);
-          tmem_ld_cols_wait<G>(t);
+          for (int j = 0; j < G; ++j) part[j] = 0.f;
+          if (t < nt) {
 #pragma unroll
-          for (int j = 0; j < G; ++j) part[j] = fmaf(__uint_as_float(t[j]), kPieceScale[p >> 1], part[j]);
+            for (int p = P - 1; p >= 0; --p) {  // the smallest pieces first
+              uint32_t v[G];
+              tmem_ld_cols<G>(tmem_base + lane_base + b * (TT * N) + t * N + p * MP + hf * HM + g * G, v);
+              tmem_ld_cols_wait<G>(v);
+#pragma unroll
+              for (int j = 0; j < G; ++j) part[j] = fmaf(__uint_as_float(v[j]), kPieceScale[p >> 1], part[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < G; ++j) dot[t][g * G + j] = part[j];
         }
-#pragma unroll
-        for (int j = 0; j < G; ++j) dot[g * G + j] = part[j];
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(dfree0 + 8 * b);
-      const int row = tile * kTileRows + r;
-      const float sc = row < a.out_dim ? __ldg(a.scale + row) : 0.f;
-      const float bi = (a.bias && row < a.out_dim) ? __ldg(a.bias + row) : 0.f;
-      if (a.splits == 1) {
 #pragma unroll
-        for (int j = 0; j < HM; ++j) {
-          const int m = hf * HM + j;
-          if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(dot[j] * __ldg(a.xinv + m), sc, bi);
-        }
-      } else {
-        // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
-        // partials in split order (so the result does not depend on arrival order) and stores.
-        float* part = a.scratch + ((size_t)tile * a.splits + split) * (MP * kTileRows);
-#pragma unroll
-        for (int j = 0; j < HM; ++j) part[(hf * HM + j) * kTileRows + r] = dot[j];
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        if (et == 0) *last_flag = (atomicAdd(a.counters + tile, 1u) == (unsigned)a.splits - 1) ? 1 : 0;
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
-        if (*last_flag) {
-          __threadfence();
-          const float* base = a.scratch + (size_t)tile * a.splits * (MP * kTileRows);
+      for (int t = 0; t < TT; ++t) {
+        if (t >= nt) break;
+        const int tile = group * TT + t;
+        const int row = tile * kTileRows + r;
+        const float sc = row < a.out_dim ? __ldg(a.scale + row) : 0.f;
+        const float bi = (a.bias && row < a.out_dim) ? __ldg(a.bias + row) : 0.f;
+        if (a.splits == 1) {
 #pragma unroll
           for (int j = 0; j < HM; ++j) {
             const int m = hf * HM + j;
-            float sum = 0.f;
-            for (int s2 = 0; s2 < a.splits; ++s2) sum += __ldcg(base + (size_t)s2 * (MP * kTileRows) + m * kTileRows + r);
-            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(sum * __ldg(a.xinv + m), sc, bi);
+            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(dot[t][j] * __ldg(a.xinv + m), sc, bi);
           }
-          if (et == 0) a.counters[tile] = 0;
+        } else {
+          // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
+          // partials in split order (so the result does not depend on arrival order) and stores.
+          float* part = a.scratch + ((size_t)tile * a.splits + split) * (MP * kTileRows);
+#pragma unroll
+          for (int j = 0; j < HM; ++j) part[(hf * HM + j) * kTileRows + r] = dot[t][j];
+          __threadfence();
+          asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+          if (et == 0) *last_flag = (atomicAdd(a.counters + tile, 1u) == (unsigned)a.splits - 1) ? 1 : 0;
+          asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+          if (*last_flag) {
+            __threadfence();
+            const float* base = a.scratch + (size_t)tile * a.splits * (MP * kTileRows);
+            float sum[HM];
+#pragma unroll
+            for (int j = 0; j < HM; ++j) sum[j] = 0.f;
+            for (int s2 = 0; s2 < a.splits; ++s2) {  // a split's HM loads are independent: all in flight together
+#pragma unroll
+              for (int j = 0; j < HM; ++j) sum[j] += __ldcg(base + (size_t)s2 * (MP * kTileRows) + (hf * HM + j) * kTileRows + r);
+            }
+#pragma unroll
+            for (int j = 0; j < HM; ++j) {
+              const int m = hf * HM + j;
+              if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(sum[j] * __ldg(a.xinv + m), sc, bi);
+            }
+            if (et == 0) a.counters[tile] = 0;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       }
     }
   }
@@ -517,10 +548,10 @@ Fp8Bufs* fp8_bufs(int device, bool allocate = true) {
   return &bufs[device];
 }
 
-template <int N, int P, int MP, bool XBF16>
+template <int N, int P, int MP, bool XBF16, int TT = 1>
 int launch_pass(const goph_fp8_linear* w, float* out, const void* x, int nb, Fp8Bufs* bufs, cudaStream_t stream) {
-  constexpr int KS = N <= 64 ? 256 : 128;
-  constexpr int kStage = kTileRows * KS + N * KS;
+  constexpr int KS = (N <= 64 && TT == 1) ? 256 : 128;
+  constexpr int kStage = TT * kTileRows * KS + N * KS;
   DeviceState& st = device_state(w->device);
   Fp8Args a;
   memset(&a, 0, sizeof a);
@@ -540,10 +571,11 @@ int launch_pass(const goph_fp8_linear* w, float* out, const void* x, int nb, Fp8
   a.nks = w->in_dim / KS;
   int max_items = (int)(kScratchFloats / ((size_t)MP * kTileRows));
   if (a.ntiles > (int)kMaxCounters) max_items = 0;
+  const int ngroups = (a.ntiles + TT - 1) / TT;  // items are groups of TT row tiles x K splits
   a.splits = options().mlx_splits > 0 ? (options().mlx_splits < a.nks ? options().mlx_splits : a.nks)
-                                      : tc_choose_splits(a.ntiles, a.nks, st.sm_count, max_items, 2.f + MP / 16.f);
+                                      : tc_choose_splits(ngroups, a.nks, st.sm_count, max_items / TT, 2.f + TT * MP / 16.f);
   while (a.splits > 1 && (long)a.ntiles * a.splits > max_items) --a.splits;
-  a.items = a.ntiles * a.splits;
+  a.items = ngroups * a.splits;
   int stages = (int)((kSmemBudget - 2048) / kStage);
   if (stages > kMaxStages) stages = kMaxStages;
   a.stages = stages;
@@ -562,7 +594,7 @@ int launch_pass(const goph_fp8_linear* w, float* out, const void* x, int nb, Fp8
   cfg.blockDim = dim3(256);
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, fp8_prep_x_kernel<P, XBF16>, x, bufs->xb, bufs->xinv, nb, w->in_dim, N, MP));
-  auto kern = fp8_mma_kernel<N, P, MP, KS>;
+  auto kern = fp8_mma_kernel<N, P, MP, KS, TT>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
   cfg.blockDim = dim3(kThreads);
@@ -627,12 +659,12 @@ int tc_gemm_fp8(const goph_fp8_linear* w, float* out, const void* x, bool x_bf16
     float* op = out + (size_t)b0 * w->out_dim;
     int rc, nb;
     if (x_bf16) {
-      // two pieces hold a bf16 value; above 32 rows the kernel that converts the weights to bf16
-      // is the faster one (8192 x 8192, 64 rows: 37 against 45 us)
-      if (left > 32) return tc_gemm_fp8_converted(w, op, xp, true, left, stream);
+      // two pieces hold a bf16 value; from 17 rows two row tiles share each B tile
+      if (options().fp8_convert && left > 32) return tc_gemm_fp8_converted(w, op, xp, true, left, stream);
       if (left <= 8) rc = launch_pass<16, 2, 8, true>(w, op, xp, nb = left, bufs, stream);
       else if (left <= 16) rc = launch_pass<32, 2, 16, true>(w, op, xp, nb = left, bufs, stream);
-      else rc = launch_pass<64, 2, 32, true>(w, op, xp, nb = left, bufs, stream);
+      else if (left <= 32) rc = launch_pass<64, 2, 32, true, 2>(w, op, xp, nb = left, bufs, stream);
+      else rc = launch_pass<128, 2, 64, true, 2>(w, op, xp, nb = left < 64 ? left : 64, bufs, stream);
     } else {
       // six pieces hold an f32 exactly
       if (left <= 2) rc = launch_pass<16, 6, 2, false>(w, op, xp, nb = left, bufs, stream);

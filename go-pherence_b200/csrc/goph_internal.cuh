@@ -60,6 +60,7 @@ struct Options {
   int mlx_unpack = 0;
   int gguf_layout = 0; // as mlx_layout, for Q4_K / Q8_0 matrices
   int fp8_layout = 0;  // as mlx_layout, for FP8 linears
+  int fp8_convert = 0; // 1: bf16 batches above 32 rows of a tensor-core FP8 linear go through the kernel that turns e4m3 into bf16
   int mlx_rows = 0, gguf_rows = 0, fp8_rows = 0;
   int mlx_ctas_per_sm = 0;  // tuning aid: cap on resident CTAs per SM of the MLX streaming kernel and of product lists (0 = by shape)
 };

@@ -165,6 +165,8 @@ GOPH_API int goph_set_option(const char* name, int value) {
     o.mlx_layout = value;
   } else if (!strcmp(name, "mlx_cluster")) {
     o.mlx_cluster = value ? 1 : 0;
+  } else if (!strcmp(name, "fp8_convert")) {
+    o.fp8_convert = value ? 1 : 0;
   } else if (!strcmp(name, "mlx_chunks")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_chunks=%d not in 0..2", value);
     o.mlx_chunks = value;

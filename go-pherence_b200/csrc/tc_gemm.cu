@@ -589,10 +589,17 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         if (*last_flag) {
           __threadfence();
           const float* base = a.scratch + (size_t)tile * a.splits * (NC * kTileRows);
-          for (int m = cq * HC; m < cq * HC + HC && m < a.batch; ++m) {
-            float sum = 0.f;
-            for (int s2 = 0; s2 < a.splits; ++s2) sum += __ldcg(base + (size_t)s2 * (NC * kTileRows) + m * kTileRows + r);
-            if (row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum);
+          float sum[HC];
+#pragma unroll
+          for (int j = 0; j < HC; ++j) sum[j] = 0.f;
+          for (int s2 = 0; s2 < a.splits; ++s2) {  // a split's HC loads are independent: all in flight together
+#pragma unroll
+            for (int j = 0; j < HC; ++j) sum[j] += __ldcg(base + (size_t)s2 * (NC * kTileRows) + (cq * HC + j) * kTileRows + r);
+          }
+#pragma unroll
+          for (int j = 0; j < HC; ++j) {
+            const int m = cq * HC + j;
+            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum[j]);
           }
           if (et == 0) a.counters[tile] = 0;
         }
