@@ -97,6 +97,9 @@ int goph_sm_count(int device);
  *                 weight): the tensor-core layout serves every batch size on the tensor cores (the
  *                 e4m3 bytes go to the MMA as they lie; f32 activations as six e4m3 pieces, exact,
  *                 bf16 activations as two); the row-major layout is served by the CUDA-core kernels
+ *   "fp8_convert" 1: bf16 batches of more than 32 rows on a tensor-core FP8 linear go through the
+ *                 kernel that turns the e4m3 bytes into bf16 (ahead at 8192 x 8192 x 64, behind on
+ *                 matrices with more row tiles); 0 (default): the e4m3 kernel serves every batch
  *   "mlx_digits"  signed base-128 digits each activation is written in on the tensor-core path,
  *                 relative to the largest magnitude of its 64-element group: 4 (default, 27 bits)
  *                 or 3 (20 bits; enough for bf16-valued activations)
