@@ -72,7 +72,7 @@ __device__ long long g_mma_trace[8][64];
 
 constexpr int kTileRows = 128;
 constexpr int kChunkK = 256;                  // elements per pipeline stage
-constexpr int kStageMBytes = kTileRows * 16;  // 16 bytes of scales per row and stage in every format
+constexpr int kStageMBytes = kTileRows * 16;  // 16 bytes of scales per row and stage (32 for Q6_K, see Fmt)
 
 // What differs between the weight formats that share this kernel.  A stage is 128 rows x 256
 // elements: the weights as the shared-memory image the tensor core (or the converters) want,
@@ -84,18 +84,28 @@ constexpr int kStageMBytes = kTileRows * 16;  // 16 bytes of scales per row and 
 //   Q80   256 signed bytes per row, stored as K-major 8x16-byte core matrices
 //         [K step][K half][row group][row][16 B] so the MMA reads them from shared memory as they
 //         lie — no conversion at all; 8 f16 block scales.  One accumulator block per 32-element block.
-enum { FMT_MLX4 = 0, FMT_Q4K = 1, FMT_Q80 = 2 };
+//   Q5K   the 5-bit values written out as 256 unsigned bytes per row at upload (1 byte per weight
+//         on the device instead of 0.69: the price of the tensor-core path), in Q80's order; the
+//         Q4_K header {d, dmin, 8 x (sc | m << 6)}.  One accumulator block per 32-element sub-block.
+//   Q6K   the 6-bit values minus 32 as 256 signed bytes per row (1 byte per weight instead of
+//         0.82), in Q80's order; 16 int8 scales + f16 d per row (32 bytes with padding).  One block
+//         per K step of 32, whose two 16-element scale groups keep their sums apart like Q4_K's
+//         sub-block pairs: the digits of the step's first 16 positions stand in B rows [0, N/2),
+//         those of the last 16 in [N/2, N).
+enum { FMT_MLX4 = 0, FMT_Q4K = 1, FMT_Q80 = 2, FMT_Q5K = 3, FMT_Q6K = 4 };
 template <int FMT>
 struct Fmt {
-  static constexpr bool kConv = FMT != FMT_Q80;                 // nibbles -> bytes through TMEM
+  static constexpr bool kConv = FMT == FMT_MLX4 || FMT == FMT_Q4K;  // nibbles -> bytes through TMEM; else the MMA reads the stage's bytes
+  static constexpr bool kHalves = FMT == FMT_Q4K || FMT == FMT_Q6K;  // two scale groups per accumulator block, in the two halves of its columns
   // accumulator blocks per 256-element chunk.  Q4_K: one block per PAIR of 32-element sub-blocks;
   // the two sub-blocks keep their sums apart inside the block because the activation digits of
   // the even sub-block stand in the first half of the B rows (zeros in the odd K steps) and those
   // of the odd sub-block in the second half: accumulator columns [0, N/2) and [N/2, N)
-  static constexpr int kBlocks = FMT == FMT_Q80 ? 8 : 4;
-  static constexpr int kGroup = FMT == FMT_MLX4 ? 64 : 32;      // elements per scale
-  static constexpr int kStageWBytes = kTileRows * (FMT == FMT_Q80 ? 256 : 128);
-  static constexpr int kStageBytes = kStageWBytes + kStageMBytes;  // the B tile follows
+  static constexpr int kBlocks = kConv ? 4 : 8;
+  static constexpr int kGroup = FMT == FMT_MLX4 ? 64 : 32;      // elements per entry of the activation tables
+  static constexpr int kStageWBytes = kTileRows * (kConv ? 128 : 256);
+  static constexpr int kMetaRow = FMT == FMT_Q6K ? 32 : 16;     // bytes of scales per row and stage
+  static constexpr int kStageBytes = kStageWBytes + kTileRows * kMetaRow;  // the B tile follows
 };
 constexpr int kStageWBytes = Fmt<FMT_MLX4>::kStageWBytes;
 constexpr int kStageBytes = Fmt<FMT_MLX4>::kStageBytes;
@@ -204,7 +214,7 @@ struct StageWalk {
 // G32: sums and scales per 32 elements (one warp each) instead of per 64.  NATURAL: the B bytes of
 // a K step in element order (for A operands that lie in memory in element order) instead of the
 // order the nibble converters produce.
-template <int DIGITS, bool G32 = false, bool NATURAL = false>
+template <int DIGITS, bool G32 = false, bool NATURAL = false, bool PAIRH = false>
 __global__ void __launch_bounds__(64)
 mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, float* __restrict__ xtab, int batch,
                   int in_dim, int N) {
@@ -258,9 +268,10 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
     int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
     q = (q - dig) >> 7;
     int n = m * DIGITS + d;
-    if (PAIRED) {  // the other sub-block's half of the rows holds zeros at this K position
-      const int other = n + ((step & 1) ? 0 : db);
-      n += (step & 1) ? db : 0;
+    if (PAIRED || PAIRH) {  // the other scale group's half of the rows holds zeros at this K position
+      const bool second = PAIRH ? (pos & 16) != 0 : (step & 1) != 0;  // Q6_K: by the half of the step; Q4_K: by the step
+      const int other = n + (second ? 0 : db);
+      n += second ? db : 0;
       xb[base + (other >> 3) * 128 + (other & 7) * 16] = 0;
     }
     xb[base + (n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
@@ -271,7 +282,7 @@ mlx_prep_x_kernel(const float* __restrict__ x, unsigned char* __restrict__ xb, f
 // pipeline starts): digits into the resident B tiles in shared memory, sums and scales into the
 // tables the epilogue reads.  A warp takes one 64-element group at a time, lane l the elements l
 // and l + 32; the arithmetic and its order are those of mlx_prep_x_kernel.
-template <int DIGITS, bool G32, bool NATURAL, int N>
+template <int DIGITS, bool G32, bool NATURAL, int N, bool PAIRH = false>
 __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int batch, int in_dim, unsigned char* bres,
                                               float* xsum, float* xfs, int warp, int lane, int nwarps, int cbegin, int cend) {
   constexpr int QBITS = DIGITS == 4 ? 26 : 19;
@@ -318,9 +329,10 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
         int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
         q = (q - dig) >> 7;
         int n = m * DIGITS + d;
-        if (PAIRED) {
-          const int other = n + ((step & 1) ? 0 : db);
-          n += (step & 1) ? db : 0;
+        if (PAIRED || PAIRH) {
+          const bool second = PAIRH ? (pos & 16) != 0 : (step & 1) != 0;
+          const int other = n + (second ? 0 : db);
+          n += second ? db : 0;
           base[(other >> 3) * 128 + (other & 7) * 16] = 0;
         }
         base[(n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
@@ -338,7 +350,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   constexpr int kEpiWarps = 4 * EP, kEpiThreads = kEpiWarps * 32;
   constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
   constexpr int kThreads = mma_threads<N, FMT>();
-  static_assert(MB * DIGITS * (FMT == FMT_Q4K ? 2 : 1) <= N, "the digits of the activation rows must fit the N columns");
+  static_assert(MB * DIGITS * (Fmt<FMT>::kHalves ? 2 : 1) <= N, "the digits of the activation rows must fit the N columns");
   static_assert(N == 8 || N == 16 || N == 32, "accumulator blocks of 8, 16 or 32 columns");
   typedef Fmt<FMT> F;
   constexpr int kBlocks = F::kBlocks;
@@ -427,7 +439,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     pdl_wait();
     // every item of this CTA covers the same K range (the grid is a multiple of the K splits)
     if (sw.live(a))
-      prep_x_in_cta<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80, N>(a.x, a.batch, a.in_dim, bres, xsum, xfs, warp, lane, kThreads / 32,
+      prep_x_in_cta<DIGITS, FMT != FMT_MLX4, !F::kConv, N, FMT == FMT_Q6K>(a.x, a.batch, a.in_dim, bres, xsum, xfs, warp, lane, kThreads / 32,
                                                                  sw.c, sw.c1);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the MMA reads the digits through the async proxy
     __syncthreads();
@@ -473,7 +485,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     // cycles an issue costs against a single diverged thread.)
     {
       // instruction descriptor: D s32, A u8 (nibbles) or s8 (Q8_0 bytes), B s8, both K-major, N, M=128
-      const uint32_t idesc = (2u << 4) | ((FMT == FMT_Q80 ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+      const uint32_t idesc = (2u << 4) | (((FMT == FMT_Q80 || FMT == FMT_Q6K) ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
       // A from shared memory (Q8_0): K-adjacent core matrices 16 row groups apart, row groups 128 B apart
       const uint64_t adesc_hi = ((uint64_t)(2048u >> 4) << 16) | ((uint64_t)(128u >> 4) << 32) | (1ull << 46);
       constexpr uint32_t kLBO = (N / 8) * 128, kSBO = 128;  // K-adjacent / N-adjacent core matrices
@@ -500,7 +512,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
 #pragma unroll
             for (int step = 0; step < 8; ++step) {  // K = 32 per step
               const uint64_t bdesc = desc_hi | (uint64_t)(((bbase + step * (N * 32)) >> 4) & 0x3FFF);
-              if (FMT != FMT_Q80) {  // two steps accumulate into the block of their 64 elements
+              if (F::kConv) {  // two steps accumulate into the block of their 64 elements
                 umma_i8_ts(dcol + (step >> 1) * N, acol + step * 8, bdesc, idesc, step & 1);
               } else {
                 const uint32_t abase = smem_u32(ring + (size_t)slot * kStage) + step * 4096;
@@ -602,14 +614,17 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       int b = i % ND, slot = i % S;
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
       uint4 mvs[C];
+      uint32_t q6d = 0;  // Q6_K: the super-block's f16 d (the 16 int8 scales are in mvs)
       const int nc = sw.nc();
       if (ok) {
         uint32_t seen = 1u;
 #pragma unroll
         for (int cc = 0; cc < C; ++cc) {
           mvs[cc] = make_uint4(0, 0, 0, 0);
-          if (cc < nc) mvs[cc] = *reinterpret_cast<const uint4*>(ring + (size_t)slot * kStage + cc * kStageBytes + kStageWBytes + r * 16);
-          seen |= mvs[cc].x;
+          const unsigned char* mrow = ring + (size_t)slot * kStage + cc * kStageBytes + kStageWBytes + r * F::kMetaRow;
+          if (cc < nc) mvs[cc] = *reinterpret_cast<const uint4*>(mrow);
+          if (FMT == FMT_Q6K) q6d = *reinterpret_cast<const uint32_t*>(mrow + 16);
+          seen |= mvs[cc].x | q6d;
         }
         // the scale data is in registers: one lane releases the stage for the warp (the values are
         // consumed by the shuffle, so every lane's loads have completed before the arrival)
@@ -689,6 +704,40 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
                   const float dot = paired_dot(hh * db + DIGITS * m) * xfs[m * groups + ti];
                   acc[m] = fmaf(sc, dot, acc[m]);
                   acc[m] = fmaf(bi, xsum[m * groups + ti], acc[m]);
+                }
+              }
+            }
+          } else if (FMT == FMT_Q5K) {
+            // one 32-element sub-block: (sc*d) and -(m*dmin), each rounded to f32 as dequantRowQ5K does
+            const float d16 = __half2float(__ushort_as_half((unsigned short)(meta[0] & 0xFFFFu)));
+            const float dmin16 = __half2float(__ushort_as_half((unsigned short)(meta[0] >> 16)));
+            const int bit = 12 * blk, wi = bit >> 5, sh = bit & 31;
+            const uint32_t lo = wi == 0 ? meta[1] : wi == 1 ? meta[2] : meta[3];
+            const uint32_t hi = wi == 0 ? meta[2] : wi == 1 ? meta[3] : 0u;
+            const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+            const float sc = __fmul_rn((float)(f & 63u), d16), bi = -__fmul_rn((float)(f >> 6), dmin16);
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+              if (MB == 1 || m < a.batch) {
+                const float dot = digits_dot(DIGITS * m) * xfs[m * groups + gbase + blk];
+                acc[m] = fmaf(sc, dot, acc[m]);
+                acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
+              }
+            }
+          } else if (FMT == FMT_Q6K) {
+            // the step's two 16-element scale groups: columns [0, N/2) and [N/2, N); multiplier
+            // d * sc rounded to f32 as dequantRowQ6K does
+            const float d16 = __half2float(__ushort_as_half((unsigned short)(q6d & 0xFFFFu)));
+            const uint32_t sw4 = (blk >> 1) == 0 ? meta[0] : (blk >> 1) == 1 ? meta[1] : (blk >> 1) == 2 ? meta[2] : meta[3];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const int s8 = (int)(signed char)((sw4 >> (8 * (2 * (blk & 1) + hh))) & 0xFFu);
+              const float sc = __fmul_rn(d16, (float)s8);
+#pragma unroll
+              for (int m = 0; m < MB; ++m) {
+                if (MB == 1 || m < a.batch) {
+                  const float dot = digits_dot(hh * (N / 2) + DIGITS * m) * xfs[m * groups + gbase + blk];
+                  acc[m] = fmaf(sc, dot, acc[m]);
                 }
               }
             }
@@ -1037,7 +1086,7 @@ static int launch_impl(const TiledDesc& w, const MmaArgs& a0, cudaStream_t strea
     cfg.gridDim = dim3(a.batch * (a.in_dim / 64));
     cfg.blockDim = dim3(64);
     note_launch();
-    GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, FMT == FMT_Q80>, a.x,
+    GOPH_CUDA(cudaLaunchKernelEx(&cfg, mlx_prep_x_kernel<DIGITS, FMT != FMT_MLX4, !Fmt<FMT>::kConv, FMT == FMT_Q6K>, a.x,
                                  const_cast<unsigned char*>(a.xb), const_cast<float*>(a.xtab), a.batch, a.in_dim, N));
   }
   auto kern = mlx_mma_kernel<N, DIGITS, MB, FMT, FUSED, C>;
@@ -1150,8 +1199,8 @@ static int tiled_launch(const TiledDesc& w, float* out, const float* x, int batc
   a.ntiles = (w.out_dim + kTileRows - 1) / kTileRows;
   a.nchunks = w.in_dim / kChunkK;
   // activation rows one launch can take: the accumulator blocks of a stage must fit TMEM twice
-  const int cap = FMT == FMT_Q4K ? (digits == 3 ? 5 : 4) : 8;  // Q4_K needs two columns per digit
-  constexpr bool kQ4K = FMT == FMT_Q4K;
+  constexpr bool kQ4K = Fmt<FMT>::kHalves;  // Q4_K and Q6_K need two columns per digit
+  const int cap = kQ4K ? (digits == 3 ? 5 : 4) : 8;
   for (int b0 = 0; b0 < batch;) {
     int nb = batch - b0 < cap ? batch - b0 : cap;
     a.x = x + (size_t)b0 * w.in_dim;
@@ -1277,20 +1326,141 @@ __global__ void q80_dequant_tiled_kernel(const unsigned char* __restrict__ tiled
   out[i] = __fmul_rn(__half2float(__ushort_as_half(d)), (float)q);
 }
 
+// Q5_K super-blocks in the streaming layout {16-byte header, 8 x 16 bytes of nibbles, 8 x 4 bytes of
+// fifth bits} -> stages of unsigned bytes in Q80's order + the header; one thread per 16-byte unit.
+__global__ void q5k_tile_kernel(const unsigned char* __restrict__ blocks, unsigned char* __restrict__ tiled, int out_dim,
+                                int ntiles, int nchunks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nstages = (size_t)ntiles * nchunks;
+  if (idx >= nstages * (128 * 17)) return;
+  size_t stg = idx / (128 * 17);
+  int rem = (int)(idx - stg * (128 * 17));
+  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
+  int r = rem / 17, hb = rem - r * 17, row = tile * 128 + r;
+  unsigned char* dst = tiled + stg * Fmt<FMT_Q5K>::kStageBytes;
+  const unsigned char* src = blocks + ((size_t)row * nchunks + chunk) * 176;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (hb == 16) {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(src);
+    *reinterpret_cast<uint4*>(dst + Fmt<FMT_Q5K>::kStageWBytes + r * 16) = v;
+    return;
+  }
+  const int step = hb >> 1, half = hb & 1;
+  if (row < out_dim) {
+    const uint2 q = *reinterpret_cast<const uint2*>(src + 16 + 16 * step + 8 * half);  // 16 nibbles
+    const uint32_t fifth = *reinterpret_cast<const uint32_t*>(src + 144 + 4 * step) >> (16 * half);
+    uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t nib = ((j < 8 ? q.x : q.y) >> (4 * (j & 7))) & 0xFu;
+      out[j >> 2] |= (nib | (((fifth >> j) & 1u) << 4)) << (8 * (j & 3));
+    }
+    v = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  *reinterpret_cast<uint4*>(dst + step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16) = v;
+}
+
+// Q6_K planes (low nibbles, two-bit highs, int8 scales, f16 d) -> stages of signed bytes (value - 32)
+// in Q80's order + {16 scales, d, padding} per row; one thread per 16-byte unit.
+__global__ void q6k_tile_kernel(const unsigned char* __restrict__ lo, const unsigned char* __restrict__ hi,
+                                const signed char* __restrict__ sc, const uint16_t* __restrict__ dd,
+                                unsigned char* __restrict__ tiled, int out_dim, int in_dim, int ntiles, int nchunks) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t nstages = (size_t)ntiles * nchunks;
+  if (idx >= nstages * (128 * 18)) return;
+  size_t stg = idx / (128 * 18);
+  int rem = (int)(idx - stg * (128 * 18));
+  int tile = (int)(stg / nchunks), chunk = (int)(stg - (size_t)tile * nchunks);
+  int r = rem / 18, hb = rem - r * 18, row = tile * 128 + r;
+  unsigned char* dst = tiled + stg * Fmt<FMT_Q6K>::kStageBytes;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (hb == 16) {
+    if (row < out_dim) v = *reinterpret_cast<const uint4*>(sc + (size_t)row * (in_dim / 16) + chunk * 16);
+    *reinterpret_cast<uint4*>(dst + Fmt<FMT_Q6K>::kStageWBytes + r * 32) = v;
+    return;
+  }
+  if (hb == 17) {
+    if (row < out_dim) v.x = dd[(size_t)row * nchunks + chunk];
+    *reinterpret_cast<uint4*>(dst + Fmt<FMT_Q6K>::kStageWBytes + r * 32 + 16) = v;
+    return;
+  }
+  const int step = hb >> 1, half = hb & 1;
+  if (row < out_dim) {
+    const size_t col = (size_t)chunk * 256 + step * 32 + half * 16;  // 16 elements: two words of nibbles, one of highs
+    const uint2 wl = *reinterpret_cast<const uint2*>(lo + (size_t)row * (in_dim / 2) + col / 2);
+    const uint32_t wh = *reinterpret_cast<const uint32_t*>(hi + (size_t)row * (in_dim / 4) + col / 4);
+    uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int q = (int)((((j < 8 ? wl.x : wl.y) >> (4 * (j & 7))) & 0xFu) | (((wh >> (2 * j)) & 3u) << 4)) - 32;
+      out[j >> 2] |= (uint32_t)(q & 0xFF) << (8 * (j & 3));
+    }
+    v = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  *reinterpret_cast<uint4*>(dst + step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16) = v;
+}
+
+// dequantRowQ5K / dequantRowQ6K from the tiled layouts (loader/gguf/quant_matrix.go:331-426), the
+// roundings of the streaming layouts' kernels.
+__global__ void q5k_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, float* __restrict__ out, int out_dim,
+                                         int in_dim, int nchunks) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)out_dim * in_dim) return;
+  int row = (int)(i / in_dim), col = (int)(i - (size_t)row * in_dim);
+  int chunk = col >> 8, k = col & 255, step = k >> 5, half = (k >> 4) & 1, r = row & 127;
+  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * Fmt<FMT_Q5K>::kStageBytes;
+  const uint4 h = *reinterpret_cast<const uint4*>(stg + Fmt<FMT_Q5K>::kStageWBytes + r * 16);
+  const int bit = 12 * step, wi = bit >> 5, sh = bit & 31;
+  const uint32_t lo = wi == 0 ? h.y : wi == 1 ? h.z : h.w, hi = wi == 0 ? h.z : wi == 1 ? h.w : 0u;
+  const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+  const float sd = __fmul_rn((float)(f & 63u), __half2float(__ushort_as_half((unsigned short)(h.x & 0xFFFFu))));
+  const float md = __fmul_rn((float)(f >> 6), __half2float(__ushort_as_half((unsigned short)(h.x >> 16))));
+  const unsigned char q = stg[step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16 + (k & 15)];
+  out[i] = __fsub_rn(__fmul_rn(sd, (float)q), md);
+}
+
+__global__ void q6k_dequant_tiled_kernel(const unsigned char* __restrict__ tiled, float* __restrict__ out, int out_dim,
+                                         int in_dim, int nchunks) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)out_dim * in_dim) return;
+  int row = (int)(i / in_dim), col = (int)(i - (size_t)row * in_dim);
+  int chunk = col >> 8, k = col & 255, step = k >> 5, half = (k >> 4) & 1, r = row & 127;
+  const unsigned char* stg = tiled + ((size_t)(row >> 7) * nchunks + chunk) * Fmt<FMT_Q6K>::kStageBytes;
+  const unsigned char* mrow = stg + Fmt<FMT_Q6K>::kStageWBytes + r * 32;
+  const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(mrow + 16)));
+  const signed char sc = (signed char)mrow[k >> 4];
+  const signed char q = (signed char)stg[step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16 + (k & 15)];
+  out[i] = __fmul_rn(__fmul_rn(d, (float)sc), (float)q);
+}
+
 bool gguf_mma_supported(int qtype, int in_dim) {
-  return (qtype == GOPH_GGUF_Q4_K || qtype == GOPH_GGUF_Q8_0) && in_dim % kChunkK == 0 && in_dim <= kMaxPrepIn;
+  return (qtype == GOPH_GGUF_Q4_K || qtype == GOPH_GGUF_Q8_0 || qtype == GOPH_GGUF_Q5_K || qtype == GOPH_GGUF_Q6_K) &&
+         in_dim % kChunkK == 0 && in_dim <= kMaxPrepIn;
 }
 
 int gguf_mma_make_tiled(goph_gguf_matrix* m) {
   const int ntiles = (m->out_dim + kTileRows - 1) / kTileRows, nchunks = m->in_dim / kChunkK;
   const bool q4 = m->qtype == GOPH_GGUF_Q4_K;
-  const size_t stage = q4 ? Fmt<FMT_Q4K>::kStageBytes : Fmt<FMT_Q80>::kStageBytes;
+  const size_t stage = q4 ? Fmt<FMT_Q4K>::kStageBytes
+                          : m->qtype == GOPH_GGUF_Q5_K ? Fmt<FMT_Q5K>::kStageBytes
+                          : m->qtype == GOPH_GGUF_Q6_K ? Fmt<FMT_Q6K>::kStageBytes : Fmt<FMT_Q80>::kStageBytes;
   const size_t bytes = (size_t)ntiles * nchunks * stage;
   unsigned char* t = nullptr;
   GOPH_CUDA(cudaMalloc(&t, bytes));
   if (q4) {
     size_t threads = (size_t)ntiles * nchunks * 128 * 9;
     q4k_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, t, m->out_dim, ntiles, nchunks);
+  } else if (m->qtype == GOPH_GGUF_Q5_K) {
+    size_t threads = (size_t)ntiles * nchunks * 128 * 17;
+    q5k_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, t, m->out_dim, ntiles, nchunks);
+  } else if (m->qtype == GOPH_GGUF_Q6_K) {
+    // planes behind one another: low nibbles in data; highs, int8 scales, f16 d in d16's buffer
+    const size_t n = (size_t)m->out_dim * m->in_dim;
+    const unsigned char* hi = reinterpret_cast<const unsigned char*>(m->d16);
+    size_t threads = (size_t)ntiles * nchunks * 128 * 18;
+    q6k_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, hi, reinterpret_cast<const signed char*>(hi + n / 4),
+                                                                reinterpret_cast<const uint16_t*>(hi + n / 4 + n / 16), t, m->out_dim,
+                                                                m->in_dim, ntiles, nchunks);
   } else {
     size_t threads = (size_t)ntiles * nchunks * 128 * 16;
     q80_tile_kernel<<<(unsigned)((threads + 255) / 256), 256>>>(m->data, m->d16, t, m->out_dim, m->in_dim, ntiles, nchunks);
@@ -1310,8 +1480,10 @@ int gguf_mma_launch(const goph_gguf_matrix* m, float* out, const float* x, int b
                     bool x_prepared) {
   if (!m->tiled) return fail(GOPH_E_UNSUPPORTED, "matrix is not in the tiled layout");
   TiledDesc d{m->tiled, m->device, m->out_dim, m->in_dim};
-  return m->qtype == GOPH_GGUF_Q4_K ? tiled_launch<FMT_Q4K>(d, out, x, batch, digits, stream, x_prepared)
-                                    : tiled_launch<FMT_Q80>(d, out, x, batch, digits, stream, x_prepared);
+  if (m->qtype == GOPH_GGUF_Q4_K) return tiled_launch<FMT_Q4K>(d, out, x, batch, digits, stream, x_prepared);
+  if (m->qtype == GOPH_GGUF_Q5_K) return tiled_launch<FMT_Q5K>(d, out, x, batch, digits, stream, x_prepared);
+  if (m->qtype == GOPH_GGUF_Q6_K) return tiled_launch<FMT_Q6K>(d, out, x, batch, digits, stream, x_prepared);
+  return tiled_launch<FMT_Q80>(d, out, x, batch, digits, stream, x_prepared);
 }
 
 int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream) {
@@ -1319,6 +1491,12 @@ int gguf_mma_dequant(const goph_gguf_matrix* m, float* out, cudaStream_t stream)
   if (m->qtype == GOPH_GGUF_Q4_K) {
     size_t units = (size_t)m->out_dim * (m->in_dim / 32);
     q4k_dequant_tiled_kernel<<<(unsigned)((units + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);
+  } else if (m->qtype == GOPH_GGUF_Q5_K || m->qtype == GOPH_GGUF_Q6_K) {
+    size_t n = (size_t)m->out_dim * m->in_dim;
+    if (m->qtype == GOPH_GGUF_Q5_K)
+      q5k_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);
+    else
+      q6k_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);
   } else {
     size_t n = (size_t)m->out_dim * m->in_dim;
     q80_dequant_tiled_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(m->tiled, out, m->out_dim, m->in_dim, nchunks);

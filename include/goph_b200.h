@@ -49,7 +49,8 @@ enum {
 
 /* GGUF tensor type ids accepted by goph_gguf_upload (loader/gguf/gguf.go:51-56).  Q5_K and Q6_K
    (176- and 210-byte super-blocks of 256 elements; loader/gguf/quant_matrix.go:331-426) go through
-   the CUDA-core streaming kernel only. */
+   the CUDA-core streaming kernel at file size, or, for large matrices ("gguf_layout"), to the
+   tensor-core kernel with their values written out as one byte per weight. */
 enum { GOPH_GGUF_Q8_0 = 8, GOPH_GGUF_Q4_K = 12, GOPH_GGUF_Q5_K = 13, GOPH_GGUF_Q6_K = 14 };
 
 typedef struct goph_mlx_weight goph_mlx_weight;   /* nvidia.GPUMLXWeight      (runtime/mlx.go:21-32)   */
@@ -89,7 +90,8 @@ int goph_sm_count(int device);
  *                 scales and biases; the row-major layout feeds the CUDA-core kernels.  0 (default):
  *                 tiled for matrices of 8 Mi weights or more, row-major below; 1: always row-major;
  *                 2: tiled whenever the shape allows
- *   "gguf_layout" the same choice for goph_gguf_upload (Q4_K and Q8_0; in_dim a multiple of 256):
+ *   "gguf_layout" the same choice for goph_gguf_upload (Q4_K, Q5_K, Q6_K, Q8_0; in_dim a multiple of 256;
+ *                 Q5_K and Q6_K take 1.06 / 1.13 bytes per weight in the tensor-core layout):
  *                 0 (default) tensor-core layout from 8 Mi weights, 1 always the streaming layout,
  *                 2 tensor-core layout whenever the shape allows.  "mlx_digits" and "mlx_splits"
  *                 apply to these products as well

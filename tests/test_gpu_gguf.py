@@ -183,13 +183,16 @@ def tiled_layout(gpu):
     assert gpu.KernelStatus() == 0   # no bounded wait gave up
 
 
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("out_dim,in_dim", [(128, 256), (64, 4096), (300, 512), (259, 2816)])
 def test_tiled_dequant_bit_exact(gpu, pkg, tiled_layout, qtype, out_dim, in_dim):
     raw = make(pkg, qtype, "deq-t", out_dim, in_dim)
     m = gpu.UploadGGUFMatrix(qtype, raw, in_dim, out_dim)
     padded = (out_dim + 127) // 128 * 128
-    assert m.ResidentBytes() == raw.size // out_dim * padded   # file bytes per row, rows padded to the 128-row tile
+    # bytes per row and 256 elements, rows padded to the 128-row tile: the file's for Q8_0 and Q4_K; Q5_K and
+    # Q6_K are written out as one byte per weight (+ 16 / 32 bytes of scales) for the tensor cores
+    per_chunk = {Q8_0: 272, Q4_K: 144, Q5_K: 272, Q6_K: 288}[qtype]
+    assert m.ResidentBytes() == padded * (in_dim // 256) * per_chunk
     out = out_with_canary(gpu, out_dim * in_dim)
     m.Dequant(out)
     gpu.Sync()
@@ -200,7 +203,7 @@ def test_tiled_dequant_bit_exact(gpu, pkg, tiled_layout, qtype, out_dim, in_dim)
 
 
 @pytest.mark.parametrize("digits", [4, 3])
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (4096, 4096), (259, 2816), (2048, 768), (64, 256), (19000, 1024)])
 def test_tiled_gemv_parity(gpu, pkg, tiled_layout, qtype, out_dim, in_dim, digits):
     gpu.SetOption("mlx_digits", digits)
@@ -227,7 +230,7 @@ def test_tiled_gemv_parity(gpu, pkg, tiled_layout, qtype, out_dim, in_dim, digit
 
 
 @pytest.mark.parametrize("splits", [1, 2, 3, 16])
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 def test_tiled_k_splits(gpu, pkg, tiled_layout, qtype, splits):
     out_dim, in_dim = 700, 4096
     gpu.SetOption("mlx_splits", splits)
@@ -247,7 +250,7 @@ def test_tiled_k_splits(gpu, pkg, tiled_layout, qtype, splits):
         gpu.SetOption("mlx_splits", 0)
 
 
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("batch", [2, 3, 4, 5, 8, 11])
 def test_tiled_batched_projection(gpu, pkg, tiled_layout, qtype, batch):
     out_dim, in_dim = 777, 2048
@@ -303,7 +306,7 @@ def test_tiled_product_while_l2_writes_back(gpu, pkg, qtype):
         t.Free()
 
 
-@pytest.mark.parametrize("qtype", [Q8_0, Q4_K])
+@pytest.mark.parametrize("qtype", [Q8_0, Q4_K, Q5_K, Q6_K])
 @pytest.mark.parametrize("batch", [1, 2])
 @pytest.mark.parametrize("out_dim,in_dim", [(1024, 4096), (300, 256), (2048, 8192), (640, 14336)])
 def test_tiled_fused_and_separate_preparation_agree(gpu, pkg, tiled_layout, qtype, out_dim, in_dim, batch):
@@ -322,7 +325,7 @@ def test_tiled_fused_and_separate_preparation_agree(gpu, pkg, tiled_layout, qtyp
             got.append(read_and_check_canary(out, batch * out_dim))
             out.Free()
     finally:
-        gpu.SetOption("mlx_fuse", 0)
+        gpu.SetOption("mlx_fuse", 1)
     assert pkg.synth.rel_err(got[0], want) <= TOL
     assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
     m.Free(); xo.Free()

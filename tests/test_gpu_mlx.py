@@ -344,7 +344,7 @@ def test_fused_and_separate_preparation_agree(gpu, pkg, out_dim, in_dim, batch, 
             got.append(read_and_check_canary(out, batch * out_dim))
             out.Free()
     finally:
-        gpu.SetOption("mlx_fuse", 0)
+        gpu.SetOption("mlx_fuse", 1)
         gpu.SetOption("mlx_digits", 4)
     assert pkg.synth.rel_err(got[0], want) <= TOL
     assert np.array_equal(got[0].view(np.uint32), got[1].view(np.uint32))
