@@ -380,10 +380,14 @@ def extras(tensor_peak):
     spec.loader.exec_module(mb)
     out = {}
     keep = ("us_per_launch", "GBps", "frac_of_hbm_peak")
+    def one(fmt, o, i):
+        r = mb.run(fmt, o, i, launches=60)
+        return {k: r[k] for k in keep}
+
+    # (Q5_K / Q6_K fractions are on the FILE's bytes per weight; on the device their tensor-core layout is a byte per weight)
     out["llama3_8b_gemv_batch1"] = {
-        fmt: {"%dx%d" % (o, i): {k: mb.run(fmt, o, i, launches=60)[k] for k in keep}
-              for o, i in ((14336, 4096), (4096, 14336), (128256, 4096))}
-        for fmt in ("mlx4", "q4k", "q8_0", "fp8")}
+        fmt: {"%dx%d" % (o, i): one(fmt, o, i) for o, i in ((14336, 4096), (4096, 14336), (128256, 4096))}
+        for fmt in ("mlx4", "q4k", "q5k", "q6k", "q8_0", "fp8")}
     out["llama3_8b_layer_chain_batch1"] = {
         fmt: {k: v for k, v in mb.run_layer_chain(fmt, layers=6, reps=3).items() if k in ("us_per_layer", "GBps", "frac_of_hbm_peak")}
         for fmt in ("q4k", "q8_0")}
