@@ -498,7 +498,9 @@ def run_ours(args):
         t = torch.tensor([worst], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         worst = float(t.cpu()[0])
-        if not worst <= 1e-4:
+        # (the measure divides by max(|whole|, 1e-3 max|whole|): f32 sums taken in another split order differ
+        # by ~1e-6 of the largest output, i.e. up to ~1e-3 here; the bound is the products' tolerance against the oracle)
+        if not worst <= 2e-3:
             raise SystemExit("row-sharded products differ from the whole products: relative difference %.3g" % worst)
         shard_check = {"max_rel_diff_vs_whole_product": float("%.3g" % worst), "products": "layer 0's four and the LM head, on every rank"}
 
