@@ -138,7 +138,7 @@ def test_fp8_tiled_dequant_bit_exact_all_codes(gpu, pkg):
 @pytest.mark.parametrize("batch", [1, 3, 8, 16, 40, 64, 100])
 @pytest.mark.parametrize("out_dim,in_dim,all_codes", [(300, 1024, True), (1024, 512, False)])
 def test_fp8_small_shapes(gpu, pkg, out_dim, in_dim, all_codes, batch, xkind):
-    # every E4M3 code (subnormals, +-448) goes through the converter of the tensor-core kernel
+    # every E4M3 code (subnormals, +-448) goes to the tensor cores
     w = _fp8_bytes(("g", out_dim, in_dim), out_dim, in_dim, all_codes=all_codes)
     _, scale, bias = pkg.synth.fp8_linear(("g", out_dim), out_dim, 16, bias=True)
     gpu.SetOption("fp8_layout", 2)
@@ -159,6 +159,67 @@ def test_fp8_small_shapes(gpu, pkg, out_dim, in_dim, all_codes, batch, xkind):
     want = orc.fp8_batch_gemv(x, batch, w, scale, bias, out_dim, in_dim, avx2=True, nthreads=8)
     assert pkg.synth.rel_err(got, want) <= TOL
     assert gpu.KernelStatus() == 0
+    for t in (lin, xo, out):
+        t.Free()
+
+
+@pytest.mark.parametrize("xkind", ["f32", "bf16"])
+@pytest.mark.parametrize("splits", [1, 2, 3, 7])
+def test_fp8_k_splits(gpu, pkg, splits, xkind):
+    # the K range of a tile shared by several CTAs (partial sums through device scratch, added in split order)
+    out_dim, in_dim, batch = 700, 4096, 5
+    w = _fp8_bytes(("ks", out_dim, in_dim), out_dim, in_dim)
+    _, scale, bias = pkg.synth.fp8_linear(("ks", out_dim), out_dim, 16, bias=True)
+    gpu.SetOption("fp8_layout", 2)
+    gpu.SetOption("mlx_splits", splits)
+    try:
+        lin = gpu.UploadFP8E4M3Linear(w, scale, bias, out_dim, in_dim)
+        x = pkg.synth.activations(("ks", xkind), batch * in_dim, bf16=(xkind == "bf16"))
+        out = out_with_canary(gpu, batch * out_dim)
+        if xkind == "bf16":
+            xo = _bf16_buffer(gpu, x)
+            gpu.GemmFP8E4M3BF16Buffer(out, xo, batch, lin)
+        else:
+            xo = gpu.from_numpy(x)
+            gpu.GemmFP8E4M3Buffer(out, xo, batch, lin)
+        gpu.Sync()
+    finally:
+        gpu.SetOption("fp8_layout", 0)
+        gpu.SetOption("mlx_splits", 0)
+    got = read_and_check_canary(out, batch * out_dim)
+    want = orc.fp8_batch_gemv(x, batch, w, scale, bias, out_dim, in_dim, avx2=True, nthreads=8)
+    assert pkg.synth.rel_err(got, want) <= TOL
+    assert gpu.KernelStatus() == 0
+    for t in (lin, xo, out):
+        t.Free()
+
+
+def test_fp8_activations_of_wide_dynamic_range(gpu, pkg):
+    # the activation pieces are e4m3 values under one power-of-two scale per row: elements 2^30 apart in
+    # one row, an all-zero row and a row of tiny values must all come out at f32 level
+    out_dim, in_dim, batch = 384, 2048, 4
+    w = _fp8_bytes("dyn", out_dim, in_dim)
+    _, scale, _ = pkg.synth.fp8_linear(("dyn", out_dim), out_dim, 16)
+    g = pkg.synth.rng("dyn-x")
+    x = g.standard_normal(batch * in_dim).astype(F).reshape(batch, in_dim)
+    x[0] *= np.exp2(g.integers(-20, 11, in_dim)).astype(F)
+    x[1] = 0
+    x[2] *= F(1e-30)
+    x[3, ::7] *= F(1e6)
+    x = x.reshape(-1)
+    gpu.SetOption("fp8_layout", 2)
+    try:
+        lin = gpu.UploadFP8E4M3Linear(w, scale, None, out_dim, in_dim)
+    finally:
+        gpu.SetOption("fp8_layout", 0)
+    xo, out = gpu.from_numpy(x), out_with_canary(gpu, batch * out_dim)
+    gpu.GemmFP8E4M3Buffer(out, xo, batch, lin)
+    gpu.Sync()
+    got = read_and_check_canary(out, batch * out_dim).reshape(batch, out_dim)
+    want = orc.fp8_batch_gemv(x, batch, w, scale, None, out_dim, in_dim, avx2=True, nthreads=8).reshape(batch, out_dim)
+    for m in range(batch):
+        assert pkg.synth.rel_err(got[m], want[m]) <= TOL, m
+    assert np.all(got[1] == 0)
     for t in (lin, xo, out):
         t.Free()
 
