@@ -415,6 +415,17 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
       // this role takes no part in the stages: on to the item's end
       wk.k = wk.k1 - 1;
       wk.next(a);
+      // the rows' scales and biases are asked for before the wait, not behind it
+      float scs[TT], bis[TT];
+#pragma unroll
+      for (int t = 0; t < TT; ++t) {
+        const int row = (group * TT + t) * kTileRows + r;
+        scs[t] = (t < nt && row < a.out_dim) ? __ldg(a.scale + row) : 0.f;
+        bis[t] = (t < nt && a.bias && row < a.out_dim) ? __ldg(a.bias + row) : 0.f;
+      }
+      float xi[HM];  // 2^-e of this warp's activation rows
+#pragma unroll
+      for (int j = 0; j < HM; ++j) xi[j] = __ldg(a.xinv + hf * HM + j);
       ok = __all_sync(0xffffffffu, mbar_wait(dfull0 + 8 * b, (it / ND) & 1, a.status, 504));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -448,13 +459,12 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
         if (t >= nt) break;
         const int tile = group * TT + t;
         const int row = tile * kTileRows + r;
-        const float sc = row < a.out_dim ? __ldg(a.scale + row) : 0.f;
-        const float bi = (a.bias && row < a.out_dim) ? __ldg(a.bias + row) : 0.f;
+        const float sc = scs[t], bi = bis[t];
         if (a.splits == 1) {
 #pragma unroll
           for (int j = 0; j < HM; ++j) {
             const int m = hf * HM + j;
-            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(dot[t][j] * __ldg(a.xinv + m), sc, bi);
+            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(dot[t][j] * xi[j], sc, bi);
           }
         } else {
           // Partial sums of this K range go to scratch; the CTA that arrives last at the tile adds the
@@ -479,7 +489,7 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
 #pragma unroll
             for (int j = 0; j < HM; ++j) {
               const int m = hf * HM + j;
-              if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(sum[j] * __ldg(a.xinv + m), sc, bi);
+              if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(sum[j] * xi[j], sc, bi);
             }
             if (et == 0) a.counters[tile] = 0;
           }
