@@ -66,6 +66,7 @@ constexpr size_t kScratchFloats = (size_t)kMaxItems * 64 * kTileRows;
 constexpr size_t kMaxCounters = 4096;
 constexpr size_t kSmemBudget = 222 * 1024;
 constexpr int kPrepSlice = 4096;                      // elements of a row one preparation CTA converts
+constexpr int kRecvBytes = 16 * 1024;                 // cluster launches: partial sums the first CTA of a cluster can receive
 
 struct Fp8Args {
   const unsigned char* w;   // tiled weight blocks [tile][chunk]
@@ -79,6 +80,9 @@ struct Fp8Args {
   unsigned int* counters;   // per-tile arrival counters, zero between launches
   int out_dim, in_dim, batch;
   int ntiles, nks, splits, items, stages;  // nks: stages along K (in_dim / KS); items = row-tile groups x splits
+  // 1: the K splits of a group are the CTAs of a thread-block cluster (every CTA has one item) and
+  // their partial sums go through the first CTA's shared memory instead of device scratch
+  int cluster;
 };
 
 struct ItemWalk {
@@ -289,10 +293,12 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)S * kStage);
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * ND);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * ND + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* recv = reinterpret_cast<float*>(tmem_holder + 4);  // cluster launches: [split - 1][tile of the group][row m][128]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * S, dfull0 = empty0 + 8 * S, dfree0 = dfull0 + 8 * ND;
+  const uint32_t clbar = dfree0 + 8 * ND;  // cluster launches: the other CTAs' partial sums have arrived (one arrival per epilogue warp)
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -303,6 +309,7 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
       mbar_init(dfull0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiWarps);
     }
+    if (a.cluster) mbar_init(clbar, kEpiWarps * (a.splits - 1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -313,6 +320,7 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (a.cluster) cluster_sync_all();  // the first CTA's barrier is initialised before any peer can arrive on it
   const uint32_t tmem_base = *tmem_holder;
   bool ok = true;
   ItemWalk wk(a);
@@ -454,6 +462,42 @@ fp8_mma_kernel(const __grid_constant__ Fp8Args a) {
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(dfree0 + 8 * b);
+      if (a.cluster) {
+        // The K splits of this group are the CTAs of this cluster (rank == split), one item each.
+        // Ranks above 0 put their sums into rank 0's shared memory and arrive on its barrier (one
+        // releasing arrival per warp); rank 0 waits, adds in split order — the order of the scratch
+        // path, so the same bits — and stores.
+        if (split != 0) {
+#pragma unroll
+          for (int t = 0; t < TT; ++t) {
+            if (t < nt) {
+#pragma unroll
+              for (int j = 0; j < HM; ++j)
+                cluster_store_f32(cluster_map(smem_u32(recv + ((size_t)((split - 1) * TT + t) * MP + hf * HM + j) * kTileRows + r), 0), dot[t][j]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) cluster_arrive_release(cluster_map(clbar, 0));
+        } else {
+          ok = __all_sync(0xffffffffu, mbar_wait_cluster(clbar, 0, a.status, 505));
+          if (ok) {
+#pragma unroll
+            for (int t = 0; t < TT; ++t) {
+              if (t < nt) {
+                const int row = (group * TT + t) * kTileRows + r;
+#pragma unroll
+                for (int j = 0; j < HM; ++j) {
+                  const int m = hf * HM + j;
+                  float sum = dot[t][j];
+                  for (int s2 = 1; s2 < a.splits; ++s2) sum += recv[((size_t)((s2 - 1) * TT + t) * MP + m) * kTileRows + r];
+                  if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = fmaf(sum * xi[j], scs[t], bis[t]);
+                }
+              }
+            }
+          }
+        }
+        continue;
+      }
 #pragma unroll
       for (int t = 0; t < TT; ++t) {
         if (t >= nt) break;
@@ -586,19 +630,24 @@ int launch_pass(const goph_fp8_linear* w, float* out, const void* x, int nb, Fp8
                                       : tc_choose_splits(ngroups, a.nks, st.sm_count, max_items / TT, 2.f + TT * MP / 16.f);
   while (a.splits > 1 && (long)a.ntiles * a.splits > max_items) --a.splits;
   a.items = ngroups * a.splits;
-  int stages = (int)((kSmemBudget - 2048) / kStage);
+  const int grid = a.items < st.sm_count ? a.items : st.sm_count;
+  // K splits that all run at once, one item per CTA, whose partial sums fit the receive area: a cluster per group
+  const bool want_cluster = options().mlx_cluster && a.splits > 1 && a.splits <= 8 && a.items == grid &&
+                            (size_t)(a.splits - 1) * TT * MP * kTileRows * 4 <= (size_t)kRecvBytes;
+  const size_t extra = 2048 + (want_cluster ? kRecvBytes : 0);
+  int stages = (int)((kSmemBudget - extra) / kStage);
   if (stages > kMaxStages) stages = kMaxStages;
   a.stages = stages;
-  size_t smem = (size_t)stages * kStage + 2048;
+  size_t smem = (size_t)stages * kStage + extra;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM (the kernel owns all of TMEM)
 
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.stream = stream;
-  cfg.attrs = &attr;
+  cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(MP, (w->in_dim + kPrepSlice - 1) / kPrepSlice);
   cfg.blockDim = dim3(256);
@@ -606,9 +655,36 @@ int launch_pass(const goph_fp8_linear* w, float* out, const void* x, int nb, Fp8
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, fp8_prep_x_kernel<P, XBF16>, x, bufs->xb, bufs->xinv, nb, w->in_dim, N, MP));
   auto kern = fp8_mma_kernel<N, P, MP, KS, TT>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
+  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
+  if (want_cluster) {
+    // only when the device holds every cluster of the grid at once (asked once per kernel, split count and device)
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = a.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    static std::mutex mu;
+    static int room[kMaxDevices][9];
+    static bool known[kMaxDevices][9] = {};
+    int resident;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (!known[w->device][a.splits]) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+          cudaGetLastError();
+          n = 0;
+        }
+        room[w->device][a.splits] = n;
+        known[w->device][a.splits] = true;
+      }
+      resident = room[w->device][a.splits];
+    }
+    if (resident * a.splits >= grid) a.cluster = 1;
+    else cfg.numAttrs = 1;
+  }
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
