@@ -102,6 +102,7 @@ struct GemmArgs {
   unsigned int* counters;    // per-tile arrival counters, zero between launches
   int out_dim, in_dim, batch;
   int ntiles, nchunks, splits, items, stages;
+  int cluster;               // 1: the K splits of a tile are the CTAs of a thread-block cluster (one item each); partial sums through the first CTA's shared memory
   int rotate;                // 1: every tile starts its K range at a different chunk (see StageWalk::chunk)
   int dbg;                   // tuning build only: parts of the kernel left out (results are then wrong)
 };
@@ -264,14 +265,16 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   unsigned char* ring = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const int S = a.stages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)S * kStage);
-  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND);
+  // bars: full[S], empty[S], a_ready[NA], a_free[NA], d_full[ND], d_free[ND], cluster
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * NA + 2 * ND + 1);
   volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* recv = reinterpret_cast<float*>(tmem_holder + 4);  // cluster launches: [split - 1][column m][128] partial sums from the other CTAs
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + S);
   const uint32_t aready0 = smem_u32(bars + 2 * S), afree0 = aready0 + 8 * NA;
   const uint32_t dfull0 = afree0 + 8 * NA, dfree0 = dfull0 + 8 * ND;
+  const uint32_t clbar = dfree0 + 8 * ND;
 
   if (tid == 0) {
     for (int s = 0; s < S; ++s) {
@@ -287,6 +290,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
       mbar_init(dfull0 + 8 * b, 1);
       mbar_init(dfree0 + 8 * b, kEpiWarps);
     }
+    if (a.cluster) mbar_init(clbar, kEpiWarps * (a.splits - 1));
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kWarpMMA) {
@@ -298,6 +302,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (a.cluster) cluster_sync_all();  // the first CTA's barrier is initialised before any peer can arrive on it
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * 128;
   bool ok = true;
@@ -561,7 +566,40 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         if (a.bias) rb = a.bias[row];
       }
       auto finish = [&](float v) { return kMLX ? v : (a.bias ? __fadd_rn(__fmul_rn(v, rs), rb) : __fmul_rn(v, rs)); };
-      if (a.splits == 1) {
+      if (a.cluster) {
+        // The K splits of this tile are the CTAs of this cluster (rank == split), one item each: ranks
+        // above 0 put their sums into rank 0's shared memory and arrive on its barrier (one releasing
+        // arrival per warp); rank 0 waits, adds in split order (the scratch path's order) and stores.
+        if (split != 0) {
+#pragma unroll
+          for (int j = 0; j < HC / 2; ++j) {
+            const int m = cq * HC + 2 * j;
+            cluster_store_f32(cluster_map(smem_u32(recv + ((size_t)(split - 1) * NC + m) * kTileRows + r), 0), acc[j].x);
+            cluster_store_f32(cluster_map(smem_u32(recv + ((size_t)(split - 1) * NC + m + 1) * kTileRows + r), 0), acc[j].y);
+          }
+          __syncwarp();
+          if (lane == 0) cluster_arrive_release(cluster_map(clbar, 0));
+        } else {
+          ok = __all_sync(0xffffffffu, mbar_wait_cluster(clbar, 0, a.status, 310));
+          if (ok) {
+#pragma unroll
+            for (int j = 0; j < HC / 2; ++j) {
+              const int m = cq * HC + 2 * j;
+              float s0 = acc[j].x, s1 = acc[j].y;
+              for (int s2 = 1; s2 < a.splits; ++s2) {
+                s0 += recv[((size_t)(s2 - 1) * NC + m) * kTileRows + r];
+                s1 += recv[((size_t)(s2 - 1) * NC + m + 1) * kTileRows + r];
+              }
+              if (row < a.out_dim) {
+                if (m < a.batch) a.out[(size_t)m * a.out_dim + row] = finish(s0);
+                if (m + 1 < a.batch) a.out[(size_t)(m + 1) * a.out_dim + row] = finish(s1);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < HC / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+      } else if (a.splits == 1) {
 #pragma unroll
         for (int j = 0; j < HC / 2; ++j) {
           const int m = cq * HC + 2 * j;
@@ -734,22 +772,27 @@ int launch_pass(const GemmDesc& w, float* out, const void* x, int nb, GemmBufs* 
                                       : tc_choose_splits(a.ntiles, a.nchunks, st.sm_count, max_items, NC / 32.f);
   while (a.splits > 1 && (long)a.ntiles * a.splits > max_items) --a.splits;
   a.items = a.ntiles * a.splits;
-  int stages = (int)((kSmemBudget2 - SM::bytes(0)) / SM::kStage);
+  const int grid = a.items < st.sm_count ? a.items : st.sm_count;
+  constexpr size_t kRecvBytes = 16 * 1024;
+  const bool want_cluster = options().mlx_cluster && a.splits > 1 && a.splits <= 8 && a.items == grid &&
+                            (size_t)(a.splits - 1) * NC * kTileRows * 4 <= kRecvBytes;
+  const size_t extra = want_cluster ? kRecvBytes : 0;
+  int stages = (int)((kSmemBudget2 - SM::bytes(0) - extra) / SM::kStage);
   if (stages > 8) stages = 8;
   if (stages < 2) return fail(GOPH_E_UNSUPPORTED, "small-batch tensor-core path: a stage of %d bytes leaves no room for a ring", SM::kStage);
   a.stages = stages;
   a.rotate = g_rotate;
   a.dbg = g_dbg;
-  size_t smem = SM::bytes(stages);
+  size_t smem = SM::bytes(stages) + extra;
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM (the kernel owns all of TMEM)
 
-  cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr.val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
   cfg.stream = stream;
-  cfg.attrs = &attr;
+  cfg.attrs = attr;
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(a.nchunks, NC / 8);
   cfg.blockDim = dim3(256);
@@ -757,9 +800,36 @@ int launch_pass(const GemmDesc& w, float* out, const void* x, int nb, GemmBufs* 
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, tc_prep_x_kernel<NC, P, FMT, XBF16>, x, bufs->xb, bufs->xtab, nb, w.in_dim));
   auto kern = tc_gemm_kernel<NC, P, FMT>;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
+  cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = smem;
+  if (want_cluster) {
+    // only when the device holds every cluster of the grid at once (asked once per kernel, split count and device)
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = a.splits;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    static std::mutex mu;
+    static int room[kMaxDevices][9];
+    static bool known[kMaxDevices][9] = {};
+    int resident;
+    {
+      std::lock_guard<std::mutex> lock(mu);
+      if (!known[w.device][a.splits]) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+          cudaGetLastError();
+          n = 0;
+        }
+        room[w.device][a.splits] = n;
+        known[w.device][a.splits] = true;
+      }
+      resident = room[w.device][a.splits];
+    }
+    if (resident * a.splits >= grid) a.cluster = 1;
+    else cfg.numAttrs = 1;
+  }
   note_launch();
   GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
   return GOPH_OK;
