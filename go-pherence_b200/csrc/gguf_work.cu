@@ -1,0 +1,272 @@
+// GGUF products addressed by a work list, for MoE layers whose experts are stacked in one matrix:
+//   * gate/up with the activation fused: out[w][i] = gelu_tanh(gate_i . x_w) * (up_i . x_w), the
+//     rows of expert work_experts[w] (nvidia.GateUpGELUQ4KBatchToBuffer / GateUpGELUQ4KByWorkToBuffer,
+//     backends/nvidia/runtime/q4k.go:322-352; kernel text backends/nvidia/ptx/q4/gate_up_gelu_q4k*.go);
+//   * down projection with a weighted scatter-add: dst[pos[w]][r] += weight[w] * (W_e[r] . x_w)
+//     (nvidia.GemvQ8_0BatchScatter / GemvQ8_0ScatterByWork, backends/nvidia/runtime/q8.go:193-222;
+//     kernel text backends/nvidia/ptx/q8/q8_scatter*.go).
+// Both for Q4_K and Q8_0 matrices in either device layout (the reference has the first for Q4_K and
+// the second for Q8_0 only).  CUDA-core kernels: one warp per (output row, work item), a lane takes
+// 32-element units of the row; the weights of an item's expert are read once per item.  The indices
+// of a work list live in device memory, so the kernels check them: an expert index outside the
+// matrix or a destination outside dst is skipped and recorded in the status word (601 / 602).
+#include <string.h>
+
+#include <mutex>
+
+#include "goph_internal.cuh"
+
+namespace goph {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kQ4KStage = 128 * 128 + 128 * 16;   // tensor-core layout: nibbles + headers of a stage
+constexpr int kQ80Stage = 128 * 256 + 128 * 16;   // bytes + f16 scales
+
+struct WorkView {
+  const uint8_t* data;
+  const uint16_t* d16;
+  const uint8_t* tiled;
+  int qtype, in_dim, out_dim, nchunks;
+};
+
+__device__ __forceinline__ float f16f(uint32_t h) { return __half2float(__ushort_as_half((unsigned short)(h & 0xFFFFu))); }
+
+// sum over the 32 elements of `unit` of row `row` of w_e * x_e, with the roundings of the
+// dequantisation (sc*d and m*dmin, d*q) and f32 accumulation
+__device__ __forceinline__ float unit_dot(const WorkView& v, int row, int unit, const float* __restrict__ x) {
+  const float4* xp = reinterpret_cast<const float4*>(x + (size_t)unit * 32);
+  float xs[32];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float4 t = __ldg(xp + k);
+    xs[4 * k] = t.x; xs[4 * k + 1] = t.y; xs[4 * k + 2] = t.z; xs[4 * k + 3] = t.w;
+  }
+  const int chunk = unit >> 3, s = unit & 7, r = row & 127;
+  if (v.qtype == GOPH_GGUF_Q4_K) {
+    uint4 h, q;
+    if (v.tiled) {
+      const uint8_t* stg = v.tiled + ((size_t)(row >> 7) * v.nchunks + chunk) * kQ4KStage;
+      h = *reinterpret_cast<const uint4*>(stg + 128 * 128 + r * 16);
+      q = *reinterpret_cast<const uint4*>(stg + r * 128 + ((s ^ (r & 7)) << 4));
+    } else {
+      const uint8_t* blk = v.data + ((size_t)row * v.nchunks + chunk) * 144;
+      h = *reinterpret_cast<const uint4*>(blk);
+      q = *reinterpret_cast<const uint4*>(blk + 16 + 16 * s);
+    }
+    const int bit = 12 * s, wi = bit >> 5, sh = bit & 31;
+    const uint32_t lo = wi == 0 ? h.y : wi == 1 ? h.z : h.w, hi = wi == 0 ? h.z : wi == 1 ? h.w : 0u;
+    const uint32_t f = __funnelshift_r(lo, hi, sh) & 0xFFFu;
+    const float sd = __fmul_rn((float)(f & 63u), f16f(h.x)), md = __fmul_rn((float)(f >> 6), f16f(h.x >> 16));
+    const uint32_t ws[4] = {q.x, q.y, q.z, q.w};
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc = fmaf(__fsub_rn(__fmul_rn(sd, (float)((ws[k] >> (4 * e)) & 0xFu)), md), xs[8 * k + e], acc);
+    }
+    return acc;
+  }
+  // Q8_0
+  float d;
+  uint4 b[2];
+  bool biased;
+  if (v.tiled) {
+    const uint8_t* stg = v.tiled + ((size_t)(row >> 7) * v.nchunks + chunk) * kQ80Stage;
+    const uint8_t* p = stg + s * 4096 + (r >> 3) * 128 + (r & 7) * 16;
+    b[0] = *reinterpret_cast<const uint4*>(p);
+    b[1] = *reinterpret_cast<const uint4*>(p + 2048);
+    d = f16f(*reinterpret_cast<const uint16_t*>(stg + 128 * 256 + r * 16 + s * 2));
+    biased = false;  // signed bytes
+  } else {
+    const uint8_t* p = v.data + (size_t)row * v.in_dim + (size_t)unit * 32;
+    b[0] = *reinterpret_cast<const uint4*>(p);
+    b[1] = *reinterpret_cast<const uint4*>(p + 16);
+    d = f16f(v.d16[(size_t)row * (v.in_dim / 32) + unit]);
+    biased = true;  // q + 128
+  }
+  float acc = 0.f;
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const uint32_t ws[4] = {b[hh].x, b[hh].y, b[hh].z, b[hh].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int byte = (int)((ws[k] >> (8 * e)) & 0xFFu);
+        const int q = biased ? byte - 128 : (int)(signed char)byte;
+        acc = fmaf(__fmul_rn(d, (float)q), xs[16 * hh + 4 * k + e], acc);
+      }
+    }
+  }
+  return acc;
+}
+
+__device__ __forceinline__ float row_dot(const WorkView& v, int row, const float* __restrict__ x, int lane) {
+  float acc = 0.f;
+  for (int unit = lane; unit < v.in_dim / 32; unit += 32) acc += unit_dot(v, row, unit, x);
+  return warp_sum(acc);
+}
+
+// GELU in the tanh form of the reference kernel: 0.5 g (1 + tanh(0.79788456 (g + 0.044715 g^3)))
+__device__ __forceinline__ float gelu_tanh(float g) {
+  const float u = 0.7978845608f * fmaf(0.044715f, g * g * g, g);
+  const float t = 2.f / (1.f + __expf(-2.f * u)) - 1.f;
+  return 0.5f * g * (1.f + t);
+}
+
+// grid (row blocks, items); a warp per (intermediate row i, item w)
+__global__ void __launch_bounds__(kWarps * 32)
+gate_up_gelu_kernel(WorkView v, const float* __restrict__ x, const uint32_t* __restrict__ work_experts, int active_experts,
+                    int inter, float* __restrict__ out, int* __restrict__ status) {
+  const int lane = threadIdx.x & 31, i = blockIdx.x * kWarps + (threadIdx.x >> 5), w = blockIdx.y;
+  if (i >= inter) return;
+  const uint32_t e = work_experts ? work_experts[w] : 0u;
+  if (e >= (uint32_t)active_experts) {
+    if (lane == 0) atomicCAS(status, 0, 601);
+    return;
+  }
+  const float* xw = x + (size_t)w * v.in_dim;
+  const int gate_row = (int)e * 2 * inter + i;
+  const float g = row_dot(v, gate_row, xw, lane), u = row_dot(v, gate_row + inter, xw, lane);
+  if (lane == 0) out[(size_t)w * inter + i] = gelu_tanh(g) * u;
+}
+
+// grid (row blocks, items); a warp per (expert row r, item w): dst[pos][r] += weight * (W_e[r] . x_w)
+__global__ void __launch_bounds__(kWarps * 32)
+scatter_by_work_kernel(WorkView v, const float* __restrict__ x, const uint32_t* __restrict__ work_active,
+                       const uint32_t* __restrict__ work_pos, const float* __restrict__ work_weight, int active_experts,
+                       int expert_out, float* __restrict__ dst, unsigned long long dst_len, int* __restrict__ status) {
+  const int lane = threadIdx.x & 31, r = blockIdx.x * kWarps + (threadIdx.x >> 5), w = blockIdx.y;
+  if (r >= expert_out) return;
+  const uint32_t e = work_active ? work_active[w] : 0u;
+  const unsigned long long at = (unsigned long long)work_pos[w] * (unsigned long long)expert_out + (unsigned long long)r;
+  if (e >= (uint32_t)active_experts || at >= dst_len) {
+    if (lane == 0) atomicCAS(status, 0, e >= (uint32_t)active_experts ? 601 : 602);
+    return;
+  }
+  const float y = row_dot(v, (int)e * expert_out + r, x + (size_t)w * v.in_dim, lane);
+  if (lane == 0) atomicAdd(dst + at, y * work_weight[w]);  // items may share a destination row
+}
+
+int* work_status(int device) {
+  static int* words[kMaxDevices] = {};
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[device]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess || cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+      cudaFree(p);
+      cudaGetLastError();
+      return nullptr;
+    }
+    words[device] = p;
+  }
+  return words[device];
+}
+
+bool valid_work_matrix(const goph_gguf_matrix* m) {
+  return m && m->magic == kMagicGGUF && (m->qtype == GOPH_GGUF_Q4_K || m->qtype == GOPH_GGUF_Q8_0) && m->in_dim > 0 &&
+         m->in_dim % 32 == 0 && m->out_dim > 0 && (m->tiled || m->data);
+}
+
+WorkView view_of(const goph_gguf_matrix* m) {
+  WorkView v;
+  v.data = m->data;
+  v.d16 = m->d16;
+  v.tiled = m->tiled;
+  v.qtype = m->qtype;
+  v.in_dim = m->in_dim;
+  v.out_dim = m->out_dim;
+  v.nchunks = m->in_dim / 256;
+  return v;
+}
+
+}  // namespace
+
+int gguf_work_status(int device) {
+  int* p = work_status(device);
+  if (!p) return 0;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return v;
+}
+
+void gguf_work_status_clear(int device) {
+  int* p = work_status(device);
+  if (p) cudaMemset(p, 0, sizeof(int));
+}
+
+}  // namespace goph
+
+using namespace goph;
+
+GOPH_API int goph_gguf_gate_up_gelu_by_work(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                                            const uint32_t* work_experts_dev, int work_len, int intermediate, int active_experts,
+                                            const goph_gguf_matrix* m, void* stream) {
+  clear_error();
+  if (work_len <= 0) return GOPH_OK;  // as the reference: nothing to do
+  if (!valid_work_matrix(m)) return fail(GOPH_E_INVALID, "gate/up by work: a Q4_K or Q8_0 matrix handle is required");
+  uint64_t need_x, need_o, need_rows;
+  if (intermediate <= 0 || active_experts <= 0 || !mul_ok((uint64_t)work_len, (uint64_t)m->in_dim, &need_x) ||
+      !mul_ok((uint64_t)work_len, (uint64_t)intermediate, &need_o) ||
+      !mul_ok((uint64_t)active_experts, 2ull * (uint64_t)intermediate, &need_rows) || (uint64_t)m->out_dim < need_rows)
+    return fail(GOPH_E_INVALID, "gate/up by work: intermediate=%d experts=%d against %d rows", intermediate, active_experts, m->out_dim);
+  if (!x_dev || x_len < need_x || !out_dev || out_len < need_o || (active_experts > 1 && !work_experts_dev))
+    return fail(GOPH_E_INVALID, "gate/up by work buffers x=%llu/%llu out=%llu/%llu", (unsigned long long)x_len,
+                (unsigned long long)need_x, (unsigned long long)out_len, (unsigned long long)need_o);
+  if ((uintptr_t)x_dev % 16) return fail(GOPH_E_INVALID, "x must be 16-byte aligned");
+  if (int rc = use_device(m->device)) return rc;
+  int* status = work_status(m->device);
+  if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the work-list kernels' status word");
+  note_launch();
+  gate_up_gelu_kernel<<<dim3((intermediate + kWarps - 1) / kWarps, work_len), kWarps * 32, 0, (cudaStream_t)stream>>>(
+      view_of(m), x_dev, work_experts_dev, active_experts, intermediate, out_dev, status);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+GOPH_API int goph_gguf_gate_up_gelu(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
+                                    int intermediate, const goph_gguf_matrix* m, void* stream) {
+  if (m && m->magic == kMagicGGUF && intermediate > 0 && m->out_dim != 2 * intermediate) {
+    clear_error();
+    return fail(GOPH_E_INVALID, "gate/up: the matrix has %d rows, not 2 x %d", m->out_dim, intermediate);
+  }
+  return goph_gguf_gate_up_gelu_by_work(out_dev, out_len, x_dev, x_len, nullptr, batch, intermediate, 1, m, stream);
+}
+
+GOPH_API int goph_gguf_scatter_by_work(float* dst_dev, uint64_t dst_len, const float* x_dev, uint64_t x_len,
+                                       const uint32_t* work_active_dev, const uint32_t* work_pos_dev,
+                                       const float* work_weight_dev, int work_len, int active_experts,
+                                       const goph_gguf_matrix* m, void* stream) {
+  clear_error();
+  if (work_len <= 0) return GOPH_OK;
+  if (!valid_work_matrix(m)) return fail(GOPH_E_INVALID, "scatter by work: a Q4_K or Q8_0 matrix handle is required");
+  uint64_t need_x;
+  if (active_experts <= 0 || m->out_dim % active_experts != 0 || !mul_ok((uint64_t)work_len, (uint64_t)m->in_dim, &need_x))
+    return fail(GOPH_E_INVALID, "scatter by work: %d rows do not divide into %d experts", m->out_dim, active_experts);
+  if (!x_dev || x_len < need_x || !dst_dev || dst_len == 0 || !work_pos_dev || !work_weight_dev ||
+      (active_experts > 1 && !work_active_dev))
+    return fail(GOPH_E_INVALID, "scatter by work buffers x=%llu/%llu", (unsigned long long)x_len, (unsigned long long)need_x);
+  if ((uintptr_t)x_dev % 16) return fail(GOPH_E_INVALID, "x must be 16-byte aligned");
+  if (int rc = use_device(m->device)) return rc;
+  int* status = work_status(m->device);
+  if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the work-list kernels' status word");
+  const int expert_out = m->out_dim / active_experts;
+  note_launch();
+  scatter_by_work_kernel<<<dim3((expert_out + kWarps - 1) / kWarps, work_len), kWarps * 32, 0, (cudaStream_t)stream>>>(
+      view_of(m), x_dev, work_active_dev, work_pos_dev, work_weight_dev, active_experts, expert_out, dst_dev,
+      (unsigned long long)dst_len, status);
+  GOPH_CUDA(cudaGetLastError());
+  return GOPH_OK;
+}
+
+GOPH_API int goph_gguf_project_scatter(float* dst_dev, uint64_t dst_len, const float* x_dev, uint64_t x_len,
+                                       const uint32_t* pos_dev, const float* weight_dev, int batch, const goph_gguf_matrix* m,
+                                       void* stream) {
+  return goph_gguf_scatter_by_work(dst_dev, dst_len, x_dev, x_len, nullptr, pos_dev, weight_dev, batch, 1, m, stream);
+}

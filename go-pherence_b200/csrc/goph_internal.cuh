@@ -74,6 +74,11 @@ void note_launch();
 int decode_ops_status();
 void decode_ops_status_clear();
 
+// Status word of the work-list kernels of gguf_work.cu (0, 601: an expert index outside the matrix,
+// 602: a destination outside dst).
+int gguf_work_status(int device);
+void gguf_work_status_clear(int device);
+
 // Largest dynamic shared-memory request the GEMV kernels make.
 constexpr int kSmemBudget = 200 * 1024;
 

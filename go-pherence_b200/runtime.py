@@ -33,6 +33,7 @@ EXPORTS = [
     "goph_mlx_gemm_host",
     "goph_gguf_upload", "goph_gguf_free", "goph_gguf_resident_bytes", "goph_gguf_dequant",
     "goph_gguf_project", "goph_gguf_project_pair", "goph_gguf_project_host",
+    "goph_gguf_gate_up_gelu", "goph_gguf_gate_up_gelu_by_work", "goph_gguf_project_scatter", "goph_gguf_scatter_by_work",
     "goph_fp8_upload", "goph_fp8_free", "goph_fp8_resident_bytes", "goph_fp8_dequant", "goph_fp8_gemm", "goph_fp8_gemm_bf16",
     "goph_fp8_gemm_host",
     "goph_moe_create", "goph_moe_set_router", "goph_moe_set_expert", "goph_moe_free", "goph_moe_forward",
@@ -435,6 +436,32 @@ def UploadQ6KMatrixRows(raw, inDim, outDim):
 def _want_qtype(m, qtype, name):
     if not isinstance(m, GPUGGUFMatrix) or not m._h or m.QType != qtype:
         raise GophError(1, "invalid %s matrix" % name)
+
+
+def GateUpGELUQ4KBatchToBuffer(out, x, batch, intermediate, m, stream=None):
+    """nvidia.GateUpGELUQ4KBatchToBuffer (runtime/q4k.go:338-352)."""
+    _check(lib().goph_gguf_gate_up_gelu(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n), int(batch),
+                                        int(intermediate), m._h, _stream_ptr(stream)))
+
+
+def GateUpGELUQ4KByWorkToBuffer(out, x, workExperts, workLen, intermediate, activeExperts, m, stream=None):
+    """nvidia.GateUpGELUQ4KByWorkToBuffer (runtime/q4k.go:322-336); workExperts: device buffer of uint32."""
+    _check(lib().goph_gguf_gate_up_gelu_by_work(C.c_void_p(out.Ptr), C.c_uint64(out.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                                                C.c_void_p(workExperts.Ptr), int(workLen), int(intermediate),
+                                                int(activeExperts), m._h, _stream_ptr(stream)))
+
+
+def GemvQ8_0BatchScatter(dst, x, pos, weight, batch, m, stream=None):
+    """nvidia.GemvQ8_0BatchScatter (runtime/q8.go:209-222); pos: device buffer of uint32, weight: of float32."""
+    _check(lib().goph_gguf_project_scatter(C.c_void_p(dst.Ptr), C.c_uint64(dst.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                                           C.c_void_p(pos.Ptr), C.c_void_p(weight.Ptr), int(batch), m._h, _stream_ptr(stream)))
+
+
+def GemvQ8_0ScatterByWork(dst, x, workActive, workPos, workWeight, workLen, activeExperts, m, stream=None):
+    """nvidia.GemvQ8_0ScatterByWork (runtime/q8.go:193-207)."""
+    _check(lib().goph_gguf_scatter_by_work(C.c_void_p(dst.Ptr), C.c_uint64(dst.n), C.c_void_p(x.Ptr), C.c_uint64(x.n),
+                                           C.c_void_p(workActive.Ptr), C.c_void_p(workPos.Ptr), C.c_void_p(workWeight.Ptr),
+                                           int(workLen), int(activeExperts), m._h, _stream_ptr(stream)))
 
 
 def GemvQ5KBatch(x, batch, m):

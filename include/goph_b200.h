@@ -234,6 +234,32 @@ int goph_gguf_dequant(const goph_gguf_matrix* m, float* out_dev, uint64_t out_le
 int goph_gguf_project_pair(float* out_a_dev, uint64_t out_a_len, float* out_b_dev, uint64_t out_b_len,
                            const float* x_dev, uint64_t x_len, int batch, const goph_gguf_matrix* a,
                            const goph_gguf_matrix* b, void* stream);
+/* nvidia.GateUpGELUQ4KBatchToBuffer (runtime/q4k.go:338-352): m holds the gate rows [0, intermediate) and
+ * the up rows [intermediate, 2 intermediate); out[b][i] = gelu(gate_i . x_b) * (up_i . x_b) with the tanh
+ * form of GELU the reference kernel uses (ptx/q4/gate_up_gelu_q4k.go:157-176).  Q4_K or Q8_0, either layout. */
+int goph_gguf_gate_up_gelu(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len, int batch,
+                           int intermediate, const goph_gguf_matrix* m, void* stream);
+/* nvidia.GateUpGELUQ4KByWorkToBuffer (runtime/q4k.go:322-336): m stacks active_experts slabs of
+ * 2 x intermediate rows (gate rows, then up rows); work item w multiplies x[w] by the slab of expert
+ * work_experts_dev[w] (u32, device memory).  An index >= active_experts is skipped and sets the kernel
+ * status word to 601.  (The pointer-table form, GateUpGELUQ4KByWorkPtrsToBuffer, takes separate
+ * matrices; stack them at upload to use this call.) */
+int goph_gguf_gate_up_gelu_by_work(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
+                                   const uint32_t* work_experts_dev, int work_len, int intermediate, int active_experts,
+                                   const goph_gguf_matrix* m, void* stream);
+/* nvidia.GemvQ8_0BatchScatter (runtime/q8.go:209-222): dst[pos[b]][r] += weight[b] * (W[r] . x_b), dst of
+ * rows of out_dim floats.  Additions are atomic (rows of dst may be shared between items); a destination
+ * past dst_len is skipped and sets the kernel status word to 602. */
+int goph_gguf_project_scatter(float* dst_dev, uint64_t dst_len, const float* x_dev, uint64_t x_len,
+                              const uint32_t* pos_dev, const float* weight_dev, int batch, const goph_gguf_matrix* m,
+                              void* stream);
+/* nvidia.GemvQ8_0ScatterByWork (runtime/q8.go:193-207): m stacks active_experts slabs of
+ * out_dim / active_experts rows; item w: dst[work_pos[w]][r] += work_weight[w] * (W_e[r] . x_w) with
+ * e = work_active[w].  Q8_0 or Q4_K, either layout. */
+int goph_gguf_scatter_by_work(float* dst_dev, uint64_t dst_len, const float* x_dev, uint64_t x_len,
+                              const uint32_t* work_active_dev, const uint32_t* work_pos_dev,
+                              const float* work_weight_dev, int work_len, int active_experts,
+                              const goph_gguf_matrix* m, void* stream);
 /* GPUGGUFMatrix.ProjectBatchToBuffer / GemvQ4KBatchToBuffer / GemvQ8_0BatchToBuffer
  * (runtime/gguf_matrix.go:121-135, q4k.go:351, q8.go:225): x [batch,in] f32 → out [batch,out]. */
 int goph_gguf_project(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
