@@ -24,6 +24,12 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <pthread.h>
+
+#include <condition_variable>
+#include <functional>
+#include <mutex>
+#include <new>
 #include <thread>
 #include <vector>
 #include <algorithm>
@@ -38,6 +44,61 @@ namespace {
 // computed by the same scalar code whichever worker owns it, so the split
 // changes timing only, never bits.
 // ---------------------------------------------------------------------------
+// Worker threads that live as long as the process: a GEMV of a few MB takes tens of microseconds per
+// thread, less than starting the threads costs, so starting them per call (as a first version did)
+// made the timed baseline slower on hosts with more cores.  One parallel region runs at a time.
+class Pool {
+ public:
+  static Pool& get() {
+    static Pool* p = make();  // never destroyed: the workers are detached and may outlive static destructors
+    return *p;
+  }
+  // job(w) for w in [0, n): w = 0 on the calling thread, the rest on the workers
+  void run(int n, const std::function<void(int)>& job) {
+    std::lock_guard<std::mutex> region(region_mu_);
+    {
+      std::lock_guard<std::mutex> l(mu_);
+      while (workers_ < n - 1) {
+        std::thread([this] { work(); }).detach();
+        ++workers_;
+      }
+      job_ = &job;
+      next_ = 1;
+      total_ = n;
+      pending_ = n - 1;
+    }
+    cv_.notify_all();
+    job(0);
+    std::unique_lock<std::mutex> l(mu_);
+    done_.wait(l, [&] { return pending_ == 0; });
+    job_ = nullptr;
+  }
+
+ private:
+  static Pool* make() {
+    Pool* p = new Pool;
+    // a forked child has none of the parent's threads: it starts its own pool on first use
+    pthread_atfork(nullptr, nullptr, [] { new (&Pool::get()) Pool; });
+    return p;
+  }
+  void work() {
+    for (;;) {
+      std::unique_lock<std::mutex> l(mu_);
+      cv_.wait(l, [&] { return job_ && next_ < total_; });
+      const int w = next_++;
+      const std::function<void(int)>* job = job_;
+      l.unlock();
+      (*job)(w);
+      l.lock();
+      if (--pending_ == 0) done_.notify_one();
+    }
+  }
+  std::mutex region_mu_, mu_;
+  std::condition_variable cv_, done_;
+  const std::function<void(int)>* job_ = nullptr;
+  int workers_ = 0, next_ = 0, total_ = 0, pending_ = 0;
+};
+
 template <class F>
 void parallel_rows(int rows, int nthreads, F&& fn) {
   if (nthreads <= 1 || rows < 2) {
@@ -45,14 +106,13 @@ void parallel_rows(int rows, int nthreads, F&& fn) {
     return;
   }
   if (nthreads > rows) nthreads = rows;
-  int chunk = (rows + nthreads - 1) / nthreads;
-  std::vector<std::thread> th;
-  for (int w = 0; w < nthreads; ++w) {
-    int r0 = w * chunk, r1 = std::min(rows, r0 + chunk);
-    if (r0 >= r1) break;
-    th.emplace_back([=, &fn] { fn(r0, r1); });
-  }
-  for (auto& t : th) t.join();
+  const int chunk = (rows + nthreads - 1) / nthreads;
+  const int parts = (rows + chunk - 1) / chunk;
+  const std::function<void(int)> job = [&](int w) {
+    const int r0 = w * chunk, r1 = std::min(rows, r0 + chunk);
+    if (r0 < r1) fn(r0, r1);
+  };
+  Pool::get().run(parts, job);
 }
 
 // half/half.go:75-96 — IEEE half to float, subnormals normalised by shifting.
