@@ -566,7 +566,7 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         if (a.bias) rb = a.bias[row];
       }
       auto finish = [&](float v) { return kMLX ? v : (a.bias ? __fadd_rn(__fmul_rn(v, rs), rb) : __fmul_rn(v, rs)); };
-      if (a.cluster) {
+      if (NC <= 32 && a.cluster) {  // (64 columns never fit the receive area: no such code, and no registers for it, in that kernel)
         // The K splits of this tile are the CTAs of this cluster (rank == split), one item each: ranks
         // above 0 put their sums into rank 0's shared memory and arrive on its barrier (one releasing
         // arrival per warp); rank 0 waits, adds in split order (the scratch path's order) and stores.
@@ -627,17 +627,24 @@ tc_gemm_kernel(const __grid_constant__ GemmArgs a) {
         if (*last_flag) {
           __threadfence();
           const float* base = a.scratch + (size_t)tile * a.splits * (NC * kTileRows);
-          float sum[HC];
+          // four columns at a time: a split's four loads are independent and in flight together (one
+          // chain of dependent L2 loads per column cost microseconds), without the registers that
+          // all HC columns at once would take from the main loop
+          constexpr int SB = HC < 4 ? HC : 4;
+#pragma unroll 1
+          for (int j0 = 0; j0 < HC; j0 += SB) {
+            float sum[SB];
 #pragma unroll
-          for (int j = 0; j < HC; ++j) sum[j] = 0.f;
-          for (int s2 = 0; s2 < a.splits; ++s2) {  // a split's HC loads are independent: all in flight together
+            for (int j = 0; j < SB; ++j) sum[j] = 0.f;
+            for (int s2 = 0; s2 < a.splits; ++s2) {
 #pragma unroll
-            for (int j = 0; j < HC; ++j) sum[j] += __ldcg(base + (size_t)s2 * (NC * kTileRows) + (cq * HC + j) * kTileRows + r);
-          }
+              for (int j = 0; j < SB; ++j) sum[j] += __ldcg(base + (size_t)s2 * (NC * kTileRows) + (cq * HC + j0 + j) * kTileRows + r);
+            }
 #pragma unroll
-          for (int j = 0; j < HC; ++j) {
-            const int m = cq * HC + j;
-            if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum[j]);
+            for (int j = 0; j < SB; ++j) {
+              const int m = cq * HC + j0 + j;
+              if (m < a.batch && row < a.out_dim) a.out[(size_t)m * a.out_dim + row] = finish(sum[j]);
+            }
           }
           if (et == 0) a.counters[tile] = 0;
         }
