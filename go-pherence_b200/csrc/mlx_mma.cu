@@ -157,6 +157,19 @@ struct MmaArgs {
   // exactly one item, and the partial sums travel through the shared memory of the cluster's first
   // CTA instead of global scratch and an atomic counter
   int cluster;
+  // Grouped launches (the selected experts of a mixture-of-experts layer): the items are the 128-row
+  // tiles of `gmats` matrices of each live work entry, every entry with its own weights, prepared
+  // activations, tables and result rows; no K split.  batch is the instantiation's MB, out_dim the
+  // pitch of a result row (gmats matrices of gtpe * 128 rows side by side).
+  const MmaGroupEntry* gwork;
+  const int* gcount;  // live entries (device memory, written by the kernel that routed the tokens)
+  int gmax;           // entries the launch was sized for
+  int gtpe;           // 128-row tiles per matrix
+  int gmats;          // matrices per entry
+  int gfirst;         // the first of them in MmaGroupEntry::w
+  int gdirect;        // result row of activation m: 0 -> entry * MB + m, 1 -> the entry's item[m]
+  int gtab;           // floats of tables per entry
+  size_t gxb;         // bytes of prepared B operand per entry
 };
 
 // Shared-memory plan (dynamic, 1024-byte aligned base): ring of stages (weights then meta),
@@ -182,27 +195,47 @@ struct MmaSmem {
 };
 
 // Walks the (tile, chunk) stages of this CTA's work items in the order every role uses.
-struct StageWalk {
+// G (grouped launches): the CTA takes one contiguous range of the live items, so that it stays with
+// one entry's activations for several tiles; item w = (entry, matrix, tile of the matrix).
+template <bool G>
+struct StageWalkT {
   int w, tile, split, c, c1;
   int cps;  // chunks per stage
+  int wend, entry, mat;  // G only
   __device__ __forceinline__ void open(const MmaArgs& a) {
-    tile = w / a.splits;
-    split = w - tile * a.splits;
-    c = split * a.nchunks / a.splits;
-    c1 = (split + 1) * a.nchunks / a.splits;
+    if (G) {
+      const int per = a.gtpe * a.gmats;
+      entry = w / per;
+      const int rem = w - entry * per;
+      mat = rem / a.gtpe;
+      tile = rem - mat * a.gtpe;
+      split = 0;
+      c = 0;
+      c1 = a.nchunks;
+    } else {
+      tile = w / a.splits;
+      split = w - tile * a.splits;
+      c = split * a.nchunks / a.splits;
+      c1 = (split + 1) * a.nchunks / a.splits;
+    }
   }
-  __device__ __forceinline__ StageWalk(const MmaArgs& a, int chunks_per_stage = 1) : w(blockIdx.x), cps(chunks_per_stage) {
-    if (w < a.items) open(a);
+  __device__ __forceinline__ StageWalkT(const MmaArgs& a, int chunks_per_stage = 1, int live_items = 0)
+      : w(blockIdx.x), cps(chunks_per_stage) {
+    if (G) {
+      w = (int)((long long)blockIdx.x * live_items / gridDim.x);
+      wend = (int)((long long)(blockIdx.x + 1) * live_items / gridDim.x);
+    }
+    if (live(a)) open(a);
   }
-  __device__ __forceinline__ bool live(const MmaArgs& a) const { return w < a.items; }
+  __device__ __forceinline__ bool live(const MmaArgs& a) const { return G ? w < wend : w < a.items; }
   // chunks of the current stage (an item with an odd number of chunks ends on a stage of one)
   __device__ __forceinline__ int nc() const { return c1 - c < cps ? c1 - c : cps; }
   __device__ __forceinline__ bool last_chunk() const { return c + nc() == c1; }
   __device__ __forceinline__ void next(const MmaArgs& a) {
     c += nc();
     if (c == c1) {
-      w += gridDim.x;
-      if (w < a.items) open(a);
+      w += G ? 1 : gridDim.x;
+      if (live(a)) open(a);
     }
   }
 };
@@ -343,9 +376,11 @@ __device__ __forceinline__ void prep_x_in_cta(const float* __restrict__ x, int b
 
 // N: B rows (accumulator columns) per group block; DIGITS: base-128 digits per activation;
 // MB: activation rows the instantiation can take (MB * DIGITS <= N).
-template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false, int C = 1>
+template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false, int C = 1, bool G = false>
 __global__ void __launch_bounds__((mma_threads<N, FMT>()), 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
+  static_assert(!G || (!FUSED && FMT == FMT_MLX4), "grouped launches: MLX 4-bit, activations prepared in front");
+  typedef StageWalkT<G> StageWalk;
   constexpr int EP = epi_parts<N, FMT>();
   constexpr int kEpiWarps = 4 * EP, kEpiThreads = kEpiWarps * 32;
   constexpr int kWarpTMA = kConvWarps + kEpiWarps, kWarpMMA = kWarpTMA + 1;
@@ -421,7 +456,21 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   const uint32_t tmem_base = *tmem_holder;
   const uint32_t tmemA0 = tmem_base, tmemD0 = tmem_base + NA * kACols;  // A: NA x kACols; D: ND x kDCols
   bool ok = true;
-  StageWalk sw(a, C);
+  int gitems = 0;
+  if (G) {
+    pdl_wait();  // the work entries come from the kernels in front
+    int n = __ldcg(a.gcount);
+    if (n > a.gmax) n = a.gmax;
+    gitems = n * a.gtpe * a.gmats;
+  }
+  StageWalk sw(a, C, gitems);
+  // where a stage's weights and prepared activations lie
+  auto wsrc = [&](const StageWalk& s) {
+    const unsigned char* base = a.w;
+    if (G) base = reinterpret_cast<const unsigned char*>(__ldg(reinterpret_cast<const unsigned long long*>(&a.gwork[s.entry].w[a.gfirst + s.mat])));
+    return base + ((size_t)s.tile * a.nchunks + s.c) * kStageBytes;
+  };
+  auto bsrc = [&](const StageWalk& s) { return a.xb + (G ? (size_t)s.entry * a.gxb : 0) + (size_t)s.c * kBTileBytes; };
   TP(const bool tr = blockIdx.x == gridDim.x / 2; if (tr && tid == 0) g_mma_trace[7][0] = clock64();)
   const int cbase = sw.live(a) ? sw.c : 0;  // first chunk of this CTA's K range
 
@@ -432,8 +481,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       StageWalk sw0 = sw;
       for (int i = 0; i < S && i < kFirstStages && sw0.live(a); ++i, sw0.next(a)) {
         mbar_expect_tx(full0 + 8 * i, sw0.nc() * kStageBytes);
-        bulk_load_1d(smem_u32(ring + (size_t)i * kStage), a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes,
-                     sw0.nc() * kStageBytes, full0 + 8 * i);
+        bulk_load_1d(smem_u32(ring + (size_t)i * kStage), wsrc(sw0), sw0.nc() * kStageBytes, full0 + 8 * i);
       }
     }
     pdl_wait();
@@ -458,12 +506,11 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         for (; i < S && i < kFirstStages && sw0.live(a); ++i, sw0.next(a)) {
           uint32_t dst = smem_u32(ring + (size_t)i * kStage);
           mbar_expect_tx(full0 + 8 * i, sw0.nc() * kStageLoad);
-          bulk_load_1d(dst, a.w + ((size_t)sw0.tile * a.nchunks + sw0.c) * kStageBytes, sw0.nc() * kStageBytes, full0 + 8 * i);
+          bulk_load_1d(dst, wsrc(sw0), sw0.nc() * kStageBytes, full0 + 8 * i);
         }
         pdl_wait();
         for (int j = 0; j < i; ++j, sw.next(a))
-          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + C * kStageBytes, a.xb + (size_t)sw.c * kBTileBytes,
-                       sw.nc() * kBTileBytes, full0 + 8 * j);
+          bulk_load_1d(smem_u32(ring + (size_t)j * kStage) + C * kStageBytes, bsrc(sw), sw.nc() * kBTileBytes, full0 + 8 * j);
       }
       for (; sw.live(a) && ok; ++i, sw.next(a)) {
         int slot = i % S, round = i / S;
@@ -472,9 +519,8 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
         if (!ok) break;
         uint32_t dst = smem_u32(ring + (size_t)slot * kStage);
         mbar_expect_tx(full0 + 8 * slot, sw.nc() * kStageLoad);
-        const unsigned char* src = a.w + ((size_t)sw.tile * a.nchunks + sw.c) * kStageBytes;
-        bulk_load_1d(dst, src, sw.nc() * kStageBytes, full0 + 8 * slot);
-        if (!FUSED) bulk_load_1d(dst + C * kStageBytes, a.xb + (size_t)sw.c * kBTileBytes, sw.nc() * kBTileBytes, full0 + 8 * slot);
+        bulk_load_1d(dst, wsrc(sw), sw.nc() * kStageBytes, full0 + 8 * slot);
+        if (!FUSED) bulk_load_1d(dst + C * kStageBytes, bsrc(sw), sw.nc() * kBTileBytes, full0 + 8 * slot);
         TP(if (tr && i < 64) g_mma_trace[0][i] = clock64();)
       }
     }
@@ -601,17 +647,32 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     float acc[MB];
 #pragma unroll
     for (int m = 0; m < MB; ++m) acc[m] = 0.f;
-    if (!FUSED) {
+    if (!FUSED && !G) {
       pdl_wait();  // the tables come from the preparation kernel in front
       for (int i = et; i < 2 * a.batch * groups; i += kEpiThreads) xsum[i] = __ldg(a.xtab + i);
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
     }
+    int nb = a.batch;    // activation rows in use (G: of the current entry)
+    int cur_entry = -1;  // G: the entry whose tables are in shared memory
+    int orow[G ? MB : 1];  // G: result row of each activation row
     constexpr int kHB = kBlocks / EP;                       // blocks of this part
     constexpr int kSub = kHB * N <= 64 ? kHB : 64 / N;      // blocks per pass (at most 64 columns in registers)
     constexpr bool kNarrow = kSub * N == 8;                 // a pass of one 8-column block: one 8-column load
     constexpr int NLD = kNarrow ? 1 : kSub * N / 16;        // 16-column loads per pass
     for (int i = 0; sw.live(a) && ok; ++i) {
       int b = i % ND, slot = i % S;
+      if (G && sw.entry != cur_entry) {
+        // a new entry: its tables, row count and result rows.  Every epilogue thread passed the barrier
+        // that ends the item before, so nobody still reads the old tables.
+        cur_entry = sw.entry;
+        const float* tab = a.xtab + (size_t)cur_entry * a.gtab;
+        for (int j = et; j < 2 * a.batch * groups; j += kEpiThreads) xsum[j] = __ldcg(tab + j);
+        const MmaGroupEntry* ge = a.gwork + cur_entry;
+        nb = __ldg(&ge->count);
+#pragma unroll
+        for (int m = 0; m < (G ? MB : 1); ++m) orow[m] = a.gdirect ? __ldg(&ge->item[m]) : cur_entry * MB + m;
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      }
       ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * slot, (i / S) & 1, a.status, 6));
       uint4 mvs[C];
       uint32_t q6d = 0;  // Q6_K: the super-block's f16 d (the 16 int8 scales are in mvs)
@@ -700,7 +761,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
               };
 #pragma unroll
               for (int m = 0; m < MB; ++m) {
-                if (MB == 1 || m < a.batch) {
+                if (MB == 1 || m < nb) {
                   const float dot = paired_dot(hh * db + DIGITS * m) * xfs[m * groups + ti];
                   acc[m] = fmaf(sc, dot, acc[m]);
                   acc[m] = fmaf(bi, xsum[m * groups + ti], acc[m]);
@@ -718,7 +779,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
             const float sc = __fmul_rn((float)(f & 63u), d16), bi = -__fmul_rn((float)(f >> 6), dmin16);
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
-              if (MB == 1 || m < a.batch) {
+              if (MB == 1 || m < nb) {
                 const float dot = digits_dot(DIGITS * m) * xfs[m * groups + gbase + blk];
                 acc[m] = fmaf(sc, dot, acc[m]);
                 acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
@@ -735,7 +796,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
               const float sc = __fmul_rn(d16, (float)s8);
 #pragma unroll
               for (int m = 0; m < MB; ++m) {
-                if (MB == 1 || m < a.batch) {
+                if (MB == 1 || m < nb) {
                   const float dot = digits_dot(hh * (N / 2) + DIGITS * m) * xfs[m * groups + gbase + blk];
                   acc[m] = fmaf(sc, dot, acc[m]);
                 }
@@ -755,7 +816,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
             }
 #pragma unroll
             for (int m = 0; m < MB; ++m) {
-              if (MB == 1 || m < a.batch) {
+              if (MB == 1 || m < nb) {
                 const float dot = digits_dot(DIGITS * m) * xfs[m * groups + gbase + blk];
                 acc[m] = fmaf(sc, dot, acc[m]);
                 if (FMT != FMT_Q80) acc[m] = fmaf(bi, xsum[m * groups + gbase + blk], acc[m]);
@@ -770,6 +831,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
       TP(if (tr && et == 0 && i < 64) g_mma_trace[6][i] = clock64();)
       const bool item_done = sw.last_chunk();
       const int tile = sw.tile, split = sw.split;
+      const int gmat = G ? sw.mat : 0;
       sw.next(a);
       if (!item_done) continue;
       // ---- the item is complete: add the parts' sums (parts above 0 -> shared memory -> part 0) ----
@@ -818,6 +880,15 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
 #pragma unroll
         for (int m = 0; m < MB; ++m) acc[m] = 0.f;
         asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      } else if (G) {
+        if (half == 0) {
+#pragma unroll
+          for (int m = 0; m < MB; ++m) {
+            if (m < nb) a.out[(size_t)orow[G ? m : 0] * a.out_dim + gmat * (a.gtpe * kTileRows) + row] = acc[m];
+            acc[m] = 0.f;
+          }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");  // pair and the tables are free for the next item
       } else if (a.splits == 1) {
         if (half == 0) {
 #pragma unroll
@@ -1232,6 +1303,156 @@ int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int bat
   if (!w->tiled) return fail(GOPH_E_UNSUPPORTED, "weight is not in the tiled layout");
   TiledDesc d{w->tiled, w->device, w->out_dim, w->in_dim};
   return tiled_launch<FMT_MLX4>(d, out, x, batch, digits, stream, x_prepared);
+}
+
+// ---- grouped launches (mixture-of-experts) -----------------------------------------------------
+
+// The activations of every (entry, row) as the tensor core wants them: block = one row of one entry,
+// a warp takes 64-element groups; arithmetic and layout are mlx_prep_x_kernel's.  PHASE 0: the row is
+// the item's token in src[tokens][in_dim]; PHASE 1: silu(g) * u of the gate and up results
+// src[entry * MB + m][2][in_dim] (kernels.SiLU then the multiply, backends/simd/kernels/activation.go:15-24;
+// single-precision exp as in the CUDA-core expert kernels).
+template <int N, int MB, int PHASE>
+__global__ void __launch_bounds__(256)
+moe_mma_prep_kernel(const MmaGroupEntry* __restrict__ work, const int* __restrict__ count, int max_entries,
+                    const float* __restrict__ src, int in_dim, int top_k, unsigned char* __restrict__ xb, size_t xb_stride,
+                    float* __restrict__ xtab, int tab_stride) {
+  constexpr int DIGITS = 4, QBITS = 26;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int entry = blockIdx.x / MB, m = blockIdx.x - entry * MB;
+  int live = __ldcg(count);
+  if (live > max_entries) live = max_entries;
+  if (entry >= live) return;
+  const MmaGroupEntry* ge = work + entry;
+  if (m >= ge->count) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, groups = in_dim / 64;
+  const float* row = PHASE == 0 ? src + (size_t)(ge->item[m] / top_k) * in_dim : src + (size_t)(entry * MB + m) * 2 * in_dim;
+  unsigned char* bdst = xb + (size_t)entry * xb_stride;
+  float* tab = xtab + (size_t)entry * tab_stride;
+  for (int g = warp; g < groups; g += 8) {
+    float v[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int k = g * 64 + h * 32 + lane;
+      if (PHASE == 0) {
+        v[h] = row[k];
+      } else {
+        const float gv = row[k], uv = row[in_dim + k];
+        v[h] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
+      }
+    }
+    float s = v[0] + v[1], mx = fmaxf(fabsf(v[0]), fabsf(v[1]));
+    // the order of mlx_prep_x_kernel: each half's butterfly, then the halves
+    float s0 = v[0], s1 = v[1];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    s = s0 + s1;
+    int e = (int)((__float_as_uint(mx) >> 23) & 0xFF);
+    if (e < QBITS + 2) e = QBITS + 2;
+    if (e > 254) e = 254;
+    if (lane == 0) {
+      tab[m * groups + g] = s;
+      tab[(MB + m) * groups + g] = __uint_as_float((uint32_t)(e - 126 - QBITS + 127) << 23);
+    }
+    const float fi = __uint_as_float((uint32_t)(QBITS - (e - 126) + 127) << 23);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      int q = __float2int_rn(v[h] * fi);
+      const int k = (g & 3) * 64 + h * 32 + lane;
+      const int step = k >> 5, w = (k & 31) >> 3, j = k & 7;
+      const int pos = 8 * w + 4 * (j & 1) + (j >> 1);
+      unsigned char* base = bdst + (size_t)(g >> 2) * (N * 256) + step * (N * 32) + (pos >> 4) * ((N / 8) * 128) + (pos & 15);
+#pragma unroll
+      for (int d = 0; d < DIGITS; ++d) {
+        const int dig = d == DIGITS - 1 ? q : ((q + 64) & 127) - 64;
+        q = (q - dig) >> 7;
+        const int n = m * DIGITS + d;
+        base[(n >> 3) * 128 + (n & 7) * 16] = (unsigned char)(dig & 0xFF);
+      }
+    }
+  }
+}
+
+bool mlx_mma_grouped_supported(int hidden, int inter) {
+  return hidden % kChunkK == 0 && inter % kChunkK == 0 && hidden % kTileRows == 0 && inter % kTileRows == 0 && hidden <= 16384 &&
+         inter <= 16384;
+}
+// four digits per activation row -> 4 * rows accumulator columns
+size_t mlx_mma_grouped_xb_bytes(int in_dim, int rows) { return (size_t)(in_dim / kChunkK) * (8 * 4 * rows * 32); }
+int mlx_mma_grouped_tab_floats(int in_dim, int rows) { return 2 * rows * (in_dim / 64); }
+
+template <int MB>
+static int launch_grouped(int device, const MmaGroupLaunch& g, cudaStream_t stream) {
+  constexpr int N = 4 * MB, C = stage_chunks<N, FMT_MLX4>();
+  MmaDeviceBufs* bufs = device_bufs(device);
+  if (!bufs) return fail(GOPH_E_NOMEM, "cannot allocate the tensor-core path's device scratch");
+  DeviceState& st = device_state(device);
+  MmaArgs a;
+  memset(&a, 0, sizeof a);
+  a.status = bufs->status;
+  a.xb = g.xb;
+  a.xtab = g.xtab;
+  a.out = g.out;
+  a.out_dim = g.mats * g.rows;
+  a.in_dim = g.in_dim;
+  a.batch = MB;
+  a.ntiles = g.rows / kTileRows;
+  a.nchunks = g.in_dim / kChunkK;
+  a.splits = 1;
+  a.items = g.max_entries * g.mats * a.ntiles;
+  a.gwork = g.work;
+  a.gcount = g.count;
+  a.gmax = g.max_entries;
+  a.gtpe = a.ntiles;
+  a.gmats = g.mats;
+  a.gfirst = g.first;
+  a.gdirect = g.phase == 1;
+  a.gtab = mlx_mma_grouped_tab_floats(g.in_dim, MB);
+  a.gxb = mlx_mma_grouped_xb_bytes(g.in_dim, MB);
+  a.dbg = g_mma_dbg;
+  size_t fixed = MmaSmem<N, FMT_MLX4, false, C>::bytes(0, MB, g.in_dim);
+  int stages = fixed < kMmaSmemBudget ? (int)((kMmaSmemBudget - fixed) / MmaSmem<N, FMT_MLX4, false, C>::kStage) : 0;
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages < 3) return fail(GOPH_E_UNSUPPORTED, "tensor-core experts: %d columns leave no room for the ring", g.in_dim);
+  a.stages = stages;
+  size_t smem = MmaSmem<N, FMT_MLX4, false, C>::bytes(stages, MB, g.in_dim);
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(g.max_entries * MB);
+  cfg.blockDim = dim3(256);
+  note_launch();
+  if (g.phase == 0)
+    GOPH_CUDA(cudaLaunchKernelEx(&cfg, moe_mma_prep_kernel<N, MB, 0>, g.work, g.count, g.max_entries, g.src, g.in_dim, g.top_k, g.xb,
+                                 a.gxb, g.xtab, a.gtab));
+  else
+    GOPH_CUDA(cudaLaunchKernelEx(&cfg, moe_mma_prep_kernel<N, MB, 1>, g.work, g.count, g.max_entries, g.src, g.in_dim, g.top_k, g.xb,
+                                 a.gxb, g.xtab, a.gtab));
+  auto kern = mlx_mma_kernel<N, 4, MB, FMT_MLX4, false, C, true>;
+  GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cfg.gridDim = dim3(a.items < st.sm_count ? a.items : st.sm_count);
+  cfg.blockDim = dim3(mma_threads<N, FMT_MLX4>());
+  cfg.dynamicSmemBytes = smem;
+  note_launch();
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, a));
+  return GOPH_OK;
+}
+
+int mlx_mma_launch_grouped(int device, const MmaGroupLaunch& g, cudaStream_t stream) {
+  if (g.entry_rows == 2) return launch_grouped<2>(device, g, stream);
+  if (g.entry_rows == 4) return launch_grouped<4>(device, g, stream);
+  return fail(GOPH_E_INVALID, "grouped launch: entries of %d items", g.entry_rows);
 }
 
 // ---- GGUF Q4_K / Q8_0 in the tiled layouts ------------------------------------------------------

@@ -26,6 +26,40 @@ __host__ __device__ inline size_t mlx_tiled_meta_offset(int row, int col, int nc
 // launch on this stream prepared the same x (same batch, same in_dim), skip the preparation.
 int mlx_mma_launch(const goph_mlx_weight* w, float* out, const float* x, int batch, int digits, cudaStream_t stream,
                    bool x_prepared = false);
+
+// ---- grouped launches: the selected experts of a mixture-of-experts layer --------------------
+// One work entry = one expert (tiled matrices of equal shapes) and up to `rows` (2 or 4, the same
+// for every entry of a call) of the (token, slot) items that chose it; an expert chosen by more
+// items has several entries.
+constexpr int kMoeMmaRowsMin = 2, kMoeMmaRowsMax = 4;
+struct __align__(16) MmaGroupEntry {
+  const unsigned char* w[3];  // tiled gate, up, down
+  int count;                  // items of this entry, 1..rows
+  int expert;
+  int item[8];                // token * top_k + slot
+};
+// True when experts of [inter x hidden] / [hidden x inter] can run as grouped launches.
+bool mlx_mma_grouped_supported(int hidden, int inter);
+// Bytes of prepared activations and floats of tables one entry of `rows` items needs for an input of in_dim.
+size_t mlx_mma_grouped_xb_bytes(int in_dim, int rows);
+int mlx_mma_grouped_tab_floats(int in_dim, int rows);
+struct MmaGroupLaunch {
+  const MmaGroupEntry* work;  // device
+  const int* count;           // device: live entries
+  int max_entries;            // entries the launch is sized for
+  int entry_rows;             // items per entry: 2 or 4
+  int first, mats;            // matrices of an entry this launch multiplies: w[first .. first + mats)
+  int rows, in_dim;           // shape of each of them
+  int phase;                  // 0: activations = row item / top_k of src; 1: silu(g) * u of src's row entry * entry_rows + m
+  int top_k;
+  const float* src;
+  unsigned char* xb;          // [max_entries][xb_bytes]
+  float* xtab;                // [max_entries][tab_floats]
+  float* out;                 // phase 0: [max_entries * entry_rows][mats * rows]; phase 1: [items][rows]
+};
+// Two launches: the entries' activations as digits, sums and scales; then the products.
+int mlx_mma_launch_grouped(int device, const MmaGroupLaunch& g, cudaStream_t stream);
+
 // Reads the device status word (0 = every wait completed); synchronises the copy stream.
 int mlx_mma_status(int device);
 void mlx_mma_status_clear(int device);

@@ -26,6 +26,7 @@
 #include <string.h>
 
 #include "goph_internal.cuh"
+#include "mlx_mma.cuh"
 
 namespace goph {
 
@@ -70,6 +71,13 @@ struct goph_moe_layer {
   int* lists;                      // [0] arrival counter of the routing CTAs, [1] number of work entries
   goph::MoeWork* work;             // [E] selected resident experts of the current call
   int* items;                      // [E][max_tokens] item = token * top_k + slot, per expert
+  // experts in the tiled layout: grouped launches of the tensor-core kernel
+  int tiled;                       // -1 no expert set yet, 0 row-major experts, 1 tiled experts
+  int max_entries;                 // work entries (expert, up to two items) a call can have
+  goph::MmaGroupEntry* mwork;      // [max_entries]
+  unsigned char* mxb;              // [max_entries] prepared activations of an entry
+  float* mxtab;                    // [max_entries] their sums and scales
+  float* gu;                       // [max_entries * 2][2][inter] gate and up results (entries of two or four items: the first holds more entries)
 };
 
 namespace goph {
@@ -197,11 +205,12 @@ moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, cons
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, int norm_topk, int tokens,
                  int max_tokens, MoeTables tb, int* __restrict__ ids, float* __restrict__ wts,
-                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items) {
+                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items,
+                 MmaGroupEntry* __restrict__ mwork, int max_entries, int entry_rows) {
   __shared__ float sp[kMoeMaxExperts];
   __shared__ int s_cnt[kMoeMaxExperts];
   __shared__ float s_mx, s_inv;
-  __shared__ int s_ok, s_last, s_n;
+  __shared__ int s_ok, s_last, s_n, s_m;
   pdl_prologue();
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
   const float* lg = logits + (size_t)t * num_experts;
@@ -287,7 +296,7 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
   // depends on scheduling; no result does (every item's arithmetic is the same in any grouping).
   __threadfence();
   for (int e = tid; e < num_experts; e += blockDim.x) s_cnt[e] = 0;
-  if (tid == 0) s_n = 0;
+  if (tid == 0) s_n = s_m = 0;
   __syncthreads();
   for (int it = tid; it < tokens * top_k; it += blockDim.x) {
     const int e = __ldcg(ids + it);
@@ -307,6 +316,21 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
       wk.count = s_cnt[e];
       wk.pad[0] = wk.pad[1] = 0;
       work[atomicAdd(&s_n, 1)] = wk;
+      if (mwork) {
+        // tiled experts: entries of up to entry_rows items, an expert's entries next to each other
+        const int n = (s_cnt[e] + entry_rows - 1) / entry_rows;
+        const int first = atomicAdd(&s_m, n);
+        for (int j = 0; j < n && first + j < max_entries; ++j) {
+          MmaGroupEntry ge;
+          ge.w[0] = reinterpret_cast<const unsigned char*>(tb.gate_w[e]);
+          ge.w[1] = reinterpret_cast<const unsigned char*>(tb.up_w[e]);
+          ge.w[2] = reinterpret_cast<const unsigned char*>(tb.down_w[e]);
+          ge.expert = e;
+          ge.count = min(entry_rows, s_cnt[e] - j * entry_rows);
+          for (int q = 0; q < 8; ++q) ge.item[q] = q < ge.count ? items[(size_t)e * max_tokens + j * entry_rows + q] : 0;
+          mwork[first + j] = ge;
+        }
+      }
     }
   }
   __syncthreads();
@@ -314,6 +338,7 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
   for (int y = s_n + tid; y < num_experts; y += blockDim.x) work[y].count = 0;
   if (tid == 0) {
     lists[1] = s_n;
+    lists[2] = min(s_m, max_entries);
     lists[0] = 0;  // ready for the next call
   }
 }
@@ -654,6 +679,8 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
   m->max_tokens = max_tokens;
   m->group_size = group_size;
   m->sb_bf16 = -1;
+  m->tiled = -1;
+  m->max_entries = min(max_tokens * top_k, num_experts * ((max_tokens + kMoeMmaRowsMin - 1) / kMoeMmaRowsMin));
   size_t n = (size_t)num_experts;
   const void*** hp[6] = {(const void***)&m->host.gate_w, &m->host.gate_sb, (const void***)&m->host.up_w,
                          &m->host.up_sb,                 (const void***)&m->host.down_w, &m->host.down_sb};
@@ -704,24 +731,65 @@ GOPH_API int goph_moe_set_expert(goph_moe_layer* m, int eid, const goph_mlx_weig
   }
   const goph_mlx_weight* ws[3] = {gate, up, down};
   const int want_out[3] = {m->inter, m->inter, m->hidden}, want_in[3] = {m->hidden, m->hidden, m->inter};
+  const int tiled = gate && gate->tiled ? 1 : 0;
   for (int i = 0; i < 3; ++i) {
     const goph_mlx_weight* w = ws[i];
     if (!w || w->magic != kMagicMLX || w->device != m->device || w->out_dim != want_out[i] || w->in_dim != want_in[i] ||
         w->group_size != m->group_size)
       return fail(GOPH_E_INVALID, "expert %d: projection %d must be an MLX weight [%d x %d] with group size %d on device %d", eid, i,
                   want_out[i], want_in[i], m->group_size, m->device);
-    if (!w->qweight || !w->sb)
-      return fail(GOPH_E_UNSUPPORTED, "expert %d: projection %d is in the tiled layout; experts use the row-major layout", eid, i);
+    if ((w->tiled != nullptr) != (tiled != 0) || (!tiled && (!w->qweight || !w->sb)))
+      return fail(GOPH_E_UNSUPPORTED, "expert %d: its projections mix the row-major and the tiled layout", eid);
+    if (m->tiled >= 0 && m->tiled != tiled)
+      return fail(GOPH_E_UNSUPPORTED, "expert %d: the experts of a layer must share one layout (row-major or tiled)", eid);
     if (m->sb_bf16 >= 0 && m->sb_bf16 != w->sb_bf16)
       return fail(GOPH_E_UNSUPPORTED, "experts mix bf16-valued and f32 scale tables");
-    m->sb_bf16 = w->sb_bf16;
   }
-  m->host.gate_w[eid] = reinterpret_cast<const uint4*>(gate->qweight);
-  m->host.gate_sb[eid] = gate->sb;
-  m->host.up_w[eid] = reinterpret_cast<const uint4*>(up->qweight);
-  m->host.up_sb[eid] = up->sb;
-  m->host.down_w[eid] = reinterpret_cast<const uint4*>(down->qweight);
-  m->host.down_sb[eid] = down->sb;
+  if (tiled && !mlx_mma_grouped_supported(m->hidden, m->inter))
+    return fail(GOPH_E_UNSUPPORTED, "tiled experts need hidden=%d and inter=%d to be multiples of 256", m->hidden, m->inter);
+  if (tiled && !m->mwork) {
+    // scratch of the grouped launches, once per layer
+    if (int rc = use_device(m->device)) return rc;
+    // sized for entries of two items (the most entries) holding four items' data (the largest entries)
+    const int big = max(m->hidden, m->inter);
+    const size_t xb = mlx_mma_grouped_xb_bytes(big, kMoeMmaRowsMax);
+    const size_t tab = (size_t)mlx_mma_grouped_tab_floats(big, kMoeMmaRowsMax);
+    const size_t ne = (size_t)m->max_entries;
+    MmaGroupEntry* mw = nullptr;
+    unsigned char* mxb = nullptr;
+    float *mxtab = nullptr, *gu = nullptr;
+    cudaError_t e = cudaMalloc(&mw, ne * sizeof(MmaGroupEntry));
+    if (e == cudaSuccess) e = cudaMalloc(&mxb, ne * xb);
+    if (e == cudaSuccess) e = cudaMalloc(&mxtab, ne * tab * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&gu, ne * kMoeMmaRowsMax * 2 * m->inter * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(mxb, 0, ne * xb);  // rows past an entry's items are multiplied too (and ignored)
+    if (e != cudaSuccess) {
+      cudaFree(mw);
+      cudaFree(mxb);
+      cudaFree(mxtab);
+      cudaFree(gu);
+      return fail_cuda(e, "cudaMalloc(MoE grouped-launch scratch)");
+    }
+    m->mwork = mw;
+    m->mxb = mxb;
+    m->mxtab = mxtab;
+    m->gu = gu;
+  }
+  m->tiled = tiled;
+  m->sb_bf16 = gate->sb_bf16;
+  if (tiled) {
+    m->host.gate_w[eid] = reinterpret_cast<const uint4*>(gate->tiled);
+    m->host.up_w[eid] = reinterpret_cast<const uint4*>(up->tiled);
+    m->host.down_w[eid] = reinterpret_cast<const uint4*>(down->tiled);
+    m->host.gate_sb[eid] = m->host.up_sb[eid] = m->host.down_sb[eid] = nullptr;
+  } else {
+    m->host.gate_w[eid] = reinterpret_cast<const uint4*>(gate->qweight);
+    m->host.gate_sb[eid] = gate->sb;
+    m->host.up_w[eid] = reinterpret_cast<const uint4*>(up->qweight);
+    m->host.up_sb[eid] = up->sb;
+    m->host.down_w[eid] = reinterpret_cast<const uint4*>(down->qweight);
+    m->host.down_sb[eid] = down->sb;
+  }
   m->tables_dirty = 1;
   return GOPH_OK;
 }
@@ -747,6 +815,10 @@ GOPH_API int goph_moe_free(goph_moe_layer* m) {
   cudaFree(m->lists);
   cudaFree(m->work);
   cudaFree(m->items);
+  cudaFree(m->mwork);
+  cudaFree(m->mxb);
+  cudaFree(m->mxtab);
+  cudaFree(m->gu);
   m->magic = 0;
   delete m;
   return GOPH_OK;
@@ -757,9 +829,46 @@ static int moe_run(goph_moe_layer* m, float* out_dev, const float* x_dev, const 
                    cudaStream_t s) {
   if (int rc = moe_upload_tables(m)) return rc;
   const int sms = device_state(m->device).sm_count;
+  // Tiled experts: items per work entry.  Two keep the narrow, faster form of the tensor-core kernel
+  // (8 accumulator columns); with many tokens most experts have more than two items and entries of
+  // four read each expert once.  Option moe_rows (2 or 4) overrides.
+  int entry_rows = tokens * m->top_k <= 2 * m->num_experts ? 2 : 4;
+  if (options().moe_rows == 2 || options().moe_rows == 4) entry_rows = options().moe_rows;
   if (int rc = moe_launch(moe_route_kernel, dim3(tokens), 128, 0, s, logits_dev, m->num_experts, m->top_k, m->norm_topk, tokens,
-                          m->max_tokens, m->dev, m->ids, m->wts, m->lists, m->work, m->items))
+                          m->max_tokens, m->dev, m->ids, m->wts, m->lists, m->work, m->items, m->tiled == 1 ? m->mwork : nullptr,
+                          m->max_entries, entry_rows))
     return rc;
+  if (m->tiled == 1) {
+    // tiled experts: gate and up of every entry in one grouped launch of the tensor-core kernel, then
+    // down (each launch preceded by the kernel that writes the entries' activations as digits)
+    MmaGroupLaunch g;
+    memset(&g, 0, sizeof g);
+    g.work = m->mwork;
+    g.count = m->lists + 2;
+    g.entry_rows = entry_rows;
+    g.max_entries = min(m->max_entries, min(tokens * m->top_k, m->num_experts * ((tokens + entry_rows - 1) / entry_rows)));
+    g.top_k = m->top_k;
+    g.xb = m->mxb;
+    g.xtab = m->mxtab;
+    g.first = 0;
+    g.mats = 2;
+    g.rows = m->inter;
+    g.in_dim = m->hidden;
+    g.phase = 0;
+    g.src = x_dev;
+    g.out = m->gu;
+    if (int rc = mlx_mma_launch_grouped(m->device, g, s)) return rc;
+    g.first = 2;
+    g.mats = 1;
+    g.rows = m->hidden;
+    g.in_dim = m->inter;
+    g.phase = 1;
+    g.src = m->gu;
+    g.out = m->dpart;
+    if (int rc = mlx_mma_launch_grouped(m->device, g, s)) return rc;
+    return moe_launch(moe_combine_kernel, dim3((m->hidden + 255) / 256, tokens), 256, 0, s, m->dev, m->dpart, m->ids, m->wts,
+                      out_dev, m->hidden, m->top_k);
+  }
   int sh = 0;
   while ((32 << sh) < m->group_size) ++sh;
   // at most this many experts can have been selected; CTAs past the actual number return at once

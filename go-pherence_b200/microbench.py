@@ -132,10 +132,12 @@ def run(fmt, out_dim, in_dim, batch=1, launches=200, copies=0, opts=(), warmup=1
     return res
 
 
-def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, launches=40, opts=(), keep_alive=None):
+def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, launches=40, opts=(), keep_alive=None,
+            expert_layout=1, eager=False):
     """Selected-expert projection at the Qwen3-30B-A3B layer shape: `layers` distinct layers are walked
     so consecutive calls do not find their experts in L2.  Bytes counted: the router plus three matrices
-    of every distinct expert the call's tokens selected."""
+    of every distinct expert the call's tokens selected.  expert_layout: 1 = row-major experts (CUDA-core
+    expert kernels), 2 = tiled experts (grouped launches of the tensor-core kernel)."""
     import numpy as np
     import torch
     pkg = load_package()
@@ -151,6 +153,7 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
         r = rt.UploadMLXWeight(*syn.mlx_weight(("r", l), experts, hidden, 64), hidden, experts, 64, True)
         m.SetRouter(r)
         keep.append(r)
+        rt.SetOption("mlx_layout", expert_layout)
         for e in range(experts):
             hs = []
             for o, i in ((inter, hidden), (inter, hidden), (hidden, inter)):
@@ -159,6 +162,7 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
                 hs.append(rt.UploadMLXWeight(w, sc, syn.bf16_round(np.float32(-8) * sc), i, o, 64, True))
             m.SetExpert(e, *hs)
             keep += hs
+        rt.SetOption("mlx_layout", 1)
         mods.append(m)
     rt.SetOption("mlx_layout", 0)
     x = torch.from_numpy(syn.activations("moe-bench", tokens * hidden)).cuda()
@@ -170,15 +174,22 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
         m.Forward(ob, xb, tokens, stream)
         torch.cuda.synchronize()
         distinct.append(len(set(m.LastRouting(tokens)[0].reshape(-1).tolist())))
-    side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        for i in range(launches):
-            mods[i % layers].Forward(ob, xb, tokens, torch.cuda.current_stream())
+    class Eager:  # plain launches instead of a graph replay (for a profiler's launch list)
+        def replay(self):
+            for i in range(launches):
+                mods[i % layers].Forward(ob, xb, tokens, torch.cuda.current_stream())
+    if eager:
+        graph = Eager()
+    else:
+        side = torch.cuda.Stream()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(launches):
+                mods[i % layers].Forward(ob, xb, tokens, torch.cuda.current_stream())
     graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 5
+    reps = 1 if eager else 5
     e0.record()
     for _ in range(reps):
         graph.replay()
@@ -338,6 +349,8 @@ def run_decode_tokens(steps=3, position=150, opts=()):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--eager", action="store_true", help="--format moe: plain launches instead of a CUDA graph")
+    ap.add_argument("--expert-layout", type=int, default=1, choices=[1, 2], help="--format moe: 1 row-major experts, 2 tiled")
     ap.add_argument("--layer-chain", action="store_true", help="decoder-layer projections at Llama-3-8B shapes as a dependent chain")
     ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q5k", "q6k", "q8_0", "fp8", "moe"])
     ap.add_argument("--out", type=int, default=4096)
@@ -365,7 +378,8 @@ def main():
                                          as_list=args.list)))
         return
     if args.format == "moe":
-        print(json.dumps(run_moe(args.tokens, opts=opts)))
+        print(json.dumps(run_moe(args.tokens, opts=opts, expert_layout=args.expert_layout, eager=args.eager,
+                                 launches=min(args.launches, 40))))
         return
     print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts, chain=args.chain, xbf16=args.xbf16)))
 

@@ -115,6 +115,9 @@ int goph_sm_count(int device);
  *   "mlx_cluster" 1 (default): K splits that all run at once are launched as thread-block clusters and
  *                 add their partial sums through shared memory; 0: always through device scratch
  *                 and an atomic counter.  Same bits either way
+ *   "moe_rows"    MoE layers whose experts are in the tiled layout: (token, slot) items per work
+ *                 entry of the grouped tensor-core launches, 2 or 4; 0 (default) = two while the
+ *                 call has at most two items per expert on average, else four.  Same bits either way
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion
  *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
@@ -359,8 +362,12 @@ int goph_moe_create(int device, int num_experts, int hidden, int inter, int grou
                     int norm_topk, int max_tokens, goph_moe_layer** out);
 /* Router weight [num_experts x hidden] (LlamaLayer.RouterW uploaded with goph_mlx_upload).  Borrowed. */
 int goph_moe_set_router(goph_moe_layer* m, const goph_mlx_weight* router);
-/* Expert eid's gate/up [inter x hidden] and down [hidden x inter] weights (borrowed; row-major
- * layout).  All three NULL marks the expert as not resident on this GPU: goph_moe_forward then
+/* Expert eid's gate/up [inter x hidden] and down [hidden x inter] weights (borrowed).  The experts
+ * of a layer share one device layout: row-major (option "mlx_layout" = 1 at upload, or the default
+ * for matrices under 8 Mi weights) runs them on the CUDA cores; tiled ("mlx_layout" = 2 at upload;
+ * hidden and inter multiples of 256) runs all selected experts as grouped launches of the
+ * tensor-core kernel, which is the faster form from a few tokens per call upwards.
+ * All three NULL marks the expert as not resident on this GPU: goph_moe_forward then
  * leaves its contribution out, which is how experts are placed across GPUs
  * (backends/placement/expert_pool.go:101-153 keeps a resident subset; here the subset is per GPU). */
 int goph_moe_set_expert(goph_moe_layer* m, int eid, const goph_mlx_weight* gate,

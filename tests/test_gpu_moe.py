@@ -20,7 +20,9 @@ def no_wait_gave_up(gpu):
 class Layer:
     """Synthetic MoE layer resident on the GPU plus the stacked host arrays the oracle takes."""
 
-    def __init__(self, rt, syn, key, experts, hidden, inter, gs=64, top_k=8, norm=True, max_tokens=32, resident=None):
+    def __init__(self, rt, syn, key, experts, hidden, inter, gs=64, top_k=8, norm=True, max_tokens=32, resident=None,
+                 layout=1):
+        # layout: 1 = experts row-major (CUDA-core expert kernels), 2 = tiled (grouped tensor-core launches)
         self.rt, self.E, self.hidden, self.inter, self.gs = rt, experts, hidden, inter, gs
         self.top_k, self.norm = top_k, norm
         g = syn.rng("moe", key, experts, hidden, inter, gs)
@@ -38,6 +40,7 @@ class Layer:
             self.rw = rt.UploadMLXWeight(*self.router, hidden, experts, gs, True)
             self.layer.SetRouter(self.rw)
             self.handles = []
+            rt.SetOption("mlx_layout", layout)
             for e in range(experts):
                 if resident is not None and e not in resident:
                     continue
@@ -107,6 +110,60 @@ def test_forward_parity(gpu, pkg, experts, hidden, inter, top_k, norm, tokens):
         want = L.oracle(x[t], ids[t], wts[t])
         assert pkg.synth.rel_err(got[t], want) <= TOL, (t, pkg.synth.rel_err(got[t], want))
     L.free()
+
+
+@pytest.mark.parametrize("experts,hidden,inter,top_k,norm,tokens", [
+    (16, 512, 256, 4, True, 3),
+    (16, 512, 256, 4, False, 5),
+    (8, 1024, 768, 8, True, 2),     # every expert selected, two items each
+    (8, 512, 256, 8, True, 6),      # six items per expert: entries of four and two
+    (4, 256, 256, 2, True, 13),     # ragged entries (4 + 4 + ...)
+    (3, 256, 256, 3, True, 32),     # 32 items per expert: eight full entries each
+    (128, 2048, 768, 8, True, 1),   # Qwen3-30B-A3B layer, decode
+    (128, 2048, 768, 8, True, 8),
+    (128, 2048, 768, 8, True, 32),
+])
+def test_forward_parity_tiled_experts(gpu, pkg, experts, hidden, inter, top_k, norm, tokens):
+    # experts uploaded in the tiled layout run as grouped launches of the tensor-core kernel
+    L = Layer(gpu, pkg.synth, "fw", experts, hidden, inter, 64, top_k, norm, max_tokens=32, layout=2)
+    x = pkg.synth.activations(("moe", experts, tokens), tokens * hidden).reshape(tokens, hidden)
+    got, ids, wts = run_forward(L, x, tokens)
+    for t in range(tokens):
+        want = L.oracle(x[t], ids[t], wts[t])
+        assert pkg.synth.rel_err(got[t], want) <= TOL, (t, pkg.synth.rel_err(got[t], want))
+    # the same tokens one at a time and in another order: a token's result does not depend on its batch
+    if tokens > 1:
+        order = list(range(tokens))[::-1]
+        again, _, _ = run_forward(L, x[order].copy(), tokens)
+        assert np.array_equal(again[::-1].view(np.uint32), got.view(np.uint32))
+        one, _, _ = run_forward(L, x[tokens - 1:tokens].copy(), 1)
+        assert np.array_equal(one[0].view(np.uint32), got[tokens - 1].view(np.uint32))
+    L.free()
+
+
+def test_tiled_expert_placement_and_layout_rules(gpu, pkg):
+    experts, hidden, inter, top_k, tokens = 32, 512, 256, 8, 4
+    full = Layer(gpu, pkg.synth, "place", experts, hidden, inter, 64, top_k, True, layout=2)
+    lo = Layer(gpu, pkg.synth, "place", experts, hidden, inter, 64, top_k, True, resident=set(range(16)), layout=2)
+    hi = Layer(gpu, pkg.synth, "place", experts, hidden, inter, 64, top_k, True, resident=set(range(16, 32)), layout=2)
+    rowmajor = Layer(gpu, pkg.synth, "place", experts, hidden, inter, 64, top_k, True, layout=1)
+    x = pkg.synth.activations("place", tokens * hidden).reshape(tokens, hidden)
+    a, ids, wts = run_forward(full, x, tokens)
+    b, ids_lo, _ = run_forward(lo, x, tokens)
+    c, ids_hi, _ = run_forward(hi, x, tokens)
+    d, ids_rm, _ = run_forward(rowmajor, x, tokens)
+    assert np.array_equal(ids, ids_lo) and np.array_equal(ids, ids_hi) and np.array_equal(ids, ids_rm)
+    for t in range(tokens):
+        assert pkg.synth.rel_err(b[t] + c[t], a[t]) <= 1e-4
+        assert pkg.synth.rel_err(a[t], full.oracle(x[t], ids[t], wts[t])) <= TOL
+        assert pkg.synth.rel_err(a[t], d[t]) <= 1e-3              # the two expert paths agree (each within 2e-3 of the oracle)
+    # a layer's experts share one layout
+    with pytest.raises(gpu.GophError):
+        full.layer.SetExpert(0, *rowmajor.handles[:3])
+    with pytest.raises(gpu.GophError):
+        rowmajor.layer.SetExpert(0, *full.handles[:3])
+    for L in (full, lo, hi, rowmajor):
+        L.free()
 
 
 @pytest.mark.parametrize("norm", [True, False])
