@@ -401,10 +401,12 @@ def extras(tensor_peak):
                     "x": r["x"], "us_per_launch": r["us_per_launch"], "frac_of_hbm_peak": r["frac_of_hbm_peak"],
                     "tflops": r["tflops"], "frac_of_bf16_tensor_peak": round(r["tflops"] / tensor_peak, 4)}
     out["llama3_70b_small_m"] = small
-    out["qwen3_30b_a3b_moe_layer"] = {
-        "T=%d" % t: {k: v for k, v in mb.run_moe(t, layers=2, launches=20).items()
-                     if k in ("us_per_call", "GBps", "frac_of_hbm_peak", "distinct_experts_per_call")}
-        for t in (1, 8, 32)}
+    # experts row-major (CUDA-core expert kernels) and tiled (grouped launches of the tensor-core kernel)
+    for name, layout in (("qwen3_30b_a3b_moe_layer", 1), ("qwen3_30b_a3b_moe_layer_tiled_experts", 2)):
+        out[name] = {
+            "T=%d" % t: {k: v for k, v in mb.run_moe(t, layers=2, launches=20, expert_layout=layout).items()
+                         if k in ("us_per_call", "GBps", "frac_of_hbm_peak", "distinct_experts_per_call")}
+            for t in (1, 8, 32)}
     return out
 
 

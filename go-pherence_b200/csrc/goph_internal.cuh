@@ -55,6 +55,7 @@ struct Options {
   int mlx_splits = 0;  // K splits on the tensor-core path (0 = by shape)
   int mlx_fuse = 1;    // 1: narrow tensor-core launches make the activation digits of their own K range themselves (one launch)
   int mlx_chunks = 0;  // 1: one 256-element chunk per pipeline stage of the tensor-core GEMV; 0: two where the format allows
+  int moe_fused = 1;   // MoE call of one token with row-major experts: 1 one cooperative launch, 0 the five launches of any token count
   int moe_rows = 0;    // tiled MoE experts: items per work entry (2 or 4); 0 = by the number of tokens
   int mlx_cluster = 1; // 1: K splits that run in one wave exchange their partial sums inside a thread-block cluster; 0: always through global scratch
   int mlx_digits = 4;  // base-128 digits per activation on the tensor-core path (4: 27 bits, 3: 20 bits)
@@ -78,6 +79,8 @@ void decode_ops_status_clear();
 // Status word of the work-list kernels of gguf_work.cu (0, 601: an expert index outside the matrix,
 // 602: a destination outside dst).
 int gguf_work_status(int device);
+int moe_status(int device);
+void moe_status_clear(int device);
 void gguf_work_status_clear(int device);
 
 // Largest dynamic shared-memory request the GEMV kernels make.

@@ -1291,6 +1291,7 @@ GOPH_API int goph_kernel_status(int device, int* out_status) {
   if (*out_status == 0) *out_status = tc_gemm_status(device);
   if (*out_status == 0) *out_status = fp8_mma_status(device);
   if (*out_status == 0) *out_status = gguf_work_status(device);
+  if (*out_status == 0) *out_status = moe_status(device);
   if (*out_status == 0) *out_status = decode_ops_status();
   return GOPH_OK;
 }
@@ -1303,6 +1304,7 @@ GOPH_API int goph_kernel_status_clear(int device) {
   tc_gemm_status_clear(device);
   fp8_mma_status_clear(device);
   gguf_work_status_clear(device);
+  moe_status_clear(device);
   decode_ops_status_clear();
   return GOPH_OK;
 }

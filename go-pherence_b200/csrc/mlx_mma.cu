@@ -380,6 +380,7 @@ template <int N, int DIGITS, int MB, int FMT = FMT_MLX4, bool FUSED = false, int
 __global__ void __launch_bounds__((mma_threads<N, FMT>()), 1)
 mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
   static_assert(!G || (!FUSED && FMT == FMT_MLX4), "grouped launches: MLX 4-bit, activations prepared in front");
+  TP(const long long t_entry = clock64();)
   typedef StageWalkT<G> StageWalk;
   constexpr int EP = epi_parts<N, FMT>();
   constexpr int kEpiWarps = 4 * EP, kEpiThreads = kEpiWarps * 32;
@@ -471,7 +472,7 @@ mlx_mma_kernel(const __grid_constant__ MmaArgs a) {
     return base + ((size_t)s.tile * a.nchunks + s.c) * kStageBytes;
   };
   auto bsrc = [&](const StageWalk& s) { return a.xb + (G ? (size_t)s.entry * a.gxb : 0) + (size_t)s.c * kBTileBytes; };
-  TP(const bool tr = blockIdx.x == gridDim.x / 2; if (tr && tid == 0) g_mma_trace[7][0] = clock64();)
+  TP(const bool tr = blockIdx.x == gridDim.x / 2 && (!(a.dbg & 8) || a.gmats == 2); if (tr && tid == 0) { g_mma_trace[7][0] = clock64(); g_mma_trace[7][3] = t_entry; })
   const int cbase = sw.live(a) ? sw.c : 0;  // first chunk of this CTA's K range
 
   if (FUSED) {

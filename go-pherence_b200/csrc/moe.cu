@@ -25,6 +25,8 @@
 // this GPU's partial sum.
 #include <string.h>
 
+#include <mutex>
+
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
 
@@ -34,7 +36,8 @@ constexpr uint32_t kMagicMoE = 0x4d4f4558;  // "MOEX"
 constexpr int kMoeWarps = 8, kMoeThreads = kMoeWarps * 32;
 constexpr int kMoeDepth = 4;             // steps of a warp's weight ring
 constexpr int kMoeStepBytes = 1024 + 512;  // two rows x 32 lanes x 16 B of weights, two rows x 32 lanes x 8 B of scales
-constexpr int kMoeMaxExperts = 1024;  // the routing kernel keeps one float and one int per expert in shared memory
+constexpr int kMoeMaxExperts = 1024;
+constexpr int kMoeMaxTopK = 64;      // slots of a token the one-launch form keeps in shared memory  // the routing kernel keeps one float and one int per expert in shared memory
 
 struct MoeTables {
   const uint4** gate_w;   // [E] packed rows (16-byte units) or null when the expert is not resident
@@ -78,6 +81,10 @@ struct goph_moe_layer {
   unsigned char* mxb;              // [max_entries] prepared activations of an entry
   float* mxtab;                    // [max_entries] their sums and scales
   float* gu;                       // [max_entries * 2][2][inter] gate and up results (entries of two or four items: the first holds more entries)
+  // one token, row-major experts: the whole call as one cooperative launch
+  unsigned* bar;                   // [0] barrier counter (only grows), [1] its value when the next launch starts
+  int token_grid;                  // CTAs of that launch (0 = not asked yet, -1 = does not fit)
+  size_t token_smem;
 };
 
 namespace goph {
@@ -100,22 +107,20 @@ __device__ __forceinline__ void pdl_prologue() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// Router logits for every token in one launch: grid (expert blocks of 16, tokens); a CTA stages its
-// token's x and each warp takes two expert rows.  (The batched MLX kernel would run ceil(T/8)
-// launches over the same small matrix.)
-template <bool SB_BF16>
-__global__ void __launch_bounds__(kMoeThreads)
-moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, const float* __restrict__ x,
-                  float* __restrict__ logits, int num_experts, int hidden, int ug_shift, int groups) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+// The router rows of one block of 16 experts against token t: a CTA stages the token's x and each
+// warp takes two expert rows.  `wait` is called once, after the first weights are in flight and
+// before x is read (the caller's dependency on the kernel in front).
+template <bool SB_BF16, typename Wait>
+__device__ __forceinline__ void moe_router_block(const uint4* __restrict__ w, const void* __restrict__ sb,
+                                                 const float* __restrict__ x, float* __restrict__ logits, int num_experts,
+                                                 int hidden, int ug_shift, int groups, int eblock, int t,
+                                                 unsigned char* smem_raw, Wait wait) {
   const int units = hidden / 32, iters = (units + 31) / 32;
   float4* xs = reinterpret_cast<float4*>(smem_raw);
   float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)iters * 256 * 16);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int t = blockIdx.y;
-  const int e0 = (blockIdx.x * kMoeWarps + warp) * 2, e1 = min(e0 + 1, num_experts - 1);
+  const int e0 = (eblock * kMoeWarps + warp) * 2, e1 = min(e0 + 1, num_experts - 1);
   const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // the weights do not depend on the kernel in front: first units in flight before the wait
   uint4 q[2];
   const bool live = e0 < num_experts;
@@ -124,7 +129,7 @@ moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, cons
     q[0] = ld_stream(w + (size_t)e0 * units + u0);
     q[1] = ld_stream(w + (size_t)e1 * units + u0);
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  wait();
   for (int idx = threadIdx.x; idx < iters * 256; idx += kMoeThreads) {
     const int it = idx >> 8, slot = (idx >> 5) & 7, l = idx & 31, unit = it * 32 + l;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -197,26 +202,36 @@ moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, cons
   }
 }
 
+// Router logits for every token in one launch: grid (expert blocks of 16, tokens).  (The batched MLX
+// kernel would run ceil(T/8) launches over the same small matrix.)
+template <bool SB_BF16>
+__global__ void __launch_bounds__(kMoeThreads)
+moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, const float* __restrict__ x,
+                  float* __restrict__ logits, int num_experts, int hidden, int ug_shift, int groups) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  moe_router_block<SB_BF16>(w, sb, x, logits, num_experts, hidden, ug_shift, groups, blockIdx.x, blockIdx.y, smem_raw,
+                            [] { asm volatile("griddepcontrol.wait;" ::: "memory"); });
+}
+
 // simd.SoftmaxInPlace + the top-k loop of moeForwardWithREAP in the reference's order
 // (model/moe.go:226-280; backends/simd/runtime/softmax.go:9-30): one CTA per token; the
 // exponentials are taken in parallel, the sum by one thread in index order, the k rounds of
 // "largest probability not yet picked, lowest id on ties" by a warp over shared memory.  The last
 // CTA to finish groups the (token, slot) items by expert into the work list.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, int norm_topk, int tokens,
-                 int max_tokens, MoeTables tb, int* __restrict__ ids, float* __restrict__ wts,
-                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items,
-                 MmaGroupEntry* __restrict__ mwork, int max_entries, int entry_rows) {
-  __shared__ float sp[kMoeMaxExperts];
-  __shared__ int s_cnt[kMoeMaxExperts];
-  __shared__ float s_mx, s_inv;
-  __shared__ int s_ok, s_last, s_n, s_m;
-  pdl_prologue();
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
-  const float* lg = logits + (size_t)t * num_experts;
-  int* my_ids = ids + (size_t)t * top_k;
-  float* my_w = wts + (size_t)t * top_k;
-  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = lg[i];
+struct MoeRouteShared {
+  float sp[kMoeMaxExperts];
+  float mx, inv;
+  int ok;
+};
+
+// One token's routing by the calling CTA (any number of threads, at least one warp): softmax over the
+// logits and the top-k rounds; ids (-1 = none) and weights go to my_ids / my_w (global or shared).
+__device__ __forceinline__ void moe_route_token(const float* __restrict__ lg, int num_experts, int top_k, int norm_topk,
+                                                int* my_ids, float* my_w, MoeRouteShared& sh) {
+  const int tid = threadIdx.x, lane = tid & 31;
+  float* sp = sh.sp;
+  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __ldcg(lg + i);
   __syncthreads();
   if (tid < 32) {
     float mx = -INFINITY;
@@ -225,20 +240,20 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
     for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     // the reference starts from x[0]: if that is NaN every comparison is false and the maximum stays NaN
     if (isnan(sp[0])) mx = sp[0];
-    if (lane == 0) s_mx = mx;
+    if (lane == 0) sh.mx = mx;
   }
   __syncthreads();
-  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = (float)exp((double)(sp[i] - s_mx));
+  for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = (float)exp((double)(sp[i] - sh.mx));
   __syncthreads();
   if (tid == 0) {
     float sum = 0.f;
     for (int i = 0; i < num_experts; ++i) sum = __fadd_rn(sum, sp[i]);
-    s_ok = !(sum == 0.f || isnan(sum) || isinf(sum));  // SoftmaxInPlace fails: no expert runs
-    s_inv = __fdiv_rn(1.f, sum);
+    sh.ok = !(sum == 0.f || isnan(sum) || isinf(sum));  // SoftmaxInPlace fails: no expert runs
+    sh.inv = __fdiv_rn(1.f, sum);
   }
   __syncthreads();
-  if (s_ok)
-    for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __fmul_rn(sp[i], s_inv);
+  if (sh.ok)
+    for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __fmul_rn(sp[i], sh.inv);
   __syncthreads();
   if (tid < 32) {
     int n = 0;
@@ -246,7 +261,7 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
     for (int k = 0; k < top_k; ++k) {
       int best = -1;
       float bs = -1.f;  // probabilities are >= 0; a picked entry is overwritten with -2 and never wins again
-      if (s_ok) {
+      if (sh.ok) {
         for (int j = lane; j < num_experts; j += 32) {
           float v = sp[j];
           if (v > bs) {
@@ -282,12 +297,28 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
       }
       if (norm_topk && n > 0 && wsum > 0.f)
         for (int k = 0; k < n; ++k) my_w[k] = __fdiv_rn(my_w[k], wsum);
-      if (tokens > 1) {
-        __threadfence();
-        s_last = atomicAdd(&lists[0], 1) == tokens - 1;
-      } else {
-        s_last = 1;  // the only CTA builds the work list itself
-      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, int norm_topk, int tokens,
+                 int max_tokens, MoeTables tb, int* __restrict__ ids, float* __restrict__ wts,
+                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items,
+                 MmaGroupEntry* __restrict__ mwork, int max_entries, int entry_rows) {
+  __shared__ MoeRouteShared sh;
+  __shared__ int s_cnt[kMoeMaxExperts];
+  __shared__ int s_last, s_n, s_m;
+  pdl_prologue();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  moe_route_token(logits + (size_t)t * num_experts, num_experts, top_k, norm_topk, ids + (size_t)t * top_k,
+                  wts + (size_t)t * top_k, sh);
+  if (tid == 0) {
+    if (tokens > 1) {
+      __threadfence();
+      s_last = atomicAdd(&lists[0], 1) == tokens - 1;
+    } else {
+      s_last = 1;  // the only CTA builds the work list itself
     }
   }
   __syncthreads();
@@ -373,12 +404,13 @@ template <bool SB_BF16, int PHASE, int M>
 __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __restrict__ items, int base, int m_now,
                                                 const float* __restrict__ src, float* __restrict__ dst, int in_dim,
                                                 int out_rows, int top_k, int ug_shift, int groups, float4* xs, float2* xc,
-                                                unsigned char* ring) {
+                                                unsigned char* ring, int bx, int nbx) {
+  // bx of nbx: this CTA's place among the CTAs that share the expert's rows
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int units = in_dim / 32, iters = (units + 31) / 32;
   const size_t sb_row = (size_t)groups * (SB_BF16 ? 4 : 8);
   const int tasks = PHASE == 0 ? out_rows : (out_rows + 1) / 2;
-  const int task_stride = gridDim.x * kMoeWarps;
+  const int task_stride = nbx * kMoeWarps;
   struct Rows {
     const uint4* w[2];
     const char* sb[2];
@@ -405,7 +437,7 @@ __device__ __forceinline__ void moe_expert_pass(const MoeWork& wk, const int* __
   // group is all the synchronisation a step needs, and kMoeDepth - 1 steps of every warp are in
   // flight while one is computed.  A step = one 32-lane iteration over the two rows of a task.
   unsigned char* wring = ring + (size_t)warp * kMoeDepth * kMoeStepBytes;
-  int task = blockIdx.x * kMoeWarps + warp;
+  int task = bx * kMoeWarps + warp;
   const int my_tasks = task < tasks ? (tasks - task + task_stride - 1) / task_stride : 0;
   const int nsteps = my_tasks * iters;
   auto issue = [&](int q) {
@@ -574,29 +606,27 @@ moe_expert_kernel(const MoeWork* __restrict__ work, const int* __restrict__ list
   // M vectors per pass: 1, 2 or 4 by how many items the expert has
   if (wk.count == 1) {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)1 * iters * 256 * 16);
-    moe_expert_pass<SB_BF16, PHASE, 1>(wk, items, 0, 1, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring);
+    moe_expert_pass<SB_BF16, PHASE, 1>(wk, items, 0, 1, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring,
+                                       blockIdx.x, gridDim.x);
   } else if (wk.count == 2) {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)2 * iters * 256 * 16);
-    moe_expert_pass<SB_BF16, PHASE, 2>(wk, items, 0, 2, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring);
+    moe_expert_pass<SB_BF16, PHASE, 2>(wk, items, 0, 2, src, dst, in_dim, out_rows, top_k, ug_shift, groups, xs, xc, ring,
+                                       blockIdx.x, gridDim.x);
   } else {
     float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)4 * iters * 256 * 16);
     for (int base = 0; base < wk.count; base += 4) {
       if (base) __syncthreads();
       moe_expert_pass<SB_BF16, PHASE, 4>(wk, items, base, min(4, wk.count - base), src, dst, in_dim, out_rows, top_k,
-                                         ug_shift, groups, xs, xc, ring);
+                                         ug_shift, groups, xs, xc, ring, blockIdx.x, gridDim.x);
     }
   }
 }
 
 // out[t][r] = sum over slots k in selection order of weight[t][k] * dpart[t][k][r]
 // (out[i] += weight * down[i], model/moe.go:336-344).  Slots whose expert is not resident here add nothing.
-__global__ void __launch_bounds__(256)
-moe_combine_kernel(MoeTables tb, const float* __restrict__ dpart, const int* __restrict__ ids,
-                   const float* __restrict__ wts, float* __restrict__ out, int hidden, int top_k) {
-  pdl_prologue();
-  const int t = blockIdx.y;
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= hidden) return;
+__device__ __forceinline__ float moe_combine_row(const MoeTables& tb, const float* __restrict__ dpart,
+                                                 const int* __restrict__ ids, const float* __restrict__ wts, int t, int r,
+                                                 int hidden, int top_k) {
   float acc = 0.f;
   for (int k0 = 0; k0 < top_k; k0 += 8) {  // eight slots at a time: their loads are issued together
     int e[8];
@@ -608,13 +638,144 @@ moe_combine_kernel(MoeTables tb, const float* __restrict__ dpart, const int* __r
     for (int j = 0; j < 8; ++j) {
       on[j] = e[j] >= 0 && tb.down_w[e[j]] != nullptr;
       w[j] = on[j] ? wts[t * top_k + k0 + j] : 0.f;
-      d[j] = on[j] ? dpart[((size_t)t * top_k + k0 + j) * hidden + r] : 0.f;
+      d[j] = on[j] ? __ldcg(dpart + ((size_t)t * top_k + k0 + j) * hidden + r) : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       if (on[j]) acc = __fadd_rn(acc, __fmul_rn(w[j], d[j]));
   }
-  out[(size_t)t * hidden + r] = acc;
+  return acc;
+}
+
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(MoeTables tb, const float* __restrict__ dpart, const int* __restrict__ ids,
+                   const float* __restrict__ wts, float* __restrict__ out, int hidden, int top_k) {
+  pdl_prologue();
+  const int t = blockIdx.y;
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= hidden) return;
+  out[(size_t)t * hidden + r] = moe_combine_row(tb, dpart, ids, wts, t, r, hidden, top_k);
+}
+
+// One token, one launch: router rows, routing, gate and up, down and the weighted sum as phases of
+// one cooperative kernel (every CTA resident) with a grid-wide barrier where a phase reads what
+// another CTA wrote.  Each phase runs the code of the kernel it replaces on the same operands, so
+// the result has the bits of the five-launch form.  The barrier: a device counter that only grows
+// (one releasing add per CTA, one polling thread per CTA, bounded; a wait that runs out records
+// 700 + the barrier's number in the status word and the CTA returns).
+constexpr long long kMoeBarrierTimeoutCycles = 2000000000LL;  // about a second
+// Tuning build only: CTA 1 records the clock at the phase boundaries of the one-launch form.
+#ifdef GOPH_TUNING
+__device__ long long g_moe_trace[16];
+#define MTP(k) if (blockIdx.x == 1 && threadIdx.x == 0) g_moe_trace[k] = clock64();
+#else
+#define MTP(k)
+#endif
+template <bool RSB_BF16, bool SB_BF16>
+__global__ void __launch_bounds__(kMoeThreads, 2)
+moe_token_kernel(MoeTables tb, const uint4* __restrict__ rw, const void* __restrict__ rsb, int r_shift, int r_groups,
+                 const float* __restrict__ x, const float* __restrict__ logits_in, float* __restrict__ logits,
+                 int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ act, float* __restrict__ dpart,
+                 float* __restrict__ out, unsigned* __restrict__ bar, int* __restrict__ status, int num_experts,
+                 int hidden, int inter, int top_k, int norm_topk, int ug_shift, int group_size) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ MoeRouteShared sh;
+  __shared__ int s_ids[kMoeMaxTopK];
+  __shared__ float s_wts[kMoeMaxTopK];
+  __shared__ unsigned s_base;
+  __shared__ int s_abort;
+  MTP(0)
+  pdl_prologue();
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    s_base = *reinterpret_cast<volatile unsigned*>(bar + 1);
+    s_abort = 0;
+  }
+  __syncthreads();
+  int nbar = 0;
+  auto grid_barrier = [&]() {
+    __syncthreads();
+    ++nbar;
+    if (tid == 0) {
+      asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(bar), "r"(1u) : "memory");
+      const unsigned target = s_base + (unsigned)nbar * gridDim.x;
+      const long long t0 = clock64();
+      unsigned seen;
+      while (true) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(bar) : "memory");
+        if ((int)(seen - target) >= 0) break;
+        if (clock64() - t0 > kMoeBarrierTimeoutCycles) {
+          s_abort = 1;
+          atomicExch(status, 700 + nbar);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    return s_abort == 0;
+  };
+  // ---- router rows (unless the caller supplied the logits) ----
+  const float* lg = logits_in;
+  if (!lg) {
+    if ((int)blockIdx.x * 2 * kMoeWarps < num_experts)
+      moe_router_block<RSB_BF16>(rw, rsb, x, logits, num_experts, hidden, r_shift, r_groups, blockIdx.x, 0, smem_raw, [] {});
+    MTP(1)
+    if (!grid_barrier()) return;
+    MTP(2)
+    lg = logits;
+  }
+  // ---- routing, by every CTA for itself ----
+  moe_route_token(lg, num_experts, top_k, norm_topk, s_ids, s_wts, sh);
+  __syncthreads();
+  MTP(3)
+  if (blockIdx.x == 0 && tid < top_k) {
+    ids[tid] = s_ids[tid];
+    wts[tid] = s_wts[tid];
+  }
+  // ---- gate and up, then down: CTA b works for slot b % top_k with the CTAs b' = b (mod top_k) ----
+  const int slot = blockIdx.x % top_k, bx = blockIdx.x / top_k, nbx = gridDim.x / top_k;
+  const int e = s_ids[slot];
+  const bool mine = bx < nbx && e >= 0 && tb.gate_w[e] != nullptr;
+  MoeWork wk;
+  if (mine) {
+    wk.w[0] = tb.gate_w[e];
+    wk.w[1] = tb.up_w[e];
+    wk.w[2] = tb.down_w[e];
+    wk.sb[0] = tb.gate_sb[e];
+    wk.sb[1] = tb.up_sb[e];
+    wk.sb[2] = tb.down_sb[e];
+  }
+  wk.expert = e;
+  wk.count = 1;
+  __shared__ int s_item;
+  if (tid == 0) s_item = slot;  // item = token * top_k + slot, token 0
+  __syncthreads();
+  const int big = hidden > inter ? hidden : inter, iters_max = (big / 32 + 31) / 32;
+  unsigned char* ring = smem_raw + (size_t)iters_max * (256 * 16 + 32 * 8);
+  float4* xs = reinterpret_cast<float4*>(smem_raw);
+  for (int phase = 0; phase < 2; ++phase) {
+    const int in_dim = phase == 0 ? hidden : inter, out_rows = phase == 0 ? inter : hidden;
+    const int iters = (in_dim / 32 + 31) / 32;
+    float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)iters * 256 * 16);
+    if (mine) {
+      if (phase == 0)
+        moe_expert_pass<SB_BF16, 0, 1>(wk, &s_item, 0, 1, x, act, in_dim, out_rows, top_k, ug_shift, in_dim / group_size, xs, xc,
+                                       ring, bx, nbx);
+      else
+        moe_expert_pass<SB_BF16, 1, 1>(wk, &s_item, 0, 1, act, dpart, in_dim, out_rows, top_k, ug_shift, in_dim / group_size, xs,
+                                       xc, ring, bx, nbx);
+    }
+    MTP(4 + 2 * phase)
+    if (!grid_barrier()) return;
+    MTP(5 + 2 * phase)
+  }
+  // ---- the weighted sum of the slots' vectors, in selection order ----
+  for (int r = blockIdx.x * kMoeThreads + tid; r < hidden; r += gridDim.x * kMoeThreads)
+    out[r] = moe_combine_row(tb, dpart, s_ids, s_wts, 0, r, hidden, top_k);
+  // the counter's value when the next launch starts (every CTA has read the old one: all of them
+  // passed the barriers above)
+  if (blockIdx.x == 0 && tid == 0) bar[1] = s_base + (unsigned)nbar * gridDim.x;
+  MTP(8)
 }
 
 template <typename... KArgs, typename... Args>
@@ -696,6 +857,8 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
   if (e == cudaSuccess) e = cudaMalloc(&m->wts, (size_t)max_tokens * top_k * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->act, (size_t)max_tokens * top_k * inter * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->dpart, (size_t)max_tokens * top_k * hidden * sizeof(float));
+  if (e == cudaSuccess) e = cudaMalloc(&m->bar, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(m->bar, 0, 2 * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMalloc(&m->lists, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(m->lists, 0, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMalloc(&m->work, (size_t)num_experts * sizeof(goph::MoeWork));
@@ -815,12 +978,110 @@ GOPH_API int goph_moe_free(goph_moe_layer* m) {
   cudaFree(m->lists);
   cudaFree(m->work);
   cudaFree(m->items);
+  cudaFree(m->bar);
   cudaFree(m->mwork);
   cudaFree(m->mxb);
   cudaFree(m->mxtab);
   cudaFree(m->gu);
   m->magic = 0;
   delete m;
+  return GOPH_OK;
+}
+
+static int* moe_status_word(int device) {
+  static int* words[kMaxDevices] = {};
+  static std::mutex mu;
+  if (device < 0 || device >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!words[device]) {
+    int* p = nullptr;
+    if (cudaMalloc(&p, sizeof(int)) != cudaSuccess || cudaMemset(p, 0, sizeof(int)) != cudaSuccess) {
+      cudaFree(p);
+      cudaGetLastError();
+      return nullptr;
+    }
+    words[device] = p;
+  }
+  return words[device];
+}
+
+namespace goph {
+int moe_status(int device) {
+  int* p = moe_status_word(device);
+  if (!p) return 0;
+  int v = 0;
+  if (cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return v;
+}
+void moe_status_clear(int device) {
+  int* p = moe_status_word(device);
+  if (p) cudaMemset(p, 0, sizeof(int));
+}
+}  // namespace goph
+
+typedef void (*MoeTokenKernel)(MoeTables, const uint4*, const void*, int, int, const float*, const float*, float*, int*, float*,
+                               float*, float*, float*, unsigned*, int*, int, int, int, int, int, int, int);
+
+// True when a call of one token can run as the one-launch form: row-major experts, a row-major
+// router (or logits from the caller), option moe_fused on, and a device that holds the grid.
+static bool moe_token_form(goph_moe_layer* m, const goph_mlx_weight* rw, MoeTokenKernel* kern) {
+  if (!options().moe_fused || m->tiled != 0 || m->top_k > kMoeMaxTopK || m->token_grid < 0) return false;
+  if (rw && !(rw->qweight && rw->sb && rw->group_size >= 32 && !(rw->group_size & (rw->group_size - 1)) && rw->in_dim % 32 == 0))
+    return false;
+  const bool rb = rw ? rw->sb_bf16 != 0 : true, eb = m->sb_bf16 != 0;
+  *kern = rb ? (eb ? moe_token_kernel<true, true> : moe_token_kernel<true, false>)
+             : (eb ? moe_token_kernel<false, true> : moe_token_kernel<false, false>);
+  if (m->token_grid == 0) {
+    const int big = max(m->hidden, m->inter), iters = (big / 32 + 31) / 32;
+    const size_t smem = (size_t)iters * (256 * 16 + 32 * 8) + (size_t)kMoeWarps * kMoeDepth * kMoeStepBytes;
+    int per_sm = 0;
+    if (smem > (size_t)kSmemBudget || cudaFuncSetAttribute(*kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, *kern, kMoeThreads, smem) != cudaSuccess || per_sm < 1) {
+      cudaGetLastError();
+      m->token_grid = -1;
+      return false;
+    }
+    if (per_sm > 2) per_sm = 2;
+    const int grid = device_state(m->device).sm_count * per_sm;
+    if (grid < m->top_k || grid * 2 * kMoeWarps < m->num_experts) {
+      m->token_grid = -1;
+      return false;
+    }
+    m->token_grid = grid;
+    m->token_smem = smem;
+  }
+  return true;
+}
+
+static int moe_run_token(goph_moe_layer* m, MoeTokenKernel kern, float* out_dev, const float* x_dev, const goph_mlx_weight* rw,
+                         const float* logits_dev, cudaStream_t s) {
+  if (int rc = moe_upload_tables(m)) return rc;
+  int* status = moe_status_word(m->device);
+  if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the MoE kernels' status word");
+  int sh = 0, rsh = 0;
+  while ((32 << sh) < m->group_size) ++sh;
+  if (rw)
+    while ((32 << rsh) < rw->group_size) ++rsh;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeCooperative;
+  attr.val.cooperative = 1;  // every CTA resident at once: the barriers between the phases need it
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(m->token_grid);
+  cfg.blockDim = dim3(kMoeThreads);
+  cfg.dynamicSmemBytes = m->token_smem;
+  cfg.stream = s;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->token_smem));
+  note_launch();
+  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, m->dev, rw ? reinterpret_cast<const uint4*>(rw->qweight) : (const uint4*)nullptr,
+                               rw ? (const void*)rw->sb : (const void*)nullptr, rsh, rw ? m->hidden / rw->group_size : 0, x_dev,
+                               logits_dev, m->logits, m->ids, m->wts, m->act, m->dpart, out_dev, m->bar, status, m->num_experts,
+                               m->hidden, m->inter, m->top_k, m->norm_topk, sh, m->group_size));
   return GOPH_OK;
 }
 
@@ -916,6 +1177,8 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
   if (!m->router) return fail(GOPH_E_INVALID, "MoE layer has no router weight");
   if (int rc = use_device(m->device)) return rc;
   const goph_mlx_weight* rw = m->router;
+  MoeTokenKernel tk = nullptr;
+  if (tokens == 1 && moe_token_form(m, rw, &tk)) return moe_run_token(m, tk, out_dev, x_dev, rw, nullptr, (cudaStream_t)stream);
   if (rw->qweight && rw->sb && rw->group_size >= 32 && !(rw->group_size & (rw->group_size - 1)) && rw->in_dim % 32 == 0) {
     // row-major router (the usual case: it is small): one launch for all tokens
     int sh = 0;
@@ -942,6 +1205,8 @@ GOPH_API int goph_moe_forward_logits(goph_moe_layer* m, float* out_dev, uint64_t
   if (int rc = moe_check_io(m, out_dev, out_len, x_dev, x_len, tokens)) return rc;
   if (!logits_dev || logits_len < (uint64_t)tokens * m->num_experts) return fail(GOPH_E_INVALID, "router logits buffer too short");
   if (int rc = use_device(m->device)) return rc;
+  MoeTokenKernel tk = nullptr;
+  if (tokens == 1 && moe_token_form(m, nullptr, &tk)) return moe_run_token(m, tk, out_dev, x_dev, nullptr, logits_dev, (cudaStream_t)stream);
   return moe_run(m, out_dev, x_dev, logits_dev, tokens, (cudaStream_t)stream);
 }
 
@@ -954,3 +1219,9 @@ GOPH_API int goph_moe_last_routing(goph_moe_layer* m, int tokens, int* ids_host,
   GOPH_CUDA(cudaMemcpy(weights_host, m->wts, (size_t)tokens * m->top_k * sizeof(float), cudaMemcpyDeviceToHost));
   return GOPH_OK;
 }
+
+#ifdef GOPH_TUNING
+GOPH_API int goph_tuning_probe_moe(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_moe_trace, 16 * sizeof(long long)) == cudaSuccess ? 0 : -1;
+}
+#endif

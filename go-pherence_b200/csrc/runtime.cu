@@ -163,6 +163,8 @@ GOPH_API int goph_set_option(const char* name, int value) {
   } else if (!strcmp(name, "mlx_layout")) {
     if (value < 0 || value > 2) return fail(GOPH_E_INVALID, "mlx_layout=%d not in 0..2", value);
     o.mlx_layout = value;
+  } else if (!strcmp(name, "moe_fused")) {
+    o.moe_fused = value ? 1 : 0;
   } else if (!strcmp(name, "moe_rows")) {
     if (value != 0 && value != 2 && value != 4) return fail(GOPH_E_INVALID, "moe_rows=%d not 0, 2 or 4", value);
     o.moe_rows = value;

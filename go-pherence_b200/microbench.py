@@ -143,6 +143,10 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
     rt.init(0)
+    tune = dict((k, v) for k, v in opts if k.startswith("tune_"))
+    opts = [(k, v) for k, v in opts if not k.startswith("tune_")]
+    if tune:  # tuning build only
+        rt.lib().goph_tuning_set_gemv(int(tune.get("tune_gemv", 0)))
     for k, v in opts:
         rt.SetOption(k, v)
     rt.SetOption("mlx_layout", 1)
@@ -188,6 +192,21 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
                 mods[i % layers].Forward(ob, xb, tokens, torch.cuda.current_stream())
     graph.replay()
     torch.cuda.synchronize()
+    trace = None
+    if hasattr(rt.lib(), "goph_tuning_probe_gemv"):  # tuning build: timeline of one CTA of the last tensor-core launch
+        import ctypes
+        buf = (ctypes.c_longlong * 512)()
+        rt.lib().goph_tuning_probe_gemv(buf)
+        t0 = buf[7 * 64]
+        names = ["loads_issued", "mma_sees_stage", "mma_issued", "conv_starts", "conv_done", "epi_sees_unit0", "epi_done"]
+        trace = {"entry": buf[7 * 64 + 3] - t0, "end": buf[7 * 64 + 1] - t0}
+        for e, n in enumerate(names):
+            trace[n] = [buf[e * 64 + i] - t0 for i in range(40) if buf[e * 64 + i]]
+    if hasattr(rt.lib(), "goph_tuning_probe_moe") and tokens == 1 and expert_layout == 1:
+        import ctypes
+        buf = (ctypes.c_longlong * 16)()
+        rt.lib().goph_tuning_probe_moe(buf)
+        trace = {"one_launch_phase_ends": [buf[i] - buf[0] for i in range(1, 9)]}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = 1 if eager else 5
     e0.record()
@@ -205,7 +224,7 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
     gbs = nbytes / us / 1e3
     return {"format": "moe-mlx4", "tokens": tokens, "experts": experts, "top_k": top_k, "hidden": hidden, "inter": inter,
             "distinct_experts_per_call": sum(distinct) / layers, "us_per_call": round(us, 2), "GBps": round(gbs, 1),
-            "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes}
+            "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes, "trace": trace}
 
 
 def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts=(), qdim=0, as_list=False):

@@ -115,6 +115,9 @@ int goph_sm_count(int device);
  *   "mlx_cluster" 1 (default): K splits that all run at once are launched as thread-block clusters and
  *                 add their partial sums through shared memory; 0: always through device scratch
  *                 and an atomic counter.  Same bits either way
+ *   "moe_fused"   1 (default): an MoE call of one token on row-major experts runs as ONE cooperative
+ *                 launch (router, routing, gate|up, down and the weighted sum as phases between
+ *                 grid-wide barriers); 0: the launches that serve any number of tokens.  Same bits
  *   "moe_rows"    MoE layers whose experts are in the tiled layout: (token, slot) items per work
  *                 entry of the grouped tensor-core launches, 2 or 4; 0 (default) = two while the
  *                 call has at most two items per expert on average, else four.  Same bits either way

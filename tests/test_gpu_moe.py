@@ -231,6 +231,49 @@ def test_results_do_not_depend_on_scheduling(gpu, pkg):
     L.free()
 
 
+@pytest.mark.parametrize("experts,hidden,inter,top_k,resident", [
+    (6, 128, 256, 2, None),
+    (16, 512, 256, 4, None),
+    (128, 2048, 768, 8, None),
+    (32, 512, 256, 8, set(range(0, 32, 2))),    # half of the experts live elsewhere
+    (5, 256, 128, 9, None),                      # top_k clamped to the expert count
+])
+def test_one_token_single_launch_form(gpu, pkg, experts, hidden, inter, top_k, resident):
+    # a call of one token runs as one cooperative launch; option moe_fused = 0 keeps the five launches.
+    # Same bits, call after call (the grid barrier's counter carries over), with and without the router.
+    L = Layer(gpu, pkg.synth, "one", experts, hidden, inter, 64, top_k, True, resident=resident)
+    g = pkg.synth.rng("one-token", experts)
+    for rep in range(3):
+        x = pkg.synth.activations(("one", experts, rep), hidden).reshape(1, hidden)
+        n0 = gpu.LaunchCount()
+        got, ids, wts = run_forward(L, x, 1)
+        assert gpu.LaunchCount() - n0 == 1
+        gpu.SetOption("moe_fused", 0)
+        try:
+            n0 = gpu.LaunchCount()
+            ref, ids2, wts2 = run_forward(L, x, 1)
+            assert gpu.LaunchCount() - n0 == 5
+        finally:
+            gpu.SetOption("moe_fused", 1)
+        assert np.array_equal(ids, ids2) and np.array_equal(wts.view(np.uint32), wts2.view(np.uint32))
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+        res = [e for e in ids[0] if e >= 0 and (resident is None or e in resident)]
+        keep = np.array([k for k, e in enumerate(ids[0]) if e in res], dtype=np.int64)
+        want = L.oracle(x[0], ids[0][keep], wts[0][keep]) if len(keep) else np.zeros(hidden, dtype=F)
+        assert pkg.synth.rel_err(got[0], want) <= TOL
+        # routing supplied by the caller (two barriers instead of three in the same launch)
+        logits = (g.standard_normal((1, experts), dtype=F) * F(2)).astype(F)
+        got_l, ids_l, wts_l = run_forward(L, x, 1, logits)
+        want_ids, want_w = orc.moe_route(logits[0], top_k, True)
+        assert list(ids_l[0]) == list(want_ids)
+        assert np.array_equal(wts_l[0].view(np.uint32), want_w.view(np.uint32))
+    logits = np.zeros((1, experts), dtype=F)
+    logits[0, 1] = np.nan                       # the softmax fails: no expert runs, the output is zero
+    got, ids, _ = run_forward(L, x, 1, logits)
+    assert np.all(ids[0] == -1) and np.all(got[0] == 0)
+    L.free()
+
+
 def test_malformed(gpu, pkg):
     rt = gpu
     with pytest.raises(rt.GophError):
