@@ -120,7 +120,7 @@ int goph_sm_count(int device);
  *                 grid-wide barriers); 0: the launches that serve any number of tokens.  Same bits
  *   "moe_rows"    MoE layers whose experts are in the tiled layout: (token, slot) items per work
  *                 entry of the grouped tensor-core launches, 2 or 4; 0 (default) = two while the
- *                 call has at most two items per expert on average, else four.  Same bits either way
+ *                 call has fewer than two items per expert on average, else four.  Same bits either way
  *   "mlx_unpack"  nibble→f32 method of the batch-1 MLX kernel: 0 one shift per nibble,
  *                 (default), 1 one shift per nibble pair, 2 integer conversion
  *   "mlx_rows" / "gguf_rows" / "fp8_rows"  rows a warp streams at once: 1, 2, 4, or 0 = by size
