@@ -219,6 +219,15 @@ moe_router_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, cons
 // exponentials are taken in parallel, the sum by one thread in index order, the k rounds of
 // "largest probability not yet picked, lowest id on ties" by a warp over shared memory.  The last
 // CTA to finish groups the (token, slot) items by expert into the work list.
+// Tuning build only: CTA 1 records the clock at the phase boundaries of the one-launch form.
+#ifdef GOPH_TUNING
+__device__ long long g_moe_trace[24];
+#define MTP(k) if (blockIdx.x == 1 && threadIdx.x == 0) g_moe_trace[k] = clock64();
+#define RTP(k) if (blockIdx.x == 1 && threadIdx.x == 0) g_moe_trace[k] = clock64();
+#else
+#define MTP(k)
+#define RTP(k)
+#endif
 struct MoeRouteShared {
   float sp[kMoeMaxExperts];
   float mx, inv;
@@ -233,6 +242,7 @@ __device__ __forceinline__ void moe_route_token(const float* __restrict__ lg, in
   float* sp = sh.sp;
   for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __ldcg(lg + i);
   __syncthreads();
+  RTP(16)
   if (tid < 32) {
     float mx = -INFINITY;
     for (int i = lane; i < num_experts; i += 32) mx = fmaxf(mx, sp[i]);  // skips NaN, as "x > mx" does
@@ -243,19 +253,80 @@ __device__ __forceinline__ void moe_route_token(const float* __restrict__ lg, in
     if (lane == 0) sh.mx = mx;
   }
   __syncthreads();
+  RTP(17)
   for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = (float)exp((double)(sp[i] - sh.mx));
   __syncthreads();
+  RTP(18)
   if (tid == 0) {
     float sum = 0.f;
-    for (int i = 0; i < num_experts; ++i) sum = __fadd_rn(sum, sp[i]);
+    // index order, one rounding per element; the loads of a batch are issued together
+    for (int i0 = 0; i0 < num_experts; i0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = i0 + j < num_experts ? sp[i0 + j] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (i0 + j < num_experts) sum = __fadd_rn(sum, v[j]);
+    }
     sh.ok = !(sum == 0.f || isnan(sum) || isinf(sum));  // SoftmaxInPlace fails: no expert runs
     sh.inv = __fdiv_rn(1.f, sum);
   }
   __syncthreads();
+  RTP(19)
   if (sh.ok)
     for (int i = tid; i < num_experts; i += blockDim.x) sp[i] = __fmul_rn(sp[i], sh.inv);
   __syncthreads();
-  if (tid < 32) {
+  RTP(20)
+  if (tid < 32 && num_experts <= 128 && top_k <= 32) {
+    // The usual sizes: a lane keeps its four candidates in registers over the rounds, lane k keeps
+    // the k-th pick, and the picks are normalised and stored by their lanes at the end.  Same picks
+    // (largest probability, lowest id on ties) and the same additions, in the same order, as the
+    // general form below.
+    // A probability p >= 0 becomes the key bits(p) + 1, which orders as p does; 0 marks "none" or
+    // "already picked".  A round = the largest key of the warp, then the lowest index that holds it.
+    uint32_t key[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p = lane + 32 * i < num_experts ? sp[lane + 32 * i] : -1.f;
+      key[i] = p >= 0.f ? __float_as_uint(p) + 1u : 0u;  // a NaN cannot be here: the sum would have failed
+    }
+    int n = 0, sel_id = -1;
+    float wsum = 0.f, sel_w = 0.f;
+    const bool ok = sh.ok != 0;
+    for (int k = 0; k < top_k && ok; ++k) {
+      uint32_t mine = 0u;
+      int at = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (key[i] > mine) {
+          mine = key[i];
+          at = i;
+        }
+      }
+      const uint32_t top = __reduce_max_sync(0xffffffffu, mine);
+      if (top == 0u) break;  // nothing left to pick, in this round and after it
+      const int best = (int)__reduce_min_sync(0xffffffffu, mine == top ? (uint32_t)(lane + 32 * at) : 0x7fffffffu);
+      const float bs = __uint_as_float(top - 1u);
+      if (lane == n) {
+        sel_id = best;
+        sel_w = bs;
+      }
+      if ((best & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if ((best >> 5) == i) key[i] = 0u;
+      }
+      wsum = __fadd_rn(wsum, bs);
+      ++n;
+    }
+    if (lane < top_k) {
+      const bool have = lane < n;
+      float w = have ? sel_w : 0.f;
+      if (have && norm_topk && wsum > 0.f) w = __fdiv_rn(w, wsum);
+      my_ids[lane] = have ? sel_id : -1;
+      my_w[lane] = w;
+    }
+  } else if (tid < 32) {
     int n = 0;
     float wsum = 0.f;
     for (int k = 0; k < top_k; ++k) {
@@ -664,13 +735,6 @@ moe_combine_kernel(MoeTables tb, const float* __restrict__ dpart, const int* __r
 // (one releasing add per CTA, one polling thread per CTA, bounded; a wait that runs out records
 // 700 + the barrier's number in the status word and the CTA returns).
 constexpr long long kMoeBarrierTimeoutCycles = 2000000000LL;  // about a second
-// Tuning build only: CTA 1 records the clock at the phase boundaries of the one-launch form.
-#ifdef GOPH_TUNING
-__device__ long long g_moe_trace[16];
-#define MTP(k) if (blockIdx.x == 1 && threadIdx.x == 0) g_moe_trace[k] = clock64();
-#else
-#define MTP(k)
-#endif
 template <bool RSB_BF16, bool SB_BF16>
 __global__ void __launch_bounds__(kMoeThreads, 2)
 moe_token_kernel(MoeTables tb, const uint4* __restrict__ rw, const void* __restrict__ rsb, int r_shift, int r_groups,
@@ -1223,6 +1287,6 @@ GOPH_API int goph_moe_last_routing(goph_moe_layer* m, int tokens, int* ids_host,
 
 #ifdef GOPH_TUNING
 GOPH_API int goph_tuning_probe_moe(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_moe_trace, 16 * sizeof(long long)) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out16, g_moe_trace, 24 * sizeof(long long)) == cudaSuccess ? 0 : -1;
 }
 #endif

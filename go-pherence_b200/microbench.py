@@ -204,9 +204,10 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
             trace[n] = [buf[e * 64 + i] - t0 for i in range(40) if buf[e * 64 + i]]
     if hasattr(rt.lib(), "goph_tuning_probe_moe") and tokens == 1 and expert_layout == 1:
         import ctypes
-        buf = (ctypes.c_longlong * 16)()
+        buf = (ctypes.c_longlong * 24)()
         rt.lib().goph_tuning_probe_moe(buf)
-        trace = {"one_launch_phase_ends": [buf[i] - buf[0] for i in range(1, 9)]}
+        trace = {"one_launch_phase_ends": [buf[i] - buf[0] for i in range(1, 9)],
+                 "routing_points": [buf[i] - buf[0] for i in range(16, 21)]}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = 1 if eager else 5
     e0.record()
