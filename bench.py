@@ -401,6 +401,11 @@ def extras(tensor_peak):
                     "x": r["x"], "us_per_launch": r["us_per_launch"], "frac_of_hbm_peak": r["frac_of_hbm_peak"],
                     "tflops": r["tflops"], "frac_of_bf16_tensor_peak": round(r["tflops"] / tensor_peak, 4)}
     out["llama3_70b_small_m"] = small
+    # the work-list GGUF products over stacked experts (Q4_K gate|up with GELU, Q8_0 down with scatter-add)
+    out["gguf_work_list_stacked_experts"] = {
+        "T=%d" % t: {k: v for k, v in mb.run_gguf_work(t, launches=10).items()
+                     if k in ("items", "us_per_call", "GBps", "frac_of_hbm_peak", "distinct_experts_per_call")}
+        for t in (1, 8, 32)}
     # experts row-major (CUDA-core expert kernels) and tiled (grouped launches of the tensor-core kernel)
     for name, layout in (("qwen3_30b_a3b_moe_layer", 1), ("qwen3_30b_a3b_moe_layer_tiled_experts", 2)):
         out[name] = {

@@ -15,6 +15,7 @@
 #include <mutex>
 
 #include "goph_internal.cuh"
+#include "gguf_fmt.cuh"
 
 namespace goph {
 namespace {
@@ -149,6 +150,226 @@ scatter_by_work_kernel(WorkView v, const float* __restrict__ x, const uint32_t* 
   if (lane == 0) atomicAdd(dst + at, y * work_weight[w]);  // items may share a destination row
 }
 
+// ---- streaming layouts: the expert's rows once per four of its items ---------------------------
+constexpr int kMaxWorkItems = 1024;  // items a CTA can collect for its expert
+constexpr int kWorkM = 4;            // items per pass over the expert's rows
+
+struct WorkArgs {
+  const uint32_t* experts;  // [work_len] or nullptr (one expert)
+  const uint32_t* pos;      // scatter: destination row of an item
+  const float* weight;      // scatter: weight of an item
+  int work_len, active_experts;
+  int expert_rows;          // rows of one expert in the matrix (gate|up: 2 * inter)
+  int inter;                // gate|up: rows of gate (and of up)
+  float* out;               // gate|up: [work_len][inter]; scatter: dst
+  unsigned long long dst_len;
+  int* status;
+};
+
+// One pass over the expert's rows for the items s_items[base .. base + m_now), m_now <= M.
+// MODE 0: out[w][i] = gelu(gate_i . x_w) * (up_i . x_w); MODE 1: dst[pos[w]][r] += weight[w] * (W_e[r] . x_w)
+template <class F, int MODE, int M>
+__device__ __forceinline__ void work_pass(const StreamArgs& a, const WorkArgs& wa, int e, const unsigned short* s_items, int base,
+                                          int m_now, unsigned char* smem_raw) {
+  constexpr int S = F::kSlots, R = 2;
+  float4* xs = reinterpret_cast<float4*>(smem_raw);
+  float2* xc = reinterpret_cast<float2*>(smem_raw + (size_t)M * a.iters * S * 32 * 16);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int iters = a.iters;
+  // a task = two rows of the expert: gate row i and up row i, or two adjacent rows
+  const int tasks = MODE == 0 ? wa.inter : (wa.expert_rows + 1) / 2;
+  const int task_stride = gridDim.x * kGWarps;
+  const int row0 = e * wa.expert_rows;
+  int task = blockIdx.x * kGWarps + warp, it = 0;
+  typename F::Row cur[R], nxt[R];
+  auto load_tile = [&](int t, int i, typename F::Row (&dst)[R]) {
+    int unit = i * 32 + lane;
+    if (unit >= a.units) unit = a.units - 1;  // the staged x is zero there
+    int row[R];
+    if (MODE == 0) {
+      row[0] = row0 + t;
+      row[1] = row0 + wa.inter + t;
+    } else {
+      row[0] = row0 + 2 * t;
+      row[1] = row0 + min(2 * t + 1, wa.expert_rows - 1);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) F::load(a, row[r], unit, dst[r]);
+  };
+  const bool has_work = task < tasks;
+  if (has_work) load_tile(task, 0, cur);  // first weights in flight while the activations are staged
+  {
+    const int per_m = iters * S * 32, total = M * per_m;
+    for (int idx = threadIdx.x; idx < total; idx += kGThreads) {
+      const int m = idx / per_m, rem = idx - m * per_m;
+      const int i = rem / (S * 32), slot = (rem >> 5) % S, l = rem & 31, unit = i * 32 + l;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (m < m_now && unit < a.units)
+        v = __ldg(reinterpret_cast<const float4*>(a.x + (size_t)s_items[base + m] * a.in_dim + (size_t)unit * (S * 4) + slot * 4));
+      xs[idx] = v;
+    }
+    __syncthreads();
+    if (F::kHasConsts) {
+      const int nsum = M * iters * 32;
+      for (int idx = threadIdx.x; idx < nsum; idx += kGThreads) {
+        const int mi = idx >> 5, l = idx & 31;
+        float se = 0.f, so = 0.f;
+#pragma unroll
+        for (int sl = 0; sl < S; ++sl) {
+          const float4 v = xs[(mi * S + sl) * 32 + l];
+          se += v.x + v.z;
+          so += v.y + v.w;
+        }
+        xc[idx] = F::consts(se, so);
+      }
+      __syncthreads();
+    }
+  }
+  if (!has_work) return;
+  float acc[R][M];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+  while (true) {
+    int ntask = task, nit = it + 1;
+    if (nit == iters) {
+      nit = 0;
+      ntask = task + task_stride;
+    }
+    const bool more = ntask < tasks;
+    if (more) load_tile(ntask, nit, nxt);
+    float4 xv[M][S];
+    float2 c[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+#pragma unroll
+      for (int sl = 0; sl < S; ++sl) xv[m][sl] = xs[((size_t)(m * iters + it) * S + sl) * 32 + lane];
+      c[m] = F::kHasConsts ? xc[(m * iters + it) * 32 + lane] : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) F::template dot<M>(cur[r], xv, c, acc[r]);
+    if (it == iters - 1) {
+      float v[R][M];
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          v[r][m] = warp_sum(acc[r][m]);
+          acc[r][m] = 0.f;
+        }
+      if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          if (m >= m_now) continue;
+          const int w = s_items[base + m];
+          if (MODE == 0) {
+            wa.out[(size_t)w * wa.inter + task] = gelu_tanh(v[0][m]) * v[1][m];
+          } else {
+            const float wt = wa.weight[w];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const int lr = 2 * task + r;
+              if (lr >= wa.expert_rows) continue;
+              const unsigned long long at = (unsigned long long)wa.pos[w] * (unsigned long long)wa.expert_rows + (unsigned long long)lr;
+              if (at < wa.dst_len) atomicAdd(wa.out + at, v[r][m] * wt);  // items may share a destination row
+              else atomicCAS(wa.status, 0, 602);
+            }
+          }
+        }
+      }
+    }
+    if (!more) break;
+#pragma unroll
+    for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+    task = ntask;
+    it = nit;
+  }
+}
+
+// grid (row blocks, Y).  BY_ITEM (lists shorter than the number of experts): Y = items, and the CTAs
+// of an item work for its expert if the item is the first of that expert in the list, else return;
+// otherwise Y = experts.  Either way a CTA collects all items of its expert and passes over the
+// expert's rows once per four of them.
+template <class F, int MODE, bool BY_ITEM>
+__global__ void __launch_bounds__(kGThreads)
+stream_work_kernel(const __grid_constant__ StreamArgs a, const __grid_constant__ WorkArgs wa) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int s_n, s_dup;
+  __shared__ unsigned short s_items[kMaxWorkItems];
+  if (threadIdx.x == 0) s_n = s_dup = 0;
+  __syncthreads();
+  uint32_t e = blockIdx.y;
+  if (BY_ITEM) {
+    e = wa.experts ? wa.experts[blockIdx.y] : 0u;
+    if (e >= (uint32_t)wa.active_experts) {
+      if (threadIdx.x == 0 && blockIdx.x == 0) atomicCAS(wa.status, 0, 601);
+      return;
+    }
+    for (int w = threadIdx.x; w < (int)blockIdx.y; w += kGThreads)
+      if ((wa.experts ? wa.experts[w] : 0u) == e) s_dup = 1;
+    __syncthreads();
+    if (s_dup) return;  // an earlier item's CTAs work for this expert
+  }
+  for (int w = threadIdx.x; w < wa.work_len; w += kGThreads) {
+    const uint32_t we = wa.experts ? wa.experts[w] : 0u;
+    if (we == e) s_items[atomicAdd(&s_n, 1)] = (unsigned short)w;
+    else if (!BY_ITEM && we >= (uint32_t)wa.active_experts && e == 0 && blockIdx.x == 0) atomicCAS(wa.status, 0, 601);
+  }
+  __syncthreads();
+  const int n = s_n;
+  if (n == 1) {
+    work_pass<F, MODE, 1>(a, wa, (int)e, s_items, 0, 1, smem_raw);
+  } else if (n == 2) {
+    work_pass<F, MODE, 2>(a, wa, (int)e, s_items, 0, 2, smem_raw);
+  } else {
+    for (int base = 0; base < n; base += kWorkM) {
+      if (base) __syncthreads();  // every warp is done with the items before
+      work_pass<F, MODE, kWorkM>(a, wa, (int)e, s_items, base, min(kWorkM, n - base), smem_raw);
+    }
+  }
+}
+
+// Launches the grouped form when the matrix is in a streaming layout and the list fits; false = not taken.
+template <int MODE>
+bool launch_stream_work(const goph_gguf_matrix* m, const float* x, const WorkArgs& wa, cudaStream_t stream, int* rc) {
+  if (!m->data || wa.work_len > kMaxWorkItems) return false;
+  StreamArgs a;
+  memset(&a, 0, sizeof a);
+  a.w = m->data;
+  a.aux = m->d16;
+  a.x = x;
+  a.rows = m->out_dim;
+  a.in_dim = m->in_dim;
+  const bool q4 = m->qtype == GOPH_GGUF_Q4_K;
+  a.units = q4 ? m->in_dim / 32 : m->in_dim / 16;
+  a.iters = (a.units + 31) / 32;
+  a.row_bytes = q4 ? m->in_dim / 256 * 144 : m->in_dim;
+  a.x_aligned = 1;
+  if (q4 && m->in_dim % 256) return false;
+  const size_t smem = q4 ? stream_smem_bytes<Q4KFmt>(kWorkM, a.iters) : stream_smem_bytes<Q80Fmt>(kWorkM, a.iters);
+  if (smem > (size_t)kSmemBudget) return false;
+  const bool by_item = wa.work_len < wa.active_experts;
+  auto kern = q4 ? (by_item ? stream_work_kernel<Q4KFmt, MODE, true> : stream_work_kernel<Q4KFmt, MODE, false>)
+                 : (by_item ? stream_work_kernel<Q80Fmt, MODE, true> : stream_work_kernel<Q80Fmt, MODE, false>);
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    *rc = fail_cuda(cudaGetLastError(), "cudaFuncSetAttribute(work-list kernel)");
+    return true;
+  }
+  const int tasks = MODE == 0 ? wa.inter : (wa.expert_rows + 1) / 2;
+  const int live = wa.active_experts < wa.work_len ? wa.active_experts : wa.work_len;  // experts that can have items
+  const int sms = device_state(m->device).sm_count;
+  int gx = (4 * sms + live - 1) / live;
+  const int max_gx = (tasks + kGWarps - 1) / kGWarps;
+  if (gx > max_gx) gx = max_gx;
+  if (gx < 1) gx = 1;
+  note_launch();
+  kern<<<dim3(gx, by_item ? wa.work_len : wa.active_experts), kGThreads, smem, stream>>>(a, wa);
+  cudaError_t e = cudaGetLastError();
+  *rc = e == cudaSuccess ? GOPH_OK : fail_cuda(e, "work-list kernel launch");
+  return true;
+}
+
 int* work_status(int device) {
   static int* words[kMaxDevices] = {};
   static std::mutex mu;
@@ -223,6 +444,19 @@ GOPH_API int goph_gguf_gate_up_gelu_by_work(float* out_dev, uint64_t out_len, co
   if (int rc = use_device(m->device)) return rc;
   int* status = work_status(m->device);
   if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the work-list kernels' status word");
+  {
+    WorkArgs wa;
+    memset(&wa, 0, sizeof wa);
+    wa.experts = work_experts_dev;
+    wa.work_len = work_len;
+    wa.active_experts = active_experts;
+    wa.expert_rows = 2 * intermediate;
+    wa.inter = intermediate;
+    wa.out = out_dev;
+    wa.status = status;
+    int rc = GOPH_OK;
+    if (launch_stream_work<0>(m, x_dev, wa, (cudaStream_t)stream, &rc)) return rc;
+  }
   note_launch();
   gate_up_gelu_kernel<<<dim3((intermediate + kWarps - 1) / kWarps, work_len), kWarps * 32, 0, (cudaStream_t)stream>>>(
       view_of(m), x_dev, work_experts_dev, active_experts, intermediate, out_dev, status);
@@ -257,6 +491,21 @@ GOPH_API int goph_gguf_scatter_by_work(float* dst_dev, uint64_t dst_len, const f
   int* status = work_status(m->device);
   if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the work-list kernels' status word");
   const int expert_out = m->out_dim / active_experts;
+  {
+    WorkArgs wa;
+    memset(&wa, 0, sizeof wa);
+    wa.experts = work_active_dev;
+    wa.pos = work_pos_dev;
+    wa.weight = work_weight_dev;
+    wa.work_len = work_len;
+    wa.active_experts = active_experts;
+    wa.expert_rows = expert_out;
+    wa.out = dst_dev;
+    wa.dst_len = (unsigned long long)dst_len;
+    wa.status = status;
+    int rc = GOPH_OK;
+    if (launch_stream_work<1>(m, x_dev, wa, (cudaStream_t)stream, &rc)) return rc;
+  }
   note_launch();
   scatter_by_work_kernel<<<dim3((expert_out + kWarps - 1) / kWarps, work_len), kWarps * 32, 0, (cudaStream_t)stream>>>(
       view_of(m), x_dev, work_active_dev, work_pos_dev, work_weight_dev, active_experts, expert_out, dst_dev,

@@ -228,6 +228,75 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes, "trace": trace}
 
 
+def run_gguf_work(tokens, experts=128, hidden=2048, inter=768, top_k=8, launches=20, layout=1):
+    """The work-list GGUF products of an MoE layer whose experts are stacked in one matrix: fused gate|up
+    (Q4_K) with tanh-GELU by work list, then the weighted scatter-add of the down projection (Q8_0) by
+    work list, `tokens * top_k` items with experts drawn like a routing (distinct per token).  Two work
+    lists alternate, so a call does not find its experts in L2.  Bytes counted: gate|up and down rows of
+    every distinct expert of a call."""
+    import numpy as np
+    import torch
+    pkg = load_package()
+    rt, syn = pkg.runtime, pkg.synth
+    rt.init(0)
+    rt.SetOption("gguf_layout", layout)
+    try:
+        gu = rt.UploadGGUFMatrix(rt.GGUF_Q4_K, syn.q4k_matrix("work-gu", experts * 2 * inter, hidden), hidden, experts * 2 * inter)
+        dn = rt.UploadGGUFMatrix(rt.GGUF_Q8_0, syn.q8_0_matrix("work-dn", experts * hidden, inter), inter, experts * hidden)
+    finally:
+        rt.SetOption("gguf_layout", 0)
+    g = syn.rng("work-lists", tokens)
+    n = tokens * top_k
+    lists, distinct = [], []
+    for _ in range(2):
+        ex = np.concatenate([g.choice(experts, size=top_k, replace=False) for _ in range(tokens)]).astype(np.uint32)
+        pos = np.repeat(np.arange(tokens, dtype=np.uint32), top_k)
+        wt = g.uniform(0.05, 0.2, n).astype(np.float32)
+        lists.append(tuple(rt.from_numpy(a) for a in (ex, pos, wt)))
+        distinct.append(len(set(ex.tolist())))
+    x = np.repeat(syn.activations("work-x", tokens * hidden).reshape(tokens, hidden), top_k, axis=0).reshape(-1)  # one row per item
+    xb = rt.from_numpy(x)
+    act = rt.Malloc(n * inter)
+    out = rt.Malloc(tokens * hidden)
+    stream = torch.cuda.current_stream()
+
+    def call(i):
+        ex, pos, wt = lists[i % 2]
+        rt.GateUpGELUQ4KByWorkToBuffer(act, xb, ex, n, inter, experts, gu, stream)
+        rt.GemvQ8_0ScatterByWork(out, act, ex, pos, wt, n, experts, dn, stream)
+
+    call(0)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        stream = torch.cuda.current_stream()
+        for i in range(launches):
+            call(i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (launches * reps)
+    per_expert = 2 * inter * hidden * 144 / 256 + hidden * inter * 34 / 32
+    nbytes = sum(distinct) / 2 * per_expert
+    peak = 6650.0
+    pk = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        peak = float(json.load(open(pk))["hbm_gbs"])
+    status = rt.KernelStatus()
+    for t in (gu, dn, xb, act, out):
+        t.Free()
+    return {"format": "gguf-work q4_k gate|up + q8_0 down", "tokens": tokens, "items": n, "layout": layout,
+            "distinct_experts_per_call": sum(distinct) / 2, "us_per_call": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+            "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 4), "bytes": nbytes, "kernel_status": status}
+
+
 def run_layer_chain(fmt, hidden=4096, ffn=14336, kv=1024, layers=8, reps=5, opts=(), qdim=0, as_list=False):
     """The projections of decoder layers (Llama-3-8B shapes by default) as one dependent chain, batch 1:
     q|k|v (qdim+2kv x hidden) -> o (hidden x qdim, fed by the first `qdim` outputs) ->
@@ -372,7 +441,7 @@ def main():
     ap.add_argument("--eager", action="store_true", help="--format moe: plain launches instead of a CUDA graph")
     ap.add_argument("--expert-layout", type=int, default=1, choices=[1, 2], help="--format moe: 1 row-major experts, 2 tiled")
     ap.add_argument("--layer-chain", action="store_true", help="decoder-layer projections at Llama-3-8B shapes as a dependent chain")
-    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q5k", "q6k", "q8_0", "fp8", "moe"])
+    ap.add_argument("--format", default="mlx4", choices=["mlx4", "q4k", "q5k", "q6k", "q8_0", "fp8", "moe", "gguf-work"])
     ap.add_argument("--out", type=int, default=4096)
     ap.add_argument("--in", dest="in_dim", type=int, default=4096)
     ap.add_argument("--batch", type=int, default=1)
@@ -396,6 +465,9 @@ def main():
     if args.layer_chain:
         print(json.dumps(run_layer_chain(args.format, args.hidden, args.ffn, args.kv, args.layers, opts=opts, qdim=args.qdim,
                                          as_list=args.list)))
+        return
+    if args.format == "gguf-work":
+        print(json.dumps(run_gguf_work(args.tokens, launches=min(args.launches, 20), layout=args.expert_layout)))
         return
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts, expert_layout=args.expert_layout, eager=args.eager,

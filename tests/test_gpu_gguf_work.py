@@ -132,6 +132,57 @@ def test_scatter_by_work_and_batch_scatter(gpu, pkg, qtype, layout):
         t.Free()
 
 
+@pytest.mark.parametrize("layout", [1, 2])
+@pytest.mark.parametrize("qtype", [Q4_K, Q8_0])
+@pytest.mark.parametrize("active,experts", [
+    (3, [0, 2, 0, 1, 2, 0, 0, 2, 1, 0, 2, 1, 1]),   # five, four and four items: passes of four and one
+    (8, [3, 1, 3, 7, 1]),                            # fewer items than experts: the grid goes by item
+    (2, [1] * 9),                                    # one expert with nine items
+])
+def test_long_and_short_work_lists(gpu, pkg, qtype, layout, active, experts):
+    # both products on one list: every item against the single-expert products, as the reference's tests do
+    inter, hidden, tokens = 64, 256, 4
+    n = len(experts)
+    raw_gu = make(pkg, qtype, ("lgu", layout, active), active * 2 * inter, hidden)
+    raw_dn = make(pkg, qtype, ("ldn", layout, active), active * hidden, inter * 4)     # down: in_dim 256
+    gpu.SetOption("gguf_layout", layout)
+    try:
+        gu = gpu.UploadGGUFMatrix(qtype, raw_gu, hidden, active * 2 * inter)
+        dn = gpu.UploadGGUFMatrix(qtype, raw_dn, inter * 4, active * hidden)
+    finally:
+        gpu.SetOption("gguf_layout", 0)
+    x = pkg.synth.activations(("long", n), n * hidden, bf16=False)
+    xo, we, out = gpu.from_numpy(x), gpu.from_numpy(np.array(experts, dtype=np.uint32)), out_with_canary(gpu, n * inter)
+    gpu.GateUpGELUQ4KByWorkToBuffer(out, xo, we, n, inter, active, gu)
+    gpu.Sync()
+    got = read_and_check_canary(out, n * inter).reshape(n, inter)
+    rb = raw_gu.size // (active * 2 * inter)
+    for w, e in enumerate(experts):
+        y = orc.gguf_gemv(x[w * hidden:(w + 1) * hidden], raw_gu[e * 2 * inter * rb:(e + 1) * 2 * inter * rb], qtype, hidden, 2 * inter, nthreads=4)
+        want = (gelu_tanh(y[:inter]) * y[inter:].astype(np.float64)).astype(F)
+        assert pkg.synth.rel_err(got[w], want) <= TOL, (w, e)
+    # scatter-add of the down products into four destination rows
+    pos = np.arange(n, dtype=np.uint32) % tokens
+    wt = pkg.synth.rng("long-w", n).uniform(0.1, 0.5, n).astype(F)
+    h = pkg.synth.activations(("long-h", n), n * inter * 4, bf16=False)
+    ho, po, wo = gpu.from_numpy(h), gpu.from_numpy(pos), gpu.from_numpy(wt)
+    base = pkg.synth.activations("long-dst", tokens * hidden, bf16=False)
+    dst = gpu.from_numpy(np.concatenate([base, np.full(64, 123.0, dtype=F)]))
+    gpu.GemvQ8_0ScatterByWork(gpu.wrap(dst.Ptr, tokens * hidden * 4), ho, we, po, wo, n, active, dn)
+    gpu.Sync()
+    res = dst.Download()
+    assert np.all(res[tokens * hidden:] == F(123.0))
+    want = base.astype(np.float64).reshape(tokens, hidden).copy()
+    rb = raw_dn.size // (active * hidden)
+    for w, e in enumerate(experts):
+        y = orc.gguf_gemv(h[w * inter * 4:(w + 1) * inter * 4], raw_dn[e * hidden * rb:(e + 1) * hidden * rb], qtype, inter * 4, hidden, nthreads=4)
+        want[pos[w]] += np.float64(wt[w]) * y
+    assert pkg.synth.rel_err(res[:tokens * hidden], want.reshape(-1).astype(F)) <= TOL
+    assert gpu.KernelStatus() == 0
+    for t in (gu, dn, xo, we, out, ho, po, wo, dst):
+        t.Free()
+
+
 def test_work_calls_reject_malformed_arguments(gpu, pkg):
     raw = make(pkg, Q4_K, "bad", 128, 256)
     m = gpu.UploadGGUFMatrix(Q4_K, raw, 256, 128)
