@@ -228,6 +228,9 @@ def run_moe(tokens, experts=128, hidden=2048, inter=768, top_k=8, layers=4, laun
             "frac_of_hbm_peak": round(gbs / peak, 4), "bytes": nbytes, "trace": trace}
 
 
+_WORK_MATRICES = {}
+
+
 def run_gguf_work(tokens, experts=128, hidden=2048, inter=768, top_k=8, launches=20, layout=1):
     """The work-list GGUF products of an MoE layer whose experts are stacked in one matrix: fused gate|up
     (Q4_K) with tanh-GELU by work list, then the weighted scatter-add of the down projection (Q8_0) by
@@ -239,12 +242,16 @@ def run_gguf_work(tokens, experts=128, hidden=2048, inter=768, top_k=8, launches
     pkg = load_package()
     rt, syn = pkg.runtime, pkg.synth
     rt.init(0)
-    rt.SetOption("gguf_layout", layout)
-    try:
-        gu = rt.UploadGGUFMatrix(rt.GGUF_Q4_K, syn.q4k_matrix("work-gu", experts * 2 * inter, hidden), hidden, experts * 2 * inter)
-        dn = rt.UploadGGUFMatrix(rt.GGUF_Q8_0, syn.q8_0_matrix("work-dn", experts * hidden, inter), inter, experts * hidden)
-    finally:
-        rt.SetOption("gguf_layout", 0)
+    key = (experts, hidden, inter, layout)
+    if key not in _WORK_MATRICES:  # kept for the life of the process: several list lengths share the uploads
+        rt.SetOption("gguf_layout", layout)
+        try:
+            _WORK_MATRICES[key] = (
+                rt.UploadGGUFMatrix(rt.GGUF_Q4_K, syn.q4k_matrix("work-gu", experts * 2 * inter, hidden), hidden, experts * 2 * inter),
+                rt.UploadGGUFMatrix(rt.GGUF_Q8_0, syn.q8_0_matrix("work-dn", experts * hidden, inter), inter, experts * hidden))
+        finally:
+            rt.SetOption("gguf_layout", 0)
+    gu, dn = _WORK_MATRICES[key]
     g = syn.rng("work-lists", tokens)
     n = tokens * top_k
     lists, distinct = [], []
@@ -290,7 +297,7 @@ def run_gguf_work(tokens, experts=128, hidden=2048, inter=768, top_k=8, launches
     if os.path.exists(pk):
         peak = float(json.load(open(pk))["hbm_gbs"])
     status = rt.KernelStatus()
-    for t in (gu, dn, xb, act, out):
+    for t in (xb, act, out):
         t.Free()
     return {"format": "gguf-work q4_k gate|up + q8_0 down", "tokens": tokens, "items": n, "layout": layout,
             "distinct_experts_per_call": sum(distinct) / 2, "us_per_call": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
