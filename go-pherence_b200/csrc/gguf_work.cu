@@ -150,6 +150,35 @@ scatter_by_work_kernel(WorkView v, const float* __restrict__ x, const uint32_t* 
   if (lane == 0) atomicAdd(dst + at, y * work_weight[w]);  // items may share a destination row
 }
 
+// The streaming policies reading the tensor-core layouts instead (one stage per 128 rows x 256
+// elements, see mlx_mma.cu): the same 16 bytes per unit, found at the stage's addresses.  StreamArgs::w
+// is the tiled buffer, row_bytes the number of 256-element chunks of a row.
+struct Q4KTiledFmt : Q4KFmt {
+  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
+    const int s = unit & 7, r = row & 127;
+    const uint8_t* stg = a.w + ((size_t)(row >> 7) * a.row_bytes + (unit >> 3)) * kQ4KStage;
+    const uint4 h = __ldg(reinterpret_cast<const uint4*>(stg + 128 * 128 + r * 16));
+    t.q = ld_stream(reinterpret_cast<const uint4*>(stg + r * 128 + ((s ^ (r & 7)) << 4)));
+    const uint32_t f = q4k_field(h, s);
+    t.sd = __fmul_rn((float)(f & 63u), f16_bits_to_f32(h.x & 0xFFFFu));
+    t.md = __fmul_rn((float)(f >> 6), f16_bits_to_f32(h.x >> 16));
+  }
+};
+struct Q80TiledFmt : Q80Fmt {
+  static __device__ __forceinline__ void load(const StreamArgs& a, int row, int unit, Row& t) {
+    // unit = 16 elements: chunk, K step of 32, half of the step
+    const int half = unit & 1, step = (unit >> 1) & 7, r = row & 127;
+    const uint8_t* stg = a.w + ((size_t)(row >> 7) * a.row_bytes + (unit >> 4)) * kQ80Stage;
+    uint4 q = ld_stream(reinterpret_cast<const uint4*>(stg + step * 4096 + half * 2048 + (r >> 3) * 128 + (r & 7) * 16));
+    q.x ^= 0x80808080u;  // signed bytes here, q + 128 in the streaming layout the arithmetic expects
+    q.y ^= 0x80808080u;
+    q.z ^= 0x80808080u;
+    q.w ^= 0x80808080u;
+    t.q = q;
+    t.d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t*>(stg + 128 * 256 + r * 16 + step * 2)));
+  }
+};
+
 // ---- streaming layouts: the expert's rows once per four of its items ---------------------------
 constexpr int kMaxWorkItems = 1024;  // items a CTA can collect for its expert
 constexpr int kWorkM = 4;            // items per pass over the expert's rows
@@ -330,28 +359,32 @@ stream_work_kernel(const __grid_constant__ StreamArgs a, const __grid_constant__
   }
 }
 
-// Launches the grouped form when the matrix is in a streaming layout and the list fits; false = not taken.
+// Launches the grouped form when the list fits a CTA's item table; false = not taken.
+template <int MODE, class F>
+static void (*pick_work_kernel(bool by_item))(const StreamArgs, const WorkArgs) {
+  return by_item ? stream_work_kernel<F, MODE, true> : stream_work_kernel<F, MODE, false>;
+}
+
 template <int MODE>
 bool launch_stream_work(const goph_gguf_matrix* m, const float* x, const WorkArgs& wa, cudaStream_t stream, int* rc) {
-  if (!m->data || wa.work_len > kMaxWorkItems) return false;
+  if (wa.work_len > kMaxWorkItems || m->in_dim % 256) return false;
   StreamArgs a;
   memset(&a, 0, sizeof a);
-  a.w = m->data;
+  const bool q4 = m->qtype == GOPH_GGUF_Q4_K, tiled = m->tiled != nullptr;
+  a.w = tiled ? m->tiled : m->data;
   a.aux = m->d16;
   a.x = x;
   a.rows = m->out_dim;
   a.in_dim = m->in_dim;
-  const bool q4 = m->qtype == GOPH_GGUF_Q4_K;
   a.units = q4 ? m->in_dim / 32 : m->in_dim / 16;
   a.iters = (a.units + 31) / 32;
-  a.row_bytes = q4 ? m->in_dim / 256 * 144 : m->in_dim;
+  a.row_bytes = tiled ? m->in_dim / 256 : (q4 ? m->in_dim / 256 * 144 : m->in_dim);
   a.x_aligned = 1;
-  if (q4 && m->in_dim % 256) return false;
   const size_t smem = q4 ? stream_smem_bytes<Q4KFmt>(kWorkM, a.iters) : stream_smem_bytes<Q80Fmt>(kWorkM, a.iters);
   if (smem > (size_t)kSmemBudget) return false;
   const bool by_item = wa.work_len < wa.active_experts;
-  auto kern = q4 ? (by_item ? stream_work_kernel<Q4KFmt, MODE, true> : stream_work_kernel<Q4KFmt, MODE, false>)
-                 : (by_item ? stream_work_kernel<Q80Fmt, MODE, true> : stream_work_kernel<Q80Fmt, MODE, false>);
+  auto kern = q4 ? (tiled ? pick_work_kernel<MODE, Q4KTiledFmt>(by_item) : pick_work_kernel<MODE, Q4KFmt>(by_item))
+                 : (tiled ? pick_work_kernel<MODE, Q80TiledFmt>(by_item) : pick_work_kernel<MODE, Q80Fmt>(by_item));
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
     *rc = fail_cuda(cudaGetLastError(), "cudaFuncSetAttribute(work-list kernel)");
     return true;

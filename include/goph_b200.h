@@ -249,9 +249,8 @@ int goph_gguf_gate_up_gelu(float* out_dev, uint64_t out_len, const float* x_dev,
  * 2 x intermediate rows (gate rows, then up rows); work item w multiplies x[w] by the slab of expert
  * work_experts_dev[w] (u32, device memory).  An index >= active_experts is skipped and sets the kernel
  * status word to 601.  (The pointer-table form, GateUpGELUQ4KByWorkPtrsToBuffer, takes separate
- * matrices; stack them at upload to use this call.)  Upload a matrix that serves the work-list
- * calls with "gguf_layout" = 1: in the streaming layout an expert's rows are read once per four of
- * its items (lists of up to 1024 items), in the tensor-core layout once per item. */
+ * matrices; stack them at upload to use this call.)  An expert's rows are read once per
+ * four of its items (lists of up to 1024 items, in_dim a multiple of 256; else once per item). */
 int goph_gguf_gate_up_gelu_by_work(float* out_dev, uint64_t out_len, const float* x_dev, uint64_t x_len,
                                    const uint32_t* work_experts_dev, int work_len, int intermediate, int active_experts,
                                    const goph_gguf_matrix* m, void* stream);
