@@ -26,6 +26,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
@@ -82,10 +83,15 @@ struct goph_moe_layer {
   float* mxtab;                    // [max_entries] their sums and scales
   float* gu;                       // [max_entries * 2][2][inter] gate and up results (entries of two or four items: the first holds more entries)
   // one token, row-major experts: the whole call as one cooperative launch
-  unsigned* bar;                   // [0] barrier counter (only grows), [1] its value when the next launch starts
+  unsigned* bar;                   // [0] barrier counter (only grows), [1] its value when the next launch starts, [2] set when a wait gave up
   int token_grid;                  // CTAs of that launch (0 = not asked yet, -1 = does not fit)
   size_t token_smem;
 };
+
+// The layers alive on each device: clearing the device's status also resets their barrier words.
+static std::mutex g_layers_mu;
+static std::vector<goph_moe_layer*> g_layers;
+
 
 namespace goph {
 
@@ -753,9 +759,12 @@ moe_token_kernel(MoeTables tb, const uint4* __restrict__ rw, const void* __restr
   const int tid = threadIdx.x;
   if (tid == 0) {
     s_base = *reinterpret_cast<volatile unsigned*>(bar + 1);
-    s_abort = 0;
+    // a launch whose wait gave up leaves the counter between two launches' values: every later
+    // launch returns at once (status already set) until goph_kernel_status_clear resets the words
+    s_abort = *reinterpret_cast<volatile unsigned*>(bar + 2) != 0u;
   }
   __syncthreads();
+  if (s_abort) return;
   int nbar = 0;
   auto grid_barrier = [&]() {
     __syncthreads();
@@ -771,6 +780,7 @@ moe_token_kernel(MoeTables tb, const uint4* __restrict__ rw, const void* __restr
         if (clock64() - t0 > kMoeBarrierTimeoutCycles) {
           s_abort = 1;
           atomicExch(status, 700 + nbar);
+          atomicExch(bar + 2, 1u);
           break;
         }
       }
@@ -921,8 +931,8 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
   if (e == cudaSuccess) e = cudaMalloc(&m->wts, (size_t)max_tokens * top_k * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->act, (size_t)max_tokens * top_k * inter * sizeof(float));
   if (e == cudaSuccess) e = cudaMalloc(&m->dpart, (size_t)max_tokens * top_k * hidden * sizeof(float));
-  if (e == cudaSuccess) e = cudaMalloc(&m->bar, 2 * sizeof(unsigned));
-  if (e == cudaSuccess) e = cudaMemset(m->bar, 0, 2 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMalloc(&m->bar, 4 * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemset(m->bar, 0, 4 * sizeof(unsigned));
   if (e == cudaSuccess) e = cudaMalloc(&m->lists, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(m->lists, 0, 4 * sizeof(int));
   if (e == cudaSuccess) e = cudaMalloc(&m->work, (size_t)num_experts * sizeof(goph::MoeWork));
@@ -933,6 +943,10 @@ GOPH_API int goph_moe_create(int device, int num_experts, int hidden, int inter,
     return rc;
   }
   m->tables_dirty = 1;
+  {
+    std::lock_guard<std::mutex> lock(g_layers_mu);
+    g_layers.push_back(m);
+  }
   *out = m;
   return GOPH_OK;
 }
@@ -1042,6 +1056,14 @@ GOPH_API int goph_moe_free(goph_moe_layer* m) {
   cudaFree(m->lists);
   cudaFree(m->work);
   cudaFree(m->items);
+  {
+    std::lock_guard<std::mutex> lock(g_layers_mu);
+    for (size_t i = 0; i < g_layers.size(); ++i)
+      if (g_layers[i] == m) {
+        g_layers.erase(g_layers.begin() + i);
+        break;
+      }
+  }
   cudaFree(m->bar);
   cudaFree(m->mwork);
   cudaFree(m->mxb);
@@ -1083,6 +1105,9 @@ int moe_status(int device) {
 void moe_status_clear(int device) {
   int* p = moe_status_word(device);
   if (p) cudaMemset(p, 0, sizeof(int));
+  std::lock_guard<std::mutex> lock(g_layers_mu);
+  for (goph_moe_layer* m : g_layers)
+    if (m->device == device) cudaMemset(m->bar, 0, 4 * sizeof(unsigned));
 }
 }  // namespace goph
 
