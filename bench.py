@@ -423,51 +423,63 @@ def moe_sharded(rt, syn, sharding, exchange, rank, world, dist):
     import torch
     experts, hidden, inter, top_k = 128, 2048, 768, 8
     g = syn.rng("moe-sharded")
-    rt.SetOption("mlx_layout", 1)
-    mods, keep = [], []
-    for l in range(2):
-        m = rt.GPUMoELayer(experts, hidden, inter, 64, top_k, True, 32)
-        r = rt.UploadMLXWeight(*syn.mlx_weight(("r", l), experts, hidden, 64), hidden, experts, 64, True)
-        m.SetRouter(r)
-        keep.append(r)
-        gen = syn.rng("moe-sharded", l)
-        for e in range(experts):
-            arrs = []
-            for o, i in ((inter, hidden), (inter, hidden), (hidden, inter)):
-                w = gen.integers(0, 2**32, size=o * i // 8, dtype=np.uint32)
-                sc = syn.bf16_round(np.abs(gen.standard_normal(o * i // 64, dtype=np.float32)) * np.float32(0.02) + np.float32(1e-3))
-                arrs.append((w, sc, syn.bf16_round(np.float32(-8) * sc), i, o))
-            if e in sharding.place_experts(experts, rank, world):
-                hs = [rt.UploadMLXWeight(w, sc, bi, i, o, 64, True) for w, sc, bi, i, o in arrs]
-                m.SetExpert(e, *hs)
-                keep += hs
-        mods.append(m)
-    rt.SetOption("mlx_layout", 0)
+
+    def build(expert_layout):
+        mods = []
+        for l in range(2):
+            m = rt.GPUMoELayer(experts, hidden, inter, 64, top_k, True, 32)
+            rt.SetOption("mlx_layout", 1)
+            r = rt.UploadMLXWeight(*syn.mlx_weight(("r", l), experts, hidden, 64), hidden, experts, 64, True)
+            m.SetRouter(r)
+            keep.append(r)
+            gen = syn.rng("moe-sharded", l)
+            rt.SetOption("mlx_layout", expert_layout)
+            for e in range(experts):
+                arrs = []
+                for o, i in ((inter, hidden), (inter, hidden), (hidden, inter)):
+                    w = gen.integers(0, 2**32, size=o * i // 8, dtype=np.uint32)
+                    sc = syn.bf16_round(np.abs(gen.standard_normal(o * i // 64, dtype=np.float32)) * np.float32(0.02) + np.float32(1e-3))
+                    arrs.append((w, sc, syn.bf16_round(np.float32(-8) * sc), i, o))
+                if e in sharding.place_experts(experts, rank, world):
+                    hs = [rt.UploadMLXWeight(w, sc, bi, i, o, 64, True) for w, sc, bi, i, o in arrs]
+                    m.SetExpert(e, *hs)
+                    keep.extend(hs)
+            mods.append(m)
+        rt.SetOption("mlx_layout", 0)
+        return mods
+
+    keep = []
+    # experts row-major (CUDA-core kernels; one launch at one token) and tiled (grouped tensor-core launches)
+    forms = {"row_major_experts": build(1), "tiled_experts": build(2)}
     res = {}
     for tokens in (1, 8, 32):
         x = torch.from_numpy(syn.activations(("moe-sharded", tokens), tokens * hidden)).cuda()
         out = torch.empty(tokens * hidden, dtype=torch.float32, device="cuda")
         xb, ob = rt.wrap(x.data_ptr(), x.numel() * 4), rt.wrap(out.data_ptr(), out.numel() * 4)
-        for m in mods:
-            exchange.MoEForward(m, ob, xb, tokens, torch.cuda.current_stream())
-        torch.cuda.synchronize()
-        side = torch.cuda.Stream()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(20):
-                exchange.MoEForward(mods[i % 2], ob, xb, tokens, torch.cuda.current_stream())
-        graph.replay()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(3):
+        entry = {"experts_per_gpu": experts // world}
+        for name, mods in forms.items():
+            for m in mods:
+                exchange.MoEForward(m, ob, xb, tokens, torch.cuda.current_stream())
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(20):
+                    exchange.MoEForward(mods[i % 2], ob, xb, tokens, torch.cuda.current_stream())
             graph.replay()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / 60 * 1e3], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        res["T=%d" % tokens] = {"us_per_call": round(float(t.cpu()[0]), 2), "experts_per_gpu": experts // world}
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b) / 60 * 1e3], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            entry["us_per_call_" + name] = round(float(t.cpu()[0]), 2)
+        entry["us_per_call"] = min(entry["us_per_call_row_major_experts"], entry["us_per_call_tiled_experts"])
+        res["T=%d" % tokens] = entry
     return res
 
 
