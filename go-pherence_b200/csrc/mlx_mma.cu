@@ -1343,16 +1343,15 @@ moe_mma_prep_kernel(const MmaGroupEntry* __restrict__ work, const int* __restric
         v[h] = __fmul_rn(__fdiv_rn(gv, __fadd_rn(1.0f, expf(-gv))), uv);
       }
     }
-    float s = v[0] + v[1], mx = fmaxf(fabsf(v[0]), fabsf(v[1]));
     // the order of mlx_prep_x_kernel: each half's butterfly, then the halves
-    float s0 = v[0], s1 = v[1];
+    float s0 = v[0], s1 = v[1], mx = fmaxf(fabsf(v[0]), fabsf(v[1]));
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       s0 += __shfl_xor_sync(0xffffffffu, s0, o);
       s1 += __shfl_xor_sync(0xffffffffu, s1, o);
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     }
-    s = s0 + s1;
+    const float s = s0 + s1;
     int e = (int)((__float_as_uint(mx) >> 23) & 0xFF);
     if (e < QBITS + 2) e = QBITS + 2;
     if (e > 254) e = 254;
