@@ -185,11 +185,12 @@ def test_routing_from_logits_is_exact(gpu, pkg, norm):
     L.free()
 
 
-def test_failed_softmax_runs_no_expert(gpu, pkg):
+@pytest.mark.parametrize("layout", [1, 2])
+def test_failed_softmax_runs_no_expert(gpu, pkg, layout):
     # simd.SoftmaxInPlace reports failure on a NaN/Inf sum and moeForward then adds nothing
     # (backends/simd/runtime/softmax.go:20-24; model/moe.go:230-233)
-    experts, hidden, inter = 8, 256, 128
-    L = Layer(gpu, pkg.synth, "nan", experts, hidden, inter, 64, 2, True)
+    experts, hidden, inter = 8, 256, 256
+    L = Layer(gpu, pkg.synth, "nan", experts, hidden, inter, 64, 2, True, layout=layout)
     logits = np.zeros((2, experts), dtype=F)
     logits[0, 3] = np.nan
     logits[1, 2] = 1.0
@@ -199,6 +200,16 @@ def test_failed_softmax_runs_no_expert(gpu, pkg):
     want_ids, want_w = orc.moe_route(logits[1], 2, True)
     assert list(ids[1]) == list(want_ids)
     assert pkg.synth.rel_err(got[1], L.oracle(x[1], want_ids, want_w)) <= TOL
+    # every token fails: no work entry at all, the output is zero
+    logits[1, 5] = np.inf
+    got, ids, _ = run_forward(L, x, 2, logits)
+    assert np.all(ids == -1) and np.all(got == 0)
+    # and the layer still works afterwards
+    logits[:] = 0
+    logits[0, 1] = logits[1, 6] = 2.0
+    got, ids, wts = run_forward(L, x, 2, logits)
+    for t in range(2):
+        assert pkg.synth.rel_err(got[t], L.oracle(x[t], ids[t], wts[t])) <= TOL
     L.free()
 
 
