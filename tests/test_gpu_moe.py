@@ -141,6 +141,20 @@ def test_forward_parity_tiled_experts(gpu, pkg, experts, hidden, inter, top_k, n
     L.free()
 
 
+@pytest.mark.parametrize("layout", [1, 2])
+def test_many_tokens_per_call(gpu, pkg, layout):
+    # 96 tokens on 16 experts with top-4: 24 items per expert on average (tiled: six work entries each)
+    experts, hidden, inter, top_k, tokens = 16, 512, 256, 4, 96
+    L = Layer(gpu, pkg.synth, "many", experts, hidden, inter, 64, top_k, True, max_tokens=tokens, layout=layout)
+    x = pkg.synth.activations(("many", tokens), tokens * hidden).reshape(tokens, hidden)
+    got, ids, wts = run_forward(L, x, tokens)
+    for t in range(0, tokens, 7):
+        assert pkg.synth.rel_err(got[t], L.oracle(x[t], ids[t], wts[t])) <= TOL, t
+    one, _, _ = run_forward(L, x[50:51].copy(), 1)
+    assert np.array_equal(one[0].view(np.uint32), got[50].view(np.uint32))
+    L.free()
+
+
 def test_tiled_expert_placement_and_layout_rules(gpu, pkg):
     experts, hidden, inter, top_k, tokens = 32, 512, 256, 8, 4
     full = Layer(gpu, pkg.synth, "place", experts, hidden, inter, 64, top_k, True, layout=2)
