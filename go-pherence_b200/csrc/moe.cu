@@ -30,6 +30,7 @@
 
 #include "goph_internal.cuh"
 #include "mlx_mma.cuh"
+#include "tc_common.cuh"
 
 namespace goph {
 
@@ -378,16 +379,36 @@ __device__ __forceinline__ void moe_route_token(const float* __restrict__ lg, in
   }
 }
 
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, int norm_topk, int tokens,
-                 int max_tokens, MoeTables tb, int* __restrict__ ids, float* __restrict__ wts,
-                 int* __restrict__ lists, MoeWork* __restrict__ work, int* __restrict__ items,
-                 MmaGroupEntry* __restrict__ mwork, int max_entries, int entry_rows) {
+struct MoeRouteArgs {
+  const float* logits;
+  int num_experts, top_k, norm_topk, tokens, max_tokens;
+  MoeTables tb;
+  int* ids;
+  float* wts;
+  int* lists;
+  MoeWork* work;
+  int* items;
+  MmaGroupEntry* mwork;
+  int max_entries, entry_rows;
+};
+
+// Token t's routing by the calling CTA; the CTA that finishes the call's last token then groups the
+// (token, slot) items by expert into the work lists.
+__device__ __forceinline__ void moe_route_body(const MoeRouteArgs& ra, int t) {
   __shared__ MoeRouteShared sh;
   __shared__ int s_cnt[kMoeMaxExperts];
   __shared__ int s_last, s_n, s_m;
-  pdl_prologue();
-  const int t = blockIdx.x, tid = threadIdx.x;
+  const float* logits = ra.logits;
+  const int num_experts = ra.num_experts, top_k = ra.top_k, norm_topk = ra.norm_topk, tokens = ra.tokens;
+  const int max_tokens = ra.max_tokens, max_entries = ra.max_entries, entry_rows = ra.entry_rows;
+  const MoeTables& tb = ra.tb;
+  int* ids = ra.ids;
+  float* wts = ra.wts;
+  int* lists = ra.lists;
+  MoeWork* work = ra.work;
+  int* items = ra.items;
+  MmaGroupEntry* mwork = ra.mwork;
+  const int tid = threadIdx.x;
   moe_route_token(logits + (size_t)t * num_experts, num_experts, top_k, norm_topk, ids + (size_t)t * top_k,
                   wts + (size_t)t * top_k, sh);
   if (tid == 0) {
@@ -449,6 +470,30 @@ moe_route_kernel(const float* __restrict__ logits, int num_experts, int top_k, i
     lists[2] = min(s_m, max_entries);
     lists[0] = 0;  // ready for the next call
   }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const __grid_constant__ MoeRouteArgs ra) {
+  pdl_prologue();
+  moe_route_body(ra, blockIdx.x);
+}
+
+// Router rows and routing in one launch: the CTAs of a token (one per block of 16 experts, at most 8)
+// form a thread-block cluster; each computes its experts' logits, the cluster meets (which orders
+// the logits it wrote), and its first CTA routes the token.
+template <bool SB_BF16>
+__global__ void __launch_bounds__(kMoeThreads)
+moe_router_route_kernel(const uint4* __restrict__ w, const void* __restrict__ sb, const float* __restrict__ x,
+                        float* __restrict__ logits, int hidden, int ug_shift, int groups, int cs,
+                        const __grid_constant__ MoeRouteArgs ra) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int t = blockIdx.x / cs, rank = blockIdx.x - t * cs;
+  moe_router_block<SB_BF16>(w, sb, x, logits, ra.num_experts, hidden, ug_shift, groups, rank, t, smem_raw,
+                            [] { asm volatile("griddepcontrol.wait;" ::: "memory"); });
+  tc::cluster_sync_all();
+  if (rank != 0) return;
+  moe_route_body(ra, t);
 }
 
 // Sums N values over the warp with N-1 + 5-log2(N) shuffles: at each of the first log2(N) butterfly
@@ -1175,20 +1220,46 @@ static int moe_run_token(goph_moe_layer* m, MoeTokenKernel kern, float* out_dev,
 }
 
 // Launches 2-5 for routing given as logits already on the device.
-static int moe_run(goph_moe_layer* m, float* out_dev, const float* x_dev, const float* logits_dev, int tokens,
-                   cudaStream_t s) {
-  if (int rc = moe_upload_tables(m)) return rc;
-  const int sms = device_state(m->device).sm_count;
+static int moe_entry_rows(const goph_moe_layer* m, int tokens) {
   // Tiled experts: items per work entry.  Two keep the narrow, faster form of the tensor-core kernel
   // (8 accumulator columns); from two items per expert on average entries of four, which read most
   // experts once, are faster (128 experts, top-8: 8 tokens 70.7 against 76.1 us, 32 tokens 133.8 against
   // 129.3 us).  Option moe_rows (2 or 4) overrides.
   int entry_rows = tokens * m->top_k < 2 * m->num_experts ? 2 : 4;
   if (options().moe_rows == 2 || options().moe_rows == 4) entry_rows = options().moe_rows;
-  if (int rc = moe_launch(moe_route_kernel, dim3(tokens), 128, 0, s, logits_dev, m->num_experts, m->top_k, m->norm_topk, tokens,
-                          m->max_tokens, m->dev, m->ids, m->wts, m->lists, m->work, m->items, m->tiled == 1 ? m->mwork : nullptr,
-                          m->max_entries, entry_rows))
-    return rc;
+  return entry_rows;
+}
+
+static MoeRouteArgs moe_route_args(goph_moe_layer* m, const float* logits_dev, int tokens) {
+  MoeRouteArgs ra;
+  memset(&ra, 0, sizeof ra);
+  ra.logits = logits_dev;
+  ra.num_experts = m->num_experts;
+  ra.top_k = m->top_k;
+  ra.norm_topk = m->norm_topk;
+  ra.tokens = tokens;
+  ra.max_tokens = m->max_tokens;
+  ra.tb = m->dev;
+  ra.ids = m->ids;
+  ra.wts = m->wts;
+  ra.lists = m->lists;
+  ra.work = m->work;
+  ra.items = m->items;
+  ra.mwork = m->tiled == 1 ? m->mwork : nullptr;
+  ra.max_entries = m->max_entries;
+  ra.entry_rows = moe_entry_rows(m, tokens);
+  return ra;
+}
+
+// routed: the routing kernel has already been launched (together with the router rows)
+static int moe_run(goph_moe_layer* m, float* out_dev, const float* x_dev, const float* logits_dev, int tokens,
+                   cudaStream_t s, bool routed = false) {
+  if (int rc = moe_upload_tables(m)) return rc;
+  const int sms = device_state(m->device).sm_count;
+  const int entry_rows = moe_entry_rows(m, tokens);
+  if (!routed) {
+    if (int rc = moe_launch(moe_route_kernel, dim3(tokens), 128, 0, s, moe_route_args(m, logits_dev, tokens))) return rc;
+  }
   if (m->tiled == 1) {
     // tiled experts: gate and up of every entry in one grouped launch of the tensor-core kernel, then
     // down (each launch preceded by the kernel that writes the entries' activations as digits)
@@ -1276,6 +1347,32 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
     const int iters = (m->hidden / 32 + 31) / 32;
     const size_t smem = (size_t)iters * (256 * 16 + 32 * 8);
     if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: hidden=%d does not fit shared memory", m->hidden);
+    const int cs = (m->num_experts + 2 * kMoeWarps - 1) / (2 * kMoeWarps);  // CTAs of a token: one per 16 experts
+    if (cs <= 8 && options().moe_fused) {
+      // router rows and routing in one launch: the CTAs of a token form a thread-block cluster
+      if (int rc = moe_upload_tables(m)) return rc;
+      auto kr = rw->sb_bf16 ? moe_router_route_kernel<true> : moe_router_route_kernel<false>;
+      GOPH_CUDA(cudaFuncSetAttribute(kr, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = options().pdl ? 1 : 0;
+      attr[1].id = cudaLaunchAttributeClusterDimension;
+      attr[1].val.clusterDim.x = cs;
+      attr[1].val.clusterDim.y = 1;
+      attr[1].val.clusterDim.z = 1;
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof cfg);
+      cfg.gridDim = dim3(cs * tokens);
+      cfg.blockDim = dim3(kMoeThreads);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = (cudaStream_t)stream;
+      cfg.attrs = attr;
+      cfg.numAttrs = cs > 1 ? 2 : 1;
+      note_launch();
+      GOPH_CUDA(cudaLaunchKernelEx(&cfg, kr, reinterpret_cast<const uint4*>(rw->qweight), (const void*)rw->sb, x_dev, m->logits,
+                                   m->hidden, sh, m->hidden / rw->group_size, cs, moe_route_args(m, m->logits, tokens)));
+      return moe_run(m, out_dev, x_dev, m->logits, tokens, (cudaStream_t)stream, true);
+    }
     auto k = rw->sb_bf16 ? moe_router_kernel<true> : moe_router_kernel<false>;
     GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (int rc = moe_launch(k, dim3((m->num_experts + 2 * kMoeWarps - 1) / (2 * kMoeWarps), tokens), kMoeThreads, smem,

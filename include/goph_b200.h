@@ -117,7 +117,8 @@ int goph_sm_count(int device);
  *                 and an atomic counter.  Same bits either way
  *   "moe_fused"   1 (default): an MoE call of one token on row-major experts runs as ONE cooperative
  *                 launch (router, routing, gate|up, down and the weighted sum as phases between
- *                 grid-wide barriers); 0: the launches that serve any number of tokens.  Same bits.
+ *                 grid-wide barriers), and with more tokens the router rows and the routing share a
+ *                 launch; 0: one launch per step of the call, for any number of tokens.  Same bits.
  *                 A barrier wait that gives up (about a second) sets the kernel status to 700 + the
  *                 barrier's number; the layer's later one-launch calls then return without
  *                 computing until goph_kernel_status_clear has been called
