@@ -478,7 +478,7 @@ def main():
         return
     if args.format == "moe":
         print(json.dumps(run_moe(args.tokens, opts=opts, expert_layout=args.expert_layout, eager=args.eager,
-                                 launches=min(args.launches, 40))))
+                                 launches=min(args.launches, 40), layers=2 if args.eager else 4)))
         return
     print(json.dumps(run(args.format, args.out, args.in_dim, args.batch, args.launches, args.copies, opts, chain=args.chain, xbf16=args.xbf16)))
 
