@@ -9,17 +9,23 @@
 //   strict-'>' argmax, optional renormalisation; for every selected expert in selection order
 //   h = silu(gate . x) * (up . x), d = down . h, out += weight * d.
 //
-// Five launches per call, whatever the number of tokens; nothing returns to the host:
-//   1. router logits     — the MLX GEMV/GEMM kernel (batch = tokens)
-//   2. moe_route_kernel  — one warp per token does the softmax/top-k in the reference's order; the
+// The steps of a call, whatever the number of tokens; nothing returns to the host:
+//   1. router logits     — moe_router_kernel, or the MLX GEMM kernel for a router in the tiled layout
+//   2. moe_route_kernel  — one CTA per token does the softmax/top-k in the reference's order; the
 //      last CTA to finish then groups the (token, slot) items by expert: the list of experts that
-//      were selected at all and, per expert, its items in (token, slot) order
-//   3. moe_gate_up_kernel — grid (row blocks, selected experts): a warp streams row r of the
-//      expert's gate and up matrices ONCE and applies it to up to four of the expert's tokens at a
-//      time (their x staged in shared memory), writing silu(g) * u per item
-//   4. moe_down_kernel   — same grouping for the down matrices, writing one vector per item
+//      were selected at all and, per expert, its items; for experts in the tiled layout also work
+//      entries of up to 2 or 4 items.  (1 and 2 are one launch, moe_router_route_kernel, for a
+//      row-major router of up to 128 experts.)
+//   3. gate and up — row-major experts: moe_expert_kernel<phase 0>, grid (row blocks, selected
+//      experts): a warp streams row r of the expert's gate and up matrices ONCE and applies it to up
+//      to four of the expert's tokens at a time (their x staged in shared memory), writing
+//      silu(g) * u per item.  Tiled experts: the entries' activations as digits
+//      (moe_mma_prep_kernel), then one grouped launch of the tensor-core GEMV kernel over the
+//      (entry, matrix, 128-row tile) items (mlx_mma.cu)
+//   4. down — the same two forms, writing one vector per item
 //   5. moe_combine_kernel — out[t] = sum over the token's slots, in selection order, of
 //      weight * vector, so the result does not depend on scheduling.
+// One token on row-major experts: all five steps as phases of one cooperative launch (moe_token_kernel).
 // Each expert matrix is read from HBM once per call however many tokens chose the expert.
 // Experts that are not resident on this GPU (multi-GPU placement) are skipped: the output is then
 // this GPU's partial sum.
