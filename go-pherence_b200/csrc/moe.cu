@@ -1196,8 +1196,11 @@ static bool moe_token_form(goph_moe_layer* m, const goph_mlx_weight* rw, MoeToke
   return true;
 }
 
+// *declined: the launch was refused for lack of co-residency and nothing ran; the caller goes on with
+// the other form.
 static int moe_run_token(goph_moe_layer* m, MoeTokenKernel kern, float* out_dev, const float* x_dev, const goph_mlx_weight* rw,
-                         const float* logits_dev, cudaStream_t s) {
+                         const float* logits_dev, cudaStream_t s, bool* declined) {
+  *declined = false;
   if (int rc = moe_upload_tables(m)) return rc;
   int* status = moe_status_word(m->device);
   if (!status) return fail(GOPH_E_NOMEM, "cannot allocate the MoE kernels' status word");
@@ -1217,11 +1220,21 @@ static int moe_run_token(goph_moe_layer* m, MoeTokenKernel kern, float* out_dev,
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   GOPH_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)m->token_smem));
+  const cudaError_t e =
+      cudaLaunchKernelEx(&cfg, kern, m->dev, rw ? reinterpret_cast<const uint4*>(rw->qweight) : (const uint4*)nullptr,
+                         rw ? (const void*)rw->sb : (const void*)nullptr, rsh, rw ? m->hidden / rw->group_size : 0, x_dev,
+                         logits_dev, m->logits, m->ids, m->wts, m->act, m->dpart, out_dev, m->bar, status, m->num_experts,
+                         m->hidden, m->inter, m->top_k, m->norm_topk, sh, m->group_size);
+  if (e == cudaErrorCooperativeLaunchTooLarge) {
+    // the device cannot hold the grid at once (it is shared, or partitioned): this layer keeps to the
+    // launches that need no co-residency from now on
+    cudaGetLastError();
+    m->token_grid = -1;
+    *declined = true;
+    return GOPH_OK;
+  }
+  if (e != cudaSuccess) return fail_cuda(e, "moe_token_kernel launch");
   note_launch();
-  GOPH_CUDA(cudaLaunchKernelEx(&cfg, kern, m->dev, rw ? reinterpret_cast<const uint4*>(rw->qweight) : (const uint4*)nullptr,
-                               rw ? (const void*)rw->sb : (const void*)nullptr, rsh, rw ? m->hidden / rw->group_size : 0, x_dev,
-                               logits_dev, m->logits, m->ids, m->wts, m->act, m->dpart, out_dev, m->bar, status, m->num_experts,
-                               m->hidden, m->inter, m->top_k, m->norm_topk, sh, m->group_size));
   return GOPH_OK;
 }
 
@@ -1345,7 +1358,11 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
   if (int rc = use_device(m->device)) return rc;
   const goph_mlx_weight* rw = m->router;
   MoeTokenKernel tk = nullptr;
-  if (tokens == 1 && moe_token_form(m, rw, &tk)) return moe_run_token(m, tk, out_dev, x_dev, rw, nullptr, (cudaStream_t)stream);
+  if (tokens == 1 && moe_token_form(m, rw, &tk)) {
+    bool declined = false;
+    const int rc = moe_run_token(m, tk, out_dev, x_dev, rw, nullptr, (cudaStream_t)stream, &declined);
+    if (rc || !declined) return rc;
+  }
   if (rw->qweight && rw->sb && rw->group_size >= 32 && !(rw->group_size & (rw->group_size - 1)) && rw->in_dim % 32 == 0) {
     // row-major router (the usual case: it is small): one launch for all tokens
     int sh = 0;
@@ -1399,7 +1416,11 @@ GOPH_API int goph_moe_forward_logits(goph_moe_layer* m, float* out_dev, uint64_t
   if (!logits_dev || logits_len < (uint64_t)tokens * m->num_experts) return fail(GOPH_E_INVALID, "router logits buffer too short");
   if (int rc = use_device(m->device)) return rc;
   MoeTokenKernel tk = nullptr;
-  if (tokens == 1 && moe_token_form(m, nullptr, &tk)) return moe_run_token(m, tk, out_dev, x_dev, nullptr, logits_dev, (cudaStream_t)stream);
+  if (tokens == 1 && moe_token_form(m, nullptr, &tk)) {
+    bool declined = false;
+    const int rc = moe_run_token(m, tk, out_dev, x_dev, nullptr, logits_dev, (cudaStream_t)stream, &declined);
+    if (rc || !declined) return rc;
+  }
   return moe_run(m, out_dev, x_dev, logits_dev, tokens, (cudaStream_t)stream);
 }
 
