@@ -92,6 +92,7 @@ struct goph_moe_layer {
   // one token, row-major experts: the whole call as one cooperative launch
   unsigned* bar;                   // [0] barrier counter (only grows), [1] its value when the next launch starts, [2] set when a wait gave up
   int token_grid;                  // CTAs of that launch (0 = not asked yet, -1 = does not fit)
+  int no_router_cluster;           // set when the device refused the router + routing cluster launch
   size_t token_smem;
 };
 
@@ -1371,7 +1372,7 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
     const size_t smem = (size_t)iters * (256 * 16 + 32 * 8);
     if (smem > (size_t)kSmemBudget) return fail(GOPH_E_UNSUPPORTED, "MoE: hidden=%d does not fit shared memory", m->hidden);
     const int cs = (m->num_experts + 2 * kMoeWarps - 1) / (2 * kMoeWarps);  // CTAs of a token: one per 16 experts
-    if (cs <= 8 && options().moe_fused) {
+    if (cs <= 8 && options().moe_fused && !m->no_router_cluster) {
       // router rows and routing in one launch: the CTAs of a token form a thread-block cluster
       if (int rc = moe_upload_tables(m)) return rc;
       auto kr = rw->sb_bf16 ? moe_router_route_kernel<true> : moe_router_route_kernel<false>;
@@ -1391,10 +1392,16 @@ GOPH_API int goph_moe_forward(goph_moe_layer* m, float* out_dev, uint64_t out_le
       cfg.stream = (cudaStream_t)stream;
       cfg.attrs = attr;
       cfg.numAttrs = cs > 1 ? 2 : 1;
-      note_launch();
-      GOPH_CUDA(cudaLaunchKernelEx(&cfg, kr, reinterpret_cast<const uint4*>(rw->qweight), (const void*)rw->sb, x_dev, m->logits,
-                                   m->hidden, sh, m->hidden / rw->group_size, cs, moe_route_args(m, m->logits, tokens)));
-      return moe_run(m, out_dev, x_dev, m->logits, tokens, (cudaStream_t)stream, true);
+      const cudaError_t e = cudaLaunchKernelEx(&cfg, kr, reinterpret_cast<const uint4*>(rw->qweight), (const void*)rw->sb, x_dev,
+                                               m->logits, m->hidden, sh, m->hidden / rw->group_size, cs,
+                                               moe_route_args(m, m->logits, tokens));
+      if (e == cudaSuccess) {
+        note_launch();
+        return moe_run(m, out_dev, x_dev, m->logits, tokens, (cudaStream_t)stream, true);
+      }
+      // a device that does not take the cluster: the two launches below, for this layer from now on
+      cudaGetLastError();
+      m->no_router_cluster = 1;
     }
     auto k = rw->sb_bf16 ? moe_router_kernel<true> : moe_router_kernel<false>;
     GOPH_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
